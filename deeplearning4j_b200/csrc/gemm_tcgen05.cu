@@ -1,0 +1,403 @@
+// bf16/fp16 GEMM on the 5th-generation tensor cores: D = act(A·B + bias) (+ residual).
+//
+// Replaces the reference's cuBLAS call sites and naive SIMT fallbacks
+// (libnd4j/include/helpers/cuda/MmulHelper.cu:41-129 usualCudaGemm, :501-517 cublas*gemm) and the
+// matmul+addBias+activation sequences of xw_plus_b / relu_layer / DenseLayer.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      : TMA producer  - cp.async.bulk.tensor tiles of A and B into a multi-stage smem ring
+//   warp 1      : MMA issuer    - one elected lane issues tcgen05.mma (128 x BLOCK_N x 16), accumulators
+//                                 live in TMEM, double-buffered (2 x BLOCK_N columns) so the epilogue of
+//                                 tile i overlaps the main loop of tile i+1
+//   warps 2..5  : epilogue      - tcgen05.ld 32 lanes x 32 columns, bias / activation / residual,
+//                                 16-byte global stores (or fp32 vector reductions for split-K)
+// Operands may be K-major (reduction dimension contiguous) or MN-major (output dimension contiguous),
+// which covers forward (X·Wᵀ), data-gradient (dY·W) and weight-gradient (dYᵀ·X) without transposes.
+#include "common.cuh"
+
+namespace dl4j {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;         // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  long ldc;               // elements
+  long ld_aux, ld_res;
+  void* C;
+  void* aux;              // optional pre-activation output (same dtype as inputs)
+  const void* bias;       // optional [N], dtype bias_fp32 ? float : input dtype
+  const void* residual;   // optional [M, N] input dtype
+  int bias_fp32;
+  int out_fp32;           // C is float
+  int act;                // 0 none, 1 relu, 2 gelu(erf), 3 gelu(tanh), 4 sigmoid, 5 tanh
+  int atomic_out;         // accumulate into fp32 C with vector reductions (split-K / grad accumulation)
+  int splits;             // split-K factor (>1 requires atomic_out)
+  int fmt;                // 0 fp16, 1 bf16
+  float alpha;
+  int* status;
+};
+
+template <int BLOCK_N, bool A_MN, bool B_MN>
+struct GemmSmem {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case 1: return fmaxf(v, 0.0f);
+    case 2: return gelu_erf(v);
+    case 3: return gelu_tanh(v);
+    case 4: return sigmoidf_(v);
+    case 5: return tanhf(v);
+    default: return v;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
+  if (fmt == 1) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float unpack_lo(uint32_t u, int fmt) {
+  if (fmt == 1) return __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&u));
+  return __half2float(*reinterpret_cast<__half*>(&u));
+}
+__device__ __forceinline__ float unpack_hi(uint32_t u, int fmt) {
+  uint32_t h = u >> 16;
+  if (fmt == 1) return __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&h));
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+  using S = GemmSmem<BLOCK_N, A_MN, B_MN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
+  const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int kb_total = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int kb_per_split = (kb_total + p.splits - 1) / p.splits;
+  const int num_work = tiles_m * tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);   // one arrive per epilogue warp
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BLOCK_N);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int tile = w / p.splits, split = w % p.splits;
+        const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, kb_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BLOCK_M / 64; ++i)
+              tma_load_2d(sa + i * (64 * BLOCK_K * 2), &tmap_a, &full_bar[stage], m0 + i * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BLOCK_N / 64; ++i)
+              tma_load_2d(sb + i * (64 * BLOCK_K * 2), &tmap_b, &full_bar[stage], n0 + i * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(p.fmt, A_MN ? 1 : 0, B_MN ? 1 : 0, BLOCK_M, BLOCK_N);
+      // K-major: 8-row groups are 1024 B apart (SBO); MN-major: 64-element column blocks are one
+      // TMA box apart (LBO = 64 rows x 128 B) and 8-row K groups 1024 B apart (SBO).
+      constexpr uint32_t LBO_A = A_MN ? 64 * BLOCK_K * 2 : 16, LBO_B = B_MN ? 64 * BLOCK_K * 2 : 16;
+      constexpr uint32_t KSTEP_A = A_MN ? UMMA_K * 128 : UMMA_K * 2, KSTEP_B = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
+        const int split = w % p.splits;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, kb_total);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait_bounded(&tmem_empty[buf], acc_phase ^ 1, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+          const uint64_t da = make_smem_desc_sw128(sa, LBO_A, 1024);
+          const uint64_t db = make_smem_desc_sw128(sb, LBO_B, 1024);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            umma_f16(tmem_d, da + ((uint64_t)(k * KSTEP_A) >> 4), db + ((uint64_t)(k * KSTEP_B) >> 4), idesc,
+                     (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);   // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&tmem_full[buf]);       // accumulator ready for the epilogue
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+    int it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
+      const int tile = w / p.splits, split = w % p.splits;
+      const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+      const int kb0 = split * kb_per_split;
+      const bool has_k = kb0 < min(kb0 + kb_per_split, kb_total);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait_bounded(&tmem_full[buf], acc_phase, p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr_row = tmem_base + buf * BLOCK_N + ((uint32_t)(q * 32) << 16);
+      const bool lead_split = split == 0;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N; c += 32) {
+        const int col0 = n0 + c;
+        if (col0 >= p.N) break;             // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(taddr_row + c, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = has_k ? __uint_as_float(r[j]) * p.alpha : 0.0f;
+        const bool full_chunk = col0 + 32 <= p.N;
+        if (p.bias != nullptr && lead_split) {
+          if (p.bias_fp32) {
+            const float* b = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (full_chunk || col0 + j < p.N) v[j] += __ldg(b + j);
+          } else if (p.fmt == 1) {
+            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (full_chunk || col0 + j < p.N) v[j] += __bfloat162float(b[j]);
+          } else {
+            const __half* b = reinterpret_cast<const __half*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (full_chunk || col0 + j < p.N) v[j] += __half2float(b[j]);
+          }
+        }
+        if (row_ok) {
+          if (p.aux != nullptr) {
+            uint16_t* a = reinterpret_cast<uint16_t*>(p.aux) + (long)row * p.ld_aux + col0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 u = make_uint4(pack2(v[j], v[j + 1], p.fmt), pack2(v[j + 2], v[j + 3], p.fmt),
+                                     pack2(v[j + 4], v[j + 5], p.fmt), pack2(v[j + 6], v[j + 7], p.fmt));
+                *reinterpret_cast<uint4*>(a + j) = u;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) a[j] = (uint16_t)(pack2(v[j], 0.f, p.fmt) & 0xffff);
+            }
+          }
+          if (p.act != 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+          }
+          if (p.residual != nullptr && lead_split) {
+            const uint16_t* rs = reinterpret_cast<const uint16_t*>(p.residual) + (long)row * p.ld_res + col0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(rs) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                const uint4 u = *reinterpret_cast<const uint4*>(rs + j);
+                v[j] += unpack_lo(u.x, p.fmt); v[j + 1] += unpack_hi(u.x, p.fmt);
+                v[j + 2] += unpack_lo(u.y, p.fmt); v[j + 3] += unpack_hi(u.y, p.fmt);
+                v[j + 4] += unpack_lo(u.z, p.fmt); v[j + 5] += unpack_hi(u.z, p.fmt);
+                v[j + 6] += unpack_lo(u.w, p.fmt); v[j + 7] += unpack_hi(u.w, p.fmt);
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) v[j] += unpack_lo((uint32_t)rs[j], p.fmt);
+            }
+          }
+          if (p.out_fp32) {
+            float* o = reinterpret_cast<float*>(p.C) + (long)row * p.ldc + col0;
+            const bool al = full_chunk && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
+            if (p.atomic_out) {
+              if (al) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(v[j]), "f"(v[j + 1]),
+                               "f"(v[j + 2]), "f"(v[j + 3]) : "memory");
+              } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd(o + j, v[j]);
+              }
+            } else if (al) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) o[j] = v[j];
+            }
+          } else {
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.C) + (long)row * p.ldc + col0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 u = make_uint4(pack2(v[j], v[j + 1], p.fmt), pack2(v[j + 2], v[j + 3], p.fmt),
+                                     pack2(v[j + 4], v[j + 5], p.fmt), pack2(v[j + 6], v[j + 7], p.fmt));
+                *reinterpret_cast<uint4*>(o + j) = u;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) o[j] = (uint16_t)(pack2(v[j], 0.f, p.fmt) & 0xffff);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BLOCK_N);
+  }
+}
+
+}  // namespace dl4j
+
+// =============================================================================== host side
+using namespace dl4j;
+
+static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                     uint32_t box_inner, uint32_t box_outer) {
+  dl4j_PFN_encodeTiled enc = dl4j_get_encode_tiled();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t es[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  using S = GemmSmem<BLOCK_N, A_MN, B_MN>;
+  static bool attr_set = false;
+  auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+// C[M,N] = act(alpha * A·B + bias) (+ residual)
+//   a_mn = 0: A stored [M, K] (row stride lda);  a_mn = 1: A stored [K, M] (row stride lda)
+//   b_mn = 0: B stored [N, K] (row stride ldb);  b_mn = 1: B stored [K, N] (row stride ldb)
+// Alignment contract (checked): base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
+DL4J_API int dl4j_gemm(const void* A, const void* B, void* C, void* aux, const void* bias, const void* residual, int M,
+                       int N, int K, long lda, long ldb, long ldc, long ld_aux, long ld_res, int a_mn, int b_mn, int fmt,
+                       int bias_fp32, int out_fp32, int act, int atomic_out, int splits, float alpha, int block_n,
+                       int num_sms, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -DL4J_ERR_BAD_ARG;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && !(atomic_out && out_fp32)) return -DL4J_ERR_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ld_aux; p.ld_res = ld_res; p.C = C; p.aux = aux; p.bias = bias;
+  p.residual = residual; p.bias_fp32 = bias_fp32; p.out_fp32 = out_fp32; p.act = act; p.atomic_out = atomic_out;
+  p.splits = splits; p.fmt = fmt; p.alpha = alpha; p.status = dl4j_status_word(dev);
+  if (block_n != 128 && block_n != 256) block_n = 256;
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BLOCK_K, BLOCK_M);
+  else       r = encode_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BLOCK_K);
+  if (r) return r > 0 ? -1000 - r : r;
+  if (!b_mn) r = encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BLOCK_K, (uint32_t)block_n);
+  else       r = encode_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BLOCK_K);
+  if (r) return r > 0 ? -1000 - r : r;
+  const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n) * splits;
+  if (num_sms <= 0) num_sms = 148;
+  const int grid = tiles < num_sms ? tiles : num_sms;
+#define DL4J_GEMM_CASE(BN, AM, BM) \
+  if (block_n == BN && a_mn == AM && b_mn == BM) return launch_gemm<BN, AM != 0, BM != 0>(ta, tb, p, grid, stream);
+  DL4J_GEMM_CASE(256, 0, 0) DL4J_GEMM_CASE(256, 0, 1) DL4J_GEMM_CASE(256, 1, 0) DL4J_GEMM_CASE(256, 1, 1)
+  DL4J_GEMM_CASE(128, 0, 0) DL4J_GEMM_CASE(128, 0, 1) DL4J_GEMM_CASE(128, 1, 0) DL4J_GEMM_CASE(128, 1, 1)
+#undef DL4J_GEMM_CASE
+  return -DL4J_ERR_BAD_ARG;
+}

@@ -1,0 +1,435 @@
+// Memory-bound fused NN kernels: layer norm (fwd/bwd), softmax + cross-entropy (fwd with gradient
+// emission), LSTM cell (fwd/bwd), bias/activation backward with bias-gradient reduction.
+//
+// Reference counterparts: layer_norm = standardize + broadcast mul + addBias
+// (libnd4j/include/ops/declarable/generic/nn/layer_norm.cpp:35-78); softMaxCuda / softmax_cross_entropy
+// (helpers/cuda/activations.cu:303-353, generic/loss/softmaxCrossEntropy*.cpp); lstmCell as NDArray
+// algebra (helpers/cuda/lstm.cu:45-110) and DL4J's LSTMHelpers.java:180-330 gate order [a, f, o, g].
+// Each op reads its operands once from HBM and writes once.
+#include "common.cuh"
+
+namespace dl4j {
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Vec8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <> __device__ __forceinline__ float ldf<__half>(const __half* p) { return __half2float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+template <> __device__ __forceinline__ void stf<__half>(__half* p, float v) { *p = __float2half(v); }
+
+// ----------------------------------------------------------------------------- layer norm
+// One warp per row; C % 8 == 0 and C <= 32 * 8 * LN_MAXV.  Optional residual input: x = x + res is
+// normalised and (when sum_out != null) the sum is also written out for the next residual branch.
+constexpr int LN_MAXV = 4;
+constexpr int LN_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const float* __restrict__ gain,
+                      const float* __restrict__ bias, T* __restrict__ y, T* __restrict__ sum_out,
+                      float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = C / 8;
+  float v[LN_MAXV][8];
+  float s = 0.f;
+  const T* xr = x + (long long)row * C;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      Vec8<T>::load(xr + vi * 8, v[i]);
+      if (res) {
+        float r[8];
+        Vec8<T>::load(res + (long long)row * C + vi * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+        if (sum_out) Vec8<T>::store(sum_out + (long long)row * C + vi * 8, v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+  }
+  const float mean = warp_sum(s) / C;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i)
+    if (lane + i * 32 < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; q += d * d; }
+    }
+  const float rstd = rsqrtf(warp_sum(q) / C + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      float g[8], b[8], o[8];
+      Vec8<float>::load(gain + vi * 8, g);
+      if (bias) Vec8<float>::load(bias + vi * 8, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + (bias ? b[j] : 0.f);
+      Vec8<T>::store(y + (long long)row * C + vi * 8, o);
+    }
+  }
+}
+
+// dx = rstd * (dy*g - mean(dy*g) - xhat * mean(dy*g*xhat));  dgain += dy*xhat;  dbias += dy.
+// Each warp walks rows with a grid stride and keeps its dgain/dbias partials in registers.
+template <typename T>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gain,
+                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+                      float* __restrict__ dgain, float* __restrict__ dbias, int rows, int C) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nvec = C / 8;
+  float ag[LN_MAXV][8], ab[LN_MAXV][8], g[LN_MAXV][8];
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { ag[i][j] = 0.f; ab[i][j] = 0.f; g[i][j] = 0.f; }
+    if (lane + i * 32 < nvec) Vec8<float>::load(gain + (lane + i * 32) * 8, g[i]);
+  }
+  for (int row = blockIdx.x * LN_WARPS + wid; row < rows; row += gridDim.x * LN_WARPS) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[LN_MAXV][8], dg[LN_MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float d[8];
+        Vec8<T>::load(dy + (long long)row * C + vi * 8, d);
+        Vec8<T>::load(x + (long long)row * C + vi * 8, xh[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          ag[i][j] += d[j] * xh[i][j];
+          ab[i][j] += d[j];
+          dg[i][j] = d[j] * g[i][j];
+          s1 += dg[i][j];
+          s2 += dg[i][j] * xh[i][j];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < LN_MAXV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (dg[i][j] - s1 - xh[i][j] * s2);
+        Vec8<T>::store(dx + (long long)row * C + vi * 8, o);
+      }
+    }
+  }
+  // block-level reduction of the partials through shared memory, then one atomic per column per block
+  __shared__ float red[LN_WARPS][32 * 8 + 1];
+  for (int i = 0; i < LN_MAXV; ++i) {
+    for (int pass = 0; pass < 2; ++pass) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) red[wid][lane * 8 + j] = pass == 0 ? ag[i][j] : ab[i][j];
+      __syncthreads();
+      for (int c = threadIdx.x; c < 256; c += LN_WARPS * 32) {
+        const int col = i * 256 + c;
+        if (col < C) {
+          float t = 0.f;
+#pragma unroll
+          for (int w = 0; w < LN_WARPS; ++w) t += red[w][c];
+          float* dst = pass == 0 ? dgain : dbias;
+          if (dst) atomicAdd(dst + col, t);
+        }
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- softmax cross entropy
+// One block per row.  labels: dense probabilities (same dtype as logits) or int64 class indices.
+// loss[r] = -sum_j labels_j * log softmax_j ; grad_out (optional) = softmax * sum(labels) - labels.
+constexpr int SX_THREADS = 256;
+
+__device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[wid] = v;
+  __syncthreads();
+  if (wid == 0) {
+    float t = lane < SX_THREADS / 32 ? sh[lane] : (is_max ? -INFINITY : 0.f);
+    t = is_max ? warp_max(t) : warp_sum(t);
+    if (lane == 0) sh[0] = t;
+  }
+  __syncthreads();
+  return sh[0];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SX_THREADS)
+softmax_xent_kernel(const T* __restrict__ logits, const T* __restrict__ dense_labels, const long long* __restrict__ idx_labels,
+                    float* __restrict__ loss, T* __restrict__ grad_out, int C, long long ld, int ignore_index) {
+  __shared__ float sh[SX_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* z = logits + row * ld;
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < C; j += SX_THREADS) mx = fmaxf(mx, ldf(z + j));
+  mx = block_reduce(mx, sh, true);
+  float se = 0.f, sl = 0.f, slz = 0.f;
+  for (int j = threadIdx.x; j < C; j += SX_THREADS) {
+    const float v = ldf(z + j);
+    se += __expf(v - mx);
+    if (dense_labels) {
+      const float l = ldf(dense_labels + row * (long long)C + j);
+      sl += l;
+      slz += l * v;
+    }
+  }
+  se = block_reduce(se, sh, false);
+  const float lse = mx + __logf(se);
+  long long tgt = -1;
+  if (dense_labels) {
+    sl = block_reduce(sl, sh, false);
+    slz = block_reduce(slz, sh, false);
+  } else {
+    tgt = idx_labels[row];
+    if (tgt == ignore_index || tgt < 0 || tgt >= C) { tgt = -1; sl = 0.f; slz = 0.f; }
+    else { sl = 1.f; slz = ldf(z + tgt); }
+  }
+  if (threadIdx.x == 0) loss[row] = sl * lse - slz;
+  if (grad_out) {
+    T* g = grad_out + row * ld;
+    const float inv = 1.f / se;
+    for (int j = threadIdx.x; j < C; j += SX_THREADS) {
+      const float pj = __expf(ldf(z + j) - mx) * inv;
+      const float l = dense_labels ? ldf(dense_labels + row * (long long)C + j) : (j == tgt ? 1.f : 0.f);
+      stf(g + j, pj * sl - l);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- LSTM cell
+// z [mb, 4n] pre-activations in DL4J gate order [a(block input), f, o, g]; c_prev fp32 [mb, n].
+// Writes h (T), c (fp32) and the activated gates (T, [mb,4n]) for the backward pass.
+template <typename T>
+__global__ void lstm_cell_fwd_kernel(const T* __restrict__ z, const float* __restrict__ c_prev, T* __restrict__ h,
+                                     float* __restrict__ c, T* __restrict__ gates, int mb, int n) {
+  const long long total = (long long)mb * n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n), j = (int)(i % n);
+    const T* zr = z + (long long)r * 4 * n;
+    const float a = tanhf(ldf(zr + j));
+    const float f = sigmoidf_(ldf(zr + n + j));
+    const float o = sigmoidf_(ldf(zr + 2 * n + j));
+    const float g = sigmoidf_(ldf(zr + 3 * n + j));
+    const float cn = f * c_prev[i] + g * a;
+    c[i] = cn;
+    stf(h + i, o * tanhf(cn));
+    if (gates) {
+      T* gr = gates + (long long)r * 4 * n;
+      stf(gr + j, a); stf(gr + n + j, f); stf(gr + 2 * n + j, o); stf(gr + 3 * n + j, g);
+    }
+  }
+}
+
+// dh (T), dc_in (fp32, gradient flowing into c from the next step, may be null) -> dz (T), dc_prev (fp32)
+template <typename T>
+__global__ void lstm_cell_bwd_kernel(const T* __restrict__ dh, const float* __restrict__ dc_in, const T* __restrict__ gates,
+                                     const float* __restrict__ c, const float* __restrict__ c_prev, T* __restrict__ dz,
+                                     float* __restrict__ dc_prev, int mb, int n) {
+  const long long total = (long long)mb * n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n), j = (int)(i % n);
+    const T* gr = gates + (long long)r * 4 * n;
+    const float a = ldf(gr + j), f = ldf(gr + n + j), o = ldf(gr + 2 * n + j), g = ldf(gr + 3 * n + j);
+    const float tc = tanhf(c[i]);
+    const float dhv = dh ? ldf(dh + i) : 0.f;
+    const float dc = (dc_in ? dc_in[i] : 0.f) + dhv * o * (1.f - tc * tc);
+    T* dr = dz + (long long)r * 4 * n;
+    stf(dr + j, dc * g * (1.f - a * a));
+    stf(dr + n + j, dc * c_prev[i] * f * (1.f - f));
+    stf(dr + 2 * n + j, dhv * tc * o * (1.f - o));
+    stf(dr + 3 * n + j, dc * a * g * (1.f - g));
+    dc_prev[i] = dc * f;
+  }
+}
+
+// ----------------------------------------------------------------------------- bias / activation backward
+// dz = dy * act'(z) (written only when dz != null) and dbias[c] += sum_r dz[r, c].
+// Block = 32 column-pairs x 8 row lanes; grid.x over column tiles of 64, grid.y over row slabs.
+__device__ __forceinline__ float act_grad(float z, int act) {
+  switch (act) {
+    case 1: return z > 0.f ? 1.f : 0.f;
+    case 2: {
+      const float cdf = 0.5f * (1.f + erff(z * 0.70710678118654752f));
+      return cdf + z * 0.3989422804014327f * __expf(-0.5f * z * z);
+    }
+    case 3: {
+      const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+      const float t = tanhf(u);
+      return 0.5f * (1.f + t) + 0.5f * z * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * z * z);
+    }
+    case 4: { const float s = sigmoidf_(z); return s * (1.f - s); }
+    case 5: { const float t = tanhf(z); return 1.f - t * t; }
+    default: return 1.f;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_act_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restrict__ dz, float* __restrict__ dbias,
+                    int rows, int C, int act, int rows_per_block) {
+  __shared__ float red[8][65];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 64 + tx * 2;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(r0 + rows_per_block, rows);
+  float s0 = 0.f, s1 = 0.f;
+  if (col < C) {
+    const bool pair = col + 1 < C;
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const long long o = (long long)r * C + col;
+      float d0 = ldf(dy + o), d1 = pair ? ldf(dy + o + 1) : 0.f;
+      if (act != 0) {
+        d0 *= act_grad(ldf(z + o), act);
+        if (pair) d1 *= act_grad(ldf(z + o + 1), act);
+      }
+      if (dz) { stf(dz + o, d0); if (pair) stf(dz + o + 1, d1); }
+      s0 += d0; s1 += d1;
+    }
+  }
+  red[ty][tx * 2] = s0; red[ty][tx * 2 + 1] = s1;
+  __syncthreads();
+  if (dbias && threadIdx.x < 64) {
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < C) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+      atomicAdd(dbias + c, t);
+    }
+  }
+}
+
+}  // namespace dl4j
+
+using namespace dl4j;
+
+// dtype: 0 = fp16, 1 = bf16, 2 = fp32
+#define DL4J_DISPATCH_T(dtype, ...)                                     \
+  if (dtype == 1) { using T = __nv_bfloat16; __VA_ARGS__; }            \
+  else if (dtype == 0) { using T = __half; __VA_ARGS__; }              \
+  else { using T = float; __VA_ARGS__; }
+
+DL4J_API int dl4j_layer_norm_fwd(const void* x, const void* res, const float* gain, const float* bias, void* y,
+                                 void* sum_out, float* mean, float* rstd, int rows, int C, float eps, int dtype, void* stream) {
+  if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
+  const int grid = (rows + LN_WARPS - 1) / LN_WARPS;
+  DL4J_DISPATCH_T(dtype, (layer_norm_fwd_kernel<T><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (const T*)x, (const T*)res, gain, bias, (T*)y, (T*)sum_out, mean, rstd, rows, C, eps)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gain, const float* mean, const float* rstd,
+                                 void* dx, float* dgain, float* dbias, int rows, int C, int dtype, void* stream) {
+  if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
+  int grid = (rows + LN_WARPS - 1) / LN_WARPS;
+  if (grid > 148 * 4) grid = 148 * 4;
+  DL4J_DISPATCH_T(dtype, (layer_norm_bwd_kernel<T><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (const T*)dy, (const T*)x, gain, mean, rstd, (T*)dx, dgain, dbias, rows, C)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_softmax_xent(const void* logits, const void* dense_labels, const long long* idx_labels, float* loss,
+                               void* grad_out, int rows, int C, long long ld, int ignore_index, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  DL4J_DISPATCH_T(dtype, (softmax_xent_kernel<T><<<rows, SX_THREADS, 0, (cudaStream_t)stream>>>(
+      (const T*)logits, (const T*)dense_labels, idx_labels, loss, (T*)grad_out, C, ld, ignore_index)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_lstm_cell_fwd(const void* z, const float* c_prev, void* h, float* c, void* gates, int mb, int n,
+                                int dtype, void* stream) {
+  long long total = (long long)mb * n;
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  DL4J_DISPATCH_T(dtype, (lstm_cell_fwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+      (const T*)z, c_prev, (T*)h, c, (T*)gates, mb, n)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_lstm_cell_bwd(const void* dh, const float* dc_in, const void* gates, const float* c, const float* c_prev,
+                                void* dz, float* dc_prev, int mb, int n, int dtype, void* stream) {
+  long long total = (long long)mb * n;
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  DL4J_DISPATCH_T(dtype, (lstm_cell_bwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+      (const T*)dh, dc_in, (const T*)gates, c, c_prev, (T*)dz, dc_prev, mb, n)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* dbias, int rows, int C, int act, int dtype,
+                               void* stream) {
+  if (rows <= 0 || C <= 0) return 0;
+  if (dy == nullptr || (act != 0 && z == nullptr)) return -DL4J_ERR_BAD_ARG;
+  const int col_tiles = (C + 63) / 64;
+  int row_slabs = (148 * 4 + col_tiles - 1) / col_tiles;
+  if (row_slabs < 1) row_slabs = 1;
+  int rpb = (rows + row_slabs - 1) / row_slabs;
+  rpb = (rpb + 7) / 8 * 8;
+  row_slabs = (rows + rpb - 1) / rpb;
+  dim3 grid(col_tiles, row_slabs);
+  DL4J_DISPATCH_T(dtype, (bias_act_bwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+      (const T*)dy, (const T*)z, (T*)dz, dbias, rows, C, act, rpb)));
+  return (int)cudaGetLastError();
+}

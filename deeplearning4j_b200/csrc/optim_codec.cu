@@ -1,0 +1,385 @@
+// Multi-segment fused updater over the flattened DL4J parameter / gradient / state buffers, and the
+// threshold ("flexible") and bitmap gradient codecs.
+//
+// Updater math: libnd4j/include/ops/declarable/helpers/cuda/updater{Adam,Nesterovs,AdaGrad,AdaDelta,
+// AdaMax,AdaBelief,AmsGrad,Nadam,RmsProp}.cu; block/regularisation order:
+// deeplearning4j-nn/.../nn/updater/UpdaterBlock.java:118-165 (L1/L2 before the updater, weight decay
+// after, then params -= update).  One launch covers every parameter of the network: a chunk table maps
+// CUDA blocks to (offset, count, segment) and a segment table carries per-parameter coefficients.
+//
+// Codec semantics: libnd4j/include/loops/cuda/type_conversions.cu:215-500 (message layout
+// [k, N, bits(tau), flag, payload...], residual kept in the source buffer, bitmap half-threshold rule).
+#include "common.cuh"
+
+namespace dl4j {
+
+struct UpdSegment {     // one per parameter array (56 bytes)
+  long long offset;     // into params / grads
+  long long block_start;// first element of the updater block this parameter belongs to
+  long long block_numel;
+  long long state_off;  // block's offset into the state buffer
+  long long shadow_off; // this parameter's offset into the (16-byte aligned per parameter) bf16 shadow buffer
+  float l1, l2, wd;     // wd already multiplied by lr when applyLR
+  int kernel_id;        // see IUpdater.KERNEL_ID
+  int hyper;            // index into UpdHyper table
+  int pad;
+};
+
+struct UpdHyper {       // per updater block, refreshed each iteration (passed by value)
+  float lr, b1, b2, eps, eps_t, mb1t, mu, rho;
+};
+
+struct UpdChunk { long long offset; int count; int seg; };
+
+constexpr int UPD_MAX_HYPER = 8;
+struct UpdHyperTable { UpdHyper h[UPD_MAX_HYPER]; };
+
+constexpr int UPD_THREADS = 256;
+
+__device__ __forceinline__ float sgnf(float x) { return (x > 0.f) - (x < 0.f); }
+
+__global__ void __launch_bounds__(UPD_THREADS)
+fused_update_kernel(float* __restrict__ params, float* __restrict__ grads, float* __restrict__ state,
+                    __nv_bfloat16* __restrict__ shadow, const UpdChunk* __restrict__ chunks,
+                    const UpdSegment* __restrict__ segs, const UpdHyperTable ht, float grad_scale, int zero_grads) {
+  const UpdChunk ch = chunks[blockIdx.x];
+  const UpdSegment sg = segs[ch.seg];
+  const UpdHyper h = ht.h[sg.hyper];
+  const long long rel0 = ch.offset - sg.block_start;
+  float* st0 = state + sg.state_off + rel0;
+  float* st1 = st0 + sg.block_numel;
+  float* st2 = st1 + sg.block_numel;
+  float* p = params + ch.offset;
+  float* g = grads + ch.offset;
+  for (int i = threadIdx.x; i < ch.count; i += UPD_THREADS) {
+    float w = p[i];
+    float gr = g[i] * grad_scale;
+    if (sg.kernel_id == 9) {            // NoOp / state parameters: leave untouched
+      if (zero_grads) g[i] = 0.f;
+      continue;
+    }
+    if (sg.l2 != 0.f) gr += sg.l2 * w;
+    if (sg.l1 != 0.f) gr += sg.l1 * sgnf(w);
+    float u;
+    switch (sg.kernel_id) {
+      case 0: u = h.lr * gr; break;                                          // Sgd
+      case 1: {                                                               // Nesterovs
+        const float prev = h.mu * st0[i];
+        const float v = prev - h.lr * gr;
+        st0[i] = v;
+        u = prev + (-h.mu - 1.f) * v;
+      } break;
+      case 2: {                                                               // Adam
+        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
+        const float v = h.b2 * st1[i] + (1.f - h.b2) * gr * gr;
+        st0[i] = m; st1[i] = v;
+        u = m * h.eps_t / (sqrtf(v) + h.eps);
+      } break;
+      case 3: {                                                               // AdaMax
+        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
+        const float uu = fmaxf(h.b2 * st1[i], fabsf(gr)) + 1e-32f;
+        st0[i] = m; st1[i] = uu;
+        u = m * h.eps_t / uu;
+      } break;
+      case 4: {                                                               // Nadam
+        const float omg = (1.f - h.b1) * gr;
+        const float m = h.b1 * st0[i] + omg;
+        const float v = h.b2 * st1[i] + (1.f - h.b2) * gr * gr;
+        st0[i] = m; st1[i] = v;
+        u = (h.lr * ((m * h.b1 + omg) / h.mb1t)) / (sqrtf(v) + h.eps);
+      } break;
+      case 5: {                                                               // AMSGrad
+        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
+        const float v = h.b2 * st1[i] + (1.f - h.b2) * gr * gr;
+        const float hh = fmaxf(st2[i], v);
+        st0[i] = m; st1[i] = v; st2[i] = hh;
+        u = h.eps_t * m / (sqrtf(hh) + h.eps);
+      } break;
+      case 6: {                                                               // AdaBelief
+        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
+        const float d = gr - m;
+        const float s = h.b2 * st1[i] + (1.f - h.b2) * d * d + h.eps;
+        st0[i] = m; st1[i] = s;
+        u = m * h.eps_t / (sqrtf(s) + h.eps);
+      } break;
+      case 7: {                                                               // AdaGrad
+        const float s = st0[i] + gr * gr;
+        st0[i] = s;
+        u = h.lr * gr / (sqrtf(s) + h.eps);
+      } break;
+      case 8: {                                                               // RmsProp
+        const float s = st0[i] * h.rho + gr * gr * (1.f - h.rho);
+        st0[i] = s;
+        u = h.lr * gr / (sqrtf(s) + h.eps);
+      } break;
+      case 10: {                                                              // AdaDelta
+        const float msg = h.rho * st0[i] + (1.f - h.rho) * gr * gr;
+        u = gr * (sqrtf(st1[i] + h.eps) / sqrtf(msg + h.eps));
+        st0[i] = msg;
+        st1[i] = h.rho * st1[i] + (1.f - h.rho) * u * u;
+      } break;
+      default: u = 0.f;
+    }
+    if (sg.wd != 0.f) u += sg.wd * w;
+    w -= u;
+    p[i] = w;
+    if (shadow) shadow[sg.shadow_off + (ch.offset - sg.offset) + i] = __float2bfloat16(w);
+    if (zero_grads) g[i] = 0.f;
+  }
+}
+
+// fp32 -> bf16 shadow copy of the parameter buffer (used once after init / setParams)
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4;
+  const long long stride = (long long)gridDim.x * blockDim.x * 4;
+  for (; i + 3 < n; i += stride) {
+    const float4 v = *reinterpret_cast<const float4*>(in + i);
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    *reinterpret_cast<uint2*>(out + i) = u;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long j = n & ~3LL; j < n; ++j) out[j] = __float2bfloat16(in[j]);
+}
+
+// ----------------------------------------------------------------------------- threshold codec
+constexpr int ENC_THREADS = 256;
+constexpr int ENC_PER_THREAD = 8;
+constexpr int ENC_TILE = ENC_THREADS * ENC_PER_THREAD;
+
+// Sparse encode: every |x[i]| >= tau becomes +-(i+1) in msg[4..], x[i] moves towards zero by tau.
+// msg[0] is the atomic slot counter (must be zero on entry); entries beyond `capacity` are not
+// encoded and their residual is left untouched.  Order inside a tile is ascending.
+__global__ void __launch_bounds__(ENC_THREADS)
+threshold_encode_kernel(float* __restrict__ x, long long n, float tau, int* __restrict__ msg, int capacity) {
+  __shared__ int warp_tot[ENC_THREADS / 32];
+  __shared__ int tile_base;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    msg[1] = (int)n;
+    msg[2] = __float_as_int(tau);
+    msg[3] = 0;
+  }
+  const long long tiles = (n + ENC_TILE - 1) / ENC_TILE;
+  for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const long long base = t * ENC_TILE + (long long)threadIdx.x * ENC_PER_THREAD;
+    float v[ENC_PER_THREAD];
+    int flags = 0, cnt = 0;
+    if (base + ENC_PER_THREAD <= n) {
+      const float4 a = *reinterpret_cast<const float4*>(x + base);
+      const float4 b = *reinterpret_cast<const float4*>(x + base + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < ENC_PER_THREAD; ++j) v[j] = (base + j < n) ? x[base + j] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < ENC_PER_THREAD; ++j)
+      if (fabsf(v[j]) >= tau) { flags |= 1 << j; ++cnt; }
+    // block exclusive scan of cnt
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    if (lane == 31) warp_tot[wid] = incl;
+    __syncthreads();
+    int woff = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < ENC_THREADS / 32; ++w) {
+      const int c = warp_tot[w];
+      if (w < wid) woff += c;
+      total += c;
+    }
+    if (threadIdx.x == 0) tile_base = total ? atomicAdd(&msg[0], total) : 0;
+    __syncthreads();
+    int slot = tile_base + woff + incl - cnt;
+    if (flags) {
+      bool touched = false;
+#pragma unroll
+      for (int j = 0; j < ENC_PER_THREAD; ++j) {
+        if (flags & (1 << j)) {
+          if (slot < capacity) {
+            const bool neg = v[j] < 0.f;
+            const int idx = (int)(base + j) + 1;
+            msg[4 + slot] = neg ? -idx : idx;
+            v[j] += neg ? tau : -tau;
+            touched = true;
+          }
+          ++slot;
+        }
+      }
+      if (touched) {
+        if (base + ENC_PER_THREAD <= n) {
+          *reinterpret_cast<float4*>(x + base) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(x + base + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < ENC_PER_THREAD; ++j) if (base + j < n) x[base + j] = v[j];
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Sparse decode: target[|e|-1] += sign(e) * scale * tau for the first min(msg[0], capacity) entries.
+__global__ void threshold_decode_kernel(const int* __restrict__ msg, int capacity, float* __restrict__ target,
+                                        long long n_target, float scale, int use_atomics, int* status) {
+  int k = msg[0];
+  if (k > capacity) k = capacity;
+  const float tau = __int_as_float(msg[2]) * scale;
+  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < k; j += gridDim.x * blockDim.x) {
+    const int e = msg[4 + j];
+    const int idx = (e < 0 ? -e : e) - 1;
+    if (idx < 0 || idx >= n_target) { if (status) atomicCAS(status, 0, DL4J_ERR_BOUNDS); continue; }
+    const float d = e < 0 ? -tau : tau;
+    if (use_atomics) atomicAdd(target + idx, d); else target[idx] += d;
+  }
+}
+
+// Bitmap encode: word w covers elements [16w, 16w+16): bit b = |x| >= tau, bit b+16 = negative; a
+// negative value with tau/2 <= |x| < tau sets only the sign bit and moves by +tau/2.
+__global__ void bitmap_encode_kernel(float* __restrict__ x, long long n, float tau, int* __restrict__ msg) {
+  __shared__ int block_cnt;
+  if (threadIdx.x == 0) block_cnt = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    msg[1] = (int)n;
+    msg[2] = __float_as_int(tau);
+    msg[3] = 1;
+  }
+  __syncthreads();
+  const long long words = (n + 15) / 16;
+  int cnt = 0;
+  const float half = tau * 0.5f;
+  for (long long w = blockIdx.x * (long long)blockDim.x + threadIdx.x; w < words; w += (long long)gridDim.x * blockDim.x) {
+    const long long base = w * 16;
+    float v[16];
+    const bool full = base + 16 <= n;
+    if (full) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 a = *reinterpret_cast<const float4*>(x + base + 4 * q);
+        v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = (base + j < n) ? x[base + j] : 0.f;
+    }
+    int word = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float a = fabsf(v[j]);
+      if (a >= tau) {
+        word |= 1 << j;
+        ++cnt;
+        if (v[j] < 0.f) { word |= 1 << (j + 16); v[j] += tau; } else { v[j] -= tau; }
+      } else if (a >= half && v[j] < 0.f) {
+        word |= 1 << (j + 16);
+        ++cnt;
+        v[j] += half;
+      }
+    }
+    msg[4 + w] = word;
+    if (word) {
+      if (full) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<float4*>(x + base + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) if (base + j < n) x[base + j] = v[j];
+      }
+    }
+  }
+  cnt = (int)warp_sum((float)cnt);   // counts per warp stay far below 2^24: exact in fp32
+  if ((threadIdx.x & 31) == 0 && cnt) atomicAdd(&block_cnt, cnt);
+  __syncthreads();
+  if (threadIdx.x == 0 && block_cnt) atomicAdd(&msg[0], block_cnt);
+}
+
+__global__ void bitmap_decode_kernel(const int* __restrict__ msg, float* __restrict__ target, long long n, float scale) {
+  const float tau = __int_as_float(msg[2]) * scale;
+  const float half = tau * 0.5f;
+  const long long words = (n + 15) / 16;
+  for (long long w = blockIdx.x * (long long)blockDim.x + threadIdx.x; w < words; w += (long long)gridDim.x * blockDim.x) {
+    const int word = msg[4 + w];
+    if (!word) continue;
+    const long long base = w * 16;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (base + j >= n) break;
+      const bool bit = word & (1 << j), sign = word & (1 << (j + 16));
+      if (bit) target[base + j] += sign ? -tau : tau;
+      else if (sign) target[base + j] -= half;
+    }
+  }
+}
+
+}  // namespace dl4j
+
+using namespace dl4j;
+
+DL4J_API int dl4j_fused_update(float* params, float* grads, float* state, void* shadow_bf16, const void* chunks,
+                               int n_chunks, const void* segs, const float* hyper, int n_hyper, float grad_scale,
+                               int zero_grads, void* stream) {
+  if (n_chunks <= 0) return 0;
+  if (n_hyper > UPD_MAX_HYPER) return -DL4J_ERR_BAD_ARG;
+  UpdHyperTable ht;
+  memset(&ht, 0, sizeof(ht));
+  memcpy(&ht, hyper, sizeof(UpdHyper) * n_hyper);
+  fused_update_kernel<<<n_chunks, UPD_THREADS, 0, (cudaStream_t)stream>>>(
+      params, grads, state, reinterpret_cast<__nv_bfloat16*>(shadow_bf16), reinterpret_cast<const UpdChunk*>(chunks),
+      reinterpret_cast<const UpdSegment*>(segs), ht, grad_scale, zero_grads);
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_cast_f32_bf16(const float* in, void* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  cast_f32_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(in, reinterpret_cast<__nv_bfloat16*>(out), n);
+  return (int)cudaGetLastError();
+}
+
+// msg must hold 4 + capacity ints and msg[0] must be zero on entry (the call zeroes it on the stream).
+DL4J_API int dl4j_threshold_encode(float* x, long long n, float tau, int* msg, int capacity, void* stream) {
+  if (n <= 0 || n >= 2147483647LL) return -DL4J_ERR_BAD_ARG;
+  cudaMemsetAsync(msg, 0, sizeof(int), (cudaStream_t)stream);
+  long long tiles = (n + ENC_TILE - 1) / ENC_TILE;
+  int grid = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
+  threshold_encode_kernel<<<grid, ENC_THREADS, 0, (cudaStream_t)stream>>>(x, n, tau, msg, capacity);
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_threshold_decode(const int* msg, int capacity, float* target, long long n_target, float scale,
+                                   int use_atomics, void* stream) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int grid = capacity / 256 + 1;
+  if (grid > 148 * 8) grid = 148 * 8;
+  threshold_decode_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(msg, capacity, target, n_target, scale, use_atomics,
+                                                                  dl4j_status_word(dev));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_bitmap_encode(float* x, long long n, float tau, int* msg, void* stream) {
+  if (n <= 0 || n >= 2147483647LL) return -DL4J_ERR_BAD_ARG;
+  cudaMemsetAsync(msg, 0, sizeof(int), (cudaStream_t)stream);
+  long long words = (n + 15) / 16;
+  long long blocks = (words + 255) / 256;
+  int grid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+  bitmap_encode_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, n, tau, msg);
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_bitmap_decode(const int* msg, float* target, long long n, float scale, void* stream) {
+  long long words = (n + 15) / 16;
+  long long blocks = (words + 255) / 256;
+  int grid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+  if (grid < 1) grid = 1;
+  bitmap_decode_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(msg, target, n, scale);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,60 @@
+// Library runtime: driver entry points obtained without linking libcuda, the per-device status
+// word that bounded waits report into, and small queries used by the Python side.
+#include "common.cuh"
+
+#include <mutex>
+
+static std::mutex g_mu;
+static dl4j_PFN_encodeTiled g_encode = nullptr;
+static int* g_status[64] = {nullptr};
+
+dl4j_PFN_encodeTiled dl4j_get_encode_tiled() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_encode) return g_encode;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  g_encode = reinterpret_cast<dl4j_PFN_encodeTiled>(fn);
+  return g_encode;
+}
+
+int* dl4j_status_word(int device) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (device < 0 || device >= 64) return nullptr;
+  if (!g_status[device]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 256);
+    g_status[device] = p;
+  }
+  return g_status[device];
+}
+
+// Returns the status word's value (0 = no bounded wait has expired) and clears it.
+DL4J_API int dl4j_read_status(int reset) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* p = dl4j_status_word(dev);
+  if (!p) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (reset && v != 0) cudaMemset(p, 0, sizeof(int));
+  return v;
+}
+
+DL4J_API void* dl4j_status_ptr() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dl4j_status_word(dev);
+}
+
+DL4J_API int dl4j_num_sms() {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+DL4J_API int dl4j_abi_version() { return 1; }

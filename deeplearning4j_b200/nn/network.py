@@ -47,6 +47,8 @@ class BaseNetwork:
         self.device = torch.device("cpu")
         self._last_etl_ms = 0.0
         self.gradient_hook = None       # set by ParallelWrapper: called between backward and the updater
+        self.flat_shadow = None
+        self.shadow_offsets = None
 
     # ------------------------------------------------------------------ to be provided by subclasses
     def _owners(self):
@@ -117,13 +119,38 @@ class BaseNetwork:
     def _make_views(self):
         self.param_views = {}
         owners = self._owners()
-        for e in self.entries:
+        self._make_shadow()
+        for i, e in enumerate(self.entries):
             key = owners[e.layer_index][0]
             v = flat_view(self.flat_params, e.offset, e.spec).detach()
             if e.spec.kind != "state":
                 v.requires_grad_(True)
                 v.grad = flat_view(self.flat_grads, e.offset, e.spec)
+                if self.flat_shadow is not None:
+                    v._lp = flat_view(self.flat_shadow, self.shadow_offsets[i], e.spec)
             self.param_views.setdefault(key, {})[e.spec.name] = v
+
+    def _make_shadow(self):
+        """Low-precision copy of the parameters for the tensor-core GEMMs (fp32 master weights stay
+        in ``flat_params``).  Every parameter starts on a 16-byte boundary so TMA can address it."""
+        self.flat_shadow, self.shadow_offsets = None, None
+        cd = self._compute_dtype()
+        if cd == self._param_dtype() or self.flat_params is None or not self.flat_params.is_cuda:
+            return
+        offs, off = [], 0
+        for e in self.entries:
+            offs.append(off)
+            off += (e.spec.numel + 63) // 64 * 64
+        self.shadow_offsets = offs
+        self.flat_shadow = torch.zeros(max(off, 1), dtype=cd, device=self.device)
+        self._refresh_shadow()
+
+    def _refresh_shadow(self):
+        if self.flat_shadow is None:
+            return
+        with torch.no_grad():
+            for e, so in zip(self.entries, self.shadow_offsets):
+                self.flat_shadow[so:so + e.spec.numel].copy_(self.flat_params[e.offset:e.end])
 
     def _rebind(self):
         """Call after the flat buffers were replaced (device move, setParams with new storage)."""
@@ -164,6 +191,7 @@ class BaseNetwork:
         t = _as_tensor(p).reshape(-1)
         with torch.no_grad():
             self.flat_params.copy_(t.to(self.flat_params.dtype).to(self.device))
+        self._refresh_shadow()
 
     setParameters = setParams
 
@@ -254,7 +282,11 @@ class BaseNetwork:
         if self.gradient_hook is not None:
             if self.gradient_hook(self) is True:   # hook consumed the gradient and stepped the params
                 return
-        self._ensure_updater().update(self.iterationCount, self.epochCount)
+        upd = self._ensure_updater()
+        upd.shadow, upd.shadow_offsets = self.flat_shadow, self.shadow_offsets
+        upd.update(self.iterationCount, self.epochCount)
+        if self.flat_shadow is not None and not getattr(upd, "_shadow_fresh", False):
+            self._refresh_shadow()
         self._apply_constraints()
 
     def _apply_constraints(self):

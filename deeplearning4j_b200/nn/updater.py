@@ -91,6 +91,9 @@ class MultiLayerUpdater:
         self.state = state_view
         self._bind()
         self._seg_table = None
+        self.shadow = None            # optional low-precision parameter shadow refreshed by the fused kernel
+        self.shadow_offsets = None
+        self._shadow_fresh = False
 
     def _bind(self):
         self.updaters = []
@@ -159,7 +162,9 @@ class MultiLayerUpdater:
             self._pre_apply()
         if use_fused is None:
             use_fused = self.params.is_cuda
+        self._shadow_fresh = False
         if use_fused and apply_step and self._fused_update(iteration, epoch):
+            self._shadow_fresh = self.shadow is not None
             return
         for b, gu in zip(self.blocks, self.updaters):
             cfg = b.config
@@ -213,4 +218,4 @@ class MultiLayerUpdater:
         from ..ops import native
         if not native.available() or self.params.dtype != torch.float32:
             return False
-        return native.fused_update(self, iteration, epoch)
+        return native.fused_update(self, iteration, epoch, self.shadow, self.shadow_offsets)

@@ -1,2 +1,605 @@
-"""placeholder, replaced below"""
-def available(): return False
+"""ctypes bindings to the in-tree sm_100a library (``csrc/libdl4j_b200.so``) and the autograd
+functions that put its kernels on the training path.
+
+The library exports a plain C ABI over raw device pointers + a CUDA stream, so loading it does
+not depend on torch's C++ ABI and building it takes seconds.  On a machine with a GPU the
+library is mandatory: ``require()`` raises if it cannot be loaded, so a silent torch fallback
+cannot masquerade as the native path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import struct
+import threading
+
+import numpy as np
+import torch
+
+_LIB = None
+_LIB_ERR = None
+_LOCK = threading.Lock()
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc", "libdl4j_b200.so")
+
+LAUNCHES = 0     # number of native kernel launches issued by this process (bench.py reports it)
+
+_ACT_IDS = {"ActivationIdentity": 0, "ActivationReLU": 1, "ActivationGELU": 3, "ActivationSigmoid": 4, "ActivationTanH": 5}
+
+
+def _load():
+    global _LIB, _LIB_ERR
+    with _LOCK:
+        if _LIB is not None or _LIB_ERR is not None:
+            return _LIB
+        path = os.path.abspath(_LIB_PATH)
+        if not os.path.exists(path):
+            _LIB_ERR = f"{path} not built (run python -m deeplearning4j_b200.csrc.build)"
+            return None
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            _LIB_ERR = str(e)
+            return None
+        vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lng = ctypes.c_long
+        sig = {
+            "dl4j_gemm": [vp, vp, vp, vp, vp, vp, i32, i32, i32, lng, lng, lng, lng, lng, i32, i32, i32, i32, i32, i32,
+                          i32, i32, f32, i32, i32, vp],
+            "dl4j_fused_update": [vp, vp, vp, vp, vp, i32, vp, vp, i32, f32, i32, vp],
+            "dl4j_cast_f32_bf16": [vp, vp, i64, vp],
+            "dl4j_threshold_encode": [vp, i64, f32, vp, i32, vp],
+            "dl4j_threshold_decode": [vp, i32, vp, i64, f32, i32, vp],
+            "dl4j_bitmap_encode": [vp, i64, f32, vp, vp],
+            "dl4j_bitmap_decode": [vp, vp, i64, f32, vp],
+            "dl4j_layer_norm_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
+            "dl4j_layer_norm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
+            "dl4j_softmax_xent": [vp, vp, vp, vp, vp, i32, i32, i64, i32, i32, vp],
+            "dl4j_lstm_cell_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
+            "dl4j_lstm_cell_bwd": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
+            "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+            "dl4j_read_status": [i32],
+            "dl4j_num_sms": [],
+            "dl4j_abi_version": [],
+        }
+        for name, args in sig.items():
+            fn = getattr(lib, name, None)
+            if fn is not None:
+                fn.argtypes = args
+                fn.restype = ctypes.c_int
+        for name in dir(lib):
+            pass
+        _LIB = lib
+        return lib
+
+
+def lib():
+    return _load()
+
+
+def available() -> bool:
+    return torch.cuda.is_available() and _load() is not None
+
+
+def require():
+    """Fail loudly when a GPU is present but the native library is not."""
+    if torch.cuda.is_available() and _load() is None:
+        raise RuntimeError(f"deeplearning4j_b200 native library unavailable on a GPU machine: {_LIB_ERR}")
+    return _LIB
+
+
+def load_error():
+    _load()
+    return _LIB_ERR
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc, what):
+    global LAUNCHES
+    LAUNCHES += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def check_status(reset=True):
+    """Raise if any bounded device-side wait expired since the last check (synchronises)."""
+    l = require()
+    if l is None:
+        return 0
+    v = l.dl4j_read_status(1 if reset else 0)
+    if v != 0:
+        names = {1: "TMA producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "peer wait", 5: "index out of bounds"}
+        raise RuntimeError(f"device-side bounded wait/ check failed: {names.get(v, v)}")
+    return v
+
+
+_DT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+_NUM_SMS = None
+
+
+def num_sms():
+    global _NUM_SMS
+    if _NUM_SMS is None:
+        _NUM_SMS = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _NUM_SMS
+
+
+# =========================================================================== GEMM
+def _operand_a(a):
+    """logical [M, K] -> (tensor, mn_major flag, leading dim) or None."""
+    if a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.stride(0) >= a.shape[1] and a.data_ptr() % 16 == 0:
+        return a, 0, a.stride(0)
+    if a.stride(0) == 1 and a.stride(1) % 8 == 0 and a.stride(1) >= a.shape[0] and a.data_ptr() % 16 == 0:
+        return a, 1, a.stride(1)
+    return None
+
+
+def _operand_b(b):
+    """logical [K, N] -> (tensor, mn_major flag, leading dim) or None."""
+    if b.stride(0) == 1 and b.stride(1) % 8 == 0 and b.stride(1) >= b.shape[0] and b.data_ptr() % 16 == 0:
+        return b, 0, b.stride(1)       # stored [N, K]
+    if b.stride(1) == 1 and b.stride(0) % 8 == 0 and b.stride(0) >= b.shape[1] and b.data_ptr() % 16 == 0:
+        return b, 1, b.stride(0)       # stored [K, N]
+    return None
+
+
+def gemm_supported(a, b) -> bool:
+    if not available() or a.dim() != 2 or b.dim() != 2 or a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    if a.shape[1] != b.shape[0] or min(a.shape[0], a.shape[1], b.shape[1]) == 0:
+        return False
+    return _operand_a(a) is not None and _operand_b(b) is not None
+
+
+def _pick_block_n(M, N, splits=1):
+    sms = num_sms()
+    best, best_cost = 256, None
+    for bn in (256, 128):
+        tiles = ((M + 127) // 128) * ((N + bn - 1) // bn) * splits
+        waves = (tiles + sms - 1) // sms
+        cost = waves * bn * (1.0 if bn == 256 else 1.08)     # 128-wide tiles pay a little more per column
+        if best_cost is None or cost < best_cost:
+            best, best_cost = bn, cost
+    return best
+
+
+def gemm_raw(a, b, out=None, bias=None, act=0, aux=None, residual=None, out_dtype=None, atomic=False, splits=1,
+             alpha=1.0, block_n=None):
+    """out[M,N] = act(alpha * a @ b + bias) + residual with a logical [M,K], b logical [K,N]."""
+    l = require()
+    oa, ob = _operand_a(a), _operand_b(b)
+    if oa is None or ob is None:
+        raise ValueError("operand layout not addressable by TMA (need unit stride in one dim, 16-byte alignment)")
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out_dtype = out_dtype or a.dtype
+        out = (torch.zeros if atomic else torch.empty)((M, N), dtype=out_dtype, device=a.device)
+    if out.stride(1) != 1:
+        raise ValueError("output must be row-major")
+    out_fp32 = 1 if out.dtype == torch.float32 else 0
+    if not out_fp32 and out.dtype != a.dtype:
+        raise ValueError("output dtype must be the input dtype or float32")
+    kb = (K + 63) // 64
+    splits = max(1, min(int(splits), kb))
+    if splits > 1 and not (atomic and out_fp32):
+        splits = 1
+    bn = block_n or _pick_block_n(M, N, splits)
+    bias_fp32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
+    if bias is not None and not bias_fp32 and bias.dtype != a.dtype:
+        bias = bias.to(a.dtype)
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
+    rc = l.dl4j_gemm(_ptr(oa[0]), _ptr(ob[0]), _ptr(out), _ptr(aux), _ptr(bias), _ptr(residual), M, N, K, oa[2], ob[2],
+                     out.stride(0), 0 if aux is None else aux.stride(0), 0 if residual is None else residual.stride(0),
+                     oa[1], ob[1], _DT[a.dtype], bias_fp32, out_fp32, int(act), 1 if atomic else 0, splits, float(alpha),
+                     bn, num_sms(), _stream())
+    _check(rc, "dl4j_gemm")
+    return out
+
+
+class _MatmulFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return gemm_raw(a, b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        a, b = ctx.saved_tensors
+        dy = dy if dy.stride(1) == 1 or dy.stride(0) == 1 else dy.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = gemm(dy, b.t())
+        if ctx.needs_input_grad[1]:
+            db = gemm(a.t(), dy)
+        return da, db
+
+
+def gemm(a, b):
+    """Differentiable 2-D matmul on the tcgen05 kernel (falls back to torch for odd layouts)."""
+    if not gemm_supported(a, b):
+        return torch.matmul(a, b)
+    if torch.is_grad_enabled() and (a.requires_grad or b.requires_grad):
+        return _MatmulFn.apply(a, b)
+    return gemm_raw(a, b)
+
+
+# =========================================================================== Linear (+bias +activation)
+def _act_id(activation):
+    if activation is None:
+        return 0
+    name = type(activation).__name__
+    if name == "ActivationGELU":
+        return 2 if getattr(activation, "precise", False) else 3
+    if name == "ActivationReLU":
+        if getattr(activation, "max", None) is not None or getattr(activation, "threshold", None) or getattr(activation, "negativeSlope", None):
+            return None
+        return 1
+    return _ACT_IDS.get(name)
+
+
+def _wgrad_splits(n_out_tiles, K):
+    sms = num_sms()
+    if n_out_tiles >= sms:
+        return 1
+    return max(1, min((K + 63) // 64, (2 * sms) // max(n_out_tiles, 1), 32))
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = act(x @ W + b).  ``W`` is the fp32 (or bf16) leaf, ``W_lp`` its low-precision shadow used
+    by the GEMMs.  When ``W`` is a leaf with a preallocated row-major-transposed ``.grad`` view (the
+    DL4J 'f' layout inside the flat gradient buffer), the weight gradient is accumulated straight
+    into it by the GEMM epilogue (split-K vector reductions) and ``None`` is returned for it."""
+
+    @staticmethod
+    def forward(ctx, x, W, b, act, W_lp):
+        need_z = act in (2, 3, 4, 5)
+        z = torch.empty((x.shape[0], W_lp.shape[1]), dtype=x.dtype, device=x.device) if need_z and any(ctx.needs_input_grad) else None
+        y = gemm_raw(x, W_lp, bias=None if b is None else b.reshape(-1), act=act, aux=z)
+        ctx.act = act
+        ctx.has_bias = b is not None
+        ctx.W_ref = W
+        ctx.b_ref = b
+        ctx.save_for_backward(x, W_lp, z if z is not None else (y if act == 1 else None))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, W_lp, saved = ctx.saved_tensors
+        act = ctx.act
+        l = require()
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        M, N = dy.shape
+        W, b = ctx.W_ref, ctx.b_ref
+        # ---- dz and bias gradient
+        db = None
+        b_acc = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            if b.is_leaf and b.grad is not None and b.grad.dtype == torch.float32 and b.grad.is_contiguous():
+                b_acc = b.grad
+            else:
+                b_acc = torch.zeros(N, dtype=torch.float32, device=dy.device)
+                db = b_acc
+        if act != 0:
+            dz = torch.empty_like(dy)
+            zz = saved
+            if zz is None:
+                raise RuntimeError("linear backward: activation input was not saved")
+            rc = l.dl4j_bias_act_bwd(_ptr(dy), _ptr(zz), _ptr(dz), _ptr(b_acc), M, N, 1 if act == 1 else act, _DT[dy.dtype], _stream())
+            _check(rc, "dl4j_bias_act_bwd")
+        else:
+            dz = dy
+            if b_acc is not None:
+                rc = l.dl4j_bias_act_bwd(_ptr(dy), None, None, _ptr(b_acc), M, N, 0, _DT[dy.dtype], _stream())
+                _check(rc, "dl4j_bias_act_bwd")
+        if db is not None:
+            db = db.reshape(b.shape).to(b.dtype)
+        # ---- data gradient: dx = dz @ W^T
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_raw(dz, W_lp.t())
+        # ---- weight gradient: dW^T [nOut, nIn] = dz^T @ x
+        dW = None
+        if ctx.needs_input_grad[1]:
+            nIn = x.shape[1]
+            tiles = ((N + 127) // 128) * ((nIn + 255) // 256)
+            splits = _wgrad_splits(tiles, M)
+            g = W.grad if (W.is_leaf and W.grad is not None) else None
+            if g is not None and g.dtype == torch.float32 and g.dim() == 2 and g.stride(0) == 1 and g.stride(1) == nIn \
+                    and g.data_ptr() % 16 == 0 and nIn % 4 == 0:
+                gemm_raw(dz.t(), x, out=g.t(), atomic=True, splits=splits)
+            else:
+                dWt = gemm_raw(dz.t(), x, out_dtype=torch.float32, atomic=True, splits=splits)
+                dW = dWt.t().to(W.dtype)
+        return dx, dW, db, None, None
+
+
+def linear(x, W, b, activation):
+    """Fused linear on the tcgen05 GEMM; returns None when the case is not covered."""
+    if not available() or x.dim() != 2:
+        return None
+    act = _act_id(activation)
+    if act is None:
+        return None
+    W_lp = getattr(W, "_lp", None)
+    if W_lp is None:
+        W_lp = W if W.dtype == x.dtype else W.detach().to(x.dtype)
+        if W.stride(0) != 1 and W.stride(1) != 1:
+            return None
+    if W_lp.dtype != x.dtype:
+        return None
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if _operand_a(x) is None or _operand_b(W_lp) is None or _operand_b(W_lp.t()) is None:
+        return None
+    # wgrad needs x as an MN-major operand: row stride multiple of 8 elements, and dz^T likewise
+    if (W_lp.shape[1] % 8) or (x.shape[1] % 8):
+        return None
+    return _LinearFn.apply(x, W, b, act, W_lp)
+
+
+# =========================================================================== layer norm
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gain, bias, eps):
+        l = require()
+        shp = x.shape
+        C = shp[-1]
+        x2 = x.reshape(-1, C)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        g32 = gain.detach().float().contiguous()
+        b32 = bias.detach().float().contiguous() if bias is not None else None
+        rc = l.dl4j_layer_norm_fwd(_ptr(x2), None, _ptr(g32), _ptr(b32), _ptr(y), None, _ptr(mean), _ptr(rstd), rows, C,
+                                   float(eps), _DT[x.dtype], _stream())
+        _check(rc, "dl4j_layer_norm_fwd")
+        ctx.save_for_backward(x2, g32, mean, rstd)
+        ctx.refs = (gain, bias)
+        ctx.shape = shp
+        return y.reshape(shp)
+
+    @staticmethod
+    def backward(ctx, dy):
+        l = require()
+        x2, g32, mean, rstd = ctx.saved_tensors
+        gain, bias = ctx.refs
+        rows, C = x2.shape
+        dy2 = dy.reshape(rows, C)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+
+        def acc_for(p):
+            if p is None:
+                return None, None
+            if p.is_leaf and p.grad is not None and p.grad.dtype == torch.float32 and p.grad.is_contiguous():
+                return p.grad, None
+            t = torch.zeros(C, dtype=torch.float32, device=dy.device)
+            return t, t
+        gacc, gret = acc_for(gain)
+        bacc, bret = acc_for(bias)
+        rc = l.dl4j_layer_norm_bwd(_ptr(dy2), _ptr(x2), _ptr(g32), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(gacc), _ptr(bacc),
+                                   rows, C, _DT[x2.dtype], _stream())
+        _check(rc, "dl4j_layer_norm_bwd")
+        if gret is not None:
+            gret = gret.reshape(gain.shape).to(gain.dtype)
+        if bret is not None:
+            bret = bret.reshape(bias.shape).to(bias.dtype)
+        return dx.reshape(ctx.shape), gret, bret, None
+
+
+def layer_norm(x, gain, bias, eps):
+    C = x.shape[-1]
+    if not available() or C % 8 != 0 or C > 1024 or x.dtype not in _DT:
+        return None
+    return _LayerNormFn.apply(x, gain, bias, eps)
+
+
+# =========================================================================== softmax cross entropy
+class _SoftmaxXentFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, sparse):
+        l = require()
+        if not logits.is_contiguous():
+            logits = logits.contiguous()
+        rows, C = logits.shape
+        loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        need_grad = ctx.needs_input_grad[0]
+        grad = torch.empty_like(logits) if need_grad else None
+        if sparse:
+            idx = labels.reshape(-1).to(torch.int64).contiguous()
+            rc = l.dl4j_softmax_xent(_ptr(logits), None, _ptr(idx), _ptr(loss), _ptr(grad), rows, C, logits.stride(0), -100,
+                                     _DT[logits.dtype], _stream())
+        else:
+            lab = labels.to(logits.dtype).contiguous()
+            rc = l.dl4j_softmax_xent(_ptr(logits), _ptr(lab), None, _ptr(loss), _ptr(grad), rows, C, logits.stride(0), -100,
+                                     _DT[logits.dtype], _stream())
+        _check(rc, "dl4j_softmax_xent")
+        ctx.save_for_backward(grad)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (grad,) = ctx.saved_tensors
+        return grad * dloss.to(grad.dtype).unsqueeze(1), None, None
+
+
+def softmax_xent(logits, labels, sparse):
+    if not available() or logits.dim() != 2 or logits.dtype not in _DT:
+        return None
+    return _SoftmaxXentFn.apply(logits, labels, bool(sparse))
+
+
+# =========================================================================== LSTM cell
+class _LstmCellFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, c_prev):
+        l = require()
+        mb, n4 = z.shape
+        n = n4 // 4
+        z = z.contiguous()
+        c_prev = c_prev.contiguous()
+        h = torch.empty((mb, n), dtype=z.dtype, device=z.device)
+        c = torch.empty((mb, n), dtype=torch.float32, device=z.device)
+        need = any(ctx.needs_input_grad)
+        gates = torch.empty_like(z) if need else None
+        rc = l.dl4j_lstm_cell_fwd(_ptr(z), _ptr(c_prev), _ptr(h), _ptr(c), _ptr(gates), mb, n, _DT[z.dtype], _stream())
+        _check(rc, "dl4j_lstm_cell_fwd")
+        ctx.save_for_backward(gates, c, c_prev)
+        return h, c
+
+    @staticmethod
+    def backward(ctx, dh, dc):
+        l = require()
+        gates, c, c_prev = ctx.saved_tensors
+        mb, n = c.shape
+        dz = torch.empty_like(gates)
+        dc_prev = torch.empty_like(c)
+        dh = dh.contiguous() if dh is not None else None
+        dc = dc.contiguous().float() if dc is not None else None
+        rc = l.dl4j_lstm_cell_bwd(_ptr(dh), _ptr(dc), _ptr(gates), _ptr(c), _ptr(c_prev), _ptr(dz), _ptr(dc_prev), mb, n,
+                                  _DT[gates.dtype], _stream())
+        _check(rc, "dl4j_lstm_cell_bwd")
+        return dz, dc_prev
+
+
+def lstm_cell(z, c_prev):
+    if not available() or z.dtype not in _DT or c_prev.dtype != torch.float32:
+        return None
+    return _LstmCellFn.apply(z, c_prev)
+
+
+def attention(q, k, v, mask, scale):
+    from . import attention_native
+    return attention_native.attention(q, k, v, mask, scale)
+
+
+# =========================================================================== fused updater
+_SEG_FMT = "<qqqqqfffiii"     # offset, block_start, block_numel, state_off, shadow_off, l1, l2, wd, kernel_id, hyper, pad
+_CHUNK_FMT = "<qii"
+_CHUNK = 16384
+
+
+def _build_tables(upd, shadow_offsets):
+    """Static part of the segment / chunk tables for a MultiLayerUpdater."""
+    segs = upd.segments(0, 0)
+    block_ids = {}
+    seg_rows, chunks = [], []
+    for si, (off, numel, st_off, bn, bs, kid, lr, l1, l2, wd, cfg) in enumerate(segs):
+        hid = block_ids.setdefault(bs, len(block_ids))
+        seg_rows.append([off, bs, bn, st_off, shadow_offsets[si] if shadow_offsets is not None else 0, l1, l2, wd, kid, hid, 0])
+        o = 0
+        while o < numel:
+            c = min(_CHUNK, numel - o)
+            chunks.append(struct.pack(_CHUNK_FMT, off + o, c, si))
+            o += c
+    return seg_rows, b"".join(chunks), len(chunks), len(block_ids)
+
+
+def fused_update(upd, iteration, epoch, shadow=None, shadow_offsets=None, grad_scale=1.0, zero_grads=True) -> bool:
+    """One launch: regularisation + updater + params -= update (+ bf16 shadow refresh, + grad zeroing)."""
+    l = require()
+    if l is None:
+        return False
+    cache = getattr(upd, "_native_tables", None)
+    if cache is None or cache["shadow"] is not shadow_offsets:
+        seg_rows, chunk_bytes, n_chunks, n_hyper = _build_tables(upd, shadow_offsets)
+        if n_hyper > 8:
+            upd._native_tables = {"unsupported": True, "shadow": shadow_offsets}
+            return False
+        dev = upd.params.device
+        chunks_t = torch.frombuffer(bytearray(chunk_bytes), dtype=torch.uint8).to(dev)
+        cache = {"seg_rows": seg_rows, "chunks": chunks_t, "n_chunks": n_chunks, "n_hyper": n_hyper, "shadow": shadow_offsets,
+                 "segs_dev": None, "segs_key": None}
+        upd._native_tables = cache
+    if cache.get("unsupported"):
+        return False
+    # dynamic part: per-block hyper-parameters and any scheduled regularisation coefficients
+    segs = upd.segments(iteration, epoch)
+    hyper = np.zeros((8, 8), dtype=np.float32)
+    key = []
+    seen = {}
+    for si, (off, numel, st_off, bn, bs, kid, lr, l1, l2, wd, cfg) in enumerate(segs):
+        key.append((l1, l2, wd))
+        hid = seen.setdefault(bs, len(seen))
+        b1 = getattr(cfg, "beta1", 0.0); b2 = getattr(cfg, "beta2", 0.0); eps = getattr(cfg, "epsilon", 0.0)
+        from ..nn.updaters import _eps_t, Nesterovs, AdaMax
+        eps_t = 0.0
+        if hasattr(cfg, "beta1"):
+            eps_t = _eps_t(lr, b1, b2, iteration, eps, with_sqrt=not isinstance(cfg, AdaMax))
+        mu = cfg.currentMomentum(iteration, epoch) if isinstance(cfg, Nesterovs) else 0.0
+        rho = getattr(cfg, "rmsDecay", getattr(cfg, "rho", 0.0))
+        mb1t = 1.0 - b1 ** (iteration + 1) if b1 else 1.0
+        hyper[hid] = (lr, b1, b2, eps, eps_t, mb1t, mu, rho)
+    key = tuple(key)
+    if cache["segs_key"] != key:
+        rows = cache["seg_rows"]
+        buf = bytearray()
+        for r, (l1, l2, wd) in zip(rows, key):
+            buf += struct.pack(_SEG_FMT, r[0], r[1], r[2], r[3], r[4], l1, l2, wd, r[8], r[9], 0)
+        cache["segs_dev"] = torch.frombuffer(buf, dtype=torch.uint8).to(upd.params.device)
+        cache["segs_key"] = key
+    state = upd.state
+    hp = hyper.ctypes.data_as(ctypes.c_void_p)
+    rc = l.dl4j_fused_update(_ptr(upd.params), _ptr(upd.grads), _ptr(state) if state.numel() else None, _ptr(shadow),
+                             _ptr(cache["chunks"]), cache["n_chunks"], _ptr(cache["segs_dev"]), hp, cache["n_hyper"],
+                             float(grad_scale), 1 if zero_grads else 0, _stream())
+    _check(rc, "dl4j_fused_update")
+    upd._fused_zeroes_grads = bool(zero_grads)
+    return True
+
+
+def cast_to_bf16(src_f32, dst_bf16):
+    l = require()
+    rc = l.dl4j_cast_f32_bf16(_ptr(src_f32), _ptr(dst_bf16), src_f32.numel(), _stream())
+    _check(rc, "dl4j_cast_f32_bf16")
+
+
+# =========================================================================== gradient codecs
+def threshold_encode(x, tau, capacity=None, msg=None):
+    """In-place sparse threshold encode of fp32 ``x`` (residual stays in ``x``); returns the int32 message."""
+    l = require()
+    n = x.numel()
+    capacity = int(capacity if capacity is not None else n)
+    if msg is None:
+        msg = torch.empty(4 + capacity, dtype=torch.int32, device=x.device)
+    rc = l.dl4j_threshold_encode(_ptr(x), n, float(tau), _ptr(msg), capacity, _stream())
+    _check(rc, "dl4j_threshold_encode")
+    return msg
+
+
+def threshold_decode(msg, target, scale=1.0, atomics=False, capacity=None):
+    l = require()
+    capacity = int(capacity if capacity is not None else msg.numel() - 4)
+    rc = l.dl4j_threshold_decode(_ptr(msg), capacity, _ptr(target), target.numel(), float(scale), 1 if atomics else 0, _stream())
+    _check(rc, "dl4j_threshold_decode")
+    return target
+
+
+def bitmap_encode(x, tau, msg=None):
+    l = require()
+    n = x.numel()
+    if msg is None:
+        msg = torch.empty(4 + (n + 15) // 16, dtype=torch.int32, device=x.device)
+    rc = l.dl4j_bitmap_encode(_ptr(x), n, float(tau), _ptr(msg), _stream())
+    _check(rc, "dl4j_bitmap_encode")
+    return msg
+
+
+def bitmap_decode(msg, target, scale=1.0):
+    l = require()
+    rc = l.dl4j_bitmap_decode(_ptr(msg), _ptr(target), target.numel(), float(scale), _stream())
+    _check(rc, "dl4j_bitmap_decode")
+    return target

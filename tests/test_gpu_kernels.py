@@ -1,0 +1,247 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 reference."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from deeplearning4j_b200.ops import native
+    native.require()
+    assert native.available(), native.load_error()
+    yield native
+    native.check_status()
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 192), (384, 136, 328), (1000, 776, 520), (64, 72, 40)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_layouts(nat, a_mn, b_mn, shape, bn):
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K + a_mn * 2 + b_mn)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+    a = A.t().contiguous().t() if a_mn else A            # logical [M,K]; MN-major => stored [K,M]
+    b = B if b_mn else B.t().contiguous().t()            # logical [K,N]; K-major => stored [N,K]
+    ref = A.float() @ B.float()
+    out = nat.gemm_raw(a, b, block_n=bn)
+    torch.cuda.synchronize()
+    nat.check_status()
+    assert out.shape == (M, N)
+    assert _rel(out, ref) < 2e-2, (a_mn, b_mn, shape, bn, _rel(out, ref))
+
+
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4, 5])
+def test_gemm_epilogue(nat, act):
+    M, N, K = 512, 384, 256
+    g = torch.Generator(device="cuda").manual_seed(act)
+    A = (torch.randn(M, K, device="cuda", generator=g) * 0.5).bfloat16()
+    W = (torch.randn(N, K, device="cuda", generator=g) * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g)
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    z = A.float() @ W.float().t() + bias
+    f = {0: lambda v: v, 1: torch.relu, 2: lambda v: torch.nn.functional.gelu(v),
+         3: lambda v: torch.nn.functional.gelu(v, approximate="tanh"), 4: torch.sigmoid, 5: torch.tanh}[act]
+    ref = f(z) + res.float()
+    aux = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = nat.gemm_raw(A, W.t(), bias=bias, act=act, aux=aux, residual=res)
+    torch.cuda.synchronize()
+    assert _rel(out, ref) < 2e-2
+    assert _rel(aux, z) < 2e-2
+
+
+def test_gemm_fp32_out_splitk_atomic(nat):
+    M, N, K = 256, 512, 4096
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+    out = torch.ones(M, N, device="cuda")
+    nat.gemm_raw(A, B, out=out, atomic=True, splits=8)
+    ref = A.float() @ B.float() + 1.0
+    torch.cuda.synchronize()
+    assert _rel(out, ref) < 1e-2
+
+
+def test_gemm_fp16(nat):
+    A = torch.randn(256, 128, device="cuda").half()
+    B = torch.randn(128, 256, device="cuda").half()
+    out = nat.gemm_raw(A, B)
+    assert _rel(out, A.float() @ B.float()) < 1e-2
+
+
+def test_linear_autograd(nat):
+    from deeplearning4j_b200.nn.activations import Activation
+    M, nIn, nOut = 256, 128, 192
+    x = torch.randn(M, nIn, device="cuda").bfloat16().requires_grad_(True)
+    Wm = (torch.randn(nOut, nIn, device="cuda") * 0.1)
+    W = Wm.t().detach().requires_grad_(True)             # logical [nIn,nOut], DL4J 'f' layout
+    W.grad = torch.zeros(nOut, nIn, device="cuda").t()
+    b = torch.randn(1, nOut, device="cuda").requires_grad_(True)
+    b.grad = torch.zeros_like(b)
+    for name in ("IDENTITY", "RELU", "GELU", "TANH"):
+        act = Activation.get(name)
+        W.grad.zero_(); b.grad.zero_(); x.grad = None
+        y = nat.linear(x, W, b, act)
+        assert y is not None
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xr = x.detach().float().requires_grad_(True)
+        Wr = W.detach().float().bfloat16().float().requires_grad_(True)
+        br = b.detach().clone().requires_grad_(True)
+        yr = act(xr @ Wr + br)
+        yr.backward(dy.float())
+        torch.cuda.synchronize()
+        assert _rel(y, yr) < 2e-2, name
+        assert _rel(x.grad, xr.grad) < 3e-2, name
+        assert _rel(W.grad, Wr.grad) < 3e-2, name
+        assert _rel(b.grad, br.grad) < 3e-2, name
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layer_norm(nat, dtype):
+    R, C = 300, 768
+    x = torch.randn(R, C, device="cuda").to(dtype).requires_grad_(True)
+    g = torch.randn(C, device="cuda").requires_grad_(True)
+    b = torch.randn(C, device="cuda").requires_grad_(True)
+    y = nat.layer_norm(x, g, b, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    gr, br = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (C,), gr, br, 1e-5)
+    yr.backward(dy.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel(y, yr) < tol
+    assert _rel(x.grad, xr.grad) < tol
+    assert _rel(g.grad, gr.grad) < tol
+    assert _rel(b.grad, br.grad) < tol
+
+
+@pytest.mark.parametrize("C", [10, 1000, 30522])
+def test_softmax_xent(nat, C):
+    R = 64
+    z = torch.randn(R, C, device="cuda").requires_grad_(True)
+    idx = torch.randint(0, C, (R,), device="cuda")
+    lab = torch.nn.functional.one_hot(idx, C).float()
+    for sparse in (False, True):
+        z.grad = None
+        loss = nat.softmax_xent(z, idx if sparse else lab, sparse)
+        loss.mean().backward()
+        zr = z.detach().clone().requires_grad_(True)
+        lr = torch.nn.functional.cross_entropy(zr, idx, reduction="none")
+        lr.mean().backward()
+        assert _rel(loss, lr) < 1e-4
+        assert _rel(z.grad, zr.grad) < 1e-4
+
+
+def test_lstm_cell(nat):
+    from deeplearning4j_b200.ops import nnops
+    mb, n = 64, 256
+    z = torch.randn(mb, 4 * n, device="cuda").requires_grad_(True)
+    c0 = torch.randn(mb, n, device="cuda").requires_grad_(True)
+    h, c = nat.lstm_cell(z, c0)
+    (h.sum() + (c * c).sum()).backward()
+    zr, cr = z.detach().clone().requires_grad_(True), c0.detach().clone().requires_grad_(True)
+    nnops.set_force_torch(True)
+    try:
+        hr, c2 = nnops.lstm_cell(zr, cr)
+    finally:
+        nnops.set_force_torch(False)
+    (hr.sum() + (c2 * c2).sum()).backward()
+    assert _rel(h, hr) < 1e-4 and _rel(c, c2) < 1e-4
+    assert _rel(z.grad, zr.grad) < 1e-3 and _rel(c0.grad, cr.grad) < 1e-3
+
+
+@pytest.mark.parametrize("n", [1000, 65536 + 17, 3_000_001])
+def test_threshold_codec(nat, n):
+    from deeplearning4j_b200.parallel import codec
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g) * 1e-3
+    tau = 2e-3
+    x_cpu, x_gpu = x.clone(), x.clone().cuda()
+    m_cpu = codec.threshold_encode(x_cpu, tau)
+    m_gpu = codec.threshold_encode(x_gpu, tau)
+    torch.cuda.synchronize()
+    k = int(m_cpu[0])
+    assert int(m_gpu[0]) == k and int(m_gpu[1]) == n and int(m_gpu[3]) == 0
+    assert torch.equal(torch.sort(m_gpu[4:4 + k].cpu()).values, torch.sort(m_cpu[4:4 + k]).values)
+    assert torch.equal(x_gpu.cpu(), x_cpu)
+    t_cpu, t_gpu = torch.zeros(n), torch.zeros(n, device="cuda")
+    codec.threshold_decode(m_cpu, t_cpu)
+    codec.threshold_decode(m_gpu, t_gpu)
+    assert torch.equal(t_gpu.cpu(), t_cpu)
+    assert torch.allclose(t_cpu + x_cpu, x, atol=1e-7)
+
+
+@pytest.mark.parametrize("n", [16, 1000, 1_000_003])
+def test_bitmap_codec(nat, n):
+    from deeplearning4j_b200.parallel import codec
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g) * 1e-3
+    tau = 1e-3
+    x_cpu, x_gpu = x.clone(), x.clone().cuda()
+    m_cpu = codec.bitmap_encode(x_cpu, tau)
+    m_gpu = codec.bitmap_encode(x_gpu, tau)
+    torch.cuda.synchronize()
+    assert torch.equal(m_gpu.cpu(), m_cpu)
+    assert torch.equal(x_gpu.cpu(), x_cpu)
+    t_cpu, t_gpu = torch.zeros(n), torch.zeros(n, device="cuda")
+    codec.bitmap_decode(m_cpu, t_cpu)
+    codec.bitmap_decode(m_gpu, t_gpu)
+    assert torch.equal(t_gpu.cpu(), t_cpu)
+
+
+@pytest.mark.parametrize("upd_name", ["Sgd", "Nesterovs", "Adam", "AdaMax", "Nadam", "AMSGrad", "AdaBelief", "AdaGrad", "RmsProp", "AdaDelta"])
+def test_fused_update_matches_torch(nat, upd_name):
+    from deeplearning4j_b200 import nn
+    U = getattr(nn, upd_name)
+
+    def make(device):
+        conf = (nn.NeuralNetConfiguration.Builder().seed(7).updater(U()).l2(1e-3).weightDecay(1e-4).list()
+                .layer(nn.DenseLayer(nIn=40, nOut=24, activation="tanh"))
+                .layer(nn.OutputLayer("MCXENT", nIn=24, nOut=5, activation="softmax")).build())
+        net = nn.MultiLayerNetwork(conf)
+        net.device = torch.device(device)
+        return net.init()
+    cpu, gpu = make("cpu"), make("cpu")
+    gpu.to("cuda")
+    gpu.setParams(cpu.flat_params)
+    g = torch.Generator().manual_seed(3)
+    for it in range(4):
+        grad = torch.randn(cpu.numParams(), generator=g) * 0.1
+        cpu.flat_grads.copy_(grad); gpu.flat_grads.copy_(grad.cuda())
+        cpu._ensure_updater().update(it, 0, use_fused=False)
+        assert gpu._ensure_updater()._fused_update(it, 0)
+    torch.cuda.synchronize()
+    assert torch.allclose(gpu.flat_params.cpu(), cpu.flat_params, rtol=2e-5, atol=2e-6), upd_name
+    assert torch.allclose(gpu.updater.state.cpu(), cpu.updater.state, rtol=2e-5, atol=2e-6), upd_name
+
+
+def test_mlp_bf16_trains_on_gpu(nat):
+    from deeplearning4j_b200 import nn, DataType
+    conf = (nn.NeuralNetConfiguration.Builder().seed(1).updater(nn.Adam(1e-3)).computeDataType(DataType.BFLOAT16).list()
+            .layer(nn.DenseLayer(nIn=784, nOut=512, activation="relu"))
+            .layer(nn.DenseLayer(nIn=512, nOut=512, activation="relu"))
+            .layer(nn.OutputLayer("MCXENT", nIn=512, nOut=16, activation="softmax")).build())
+    net = nn.MultiLayerNetwork(conf)
+    net.device = torch.device("cuda")
+    net.init()
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(128, 784, generator=g).cuda()
+    y = torch.nn.functional.one_hot(torch.randint(0, 16, (128,), generator=g), 16).float().cuda()
+    before = nat.LAUNCHES
+    s0 = None
+    for i in range(40):
+        net.fit(x, y)
+        if i == 0:
+            s0 = net.score()
+    assert nat.LAUNCHES - before >= 40 * 8
+    assert net.score() < 0.3 * s0, (s0, net.score())
+    nat.check_status()
