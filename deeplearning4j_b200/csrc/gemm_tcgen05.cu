@@ -38,6 +38,10 @@ struct GemmParams {
   int fmt;                // 0 fp16, 1 bf16
   float alpha;
   int* status;
+  int batch1, batch2;     // two batch dimensions (1 when unused); batch index = b2 * batch1 + b1
+  long c_stride_b1, c_stride_b2;   // output batch strides in elements
+  int tma_store;          // epilogue stages tiles in shared memory and writes them with TMA (needs 16-byte aligned C rows)
+  int tma_aux;            // same for the auxiliary pre-activation output
 };
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
@@ -46,7 +50,9 @@ struct GemmSmem {
   static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BLOCK_N == 256) ? 4 : 6;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int EPI_SLAB = 32 * 128;                 // one warp's 32 rows x 128 bytes
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_SLAB;        // 4 epilogue warps x 2 ring buffers
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -88,12 +94,14 @@ __device__ __forceinline__ float unpack_hi(uint32_t u, int fmt) {
 template <int BLOCK_N, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
                     const GemmParams p) {
   using S = GemmSmem<BLOCK_N, A_MN, B_MN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint8_t* epi_smem = smem + STAGES * S::STAGE_BYTES;       // 1024-byte aligned (stage sizes are multiples of 1024)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + S::EPI_BYTES);
   uint64_t* full_bar = bars;                    // [STAGES]
   uint64_t* empty_bar = bars + STAGES;          // [STAGES]
   uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
@@ -107,7 +115,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int kb_total = (p.K + BLOCK_K - 1) / BLOCK_K;
   const int kb_per_split = (kb_total + p.splits - 1) / p.splits;
-  const int num_work = tiles_m * tiles_n * p.splits;
+  const int per_batch = tiles_m * tiles_n * p.splits;
+  const int num_work = per_batch * p.batch1 * p.batch2;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -138,7 +147,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-        const int tile = w / p.splits, split = w % p.splits;
+        const int batch = w / per_batch, wr = w % per_batch;
+        const int b1 = batch % p.batch1, b2 = batch / p.batch1;
+        const int tile = wr / p.splits, split = wr % p.splits;
         const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, kb_total);
@@ -149,18 +160,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
           if (!A_MN) {
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+            tma_load_4d(sa, &tmap_a, &full_bar[stage], k0, m0, b1, b2);
           } else {
 #pragma unroll
             for (int i = 0; i < BLOCK_M / 64; ++i)
-              tma_load_2d(sa + i * (64 * BLOCK_K * 2), &tmap_a, &full_bar[stage], m0 + i * 64, k0);
+              tma_load_4d(sa + i * (64 * BLOCK_K * 2), &tmap_a, &full_bar[stage], m0 + i * 64, k0, b1, b2);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            tma_load_4d(sb, &tmap_b, &full_bar[stage], k0, n0, b1, b2);
           } else {
 #pragma unroll
             for (int i = 0; i < BLOCK_N / 64; ++i)
-              tma_load_2d(sb + i * (64 * BLOCK_K * 2), &tmap_b, &full_bar[stage], n0 + i * 64, k0);
+              tma_load_4d(sb + i * (64 * BLOCK_K * 2), &tmap_b, &full_bar[stage], n0 + i * 64, k0, b1, b2);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -179,7 +190,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
-        const int split = w % p.splits;
+        const int split = (w % per_batch) % p.splits;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, kb_total);
         const int buf = it & 1;
@@ -211,7 +222,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     int it = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
-      const int tile = w / p.splits, split = w % p.splits;
+      const int batch = w / per_batch, wr = w % per_batch;
+      const long c_off = (long)(batch % p.batch1) * p.c_stride_b1 + (long)(batch / p.batch1) * p.c_stride_b2;
+      const int tile = wr / p.splits, split = wr % p.splits;
       const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
       const int kb0 = split * kb_per_split;
       const bool has_k = kb0 < min(kb0 + kb_per_split, kb_total);
@@ -223,6 +236,120 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < p.M;
       const uint32_t taddr_row = tmem_base + buf * BLOCK_N + ((uint32_t)(q * 32) << 16);
       const bool lead_split = split == 0;
+      if (p.tma_store) {
+        // -------- staged epilogue: registers -> swizzled smem slab (32 rows x 128 B per warp) -> TMA store / reduce
+        const int b1 = batch % p.batch1, b2 = batch / p.batch1;
+        uint8_t* ring = epi_smem + q * (2 * S::EPI_SLAB);
+        const int sw = lane & 7;
+        uint8_t* my_row0 = ring + lane * 128;
+        const int cols_per_store = p.out_fp32 ? 32 : 64;
+        int ring_idx = 0;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N; c += cols_per_store) {
+          if (n0 + c >= p.N) break;                                   // warp-uniform
+          const bool want_aux = p.aux != nullptr && p.tma_aux;
+          // buffers: without aux alternate the ring (one store may still be reading the other slab);
+          // with aux both slabs are filled in this iteration, so every earlier store must have been read.
+          if (lane == 0) { if (want_aux) bulk_wait_read<0>(); else bulk_wait_read<1>(); }
+          __syncwarp();
+          uint8_t* slab_out = my_row0 + (want_aux ? S::EPI_SLAB : ring_idx * S::EPI_SLAB);
+          uint8_t* slab_aux = my_row0;
+          const int halves = p.out_fp32 ? 1 : 2;
+#pragma unroll 1
+          for (int hf = 0; hf < halves; ++hf) {
+            const int col0 = n0 + c + hf * 32;
+            if (col0 >= p.N) break;                                   // warp-uniform; TMA clips the unwritten half
+            uint32_t r[32];
+            tmem_ld_32x32(taddr_row + c + hf * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = has_k ? __uint_as_float(r[j]) * p.alpha : 0.0f;
+            if (p.bias != nullptr && lead_split) {
+              if (col0 + 32 <= p.N) {
+                if (p.bias_fp32) {
+                  const float4* b4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+                  if ((reinterpret_cast<uintptr_t>(b4) & 15) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { const float4 t = __ldg(b4 + j); v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w; }
+                  } else {
+                    const float* b = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += __ldg(b + j);
+                  }
+                } else {
+                  const uint16_t* b = reinterpret_cast<const uint16_t*>(p.bias) + col0;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] += unpack_lo((uint32_t)b[j], p.fmt);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N)
+                    v[j] += p.bias_fp32 ? __ldg(reinterpret_cast<const float*>(p.bias) + col0 + j)
+                                        : unpack_lo((uint32_t)reinterpret_cast<const uint16_t*>(p.bias)[col0 + j], p.fmt);
+              }
+            }
+            if (want_aux) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 u = make_uint4(pack2(v[8 * j], v[8 * j + 1], p.fmt), pack2(v[8 * j + 2], v[8 * j + 3], p.fmt),
+                                           pack2(v[8 * j + 4], v[8 * j + 5], p.fmt), pack2(v[8 * j + 6], v[8 * j + 7], p.fmt));
+                *reinterpret_cast<uint4*>(slab_aux + (((hf * 4 + j) ^ sw) << 4)) = u;
+              }
+            }
+            if (p.act != 0) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+            }
+            if (p.residual != nullptr && lead_split && row_ok) {
+              const uint16_t* rs = reinterpret_cast<const uint16_t*>(p.residual) + (long)row * p.ld_res + col0;
+              if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(rs) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  const uint4 u = *reinterpret_cast<const uint4*>(rs + j);
+                  v[j] += unpack_lo(u.x, p.fmt); v[j + 1] += unpack_hi(u.x, p.fmt);
+                  v[j + 2] += unpack_lo(u.y, p.fmt); v[j + 3] += unpack_hi(u.y, p.fmt);
+                  v[j + 4] += unpack_lo(u.z, p.fmt); v[j + 5] += unpack_hi(u.z, p.fmt);
+                  v[j + 6] += unpack_lo(u.w, p.fmt); v[j + 7] += unpack_hi(u.w, p.fmt);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (col0 + j < p.N) v[j] += unpack_lo((uint32_t)rs[j], p.fmt);
+              }
+            }
+            if (p.out_fp32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(slab_out + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 u = make_uint4(pack2(v[8 * j], v[8 * j + 1], p.fmt), pack2(v[8 * j + 2], v[8 * j + 3], p.fmt),
+                                           pack2(v[8 * j + 4], v[8 * j + 5], p.fmt), pack2(v[8 * j + 6], v[8 * j + 7], p.fmt));
+                *reinterpret_cast<uint4*>(slab_out + (((hf * 4 + j) ^ sw) << 4)) = u;
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int r0 = m0 + q * 32;
+            if (r0 < p.M) {
+              if (want_aux) tma_store_4d(&tmap_aux, ring, n0 + c, r0, b1, b2);
+              uint8_t* src = ring + (want_aux ? S::EPI_SLAB : ring_idx * S::EPI_SLAB);
+              if (p.atomic_out) tma_reduce_add_4d(&tmap_c, src, n0 + c, r0, b1, b2);
+              else tma_store_4d(&tmap_c, src, n0 + c, r0, b1, b2);
+            }
+            bulk_commit();
+          }
+          ring_idx ^= 1;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N; c += 32) {
         const int col0 = n0 + c;
@@ -283,7 +410,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
           if (p.out_fp32) {
-            float* o = reinterpret_cast<float*>(p.C) + (long)row * p.ldc + col0;
+            float* o = reinterpret_cast<float*>(p.C) + c_off + (long)row * p.ldc + col0;
             const bool al = full_chunk && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
             if (p.atomic_out) {
               if (al) {
@@ -301,7 +428,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) o[j] = v[j];
             }
           } else {
-            uint16_t* o = reinterpret_cast<uint16_t*>(p.C) + (long)row * p.ldc + col0;
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.C) + c_off + (long)row * p.ldc + col0;
             if (full_chunk && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -319,6 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
+    if (lane == 0) bulk_wait<0>();          // staged tiles must have left shared memory before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -336,30 +464,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 using namespace dl4j;
 
 static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
-                     uint32_t box_inner, uint32_t box_outer) {
+                     uint32_t box_inner, uint32_t box_outer, uint64_t nb1 = 1, uint64_t nb2 = 1, uint64_t sb1_bytes = 0,
+                     uint64_t sb2_bytes = 0, CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
   dl4j_PFN_encodeTiled enc = dl4j_get_encode_tiled();
   if (!enc) return -1;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {row_stride_bytes};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t es[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+  // rank-4 map {inner, outer, batch1, batch2}; unit batch dims get a harmless 16-byte-multiple stride
+  if (sb1_bytes == 0) sb1_bytes = row_stride_bytes * outer;
+  if (sb2_bytes == 0) sb2_bytes = sb1_bytes * nb1;
+  cuuint64_t dims[4] = {inner, outer, nb1, nb2};
+  cuuint64_t strides[3] = {row_stride_bytes, sb1_bytes, sb2_bytes};
+  cuuint32_t box[4] = {box_inner, box_outer, 1, 1};
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+                       const GemmParams& p, int grid, cudaStream_t stream) {
   using S = GemmSmem<BLOCK_N, A_MN, B_MN>;
-  static bool attr_set = false;
   auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN>;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, p);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, tc, tx, p);
   return (int)cudaGetLastError();
 }
 
@@ -367,10 +496,11 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 //   a_mn = 0: A stored [M, K] (row stride lda);  a_mn = 1: A stored [K, M] (row stride lda)
 //   b_mn = 0: B stored [N, K] (row stride ldb);  b_mn = 1: B stored [K, N] (row stride ldb)
 // Alignment contract (checked): base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
-DL4J_API int dl4j_gemm(const void* A, const void* B, void* C, void* aux, const void* bias, const void* residual, int M,
-                       int N, int K, long lda, long ldb, long ldc, long ld_aux, long ld_res, int a_mn, int b_mn, int fmt,
-                       int bias_fp32, int out_fp32, int act, int atomic_out, int splits, float alpha, int block_n,
-                       int num_sms, void* stream_) {
+static int gemm_impl(const void* A, const void* B, void* C, void* aux, const void* bias, const void* residual, int M,
+                     int N, int K, long lda, long ldb, long ldc, long ld_aux, long ld_res, int a_mn, int b_mn, int fmt,
+                     int bias_fp32, int out_fp32, int act, int atomic_out, int splits, float alpha, int block_n,
+                     int num_sms, void* stream_, int batch1, int batch2, const long* a_bs, const long* b_bs,
+                     const long* c_bs) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7)) return -DL4J_ERR_BAD_ARG;
@@ -382,22 +512,66 @@ DL4J_API int dl4j_gemm(const void* A, const void* B, void* C, void* aux, const v
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ld_aux; p.ld_res = ld_res; p.C = C; p.aux = aux; p.bias = bias;
   p.residual = residual; p.bias_fp32 = bias_fp32; p.out_fp32 = out_fp32; p.act = act; p.atomic_out = atomic_out;
   p.splits = splits; p.fmt = fmt; p.alpha = alpha; p.status = dl4j_status_word(dev);
+  p.batch1 = batch1; p.batch2 = batch2; p.c_stride_b1 = c_bs[0]; p.c_stride_b2 = c_bs[1];
+  if ((a_bs[0] & 7) || (a_bs[1] & 7) || (b_bs[0] & 7) || (b_bs[1] & 7)) return -DL4J_ERR_BAD_ARG;
+  const uint64_t nb1 = batch1, nb2 = batch2;
   if (block_n != 128 && block_n != 256) block_n = 256;
   CUtensorMap ta, tb;
   int r;
-  if (!a_mn) r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BLOCK_K, BLOCK_M);
-  else       r = encode_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BLOCK_K);
+  if (!a_mn) r = encode_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BLOCK_K, BLOCK_M, nb1, nb2, a_bs[0] * 2, a_bs[1] * 2);
+  else       r = encode_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BLOCK_K, nb1, nb2, a_bs[0] * 2, a_bs[1] * 2);
   if (r) return r > 0 ? -1000 - r : r;
-  if (!b_mn) r = encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BLOCK_K, (uint32_t)block_n);
-  else       r = encode_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BLOCK_K);
+  if (!b_mn) r = encode_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BLOCK_K, (uint32_t)block_n, nb1, nb2, b_bs[0] * 2, b_bs[1] * 2);
+  else       r = encode_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BLOCK_K, nb1, nb2, b_bs[0] * 2, b_bs[1] * 2);
   if (r) return r > 0 ? -1000 - r : r;
-  const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n) * splits;
+  // output maps: a 32-row x 128-byte box per epilogue warp (64 16-bit or 32 fp32 columns)
+  CUtensorMap tc, tx;
+  memset(&tc, 0, sizeof(tc));
+  memset(&tx, 0, sizeof(tx));
+  const int esz = out_fp32 ? 4 : 2;
+  p.tma_store = 0; p.tma_aux = 0;
+  if (!(reinterpret_cast<uintptr_t>(C) & 15) && ((ldc * esz) % 16 == 0) && ((c_bs[0] * esz) % 16 == 0) && ((c_bs[1] * esz) % 16 == 0) &&
+      (!aux || (!(reinterpret_cast<uintptr_t>(aux) & 15) && (ld_aux * 2) % 16 == 0))) {
+    r = encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * esz, out_fp32 ? 32 : 64, 32, nb1, nb2, c_bs[0] * esz,
+                  c_bs[1] * esz, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+    if (r == 0) p.tma_store = 1;
+    if (r == 0 && aux) {
+      r = encode_2d(&tx, aux, (uint64_t)N, (uint64_t)M, (uint64_t)ld_aux * 2, 64, 32, 1, 1, 0, 0);
+      if (r == 0) p.tma_aux = 1; else p.tma_store = 0;
+    }
+  }
+  const long tiles_l = (long)((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n) * splits * batch1 * batch2;
+  if (tiles_l > 0x7fffffffL) return -DL4J_ERR_BAD_ARG;
+  const int tiles = (int)tiles_l;
   if (num_sms <= 0) num_sms = 148;
   const int grid = tiles < num_sms ? tiles : num_sms;
 #define DL4J_GEMM_CASE(BN, AM, BM) \
-  if (block_n == BN && a_mn == AM && b_mn == BM) return launch_gemm<BN, AM != 0, BM != 0>(ta, tb, p, grid, stream);
+  if (block_n == BN && a_mn == AM && b_mn == BM) return launch_gemm<BN, AM != 0, BM != 0>(ta, tb, tc, tx, p, grid, stream);
   DL4J_GEMM_CASE(256, 0, 0) DL4J_GEMM_CASE(256, 0, 1) DL4J_GEMM_CASE(256, 1, 0) DL4J_GEMM_CASE(256, 1, 1)
   DL4J_GEMM_CASE(128, 0, 0) DL4J_GEMM_CASE(128, 0, 1) DL4J_GEMM_CASE(128, 1, 0) DL4J_GEMM_CASE(128, 1, 1)
 #undef DL4J_GEMM_CASE
   return -DL4J_ERR_BAD_ARG;
+}
+
+// C[M,N] = act(alpha * A·B + bias) (+ residual)
+//   a_mn = 0: A stored [M, K] (row stride lda);  a_mn = 1: A stored [K, M] (row stride lda)
+//   b_mn = 0: B stored [N, K] (row stride ldb);  b_mn = 1: B stored [K, N] (row stride ldb)
+// Alignment contract (checked): base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
+DL4J_API int dl4j_gemm(const void* A, const void* B, void* C, void* aux, const void* bias, const void* residual, int M,
+                       int N, int K, long lda, long ldb, long ldc, long ld_aux, long ld_res, int a_mn, int b_mn, int fmt,
+                       int bias_fp32, int out_fp32, int act, int atomic_out, int splits, float alpha, int block_n,
+                       int num_sms, void* stream_) {
+  const long z[2] = {0, 0};
+  return gemm_impl(A, B, C, aux, bias, residual, M, N, K, lda, ldb, ldc, ld_aux, ld_res, a_mn, b_mn, fmt, bias_fp32, out_fp32,
+                   act, atomic_out, splits, alpha, block_n, num_sms, stream_, 1, 1, z, z, z);
+}
+
+// Batched form: batch index (b1, b2) with per-operand element strides {stride_b1, stride_b2} (multiples of 8 for A and B).
+// Used for attention (batch = [heads, examples] over strided views of the fused QKV buffer) and batched_gemm.
+DL4J_API int dl4j_gemm_batched(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                               int a_mn, int b_mn, int fmt, int out_fp32, float alpha, int block_n, int num_sms,
+                               int batch1, int batch2, const long* a_bs, const long* b_bs, const long* c_bs, void* stream_) {
+  if (batch1 < 1 || batch2 < 1) return 0;
+  return gemm_impl(A, B, C, nullptr, nullptr, nullptr, M, N, K, lda, ldb, ldc, 0, 0, a_mn, b_mn, fmt, 0, out_fp32, 0, 0, 1,
+                   alpha, block_n, num_sms, stream_, batch1, batch2, a_bs, b_bs, c_bs);
 }

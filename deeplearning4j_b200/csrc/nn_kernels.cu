@@ -361,6 +361,89 @@ bias_act_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __rest
   }
 }
 
+// ----------------------------------------------------------------------------- attention softmax
+// In-place row softmax over scores S [rows, Tk] (already scaled by the GEMM epilogue) with an optional
+// key mask [B, Tk] (non-zero = keep); row r belongs to example r / rows_per_example.  One warp per row.
+template <typename T>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+attn_softmax_fwd_kernel(T* __restrict__ S, const float* __restrict__ key_mask, long long rows, int Tk, int rows_per_example) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = Tk / 8;
+  T* sr = S + row * Tk;
+  const float* mk = key_mask ? key_mask + (row / rows_per_example) * Tk : nullptr;
+  float v[LN_MAXV][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      Vec8<T>::load(sr + vi * 8, v[i]);
+      if (mk) {
+        float m[8];
+        Vec8<float>::load(mk + vi * 8, m);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (m[j] == 0.f) v[i][j] = -INFINITY;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, v[i][j]);
+    }
+  }
+  mx = warp_max(mx);
+  if (mx == -INFINITY) mx = 0.f;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i)
+    if (lane + i * 32 < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[i][j] = __expf(v[i][j] - mx); s += v[i][j]; }
+    }
+  s = warp_sum(s);
+  const float inv = s > 0.f ? 1.f / s : 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] *= inv;
+      Vec8<T>::store(sr + vi * 8, v[i]);
+    }
+  }
+}
+
+// dS = scale * P * (dP - sum_j dP_j P_j), written over dP.
+template <typename T>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+attn_softmax_bwd_kernel(const T* __restrict__ P, T* __restrict__ dP, long long rows, int Tk, float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = Tk / 8;
+  float p[LN_MAXV][8], d[LN_MAXV][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      Vec8<T>::load(P + row * Tk + vi * 8, p[i]);
+      Vec8<T>::load(dP + row * Tk + vi * 8, d[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += p[i][j] * d[i][j];
+    }
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int i = 0; i < LN_MAXV; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d[i][j] = scale * p[i][j] * (d[i][j] - dot);
+      Vec8<T>::store(dP + row * Tk + vi * 8, d[i]);
+    }
+  }
+}
+
 }  // namespace dl4j
 
 using namespace dl4j;
@@ -431,5 +514,24 @@ DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* d
   dim3 grid(col_tiles, row_slabs);
   DL4J_DISPATCH_T(dtype, (bias_act_bwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
       (const T*)dy, (const T*)z, (T*)dz, dbias, rows, C, act, rpb)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_attn_softmax_fwd(void* S, const float* key_mask, long long rows, int Tk, int rows_per_example, int dtype,
+                                   void* stream) {
+  if (rows <= 0) return 0;
+  if (Tk % 8 != 0 || Tk > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
+  const long long grid = (rows + LN_WARPS - 1) / LN_WARPS;
+  DL4J_DISPATCH_T(dtype, (attn_softmax_fwd_kernel<T><<<(unsigned)grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (T*)S, key_mask, rows, Tk, rows_per_example)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_attn_softmax_bwd(const void* P, void* dP, long long rows, int Tk, float scale, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  if (Tk % 8 != 0 || Tk > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
+  const long long grid = (rows + LN_WARPS - 1) / LN_WARPS;
+  DL4J_DISPATCH_T(dtype, (attn_softmax_bwd_kernel<T><<<(unsigned)grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(
+      (const T*)P, (T*)dP, rows, Tk, scale)));
   return (int)cudaGetLastError();
 }

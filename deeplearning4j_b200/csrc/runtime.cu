@@ -58,3 +58,18 @@ DL4J_API int dl4j_num_sms() {
 }
 
 DL4J_API int dl4j_abi_version() { return 1; }
+
+// Binds `device`'s primary context to the calling thread for this library's runtime instance.  The
+// library is linked against its own (static) CUDA runtime; a thread that has only used another runtime
+// instance so far (e.g. an autograd worker thread) may have no context bound yet, and driver entry
+// points such as cuTensorMapEncodeTiled then fail with CUDA_ERROR_INVALID_CONTEXT.
+DL4J_API int dl4j_bind_device(int device) {
+  static thread_local int bound = -1;
+  if (bound == device) return 0;
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFree(nullptr);
+  if (e != cudaSuccess) return (int)e;
+  bound = device;
+  return 0;
+}

@@ -1,7 +1,137 @@
-"""Attention on the native kernels.  Returns None when a case is not covered so that the
-caller falls back to the reference torch formulation."""
+"""Scaled dot-product attention on the native kernels.
+
+Reference formulation: ``libnd4j/include/helpers/impl/AttentionHelper.cpp:189-470`` (matmul,
+scale, mask add, softmax over the full score matrix, matmul) and the ``dot_product_attention``
+/ ``multi_head_dot_product_attention`` ops.  Here every matmul is one launch of the batched
+tcgen05 GEMM over strided views of the packed projection buffer (no transposes, no per-head
+copies), the scale is folded into the GEMM epilogue, masking + softmax is one in-place fused
+kernel, and the backward pass is four batched GEMMs plus one fused softmax-gradient kernel.
+The output is produced directly in ``[B, Tq, H, D]`` memory order so the following
+``[B*Tq, H*D]`` reshape for the output projection is free.
+"""
 from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import native
+
+_LONG2 = ctypes.c_long * 2
+
+
+def _ok_view(t):
+    """[B, H, T, D] view usable by a rank-4 tensor map: unit inner stride, 16-byte aligned strides."""
+    return (t.dim() == 4 and t.stride(3) == 1 and t.stride(2) % 8 == 0 and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0 and t.shape[3] % 8 == 0)
+
+
+def _prep(t):
+    return t if _ok_view(t) else t.contiguous()
+
+
+def _bgemm(l, A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, alpha, H, Bn, a_bs, b_bs, c_bs, dtype, out_fp32=0):
+    if not hasattr(l.dl4j_gemm_batched, "_typed"):
+        vp, i32, lng, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+        l.dl4j_gemm_batched.argtypes = [vp, vp, vp, i32, i32, i32, lng, lng, lng, i32, i32, i32, i32, f32, i32, i32, i32, i32,
+                                        ctypes.POINTER(ctypes.c_long), ctypes.POINTER(ctypes.c_long),
+                                        ctypes.POINTER(ctypes.c_long), vp]
+        l.dl4j_gemm_batched.restype = ctypes.c_int
+        l.dl4j_gemm_batched._typed = True
+    bn = 256 if N > 128 else 128
+    rc = l.dl4j_gemm_batched(ctypes.c_void_p(A), ctypes.c_void_p(B), ctypes.c_void_p(C), M, N, K, lda, ldb, ldc, a_mn, b_mn,
+                             native._DT[dtype], out_fp32, float(alpha), bn, native.num_sms(), H, Bn, _LONG2(*a_bs),
+                             _LONG2(*b_bs), _LONG2(*c_bs), native._stream())
+    native._check(rc, "dl4j_gemm_batched")
+
+
+def _typed_softmax(l):
+    if not hasattr(l.dl4j_attn_softmax_fwd, "_typed"):
+        vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        l.dl4j_attn_softmax_fwd.argtypes = [vp, vp, i64, i32, i32, i32, vp]
+        l.dl4j_attn_softmax_fwd.restype = ctypes.c_int
+        l.dl4j_attn_softmax_bwd.argtypes = [vp, vp, i64, i32, f32, i32, vp]
+        l.dl4j_attn_softmax_bwd.restype = ctypes.c_int
+        l.dl4j_attn_softmax_fwd._typed = True
+
+
+class _AttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, key_mask, scale):
+        l = native.require()
+        _typed_softmax(l)
+        q, k, v = _prep(q), _prep(k), _prep(v)
+        Bn, H, Tq, D = q.shape
+        Tk = k.shape[2]
+        dt = q.dtype
+        P = torch.empty((Bn, H, Tq, Tk), dtype=dt, device=q.device)
+        # S = scale * Q K^T
+        _bgemm(l, q.data_ptr(), k.data_ptr(), P.data_ptr(), Tq, Tk, D, q.stride(2), k.stride(2), Tk, 0, 0, scale, H, Bn,
+               (q.stride(1), q.stride(0)), (k.stride(1), k.stride(0)), (Tq * Tk, H * Tq * Tk), dt)
+        mk = None
+        if key_mask is not None:
+            mk = key_mask.to(torch.float32).contiguous()
+        rc = l.dl4j_attn_softmax_fwd(native._ptr(P), native._ptr(mk), Bn * H * Tq, Tk, H * Tq, native._DT[dt], native._stream())
+        native._check(rc, "dl4j_attn_softmax_fwd")
+        # O = P V, written as [B, Tq, H, D]
+        O = torch.empty((Bn, Tq, H, D), dtype=dt, device=q.device)
+        _bgemm(l, P.data_ptr(), v.data_ptr(), O.data_ptr(), Tq, D, Tk, Tk, v.stride(2), H * D, 0, 1, 1.0, H, Bn,
+               (Tq * Tk, H * Tq * Tk), (v.stride(1), v.stride(0)), (D, Tq * H * D), dt)
+        ctx.save_for_backward(q, k, v, P)
+        ctx.scale = scale
+        return O.permute(0, 2, 1, 3)
+
+    @staticmethod
+    def backward(ctx, dO):
+        l = native.require()
+        q, k, v, P = ctx.saved_tensors
+        Bn, H, Tq, D = q.shape
+        Tk = k.shape[2]
+        dt = q.dtype
+        dO = _prep(dO)
+        same_len = Tq == Tk
+        # packed gradient buffer [B, T, 3, H, D] when possible so the three results share one allocation
+        if same_len:
+            dqkv = torch.empty((Bn, Tq, 3, H, D), dtype=dt, device=q.device)
+            dq_t, dk_t, dv_t = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]          # [B, T, H, D] views
+        else:
+            dq_t = torch.empty((Bn, Tq, H, D), dtype=dt, device=q.device)
+            dk_t = torch.empty((Bn, Tk, H, D), dtype=dt, device=q.device)
+            dv_t = torch.empty((Bn, Tk, H, D), dtype=dt, device=q.device)
+        pbs = (Tq * Tk, H * Tq * Tk)
+
+        def obs(t):   # batch strides (head, example) and row stride of a [B, T, H, D] output view
+            return (t.stride(2), t.stride(0)), t.stride(1)
+        # dV = P^T dO
+        cbs, ldc = obs(dv_t)
+        _bgemm(l, P.data_ptr(), dO.data_ptr(), dv_t.data_ptr(), Tk, D, Tq, Tk, dO.stride(2), ldc, 1, 1, 1.0, H, Bn,
+               pbs, (dO.stride(1), dO.stride(0)), cbs, dt)
+        # dP = dO V^T
+        dP = torch.empty_like(P)
+        _bgemm(l, dO.data_ptr(), v.data_ptr(), dP.data_ptr(), Tq, Tk, D, dO.stride(2), v.stride(2), Tk, 0, 0, 1.0, H, Bn,
+               (dO.stride(1), dO.stride(0)), (v.stride(1), v.stride(0)), pbs, dt)
+        rc = l.dl4j_attn_softmax_bwd(native._ptr(P), native._ptr(dP), Bn * H * Tq, Tk, float(ctx.scale), native._DT[dt],
+                                     native._stream())
+        native._check(rc, "dl4j_attn_softmax_bwd")
+        # dQ = dS K
+        cbs, ldc = obs(dq_t)
+        _bgemm(l, dP.data_ptr(), k.data_ptr(), dq_t.data_ptr(), Tq, D, Tk, Tk, k.stride(2), ldc, 0, 1, 1.0, H, Bn,
+               pbs, (k.stride(1), k.stride(0)), cbs, dt)
+        # dK = dS^T Q
+        cbs, ldc = obs(dk_t)
+        _bgemm(l, dP.data_ptr(), q.data_ptr(), dk_t.data_ptr(), Tk, D, Tq, Tk, q.stride(2), ldc, 1, 1, 1.0, H, Bn,
+               pbs, (q.stride(1), q.stride(0)), cbs, dt)
+        return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None
 
 
 def attention(q, k, v, mask, scale):
-    return None
+    """q, k, v: [B, H, T, D]; ``mask``: None or a [B, Tk] key mask (non-zero = attend)."""
+    if not native.available() or q.dim() != 4 or q.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    if mask is not None and (mask.dim() != 2 or mask.shape[0] != q.shape[0] or mask.shape[1] != k.shape[2]):
+        return None
+    D, Tk, Tq = q.shape[3], k.shape[2], q.shape[2]
+    if D % 8 or Tk % 8 or Tq % 8 or Tk > 1024:
+        return None
+    scale = float(scale) if scale is not None else D ** -0.5
+    return _AttentionFn.apply(q, k, v, mask, scale)

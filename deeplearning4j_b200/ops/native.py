@@ -59,6 +59,7 @@ def _load():
             "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
+            "dl4j_bind_device": [i32],
             "dl4j_abi_version": [],
         }
         for name, args in sig.items():
@@ -97,6 +98,11 @@ def _ptr(t):
 
 
 def _stream():
+    """Current torch stream handle; also binds the current device's context to this thread for the
+    library's own CUDA runtime instance (autograd worker threads may not have one bound yet)."""
+    rc = _LIB.dl4j_bind_device(torch.cuda.current_device())
+    if rc != 0:
+        raise RuntimeError(f"dl4j_bind_device failed with CUDA error {rc}")
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -262,6 +268,8 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, W, b, act, W_lp):
         need_z = act in (2, 3, 4, 5)
         z = torch.empty((x.shape[0], W_lp.shape[1]), dtype=x.dtype, device=x.device) if need_z and any(ctx.needs_input_grad) else None
+        W = getattr(W, "_master", W)          # accumulate weight/bias gradients straight into the fp32 masters
+        b = getattr(b, "_master", b) if b is not None else None
         y = gemm_raw(x, W_lp, bias=None if b is None else b.reshape(-1), act=act, aux=z)
         ctx.act = act
         ctx.has_bias = b is not None
@@ -316,6 +324,11 @@ class _LinearFn(torch.autograd.Function):
             if g is not None and g.dtype == torch.float32 and g.dim() == 2 and g.stride(0) == 1 and g.stride(1) == nIn \
                     and g.data_ptr() % 16 == 0 and nIn % 4 == 0:
                 gemm_raw(dz.t(), x, out=g.t(), atomic=True, splits=splits)
+            elif g is not None and g.dtype == torch.float32 and g.dim() == 2 and g.is_contiguous() and g.data_ptr() % 16 == 0 \
+                    and N % 4 == 0:
+                # row-major [nIn, nOut] master (SameDiff variables): dW = x^T dz accumulated in place
+                tiles2 = ((nIn + 127) // 128) * ((N + 255) // 256)
+                gemm_raw(x.t(), dz, out=g, atomic=True, splits=_wgrad_splits(tiles2, M))
             else:
                 dWt = gemm_raw(dz.t(), x, out_dtype=torch.float32, atomic=True, splits=splits)
                 dW = dWt.t().to(W.dtype)
@@ -331,7 +344,7 @@ def linear(x, W, b, activation):
         return None
     W_lp = getattr(W, "_lp", None)
     if W_lp is None:
-        W_lp = W if W.dtype == x.dtype else W.detach().to(x.dtype)
+        W_lp = W.detach() if W.dtype == x.dtype else W.detach().to(x.dtype)
         if W.stride(0) != 1 and W.stride(1) != 1:
             return None
     if W_lp.dtype != x.dtype:
@@ -360,8 +373,10 @@ class _LayerNormFn(torch.autograd.Function):
         y = torch.empty_like(x2)
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        g32 = gain.detach().float().contiguous()
-        b32 = bias.detach().float().contiguous() if bias is not None else None
+        gain = getattr(gain, "_master", gain)
+        bias = getattr(bias, "_master", bias) if bias is not None else None
+        g32 = gain.detach().float().contiguous().reshape(-1)
+        b32 = bias.detach().float().contiguous().reshape(-1) if bias is not None else None
         rc = l.dl4j_layer_norm_fwd(_ptr(x2), None, _ptr(g32), _ptr(b32), _ptr(y), None, _ptr(mean), _ptr(rstd), rows, C,
                                    float(eps), _DT[x.dtype], _stream())
         _check(rc, "dl4j_layer_norm_fwd")

@@ -1,0 +1,54 @@
+"""Batched tcgen05 GEMM attention vs the fp32 torch formulation."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.detach().float() - b.detach().float()).abs().max() / (b.detach().float().abs().max() + 1e-6))
+
+
+def _ref(q, k, v, mask, scale):
+    s = (q.float() @ k.float().transpose(-1, -2)) * scale
+    if mask is not None:
+        s = s.masked_fill(mask[:, None, None, :] == 0, float("-inf"))
+    return torch.softmax(s, -1) @ v.float()
+
+
+@pytest.mark.parametrize("B,H,T,D", [(2, 3, 128, 64), (1, 12, 512, 64), (3, 2, 136, 32)])
+@pytest.mark.parametrize("packed", [True, False])
+@pytest.mark.parametrize("use_mask", [False, True])
+def test_attention_fwd_bwd(B, H, T, D, packed, use_mask):
+    from deeplearning4j_b200.ops import native, attention_native
+    native.require()
+    g = torch.Generator(device="cuda").manual_seed(B * 100 + T + D)
+    if packed:
+        qkv = (torch.randn(B, T, 3, H, D, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    else:
+        q, k, v = ((torch.randn(B, H, T, D, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True) for _ in range(3))
+    mask = None
+    if use_mask:
+        mask = (torch.rand(B, T, device="cuda", generator=g) > 0.3).float()
+        mask[:, 0] = 1
+    scale = D ** -0.5
+    o = attention_native.attention(q, k, v, mask, scale)
+    assert o is not None and o.shape == (B, H, T, D)
+    do = torch.randn(B, H, T, D, device="cuda", generator=g).bfloat16()
+    o.backward(do)
+    torch.cuda.synchronize()
+    native.check_status()
+    if packed:
+        qr = qkv.detach().float().requires_grad_(True)
+        q2, k2, v2 = (qr[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    else:
+        q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf = _ref(q2, k2, v2, mask, scale)
+    orf.backward(do.float())
+    assert _rel(o, orf) < 3e-2
+    if packed:
+        assert _rel(qkv.grad, qr.grad) < 4e-2
+    else:
+        for a, b in ((q, q2), (k, k2), (v, v2)):
+            assert _rel(a.grad, b.grad) < 4e-2
