@@ -1,0 +1,452 @@
+// Fused gradient-sharing kernels over NVLink / NVSwitch peer memory (one rank per GPU, up to 8 ranks).
+//
+// The reference's multi-GPU primitives are single-process kernels that dereference an array of per-device
+// pointers (libnd4j/include/loops/cuda/specials/averagingKernel.cu:29-76, accumulateKernel.cu:38-70) plus the
+// threshold/bitmap codec (loops/cuda/type_conversions.cu:215-500); the training-side logic that used them
+// (parameter averaging, threshold-encoded gradient sharing) is rebuilt here as two persistent kernels:
+//
+//  * allreduce_update_kernel ("dense averaging"): reduce-scatter of the gradients by peer loads (or
+//    multimem.ld_reduce through the switch) -> regularisation + updater + step on the owned slice ->
+//    all-gather of the new parameters (fp32 master + bf16 shadow) by peer stores (or multimem.st), then the
+//    local gradient buffer is cleared.  One launch per step instead of allreduce + updater + broadcast.
+//  * threshold_share_kernel ("shared gradients"): updater on the local gradient, accumulate into the
+//    residual, bitmap-encode the residual into this rank's message slot, exchange by peer loads, decode the
+//    sum of every rank's message and apply it to the local parameters.
+//
+// Synchronisation: cross-GPU barriers are release/acquire flags in every rank's signal pad, grid-wide
+// barriers are atomic counters in local scratch.  Every wait is bounded; on expiry the kernel records
+// DL4J_ERR_TIMEOUT_PEER in the status word, skips the remaining phases and returns.
+// No TMA is used here at all (and in particular no cluster-multicast load of peer memory).
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "updater_math.cuh"
+
+namespace dl4j {
+
+constexpr int MAX_RANKS = 8;
+constexpr int COMM_THREADS = 512;
+
+struct CommCtx {
+  int rank, world;
+  float* grads[MAX_RANKS];
+  float* params[MAX_RANKS];
+  __nv_bfloat16* shadow[MAX_RANKS];
+  uint32_t* signal[MAX_RANKS];     // per rank: [slots][MAX_RANKS] flags
+  int* msg[MAX_RANKS];             // threshold sharing: per rank message slot
+  float* mc_grads;                 // multicast (NVLS) addresses, null when unavailable
+  float* mc_params;
+  __nv_bfloat16* mc_shadow;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_peer_f(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_peer_i(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st_b64(void* mc, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)) : "memory");
+}
+
+// Cross-GPU barrier executed by block 0: thread t signals rank t and waits for rank t's signal.
+// `epoch` must increase monotonically per slot.  Returns false (for the whole block) on timeout.
+__device__ bool peer_barrier(const CommCtx& c, int slot, uint32_t epoch, int* status) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.signal[threadIdx.x] + slot * MAX_RANKS + c.rank, epoch);
+    const uint32_t* mine = c.signal[c.rank] + slot * MAX_RANKS + threadIdx.x;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && (clock64() - t0 > 2000000000LL || *((volatile int*)status) != 0)) {
+        atomicCAS(status, 0, DL4J_ERR_TIMEOUT_PEER);
+        ok_flag = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+// Grid-wide barrier on a monotonically increasing counter in local scratch (all blocks co-resident:
+// cooperative launch).  `target` = gridDim.x * (number of barriers passed so far + 1).
+__device__ bool grid_barrier(unsigned int* counter, unsigned int target, int* status) {
+  __shared__ int ok_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok_flag = 1;
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (*((volatile unsigned int*)counter) < target) {
+      if ((++spins & 0xff) == 0 && (clock64() - t0 > 4000000000LL || *((volatile int*)status) != 0)) {
+        atomicCAS(status, 0, DL4J_ERR_TIMEOUT_PEER);
+        ok_flag = 0;
+        break;
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+// ------------------------------------------------------------------------------------------------ K2
+// scratch[0] = grid barrier counter (zeroed by the host before every launch)
+__global__ void __launch_bounds__(COMM_THREADS)
+allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChunk* __restrict__ chunks, int n_chunks,
+                        const UpdSegment* __restrict__ segs, const UpdHyperTable ht, float grad_scale, long long n_total,
+                        uint32_t epoch, unsigned int* scratch, int use_multimem, int* status) {
+  unsigned int bar = 0;
+  bool ok = true;
+  // ---- phase 0: every rank has finished writing its gradients
+  if (blockIdx.x == 0) ok = peer_barrier(c, 0, epoch, status);
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok && *((volatile int*)status) == 0;
+
+  if (ok) {
+    // ---- phase 1: owned chunks: reduce -> updater -> broadcast
+    const int c0 = (int)((long long)n_chunks * c.rank / c.world), c1 = (int)((long long)n_chunks * (c.rank + 1) / c.world);
+    float* my_params = c.params[c.rank];
+    for (int ci = c0 + blockIdx.x; ci < c1; ci += gridDim.x) {
+      const UpdChunk ch = chunks[ci];
+      const UpdSegment sg = segs[ch.seg];
+      const UpdHyper h = ht.h[sg.hyper];
+      const long long rel0 = ch.offset - sg.block_start;
+      float* st0 = state + sg.state_off + rel0;
+      float* st1 = st0 + sg.block_numel;
+      float* st2 = st1 + sg.block_numel;
+      const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+      const bool vec_ok = ((ch.offset & 3) == 0);
+      const bool sh_vec = ((sh0 & 3) == 0);
+      const int nvec = vec_ok ? ch.count / 4 : 0;
+      for (int v = threadIdx.x; v < nvec; v += COMM_THREADS) {
+        const long long i = ch.offset + 4LL * v;
+        float4 g;
+        if (use_multimem) {
+          g = multimem_ld_reduce_f4(c.mc_grads + i);
+        } else {
+          g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r) {
+            if (r < c.world) {
+              const float4 t = ld_peer_f4(c.grads[(c.rank + r) % c.world] + i);
+              g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+            }
+          }
+        }
+        float4 w = *reinterpret_cast<const float4*>(my_params + i);
+        if (sg.kernel_id != 9) {
+          const int e = 4 * v;
+          w.x -= updater_step(sg, h, w.x, g.x * grad_scale, st0 + e, st1 + e, st2 + e);
+          w.y -= updater_step(sg, h, w.y, g.y * grad_scale, st0 + e + 1, st1 + e + 1, st2 + e + 1);
+          w.z -= updater_step(sg, h, w.z, g.z * grad_scale, st0 + e + 2, st1 + e + 2, st2 + e + 2);
+          w.w -= updater_step(sg, h, w.w, g.w * grad_scale, st0 + e + 3, st1 + e + 3, st2 + e + 3);
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+        const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        if (use_multimem) {
+          multimem_st_f4(c.mc_params + i, w);
+          if (c.mc_shadow) {
+            if (sh_vec) multimem_st_b64(c.mc_shadow + sh0 + 4LL * v, packed);
+            else
+              for (int r = 0; r < c.world; ++r) {
+                __nv_bfloat16* s = c.shadow[r] + sh0 + 4LL * v;
+                s[0] = __float2bfloat16(w.x); s[1] = __float2bfloat16(w.y); s[2] = __float2bfloat16(w.z); s[3] = __float2bfloat16(w.w);
+              }
+          }
+        } else {
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r) {
+            if (r < c.world) {
+              const int pr = (c.rank + r) % c.world;
+              *reinterpret_cast<float4*>(c.params[pr] + i) = w;
+              if (c.shadow[pr]) {
+                __nv_bfloat16* s = c.shadow[pr] + sh0 + 4LL * v;
+                if (sh_vec) *reinterpret_cast<uint2*>(s) = packed;
+                else { s[0] = __float2bfloat16(w.x); s[1] = __float2bfloat16(w.y); s[2] = __float2bfloat16(w.z); s[3] = __float2bfloat16(w.w); }
+              }
+            }
+          }
+        }
+      }
+      // scalar tail (and whole chunk when its offset is not 16-byte aligned)
+      for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) {
+        const long long i = ch.offset + e;
+        float g = 0.f;
+        for (int r = 0; r < c.world; ++r) g += ld_peer_f(c.grads[r] + i);
+        float w = my_params[i];
+        if (sg.kernel_id != 9) w -= updater_step(sg, h, w, g * grad_scale, st0 + e, st1 + e, st2 + e);
+        for (int r = 0; r < c.world; ++r) {
+          c.params[r][i] = w;
+          if (c.shadow[r]) c.shadow[r][sh0 + e] = __float2bfloat16(w);
+        }
+      }
+    }
+    __threadfence_system();
+  }
+  // ---- phase 2: all ranks have read my gradients and written my parameters
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok;
+  if (blockIdx.x == 0 && ok) ok = peer_barrier(c, 1, epoch, status);
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok && *((volatile int*)status) == 0;
+  // ---- phase 3: clear the local gradient buffer for the next backward pass
+  if (ok) {
+    float4* g4 = reinterpret_cast<float4*>(c.grads[c.rank]);
+    const long long n4 = n_total / 4;
+    for (long long i = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; i < n4; i += (long long)gridDim.x * COMM_THREADS)
+      g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (blockIdx.x == 0)
+      for (long long i = n4 * 4 + threadIdx.x; i < n_total; i += COMM_THREADS) c.grads[c.rank][i] = 0.f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ K1
+// Threshold ("shared gradients") step.  msg layout per rank: [k, N, bits(tau), 1, words...] (bitmap encoding).
+__global__ void __launch_bounds__(COMM_THREADS)
+threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __restrict__ residual,
+                       const UpdChunk* __restrict__ chunks, int n_chunks, const UpdSegment* __restrict__ segs,
+                       const UpdHyperTable ht, float grad_scale, float tau, long long n_total, uint32_t epoch,
+                       unsigned int* scratch, int msg_parity, long long msg_stride_ints, int* status) {
+  unsigned int bar = 0;
+  bool ok = true;
+  float* grads = c.grads[c.rank];
+  float* params = c.params[c.rank];
+  __nv_bfloat16* shadow = c.shadow[c.rank];
+  // ---- phase 1a: updater on the local gradient, accumulated into the residual; gradient cleared
+  for (int ci = blockIdx.x; ci < n_chunks; ci += gridDim.x) {
+    const UpdChunk ch = chunks[ci];
+    const UpdSegment sg = segs[ch.seg];
+    const UpdHyper h = ht.h[sg.hyper];
+    const long long rel0 = ch.offset - sg.block_start;
+    float* st0 = state + sg.state_off + rel0;
+    float* st1 = st0 + sg.block_numel;
+    float* st2 = st1 + sg.block_numel;
+    for (int e = threadIdx.x; e < ch.count; e += COMM_THREADS) {
+      const long long i = ch.offset + e;
+      if (sg.kernel_id != 9) residual[i] += updater_step(sg, h, params[i], grads[i] * grad_scale, st0 + e, st1 + e, st2 + e);
+      grads[i] = 0.f;
+    }
+  }
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status);
+  // ---- phase 1b: bitmap-encode the residual into this rank's message slot (residual keeps the remainder)
+  int* my_msg = c.msg[c.rank] + (long long)msg_parity * msg_stride_ints;
+  const long long words = (n_total + 15) / 16;
+  const float half = tau * 0.5f;
+  if (ok) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) { my_msg[1] = (int)n_total; my_msg[2] = __float_as_int(tau); my_msg[3] = 1; }
+    for (long long w = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; w < words; w += (long long)gridDim.x * COMM_THREADS) {
+      const long long base = w * 16;
+      int word = 0;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float v[4];
+        if (base + 4 * q4 + 4 <= n_total) {
+          const float4 a = *reinterpret_cast<const float4*>(residual + base + 4 * q4);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = (base + 4 * q4 + j < n_total) ? residual[base + 4 * q4 + j] : 0.f;
+        }
+        bool touched = false;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int bit = 4 * q4 + j;
+          const float a = fabsf(v[j]);
+          if (a >= tau) {
+            word |= 1 << bit;
+            if (v[j] < 0.f) { word |= 1 << (bit + 16); v[j] += tau; } else { v[j] -= tau; }
+            touched = true;
+          } else if (a >= half && v[j] < 0.f) {
+            word |= 1 << (bit + 16);
+            v[j] += half;
+            touched = true;
+          }
+        }
+        if (touched) {
+          if (base + 4 * q4 + 4 <= n_total) *reinterpret_cast<float4*>(residual + base + 4 * q4) = make_float4(v[0], v[1], v[2], v[3]);
+          else
+            for (int j = 0; j < 4; ++j) if (base + 4 * q4 + j < n_total) residual[base + 4 * q4 + j] = v[j];
+        }
+      }
+      my_msg[4 + w] = word;
+    }
+    __threadfence_system();
+  }
+  // ---- exchange: every rank's message is complete
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok;
+  if (blockIdx.x == 0 && ok) ok = peer_barrier(c, 2, epoch, status);
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok && *((volatile int*)status) == 0;
+  // ---- phase 2: decode the sum of all ranks' messages and apply it to the local parameters
+  if (ok) {
+    const float ntau = tau, nhalf = half;
+    for (long long w = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; w < words; w += (long long)gridDim.x * COMM_THREADS) {
+      int wr[MAX_RANKS];
+      int any = 0;
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) {
+        wr[r] = 0;
+        if (r < c.world) {
+          wr[r] = ld_peer_i(c.msg[r] + (long long)msg_parity * msg_stride_ints + 4 + w);
+          any |= wr[r];
+        }
+      }
+      if (!any) continue;
+      const long long base = w * 16;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (base + j >= n_total) break;
+        float d = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          const bool bit = wr[r] & (1 << j), sign = wr[r] & (1 << (j + 16));
+          if (bit) d += sign ? -ntau : ntau;
+          else if (sign) d -= nhalf;
+        }
+        if (d != 0.f) {
+          const float nw = params[base + j] - d;
+          params[base + j] = nw;
+        }
+      }
+    }
+  }
+  (void)shadow;
+}
+
+// Refreshes the bf16 shadow from the fp32 parameters following the segment table (used after a
+// threshold-sharing step, whose decode works on flat indices).
+__global__ void shadow_refresh_kernel(const float* __restrict__ params, __nv_bfloat16* __restrict__ shadow,
+                                      const UpdChunk* __restrict__ chunks, const UpdSegment* __restrict__ segs) {
+  const UpdChunk ch = chunks[blockIdx.x];
+  const UpdSegment sg = segs[ch.seg];
+  const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+  for (int e = threadIdx.x; e < ch.count; e += blockDim.x) shadow[sh0 + e] = __float2bfloat16(params[ch.offset + e]);
+}
+
+}  // namespace dl4j
+
+using namespace dl4j;
+
+struct HostCommArgs {      // mirrors the ctypes structure built in parallel/fused.py
+  int rank, world;
+  void* grads[MAX_RANKS];
+  void* params[MAX_RANKS];
+  void* shadow[MAX_RANKS];
+  void* signal[MAX_RANKS];
+  void* msg[MAX_RANKS];
+  void* mc_grads;
+  void* mc_params;
+  void* mc_shadow;
+};
+
+static CommCtx make_ctx(const HostCommArgs* a) {
+  CommCtx c;
+  c.rank = a->rank; c.world = a->world;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    c.grads[i] = (float*)a->grads[i]; c.params[i] = (float*)a->params[i]; c.shadow[i] = (__nv_bfloat16*)a->shadow[i];
+    c.signal[i] = (uint32_t*)a->signal[i]; c.msg[i] = (int*)a->msg[i];
+  }
+  c.mc_grads = (float*)a->mc_grads; c.mc_params = (float*)a->mc_params; c.mc_shadow = (__nv_bfloat16*)a->mc_shadow;
+  return c;
+}
+
+template <typename K>
+static int coop_grid(K kernel, int threads) {
+  int dev = 0, sms = 0, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) return 0;
+  if (per_sm > 2) per_sm = 2;
+  return sms * per_sm;
+}
+
+DL4J_API int dl4j_allreduce_update(const void* comm_args, float* state, const void* chunks, int n_chunks, const void* segs,
+                                   const float* hyper, int n_hyper, float grad_scale, long long n_total, unsigned int epoch,
+                                   void* scratch, int use_multimem, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const HostCommArgs* a = reinterpret_cast<const HostCommArgs*>(comm_args);
+  if (a->world < 1 || a->world > MAX_RANKS || n_hyper > UPD_MAX_HYPER) return -DL4J_ERR_BAD_ARG;
+  if (use_multimem && (!a->mc_grads || !a->mc_params)) return -DL4J_ERR_BAD_ARG;
+  CommCtx c = make_ctx(a);
+  UpdHyperTable ht;
+  memset(&ht, 0, sizeof(ht));
+  memcpy(&ht, hyper, sizeof(UpdHyper) * n_hyper);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* status = dl4j_status_word(dev);
+  const int grid = coop_grid(allreduce_update_kernel, COMM_THREADS);
+  if (grid < 1) return -DL4J_ERR_BAD_ARG;
+  cudaMemsetAsync(scratch, 0, 16, stream);
+  const UpdChunk* ch = reinterpret_cast<const UpdChunk*>(chunks);
+  const UpdSegment* sg = reinterpret_cast<const UpdSegment*>(segs);
+  unsigned int* sc = reinterpret_cast<unsigned int*>(scratch);
+  void* args[] = {(void*)&c, (void*)&state, (void*)&ch, (void*)&n_chunks, (void*)&sg, (void*)&ht, (void*)&grad_scale,
+                  (void*)&n_total, (void*)&epoch, (void*)&sc, (void*)&use_multimem, (void*)&status};
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)allreduce_update_kernel, dim3(grid), dim3(COMM_THREADS), args, 0, stream);
+  return (int)e;
+}
+
+DL4J_API int dl4j_threshold_share(const void* comm_args, float* state, float* residual, const void* chunks, int n_chunks,
+                                  const void* segs, const float* hyper, int n_hyper, float grad_scale, float tau,
+                                  long long n_total, unsigned int epoch, void* scratch, int msg_parity,
+                                  long long msg_stride_ints, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const HostCommArgs* a = reinterpret_cast<const HostCommArgs*>(comm_args);
+  if (a->world < 1 || a->world > MAX_RANKS || n_hyper > UPD_MAX_HYPER || n_total >= 2147483647LL) return -DL4J_ERR_BAD_ARG;
+  CommCtx c = make_ctx(a);
+  UpdHyperTable ht;
+  memset(&ht, 0, sizeof(ht));
+  memcpy(&ht, hyper, sizeof(UpdHyper) * n_hyper);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* status = dl4j_status_word(dev);
+  const int grid = coop_grid(threshold_share_kernel, COMM_THREADS);
+  if (grid < 1) return -DL4J_ERR_BAD_ARG;
+  cudaMemsetAsync(scratch, 0, 16, stream);
+  const UpdChunk* ch = reinterpret_cast<const UpdChunk*>(chunks);
+  const UpdSegment* sg = reinterpret_cast<const UpdSegment*>(segs);
+  unsigned int* sc = reinterpret_cast<unsigned int*>(scratch);
+  void* args[] = {(void*)&c, (void*)&state, (void*)&residual, (void*)&ch, (void*)&n_chunks, (void*)&sg, (void*)&ht,
+                  (void*)&grad_scale, (void*)&tau, (void*)&n_total, (void*)&epoch, (void*)&sc, (void*)&msg_parity,
+                  (void*)&msg_stride_ints, (void*)&status};
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)threshold_share_kernel, dim3(grid), dim3(COMM_THREADS), args, 0, stream);
+  return (int)e;
+}
+
+DL4J_API int dl4j_shadow_refresh(const float* params, void* shadow, const void* chunks, int n_chunks, const void* segs, void* stream) {
+  if (n_chunks <= 0) return 0;
+  shadow_refresh_kernel<<<n_chunks, 256, 0, (cudaStream_t)stream>>>(params, reinterpret_cast<__nv_bfloat16*>(shadow),
+                                                                    reinterpret_cast<const UpdChunk*>(chunks),
+                                                                    reinterpret_cast<const UpdSegment*>(segs));
+  return (int)cudaGetLastError();
+}

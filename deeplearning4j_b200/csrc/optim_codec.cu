@@ -10,37 +10,17 @@
 // Codec semantics: libnd4j/include/loops/cuda/type_conversions.cu:215-500 (message layout
 // [k, N, bits(tau), flag, payload...], residual kept in the source buffer, bitmap half-threshold rule).
 #include "common.cuh"
+#include "updater_math.cuh"
 
 namespace dl4j {
 
-struct UpdSegment {     // one per parameter array (56 bytes)
-  long long offset;     // into params / grads
-  long long block_start;// first element of the updater block this parameter belongs to
-  long long block_numel;
-  long long state_off;  // block's offset into the state buffer
-  long long shadow_off; // this parameter's offset into the (16-byte aligned per parameter) bf16 shadow buffer
-  float l1, l2, wd;     // wd already multiplied by lr when applyLR
-  int kernel_id;        // see IUpdater.KERNEL_ID
-  int hyper;            // index into UpdHyper table
-  int pad;
-};
-
-struct UpdHyper {       // per updater block, refreshed each iteration (passed by value)
-  float lr, b1, b2, eps, eps_t, mb1t, mu, rho;
-};
-
-struct UpdChunk { long long offset; int count; int seg; };
-
-constexpr int UPD_MAX_HYPER = 8;
-struct UpdHyperTable { UpdHyper h[UPD_MAX_HYPER]; };
-
 constexpr int UPD_THREADS = 256;
 
-__device__ __forceinline__ float sgnf(float x) { return (x > 0.f) - (x < 0.f); }
-
+// mode 0: params -= update (and refresh the bf16 shadow); mode 1: residual += update, params untouched
+// (threshold gradient sharing accumulates the post-updater update before encoding it).
 __global__ void __launch_bounds__(UPD_THREADS)
 fused_update_kernel(float* __restrict__ params, float* __restrict__ grads, float* __restrict__ state,
-                    __nv_bfloat16* __restrict__ shadow, const UpdChunk* __restrict__ chunks,
+                    __nv_bfloat16* __restrict__ shadow, float* __restrict__ residual, const UpdChunk* __restrict__ chunks,
                     const UpdSegment* __restrict__ segs, const UpdHyperTable ht, float grad_scale, int zero_grads) {
   const UpdChunk ch = chunks[blockIdx.x];
   const UpdSegment sg = segs[ch.seg];
@@ -52,78 +32,19 @@ fused_update_kernel(float* __restrict__ params, float* __restrict__ grads, float
   float* p = params + ch.offset;
   float* g = grads + ch.offset;
   for (int i = threadIdx.x; i < ch.count; i += UPD_THREADS) {
-    float w = p[i];
-    float gr = g[i] * grad_scale;
     if (sg.kernel_id == 9) {            // NoOp / state parameters: leave untouched
       if (zero_grads) g[i] = 0.f;
       continue;
     }
-    if (sg.l2 != 0.f) gr += sg.l2 * w;
-    if (sg.l1 != 0.f) gr += sg.l1 * sgnf(w);
-    float u;
-    switch (sg.kernel_id) {
-      case 0: u = h.lr * gr; break;                                          // Sgd
-      case 1: {                                                               // Nesterovs
-        const float prev = h.mu * st0[i];
-        const float v = prev - h.lr * gr;
-        st0[i] = v;
-        u = prev + (-h.mu - 1.f) * v;
-      } break;
-      case 2: {                                                               // Adam
-        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
-        const float v = h.b2 * st1[i] + (1.f - h.b2) * gr * gr;
-        st0[i] = m; st1[i] = v;
-        u = m * h.eps_t / (sqrtf(v) + h.eps);
-      } break;
-      case 3: {                                                               // AdaMax
-        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
-        const float uu = fmaxf(h.b2 * st1[i], fabsf(gr)) + 1e-32f;
-        st0[i] = m; st1[i] = uu;
-        u = m * h.eps_t / uu;
-      } break;
-      case 4: {                                                               // Nadam
-        const float omg = (1.f - h.b1) * gr;
-        const float m = h.b1 * st0[i] + omg;
-        const float v = h.b2 * st1[i] + (1.f - h.b2) * gr * gr;
-        st0[i] = m; st1[i] = v;
-        u = (h.lr * ((m * h.b1 + omg) / h.mb1t)) / (sqrtf(v) + h.eps);
-      } break;
-      case 5: {                                                               // AMSGrad
-        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
-        const float v = h.b2 * st1[i] + (1.f - h.b2) * gr * gr;
-        const float hh = fmaxf(st2[i], v);
-        st0[i] = m; st1[i] = v; st2[i] = hh;
-        u = h.eps_t * m / (sqrtf(hh) + h.eps);
-      } break;
-      case 6: {                                                               // AdaBelief
-        const float m = h.b1 * st0[i] + (1.f - h.b1) * gr;
-        const float d = gr - m;
-        const float s = h.b2 * st1[i] + (1.f - h.b2) * d * d + h.eps;
-        st0[i] = m; st1[i] = s;
-        u = m * h.eps_t / (sqrtf(s) + h.eps);
-      } break;
-      case 7: {                                                               // AdaGrad
-        const float s = st0[i] + gr * gr;
-        st0[i] = s;
-        u = h.lr * gr / (sqrtf(s) + h.eps);
-      } break;
-      case 8: {                                                               // RmsProp
-        const float s = st0[i] * h.rho + gr * gr * (1.f - h.rho);
-        st0[i] = s;
-        u = h.lr * gr / (sqrtf(s) + h.eps);
-      } break;
-      case 10: {                                                              // AdaDelta
-        const float msg = h.rho * st0[i] + (1.f - h.rho) * gr * gr;
-        u = gr * (sqrtf(st1[i] + h.eps) / sqrtf(msg + h.eps));
-        st0[i] = msg;
-        st1[i] = h.rho * st1[i] + (1.f - h.rho) * u * u;
-      } break;
-      default: u = 0.f;
+    float w = p[i];
+    const float u = updater_step(sg, h, w, g[i] * grad_scale, st0 + i, st1 + i, st2 + i);
+    if (residual) {
+      residual[ch.offset + i] += u;
+    } else {
+      w -= u;
+      p[i] = w;
+      if (shadow) shadow[sg.shadow_off + (ch.offset - sg.offset) + i] = __float2bfloat16(w);
     }
-    if (sg.wd != 0.f) u += sg.wd * w;
-    w -= u;
-    p[i] = w;
-    if (shadow) shadow[sg.shadow_off + (ch.offset - sg.offset) + i] = __float2bfloat16(w);
     if (zero_grads) g[i] = 0.f;
   }
 }
@@ -321,16 +242,16 @@ __global__ void bitmap_decode_kernel(const int* __restrict__ msg, float* __restr
 
 using namespace dl4j;
 
-DL4J_API int dl4j_fused_update(float* params, float* grads, float* state, void* shadow_bf16, const void* chunks,
-                               int n_chunks, const void* segs, const float* hyper, int n_hyper, float grad_scale,
-                               int zero_grads, void* stream) {
+DL4J_API int dl4j_fused_update(float* params, float* grads, float* state, void* shadow_bf16, float* residual,
+                               const void* chunks, int n_chunks, const void* segs, const float* hyper, int n_hyper,
+                               float grad_scale, int zero_grads, void* stream) {
   if (n_chunks <= 0) return 0;
   if (n_hyper > UPD_MAX_HYPER) return -DL4J_ERR_BAD_ARG;
   UpdHyperTable ht;
   memset(&ht, 0, sizeof(ht));
   memcpy(&ht, hyper, sizeof(UpdHyper) * n_hyper);
   fused_update_kernel<<<n_chunks, UPD_THREADS, 0, (cudaStream_t)stream>>>(
-      params, grads, state, reinterpret_cast<__nv_bfloat16*>(shadow_bf16), reinterpret_cast<const UpdChunk*>(chunks),
+      params, grads, state, reinterpret_cast<__nv_bfloat16*>(shadow_bf16), residual, reinterpret_cast<const UpdChunk*>(chunks),
       reinterpret_cast<const UpdSegment*>(segs), ht, grad_scale, zero_grads);
   return (int)cudaGetLastError();
 }

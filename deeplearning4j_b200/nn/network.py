@@ -142,7 +142,8 @@ class BaseNetwork:
             offs.append(off)
             off += (e.spec.numel + 63) // 64 * 64
         self.shadow_offsets = offs
-        self.flat_shadow = torch.zeros(max(off, 1), dtype=cd, device=self.device)
+        alloc = getattr(self, "_flat_allocator", None)
+        self.flat_shadow = alloc(off, cd, self.device) if alloc is not None else torch.zeros(max(off, 1), dtype=cd, device=self.device)
         self._refresh_shadow()
 
     def _refresh_shadow(self):
@@ -157,10 +158,13 @@ class BaseNetwork:
         self._make_views()
         if self.updater is not None:
             self.updater.params, self.updater.grads = self.flat_params, self.flat_grads
+            self.updater.shadow, self.updater.shadow_offsets = self.flat_shadow, self.shadow_offsets
+            self.updater._native_tables = None
 
     def _ensure_updater(self):
         if self.updater is None:
             self.updater = MultiLayerUpdater(self.entries, self.flat_params, self.flat_grads)
+        self.updater.shadow, self.updater.shadow_offsets = self.flat_shadow, self.shadow_offsets
         return self.updater
 
     # ------------------------------------------------------------------ device

@@ -45,7 +45,7 @@ def _load():
         sig = {
             "dl4j_gemm": [vp, vp, vp, vp, vp, vp, i32, i32, i32, lng, lng, lng, lng, lng, i32, i32, i32, i32, i32, i32,
                           i32, i32, f32, i32, i32, vp],
-            "dl4j_fused_update": [vp, vp, vp, vp, vp, i32, vp, vp, i32, f32, i32, vp],
+            "dl4j_fused_update": [vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, f32, i32, vp],
             "dl4j_cast_f32_bf16": [vp, vp, i64, vp],
             "dl4j_threshold_encode": [vp, i64, f32, vp, i32, vp],
             "dl4j_threshold_decode": [vp, i32, vp, i64, f32, i32, vp],
@@ -507,13 +507,23 @@ _CHUNK_FMT = "<qii"
 _CHUNK = 16384
 
 
+def _cfg_index(known, cfg):
+    """Index of ``cfg`` among the distinct updater configurations seen so far (hyper-parameter sets are per
+    configuration, not per state block)."""
+    for i, c in enumerate(known):
+        if c is cfg or c == cfg:
+            return i
+    known.append(cfg)
+    return len(known) - 1
+
+
 def _build_tables(upd, shadow_offsets):
     """Static part of the segment / chunk tables for a MultiLayerUpdater."""
     segs = upd.segments(0, 0)
-    block_ids = {}
+    block_ids = []
     seg_rows, chunks = [], []
     for si, (off, numel, st_off, bn, bs, kid, lr, l1, l2, wd, cfg) in enumerate(segs):
-        hid = block_ids.setdefault(bs, len(block_ids))
+        hid = _cfg_index(block_ids, cfg)
         seg_rows.append([off, bs, bn, st_off, shadow_offsets[si] if shadow_offsets is not None else 0, l1, l2, wd, kid, hid, 0])
         o = 0
         while o < numel:
@@ -523,32 +533,29 @@ def _build_tables(upd, shadow_offsets):
     return seg_rows, b"".join(chunks), len(chunks), len(block_ids)
 
 
-def fused_update(upd, iteration, epoch, shadow=None, shadow_offsets=None, grad_scale=1.0, zero_grads=True) -> bool:
-    """One launch: regularisation + updater + params -= update (+ bf16 shadow refresh, + grad zeroing)."""
-    l = require()
-    if l is None:
-        return False
+def update_tables(upd, iteration, epoch, shadow_offsets=None):
+    """Device chunk/segment tables + this iteration's hyper-parameter table for ``upd``; None if unsupported."""
     cache = getattr(upd, "_native_tables", None)
     if cache is None or cache["shadow"] is not shadow_offsets:
         seg_rows, chunk_bytes, n_chunks, n_hyper = _build_tables(upd, shadow_offsets)
         if n_hyper > 8:
             upd._native_tables = {"unsupported": True, "shadow": shadow_offsets}
-            return False
+            return None
         dev = upd.params.device
         chunks_t = torch.frombuffer(bytearray(chunk_bytes), dtype=torch.uint8).to(dev)
         cache = {"seg_rows": seg_rows, "chunks": chunks_t, "n_chunks": n_chunks, "n_hyper": n_hyper, "shadow": shadow_offsets,
                  "segs_dev": None, "segs_key": None}
         upd._native_tables = cache
     if cache.get("unsupported"):
-        return False
+        return None
     # dynamic part: per-block hyper-parameters and any scheduled regularisation coefficients
     segs = upd.segments(iteration, epoch)
     hyper = np.zeros((8, 8), dtype=np.float32)
     key = []
-    seen = {}
+    seen = []
     for si, (off, numel, st_off, bn, bs, kid, lr, l1, l2, wd, cfg) in enumerate(segs):
         key.append((l1, l2, wd))
-        hid = seen.setdefault(bs, len(seen))
+        hid = _cfg_index(seen, cfg)
         b1 = getattr(cfg, "beta1", 0.0); b2 = getattr(cfg, "beta2", 0.0); eps = getattr(cfg, "epsilon", 0.0)
         from ..nn.updaters import _eps_t, Nesterovs, AdaMax
         eps_t = 0.0
@@ -566,10 +573,24 @@ def fused_update(upd, iteration, epoch, shadow=None, shadow_offsets=None, grad_s
             buf += struct.pack(_SEG_FMT, r[0], r[1], r[2], r[3], r[4], l1, l2, wd, r[8], r[9], 0)
         cache["segs_dev"] = torch.frombuffer(buf, dtype=torch.uint8).to(upd.params.device)
         cache["segs_key"] = key
+    cache["hyper"] = hyper
+    return cache
+
+
+def fused_update(upd, iteration, epoch, shadow=None, shadow_offsets=None, grad_scale=1.0, zero_grads=True, residual=None) -> bool:
+    """One launch: regularisation + updater + params -= update (+ bf16 shadow refresh, + grad zeroing); with
+    ``residual`` the update is accumulated into it instead and the parameters are left untouched."""
+    l = require()
+    if l is None:
+        return False
+    cache = update_tables(upd, iteration, epoch, shadow_offsets)
+    if cache is None:
+        return False
+    hyper = cache["hyper"]
     state = upd.state
     hp = hyper.ctypes.data_as(ctypes.c_void_p)
     rc = l.dl4j_fused_update(_ptr(upd.params), _ptr(upd.grads), _ptr(state) if state.numel() else None, _ptr(shadow),
-                             _ptr(cache["chunks"]), cache["n_chunks"], _ptr(cache["segs_dev"]), hp, cache["n_hyper"],
+                             _ptr(residual), _ptr(cache["chunks"]), cache["n_chunks"], _ptr(cache["segs_dev"]), hp, cache["n_hyper"],
                              float(grad_scale), 1 if zero_grads else 0, _stream())
     _check(rc, "dl4j_fused_update")
     upd._fused_zeroes_grads = bool(zero_grads)

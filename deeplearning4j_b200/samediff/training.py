@@ -147,10 +147,26 @@ class _ShadowParam(torch.autograd.Function):
 
 
 class TrainingState:
-    def __init__(self, sd):
-        tc = sd.trainingConfig
-        self.sd, self.tc = sd, tc
+    def __init__(self, sd, alloc=None):
+        self.sd, self.tc = sd, sd.trainingConfig
+        self.gradient_hook = None
+        self.score = None
+        self.updater = None
+        self._build(alloc)
+
+    def reallocate(self, alloc):
+        """Move the flat buffers to memory obtained from ``alloc(numel, dtype, device)`` (e.g. symmetric
+        memory for peer access), keeping parameter values and updater state."""
+        old_state = self.updater.state.clone() if self.updater is not None else None
+        self._build(alloc)
+        if old_state is not None and old_state.numel() == self.updater.state.numel():
+            self.updater.state.copy_(old_state)
+
+    def _build(self, alloc=None):
+        sd, tc = self.sd, self.tc
         dev = sd.device
+        if alloc is None:
+            alloc = lambda n, dt, d: torch.zeros(max(int(n), 1), dtype=dt, device=d)
         owner = _VarOwner(tc)
         entries, off = [], 0
         names = []
@@ -160,10 +176,11 @@ class TrainingState:
             spec = ParamSpec(v.name, tuple(arr.shape), "c", kind)
             entries.append(ParamEntry(i, owner, spec, off, v.name))
             names.append(v.name)
-            off += spec.numel
+            off += (spec.numel + 63) // 64 * 64      # every variable starts on a 256-byte boundary (vector / TMA access)
         self.entries, self.names = entries, names
-        self.flat_params = torch.zeros(off, dtype=torch.float32, device=dev)
-        self.flat_grads = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.flat_params = alloc(off, torch.float32, dev)
+        self.flat_grads = alloc(off, torch.float32, dev)
+        self.flat_grads.zero_()
         self.views, self.compute_views = {}, {}
         cd = tc.computeDataType.to_torch() if tc.computeDataType is not None else torch.float32
         self.compute_dtype = cd
@@ -175,8 +192,9 @@ class TrainingState:
                 offs.append(so)
                 so += (e.spec.numel + 63) // 64 * 64
             self.shadow_offsets = offs
-            self.flat_shadow = torch.zeros(max(so, 1), dtype=cd, device=dev)
+            self.flat_shadow = alloc(so, cd, dev)
         with torch.no_grad():
+            self.flat_params.zero_()
             for i, e in enumerate(entries):
                 seg = self.flat_params[e.offset:e.end]
                 seg.copy_(sd.arrays[e.spec.name].reshape(-1).to(torch.float32))
@@ -187,8 +205,6 @@ class TrainingState:
         self.updater = MultiLayerUpdater(entries, self.flat_params, self.flat_grads)
         self.updater.shadow, self.updater.shadow_offsets = self.flat_shadow, self.shadow_offsets
         self.refresh_shadow()
-        self.gradient_hook = None
-        self.score = None
 
     def refresh_shadow(self):
         if self.flat_shadow is None:

@@ -1,0 +1,144 @@
+"""Worker for the multi-GPU tests (launched by torchrun, one rank per GPU): fused NVLink kernels against
+the NCCL / host-codec paths, and a bounded-wait timeout check."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def make_net(rank, updater, bf16):
+    from deeplearning4j_b200 import nn, DataType
+    b = nn.NeuralNetConfiguration.Builder().seed(100 + rank).updater(updater).l2(1e-4)
+    if bf16:
+        b.computeDataType(DataType.BFLOAT16)
+    conf = (b.list().layer(nn.DenseLayer(nIn=256, nOut=512, activation="relu"))
+            .layer(nn.DenseLayer(nIn=512, nOut=264, activation="tanh"))
+            .layer(nn.OutputLayer("MCXENT", nIn=264, nOut=16, activation="softmax")).build())
+    net = nn.MultiLayerNetwork(conf)
+    net.device = torch.device("cuda", torch.cuda.current_device())
+    return net.init()
+
+
+def data(rank, step):
+    g = torch.Generator().manual_seed(1000 * rank + step)
+    x = torch.rand(64, 256, generator=g).cuda()
+    y = torch.nn.functional.one_hot(torch.randint(0, 16, (64,), generator=g), 16).float().cuda()
+    return x, y
+
+
+def gather_equal(t, tol=0.0):
+    world = dist.get_world_size()
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t.contiguous())
+    return all(float((out[0] - o).abs().max()) <= tol for o in out)
+
+
+def run_pair(mode, updater_fn, bf16, multimem, steps=6):
+    from deeplearning4j_b200.parallel.sharing import attach_gradient_sharing, FixedThresholdAlgorithm
+    from deeplearning4j_b200.parallel import codec
+    from deeplearning4j_b200.ops import native
+    rank = dist.get_rank()
+    a, b = make_net(rank, updater_fn(), bf16), make_net(rank, updater_fn(), bf16)
+    sa = sb = None
+    if mode == "averaging":
+        attach_gradient_sharing(a, "averaging", "fused", use_multimem=multimem)
+        attach_gradient_sharing(b, "averaging", "nccl")
+    else:
+        sa = attach_gradient_sharing(a, "shared_gradients", "fused", FixedThresholdAlgorithm(1e-3))
+        sb = attach_gradient_sharing(b, "shared_gradients", "host", FixedThresholdAlgorithm(1e-3))
+        sb.encoding = codec.BITMAP_ENCODING
+    assert torch.equal(a.flat_params, b.flat_params)
+    for st in range(steps):
+        x, y = data(rank, st)
+        a.fit(x, y)
+        b.fit(x, y)
+        if st == 0 and mode != "averaging" and not bf16:
+            # from identical parameters and empty residuals one step must agree exactly (same messages)
+            mism = int((a.flat_params != b.flat_params).sum())
+            assert mism <= 2, ("first threshold step differs", mism)
+    torch.cuda.synchronize()
+    native.check_status()
+    tol = 2e-2 if bf16 else 2e-5
+    d = float((a.flat_params - b.flat_params).abs().max())
+    if mode == "averaging":
+        assert d <= tol, (mode, bf16, multimem, d)
+    else:
+        # Elements whose accumulated update sits exactly at the threshold may be sent one step earlier or later
+        # by the two implementations (last-bit differences in the updater math); what must agree is the quantity
+        # the protocol conserves: parameters minus the sum of every rank's unsent residual.
+        ra, rb = sa.fused.residual.clone(), sb.residual.clone()
+        dist.all_reduce(ra); dist.all_reduce(rb)
+        inv = float(((a.flat_params - ra) - (b.flat_params - rb)).abs().max())
+        assert inv <= (5e-3 if bf16 else 5e-4), (mode, bf16, inv)
+        assert d <= 8e-3, (mode, bf16, d)
+        assert float((a.flat_params - b.flat_params).abs().mean()) <= 3e-4
+    assert gather_equal(a.flat_params), "fused replicas diverged"
+    if a.flat_shadow is not None:
+        assert gather_equal(a.flat_shadow.float())
+        ref = a.flat_params.clone()
+        for e, so in zip(a.entries, a.shadow_offsets):
+            sh = a.flat_shadow[so:so + e.spec.numel].float()
+            assert float((sh - ref[e.offset:e.end]).abs().max()) <= 1e-2
+    assert float(a.flat_grads.abs().max()) == 0.0
+    return d
+
+
+def timeout_case():
+    """Rank 1 skips a step: rank 0's peer wait must expire and report through the status word, leaving the
+    context usable."""
+    from deeplearning4j_b200 import nn
+    from deeplearning4j_b200.parallel.sharing import attach_gradient_sharing
+    from deeplearning4j_b200.ops import native
+    rank = dist.get_rank()
+    net = make_net(rank, nn.Sgd(0.1), False)
+    attach_gradient_sharing(net, "averaging", "fused", use_multimem=False)
+    x, y = data(rank, 0)
+    net.fit(x, y)
+    torch.cuda.synchronize()
+    native.check_status()
+    dist.barrier()
+    if rank == 0:
+        net.fit(x, y)                   # nobody answers
+        torch.cuda.synchronize()
+        try:
+            native.check_status()
+            raised = False
+        except RuntimeError as e:
+            raised = "peer wait" in str(e)
+        assert raised, "bounded peer wait did not report a timeout"
+        z = torch.ones(8, device="cuda").sum().item()     # context still usable
+        assert z == 8.0
+    dist.barrier()
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from deeplearning4j_b200 import nn
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    res = {}
+    if what in ("all", "averaging"):
+        for upd in (lambda: nn.Adam(1e-3), lambda: nn.Nesterovs(0.05, 0.9)):
+            for bf16 in (False, True):
+                for mm in (False, True):
+                    res[("avg", upd().JAVA, bf16, mm)] = run_pair("averaging", upd, bf16, mm)
+    if what in ("all", "threshold"):
+        for bf16 in (False, True):
+            # plain SGD: the update is a smooth function of the gradient, so the two implementations stay comparable
+            res[("thr", bf16)] = run_pair("threshold", lambda: nn.Sgd(0.5), bf16, False)
+    if what == "timeout":
+        timeout_case()
+    if dist.get_rank() == 0:
+        print("RESULT", {str(k): v for k, v in res.items()})
+        print("WORKER_OK")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
