@@ -1,2 +1,211 @@
-"""Runners for the remaining baseline configurations (filled in as the model families land)."""
-TABLE = {}
+"""Runners for the remaining baseline configurations: ResNet-50 (ComputationGraph, Nesterovs,
+threshold sharing), character LSTM (tBPTT 50), the config-1 MLP and the gradient-exchange microbenchmark."""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..nd.dtype import DataType
+from .runners import BaseRunner
+
+
+class _NetRunner(BaseRunner):
+    sharing_mode = "shared_gradients"
+
+    def _attach(self, net):
+        if self.world > 1:
+            from ..parallel.sharing import FixedThresholdAlgorithm, attach_gradient_sharing
+            impl = "host" if (self.args.library_baseline or self.args.mode == "nccl") else "fused"
+            if self.sharing_mode == "averaging" and impl == "host":
+                impl = "nccl"
+            attach_gradient_sharing(net, self.sharing_mode, impl, FixedThresholdAlgorithm(1e-3))
+
+    def device_step(self):
+        x, y = self.dev[self.i % len(self.dev)]
+        self.i += 1
+        self.net.fit(x, y)
+
+    def e2e_step(self):
+        x, y = self.host[self.i % len(self.host)]
+        self.i += 1
+        self.net.fit(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True))
+        self.last = self.net.score()          # device -> host read of the loss
+
+    def h2d_bytes(self):
+        return sum(t.numel() * t.element_size() for t in self.host[0])
+
+
+class ResNet50Runner(_NetRunner):
+    metric = "ResNet-50 training throughput"
+    unit = "images/s"
+
+    def build(self):
+        from ..models.zoo import ResNet50
+        from ..nn.updaters import Nesterovs
+        self.batch = self.args.batch or 256
+        net = ResNet50(numClasses=1000, updater=Nesterovs(0.01, 0.9), computeDataType=DataType.BFLOAT16).init(self.device)
+        self.net = net
+        g = torch.Generator().manual_seed(7 + self.rank)
+        self.host, self.dev = [], []
+        for _ in range(2):
+            x = torch.randn(self.batch, 3, 224, 224, generator=g).pin_memory()
+            y = torch.nn.functional.one_hot(torch.randint(0, 1000, (self.batch,), generator=g), 1000).float().pin_memory()
+            self.host.append((x, y))
+            self.dev.append((x.to(self.device).to(memory_format=torch.channels_last), y.to(self.device)))
+        self.i = 0
+        self._attach(net)
+
+    def work_per_step(self):
+        return self.batch
+
+    def config(self):
+        return {"model": "ResNet-50 ComputationGraph (zoo architecture, 1000 classes)", "global_batch": self.batch * self.world,
+                "input": "224x224x3", "updater": "Nesterovs(0.9)", "parallelism": f"dp{self.world} threshold-encoded sharing"}
+
+
+class LstmRunner(_NetRunner):
+    metric = "char-LSTM training throughput"
+    unit = "chars/s"
+
+    def build(self):
+        from ..models.zoo import TextGenerationLSTM
+        from ..nn.updaters import Adam
+        self.batch, self.T, self.vocab = self.args.batch or 64, 1000, 98
+        net = TextGenerationLSTM(totalUniqueCharacters=self.vocab, hidden=1024, layers=2, tbptt=50, updater=Adam(1e-3),
+                                 computeDataType=DataType.BFLOAT16).init(self.device)
+        self.net = net
+        g = torch.Generator().manual_seed(3 + self.rank)
+        self.host, self.dev = [], []
+        for _ in range(2):
+            idx = torch.randint(0, self.vocab, (self.batch, self.T + 1), generator=g)
+            x = torch.nn.functional.one_hot(idx[:, :-1], self.vocab).float().permute(0, 2, 1).contiguous().pin_memory()
+            y = torch.nn.functional.one_hot(idx[:, 1:], self.vocab).float().permute(0, 2, 1).contiguous().pin_memory()
+            self.host.append((x, y))
+            self.dev.append((x.to(self.device), y.to(self.device)))
+        self.i = 0
+        self._attach(net)
+
+    def work_per_step(self):
+        return self.batch * self.T
+
+    def config(self):
+        return {"model": "2x LSTM(1024) + RnnOutput softmax, vocab 98 one-hot", "global_batch": self.batch * self.world,
+                "seq_len": self.T, "tbptt": 50, "updater": "Adam", "parallelism": f"dp{self.world} threshold-encoded sharing"}
+
+
+class MlpRunner(_NetRunner):
+    metric = "MLP 784-512-512-10 training throughput"
+    unit = "examples/s"
+    sharing_mode = "shared_gradients"
+
+    def build(self):
+        from .. import nn
+        self.batch = self.args.batch or 128
+        conf = (nn.NeuralNetConfiguration.Builder().seed(123).updater(nn.Adam(1e-3)).list()
+                .layer(nn.DenseLayer(nIn=784, nOut=512, activation="relu"))
+                .layer(nn.DenseLayer(nIn=512, nOut=512, activation="relu"))
+                .layer(nn.OutputLayer("MCXENT", nIn=512, nOut=10, activation="softmax")).build())
+        net = nn.MultiLayerNetwork(conf)
+        net.device = self.device
+        self.net = net.init()
+        g = torch.Generator().manual_seed(self.rank)
+        x = torch.rand(self.batch, 784, generator=g).pin_memory()
+        y = torch.nn.functional.one_hot(torch.randint(0, 10, (self.batch,), generator=g), 10).float().pin_memory()
+        self.host, self.dev, self.i = [(x, y)], [(x.to(self.device), y.to(self.device))], 0
+        self._attach(self.net)
+
+    def work_per_step(self):
+        return self.batch
+
+    def config(self):
+        return {"model": "MultiLayerNetwork MLP 784-512-512-10 fp32", "global_batch": self.batch * self.world, "updater": "Adam"}
+
+
+TABLE = {"resnet50": ResNet50Runner, "lstm": LstmRunner, "mlp": MlpRunner}
+
+
+class GradShareRunner(BaseRunner):
+    """Gradient-exchange microbenchmark: fp32 buffers of 1 MB .. 1 GB, values N(0, 1e-3), threshold 1e-3.
+    Reports, per size, the time of one fused dense step (reduce-scatter + SGD + all-gather in one kernel), one
+    fused threshold step (updater + encode + exchange + decode + apply) and the NCCL all_reduce + updater baseline,
+    with algorithm bandwidth (buffer bytes / time) and the achieved fraction of the NVLink roofline
+    (bytes that must cross the link per GPU / 770 GB/s measured peer-copy bandwidth per direction)."""
+    metric = "gradient exchange bandwidth"
+    unit = "GB/s"
+    LINK_GBS = 770.0
+
+    def run(self, sampler):
+        from .. import nn
+        from ..ops import native
+        from ..parallel.sharing import FixedThresholdAlgorithm, attach_gradient_sharing
+        W = self.world
+        if W < 2:
+            raise SystemExit("gradshare needs --gpus >= 2")
+        sides = [512, 2048, 4096, 8192, 16384]
+        rows = []
+        sampler.start()
+        for side in sides:
+            n = side * side
+            res = {"bytes": 4 * n}
+            for mode, impl in (("averaging", "fused"), ("averaging", "nccl"), ("shared_gradients", "fused")):
+                conf = (nn.NeuralNetConfiguration.Builder().seed(1).updater(nn.Sgd(0.1)).list()
+                        .layer(nn.DenseLayer(nIn=side, nOut=side, hasBias=False, activation="identity"))
+                        .layer(nn.LossLayer("MSE", activation="identity")).build())
+                net = nn.MultiLayerNetwork(conf)
+                net.device = self.device
+                net.init()
+                s = attach_gradient_sharing(net, mode, impl, FixedThresholdAlgorithm(1e-3))
+                g = torch.Generator(device=self.device).manual_seed(5 + self.rank)
+                src = torch.randn(n, device=self.device, generator=g) * 1e-3
+                if mode == "shared_gradients":
+                    src = src * 10.0          # SGD lr 0.1 scales the update back to N(0, 1e-3)
+
+                def step():
+                    net.flat_grads.copy_(src)
+                    if net.gradient_hook(net) is not True:
+                        net._ensure_updater().update(0, 0)
+                for _ in range(3):
+                    step()
+                torch.cuda.synchronize()
+                native.check_status()
+                iters = 10
+                dist.barrier()
+                torch.cuda.synchronize()
+                ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+                for a, b in ev:
+                    net.flat_grads.copy_(src)
+                    a.record()
+                    if net.gradient_hook(net) is not True:
+                        net._ensure_updater().update(0, 0)
+                    b.record()
+                torch.cuda.synchronize()
+                ms = sorted(a.elapsed_time(b) for a, b in ev)[iters // 2]
+                t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t[0])
+                key = f"{'dense' if mode == 'averaging' else 'threshold'}_{impl}"
+                res[key + "_ms"] = ms
+                res[key + "_algbw_gbs"] = 4 * n / ms / 1e6
+                if key == "dense_fused":
+                    link_bytes = (W - 1) / W * 4 * n
+                    res["dense_fused_roofline_frac"] = (link_bytes / (self.LINK_GBS * 1e9)) / (ms / 1e3)
+                    res["dense_fused_multimem"] = bool(s.fused.use_multimem)
+                if key == "threshold_fused":
+                    link_bytes = (W - 1) * (n / 16 + 4) * 4
+                    res["threshold_fused_roofline_frac"] = (link_bytes / (self.LINK_GBS * 1e9)) / (ms / 1e3)
+                    res["threshold_hbm_bound_ms"] = (4 * n * 7) / 6.5475e12 * 1e3
+                net.gradient_hook = None
+                del net, s, src
+                torch.cuda.empty_cache()
+            rows.append(res)
+        clocks = sampler.stop()
+        native.check_status()
+        big = rows[-1]
+        return {"metric": self.metric, "value": big["dense_fused_algbw_gbs"], "unit": self.unit, "ms_per_step": big["dense_fused_ms"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+                "config": {"model": "gradient exchange microbenchmark", "sizes_bytes": [r["bytes"] for r in rows],
+                           "threshold": 1e-3, "parallelism": f"dp{W}"}, "rows": rows, "clocks": clocks,
+                "gpu_launches": native.LAUNCHES}
+
+
+TABLE["gradshare"] = GradShareRunner

@@ -777,11 +777,11 @@ class BatchNormalization(FeedForwardLayer):
                     rv_b = (rv - self.decay * var) * ((cnt - 1.0) / cnt) + self.decay * var
                 else:
                     rv_b = rv
-                mean.detach().copy_(rm)
+                mean.data.copy_(rm)          # .data: no version bump on the shared flat buffer
                 if self.useLogStd:
-                    sv.detach().copy_(0.5 * torch.log10(rv_b.clamp_min(1e-30)))
+                    sv.data.copy_(0.5 * torch.log10(rv_b.clamp_min(1e-30)))
                 else:
-                    sv.detach().copy_(rv_b)
+                    sv.data.copy_(rv_b)
         else:
             y = F.batch_norm(x, mean.detach(), var, g, b, False, 0.0, self.eps)
         y = self.activation(y, training) if self.activation is not None else y
