@@ -101,3 +101,15 @@ def op_hash(name: str) -> int:
         h = ((h * HMULT) & 0xFFFFFFFFFFFFFFFF) ^ t[c & 0xFF]
         h = ((h * HMULT) & 0xFFFFFFFFFFFFFFFF) ^ t[(c >> 8) & 0xFF]
     return h - (1 << 64) if h >= (1 << 63) else h
+
+
+_BY_HASH = None
+
+
+def name_for_hash(h: int) -> str:
+    """Inverse of :func:`op_hash` over the registered names (FlatNode.opNum -> op name)."""
+    global _BY_HASH
+    if _BY_HASH is None or len(_BY_HASH) != len(REGISTRY):
+        load_all()
+        _BY_HASH = {op_hash(n): n for n in REGISTRY}
+    return _BY_HASH[int(h)]
