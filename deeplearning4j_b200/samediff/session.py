@@ -88,6 +88,11 @@ class InferenceSession:
                         raise ValueError(f"variable '{i}' has no value (op '{node.name}')")
                 ins.append(v)
             args = node.args
+            if listeners:
+                for l in listeners:
+                    fn = getattr(l, "preOpExecution", None)
+                    if fn is not None:
+                        fn(sd, node)
             if node.opName == "while_loop":
                 res = _run_while(sd, ins, args["body"], vals)
             elif d.group == "random" and not ins and "shape" in args:
