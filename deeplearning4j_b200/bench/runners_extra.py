@@ -187,7 +187,8 @@ class GradShareRunner(BaseRunner):
                 res[key + "_ms"] = ms
                 res[key + "_algbw_gbs"] = 4 * n / ms / 1e6
                 if key == "dense_fused":
-                    link_bytes = (W - 1) / W * 4 * n
+                    # per direction and GPU: reduce-scatter pulls (W-1)/W of the buffer in, all-gather receives the same again
+                    link_bytes = 2 * (W - 1) / W * 4 * n
                     res["dense_fused_roofline_frac"] = (link_bytes / (self.LINK_GBS * 1e9)) / (ms / 1e3)
                     res["dense_fused_multimem"] = bool(s.fused.use_multimem)
                 if key == "threshold_fused":

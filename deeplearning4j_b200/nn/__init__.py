@@ -18,3 +18,10 @@ from .layers.recurrent import *  # noqa: F401,F403
 from .layers.attention import *  # noqa: F401,F403
 from .multilayer import MultiLayerNetwork
 from .serializer import ModelSerializer, ModelGuesser
+from .graph import ComputationGraph  # noqa: E402
+from .conf.graphconf import (ComputationGraphConfiguration, ElementWiseVertex, MergeVertex, SubsetVertex, StackVertex,  # noqa: E402
+                             UnstackVertex, ScaleVertex, ShiftVertex, L2NormalizeVertex, L2Vertex, ReshapeVertex,
+                             PreprocessorVertex, PoolHelperVertex, FrozenVertex, LayerVertex)
+from .earlystopping import (EarlyStoppingConfiguration, EarlyStoppingTrainer, EarlyStoppingGraphTrainer,  # noqa: E402
+                            EarlyStoppingResult)
+from .transferlearning import FineTuneConfiguration, TransferLearning, TransferLearningHelper  # noqa: E402
