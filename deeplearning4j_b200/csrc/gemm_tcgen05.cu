@@ -66,6 +66,23 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+// Warp-uniform dispatch hoisted out of the element loop.
+__device__ __forceinline__ void apply_act32(float (&v)[32], int act) {
+  if (act == 1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+  } else if (act == 2) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+  } else if (act == 3) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f(T v);
 template <>
@@ -298,10 +315,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 *reinterpret_cast<uint4*>(slab_aux + (((hf * 4 + j) ^ sw) << 4)) = u;
               }
             }
-            if (p.act != 0) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-            }
+            if (p.act != 0) apply_act32(v, p.act);
             if (p.residual != nullptr && lead_split && row_ok) {
               const uint16_t* rs = reinterpret_cast<const uint16_t*>(p.residual) + (long)row * p.ld_res + col0;
               if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(rs) & 15) == 0)) {

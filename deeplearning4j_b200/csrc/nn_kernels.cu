@@ -123,38 +123,45 @@ layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
 }
 
 // dx = rstd * (dy*g - mean(dy*g) - xhat * mean(dy*g*xhat));  dgain += dy*xhat;  dbias += dy.
-// Each warp walks rows with a grid stride and keeps its dgain/dbias partials in registers.
-template <typename T>
+// Each warp walks rows with a grid stride.  The per-column sums for dgain / dbias are kept in shared memory
+// (one float per column and sum, lanes hit distinct banks) instead of registers: that keeps the kernel near
+// 64 registers, so four blocks fit per SM and enough loads are in flight to follow HBM.  NV = C / 256 rounded up.
+template <typename T, int NV>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gain,
                       const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
                       float* __restrict__ dgain, float* __restrict__ dbias, int rows, int C) {
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int nvec = C / 8;
-  float ag[LN_MAXV][8], ab[LN_MAXV][8], g[LN_MAXV][8];
-#pragma unroll
-  for (int i = 0; i < LN_MAXV; ++i) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { ag[i][j] = 0.f; ab[i][j] = 0.f; g[i][j] = 0.f; }
-    if (lane + i * 32 < nvec) Vec8<float>::load(gain + (lane + i * 32) * 8, g[i]);
-  }
+  // column c = (vi * 8 + j) lives at acc[..][j * (NV * 32) + vi]: the 32 lanes of a warp (consecutive vi) hit 32 banks
+  __shared__ float acc[2][NV * 256];
+  for (int i = threadIdx.x; i < 2 * NV * 256; i += LN_WARPS * 32) (&acc[0][0])[i] = 0.f;
+  __syncthreads();
   for (int row = blockIdx.x * LN_WARPS + wid; row < rows; row += gridDim.x * LN_WARPS) {
     const float mean = mean_in[row], rstd = rstd_in[row];
-    float xh[LN_MAXV][8], dg[LN_MAXV][8];
+    float xh[NV][8], dg[NV][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < LN_MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int vi = lane + i * 32;
       if (vi < nvec) {
-        float d[8];
-        Vec8<T>::load(dy + (long long)row * C + vi * 8, d);
+        Vec8<T>::load(dy + (long long)row * C + vi * 8, dg[i]);
         Vec8<T>::load(x + (long long)row * C + vi * 8, xh[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float g[8];
+        Vec8<float>::load(gain + vi * 8, g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xh[i][j] - mean) * rstd;
-          ag[i][j] += d[j] * xh[i][j];
-          ab[i][j] += d[j];
-          dg[i][j] = d[j] * g[i][j];
+          const float d = dg[i][j];
+          atomicAdd(&acc[0][j * (NV * 32) + vi], d * xh[i][j]);
+          atomicAdd(&acc[1][j * (NV * 32) + vi], d);
+          dg[i][j] = d * g[j];
           s1 += dg[i][j];
           s2 += dg[i][j] * xh[i][j];
         }
@@ -163,7 +170,7 @@ layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
     s1 = warp_sum(s1) / C;
     s2 = warp_sum(s2) / C;
 #pragma unroll
-    for (int i = 0; i < LN_MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int vi = lane + i * 32;
       if (vi < nvec) {
         float o[8];
@@ -173,24 +180,13 @@ layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
       }
     }
   }
-  // block-level reduction of the partials through shared memory, then one atomic per column per block
-  __shared__ float red[LN_WARPS][32 * 8 + 1];
-  for (int i = 0; i < LN_MAXV; ++i) {
-    for (int pass = 0; pass < 2; ++pass) {
-      __syncthreads();
-#pragma unroll
-      for (int j = 0; j < 8; ++j) red[wid][lane * 8 + j] = pass == 0 ? ag[i][j] : ab[i][j];
-      __syncthreads();
-      for (int c = threadIdx.x; c < 256; c += LN_WARPS * 32) {
-        const int col = i * 256 + c;
-        if (col < C) {
-          float t = 0.f;
-#pragma unroll
-          for (int w = 0; w < LN_WARPS; ++w) t += red[w][c];
-          float* dst = pass == 0 ? dgain : dbias;
-          if (dst) atomicAdd(dst + col, t);
-        }
-      }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < NV * 256; idx += LN_WARPS * 32) {
+    const int j = idx / (NV * 32), vi = idx - j * (NV * 32);
+    const int col = vi * 8 + j;
+    if (col < C) {
+      if (dgain) atomicAdd(dgain + col, acc[0][idx]);
+      if (dbias) atomicAdd(dbias + col, acc[1][idx]);
     }
   }
 }
@@ -468,8 +464,15 @@ DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gai
   if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
   int grid = (rows + LN_WARPS - 1) / LN_WARPS;
   if (grid > 148 * 4) grid = 148 * 4;
-  DL4J_DISPATCH_T(dtype, (layer_norm_bwd_kernel<T><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(
-      (const T*)dy, (const T*)x, gain, mean, rstd, (T*)dx, dgain, dbias, rows, C)));
+  const int nv = (C + 255) / 256;
+#define DL4J_LN_BWD(NVV)                                                                                       \
+  DL4J_DISPATCH_T(dtype, (layer_norm_bwd_kernel<T, NVV><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(     \
+      (const T*)dy, (const T*)x, gain, mean, rstd, (T*)dx, dgain, dbias, rows, C)))
+  if (nv == 1) { DL4J_LN_BWD(1); }
+  else if (nv == 2) { DL4J_LN_BWD(2); }
+  else if (nv == 3) { DL4J_LN_BWD(3); }
+  else { DL4J_LN_BWD(4); }
+#undef DL4J_LN_BWD
   return (int)cudaGetLastError();
 }
 

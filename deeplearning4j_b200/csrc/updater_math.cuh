@@ -28,6 +28,17 @@ struct UpdHyperTable { UpdHyper h[UPD_MAX_HYPER]; };
 
 __device__ __forceinline__ float sgnf(float x) { return (x > 0.f) - (x < 0.f); }
 
+// state arrays per parameter element, by kernel id (0 Sgd, 1 Nesterovs, 2 Adam, 3 AdaMax, 4 Nadam, 5 AMSGrad,
+// 6 AdaBelief, 7 AdaGrad, 8 RmsProp, 9 NoOp, 10 AdaDelta)
+__device__ __forceinline__ int upd_n_state(int kernel_id) {
+  switch (kernel_id) {
+    case 0: case 9: return 0;
+    case 1: case 7: case 8: return 1;
+    case 5: return 3;
+    default: return 2;
+  }
+}
+
 // One element of regularisation + updater + weight decay.  `gr` is the (already scaled) gradient, `w` the
 // parameter; st0/st1/st2 point at this element's state slots.  Returns the update (params -= update).
 __device__ __forceinline__ float updater_step(const UpdSegment& sg, const UpdHyper& h, float w, float gr, float* st0,

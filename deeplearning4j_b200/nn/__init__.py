@@ -16,6 +16,7 @@ from .layers.core import *      # noqa: F401,F403
 from .layers.conv import *      # noqa: F401,F403
 from .layers.recurrent import *  # noqa: F401,F403
 from .layers.attention import *  # noqa: F401,F403
+from .layers.special import *  # noqa: F401,F403
 from .multilayer import MultiLayerNetwork
 from .serializer import ModelSerializer, ModelGuesser
 from .graph import ComputationGraph  # noqa: E402

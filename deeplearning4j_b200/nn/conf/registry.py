@@ -63,6 +63,9 @@ def _wrapper_keys(cls):
 def object_from_json(d):
     """Generic fallback for nested typed objects inside a layer config."""
     jc = d["@class"]
+    if "ReconstructionDistribution" in jc or jc.endswith("variational.LossFunctionWrapper"):
+        from ..layers.special import reconstruction_from_json
+        return reconstruction_from_json(d)
     if ".layers." in jc:
         return layer_from_json(d)
     if ".preprocessor." in jc:

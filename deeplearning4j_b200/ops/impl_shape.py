@@ -101,7 +101,40 @@ def stack(*xs, dimension=0, **kw):
     return torch.stack(xs, dim=int(dimension))
 
 
-op("unstack", n_out=-1)(lambda x, dimension=0, num=None, **kw: tuple(torch.unbind(x, dim=int(dimension))))
+class _UnstackFn(torch.autograd.Function):
+    """``unbind`` whose backward recognises gradients that already sit side by side in one buffer (the fused
+    attention backward writes dq/dk/dv into a packed [.., 3, ..] tensor) and returns that buffer instead of
+    re-assembling it with a concatenation copy."""
+
+    @staticmethod
+    def forward(ctx, x, dim):
+        ctx.dim, ctx.shape = dim, x.shape
+        return tuple(x.unbind(dim))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        dim, shape = ctx.dim, ctx.shape
+        g0 = next((g for g in grads if g is not None), None)
+        if g0 is not None and all(g is not None for g in grads):
+            strides = list(torch.empty(shape, device="meta").stride())
+            sub = strides[:dim] + strides[dim + 1:]
+            st = g0.untyped_storage().data_ptr()
+            base = g0.storage_offset()
+            if all(g.untyped_storage().data_ptr() == st and list(g.stride()) == sub and g.dtype == g0.dtype
+                   and g.storage_offset() == base + i * strides[dim] for i, g in enumerate(grads)):
+                return torch.as_strided(g0, tuple(shape), strides, base), None
+        zeros = [g if g is not None else torch.zeros_like(g0) for g in grads]
+        return torch.stack(zeros, dim), None
+
+
+def _unstack(x, dimension=0, num=None, **kw):
+    d = int(dimension) % x.dim()
+    if x.requires_grad and torch.is_grad_enabled():
+        return _UnstackFn.apply(x, d)
+    return tuple(torch.unbind(x, dim=d))
+
+
+op("unstack", n_out=-1)(_unstack)
 op("tear", n_out=-1)(lambda x, dimensions=(0,), **kw: tuple(torch.unbind(x, dim=_ints(dimensions)[0])))
 
 
