@@ -192,6 +192,14 @@ class MultiDataSet:
     def getLabelsMaskArray(self, i): return None if self.labelsMasks is None else self.labelsMasks[i]
     def numFeatureArrays(self): return len(self.features)
     def numLabelsArrays(self): return len(self.labels)
+    def setFeatures(self, *a):
+        if len(a) == 2: self.features[a[0]] = _t(a[1])
+        else: self.features = [_t(e) for e in a[0]]
+    def setLabels(self, *a):
+        if len(a) == 2: self.labels[a[0]] = _t(a[1])
+        else: self.labels = [_t(e) for e in a[0]]
+    def setFeaturesMaskArrays(self, m): self.featuresMasks = None if m is None else [_t(e) for e in m]
+    def setLabelsMaskArrays(self, m): self.labelsMasks = None if m is None else [_t(e) for e in m]
     def hasMaskArrays(self): return self.featuresMasks is not None or self.labelsMasks is not None
     def numExamples(self): return int(self.features[0].shape[0]) if self.features else 0
 
