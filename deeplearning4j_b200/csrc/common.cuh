@@ -201,12 +201,17 @@ __host__ __device__ constexpr uint32_t make_idesc(int fmt, int a_mn, int b_mn, i
 }
 
 // ----------------------------------------------------------------------------- math
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 // erf by the rational-exponential form 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1 / (1 + p|x|) (absolute error
 // below 2e-7 in exact arithmetic); one reciprocal and one ex2 on the special-function unit instead of the
 // branchy libm erff, which made GEMM epilogues the bottleneck for short K.
 __device__ __forceinline__ float erf_fast(float x) {
   const float ax = fabsf(x);
-  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+  const float t = rcp_approx(fmaf(0.3275911f, ax, 1.0f));
   float poly = fmaf(t, 1.061405429f, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
@@ -221,7 +226,13 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
   return 0.5f * x * (1.0f + th);
 }
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// x * sigmoid(1.702 x), written through sigmoid(y) = 0.5 tanh(y / 2) + 0.5 so that it costs one tanh.approx
+__device__ __forceinline__ float gelu_sigmoid(float x) {
+  float th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.851f * x));
+  return 0.5f * x * (1.0f + th);
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp_approx(1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -62,6 +62,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case 3: return gelu_tanh(v);
     case 4: return sigmoidf_(v);
     case 5: return tanhf(v);
+    case 6: return gelu_sigmoid(v);
     default: return v;
   }
 }
@@ -77,6 +78,15 @@ __device__ __forceinline__ void apply_act32(float (&v)[32], int act) {
   } else if (act == 3) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+  } else if (act == 6) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_sigmoid(v[j]);
+  } else if (act == 4) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = sigmoidf_(v[j]);
+  } else if (act == 5) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = tanhf(v[j]);
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
@@ -101,6 +111,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
 __device__ __forceinline__ float unpack_lo(uint32_t u, int fmt) {
   if (fmt == 1) return __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(&u));
   return __half2float(*reinterpret_cast<__half*>(&u));
+}
+
+// bias[col] as float (0 beyond N); the bias vector is fp32 or the operand type
+__device__ __forceinline__ float load_bias(const GemmParams& p, int col) {
+  if (col >= p.N) return 0.f;
+  return p.bias_fp32 ? __ldg(reinterpret_cast<const float*>(p.bias) + col)
+                     : unpack_lo((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.bias) + col), p.fmt);
 }
 __device__ __forceinline__ float unpack_hi(uint32_t u, int fmt) {
   uint32_t h = u >> 16;
@@ -247,12 +264,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool has_k = kb0 < min(kb0 + kb_per_split, kb_total);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      const bool lead_split = split == 0;
+      // lane L of the warp fetches bias[col0 + L] one 32-column group ahead of its use (first group here, before the
+      // wait for the accumulator), and the group is broadcast with shuffles: no load latency inside the tile loop
+      const bool use_bias = p.bias != nullptr && lead_split;
+      float bias_cur = use_bias ? load_bias(p, n0 + lane) : 0.f;
       if (!mbar_wait_bounded(&tmem_full[buf], acc_phase, p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr_row = tmem_base + buf * BLOCK_N + ((uint32_t)(q * 32) << 16);
-      const bool lead_split = split == 0;
       if (p.tma_store) {
         // -------- staged epilogue: registers -> swizzled smem slab (32 rows x 128 B per warp) -> TMA store / reduce
         const int b1 = batch % p.batch1, b2 = batch / p.batch1;
@@ -282,30 +303,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = has_k ? __uint_as_float(r[j]) * p.alpha : 0.0f;
-            if (p.bias != nullptr && lead_split) {
-              if (col0 + 32 <= p.N) {
-                if (p.bias_fp32) {
-                  const float4* b4 = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
-                  if ((reinterpret_cast<uintptr_t>(b4) & 15) == 0) {
+            if (use_bias) {
+              const int next_col0 = hf + 1 < halves ? col0 + 32 : n0 + c + cols_per_store;
+              const float bias_next = load_bias(p, next_col0 + lane);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) { const float4 t = __ldg(b4 + j); v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w; }
-                  } else {
-                    const float* b = reinterpret_cast<const float*>(p.bias) + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] += __ldg(b + j);
-                  }
-                } else {
-                  const uint16_t* b = reinterpret_cast<const uint16_t*>(p.bias) + col0;
-#pragma unroll
-                  for (int j = 0; j < 32; ++j) v[j] += unpack_lo((uint32_t)b[j], p.fmt);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N)
-                    v[j] += p.bias_fp32 ? __ldg(reinterpret_cast<const float*>(p.bias) + col0 + j)
-                                        : unpack_lo((uint32_t)reinterpret_cast<const uint16_t*>(p.bias)[col0 + j], p.fmt);
-              }
+              for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_cur, j);
+              bias_cur = bias_next;
             }
             if (want_aux) {
 #pragma unroll

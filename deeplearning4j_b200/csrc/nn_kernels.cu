@@ -317,6 +317,7 @@ __device__ __forceinline__ float act_grad(float z, int act) {
     }
     case 4: { const float s = sigmoidf_(z); return s * (1.f - s); }
     case 5: { const float t = tanhf(z); return 1.f - t * t; }
+    case 6: { const float s = sigmoidf_(1.702f * z); return s + 1.702f * z * s * (1.f - s); }
     default: return 1.f;
   }
 }

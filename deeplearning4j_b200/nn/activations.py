@@ -68,7 +68,7 @@ def _rrelu(self, x, training=False):
 ActivationCube = _mk("cube", "Cube", lambda s, x, training=False: x * x * x)
 ActivationELU = _mk("elu", "ELU", lambda s, x, training=False: F.elu(x, s.alpha), ("alpha",), {"alpha": 1.0})
 ActivationGELU = _mk("gelu", "GELU",
-                     lambda s, x, training=False: F.gelu(x, approximate="none" if s.precise else "tanh"),
+                     lambda s, x, training=False: F.gelu(x, approximate="tanh") if s.precise else x * torch.sigmoid(1.702 * x),
                      ("precise",), {"precise": False})
 ActivationHardSigmoid = _mk("hardsigmoid", "HardSigmoid",
                             lambda s, x, training=False: torch.clamp(0.2 * x + 0.5, 0.0, 1.0))

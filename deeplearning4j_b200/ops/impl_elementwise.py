@@ -49,8 +49,10 @@ _unary("rationaltanh", _rational_tanh)
 _unary("hardtanh", F.hardtanh)
 _unary("hardsigmoid", lambda x: torch.clamp(0.2 * x + 0.5, 0, 1))
 _unary("identity", lambda x: x)
-_unary("gelu", lambda x: F.gelu(x, approximate="tanh"))
-_unary("precise_gelu", F.gelu)
+# libnd4j ops.h: GELU = x * sigmoid(1.702 x); PreciseGELU = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+_unary("gelu", lambda x: x * torch.sigmoid(1.702 * x))
+_unary("precise_gelu", lambda x: F.gelu(x, approximate="tanh"))
+_unary("gelu_erf", F.gelu)
 _unary("swish", F.silu)
 _unary("mish", F.mish)
 

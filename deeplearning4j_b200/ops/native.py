@@ -23,7 +23,7 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc
 
 LAUNCHES = 0     # number of native kernel launches issued by this process (bench.py reports it)
 
-_ACT_IDS = {"ActivationIdentity": 0, "ActivationReLU": 1, "ActivationGELU": 3, "ActivationSigmoid": 4, "ActivationTanH": 5}
+_ACT_IDS = {"ActivationIdentity": 0, "ActivationReLU": 1, "ActivationGELU": 6, "ActivationSigmoid": 4, "ActivationTanH": 5}
 
 
 def _load():
@@ -243,7 +243,7 @@ def _act_id(activation):
         return 0
     name = type(activation).__name__
     if name == "ActivationGELU":
-        return 2 if getattr(activation, "precise", False) else 3
+        return 3 if getattr(activation, "precise", False) else 6      # tanh form / x * sigmoid(1.702 x)
     if name == "ActivationReLU":
         if getattr(activation, "max", None) is not None or getattr(activation, "threshold", None) or getattr(activation, "negativeSlope", None):
             return None
@@ -266,7 +266,7 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, W, b, act, W_lp):
-        need_z = act in (2, 3, 4, 5)
+        need_z = act in (2, 3, 4, 5, 6)
         z = torch.empty((x.shape[0], W_lp.shape[1]), dtype=x.dtype, device=x.device) if need_z and any(ctx.needs_input_grad) else None
         W = getattr(W, "_master", W)          # accumulate weight/bias gradients straight into the fp32 masters
         b = getattr(b, "_master", b) if b is not None else None

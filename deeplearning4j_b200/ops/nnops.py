@@ -71,6 +71,8 @@ def softmax_xent(logits, labels, sparse=False):
 
 
 def gelu(x, approximate="none"):
+    if approximate == "sigmoid":
+        return x * torch.sigmoid(1.702 * x)
     return F.gelu(x, approximate=approximate)
 
 

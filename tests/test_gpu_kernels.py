@@ -38,7 +38,7 @@ def test_gemm_layouts(nat, a_mn, b_mn, shape, bn):
     assert _rel(out, ref) < 2e-2, (a_mn, b_mn, shape, bn, _rel(out, ref))
 
 
-@pytest.mark.parametrize("act", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("act", [0, 1, 2, 3, 4, 5, 6])
 def test_gemm_epilogue(nat, act):
     M, N, K = 512, 384, 256
     g = torch.Generator(device="cuda").manual_seed(act)
@@ -48,7 +48,8 @@ def test_gemm_epilogue(nat, act):
     res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
     z = A.float() @ W.float().t() + bias
     f = {0: lambda v: v, 1: torch.relu, 2: lambda v: torch.nn.functional.gelu(v),
-         3: lambda v: torch.nn.functional.gelu(v, approximate="tanh"), 4: torch.sigmoid, 5: torch.tanh}[act]
+         3: lambda v: torch.nn.functional.gelu(v, approximate="tanh"), 4: torch.sigmoid, 5: torch.tanh,
+         6: lambda v: v * torch.sigmoid(1.702 * v)}[act]
     ref = f(z) + res.float()
     aux = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     out = nat.gemm_raw(A, W.t(), bias=bias, act=act, aux=aux, residual=res)
