@@ -516,6 +516,39 @@ class GraphBuilder:
     def allowDisconnected(self, b): return self
     def allowNoOutput(self, b): return self
 
+    def _infer_types(self, order):
+        """Propagates InputTypes through the (possibly partial) graph, setting nIn and pre-processors on the way."""
+        c = self.c
+        types = dict(zip(c.networkInputs, self._inputTypes))
+        for n in order:
+            v = c.vertices[n]
+            its = [types[i] for i in c.vertexInputs[n]]
+            if isinstance(v, LayerVertex):
+                it = its[0]
+                pp = v.preProcessor if v.preProcessor is not None else self._pp.get(n)
+                if pp is None:
+                    pp = v.preProcessor = v.layer.preprocessor_for(it)
+                if pp is not None:
+                    it = pp.output_type(it)
+                v.layer.setNIn(it, True)
+                types[n] = v.layer.output_type(it)
+            else:
+                if isinstance(v, AttentionVertex) and not v.nInQueries:
+                    v.nInQueries, v.nInKeys, v.nInValues = its[0].size, its[min(1, len(its) - 1)].size, its[-1].size
+                types[n] = v.output_type(*its)
+        return types
+
+    def getLayerActivationTypes(self):
+        """Output InputType of every vertex added so far (``GraphBuilder.getLayerActivationTypes``); needs setInputTypes."""
+        if self._inputTypes is None:
+            raise ValueError("setInputTypes(...) must be called before activation types can be computed")
+        self.c.topologicalOrder = None
+        types = self._infer_types(self.c.topological_order())
+        self.c.topologicalOrder = None               # the graph is still being built
+        return types
+
+    def getVertices(self): return self.c.vertices
+
     def build(self):
         c, p = self.c, self.parent
         c.dataType, c.computeDataType = p._dataType, p._computeDataType
@@ -528,22 +561,7 @@ class GraphBuilder:
                     raise ValueError(f"vertex '{n}' has unknown input '{i}'")
         order = c.topological_order()
         if self._inputTypes is not None:
-            types = dict(zip(c.networkInputs, self._inputTypes))
-            for n in order:
-                v = c.vertices[n]
-                its = [types[i] for i in c.vertexInputs[n]]
-                if isinstance(v, LayerVertex):
-                    it = its[0]
-                    if v.preProcessor is None:
-                        v.preProcessor = v.layer.preprocessor_for(it)
-                    if v.preProcessor is not None:
-                        it = v.preProcessor.output_type(it)
-                    v.layer.setNIn(it, True)
-                    types[n] = v.layer.output_type(it)
-                else:
-                    if isinstance(v, AttentionVertex) and not v.nInQueries:
-                        v.nInQueries, v.nInKeys, v.nInValues = its[0].size, its[min(1, len(its) - 1)].size, its[-1].size
-                    types[n] = v.output_type(*its)
+            self._infer_types(order)
             c.inputTypes = self._inputTypes
         for n in order:
             v = c.vertices[n]

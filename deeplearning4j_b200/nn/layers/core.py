@@ -174,6 +174,9 @@ class CnnLossLayer(BaseOutputLayer):
     HAS_PARAMS = False
     DEFAULTS = {"format": "NCHW"}
 
+    def preprocessor_for(self, input_type):
+        return None                      # consumes the convolutional activations as they are
+
     def param_specs(self):
         return []
 
@@ -259,6 +262,7 @@ class ActivationLayer(NoParamLayer):
     def _positional(self, *args):
         if args:
             self.activation = args[0]
+            self._explicit.add("activation")       # a positional value must not be replaced by the global default
 
     def _finalise(self):
         super()._finalise()
@@ -276,6 +280,7 @@ class DropoutLayer(FeedForwardLayer):
     def _positional(self, *args):
         if args:
             self.dropOut = args[0]
+            self._explicit.add("dropOut")
 
     def param_specs(self):
         return []

@@ -490,8 +490,11 @@ class Yolo2OutputLayer(NoParamLayer):
 
     def to_json(self):
         d = super().to_json()
-        d["boundingBoxes"] = None if self.boundingBoxes is None else self.boundingBoxes.tolist()
+        d["boundingBoxes"] = None if self.boundingBoxes is None else torch.as_tensor(self.boundingBoxes).tolist()
         return d
+
+    def _post_json(self):
+        self._finalise()
 
     def boundingBoxPriors(self, priors):
         self.boundingBoxes = torch.as_tensor(priors, dtype=torch.float32).reshape(-1, 2)

@@ -117,7 +117,10 @@ class MemoryWorkspace:
         nbytes = int(nbytes)
         if self.conf.maxSize and nbytes > self.conf.maxSize:
             nbytes = self.conf.maxSize
-        self.slab = torch.empty(max(nbytes, _ALIGN), dtype=torch.uint8, device=self.device)
+        raw = torch.empty(max(nbytes, _ALIGN) + _ALIGN, dtype=torch.uint8, device=self.device)
+        skew = (-raw.data_ptr()) % _ALIGN            # host allocations are only 64-byte aligned: start the slab on a 256-byte boundary
+        self._raw = raw
+        self.slab = raw[skew:skew + max(nbytes, _ALIGN)]
 
     def initializeWorkspace(self):
         want = self.max_cycle
