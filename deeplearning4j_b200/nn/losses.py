@@ -18,6 +18,11 @@ from .activations import Activation, ActivationSoftmax, ActivationSigmoid, IActi
 _PKG = "org.nd4j.linalg.lossfunctions.impl."
 
 
+def _up(t):
+    """At least float32: half / bf16 inputs are computed in fp32, fp64 stays fp64 (gradient checks)."""
+    return t if t.dtype in (torch.float32, torch.float64) else t.float()
+
+
 def _apply_mask(score, mask):
     if mask is None:
         return score
@@ -82,8 +87,8 @@ class LossMCXENT(ILossFunction):
     def _elem(self, labels, preout, act):
         if isinstance(act, ActivationSoftmax):
             dim = 1 if preout.dim() == 3 else -1
-            return -(labels * F.log_softmax(preout.float(), dim=dim))
-        out = act(preout).float()
+            return -(labels * F.log_softmax(_up(preout), dim=dim))
+        out = _up(act(preout))
         return -(labels * torch.log(out.clamp(self.softmaxClipEps, 1.0 - self.softmaxClipEps)))
 
 
@@ -99,9 +104,9 @@ class LossSparseMCXENT(LossMCXENT):
         act = Activation.get(act)
         idx = labels.reshape(labels.shape[0], -1)[:, 0].long() if preout.dim() == 2 else labels.long()
         if isinstance(act, ActivationSoftmax) and preout.dim() == 2:
-            s = F.cross_entropy(preout.float(), idx, reduction="none")
+            s = F.cross_entropy(_up(preout), idx, reduction="none")
         else:
-            out = act(preout).float().clamp(self.softmaxClipEps, 1 - self.softmaxClipEps)
+            out = _up(act(preout)).clamp(self.softmaxClipEps, 1 - self.softmaxClipEps)
             s = -torch.log(out.gather(1, idx.reshape(-1, 1))).reshape(-1)
         return _apply_mask(s, mask)
 
@@ -116,8 +121,8 @@ class LossBinaryXENT(ILossFunction):
 
     def _elem(self, labels, preout, act):
         if isinstance(act, ActivationSigmoid):
-            return F.binary_cross_entropy_with_logits(preout.float(), labels.float(), reduction="none")
-        out = act(preout).float()
+            return F.binary_cross_entropy_with_logits(_up(preout), _up(labels), reduction="none")
+        out = _up(act(preout))
         if self.clipEps:
             out = out.clamp(self.clipEps, 1.0 - self.clipEps)
         return -(labels * torch.log(out) + (1 - labels) * torch.log(1 - out))

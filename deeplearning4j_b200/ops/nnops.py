@@ -13,6 +13,11 @@ import torch.nn.functional as F
 _FORCE_TORCH = False
 
 
+def _up(t):
+    """At least float32: half / bf16 inputs are computed in fp32, fp64 stays fp64 (gradient checks)."""
+    return t if t.dtype in (torch.float32, torch.float64) else t.float()
+
+
 def set_force_torch(v: bool):
     """Route everything through torch (used to produce the library-only baseline)."""
     global _FORCE_TORCH
@@ -64,7 +69,7 @@ def softmax_xent(logits, labels, sparse=False):
         y = nat.softmax_xent(logits, labels, sparse)
         if y is not None:
             return y
-    lp = F.log_softmax(logits.float(), dim=-1)
+    lp = F.log_softmax(_up(logits), dim=-1)
     if sparse:
         return -lp.gather(1, labels.reshape(-1, 1).long()).reshape(-1)
     return -(labels.to(lp.dtype) * lp).sum(-1)
@@ -88,7 +93,7 @@ def attention(q, k, v, mask=None, scale=None, dropout_p=0.0, training=False):
     s = torch.matmul(q, k.transpose(-1, -2)) * scale
     if mask is not None:
         s = s.masked_fill(mask[:, None, None, :] == 0, float("-inf")) if mask.dim() == 2 else s + mask
-    p = torch.softmax(s.float(), dim=-1).to(q.dtype)
+    p = torch.softmax(_up(s), dim=-1).to(q.dtype)
     if dropout_p > 0.0 and training:
         p = F.dropout(p, dropout_p, True)
     return torch.matmul(p, v)
