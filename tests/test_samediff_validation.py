@@ -1,0 +1,44 @@
+"""SameDiff GradCheckUtil / OpValidation over a sample of ops (the reference's opvalidation suites)."""
+import math
+
+import torch
+
+from deeplearning4j_b200 import DataType
+from deeplearning4j_b200.samediff.core import SameDiff
+from deeplearning4j_b200.samediff.validation import GradCheckUtil, OpTestCase, OpValidation, TestCase
+
+
+def test_graph_gradients_match_numerical():
+    sd = SameDiff.create()
+    g = torch.Generator().manual_seed(0)
+    x = sd.placeHolder("x", DataType.DOUBLE, -1, 4)
+    y = sd.placeHolder("y", DataType.DOUBLE, -1, 3)
+    w1 = sd.var("w1", torch.randn(4, 6, generator=g, dtype=torch.float64) * 0.5)
+    b1 = sd.var("b1", torch.randn(6, generator=g, dtype=torch.float64) * 0.1)
+    gam = sd.var("gam", torch.rand(6, generator=g, dtype=torch.float64) + 0.5)
+    bet = sd.var("bet", torch.zeros(6, dtype=torch.float64))
+    w2 = sd.var("w2", torch.randn(6, 3, generator=g, dtype=torch.float64) * 0.5)
+    h = sd.nn.layerNorm(sd.nn.tanh(x.mmul(w1).add(b1)), gam, bet, False, 1)
+    h = sd.math.square(h).add(sd.nn.softplus(h))
+    loss = sd.loss.softmaxCrossEntropy("loss", y, h.mmul(w2))
+    sd.setLossVariables("loss")
+    ph = {"x": torch.randn(5, 4, generator=g, dtype=torch.float64), "y": torch.nn.functional.one_hot(torch.randint(0, 3, (5,), generator=g), 3).double()}
+    assert GradCheckUtil.checkGradients(sd, ph, print_=False)
+    tc = TestCase(sd).testName("mlp").placeholderValues(ph).expectedOutput("loss", lambda t: True if t.numel() == 1 else "not scalar")
+    assert OpValidation.validate(tc) is None
+    bad = TestCase(sd).placeholderValues(ph).expectedOutput("loss", torch.tensor(123.0)).gradientCheck(False)
+    assert "differs" in OpValidation.validate(bad)
+
+
+def test_single_op_cases_and_coverage():
+    x = torch.tensor([[1.0, -2.0, 3.0], [0.5, 0.0, -1.0]])
+    cases = [OpTestCase("add", [x, x]).expectedOutput(0, 2 * x), OpTestCase("reduce_sum", [x], dimensions=[1]).expectedOutput(0, x.sum(1)),
+             OpTestCase("softmax", [x]).expectedOutput(0, torch.softmax(x, -1)), OpTestCase("transpose", [x]).expectedOutputShape(0, (3, 2)),
+             OpTestCase("gelu", [x]).expectedOutput(0, x * torch.sigmoid(1.702 * x)), OpTestCase("precise_gelu", [x]).expectedOutput(0, torch.nn.functional.gelu(x, approximate="tanh")),
+             OpTestCase("matmul", [x, x.t()]).expectedOutput(0, x @ x.t()), OpTestCase("argmax", [x], dimensions=[1]).expectedOutput(0, x.argmax(1)),
+             OpTestCase("cumsum", [x], dimensions=[1]).expectedOutput(0, x.cumsum(1)), OpTestCase("tile", [x], reps=[2, 1]).expectedOutputShape(0, (4, 3))]
+    for c in cases:
+        assert OpValidation.validate(c) is None, c.opName
+    assert "differs" in OpValidation.validate(OpTestCase("add", [x, x]).expectedOutput(0, x))
+    cov = OpValidation.coverage()
+    assert cov["validated"] >= 10 and cov["total"] > 500 and "Op validation coverage" in OpValidation.logCoverageInformation()
