@@ -1,0 +1,390 @@
+"""Keras model import (``deeplearning4j-modelimport``: ``KerasModelImport``, ``KerasSequentialModel``, ``KerasModel``
+and the ``Keras*`` layer mappers).  A model is its architecture JSON (``model.to_json()`` / the ``model_config``
+attribute of an HDF5 file) plus weights.  Weights come from a ``{layer name: [arrays]}`` dict, an ``.npz`` file
+with ``<layer>/<index>`` keys, or an HDF5 file when ``h5py`` is installed (it is optional: without it the HDF5
+entry points raise with that explanation).  Sequential models become a ``MultiLayerNetwork``, functional models a
+``ComputationGraph``; Keras channels-last tensors map onto the NCHW layers by permuting kernels at import time and
+inserting the flatten order fix for ``Flatten`` -> ``Dense``."""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import torch
+
+from .. import nn
+from ..nn.conf.graphconf import ElementWiseVertex, MergeVertex
+from ..nn.conf.preprocessors import CnnToFeedForwardPreProcessor
+
+_ACT = {"relu": "RELU", "sigmoid": "SIGMOID", "tanh": "TANH", "softmax": "SOFTMAX", "linear": "IDENTITY", None: "IDENTITY", "elu": "ELU", "selu": "SELU",
+        "softplus": "SOFTPLUS", "softsign": "SOFTSIGN", "hard_sigmoid": "HARDSIGMOID", "swish": "SWISH", "gelu": "GELU", "leaky_relu": "LEAKYRELU", "relu6": "RELU6"}
+_LOSS = {"categorical_crossentropy": "MCXENT", "sparse_categorical_crossentropy": "SPARSE_MCXENT", "binary_crossentropy": "XENT", "mse": "MSE",
+         "mean_squared_error": "MSE", "mae": "MEAN_ABSOLUTE_ERROR", "mean_absolute_error": "MEAN_ABSOLUTE_ERROR", "kullback_leibler_divergence": "KL_DIVERGENCE",
+         "hinge": "HINGE", "squared_hinge": "SQUARED_HINGE", "poisson": "POISSON", "cosine_proximity": "COSINE_PROXIMITY"}
+
+
+class InvalidKerasConfigurationException(ValueError):
+    pass
+
+
+class UnsupportedKerasConfigurationException(NotImplementedError):
+    pass
+
+
+def _act(cfg):
+    a = cfg.get("activation")
+    if isinstance(a, dict):
+        a = a.get("class_name", "linear").lower()
+    if a not in _ACT:
+        raise UnsupportedKerasConfigurationException(f"Unsupported Keras activation: {a}")
+    return _ACT[a]
+
+
+def _pair(v):
+    return [int(v), int(v)] if isinstance(v, int) else [int(x) for x in v]
+
+
+def _mode(cfg):
+    return "Same" if str(cfg.get("padding", "valid")).lower() == "same" else "Truncate"
+
+
+def _map_layer(cls, cfg, is_last, loss):
+    """-> (layer or None, kind) where kind in {'layer', 'flatten', 'input', 'skip', 'merge-add', 'merge-concat', ...}."""
+    name = cfg.get("name")
+    if cls == "InputLayer":
+        return None, "input"
+    if cls == "Dense":
+        if is_last and loss:
+            return nn.OutputLayer(loss, nOut=cfg["units"], activation=_act(cfg), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+        return nn.DenseLayer(nOut=cfg["units"], activation=_act(cfg), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls in ("Conv2D", "Convolution2D"):
+        return nn.ConvolutionLayer(_pair(cfg["kernel_size"]), _pair(cfg.get("strides", 1)), nOut=cfg["filters"], activation=_act(cfg), convolutionMode=_mode(cfg),
+                                   dilation=_pair(cfg.get("dilation_rate", 1)), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls in ("Conv1D", "Convolution1D"):
+        k = cfg["kernel_size"][0] if isinstance(cfg["kernel_size"], (list, tuple)) else cfg["kernel_size"]
+        s = cfg.get("strides", 1)
+        s = s[0] if isinstance(s, (list, tuple)) else s
+        return nn.Convolution1DLayer([int(k)], [int(s)], nOut=cfg["filters"], activation=_act(cfg), convolutionMode=_mode(cfg), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls == "SeparableConv2D":
+        return nn.SeparableConvolution2D(_pair(cfg["kernel_size"]), _pair(cfg.get("strides", 1)), nOut=cfg["filters"], activation=_act(cfg), convolutionMode=_mode(cfg),
+                                         depthMultiplier=cfg.get("depth_multiplier", 1), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls == "DepthwiseConv2D":
+        return nn.DepthwiseConvolution2D(_pair(cfg["kernel_size"]), _pair(cfg.get("strides", 1)), activation=_act(cfg), convolutionMode=_mode(cfg),
+                                         depthMultiplier=cfg.get("depth_multiplier", 1), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls in ("Conv2DTranspose", "Deconvolution2D"):
+        return nn.Deconvolution2D(_pair(cfg["kernel_size"]), _pair(cfg.get("strides", 1)), nOut=cfg["filters"], activation=_act(cfg), convolutionMode=_mode(cfg),
+                                  hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls in ("MaxPooling2D", "AveragePooling2D"):
+        ps = _pair(cfg.get("pool_size", 2))
+        return nn.SubsamplingLayer("MAX" if cls.startswith("Max") else "AVG", ps, _pair(cfg.get("strides") or ps), convolutionMode=_mode(cfg), layerName=name), "layer"
+    if cls in ("MaxPooling1D", "AveragePooling1D"):
+        ps = cfg.get("pool_size", 2)
+        ps = ps[0] if isinstance(ps, (list, tuple)) else ps
+        st = cfg.get("strides") or ps
+        st = st[0] if isinstance(st, (list, tuple)) else st
+        return nn.Subsampling1DLayer("MAX" if cls.startswith("Max") else "AVG", [int(ps)], [int(st)], convolutionMode=_mode(cfg), layerName=name), "layer"
+    if cls in ("GlobalAveragePooling2D", "GlobalMaxPooling2D", "GlobalAveragePooling1D", "GlobalMaxPooling1D"):
+        return nn.GlobalPoolingLayer("AVG" if "Average" in cls else "MAX", layerName=name), "layer"
+    if cls == "Flatten":
+        return None, "flatten"
+    if cls in ("Dropout", "SpatialDropout2D", "SpatialDropout1D", "GaussianDropout", "AlphaDropout"):
+        return nn.DropoutLayer(1.0 - float(cfg.get("rate", 0.5)), layerName=name), "layer"        # DL4J stores the retain probability
+    if cls == "Activation":
+        return nn.ActivationLayer(_act(cfg), layerName=name), "layer"
+    if cls == "LeakyReLU":
+        return nn.ActivationLayer(nn.activations.ActivationLReLU(alpha=float(cfg.get("alpha", cfg.get("negative_slope", 0.3)))), layerName=name), "layer"
+    if cls == "ReLU":
+        return nn.ActivationLayer("RELU", layerName=name), "layer"
+    if cls == "Softmax":
+        return nn.ActivationLayer("SOFTMAX", layerName=name), "layer"
+    if cls == "BatchNormalization":
+        return nn.BatchNormalization(eps=float(cfg.get("epsilon", 1e-3)), decay=float(cfg.get("momentum", 0.99)), layerName=name), "layer"
+    if cls == "Embedding":
+        return nn.EmbeddingSequenceLayer(nIn=cfg["input_dim"], nOut=cfg["output_dim"], hasBias=False, activation="IDENTITY", layerName=name), "layer"
+    if cls == "LSTM":
+        l = nn.LSTM(nOut=cfg["units"], activation=_act(cfg), gateActivationFn=_ACT.get(cfg.get("recurrent_activation", "sigmoid"), "SIGMOID"), layerName=name)
+        return (l if cfg.get("return_sequences", False) else nn.LastTimeStep(l)), "layer"
+    if cls == "SimpleRNN":
+        l = nn.SimpleRnn(nOut=cfg["units"], activation=_act(cfg), layerName=name)
+        return (l if cfg.get("return_sequences", False) else nn.LastTimeStep(l)), "layer"
+    if cls == "ZeroPadding2D":
+        p = cfg.get("padding", 1)
+        p = [p, p, p, p] if isinstance(p, int) else ([p[0], p[0], p[1], p[1]] if isinstance(p[0], int) else [p[0][0], p[0][1], p[1][0], p[1][1]])
+        return nn.ZeroPaddingLayer(*[int(v) for v in p], layerName=name), "layer"
+    if cls == "Cropping2D":
+        p = cfg.get("cropping", 0)
+        p = [p, p, p, p] if isinstance(p, int) else ([p[0], p[0], p[1], p[1]] if isinstance(p[0], int) else [p[0][0], p[0][1], p[1][0], p[1][1]])
+        return nn.Cropping2D(*[int(v) for v in p], layerName=name), "layer"
+    if cls == "UpSampling2D":
+        return nn.Upsampling2D(_pair(cfg.get("size", 2)), layerName=name), "layer"
+    if cls == "Add":
+        return ElementWiseVertex("Add"), "vertex"
+    if cls == "Multiply":
+        return ElementWiseVertex("Product"), "vertex"
+    if cls == "Subtract":
+        return ElementWiseVertex("Subtract"), "vertex"
+    if cls == "Average":
+        return ElementWiseVertex("Average"), "vertex"
+    if cls == "Maximum":
+        return ElementWiseVertex("Max"), "vertex"
+    if cls == "Concatenate":
+        return MergeVertex(), "vertex"
+    raise UnsupportedKerasConfigurationException(f"Unsupported keras layer type {cls}")
+
+
+def _input_type(shape):
+    shape = [s for s in shape[1:]]
+    if len(shape) == 3:
+        return nn.InputType.convolutional(shape[0], shape[1], shape[2]), "cnn"           # NHWC -> h, w, c
+    if len(shape) == 2:
+        return nn.InputType.recurrent(shape[1], shape[0] if shape[0] else -1), "rnn"
+    return nn.InputType.feedForward(shape[0]), "ff"
+
+
+def _convert_weights(layer, arrays, flatten_from=None):
+    """Keras arrays -> {param name: tensor} for a DL4J layer."""
+    t = [torch.from_numpy(np.asarray(a, dtype=np.float32)) for a in arrays]
+    cls = type(layer).__name__
+    if cls == "LastTimeStep":
+        return _convert_weights(layer.underlying, arrays)
+    if cls in ("DenseLayer", "OutputLayer"):
+        W = t[0]
+        if flatten_from is not None:                                                   # rows are in (h, w, c) order; DL4J flattens (c, h, w)
+            h, w, c = flatten_from
+            W = W.reshape(h, w, c, -1).permute(2, 0, 1, 3).reshape(h * w * c, -1)
+        out = {"W": W}
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "ConvolutionLayer":
+        out = {"W": t[0].permute(3, 2, 0, 1)}                                          # HWIO -> OIHW
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "Deconvolution2D":
+        out = {"W": t[0].permute(3, 2, 0, 1)}                                          # [kh, kw, out, in] -> [in, out, kh, kw]
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "Convolution1DLayer":
+        out = {"W": t[0].permute(2, 1, 0).unsqueeze(-1)}                               # [k, in, out] -> [out, in, k, 1]
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "DepthwiseConvolution2D":
+        out = {"W": t[0].permute(3, 2, 0, 1)}                                          # [kh, kw, in, mult] -> [mult, in, kh, kw]
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "SeparableConvolution2D":
+        out = {"W": t[0].permute(3, 2, 0, 1), "pW": t[1].permute(3, 2, 0, 1)}
+        if len(t) > 2:
+            out["b"] = t[2].reshape(1, -1)
+        return out
+    if cls == "BatchNormalization":
+        gamma, beta, mean, var = t if len(t) == 4 else (torch.ones_like(t[0]), *t)
+        return {"gamma": gamma.reshape(1, -1), "beta": beta.reshape(1, -1), "mean": mean.reshape(1, -1), "var": var.reshape(1, -1)}
+    if cls == "EmbeddingSequenceLayer":
+        return {"W": t[0]}
+    if cls == "LSTM":
+        # Keras gate order (i, f, c, o) -> DL4J column blocks (c, f, o, i)
+        def reorder(m):
+            i, f, c, o = m.chunk(4, dim=-1)
+            return torch.cat([c, f, o, i], dim=-1)
+        out = {"W": reorder(t[0]), "RW": reorder(t[1])}
+        if len(t) > 2:
+            out["b"] = reorder(t[2]).reshape(1, -1)
+        return out
+    if cls == "SimpleRnn":
+        out = {"W": t[0], "RW": t[1]}
+        if len(t) > 2:
+            out["b"] = t[2].reshape(1, -1)
+        return out
+    return {}
+
+
+def _set_params(net, key, layer, arrays, flatten_from=None):
+    table = net.paramTable()
+    conv = _convert_weights(layer, arrays, flatten_from)
+    with torch.no_grad():
+        for pn, val in conv.items():
+            k = f"{key}_{pn}"
+            if pn == "var" and k not in table:
+                k2 = f"{key}_log10stdev"
+                if k2 in table:
+                    dst = table[k2].t
+                    dst.copy_((0.5 * torch.log10(val.clamp_min(1e-30))).reshape(dst.shape))     # stored as log10(stdev)
+                    continue
+            if k not in table:
+                continue
+            dst = table[k].t
+            if tuple(dst.shape) != tuple(val.shape):
+                if dst.numel() != val.numel():
+                    raise InvalidKerasConfigurationException(f"weight shape mismatch for {k}: keras {tuple(val.shape)} vs {tuple(dst.shape)}")
+                val = val.reshape(dst.shape)
+            dst.copy_(val)
+    if getattr(net, "flat_shadow", None) is not None:
+        net._refresh_shadow()
+
+
+def _load_weights(weights):
+    if weights is None:
+        return {}
+    if isinstance(weights, dict):
+        return {k: list(v) for k, v in weights.items()}
+    path = str(weights)
+    if path.endswith(".npz"):
+        z = np.load(path)
+        out = {}
+        for k in sorted(z.files, key=lambda s: (s.rsplit("/", 1)[0], int(s.rsplit("/", 1)[1]))):
+            out.setdefault(k.rsplit("/", 1)[0], []).append(z[k])
+        return out
+    try:
+        import h5py
+    except ImportError as e:
+        raise UnsupportedKerasConfigurationException("reading Keras HDF5 weights needs h5py, which is not installed; export the weights with "
+                                                     "numpy.savez(path, **{'<layer>/<i>': array}) instead") from e
+    out = {}
+    with h5py.File(path, "r") as f:
+        g = f["model_weights"] if "model_weights" in f else f
+        for lname in g.attrs.get("layer_names", list(g.keys())):
+            lname = lname.decode() if isinstance(lname, bytes) else lname
+            names = [n.decode() if isinstance(n, bytes) else n for n in g[lname].attrs.get("weight_names", [])]
+            out[lname] = [np.asarray(g[lname][n]) for n in names]
+    return out
+
+
+class KerasModelImport:
+    @staticmethod
+    def _config(model_json):
+        cfg = json.loads(model_json) if isinstance(model_json, str) and model_json.lstrip().startswith("{") else json.load(open(model_json))
+        loss = None
+        tc = cfg.get("training_config") or {}
+        l = tc.get("loss")
+        if isinstance(l, dict):
+            l = l.get("class_name") or next(iter(l.values()), None)
+        if isinstance(l, str):
+            key = "".join("_" + c.lower() if c.isupper() else c for c in l).lstrip("_") if any(c.isupper() for c in l) else l
+            loss = _LOSS.get(key) or _LOSS.get(l)
+        return cfg, loss
+
+    @staticmethod
+    def importKerasSequentialModelAndWeights(model_json, weights=None, enforceTrainingConfig=False, loss=None):
+        cfg, cfg_loss = KerasModelImport._config(model_json)
+        loss = loss or cfg_loss
+        if cfg.get("class_name") != "Sequential":
+            raise InvalidKerasConfigurationException(f"Model class name must be Sequential (found {cfg.get('class_name')})")
+        layers_cfg = cfg["config"]["layers"] if isinstance(cfg["config"], dict) else cfg["config"]
+        in_shape = None
+        for lc in layers_cfg:
+            c = lc["config"]
+            in_shape = c.get("batch_input_shape") or c.get("batch_shape") or in_shape
+            if in_shape:
+                break
+        if in_shape is None:
+            raise InvalidKerasConfigurationException("could not determine the input shape (no batch_input_shape on the first layer)")
+        it, kind = _input_type(in_shape)
+        lb = nn.NeuralNetConfiguration.Builder().list()
+        mapped = []                      # (dl4j index, keras name, layer, flatten_from)
+        idx, cur, pending_flatten = 0, it, None
+        real = [lc for lc in layers_cfg if lc["class_name"] != "InputLayer"]
+        for k, lc in enumerate(real):
+            layer, what = _map_layer(lc["class_name"], lc["config"], k == len(real) - 1, loss)
+            if what == "flatten":
+                if cur.kind == nn.InputType.CNN:
+                    pending_flatten = (cur.height, cur.width, cur.channels)
+                continue
+            if what in ("input", "skip"):
+                continue
+            if what == "vertex":
+                raise InvalidKerasConfigurationException("merge layers need the functional API: use importKerasModelAndWeights")
+            lb.layer(idx, layer)
+            mapped.append((idx, lc["config"]["name"], layer, pending_flatten if type(layer).__name__ in ("DenseLayer", "OutputLayer") else None))
+            if pending_flatten is not None and type(layer).__name__ in ("DenseLayer", "OutputLayer"):
+                pending_flatten = None
+            pp = layer.preprocessor_for(cur)
+            if pp is not None:
+                cur = pp.output_type(cur)
+            layer.setNIn(cur, True)
+            cur = layer.output_type(cur)
+            idx += 1
+        lb.setInputType(it).validateOutputLayerConfig(False)
+        net = nn.MultiLayerNetwork(lb.build()).init()
+        w = _load_weights(weights)
+        for i, kname, layer, ff in mapped:
+            if kname in w and w[kname]:
+                _set_params(net, str(i), net.conf.layers()[i], w[kname], ff)
+        net.kerasInputLayout = "NHWC" if kind == "cnn" else ("NWC" if kind == "rnn" else "NC")
+        return net
+
+    @staticmethod
+    def importKerasModelAndWeights(model_json, weights=None, enforceTrainingConfig=False, loss=None):
+        cfg, cfg_loss = KerasModelImport._config(model_json)
+        loss = loss or cfg_loss
+        if cfg.get("class_name") == "Sequential":
+            return KerasModelImport.importKerasSequentialModelAndWeights(model_json, weights, enforceTrainingConfig, loss)
+        c = cfg["config"]
+        gb = nn.NeuralNetConfiguration.Builder().graphBuilder()
+        names = lambda spec: [s[0] for s in spec]
+        in_names = names(c["input_layers"])
+        out_names = names(c["output_layers"])
+        gb.addInputs(*in_names)
+        its, mapped, flatten_of = [], [], {}
+        by_name = {lc["config"]["name"] if "name" in lc["config"] else lc["name"]: lc for lc in c["layers"]}
+        for n in in_names:
+            sh = by_name[n]["config"].get("batch_input_shape") or by_name[n]["config"].get("batch_shape")
+            its.append(_input_type(sh)[0])
+        gb.setInputTypes(*its)
+        alias = {}
+        for lc in c["layers"]:
+            name = lc.get("name") or lc["config"]["name"]
+            if lc["class_name"] == "InputLayer":
+                continue
+            inbound = lc.get("inbound_nodes") or []
+            srcs = []
+            if inbound:
+                node0 = inbound[0]
+                if isinstance(node0, dict):                                            # Keras 3 format
+                    def walk(o):
+                        if isinstance(o, dict) and o.get("class_name") == "__keras_tensor__":
+                            srcs.append(o["config"]["keras_history"][0])
+                        elif isinstance(o, dict):
+                            [walk(v) for v in o.values()]
+                        elif isinstance(o, (list, tuple)):
+                            [walk(v) for v in o]
+                    walk(node0.get("args", []))
+                else:
+                    srcs = [s[0] for s in node0]
+            srcs = [alias.get(s, s) for s in srcs]
+            layer, what = _map_layer(lc["class_name"], lc["config"], name in out_names, loss)
+            if what == "flatten":
+                alias[name] = srcs[0]
+                flatten_of[name] = srcs[0]
+                continue
+            if what == "vertex":
+                gb.addVertex(name, layer, *srcs)
+            else:
+                gb.addLayer(name, layer, *srcs)
+                mapped.append((name, layer, srcs))
+        gb.setOutputs(*[alias.get(o, o) for o in out_names]).validateOutputLayerConfig(False)
+        types = gb.getLayerActivationTypes()
+        conf = gb.build()
+        from ..nn.graph import ComputationGraph
+        net = ComputationGraph(conf).init()
+        w = _load_weights(weights)
+        for name, layer, srcs in mapped:
+            if name in w and w[name]:
+                ff = None
+                src_t = types.get(srcs[0]) if srcs else None
+                if type(layer).__name__ in ("DenseLayer", "OutputLayer") and src_t is not None and src_t.kind == nn.InputType.CNN:
+                    ff = (src_t.height, src_t.width, src_t.channels)
+                _set_params(net, name, conf.vertices[name].layer, w[name], ff)
+        return net
+
+    @staticmethod
+    def importKerasModelConfiguration(model_json):
+        return KerasModelImport.importKerasModelAndWeights(model_json).conf
+
+    @staticmethod
+    def importKerasSequentialConfiguration(model_json):
+        return KerasModelImport.importKerasSequentialModelAndWeights(model_json).conf

@@ -784,7 +784,7 @@ class BatchNormalization(FeedForwardLayer):
                     sv.data.copy_(rv_b)
         else:
             y = F.batch_norm(x, mean.detach(), var, g, b, False, 0.0, self.eps)
-        y = self.activation(y, training) if self.activation is not None else y
+        # no activation: the reference layer applies the normalisation only (its activationFn is never used)
         return y.permute(0, 2, 3, 1) if nhwc else y
 
 
