@@ -86,3 +86,16 @@ def test_compression_spi():
     c.setDefaultCompression("GZIP")
     assert c.getDefaultCompression() == "GZIP"
     c.setDefaultCompression("FLOAT16")
+
+
+def test_serde_extras_round_trips(tmp_path):
+    from deeplearning4j_b200.serde.extras import ArrowSerde, BinarySerde, NDArrayTextSerializer, Nd4jBase64
+    x = INDArray(torch.arange(12.0).reshape(3, 4))
+    assert torch.equal(BinarySerde.toArray(BinarySerde.toByteBuffer(x)).t, x.t)
+    BinarySerde.writeArrayToDisk(x, str(tmp_path / "a.bin"))
+    assert torch.equal(BinarySerde.readFromDisk(str(tmp_path / "a.bin")).t, x.t)
+    assert torch.equal(Nd4jBase64.fromBase64(Nd4jBase64.base64String(x)).t, x.t)
+    assert [a.t.tolist() for a in Nd4jBase64.arraysFromBase64(Nd4jBase64.arraysToBase64([x, x]))] == [x.t.tolist()] * 2
+    assert torch.equal(Nd4jBase64.fromNpyBase64(Nd4jBase64.base64StringNumpy(x)).t, x.t)
+    assert torch.equal(NDArrayTextSerializer.fromJson(NDArrayTextSerializer.toJson(x)).t, x.t)
+    assert torch.equal(ArrowSerde.fromBytes(ArrowSerde.toBytes(x)).t, x.t)
