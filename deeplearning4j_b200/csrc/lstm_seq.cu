@@ -1,0 +1,297 @@
+// Persistent LSTM sequence kernel: all time steps of one layer in a single cooperative launch.
+//
+// Math per step (DL4J gate order a|f|o|g along the 4n axis, libnd4j lstmLayer / LSTMHelpers.java):
+//   z_t = zx_t + h_{t-1} RW          zx_t = x_t W + b is computed beforehand by one large GEMM
+//   a = tanh(z_a)  f = sigm(z_f)  o = sigm(z_o)  g = sigm(z_g)
+//   c_t = f * c_{t-1} + g * a        h_t = o * tanh(c_t)
+//
+// Work split: CTA j owns hidden units [16 j, 16 j + 16) and keeps their 64 recurrent weight rows
+// (4 gates x 16 units, each row = n bf16 values) resident in shared memory for the whole sequence, so the
+// recurrent weights are read from HBM once per launch instead of once per step.  Per step the CTA streams
+// h_{t-1} ([mb, n] bf16, L2 resident) through a 4-stage TMA ring as the M operand of tcgen05.mma
+// (M = 128 batch rows, zero filled beyond mb; N = 64 gate rows; K = n), accumulates in TMEM, and its four
+// epilogue warps (one thread per batch row) apply the cell non-linearities with c_t held in registers across
+// steps, then publish their slice of h_t.  Steps are separated by a grid-wide arrive/wait on a global counter;
+// every wait is bounded and reports through the status word.
+#include "common.cuh"
+
+namespace dl4j {
+
+constexpr int LS_UNITS = 16;                 // hidden units per CTA
+constexpr int LS_N = 4 * LS_UNITS;           // MMA N: gate rows per CTA
+constexpr int LS_M = 128;                    // MMA M: batch rows (zero padded)
+constexpr int LS_BK = 64;                    // K elements per stage (128 bytes, SWIZZLE_128B)
+constexpr int LS_STAGES = 4;
+constexpr int LS_A_STAGE = LS_M * LS_BK * 2; // 16 KB
+constexpr int LS_B_KB = LS_N * LS_BK * 2;    // 8 KB per k-block of resident weights
+constexpr int LS_THREADS = 192;              // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+
+struct LstmSeqParams {
+  const __nv_bfloat16* zx;   // [T, mb, 4n]
+  __nv_bfloat16* h_all;      // [T + 1, mb, n]; slot 0 holds h_0, step s writes slot s + 1
+  const float* c0;           // [mb, n]
+  float* cs;                 // [T, mb, n]  c_t (time index, not step index)
+  __nv_bfloat16* gates;      // [T, mb, 4n] activated gates (for the backward pass)
+  int T, mb, n, reverse;
+  unsigned int* counter;     // zero on entry
+  int* status;
+};
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, int* status) {
+  if (*((volatile const unsigned int*)counter) >= target) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (*((volatile const unsigned int*)counter) < target) {
+    if ((++spins & 0xff) == 0 && (clock64() - t0 > 4000000000LL || *((volatile int*)status) != 0)) {
+      atomicCAS(status, 0, DL4J_ERR_TIMEOUT_PEER);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// sigmoid(x) = 0.5 tanh(x / 2) + 0.5: one special-function instruction
+__device__ __forceinline__ float sigm_fast(float x) { return fmaf(0.5f, tanh_fast(0.5f * x), 0.5f); }
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* o) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return u;
+}
+
+__global__ void __launch_bounds__(LS_THREADS, 1)
+lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int kblocks = p.n / LS_BK;
+  uint8_t* w_smem = smem;                                   // kblocks x 8 KB, resident
+  uint8_t* a_smem = w_smem + kblocks * LS_B_KB;             // LS_STAGES x 16 KB ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_smem + LS_STAGES * LS_A_STAGE);
+  uint64_t* full_bar = bars;                  // [LS_STAGES]
+  uint64_t* empty_bar = bars + LS_STAGES;     // [LS_STAGES]
+  uint64_t* w_full = bars + 2 * LS_STAGES;
+  uint64_t* acc_full = w_full + 1;
+  uint64_t* acc_empty = w_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 3);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit0 = blockIdx.x * LS_UNITS;
+  const unsigned int arrivals_per_step = 4u * gridDim.x;    // one arrive per epilogue warp per CTA
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_h);
+    prefetch_tmap(&tmap_w);
+    for (int i = 0; i < LS_STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    mbar_init(w_full, 1);
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, LS_N);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // resident weights: per k-block four boxes of 16 rows (one per gate) placed 2 KB apart
+      mbar_expect_tx(w_full, (uint32_t)(kblocks * LS_B_KB));
+      for (int kb = 0; kb < kblocks; ++kb)
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          tma_load_4d(w_smem + kb * LS_B_KB + g * (LS_UNITS * 128), &tmap_w, w_full, kb * LS_BK, g * p.n + unit0, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int s = 0; s < p.T && ok; ++s) {
+        if (s > 0) {
+          ok = wait_counter(p.counter, arrivals_per_step * (unsigned)s, p.status);   // every CTA published h of step s-1
+          if (!ok) break;
+          __threadfence();
+          fence_proxy_async_all();       // generic-proxy stores of other CTAs -> async-proxy (TMA) reads below
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], LS_A_STAGE);
+          tma_load_4d(a_smem + stage * LS_A_STAGE, &tmap_h, &full_bar[stage], kb * LS_BK, 0, s, 0);
+          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LS_N);
+      bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
+      tc_fence_after();
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int s = 0; s < p.T && ok; ++s) {
+        if (!mbar_wait_bounded(acc_empty, (uint32_t)((s & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * LS_A_STAGE), 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LS_B_KB), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < LS_BK / 16; ++k)
+            umma_f16(tmem_base, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(acc_full);
+      }
+    }
+  } else {
+    const int q = warp & 3;                       // TMEM lane quadrant of this warp
+    const int b = q * 32 + lane;                  // batch row handled by this thread
+    const bool row_ok = b < p.mb;
+    const long n4 = 4L * p.n;
+    float c[LS_UNITS];
+#pragma unroll
+    for (int u = 0; u < LS_UNITS; ++u) c[u] = 0.f;
+    if (row_ok) {
+      const float4* cp = reinterpret_cast<const float4*>(p.c0 + (long)b * p.n + unit0);
+#pragma unroll
+      for (int i = 0; i < LS_UNITS / 4; ++i) { const float4 v = cp[i]; c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w; }
+    }
+    bool ok = true;
+    for (int s = 0; s < p.T && ok; ++s) {
+      const int t = p.reverse ? p.T - 1 - s : s;
+      // input contribution of this step, fetched before the accumulator is ready
+      uint4 zraw[8];
+      if (row_ok) {
+        const __nv_bfloat16* zrow = p.zx + ((long)t * p.mb + b) * n4 + unit0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint4* src = reinterpret_cast<const uint4*>(zrow + (long)g * p.n);
+          zraw[2 * g] = __ldg(src);
+          zraw[2 * g + 1] = __ldg(src + 1);
+        }
+      }
+      if (!mbar_wait_bounded(acc_full, (uint32_t)(s & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+      tmem_ld_32x32(taddr, r0);
+      tmem_ld_32x32(taddr + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);      // accumulator drained: the next step's MMAs may overwrite it
+      if (row_ok) {
+        float za[16], zf[16], zo[16], zg[16];
+        unpack8(zraw[0], za); unpack8(zraw[1], za + 8);
+        unpack8(zraw[2], zf); unpack8(zraw[3], zf + 8);
+        unpack8(zraw[4], zo); unpack8(zraw[5], zo + 8);
+        unpack8(zraw[6], zg); unpack8(zraw[7], zg + 8);
+        float h[16];
+#pragma unroll
+        for (int u = 0; u < LS_UNITS; ++u) {
+          const float a = tanh_fast(za[u] + __uint_as_float(r0[u]));
+          const float f = sigm_fast(zf[u] + __uint_as_float(r0[16 + u]));
+          const float o = sigm_fast(zo[u] + __uint_as_float(r1[u]));
+          const float g = sigm_fast(zg[u] + __uint_as_float(r1[16 + u]));
+          c[u] = fmaf(f, c[u], g * a);
+          h[u] = o * tanh_fast(c[u]);
+          za[u] = a; zf[u] = f; zo[u] = o; zg[u] = g;
+        }
+        __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
+        uint4* gd;
+        gd = reinterpret_cast<uint4*>(grow);               gd[0] = pack8(za); gd[1] = pack8(za + 8);
+        gd = reinterpret_cast<uint4*>(grow + (long)p.n);     gd[0] = pack8(zf); gd[1] = pack8(zf + 8);
+        gd = reinterpret_cast<uint4*>(grow + 2L * p.n);      gd[0] = pack8(zo); gd[1] = pack8(zo + 8);
+        gd = reinterpret_cast<uint4*>(grow + 3L * p.n);      gd[0] = pack8(zg); gd[1] = pack8(zg + 8);
+        float4* cd = reinterpret_cast<float4*>(p.cs + ((long)t * p.mb + b) * p.n + unit0);
+#pragma unroll
+        for (int i = 0; i < LS_UNITS / 4; ++i) cd[i] = make_float4(c[4 * i], c[4 * i + 1], c[4 * i + 2], c[4 * i + 3]);
+        uint4* hd = reinterpret_cast<uint4*>(p.h_all + ((long)(s + 1) * p.mb + b) * p.n + unit0);
+        hd[0] = pack8(h);
+        hd[1] = pack8(h + 8);
+      }
+      __threadfence();
+      fence_proxy_async_all();
+      __syncwarp();
+      if (lane == 0) atomicAdd(p.counter, 1u);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, LS_N);
+  }
+}
+
+}  // namespace dl4j
+
+using namespace dl4j;
+
+static int ls_encode(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t nb1, uint64_t row_stride_bytes,
+                     uint64_t sb1_bytes, uint32_t box_inner, uint32_t box_outer) {
+  dl4j_PFN_encodeTiled enc = dl4j_get_encode_tiled();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {inner, outer, nb1, 1};
+  cuuint64_t strides[3] = {row_stride_bytes, sb1_bytes, sb1_bytes * nb1};
+  cuuint32_t box[4] = {box_inner, box_outer, 1, 1};
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// zx [T, mb, 4n] bf16; rw [4n, n] bf16 (row g*n + j = recurrent weights into gate g of unit j); h_all [T+1, mb, n] bf16 with slot 0 = h_0;
+// c0 [mb, n] fp32; cs [T, mb, n] fp32; gates [T, mb, 4n] bf16; counter: one unsigned int of device scratch.
+// Limits: n % 64 == 0, n <= 1216 (weights resident in shared memory), n / 16 <= SM count, 1 <= mb <= 128.
+DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, const float* c0, float* cs, void* gates, int T, int mb, int n,
+                               int reverse, unsigned int* counter, void* stream_) {
+  if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
+  const int kblocks = n / LS_BK;
+  const size_t smem = (size_t)kblocks * LS_B_KB + LS_STAGES * LS_A_STAGE + 1024 + 256;
+  if (smem > 227 * 1024) return -DL4J_ERR_BAD_ARG;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = n / LS_UNITS;
+  if (grid > sms) return -DL4J_ERR_BAD_ARG;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  CUtensorMap th, tw;
+  int r = ls_encode(&th, h_all, (uint64_t)n, (uint64_t)mb, (uint64_t)T + 1, (uint64_t)n * 2, (uint64_t)mb * n * 2, LS_BK, LS_M);
+  if (r) return -1000 - r;
+  r = ls_encode(&tw, rw, (uint64_t)n, (uint64_t)4 * n, 1, (uint64_t)n * 2, (uint64_t)4 * n * n * 2, LS_BK, LS_UNITS);
+  if (r) return -1000 - r;
+  LstmSeqParams p;
+  p.zx = reinterpret_cast<const __nv_bfloat16*>(zx);
+  p.h_all = reinterpret_cast<__nv_bfloat16*>(h_all);
+  p.c0 = c0; p.cs = cs;
+  p.gates = reinterpret_cast<__nv_bfloat16*>(gates);
+  p.T = T; p.mb = mb; p.n = n; p.reverse = reverse;
+  p.counter = counter;
+  p.status = dl4j_status_word(dev);
+  cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFuncSetAttribute(lstm_seq_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  void* args[] = {(void*)&th, (void*)&tw, (void*)&p};
+  e = cudaLaunchCooperativeKernel((void*)lstm_seq_fwd_kernel, dim3(grid), dim3(LS_THREADS), args, smem, stream);
+  return (int)e;
+}

@@ -127,16 +127,18 @@ layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
 // (one float per column and sum, lanes hit distinct banks) instead of registers: that keeps the kernel near
 // 64 registers, so four blocks fit per SM and enough loads are in flight to follow HBM.  NV = C / 256 rounded up.
 template <typename T, int NV>
-__global__ void __launch_bounds__(LN_WARPS * 32)
+__global__ void __launch_bounds__(LN_WARPS * 32, 2)
 layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gain,
                       const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
                       float* __restrict__ dgain, float* __restrict__ dbias, int rows, int C) {
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int nvec = C / 8;
-  // column c = (vi * 8 + j) lives at acc[..][j * (NV * 32) + vi]: the 32 lanes of a warp (consecutive vi) hit 32 banks
-  __shared__ float acc[2][NV * 256];
-  for (int i = threadIdx.x; i < 2 * NV * 256; i += LN_WARPS * 32) (&acc[0][0])[i] = 0.f;
-  __syncthreads();
+  // per-lane column partial sums live in registers for the whole kernel; they meet in shared memory once at the end
+  float ag[NV][8], ab[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { ag[i][j] = 0.f; ab[i][j] = 0.f; }
   for (int row = blockIdx.x * LN_WARPS + wid; row < rows; row += gridDim.x * LN_WARPS) {
     const float mean = mean_in[row], rstd = rstd_in[row];
     float xh[NV][8], dg[NV][8];
@@ -153,17 +155,17 @@ layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
     for (int i = 0; i < NV; ++i) {
       const int vi = lane + i * 32;
       if (vi < nvec) {
-        float g[8];
-        Vec8<float>::load(gain + vi * 8, g);
+        float gn[8];
+        Vec8<float>::load(gain + vi * 8, gn);      // L1 resident after the first row
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xh[i][j] - mean) * rstd;
           const float d = dg[i][j];
-          atomicAdd(&acc[0][j * (NV * 32) + vi], d * xh[i][j]);
-          atomicAdd(&acc[1][j * (NV * 32) + vi], d);
-          dg[i][j] = d * g[j];
+          ag[i][j] = fmaf(d, xh[i][j], ag[i][j]);
+          ab[i][j] += d;
+          dg[i][j] = d * gn[j];
           s1 += dg[i][j];
-          s2 += dg[i][j] * xh[i][j];
+          s2 = fmaf(dg[i][j], xh[i][j], s2);
         }
       }
     }
@@ -180,7 +182,23 @@ layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
       }
     }
   }
-  __syncthreads();
+  // column c = (vi * 8 + j) lives at acc[..][j * (NV * 32) + vi]: the 32 lanes of a warp (consecutive vi) hit 32 banks
+  __shared__ float acc[2][NV * 256];
+  for (int w = 0; w < LN_WARPS; ++w) {
+    if (wid == w) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = lane + i * 32;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int idx = j * (NV * 32) + vi;
+          if (w == 0) { acc[0][idx] = ag[i][j]; acc[1][idx] = ab[i][j]; }
+          else { acc[0][idx] += ag[i][j]; acc[1][idx] += ab[i][j]; }
+        }
+      }
+    }
+    __syncthreads();
+  }
   for (int idx = threadIdx.x; idx < NV * 256; idx += LN_WARPS * 32) {
     const int j = idx / (NV * 32), vi = idx - j * (NV * 32);
     const int col = vi * 8 + j;
@@ -358,6 +376,61 @@ bias_act_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __rest
   }
 }
 
+// Vector form for C % 8 == 0: a thread owns 8 adjacent columns (one 16-byte load per row), a warp spans 256 columns,
+// the 8 warps of a block walk rows with four independent row loads in flight per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restrict__ dz, float* __restrict__ dbias,
+                        int rows, int C, int act, int rows_per_block) {
+  __shared__ float red[8][256 + 8];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + tx * 8;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(r0 + rows_per_block, rows);
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  if (col < C) {
+    for (int r = r0 + ty; r < r1; r += 32) {
+      float d[4][8], zz[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * 8;
+        if (rr < r1) {
+          const long long o = (long long)rr * C + col;
+          Vec8<T>::load(dy + o, d[u]);
+          if (act != 0) Vec8<T>::load(z + o, zz[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * 8;
+        if (rr < r1) {
+          if (act != 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d[u][j] *= act_grad(zz[u][j], act);
+          }
+          if (dz) Vec8<T>::store(dz + (long long)rr * C + col, d[u]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s[j] += d[u][j];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[ty][tx * 8 + j] = s[j];
+  __syncthreads();
+  if (dbias) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < C) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+      atomicAdd(dbias + c, t);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- attention softmax
 // In-place row softmax over scores S [rows, Tk] (already scaled by the GEMM epilogue) with an optional
 // key mask [B, Tk] (non-zero = keep); row r belongs to example r / rows_per_example.  One warp per row.
@@ -464,7 +537,7 @@ DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gai
                                  void* dx, float* dgain, float* dbias, int rows, int C, int dtype, void* stream) {
   if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
   int grid = (rows + LN_WARPS - 1) / LN_WARPS;
-  if (grid > 148 * 4) grid = 148 * 4;
+  if (grid > 148 * 2) grid = 148 * 2;
   const int nv = (C + 255) / 256;
 #define DL4J_LN_BWD(NVV)                                                                                       \
   DL4J_DISPATCH_T(dtype, (layer_norm_bwd_kernel<T, NVV><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(     \
@@ -509,6 +582,17 @@ DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* d
                                void* stream) {
   if (rows <= 0 || C <= 0) return 0;
   if (dy == nullptr || (act != 0 && z == nullptr)) return -DL4J_ERR_BAD_ARG;
+  if (C % 8 == 0) {
+    const int ct = (C + 255) / 256;
+    int slabs = (148 * 6 + ct - 1) / ct;
+    int rpb = (rows + slabs - 1) / slabs;
+    rpb = (rpb + 31) / 32 * 32;
+    slabs = (rows + rpb - 1) / rpb;
+    dim3 grid(ct, slabs);
+    DL4J_DISPATCH_T(dtype, (bias_act_bwd_vec_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        (const T*)dy, (const T*)z, (T*)dz, dbias, rows, C, act, rpb)));
+    return (int)cudaGetLastError();
+  }
   const int col_tiles = (C + 63) / 64;
   int row_slabs = (148 * 4 + col_tiles - 1) / col_tiles;
   if (row_slabs < 1) row_slabs = 1;

@@ -107,6 +107,13 @@ class LSTM(BaseRecurrentLayer):
         zx = nnops.linear(xt.reshape(T * mb, -1), W, b).reshape(T, mb, 4 * n)
         gate, act = self.gateActivationFn, self.activation
         plain = isinstance(gate, ActivationSigmoid) and isinstance(act, ActivationTanH) and not self.PEEPHOLE
+        if plain and mask is None and c.dtype == torch.float32:
+            from ...ops import native as nat
+            if nat.lstm_seq_supported(zx, n, mb) and h.dtype == zx.dtype:
+                # whole sequence in one persistent kernel (recurrent weights resident on chip)
+                hs, h, c = nat.lstm_seq(zx, RW if RW.shape[1] == 4 * n else RW4, h, c, reverse)
+                self._store(ctx, key, (h, c))
+                return self._from_tmn(hs)
         outs = [None] * T
         steps = range(T - 1, -1, -1) if reverse else range(T)
         mt = None if mask is None else mask.to(x.dtype).t().unsqueeze(2)   # [T, mb, 1]

@@ -56,6 +56,7 @@ def _load():
             "dl4j_softmax_xent": [vp, vp, vp, vp, vp, i32, i32, i64, i32, i32, vp],
             "dl4j_lstm_cell_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_lstm_cell_bwd": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
+            "dl4j_lstm_seq_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
@@ -494,6 +495,99 @@ def lstm_cell(z, c_prev):
     if not available() or z.dtype not in _DT or c_prev.dtype != torch.float32:
         return None
     return _LstmCellFn.apply(z, c_prev)
+
+
+class _LstmSeqFn(torch.autograd.Function):
+    """Whole-sequence LSTM layer: forward is one persistent cooperative kernel (recurrent weights resident in
+    shared memory, tcgen05 MMAs per step, grid-wide step barrier); backward walks the steps with the fused
+    cell-gradient kernel plus one small GEMM per step and finishes with a single large weight-gradient GEMM.
+    Gate order and math: libnd4j ops/declarable/helpers/impl/lstmLayer.cpp, LSTMHelpers.java."""
+
+    _scratch = {}
+
+    @staticmethod
+    def forward(ctx, zx, rw, h0, c0, reverse, rw_lp):
+        l = require()
+        T, mb, n4 = zx.shape
+        n = n4 // 4
+        zx = zx.contiguous()
+        rw_t = rw_lp.t().contiguous()              # [4n, n]; a no-op for the 'f'-ordered parameter view
+        ctx.rw_dtype = rw.dtype
+        dev = zx.device
+        h_all = torch.empty((T + 1, mb, n), dtype=torch.bfloat16, device=dev)
+        h_all[0].copy_(h0)
+        cs = torch.empty((T, mb, n), dtype=torch.float32, device=dev)
+        gates = torch.empty((T, mb, n4), dtype=torch.bfloat16, device=dev)
+        counter = _LstmSeqFn._scratch.get(dev)
+        if counter is None:
+            counter = _LstmSeqFn._scratch[dev] = torch.zeros(64, dtype=torch.int32, device=dev)
+        c0 = c0.contiguous()
+        rc = l.dl4j_lstm_seq_fwd(_ptr(zx), _ptr(rw_t), _ptr(h_all), _ptr(c0), _ptr(cs), _ptr(gates), T, mb, n, int(bool(reverse)),
+                                 _ptr(counter), _stream())
+        _check(rc, "dl4j_lstm_seq_fwd")
+        ctx.reverse = bool(reverse)
+        ctx.save_for_backward(rw_t, h_all, cs, gates, c0)
+        out = h_all[1:].flip(0) if reverse else h_all[1:]
+        t_last = 0 if reverse else T - 1
+        return out, h_all[T], cs[t_last]
+
+    @staticmethod
+    def backward(ctx, dout, dh_last, dc_last):
+        l = require()
+        rw_t, h_all, cs, gates, c0 = ctx.saved_tensors
+        T, mb, n = cs.shape
+        rev = ctx.reverse
+        dout = dout.contiguous() if dout is not None else torch.zeros((T, mb, n), dtype=torch.bfloat16, device=cs.device)
+        dzx = torch.empty_like(gates)
+        dc = dc_last.contiguous().float() if dc_last is not None else None
+        dh_rec = dh_last.to(torch.bfloat16) if dh_last is not None else None
+        dt = _DT[gates.dtype]
+        stream = _stream()
+        dc_bufs = (torch.empty_like(c0), torch.empty_like(c0))
+        for s in range(T - 1, -1, -1):
+            t = T - 1 - s if rev else s
+            if s == T - 1:
+                dh = dout[t] if dh_rec is None else dout[t] + dh_rec
+            else:
+                dh = dh_rec
+            if s > 0:
+                tp = t + 1 if rev else t - 1
+                c_prev = cs[tp]
+            else:
+                c_prev = c0
+            dc_new = dc_bufs[s & 1]
+            rc = l.dl4j_lstm_cell_bwd(_ptr(dh), _ptr(dc), _ptr(gates[t]), _ptr(cs[t]), _ptr(c_prev), _ptr(dzx[t]), _ptr(dc_new), mb, n,
+                                      dt, stream)
+            _check(rc, "dl4j_lstm_cell_bwd")
+            dc = dc_new
+            if s > 0:
+                tn = t + 1 if rev else t - 1           # time index processed by step s - 1
+                dh_rec = torch.addmm(dout[tn], dzx[t], rw_t)
+            else:
+                dh_rec = torch.mm(dzx[t], rw_t) if ctx.needs_input_grad[2] else None
+        drw = None
+        if ctx.needs_input_grad[1]:
+            h_prev = h_all[:T].flip(0) if rev else h_all[:T]      # hidden state entering each time index
+            a, b = dzx.reshape(T * mb, 4 * n).t(), h_prev.reshape(T * mb, n)
+            if ctx.rw_dtype == torch.float32 and _operand_a(a) is not None and _operand_b(b) is not None:
+                drw_t = gemm_raw(a, b, out_dtype=torch.float32)
+            else:
+                drw_t = torch.mm(a, b).to(ctx.rw_dtype)
+            drw = drw_t.t()
+        return dzx, drw, dh_rec, (dc if ctx.needs_input_grad[3] else None), None, None
+
+
+def lstm_seq_supported(zx, n, mb):
+    return (available() and zx.is_cuda and zx.dtype == torch.bfloat16 and n % 64 == 0 and 64 <= n <= 1280 and 1 <= mb <= 128)
+
+
+def lstm_seq(zx, rw, h0, c0, reverse=False):
+    """``zx`` [T, mb, 4n] bf16 input pre-activations, ``rw`` [n, 4n] recurrent weights.  Returns (h for every
+    time index [T, mb, n], last h, last c)."""
+    rw_lp = getattr(rw, "_lp", None)
+    if rw_lp is None or rw_lp.dtype != zx.dtype:
+        rw_lp = rw.detach() if rw.dtype == zx.dtype else rw.detach().to(zx.dtype)
+    return _LstmSeqFn.apply(zx, rw, h0, c0, reverse, rw_lp)
 
 
 def attention(q, k, v, mask, scale):

@@ -246,3 +246,44 @@ def test_mlp_bf16_trains_on_gpu(nat):
     assert nat.LAUNCHES - before >= 40 * 8
     assert net.score() < 0.3 * s0, (s0, net.score())
     nat.check_status()
+
+
+def _lstm_ref(zx, rw, h0, c0, reverse):
+    """fp32 step loop with the DL4J gate order a|f|o|g; h is rounded to bf16 between steps like the kernel's state."""
+    T, mb, n4 = zx.shape
+    n = n4 // 4
+    h, c = h0.float(), c0.float()
+    outs = [None] * T
+    for s in range(T):
+        t = T - 1 - s if reverse else s
+        z = zx[t].float() + h.bfloat16().float() @ rw.float()
+        a, f, o, g = torch.tanh(z[:, :n]), torch.sigmoid(z[:, n:2 * n]), torch.sigmoid(z[:, 2 * n:3 * n]), torch.sigmoid(z[:, 3 * n:])
+        c = f * c + g * a
+        h = o * torch.tanh(c)
+        outs[t] = h
+    return torch.stack(outs, 0), h, c
+
+
+@pytest.mark.parametrize("T,mb,n,reverse", [(5, 64, 256, False), (7, 33, 128, True), (12, 128, 1024, False)])
+def test_lstm_sequence_kernel(nat, T, mb, n, reverse):
+    g = torch.Generator(device="cuda").manual_seed(T * 100 + mb + n)
+    zx = (torch.randn(T, mb, 4 * n, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+    rw_store = (torch.randn(4 * n, n, device="cuda", generator=g) / math.sqrt(n)).bfloat16()
+    rw = rw_store.t().requires_grad_(True)                       # logical [n, 4n], column-major storage like the parameter view
+    h0 = (torch.randn(mb, n, device="cuda", generator=g) * 0.3).bfloat16().requires_grad_(True)
+    c0 = (torch.randn(mb, n, device="cuda", generator=g) * 0.3).requires_grad_(True)
+    hs, h_last, c_last = nat.lstm_seq(zx, rw, h0, c0, reverse)
+    torch.cuda.synchronize()
+    nat.check_status()
+    w = torch.randn(T, mb, n, device="cuda", generator=g)
+    (hs.float() * w).sum().backward()
+    got = [zx.grad.clone(), rw.grad.clone(), h0.grad.clone(), c0.grad.clone()]
+    for t_ in (zx, rw, h0, c0):
+        t_.grad = None
+    ref_hs, ref_h, ref_c = _lstm_ref(zx, rw, h0, c0, reverse)
+    assert _rel(hs, ref_hs) < 2e-2, _rel(hs, ref_hs)
+    assert _rel(h_last, ref_h) < 2e-2
+    assert _rel(c_last, ref_c) < 2e-2
+    (ref_hs * w).sum().backward()
+    for name, a, b in zip(("dzx", "drw", "dh0", "dc0"), got, (zx.grad, rw.grad, h0.grad, c0.grad)):
+        assert _rel(a, b) < 6e-2, (name, _rel(a, b))
