@@ -242,6 +242,225 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
   }
 }
 
+// ----------------------------------------------------------------------------- backward
+// Walks the steps in reverse inside one cooperative launch.  CTA j owns the same 16 hidden units as in the forward
+// kernel and keeps RW[units, :] (16 rows x 4n gate columns, K-major) resident in shared memory.  Per step it forms
+//   dh_s[:, units] = dout_t[:, units] + dz_{s+1} RW[units, :]^T        (tcgen05, M = 128 batch rows, N = 16, K = 4n)
+// streaming dz_{s+1} ([mb, 4n] bf16, written by all CTAs in the previous step) through the TMA ring, then applies the
+// cell gradient with dc carried in registers and publishes its 64 columns of dz_s.  One extra MMA round after step 0
+// yields the gradient of the initial hidden state.
+struct LstmSeqBwdParams {
+  const __nv_bfloat16* dout;   // [T, mb, n]
+  const __nv_bfloat16* gates;  // [T, mb, 4n]
+  const float* cs;             // [T, mb, n]
+  const float* c0;             // [mb, n]
+  const float* dc_last;        // [mb, n] or null
+  __nv_bfloat16* dzx;          // [T, mb, 4n]
+  __nv_bfloat16* dh0;          // [mb, n] or null
+  float* dc0;                  // [mb, n] or null
+  int T, mb, n, reverse;
+  unsigned int* counter;
+  int* status;
+};
+
+constexpr int LB_N = LS_UNITS;               // MMA N
+constexpr int LB_B_KB = LB_N * LS_BK * 2;    // 2 KB of resident weights per k-block
+constexpr int LB_TMEM_COLS = 32;
+
+__global__ void __launch_bounds__(LS_THREADS, 1)
+lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int kblocks = 4 * p.n / LS_BK;
+  uint8_t* w_smem = smem;
+  uint8_t* a_smem = w_smem + kblocks * LB_B_KB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_smem + LS_STAGES * LS_A_STAGE);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + LS_STAGES;
+  uint64_t* w_full = bars + 2 * LS_STAGES;
+  uint64_t* acc_full = w_full + 1;
+  uint64_t* acc_empty = w_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 3);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit0 = blockIdx.x * LS_UNITS;
+  const unsigned int arrivals_per_step = 4u * gridDim.x;
+  const int rounds = p.T - 1 + (p.dh0 ? 1 : 0);     // MMA rounds: one per step except the last one in time, plus dh0
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_dz);
+    prefetch_tmap(&tmap_w);
+    for (int i = 0; i < LS_STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    mbar_init(w_full, 1);
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, LB_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(w_full, (uint32_t)(kblocks * LB_B_KB));
+      for (int kb = 0; kb < kblocks; ++kb) tma_load_4d(w_smem + kb * LB_B_KB, &tmap_w, w_full, kb * LS_BK, unit0, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        const int s_src = p.T - 1 - r;                         // step whose dz feeds this round
+        const int t_src = p.reverse ? p.T - 1 - s_src : s_src;
+        ok = wait_counter(p.counter, arrivals_per_step * (unsigned)(r + 1), p.status);
+        if (!ok) break;
+        __threadfence();
+        fence_proxy_async_all();
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], LS_A_STAGE);
+          tma_load_4d(a_smem + stage * LS_A_STAGE, &tmap_dz, &full_bar[stage], kb * LS_BK, 0, t_src, 0);
+          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LB_N);
+      bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
+      tc_fence_after();
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int r = 0; r < rounds && ok; ++r) {
+        if (!mbar_wait_bounded(acc_empty, (uint32_t)((r & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * LS_A_STAGE), 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LB_B_KB), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < LS_BK / 16; ++k)
+            umma_f16(tmem_base, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(acc_full);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int b = q * 32 + lane;
+    const bool row_ok = b < p.mb;
+    const long n4 = 4L * p.n;
+    float dc[LS_UNITS];
+#pragma unroll
+    for (int u = 0; u < LS_UNITS; ++u) dc[u] = 0.f;
+    if (row_ok && p.dc_last) {
+      const float4* cp = reinterpret_cast<const float4*>(p.dc_last + (long)b * p.n + unit0);
+#pragma unroll
+      for (int i = 0; i < LS_UNITS / 4; ++i) { const float4 v = cp[i]; dc[4 * i] = v.x; dc[4 * i + 1] = v.y; dc[4 * i + 2] = v.z; dc[4 * i + 3] = v.w; }
+    }
+    bool ok = true;
+    for (int s = p.T - 1; s >= -1 && ok; --s) {
+      if (s < 0 && !p.dh0) break;
+      const int r = p.T - 2 - s;                     // MMA round that produced this step's recurrent gradient (none for s = T-1)
+      const int t = p.reverse ? p.T - 1 - s : s;
+      uint4 graw[8], draw[2];
+      float ct[LS_UNITS], cp_[LS_UNITS];
+      if (row_ok && s >= 0) {
+        const __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint4* src = reinterpret_cast<const uint4*>(grow + (long)g * p.n);
+          graw[2 * g] = __ldg(src);
+          graw[2 * g + 1] = __ldg(src + 1);
+        }
+        const uint4* dsrc = reinterpret_cast<const uint4*>(p.dout + ((long)t * p.mb + b) * p.n + unit0);
+        draw[0] = __ldg(dsrc);
+        draw[1] = __ldg(dsrc + 1);
+        const float4* c4 = reinterpret_cast<const float4*>(p.cs + ((long)t * p.mb + b) * p.n + unit0);
+        const int tp = p.reverse ? t + 1 : t - 1;
+        const float4* p4 = reinterpret_cast<const float4*>((s > 0 ? p.cs + ((long)tp * p.mb + b) * p.n : p.c0 + (long)b * p.n) + unit0);
+#pragma unroll
+        for (int i = 0; i < LS_UNITS / 4; ++i) {
+          const float4 v = __ldg(c4 + i), w = __ldg(p4 + i);
+          ct[4 * i] = v.x; ct[4 * i + 1] = v.y; ct[4 * i + 2] = v.z; ct[4 * i + 3] = v.w;
+          cp_[4 * i] = w.x; cp_[4 * i + 1] = w.y; cp_[4 * i + 2] = w.z; cp_[4 * i + 3] = w.w;
+        }
+      }
+      uint32_t acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = 0u;
+      if (r >= 0) {
+        if (!mbar_wait_bounded(acc_full, (uint32_t)(r & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        tc_fence_after();
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), acc);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);
+      }
+      if (s < 0) {
+        if (row_ok) {
+          float h[16];
+#pragma unroll
+          for (int u = 0; u < LS_UNITS; ++u) h[u] = __uint_as_float(acc[u]);
+          uint4* hd = reinterpret_cast<uint4*>(p.dh0 + (long)b * p.n + unit0);
+          hd[0] = pack8(h);
+          hd[1] = pack8(h + 8);
+        }
+        break;
+      }
+      if (row_ok) {
+        float ga[16], gf[16], go[16], gg[16], dh[16];
+        unpack8(graw[0], ga); unpack8(graw[1], ga + 8);
+        unpack8(graw[2], gf); unpack8(graw[3], gf + 8);
+        unpack8(graw[4], go); unpack8(graw[5], go + 8);
+        unpack8(graw[6], gg); unpack8(graw[7], gg + 8);
+        unpack8(draw[0], dh); unpack8(draw[1], dh + 8);
+#pragma unroll
+        for (int u = 0; u < LS_UNITS; ++u) {
+          const float a = ga[u], f = gf[u], o = go[u], g = gg[u];
+          const float dhv = dh[u] + __uint_as_float(acc[u]);
+          const float tc = tanh_fast(ct[u]);
+          const float dcv = dc[u] + dhv * o * (1.f - tc * tc);
+          ga[u] = dcv * g * (1.f - a * a);
+          gf[u] = dcv * cp_[u] * f * (1.f - f);
+          go[u] = dhv * tc * o * (1.f - o);
+          gg[u] = dcv * a * g * (1.f - g);
+          dc[u] = dcv * f;
+        }
+        __nv_bfloat16* drow = p.dzx + ((long)t * p.mb + b) * n4 + unit0;
+        uint4* gd;
+        gd = reinterpret_cast<uint4*>(drow);               gd[0] = pack8(ga); gd[1] = pack8(ga + 8);
+        gd = reinterpret_cast<uint4*>(drow + (long)p.n);     gd[0] = pack8(gf); gd[1] = pack8(gf + 8);
+        gd = reinterpret_cast<uint4*>(drow + 2L * p.n);      gd[0] = pack8(go); gd[1] = pack8(go + 8);
+        gd = reinterpret_cast<uint4*>(drow + 3L * p.n);      gd[0] = pack8(gg); gd[1] = pack8(gg + 8);
+      }
+      __threadfence();
+      fence_proxy_async_all();
+      __syncwarp();
+      if (lane == 0) atomicAdd(p.counter, 1u);
+    }
+    if (row_ok && p.dc0) {
+      float4* cd = reinterpret_cast<float4*>(p.dc0 + (long)b * p.n + unit0);
+#pragma unroll
+      for (int i = 0; i < LS_UNITS / 4; ++i) cd[i] = make_float4(dc[4 * i], dc[4 * i + 1], dc[4 * i + 2], dc[4 * i + 3]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, LB_TMEM_COLS);
+  }
+}
+
 }  // namespace dl4j
 
 using namespace dl4j;
@@ -293,5 +512,44 @@ DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, cons
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)&th, (void*)&tw, (void*)&p};
   e = cudaLaunchCooperativeKernel((void*)lstm_seq_fwd_kernel, dim3(grid), dim3(LS_THREADS), args, smem, stream);
+  return (int)e;
+}
+
+// dout [T, mb, n] bf16; gates [T, mb, 4n] bf16; cs [T, mb, n] fp32; c0 [mb, n] fp32; rwt [n, 4n] bf16 row-major (row j = weights
+// from unit j into every gate column); dzx [T, mb, 4n] bf16 out; dc_last / dh0 / dc0 optional.  Same limits as the forward entry.
+DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float* cs, const float* c0, const void* rwt, void* dzx,
+                               const float* dc_last, void* dh0, float* dc0, int T, int mb, int n, int reverse, unsigned int* counter,
+                               void* stream_) {
+  if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
+  const int kblocks = 4 * n / LS_BK;
+  const size_t smem = (size_t)kblocks * LB_B_KB + LS_STAGES * LS_A_STAGE + 1024 + 256;
+  if (smem > 227 * 1024) return -DL4J_ERR_BAD_ARG;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = n / LS_UNITS;
+  if (grid > sms) return -DL4J_ERR_BAD_ARG;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  CUtensorMap td, tw;
+  int r = ls_encode(&td, dzx, (uint64_t)4 * n, (uint64_t)mb, (uint64_t)T, (uint64_t)4 * n * 2, (uint64_t)mb * 4 * n * 2, LS_BK, LS_M);
+  if (r) return -1000 - r;
+  r = ls_encode(&tw, rwt, (uint64_t)4 * n, (uint64_t)n, 1, (uint64_t)4 * n * 2, (uint64_t)4 * n * n * 2, LS_BK, LS_UNITS);
+  if (r) return -1000 - r;
+  LstmSeqBwdParams p;
+  p.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
+  p.gates = reinterpret_cast<const __nv_bfloat16*>(gates);
+  p.cs = cs; p.c0 = c0; p.dc_last = dc_last;
+  p.dzx = reinterpret_cast<__nv_bfloat16*>(dzx);
+  p.dh0 = reinterpret_cast<__nv_bfloat16*>(dh0);
+  p.dc0 = dc0;
+  p.T = T; p.mb = mb; p.n = n; p.reverse = reverse;
+  p.counter = counter;
+  p.status = dl4j_status_word(dev);
+  cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFuncSetAttribute(lstm_seq_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  void* args[] = {(void*)&td, (void*)&tw, (void*)&p};
+  e = cudaLaunchCooperativeKernel((void*)lstm_seq_bwd_kernel, dim3(grid), dim3(LS_THREADS), args, smem, stream);
   return (int)e;
 }

@@ -57,6 +57,7 @@ def _load():
             "dl4j_lstm_cell_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_lstm_cell_bwd": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_lstm_seq_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
+            "dl4j_lstm_seq_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
@@ -504,6 +505,7 @@ class _LstmSeqFn(torch.autograd.Function):
     Gate order and math: libnd4j ops/declarable/helpers/impl/lstmLayer.cpp, LSTMHelpers.java."""
 
     _scratch = {}
+    PERSISTENT_BACKWARD = True       # False: per-step cell-gradient kernel + GEMM (kept as the cross-check path)
 
     @staticmethod
     def forward(ctx, zx, rw, h0, c0, reverse, rw_lp):
@@ -543,8 +545,22 @@ class _LstmSeqFn(torch.autograd.Function):
         dh_rec = dh_last.to(torch.bfloat16) if dh_last is not None else None
         dt = _DT[gates.dtype]
         stream = _stream()
-        dc_bufs = (torch.empty_like(c0), torch.empty_like(c0))
-        for s in range(T - 1, -1, -1):
+        persistent = _LstmSeqFn.PERSISTENT_BACKWARD and dout.dtype == torch.bfloat16
+        if persistent:
+            # every step of the gradient recursion in one cooperative kernel; weights as [n, 4n] row-major
+            if dh_rec is not None:
+                dout = dout.clone()
+                dout[0 if rev else T - 1] += dh_rec
+            rwt = rw_t.t().contiguous()
+            need_h0, need_c0 = ctx.needs_input_grad[2], ctx.needs_input_grad[3]
+            dh0 = torch.empty((mb, n), dtype=torch.bfloat16, device=cs.device) if need_h0 else None
+            dc0 = torch.empty_like(c0) if need_c0 else None
+            counter = _LstmSeqFn._scratch[cs.device]
+            rc = l.dl4j_lstm_seq_bwd(_ptr(dout), _ptr(gates), _ptr(cs), _ptr(c0), _ptr(rwt), _ptr(dzx), _ptr(dc), _ptr(dh0), _ptr(dc0),
+                                     T, mb, n, int(rev), _ptr(counter), stream)
+            _check(rc, "dl4j_lstm_seq_bwd")
+            dh_rec, dc = dh0, dc0
+        for s in (range(T - 1, -1, -1) if not persistent else ()):
             t = T - 1 - s if rev else s
             if s == T - 1:
                 dh = dout[t] if dh_rec is None else dout[t] + dh_rec

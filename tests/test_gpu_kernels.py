@@ -264,8 +264,10 @@ def _lstm_ref(zx, rw, h0, c0, reverse):
     return torch.stack(outs, 0), h, c
 
 
-@pytest.mark.parametrize("T,mb,n,reverse", [(5, 64, 256, False), (7, 33, 128, True), (12, 128, 1024, False)])
-def test_lstm_sequence_kernel(nat, T, mb, n, reverse):
+@pytest.mark.parametrize("persistent_bwd", [True, False])
+@pytest.mark.parametrize("T,mb,n,reverse", [(5, 64, 256, False), (7, 33, 128, True), (12, 128, 1024, False), (1, 16, 64, False)])
+def test_lstm_sequence_kernel(nat, T, mb, n, reverse, persistent_bwd, monkeypatch):
+    monkeypatch.setattr(nat._LstmSeqFn, "PERSISTENT_BACKWARD", persistent_bwd)
     g = torch.Generator(device="cuda").manual_seed(T * 100 + mb + n)
     zx = (torch.randn(T, mb, 4 * n, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
     rw_store = (torch.randn(4 * n, n, device="cuda", generator=g) / math.sqrt(n)).bfloat16()
@@ -277,6 +279,8 @@ def test_lstm_sequence_kernel(nat, T, mb, n, reverse):
     nat.check_status()
     w = torch.randn(T, mb, n, device="cuda", generator=g)
     (hs.float() * w).sum().backward()
+    torch.cuda.synchronize()
+    nat.check_status()
     got = [zx.grad.clone(), rw.grad.clone(), h0.grad.clone(), c0.grad.clone()]
     for t_ in (zx, rw, h0, c0):
         t_.grad = None
