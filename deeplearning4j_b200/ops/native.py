@@ -560,6 +560,7 @@ class _LstmSeqFn(torch.autograd.Function):
                                      T, mb, n, int(rev), _ptr(counter), stream)
             _check(rc, "dl4j_lstm_seq_bwd")
             dh_rec, dc = dh0, dc0
+        dc_bufs = (torch.empty_like(c0), torch.empty_like(c0))
         for s in (range(T - 1, -1, -1) if not persistent else ()):
             t = T - 1 - s if rev else s
             if s == T - 1:
