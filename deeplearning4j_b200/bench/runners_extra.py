@@ -147,14 +147,16 @@ class GradShareRunner(BaseRunner):
         for side in sides:
             n = side * side
             res = {"bytes": 4 * n}
-            for mode, impl in (("averaging", "fused"), ("averaging", "nccl"), ("shared_gradients", "fused")):
+            default_mm = W >= 4          # FusedSharing's own policy: in-switch reduction pays from four ranks on
+            for mode, impl, mm in (("averaging", "fused", None), ("averaging", "fused", not default_mm), ("averaging", "nccl", None),
+                                   ("shared_gradients", "fused", None)):
                 conf = (nn.NeuralNetConfiguration.Builder().seed(1).updater(nn.Sgd(0.1)).list()
                         .layer(nn.DenseLayer(nIn=side, nOut=side, hasBias=False, activation="identity"))
                         .layer(nn.LossLayer("MSE", activation="identity")).build())
                 net = nn.MultiLayerNetwork(conf)
                 net.device = self.device
                 net.init()
-                s = attach_gradient_sharing(net, mode, impl, FixedThresholdAlgorithm(1e-3))
+                s = attach_gradient_sharing(net, mode, impl, FixedThresholdAlgorithm(1e-3), use_multimem=mm)
                 g = torch.Generator(device=self.device).manual_seed(5 + self.rank)
                 src = torch.randn(n, device=self.device, generator=g) * 1e-3
                 if mode == "shared_gradients":
@@ -183,7 +185,9 @@ class GradShareRunner(BaseRunner):
                 t = torch.tensor([ms], dtype=torch.float64, device=self.device)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t[0])
-                key = f"{'dense' if mode == 'averaging' else 'threshold'}_{impl}"
+                key = f"{'dense' if mode == 'averaging' else 'threshold'}_{impl}" + ("_alt" if mm is not None else "")
+                if mm is not None:
+                    res[key + "_multimem"] = bool(s.fused.use_multimem)
                 res[key + "_ms"] = ms
                 res[key + "_algbw_gbs"] = 4 * n / ms / 1e6
                 if key == "dense_fused":

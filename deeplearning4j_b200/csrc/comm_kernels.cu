@@ -148,55 +148,75 @@ allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChu
       float* st1 = st0 + sg.block_numel;
       float* st2 = st1 + sg.block_numel;
       const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
-      const bool vec_ok = ((ch.offset & 3) == 0);
+      const int ns = upd_n_state(sg.kernel_id);
+      __nv_bfloat16* my_shadow = c.shadow[c.rank];
+      const uintptr_t al = (uintptr_t)(ch.offset & 3) | (ns > 0 ? reinterpret_cast<uintptr_t>(st0) : 0) |
+                           (ns > 1 ? reinterpret_cast<uintptr_t>(st1) : 0) | (ns > 2 ? reinterpret_cast<uintptr_t>(st2) : 0);
+      const bool vec_ok = (al & 15) == 0;
       const bool sh_vec = ((sh0 & 3) == 0);
       const int nvec = vec_ok ? ch.count / 4 : 0;
-      for (int v = threadIdx.x; v < nvec; v += COMM_THREADS) {
-        const long long i = ch.offset + 4LL * v;
-        float4 g;
-        if (use_multimem) {
-          g = multimem_ld_reduce_f4(c.mc_grads + i);
-        } else {
-          g = make_float4(0.f, 0.f, 0.f, 0.f);
+      // two vectors per thread and iteration: every load of both (peer gradients, parameters, state) is issued
+      // before the first use so that enough bytes are in flight to cover the NVLink round trip
+      constexpr int U = 2;
+      for (int v0 = threadIdx.x; v0 < nvec; v0 += COMM_THREADS * U) {
+        float4 g[U], w[U], a4[U], b4[U], c4[U];
 #pragma unroll
-          for (int r = 0; r < MAX_RANKS; ++r) {
-            if (r < c.world) {
-              const float4 t = ld_peer_f4(c.grads[(c.rank + r) % c.world] + i);
-              g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + u * COMM_THREADS;
+          g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          w[u] = g[u]; a4[u] = g[u]; b4[u] = g[u]; c4[u] = g[u];
+          if (v < nvec) {
+            const long long i = ch.offset + 4LL * v;
+            if (use_multimem) {
+              g[u] = multimem_ld_reduce_f4(c.mc_grads + i);
+            } else {
+#pragma unroll
+              for (int r = 0; r < MAX_RANKS; ++r) {
+                if (r < c.world) {
+                  const float4 t = ld_peer_f4(c.grads[(c.rank + r) % c.world] + i);
+                  g[u].x += t.x; g[u].y += t.y; g[u].z += t.z; g[u].w += t.w;
+                }
+              }
             }
+            w[u] = *reinterpret_cast<const float4*>(my_params + i);
+            if (ns > 0) a4[u] = *reinterpret_cast<const float4*>(st0 + 4 * v);
+            if (ns > 1) b4[u] = *reinterpret_cast<const float4*>(st1 + 4 * v);
+            if (ns > 2) c4[u] = *reinterpret_cast<const float4*>(st2 + 4 * v);
           }
         }
-        float4 w = *reinterpret_cast<const float4*>(my_params + i);
-        if (sg.kernel_id != 9) {
-          const int e = 4 * v;
-          w.x -= updater_step(sg, h, w.x, g.x * grad_scale, st0 + e, st1 + e, st2 + e);
-          w.y -= updater_step(sg, h, w.y, g.y * grad_scale, st0 + e + 1, st1 + e + 1, st2 + e + 1);
-          w.z -= updater_step(sg, h, w.z, g.z * grad_scale, st0 + e + 2, st1 + e + 2, st2 + e + 2);
-          w.w -= updater_step(sg, h, w.w, g.w * grad_scale, st0 + e + 3, st1 + e + 3, st2 + e + 3);
-        }
-        __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
-        const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-        if (use_multimem) {
-          multimem_st_f4(c.mc_params + i, w);
-          if (c.mc_shadow) {
-            if (sh_vec) multimem_st_b64(c.mc_shadow + sh0 + 4LL * v, packed);
-            else
-              for (int r = 0; r < c.world; ++r) {
-                __nv_bfloat16* s = c.shadow[r] + sh0 + 4LL * v;
-                s[0] = __float2bfloat16(w.x); s[1] = __float2bfloat16(w.y); s[2] = __float2bfloat16(w.z); s[3] = __float2bfloat16(w.w);
-              }
-          }
-        } else {
 #pragma unroll
-          for (int r = 0; r < MAX_RANKS; ++r) {
-            if (r < c.world) {
-              const int pr = (c.rank + r) % c.world;
-              *reinterpret_cast<float4*>(c.params[pr] + i) = w;
-              if (c.shadow[pr]) {
-                __nv_bfloat16* s = c.shadow[pr] + sh0 + 4LL * v;
-                if (sh_vec) *reinterpret_cast<uint2*>(s) = packed;
-                else { s[0] = __float2bfloat16(w.x); s[1] = __float2bfloat16(w.y); s[2] = __float2bfloat16(w.z); s[3] = __float2bfloat16(w.w); }
-              }
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + u * COMM_THREADS;
+          if (v >= nvec) continue;
+          const long long i = ch.offset + 4LL * v;
+          float wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+          if (sg.kernel_id != 9) {
+            float sa[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w}, sb[4] = {b4[u].x, b4[u].y, b4[u].z, b4[u].w},
+                  sc[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] -= updater_step(sg, h, wv[j], gv[j] * grad_scale, sa + j, sb + j, sc + j);
+            if (ns > 0) *reinterpret_cast<float4*>(st0 + 4 * v) = make_float4(sa[0], sa[1], sa[2], sa[3]);
+            if (ns > 1) *reinterpret_cast<float4*>(st1 + 4 * v) = make_float4(sb[0], sb[1], sb[2], sb[3]);
+            if (ns > 2) *reinterpret_cast<float4*>(st2 + 4 * v) = make_float4(sc[0], sc[1], sc[2], sc[3]);
+          }
+          const float4 wn = make_float4(wv[0], wv[1], wv[2], wv[3]);
+          if (use_multimem) {
+            multimem_st_f4(c.mc_params + i, wn);
+          } else {
+#pragma unroll
+            for (int r = 0; r < MAX_RANKS; ++r)
+              if (r < c.world) *reinterpret_cast<float4*>(c.params[(c.rank + r) % c.world] + i) = wn;
+          }
+          // only the fp32 master crosses the link; every rank derives its own bf16 shadow (here for the owned chunks,
+          // in the last phase for the others)
+          if (my_shadow) {
+            __nv_bfloat16* sp = my_shadow + sh0 + 4LL * v;
+            if (sh_vec) {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(wv[0], wv[1]), hi = __floats2bfloat162_rn(wv[2], wv[3]);
+              *reinterpret_cast<uint2*>(sp) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) sp[j] = __float2bfloat16(wv[j]);
             }
           }
         }
@@ -208,10 +228,8 @@ allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChu
         for (int r = 0; r < c.world; ++r) g += ld_peer_f(c.grads[r] + i);
         float w = my_params[i];
         if (sg.kernel_id != 9) w -= updater_step(sg, h, w, g * grad_scale, st0 + e, st1 + e, st2 + e);
-        for (int r = 0; r < c.world; ++r) {
-          c.params[r][i] = w;
-          if (c.shadow[r]) c.shadow[r][sh0 + e] = __float2bfloat16(w);
-        }
+        for (int r = 0; r < c.world; ++r) c.params[r][i] = w;
+        if (my_shadow) my_shadow[sh0 + e] = __float2bfloat16(w);
       }
     }
     __threadfence_system();
@@ -228,6 +246,29 @@ allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChu
       g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (blockIdx.x == 0)
       for (long long i = n4 * 4 + threadIdx.x; i < n_total; i += COMM_THREADS) c.grads[c.rank][i] = 0.f;
+    // bf16 shadow of the chunks that other ranks own, from the fp32 values they stored here in phase 1
+    __nv_bfloat16* my_shadow = c.shadow[c.rank];
+    if (my_shadow) {
+      const int c0 = (int)((long long)n_chunks * c.rank / c.world), c1 = (int)((long long)n_chunks * (c.rank + 1) / c.world);
+      const float* my_params = c.params[c.rank];
+      const int n_other = n_chunks - (c1 - c0);
+      for (int k = blockIdx.x; k < n_other; k += gridDim.x) {
+        const int ci = k < c0 ? k : k + (c1 - c0);
+        const UpdChunk ch = chunks[ci];
+        const UpdSegment sg = segs[ch.seg];
+        const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+        const float* src = my_params + ch.offset;
+        __nv_bfloat16* dst = my_shadow + sh0;
+        const bool vec = ((ch.offset & 3) == 0) && ((sh0 & 3) == 0);
+        const int nvec = vec ? ch.count / 4 : 0;
+        for (int v = threadIdx.x; v < nvec; v += COMM_THREADS) {
+          const float4 w = __ldcg(reinterpret_cast<const float4*>(src) + v);
+          __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+          reinterpret_cast<uint2*>(dst)[v] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+        for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) dst[e] = __float2bfloat16(__ldcg(src + e));
+      }
+    }
   }
 }
 

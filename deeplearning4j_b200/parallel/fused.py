@@ -87,7 +87,9 @@ class FusedSharing:
             a.msg[r] = hm.buffer_ptrs[r] if hm is not None else None
         mc_ok = bool(getattr(hg, "multicast_ptr", 0)) and bool(getattr(hp, "multicast_ptr", 0)) and \
             (hs is None or bool(getattr(hs, "multicast_ptr", 0)))
-        self.use_multimem = mc_ok if use_multimem is None else (bool(use_multimem) and mc_ok)
+        # multimem.ld_reduce / multimem.st also move the requester's own copy through the switch, so plain peer loads and
+        # stores carry fewer bytes per GPU below four ranks; from four ranks on the in-switch reduction wins
+        self.use_multimem = (mc_ok and self.world >= 4) if use_multimem is None else (bool(use_multimem) and mc_ok)
         a.mc_grads = hg.multicast_ptr if mc_ok else None
         a.mc_params = hp.multicast_ptr if mc_ok else None
         a.mc_shadow = hs.multicast_ptr if (mc_ok and hs is not None) else None
