@@ -334,7 +334,11 @@ class SameDiff:
     def placeHolder(self, name, dtype=DataType.FLOAT, *shape):
         if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
             shape = shape[0]
-        return self._add_var(name, VariableType.PLACEHOLDER, dtype, shape)
+        return self._add_var(self._scoped(name), VariableType.PLACEHOLDER, dtype, shape)
+
+    def _scoped(self, name):
+        """Explicit names are prefixed with the active name scope (``SameDiff.java`` ``withNameScope``)."""
+        return "/".join(self._scopes) + "/" + name if self._scopes else name
 
     def var(self, name=None, *args, dtype=None, shape=None, weightInit=None):
         """``var(name, array)``, ``var(name, dtype, *shape)``, ``var(name, weightInitScheme, dtype, *shape)``."""
@@ -349,7 +353,7 @@ class SameDiff:
             dtype = rest.pop(0)
         if rest:
             shape = rest[0] if len(rest) == 1 and isinstance(rest[0], (list, tuple)) else rest
-        name = name or self._unique("sd_var")
+        name = self._scoped(name) if name else self._unique("sd_var")
         if arr is None:
             dtype = dtype or DataType.FLOAT
             shape = tuple(int(s) for s in shape)
@@ -361,7 +365,8 @@ class SameDiff:
                 if len(shape) > 2:
                     rf = int(np.prod(shape[2:]))
                     fan_in, fan_out = shape[1] * rf, shape[0] * rf
-                g = torch.Generator().manual_seed(hash(name) & 0x7FFFFFFF)
+                import zlib
+                g = torch.Generator().manual_seed(zlib.crc32(name.encode()) & 0x7FFFFFFF)   # same on every rank and run
                 tmp = torch.empty(shape, dtype=torch.float32)
                 wi.init(fan_in, fan_out, tmp, g)
                 arr = tmp.to(dtype.to_torch())
@@ -375,7 +380,7 @@ class SameDiff:
         if value is None and not isinstance(name, str):
             name, value = None, name
         t = _scalar_like(value) if not isinstance(value, (torch.Tensor, INDArray, np.ndarray)) else _tensor(value)
-        name = name or self._unique("const")
+        name = self._scoped(name) if name else self._unique("const")
         v = self._add_var(name, VariableType.CONSTANT, DataType.from_torch(t.dtype), t.shape)
         self.arrays[name] = t.to(self.device)
         return v
@@ -505,13 +510,45 @@ class SameDiff:
         return self._op("select", [c, t, f], name=names[0] if names and names[0] else None)
 
     def whileLoop(self, *a):
-        """``whileLoop([outputNames, loopName,] loopVars, cond_fn, body_fn)`` — the loop body is captured as
-        Python callables over torch tensors and executed eagerly by one ``while_loop`` node."""
-        loop_vars = next(x for x in a if isinstance(x, (list, tuple)) and x and isinstance(x[0], SDVariable))
+        """``whileLoop([outputNames, loopName,] loopVars, cond, body)`` (``SameDiff.java`` ``whileLoop``).
+
+        ``cond`` / ``body`` are either SameDiff lambdas ``(sd, SDVariable[]) -> SDVariable | SDVariable[]`` that
+        define ops on this instance (captured once and replayed per iteration; they may read outer variables), or
+        plain callables over torch tensors ``(*tensors) -> tensor(s)``.  Both run eagerly inside one
+        ``while_loop`` node."""
+        import inspect
+        loop_vars = list(next(x for x in a if isinstance(x, (list, tuple)) and x and isinstance(x[0], SDVariable)))
         fns = [f for f in a if callable(f)]
         cond_fn, body_fn = fns
-        sub = (self, cond_fn, body_fn, len(loop_vars))
-        outs = self._op("while_loop", list(loop_vars), n_out=len(loop_vars), body=sub)
+        try:
+            graph_mode = len(inspect.signature(cond_fn).parameters) == 2
+        except (TypeError, ValueError):
+            graph_mode = False
+        if not graph_mode:
+            sub = (self, cond_fn, body_fn, len(loop_vars))
+            outs = self._op("while_loop", loop_vars, n_out=len(loop_vars), body=sub)
+            return outs if isinstance(outs, list) else [outs]
+        loop_name = next((x for x in a if isinstance(x, str)), None) or self._unique("while")
+        phs = [self._add_var(self._unique(f"{loop_name}/in{i}"), VariableType.ARRAY, v.dataType(), v.getShape())
+               for i, v in enumerate(loop_vars)]
+        mark = len(self.ops)
+        c = cond_fn(self, phs)
+        cond_ops = self.ops[mark:]
+        del self.ops[mark:]
+        r = body_fn(self, phs)
+        r = list(r) if isinstance(r, (list, tuple)) else [r]
+        body_ops = self.ops[mark:]
+        del self.ops[mark:]
+        if len(r) != len(loop_vars):
+            raise ValueError(f"loop body returned {len(r)} variables for {len(loop_vars)} loop variables")
+        produced = {o for op in cond_ops + body_ops for o in op.outputs} | {p.name for p in phs}
+        extra = []
+        for op in cond_ops + body_ops:
+            for i in op.inputs:
+                if i is not None and i not in produced and i not in extra and self.variables[i].variableType == VariableType.ARRAY:
+                    extra.append(i)
+        sub = ("graph", [p.name for p in phs], c.name, cond_ops, [v.name for v in r], body_ops, extra)
+        outs = self._op("while_loop", loop_vars + [self.variables[e] for e in extra], n_out=len(loop_vars), body=sub)
         return outs if isinstance(outs, list) else [outs]
 
     # ------------------------------------------------------------------ loss / training config

@@ -121,8 +121,55 @@ class InferenceSession:
         return vals
 
 
+def _exec_ops(sd, ops, local, training=False):
+    """Run a captured op list (loop condition / body) over ``local`` values, falling back to the graph's arrays."""
+    for node in ops:
+        d = registry.get(node.opName)
+        ins = []
+        for i in node.inputs:
+            if i is None:
+                ins.append(None)
+                continue
+            v = local.get(i)
+            if v is None:
+                v = sd.arrays.get(i)
+            if v is None:
+                raise ValueError(f"variable '{i}' has no value inside loop op '{node.name}'")
+            ins.append(v)
+        if node.opName == "while_loop":
+            res = _run_while(sd, ins, node.args["body"], local)
+        elif node.opName in _TRAINING_AWARE:
+            res = d.fn(*ins, training=training, **node.args)
+        else:
+            res = d.fn(*ins, **node.args)
+        if isinstance(res, (tuple, list)) and not (len(node.outputs) == 1 and d.n_out == 1):
+            for o, r in zip(node.outputs, res):
+                local[o] = r
+        else:
+            local[node.outputs[0]] = res
+
+
 def _run_while(sd, ins, body, vals):
-    """Eager loop: ``cond_fn`` / ``body_fn`` receive and return torch tensors."""
+    """Eager loop.  Two body forms: Python callables over torch tensors, or op lists captured from SameDiff
+    lambdas (``SameDiff.whileLoop``), whose loop-carried inputs are fed through stand-in variables."""
+    if body[0] == "graph":
+        _, ph_names, cond_name, cond_ops, out_names, body_ops, extra_names = body
+        n = len(ph_names)
+        state = list(ins[:n])
+        outer = dict(zip(extra_names, ins[n:]))
+        it = 0
+        while True:
+            local = dict(outer)
+            local.update(zip(ph_names, state))
+            _exec_ops(sd, cond_ops, local)
+            if not bool(torch.as_tensor(local[cond_name]).all()):
+                break
+            _exec_ops(sd, body_ops, local)
+            state = [local[o] for o in out_names]
+            it += 1
+            if it > 10_000_000:
+                raise RuntimeError("whileLoop exceeded 1e7 iterations")
+        return tuple(state)
     _, cond_fn, body_fn, n = body
     state = list(ins)
     it = 0
