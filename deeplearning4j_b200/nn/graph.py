@@ -15,6 +15,9 @@ from .conf.graphconf import AttentionVertex, ComputationGraphConfiguration, Froz
 from .network import BaseNetwork, _as_tensor
 
 
+from .conf.graphconf import ElementWiseVertex
+
+
 class _VertexOwner:
     """Lets a parameterised non-layer vertex (AttentionVertex) take part in the updater machinery."""
     gradientNormalization = None
@@ -120,8 +123,59 @@ class ComputationGraph(BaseNetwork):
             inputs = [inputs]
         return {n: self._prep(x) for n, x in zip(self.conf.networkInputs, inputs)}
 
+    def _fusion_plan(self):
+        """Peephole plan for the executor: ``BatchNormalization -> ActivationLayer(ReLU)`` and
+        ``BatchNormalization -> ElementWiseVertex(Add) -> ActivationLayer(ReLU)`` chains whose intermediate results have no
+        other consumer run as one fused normalise(+add)+ReLU step.  vertex name -> action tuple."""
+        plan = getattr(self, "_fuse_plan", None)
+        if plan is not None:
+            return plan
+        from .activations import ActivationReLU
+        from .layers.conv import BatchNormalization
+        from .layers.core import ActivationLayer
+        conf = self.conf
+        consumers = {}
+        for n in self.order:
+            for i in conf.vertexInputs[n]:
+                consumers.setdefault(i, []).append(n)
+        outs = set(conf.networkOutputs)
+
+        def plain_layer(n, cls):
+            v = conf.vertices.get(n)
+            return isinstance(v, LayerVertex) and type(v.layer) is cls and v.preProcessor is None and n not in outs \
+                and getattr(v.layer, "dropOut", None) is None
+
+        def is_relu(n):
+            a = conf.vertices[n].layer.activation if plain_layer(n, ActivationLayer) else None
+            return isinstance(a, ActivationReLU) and a.max is None and not a.threshold and not a.negativeSlope
+
+        plan = {}
+        for n in self.order:
+            if not plain_layer(n, BatchNormalization) or n in plan:
+                continue
+            cs = consumers.get(n, [])
+            if len(cs) != 1:
+                continue
+            c = cs[0]
+            if is_relu(c):
+                plan[n] = ("bn_relu",)
+                plan[c] = ("alias", n)
+                continue
+            v = conf.vertices[c]
+            if isinstance(v, ElementWiseVertex) and v.op == "Add" and len(conf.vertexInputs[c]) == 2 and c not in outs and c not in plan:
+                cc = consumers.get(c, [])
+                if len(cc) == 1 and is_relu(cc[0]):
+                    other = [i for i in conf.vertexInputs[c] if i != n]
+                    if len(other) == 1:
+                        plan[n] = ("defer",)
+                        plan[c] = ("bn_add_relu", n, other[0])
+                        plan[cc[0]] = ("alias", c)
+        self._fuse_plan = plan
+        return plan
+
     def _forward(self, inputs: dict, training, fmasks=None, ctx=None, stop_at_preout=False):
         ctx = ctx if ctx is not None else {}
+        fuse = self._fusion_plan() if ctx.get("fuse") else {}
         acts = dict(inputs)
         masks = dict(fmasks or {})
         first = next(iter(inputs.values()))
@@ -134,6 +188,21 @@ class ComputationGraph(BaseNetwork):
             v = conf.vertices[n]
             ins = [acts[i] for i in conf.vertexInputs[n]]
             in_masks = [masks.get(i) for i in conf.vertexInputs[n]]
+            act = fuse.get(n)
+            if act is not None:
+                if act[0] == "bn_relu":
+                    y = v.layer.forward(self.param_views.get(n, {}), ins[0], training, in_masks[0], None, fuse_relu=True)
+                elif act[0] == "defer":
+                    y = ins[0]                      # normalised later, at the add vertex that consumes it
+                elif act[0] == "bn_add_relu":
+                    bn = conf.vertices[act[1]]
+                    y = bn.layer.forward(self.param_views.get(act[1], {}), acts[act[1]], training, masks.get(act[1]), None,
+                                         fuse_relu=True, residual=acts[act[2]])
+                else:                               # alias: the ReLU already happened upstream
+                    y = acts[act[1]]
+                masks[n] = in_masks[0]
+                acts[n] = y
+                continue
             if isinstance(v, LayerVertex):
                 x, m = ins[0], in_masks[0]
                 if v.preProcessor is not None:
@@ -189,6 +258,7 @@ class ComputationGraph(BaseNetwork):
     # ------------------------------------------------------------------ loss
     def _loss(self, ins, labels, fmasks=None, lmasks=None, training=True, ctx=None):
         ctx = ctx if ctx is not None else {}
+        ctx.setdefault("fuse", True)      # only the outputs are read here, so fused chains may skip intermediate activations
         self._forward(ins, training, fmasks, ctx)
         total = None
         mb = ctx["minibatch"]

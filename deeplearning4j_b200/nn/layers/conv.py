@@ -748,11 +748,15 @@ class BatchNormalization(FeedForwardLayer):
     def regularizers(self, spec):
         return []   # the reference never regularises batch-norm parameters
 
-    def forward(self, p, x, training, mask=None, ctx=None):
+    def forward(self, p, x, training, mask=None, ctx=None, fuse_relu=False, residual=None):
+        """``fuse_relu`` / ``residual`` are set by the graph executor when this layer is followed by a ReLU (optionally
+        after an element-wise add): the result is then ``relu(bn(x) [+ residual])`` from one fused kernel chain."""
         n = self.nOut or self.nIn
         nhwc = x.dim() == 4 and self.cnn2DFormat == CNN2DFormat.NHWC
         if nhwc:
             x = x.permute(0, 3, 1, 2)
+            if residual is not None:
+                residual = residual.permute(0, 3, 1, 2)
         if self.lockGammaBeta:
             g = torch.full((n,), self.gamma, device=x.device, dtype=torch.float32)
             b = torch.full((n,), self.beta, device=x.device, dtype=torch.float32)
@@ -761,10 +765,22 @@ class BatchNormalization(FeedForwardLayer):
         mean = p["mean"].reshape(-1)
         if self.useLogStd:
             sv = p["log10stdev"].reshape(-1)
-            var = torch.pow(10.0, 2.0 * sv.detach())
         else:
             sv = p["var"].reshape(-1)
-            var = sv.detach()
+        from ...ops import native as nat
+        from ...ops import nnops
+        if not nnops._FORCE_TORCH and x.dim() in (2, 4) and mean.dtype == torch.float32 and nat.bn_supported(x):
+            # hand-written channels-last kernels: statistics, running-stat update, normalise (+ add) (+ ReLU)
+            if training:
+                y = nat.bn_act_train(x, residual, g, b, mean.detach(), sv.detach(), self.useLogStd, self.decay, self.eps, fuse_relu)
+            else:
+                with torch.no_grad():
+                    var = torch.pow(10.0, 2.0 * sv) if self.useLogStd else sv
+                    scale = g.float() * torch.rsqrt(var + self.eps)
+                    shift = b.float() - mean * scale
+                y = nat.bn_act_eval(x, residual, scale, shift, fuse_relu)
+            return y.permute(0, 2, 3, 1) if nhwc else y
+        var = torch.pow(10.0, 2.0 * sv.detach()) if self.useLogStd else sv.detach()
         if training:
             # batch statistics; running stats use DL4J's decay: global = decay*global + (1-decay)*batch
             rm, rv = mean.detach().clone(), var.clone()
@@ -784,7 +800,11 @@ class BatchNormalization(FeedForwardLayer):
                     sv.data.copy_(rv_b)
         else:
             y = F.batch_norm(x, mean.detach(), var, g, b, False, 0.0, self.eps)
-        # no activation: the reference layer applies the normalisation only (its activationFn is never used)
+        # no activation of its own: the reference layer applies the normalisation only (its activationFn is never used)
+        if residual is not None:
+            y = y + residual
+        if fuse_relu:
+            y = torch.relu(y)
         return y.permute(0, 2, 3, 1) if nhwc else y
 
 

@@ -59,6 +59,10 @@ def _load():
             "dl4j_lstm_seq_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_lstm_seq_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+            "dl4j_bn_fwd_train": [vp, vp, vp, vp, vp, vp, i32, f32, f32, i32, vp, vp, vp, vp, i64, i32, vp],
+            "dl4j_bn_apply": [vp, vp, vp, vp, i32, vp, i64, i32, vp],
+            "dl4j_bn_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, vp],
+            "dl4j_add_relu": [vp, vp, vp, i64, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
             "dl4j_bind_device": [i32],
@@ -605,6 +609,120 @@ def lstm_seq(zx, rw, h0, c0, reverse=False):
     if rw_lp is None or rw_lp.dtype != zx.dtype:
         rw_lp = rw.detach() if rw.dtype == zx.dtype else rw.detach().to(zx.dtype)
     return _LstmSeqFn.apply(zx, rw, h0, c0, reverse, rw_lp)
+
+
+# =========================================================================== batch norm (+ residual) (+ ReLU)
+def _rows_c(x):
+    """(rows, C) of a channels-last 4-D or a plain 2-D activation."""
+    if x.dim() == 4:
+        return x.shape[0] * x.shape[2] * x.shape[3], x.shape[1]
+    return x.shape[0], x.shape[1]
+
+
+def _dense_cl(x):
+    """Channels-last dense layout for 4-D tensors, row-major for 2-D ones (copies only when needed)."""
+    if x.dim() == 4:
+        return x if x.is_contiguous(memory_format=torch.channels_last) else x.contiguous(memory_format=torch.channels_last)
+    return x.contiguous()
+
+
+class _BnActFn(torch.autograd.Function):
+    """y = act(batchnorm_train(x) [+ res]) over channels-last bf16 activations; running statistics are updated in place by
+    the kernel (``nn/layers/normalization/BatchNormalization.java`` semantics: biased batch variance, decay rule)."""
+
+    @staticmethod
+    def forward(ctx, x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu):
+        l = require()
+        x = _dense_cl(x)
+        res = _dense_cl(res) if res is not None else None
+        rows, C = _rows_c(x)
+        y = torch.empty_like(x)
+        save = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+        work = torch.empty(4 * C, dtype=torch.float32, device=x.device)
+        g = gamma.detach().float().contiguous() if gamma is not None else None
+        b = beta.detach().float().contiguous() if beta is not None else None
+        rc = l.dl4j_bn_fwd_train(_ptr(x), _ptr(res), _ptr(g), _ptr(b), _ptr(run_mean), _ptr(run_stat), int(bool(use_log_std)),
+                                 float(decay), float(eps), int(bool(relu)), _ptr(y), _ptr(save), _ptr(save[C:]), _ptr(work), rows, C,
+                                 _stream())
+        _check(rc, "dl4j_bn_fwd_train")
+        global LAUNCHES
+        LAUNCHES += 2
+        ctx.relu, ctx.has_res, ctx.has_affine = bool(relu), res is not None, gamma is not None
+        ctx.save_for_backward(x, y if (res is not None and relu) else None, save, work)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        l = require()
+        x, y, save, work = ctx.saved_tensors
+        rows, C = _rows_c(x)
+        dy = _dense_cl(dy)
+        dx = torch.empty_like(x)
+        dres = torch.empty_like(x) if ctx.has_res else None
+        dgb = torch.zeros(2 * C, dtype=torch.float32, device=x.device) if ctx.has_affine else None
+        rc = l.dl4j_bn_bwd(_ptr(dy), _ptr(x), _ptr(y), _ptr(save), _ptr(save[C:]), _ptr(work), _ptr(dx), _ptr(dres),
+                           _ptr(dgb), _ptr(dgb[C:]) if dgb is not None else None, rows, C, int(ctx.relu), _stream())
+        _check(rc, "dl4j_bn_bwd")
+        global LAUNCHES
+        LAUNCHES += 1
+        dg = dgb[:C] if dgb is not None and ctx.needs_input_grad[2] else None
+        db = dgb[C:] if dgb is not None and ctx.needs_input_grad[3] else None
+        return dx, dres, dg, db, None, None, None, None, None, None
+
+
+def bn_supported(x):
+    if not (available() and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() in (2, 4)):
+        return False
+    rows, C = _rows_c(x)
+    return rows > 0 and 8 <= C <= 2048 and (C & (C - 1)) == 0
+
+
+def bn_act_train(x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu):
+    """Fused training-mode batch norm; ``gamma`` / ``beta`` fp32 [C] (or None), running buffers fp32 [C] updated in place."""
+    shape_g = None if gamma is None else gamma.shape
+    y = _BnActFn.apply(x, res, gamma.reshape(-1) if gamma is not None else None, beta.reshape(-1) if beta is not None else None,
+                       run_mean, run_stat, use_log_std, decay, eps, relu)
+    return y
+
+
+def bn_act_eval(x, res, scale, shift, relu):
+    """y = act(x * scale + shift [+ res]) with fp32 per-channel scale / shift (inference statistics folded in)."""
+    l = require()
+    x = _dense_cl(x)
+    res = _dense_cl(res) if res is not None else None
+    rows, C = _rows_c(x)
+    y = torch.empty_like(x)
+    rc = l.dl4j_bn_apply(_ptr(x), _ptr(res), _ptr(scale.float().contiguous()), _ptr(shift.float().contiguous()), int(bool(relu)), _ptr(y),
+                         rows, C, _stream())
+    _check(rc, "dl4j_bn_apply")
+    return y
+
+
+class _AddReluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b):
+        l = require()
+        a = _dense_cl(a)
+        b = _dense_cl(b)
+        if b.stride() != a.stride():
+            b = b.contiguous(memory_format=torch.channels_last) if a.dim() == 4 else b.contiguous()
+        y = torch.empty_like(a)
+        rc = l.dl4j_add_relu(_ptr(a), _ptr(b), _ptr(y), a.numel(), _stream())
+        _check(rc, "dl4j_add_relu")
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        g = dy * (y > 0).to(dy.dtype)
+        return g, g
+
+
+def add_relu(a, b):
+    if not (available() and a.is_cuda and a.dtype == torch.bfloat16 and a.shape == b.shape and a.numel() % 8 == 0 and a.dim() in (2, 4)):
+        return None
+    return _AddReluFn.apply(a, b)
 
 
 def attention(q, k, v, mask, scale):

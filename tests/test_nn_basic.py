@@ -268,3 +268,37 @@ def test_gradient_and_score_api():
     assert g.gradient().length() == net.numParams()
     assert set(g.gradientForVariable().keys()) == set(net.paramTable().keys())
     assert math.isfinite(net.score()) and net.score() > 0
+
+
+def test_graph_fuses_batchnorm_add_relu_chains_without_changing_results():
+    def build():
+        return (nn.NeuralNetConfiguration.Builder().seed(9).updater(nn.Sgd(0.05)).graphBuilder()
+                .addInputs("in")
+                .addLayer("c1", nn.ConvolutionLayer(kernelSize=(3, 3), padding=(1, 1), nIn=8, nOut=8, activation="identity"), "in")
+                .addLayer("bn1", nn.BatchNormalization(nOut=8), "c1")
+                .addLayer("r1", nn.ActivationLayer("relu"), "bn1")
+                .addLayer("c2", nn.ConvolutionLayer(kernelSize=(1, 1), nIn=8, nOut=8, activation="identity"), "r1")
+                .addLayer("bn2", nn.BatchNormalization(nOut=8), "c2")
+                .addVertex("add", nn.ElementWiseVertex("Add"), "bn2", "in")
+                .addLayer("r2", nn.ActivationLayer("relu"), "add")
+                .addLayer("gp", nn.GlobalPoolingLayer("AVG"), "r2")
+                .addLayer("out", nn.OutputLayer("MCXENT", nIn=8, nOut=3, activation="softmax"), "gp")
+                .setOutputs("out").setInputTypes(nn.InputType.convolutional(6, 6, 8)).build())
+    a, b = nn.ComputationGraph(build()), nn.ComputationGraph(build())
+    a.init()
+    b.init()
+    plan = a._fusion_plan()
+    assert plan["bn1"] == ("bn_relu",) and plan["r1"] == ("alias", "bn1")
+    assert plan["bn2"] == ("defer",) and plan["add"] == ("bn_add_relu", "bn2", "in") and plan["r2"] == ("alias", "add")
+    b._fuse_plan = {}                                  # reference: no fusion
+    rng = np.random.default_rng(1)
+    x = Nd4j.create(rng.normal(size=(4, 8, 6, 6)).astype(np.float32))
+    y = Nd4j.create(np.eye(3, dtype=np.float32)[[0, 1, 2, 1]])
+    from deeplearning4j_b200.data import DataSet as DS
+    for _ in range(3):
+        a.fit(DS(x, y))
+        b.fit(DS(x, y))
+    np.testing.assert_allclose(a.params().numpy(), b.params().numpy(), rtol=1e-5, atol=1e-6)
+    # feedForward still exposes every intermediate activation (fusion is only used on the loss path)
+    acts = a.feedForward([x], False)
+    assert float(acts["bn1"].numpy().min()) < 0 <= float(acts["r1"].numpy().min())
