@@ -83,7 +83,7 @@ bn_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ sums, l
 __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
                                    float* __restrict__ run_mean, float* __restrict__ run_stat, int use_log_std, float decay, float eps,
                                    float inv_rows, float* __restrict__ save_mean, float* __restrict__ save_invstd,
-                                   float* __restrict__ scale, float* __restrict__ shift, int C) {
+                                   float* __restrict__ scale, float* __restrict__ shift, const float* __restrict__ pre_bias, int C) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const float mean = sums[c] * inv_rows;
@@ -94,7 +94,9 @@ __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* 
   save_invstd[c] = invstd;
   scale[c] = g * invstd;
   shift[c] = b - mean * g * invstd;
-  if (run_mean) run_mean[c] = decay * run_mean[c] + (1.f - decay) * mean;
+  // pre_bias: bias of the producing convolution, left out of x because the batch mean cancels it; the running mean
+  // (used at inference, where it does not cancel) still has to see it
+  if (run_mean) run_mean[c] = decay * run_mean[c] + (1.f - decay) * (mean + (pre_bias ? pre_bias[c] : 0.f));
   if (run_stat) {
     const float old_var = use_log_std ? exp10f(2.f * run_stat[c]) : run_stat[c];
     const float nv = decay * old_var + (1.f - decay) * var;
@@ -262,7 +264,7 @@ using namespace dl4j;
 // save_mean / save_invstd are kept by the caller for the backward pass.  run_mean / run_stat may be null.
 DL4J_API int dl4j_bn_fwd_train(const void* x, const void* res, const float* gamma, const float* beta, float* run_mean, float* run_stat,
                                int use_log_std, float decay, float eps, int relu, void* y, float* save_mean, float* save_invstd,
-                               float* work, long long rows, int C, void* stream_) {
+                               float* work, const float* pre_bias, long long rows, int C, void* stream_) {
   if (!bn_shape_ok(rows, C)) return -DL4J_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream_;
   float* sums = work;
@@ -273,7 +275,7 @@ DL4J_API int dl4j_bn_fwd_train(const void* x, const void* res, const float* gamm
   const int g1 = bn_grid_rows(rows, C, &rpb);
   bn_stats_kernel<<<g1, BN_THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), sums, rows, C, rpb);
   bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, 1.0f / (float)rows,
-                                                      save_mean, save_invstd, scale, shift, C);
+                                                      save_mean, save_invstd, scale, shift, pre_bias, C);
   const long long n_vec = rows * (C >> 3);
   bn_apply_kernel<<<bn_grid_elems(n_vec), BN_THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                                                 reinterpret_cast<const __nv_bfloat16*>(res), scale, shift,

@@ -1,0 +1,141 @@
+// Max pooling over channels-last bf16 activations [N, H, W, C] (C % 8 == 0), 8 channels per thread.
+// Forward also records, per output element, which window position (kh * kW + kw, first maximum in scan order like
+// the reference's argmax) won; backward is then a gather: every input element sums the output gradients of the (few)
+// windows that selected it, so no atomics and no 8-byte indices are needed
+// (libnd4j pooling2d / ConvolutionUtils::pooling2dBP semantics for MAX pooling).
+#include "common.cuh"
+
+namespace dl4j {
+
+constexpr int PL_THREADS = 256;
+
+struct PoolShape {
+  int N, H, W, C, OH, OW, kH, kW, sH, sW, pH, pW;
+};
+
+__device__ __forceinline__ void pl_unpack8(const uint4& u, float* o) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ uint4 pl_pack8(const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return u;
+}
+
+__global__ void __launch_bounds__(PL_THREADS)
+maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, unsigned char* __restrict__ idx, const PoolShape s) {
+  const int cv_n = s.C >> 3;
+  const long long total = (long long)s.N * s.OH * s.OW * cv_n;
+  for (long long g = blockIdx.x * (long long)PL_THREADS + threadIdx.x; g < total; g += (long long)gridDim.x * PL_THREADS) {
+    const int cv = (int)(g % cv_n);
+    long long t = g / cv_n;
+    const int ow = (int)(t % s.OW); t /= s.OW;
+    const int oh = (int)(t % s.OH);
+    const int n = (int)(t / s.OH);
+    float best[8];
+    unsigned char bi[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; bi[j] = 0; }
+    const int ih0 = oh * s.sH - s.pH, iw0 = ow * s.sW - s.pW;
+    for (int kh = 0; kh < s.kH; ++kh) {
+      const int ih = ih0 + kh;
+      if (ih < 0 || ih >= s.H) continue;
+      for (int kw = 0; kw < s.kW; ++kw) {
+        const int iw = iw0 + kw;
+        if (iw < 0 || iw >= s.W) continue;
+        float v[8];
+        pl_unpack8(__ldg(reinterpret_cast<const uint4*>(x + (((long long)n * s.H + ih) * s.W + iw) * s.C) + cv), v);
+        const unsigned char pos = (unsigned char)(kh * s.kW + kw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (v[j] > best[j]) { best[j] = v[j]; bi[j] = pos; }
+      }
+    }
+    reinterpret_cast<uint4*>(y)[g] = pl_pack8(best);
+    if (idx) {
+      uint2 p;
+      p.x = bi[0] | (bi[1] << 8) | (bi[2] << 16) | ((unsigned)bi[3] << 24);
+      p.y = bi[4] | (bi[5] << 8) | (bi[6] << 16) | ((unsigned)bi[7] << 24);
+      reinterpret_cast<uint2*>(idx)[g] = p;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(PL_THREADS)
+maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const unsigned char* __restrict__ idx, __nv_bfloat16* __restrict__ dx, const PoolShape s) {
+  const int cv_n = s.C >> 3;
+  const long long total = (long long)s.N * s.H * s.W * cv_n;
+  for (long long g = blockIdx.x * (long long)PL_THREADS + threadIdx.x; g < total; g += (long long)gridDim.x * PL_THREADS) {
+    const int cv = (int)(g % cv_n);
+    long long t = g / cv_n;
+    const int iw = (int)(t % s.W); t /= s.W;
+    const int ih = (int)(t % s.H);
+    const int n = (int)(t / s.H);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    // windows (oh, ow) that contain (ih, iw): oh * sH - pH <= ih < oh * sH - pH + kH
+    const int hp = ih + s.pH, wp = iw + s.pW;
+    const int oh_hi = min(hp / s.sH, s.OH - 1);
+    const int oh_lo = max(hp - s.kH + s.sH, 0) / s.sH;        // ceil((hp - kH + 1) / sH) clamped at 0
+    const int ow_hi = min(wp / s.sW, s.OW - 1);
+    const int ow_lo = max(wp - s.kW + s.sW, 0) / s.sW;
+    for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+      const int kh = hp - oh * s.sH;
+      for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+        const int kw = wp - ow * s.sW;
+        const unsigned pos = (unsigned)(kh * s.kW + kw);
+        const long long o = (((long long)n * s.OH + oh) * s.OW + ow) * cv_n + cv;
+        const uint2 p = __ldg(reinterpret_cast<const uint2*>(idx) + o);
+        float d[8];
+        pl_unpack8(__ldg(reinterpret_cast<const uint4*>(dy) + o), d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (((p.x >> (8 * j)) & 0xffu) == pos) acc[j] += d[j];
+          if (((p.y >> (8 * j)) & 0xffu) == pos) acc[4 + j] += d[4 + j];
+        }
+      }
+    }
+    reinterpret_cast<uint4*>(dx)[g] = pl_pack8(acc);
+  }
+}
+
+static inline int pl_grid(long long total) {
+  long long b = (total + PL_THREADS - 1) / PL_THREADS;
+  if (b > 148 * 16) b = 148 * 16;
+  return (int)(b < 1 ? 1 : b);
+}
+
+static inline bool pl_ok(const PoolShape& s) {
+  return s.N > 0 && s.H > 0 && s.W > 0 && s.C >= 8 && s.C % 8 == 0 && s.OH > 0 && s.OW > 0 && s.kH > 0 && s.kW > 0 && s.kH * s.kW <= 255 &&
+         s.sH > 0 && s.sW > 0 && s.pH >= 0 && s.pW >= 0 && s.pH < s.kH && s.pW < s.kW;
+}
+
+}  // namespace dl4j
+
+using namespace dl4j;
+
+// shape: 12 ints {N, H, W, C, OH, OW, kH, kW, sH, sW, pH, pW}; idx (N*OH*OW*C bytes) may be null for inference
+DL4J_API int dl4j_maxpool_fwd(const void* x, void* y, void* idx, const int* shape, void* stream) {
+  PoolShape s;
+  memcpy(&s, shape, sizeof(s));
+  if (!pl_ok(s)) return -DL4J_ERR_BAD_ARG;
+  const long long total = (long long)s.N * s.OH * s.OW * (s.C >> 3);
+  maxpool_fwd_kernel<<<pl_grid(total), PL_THREADS, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(y), reinterpret_cast<unsigned char*>(idx), s);
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_maxpool_bwd(const void* dy, const void* idx, void* dx, const int* shape, void* stream) {
+  PoolShape s;
+  memcpy(&s, shape, sizeof(s));
+  if (!pl_ok(s) || !idx) return -DL4J_ERR_BAD_ARG;
+  const long long total = (long long)s.N * s.H * s.W * (s.C >> 3);
+  maxpool_bwd_kernel<<<pl_grid(total), PL_THREADS, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const unsigned char*>(idx), reinterpret_cast<__nv_bfloat16*>(dx), s);
+  return (int)cudaGetLastError();
+}

@@ -170,12 +170,33 @@ class ComputationGraph(BaseNetwork):
                         plan[n] = ("defer",)
                         plan[c] = ("bn_add_relu", n, other[0])
                         plan[cc[0]] = ("alias", c)
+        # convolution bias -> following batch norm: batch statistics cancel the bias in training, so the convolution runs
+        # without it and the batch norm accounts for it in its running mean / inference shift
+        from .activations import ActivationIdentity
+        from .layers.conv import ConvolutionLayer
+        bias_of = {}
+        for n in self.order:
+            v = conf.vertices.get(n)
+            if not (isinstance(v, LayerVertex) and type(v.layer) is ConvolutionLayer and v.layer.hasBias and n not in outs
+                    and isinstance(v.layer.activation, ActivationIdentity) and getattr(v.layer, "weightNoise", None) is None
+                    and getattr(v.layer, "dropOut", None) is None):
+                continue
+            cs = consumers.get(n, [])
+            if len(cs) == 1 and plain_layer(cs[0], BatchNormalization):
+                plan[n] = ("conv_nobias",)
+                bias_of[cs[0]] = n
+        self._fuse_bias = bias_of
         self._fuse_plan = plan
         return plan
 
     def _forward(self, inputs: dict, training, fmasks=None, ctx=None, stop_at_preout=False):
         ctx = ctx if ctx is not None else {}
         fuse = self._fusion_plan() if ctx.get("fuse") else {}
+        bias_of = self._fuse_bias if fuse else {}
+
+        def pre_bias(bn_name):
+            c = bias_of.get(bn_name)
+            return None if c is None else self.param_views[c]["b"]
         acts = dict(inputs)
         masks = dict(fmasks or {})
         first = next(iter(inputs.values()))
@@ -189,15 +210,21 @@ class ComputationGraph(BaseNetwork):
             ins = [acts[i] for i in conf.vertexInputs[n]]
             in_masks = [masks.get(i) for i in conf.vertexInputs[n]]
             act = fuse.get(n)
+            extra = {}
+            if act is not None and act[0] == "conv_nobias":
+                act, extra = None, {"skip_bias": True}
+            elif act is None and n in bias_of:
+                extra = {"pre_bias": pre_bias(n)}
             if act is not None:
                 if act[0] == "bn_relu":
-                    y = v.layer.forward(self.param_views.get(n, {}), ins[0], training, in_masks[0], None, fuse_relu=True)
+                    y = v.layer.forward(self.param_views.get(n, {}), ins[0], training, in_masks[0], None, fuse_relu=True,
+                                        pre_bias=pre_bias(n))
                 elif act[0] == "defer":
                     y = ins[0]                      # normalised later, at the add vertex that consumes it
                 elif act[0] == "bn_add_relu":
                     bn = conf.vertices[act[1]]
                     y = bn.layer.forward(self.param_views.get(act[1], {}), acts[act[1]], training, masks.get(act[1]), None,
-                                         fuse_relu=True, residual=acts[act[2]])
+                                         fuse_relu=True, residual=acts[act[2]], pre_bias=pre_bias(act[1]))
                 else:                               # alias: the ReLU already happened upstream
                     y = acts[act[1]]
                 masks[n] = in_masks[0]
@@ -210,7 +237,7 @@ class ComputationGraph(BaseNetwork):
                     m = v.preProcessor.feed_forward_mask(m, ctx["minibatch"])
                 lctx = {"minibatch": ctx["minibatch"], "rnn_state_in": ctx.get("rnn_state_in", {}),
                         "rnn_state_out": ctx.setdefault("rnn_state_out", {})}
-                y = v.layer.forward(self.param_views.get(n, {}), x, training, m, lctx)
+                y = v.layer.forward(self.param_views.get(n, {}), x, training, m, lctx, **extra)
                 if "preout" in lctx:
                     preouts[n] = lctx["preout"]
                     for k in ("center_in", "centers"):

@@ -115,15 +115,30 @@ class ConvolutionLayer(FeedForwardLayer):
         s.append(ParamSpec("W", (self.nOut, self.nIn, k[0], k[1]), "c", "weight", fan_in, fan_out))
         return s
 
-    def forward(self, p, x, training, mask=None, ctx=None):
+    def forward(self, p, x, training, mask=None, ctx=None, skip_bias=False):
+        """``skip_bias``: the graph executor hands the bias to the batch norm that follows (see its ``pre_bias``)."""
         x = self.apply_dropout(x, training)
         p = self.noisy(p, training)
         nhwc = self.cnn2dDataFormat == CNN2DFormat.NHWC
         if nhwc:
             x = x.permute(0, 3, 1, 2)
+        if tuple(self.kernelSize) == (1, 1) and tuple(self.padding) == (0, 0) and x.is_cuda and type(self) is ConvolutionLayer:
+            # pointwise convolution = GEMM over the channels-last activation: runs on the tcgen05 kernel
+            from ...ops import native as nat
+            from ...ops import nnops
+            if not nnops._FORCE_TORCH:
+                z = nat.conv1x1(x, p["W"], p["b"] if self.hasBias and not skip_bias else None, tuple(self.stride))
+                if z is not None:
+                    z = self.activation(z, training)
+                    return z.permute(0, 2, 3, 1) if nhwc else z
         W = p["W"].to(x.dtype) if p["W"].dtype != x.dtype else p["W"]
-        b = p["b"].reshape(-1).to(x.dtype) if self.hasBias else None
+        b = p["b"].reshape(-1).to(x.dtype) if self.hasBias and not skip_bias else None
         x, pad = _pad_for_mode(x, self.kernelSize, self.stride, self.padding, self.dilation, self._mode())
+        if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.shape[1] < 8 and x.dim() == 4:
+            # an RGB stem has too few input channels for the tensor-core convolution kernels: zero-pad them to 8
+            extra = 8 - x.shape[1]
+            x = F.pad(x, (0, 0, 0, 0, 0, extra)).contiguous(memory_format=torch.channels_last)
+            W = F.pad(W, (0, 0, 0, 0, 0, extra))
         z = nnops_conv2d(x, W, b, self.stride, pad, self.dilation)
         z = self.activation(z, training)
         return z.permute(0, 2, 3, 1) if nhwc else z
@@ -382,6 +397,12 @@ class SubsamplingLayer(NoParamLayer):
         fns = {1: (F.max_pool1d, F.avg_pool1d, F.lp_pool1d), 2: (F.max_pool2d, F.avg_pool2d, F.lp_pool2d),
                3: (F.max_pool3d, F.avg_pool3d, getattr(F, "lp_pool3d", None))}[self.ND]
         if self.poolingType == PoolingType.MAX:
+            if self.ND == 2 and x.is_cuda and d == (1, 1):
+                from ...ops import native as nat
+                from ...ops import nnops
+                z = None if nnops._FORCE_TORCH else nat.maxpool2d(x, k, s, tuple(pad))
+                if z is not None:
+                    return z
             return fns[0](x, k, s, tuple(pad), d)
         if self.poolingType == PoolingType.AVG:
             return fns[1](x, k, s, tuple(pad), count_include_pad=self.avgPoolIncludePadInDivisor)
@@ -748,9 +769,12 @@ class BatchNormalization(FeedForwardLayer):
     def regularizers(self, spec):
         return []   # the reference never regularises batch-norm parameters
 
-    def forward(self, p, x, training, mask=None, ctx=None, fuse_relu=False, residual=None):
+    def forward(self, p, x, training, mask=None, ctx=None, fuse_relu=False, residual=None, pre_bias=None):
         """``fuse_relu`` / ``residual`` are set by the graph executor when this layer is followed by a ReLU (optionally
-        after an element-wise add): the result is then ``relu(bn(x) [+ residual])`` from one fused kernel chain."""
+        after an element-wise add): the result is then ``relu(bn(x) [+ residual])`` from one fused kernel chain.
+        ``pre_bias`` is the bias of the convolution that produced ``x`` when the executor left it out of ``x``: batch
+        statistics cancel it in training (its gradient is exactly zero), so it only enters the running mean and the
+        inference-time shift."""
         n = self.nOut or self.nIn
         nhwc = x.dim() == 4 and self.cnn2DFormat == CNN2DFormat.NHWC
         if nhwc:
@@ -772,14 +796,19 @@ class BatchNormalization(FeedForwardLayer):
         if not nnops._FORCE_TORCH and x.dim() in (2, 4) and mean.dtype == torch.float32 and nat.bn_supported(x):
             # hand-written channels-last kernels: statistics, running-stat update, normalise (+ add) (+ ReLU)
             if training:
-                y = nat.bn_act_train(x, residual, g, b, mean.detach(), sv.detach(), self.useLogStd, self.decay, self.eps, fuse_relu)
+                y = nat.bn_act_train(x, residual, g, b, mean.detach(), sv.detach(), self.useLogStd, self.decay, self.eps, fuse_relu,
+                                     pre_bias)
             else:
                 with torch.no_grad():
                     var = torch.pow(10.0, 2.0 * sv) if self.useLogStd else sv
                     scale = g.float() * torch.rsqrt(var + self.eps)
                     shift = b.float() - mean * scale
+                    if pre_bias is not None:
+                        shift = shift + pre_bias.reshape(-1).float() * scale
                 y = nat.bn_act_eval(x, residual, scale, shift, fuse_relu)
             return y.permute(0, 2, 3, 1) if nhwc else y
+        if pre_bias is not None:
+            x = x + pre_bias.reshape(1, -1, *([1] * (x.dim() - 2))).to(x.dtype)
         var = torch.pow(10.0, 2.0 * sv.detach()) if self.useLogStd else sv.detach()
         if training:
             # batch statistics; running stats use DL4J's decay: global = decay*global + (1-decay)*batch

@@ -59,10 +59,12 @@ def _load():
             "dl4j_lstm_seq_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_lstm_seq_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
-            "dl4j_bn_fwd_train": [vp, vp, vp, vp, vp, vp, i32, f32, f32, i32, vp, vp, vp, vp, i64, i32, vp],
+            "dl4j_bn_fwd_train": [vp, vp, vp, vp, vp, vp, i32, f32, f32, i32, vp, vp, vp, vp, vp, i64, i32, vp],
             "dl4j_bn_apply": [vp, vp, vp, vp, i32, vp, i64, i32, vp],
             "dl4j_bn_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, vp],
             "dl4j_add_relu": [vp, vp, vp, i64, vp],
+            "dl4j_maxpool_fwd": [vp, vp, vp, vp, vp],
+            "dl4j_maxpool_bwd": [vp, vp, vp, vp, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
             "dl4j_bind_device": [i32],
@@ -327,6 +329,8 @@ class _LinearFn(torch.autograd.Function):
             tiles = ((N + 127) // 128) * ((nIn + 255) // 256)
             splits = _wgrad_splits(tiles, M)
             g = W.grad if (W.is_leaf and W.grad is not None) else None
+            if g is not None and g.dim() == 4 and g.shape[2] == 1 and g.shape[3] == 1 and g.is_contiguous():
+                g = g.view(g.shape[0], g.shape[1]).t()      # 1x1 convolution kernel [nOut, nIn, 1, 1]: same memory as an 'f' dense weight
             if g is not None and g.dtype == torch.float32 and g.dim() == 2 and g.stride(0) == 1 and g.stride(1) == nIn \
                     and g.data_ptr() % 16 == 0 and nIn % 4 == 0:
                 gemm_raw(dz.t(), x, out=g.t(), atomic=True, splits=splits)
@@ -337,7 +341,7 @@ class _LinearFn(torch.autograd.Function):
                 gemm_raw(x.t(), dz, out=g, atomic=True, splits=_wgrad_splits(tiles2, M))
             else:
                 dWt = gemm_raw(dz.t(), x, out_dtype=torch.float32, atomic=True, splits=splits)
-                dW = dWt.t().to(W.dtype)
+                dW = dWt.reshape(W.shape).to(W.dtype) if W.dim() == 4 else dWt.t().to(W.dtype)
         return dx, dW, db, None, None
 
 
@@ -611,6 +615,74 @@ def lstm_seq(zx, rw, h0, c0, reverse=False):
     return _LstmSeqFn.apply(zx, rw, h0, c0, reverse, rw_lp)
 
 
+def conv1x1(x, W, b, stride=(1, 1)):
+    """1x1 convolution over a channels-last activation as one tcgen05 GEMM: [N*H*W, Cin] x [Cin, Cout] (forward, data
+    gradient and weight gradient all run on the hand-written kernel).  ``W`` is the [Cout, Cin, 1, 1] parameter; returns
+    None when the case is not covered."""
+    if not available() or not x.is_cuda or x.dim() != 4 or x.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    Cout, Cin = W.shape[0], W.shape[1]
+    if W.dim() != 4 or W.shape[2] != 1 or W.shape[3] != 1 or Cin % 8 or Cout % 8 or x.shape[1] != Cin:
+        return None
+    W_lp = getattr(W, "_lp", None)
+    if W_lp is None or W_lp.dtype != x.dtype:
+        W_lp = W.detach() if W.dtype == x.dtype else W.detach().to(x.dtype)
+    if not W_lp.is_contiguous() or W_lp.data_ptr() % 16:
+        return None
+    if stride[0] != 1 or stride[1] != 1:
+        x = x[:, :, ::stride[0], ::stride[1]]
+    x = _dense_cl(x)
+    N, _, H, Wd = x.shape
+    x2 = x.permute(0, 2, 3, 1).reshape(N * H * Wd, Cin)
+    if _operand_a(x2) is None:
+        return None
+    y2 = _LinearFn.apply(x2, W, b, 0, W_lp.view(Cout, Cin).t())
+    return y2.view(N, H, Wd, Cout).permute(0, 3, 1, 2)
+
+
+class _MaxPoolFn(torch.autograd.Function):
+    """Channels-last max pooling; forward keeps one byte per output element (winning window position), backward gathers."""
+
+    @staticmethod
+    def forward(ctx, x, k, s, p):
+        l = require()
+        x = _dense_cl(x)
+        N, C, H, W = x.shape
+        OH = (H + 2 * p[0] - k[0]) // s[0] + 1
+        OW = (W + 2 * p[1] - k[1]) // s[1] + 1
+        y = torch.empty((N, C, OH, OW), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        need = ctx.needs_input_grad[0]
+        idx = torch.empty(N * OH * OW * C, dtype=torch.uint8, device=x.device) if need else None
+        shape = (ctypes.c_int * 12)(N, H, W, C, OH, OW, k[0], k[1], s[0], s[1], p[0], p[1])
+        rc = l.dl4j_maxpool_fwd(_ptr(x), _ptr(y), _ptr(idx), shape, _stream())
+        _check(rc, "dl4j_maxpool_fwd")
+        ctx.shape = (N, H, W, C, OH, OW, k[0], k[1], s[0], s[1], p[0], p[1])
+        ctx.save_for_backward(idx)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        l = require()
+        (idx,) = ctx.saved_tensors
+        N, H, W, C = ctx.shape[:4]
+        dy = _dense_cl(dy)
+        dx = torch.empty((N, C, H, W), dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+        shape = (ctypes.c_int * 12)(*ctx.shape)
+        rc = l.dl4j_maxpool_bwd(_ptr(dy), _ptr(idx), _ptr(dx), shape, _stream())
+        _check(rc, "dl4j_maxpool_bwd")
+        return dx, None, None, None
+
+
+def maxpool2d(x, k, s, p):
+    if not (available() and x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0):
+        return None
+    if k[0] * k[1] > 255 or p[0] >= k[0] or p[1] >= k[1] or min(x.shape) == 0:
+        return None
+    if (x.shape[2] + 2 * p[0] - k[0]) < 0 or (x.shape[3] + 2 * p[1] - k[1]) < 0:
+        return None
+    return _MaxPoolFn.apply(x, tuple(int(v) for v in k), tuple(int(v) for v in s), tuple(int(v) for v in p))
+
+
 # =========================================================================== batch norm (+ residual) (+ ReLU)
 def _rows_c(x):
     """(rows, C) of a channels-last 4-D or a plain 2-D activation."""
@@ -631,7 +703,7 @@ class _BnActFn(torch.autograd.Function):
     the kernel (``nn/layers/normalization/BatchNormalization.java`` semantics: biased batch variance, decay rule)."""
 
     @staticmethod
-    def forward(ctx, x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu):
+    def forward(ctx, x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu, pre_bias=None):
         l = require()
         x = _dense_cl(x)
         res = _dense_cl(res) if res is not None else None
@@ -642,8 +714,8 @@ class _BnActFn(torch.autograd.Function):
         g = gamma.detach().float().contiguous() if gamma is not None else None
         b = beta.detach().float().contiguous() if beta is not None else None
         rc = l.dl4j_bn_fwd_train(_ptr(x), _ptr(res), _ptr(g), _ptr(b), _ptr(run_mean), _ptr(run_stat), int(bool(use_log_std)),
-                                 float(decay), float(eps), int(bool(relu)), _ptr(y), _ptr(save), _ptr(save[C:]), _ptr(work), rows, C,
-                                 _stream())
+                                 float(decay), float(eps), int(bool(relu)), _ptr(y), _ptr(save), _ptr(save[C:]), _ptr(work),
+                                 _ptr(pre_bias), rows, C, _stream())
         _check(rc, "dl4j_bn_fwd_train")
         global LAUNCHES
         LAUNCHES += 2
@@ -667,7 +739,7 @@ class _BnActFn(torch.autograd.Function):
         LAUNCHES += 1
         dg = dgb[:C] if dgb is not None and ctx.needs_input_grad[2] else None
         db = dgb[C:] if dgb is not None and ctx.needs_input_grad[3] else None
-        return dx, dres, dg, db, None, None, None, None, None, None
+        return dx, dres, dg, db, None, None, None, None, None, None, None
 
 
 def bn_supported(x):
@@ -677,12 +749,12 @@ def bn_supported(x):
     return rows > 0 and 8 <= C <= 2048 and (C & (C - 1)) == 0
 
 
-def bn_act_train(x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu):
-    """Fused training-mode batch norm; ``gamma`` / ``beta`` fp32 [C] (or None), running buffers fp32 [C] updated in place."""
-    shape_g = None if gamma is None else gamma.shape
-    y = _BnActFn.apply(x, res, gamma.reshape(-1) if gamma is not None else None, beta.reshape(-1) if beta is not None else None,
-                       run_mean, run_stat, use_log_std, decay, eps, relu)
-    return y
+def bn_act_train(x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu, pre_bias=None):
+    """Fused training-mode batch norm; ``gamma`` / ``beta`` fp32 [C] (or None), running buffers fp32 [C] updated in place.
+    ``pre_bias`` (fp32 [C]) is a bias that the producer left out of ``x``: it only enters the running mean."""
+    pb = pre_bias.detach().float().reshape(-1).contiguous() if pre_bias is not None else None
+    return _BnActFn.apply(x, res, gamma.reshape(-1) if gamma is not None else None, beta.reshape(-1) if beta is not None else None,
+                          run_mean, run_stat, use_log_std, decay, eps, relu, pb)
 
 
 def bn_act_eval(x, res, scale, shift, relu):

@@ -1,0 +1,79 @@
+"""Pointwise convolution on the tcgen05 GEMM and channels-last max pooling against PyTorch references."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from deeplearning4j_b200.ops import native
+    native.require()
+    assert native.available(), native.load_error()
+    yield native
+    native.check_status()
+
+
+def _rel(a, b):
+    return float((a.detach().float() - b.detach().float()).abs().max() / (b.detach().float().abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("shape,cout,stride", [((4, 64, 14, 14), 256, (1, 1)), ((2, 256, 9, 7), 64, (1, 1)), ((3, 128, 14, 14), 512, (2, 2))])
+@pytest.mark.parametrize("bias", [False, True])
+def test_conv1x1_matches_conv2d(nat, shape, cout, stride, bias):
+    g = torch.Generator(device="cuda").manual_seed(sum(shape) + cout)
+    x = torch.randn(shape, device="cuda", generator=g).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    W = (torch.randn(cout, shape[1], 1, 1, device="cuda", generator=g) / shape[1] ** 0.5).requires_grad_(True)     # fp32 master
+    W.grad = torch.zeros_like(W)
+    b = torch.randn(1, cout, device="cuda", generator=g).requires_grad_(True) if bias else None
+    y = nat.conv1x1(x, W, b, stride)
+    assert y is not None and y.is_contiguous(memory_format=torch.channels_last)
+    w = torch.randn(y.shape, device="cuda", generator=g)
+    (y.float() * w).sum().backward()
+    torch.cuda.synchronize()
+    nat.check_status()
+    got = [x.grad.clone(), W.grad.clone()] + ([b.grad.clone()] if bias else [])
+    x.grad = None
+    W.grad = None
+    if bias:
+        b.grad = None
+    ref = F.conv2d(x.float(), W.bfloat16().float(), b.reshape(-1) if bias else None, stride=stride)
+    assert _rel(y, ref) < 2e-2
+    (ref * w).sum().backward()
+    want = [x.grad, W.grad] + ([b.grad] if bias else [])
+    for name, a, r in zip(("dx", "dW", "db"), got, want):
+        assert _rel(a, r) < 3e-2, (name, _rel(a, r))
+
+
+@pytest.mark.parametrize("shape,k,s,p", [((2, 64, 16, 16), (3, 3), (2, 2), (0, 0)), ((3, 8, 11, 9), (3, 3), (2, 2), (1, 1)),
+                                         ((2, 32, 8, 8), (2, 2), (2, 2), (0, 0)), ((1, 16, 7, 7), (3, 2), (1, 2), (1, 0))])
+def test_maxpool_channels_last(nat, shape, k, s, p):
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    # quantised values make ties frequent: the first maximum in scan order must receive the gradient
+    x = (torch.randint(-3, 4, shape, device="cuda", generator=g).float() / 2).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    y = nat.maxpool2d(x, k, s, p)
+    assert y is not None
+    w = torch.randn(y.shape, device="cuda", generator=g).bfloat16().float()
+    (y.float() * w).sum().backward()
+    got = x.grad.clone()
+    x.grad = None
+    xr = x.detach().float().contiguous().requires_grad_(True)
+    ref = F.max_pool2d(xr, k, s, p)
+    assert torch.equal(y.float(), ref)
+    (ref * w).sum().backward()
+    assert _rel(got, xr.grad) < 1e-2
+
+
+def test_rgb_stem_convolution_pads_channels(nat):
+    from deeplearning4j_b200 import nn
+    layer = nn.ConvolutionLayer(kernelSize=(7, 7), stride=(2, 2), padding=(3, 3), nIn=3, nOut=16, activation="identity")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(2, 3, 32, 32, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    W = (torch.randn(16, 3, 7, 7, device="cuda", generator=g) * 0.1).requires_grad_(True)
+    b = torch.zeros(1, 16, device="cuda").requires_grad_(True)
+    y = layer.forward({"W": W, "b": b}, x, True)
+    ref = F.conv2d(x.float(), W.bfloat16().float(), None, stride=2, padding=3)
+    assert _rel(y, ref) < 2e-2
+    y.float().sum().backward()
+    assert W.grad is not None and W.grad.shape == W.shape and x.grad.shape == x.shape
