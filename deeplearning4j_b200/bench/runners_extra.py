@@ -20,15 +20,41 @@ class _NetRunner(BaseRunner):
                 impl = "nccl"
             attach_gradient_sharing(net, self.sharing_mode, impl, FixedThresholdAlgorithm(1e-3))
 
+    def _graphs(self, net):
+        """Launch-bound networks replay their forward + backward pass from a CUDA graph (off for the library baseline)."""
+        import os
+        if not self.args.library_baseline and os.environ.get("DL4J_CUDA_GRAPHS", "1") != "0":
+            net.setCudaGraphs(True)
+
     def device_step(self):
         x, y = self.dev[self.i % len(self.dev)]
         self.i += 1
         self.net.fit(x, y)
 
+    def _issue(self, i):
+        """Start the host -> device copy of batch ``i`` on the copy stream (pinned source, so it overlaps compute)."""
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream()
+        x, y = self.host[i % len(self.host)]
+        with torch.cuda.stream(self._copy_stream):
+            xd, yd = x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._copy_stream)
+        return xd, yd, ev
+
     def e2e_step(self):
-        x, y = self.host[self.i % len(self.host)]
+        # double-buffered input pipeline, as the framework's AsyncDataSetIterator does: the copy of the next batch is in
+        # flight while this batch trains; every step still moves one full batch host -> device and reads the loss back
+        if getattr(self, "_pf", None) is None:
+            self._pf = self._issue(self.i)
+        x, y, ev = self._pf
         self.i += 1
-        self.net.fit(x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True))
+        self._pf = self._issue(self.i)
+        cur = torch.cuda.current_stream()
+        cur.wait_event(ev)
+        x.record_stream(cur)
+        y.record_stream(cur)
+        self.net.fit(x, y)
         self.last = self.net.score()          # device -> host read of the loss
 
     def h2d_bytes(self):
@@ -54,6 +80,7 @@ class ResNet50Runner(_NetRunner):
             self.dev.append((x.to(self.device).to(memory_format=torch.channels_last), y.to(self.device)))
         self.i = 0
         self._attach(net)
+        self._graphs(net)
 
     def work_per_step(self):
         return self.batch
@@ -113,6 +140,7 @@ class MlpRunner(_NetRunner):
         y = torch.nn.functional.one_hot(torch.randint(0, 10, (self.batch,), generator=g), 10).float().pin_memory()
         self.host, self.dev, self.i = [(x, y)], [(x.to(self.device), y.to(self.device))], 0
         self._attach(self.net)
+        self._graphs(self.net)
 
     def work_per_step(self):
         return self.batch

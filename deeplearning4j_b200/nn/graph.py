@@ -355,9 +355,13 @@ class ComputationGraph(BaseNetwork):
             self._train_step(ins, labs, fm, lm)
 
     def _train_step(self, ins, labs, fm=None, lm=None, ctx=None):
-        loss = self._loss(ins, labs, fm, lm, True, ctx)
-        loss.backward()
-        self._score = loss.detach()
+        names = list(ins.keys())
+        n_in = len(names)
+
+        def loss_fn(ts):
+            return self._loss(dict(zip(names, ts[:n_in])), list(ts[n_in:]), fm, lm, True, ctx)
+        plain = fm is None and (lm is None or all(m is None for m in lm)) and not ctx
+        self._score = self._loss_backward([ins[n] for n in names] + list(labs), loss_fn, eager_ok=plain)
         self._last_batch = next(iter(ins.values())).shape[0]
         if self.listeners:
             self._fire("onGradientCalculation")

@@ -238,9 +238,8 @@ class MultiLayerNetwork(BaseNetwork):
             self._train_step(x, y, fm, lm)
 
     def _train_step(self, x, y, fm=None, lm=None, ctx=None):
-        loss = self._loss(x, y, fm, lm, True, ctx)
-        loss.backward()
-        self._score = loss.detach()
+        self._score = self._loss_backward([x, y], lambda ts: self._loss(ts[0], ts[1], fm, lm, True, ctx),
+                                          eager_ok=fm is None and lm is None and not ctx)
         self._last_batch = x.shape[0]
         if self.listeners:
             self._fire("onGradientCalculation")

@@ -280,6 +280,49 @@ class BaseNetwork:
     def getLastEtlTime(self): return self._last_etl_ms
     def setLastEtlTime(self, ms): self._last_etl_ms = ms
 
+    # ------------------------------------------------------------------ CUDA-graph capture of forward + backward
+    def setCudaGraphs(self, enabled=True, warmup=1):
+        """Capture the loss + backward pass of a training step into a CUDA graph (one per input signature) and replay it
+        on later steps, which removes the per-kernel launch cost of launch-bound networks.  The first ``warmup`` steps
+        of a signature run eagerly; the updater / gradient-sharing step stays outside the graph so schedules and
+        iteration-dependent hyper-parameters keep working.  Steps with masks or carried recurrent state run eagerly."""
+        self._cg = {"on": bool(enabled), "warmup": int(warmup), "entries": {}}
+        return self
+
+    def _loss_backward(self, tensors, loss_fn, eager_ok=True):
+        """Runs ``loss = loss_fn(tensors); loss.backward()`` either eagerly or through a captured CUDA graph.
+        ``tensors`` is a flat list of input / label tensors; returns the detached loss."""
+        cg = getattr(self, "_cg", None)
+        if not (cg and cg["on"] and eager_ok and self.flat_params.is_cuda):
+            loss = loss_fn(tensors)
+            loss.backward()
+            return loss.detach()
+        from ..ops import native
+        key = tuple((tuple(t.shape), t.dtype, tuple(t.stride())) for t in tensors)
+        e = cg["entries"].setdefault(key, {"seen": 0, "graph": None})
+        if e["graph"] is None:
+            e["seen"] += 1
+            if e["seen"] <= cg["warmup"]:
+                loss = loss_fn(tensors)
+                loss.backward()
+                return loss.detach()
+            e["static"] = [t.clone() for t in tensors]
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = native.LAUNCHES
+            with torch.cuda.graph(g):
+                loss = loss_fn(e["static"])
+                loss.backward()
+            e["launches"] = native.LAUNCHES - n0
+            native.LAUNCHES = n0                    # capture launched nothing
+            e["loss"] = loss.detach()
+            e["graph"] = g
+        for dst, src in zip(e["static"], tensors):
+            dst.copy_(src, non_blocking=True)
+        e["graph"].replay()
+        native.LAUNCHES += e["launches"]
+        return e["loss"]
+
     # ------------------------------------------------------------------ step skeleton
     def _apply_update(self):
         """updater -> step (-> constraints), between backward and ``iterationDone``."""
