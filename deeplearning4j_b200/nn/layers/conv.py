@@ -135,6 +135,10 @@ class ConvolutionLayer(FeedForwardLayer):
         b = p["b"].reshape(-1).to(x.dtype) if self.hasBias and not skip_bias else None
         x, pad = _pad_for_mode(x, self.kernelSize, self.stride, self.padding, self.dilation, self._mode())
         if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.shape[1] < 8 and x.dim() == 4:
+            if tuple(self.stride) == (2, 2) and tuple(self.dilation) == (1, 1) and x.shape[1] <= 4:
+                z = _stem_space_to_depth(x, W, b, tuple(self.kernelSize), tuple(pad))
+                z = self.activation(z, training)
+                return z.permute(0, 2, 3, 1) if nhwc else z
             # an RGB stem has too few input channels for the tensor-core convolution kernels: zero-pad them to 8
             extra = 8 - x.shape[1]
             x = F.pad(x, (0, 0, 0, 0, 0, extra)).contiguous(memory_format=torch.channels_last)
@@ -145,6 +149,29 @@ class ConvolutionLayer(FeedForwardLayer):
 
 
 Convolution2D = ConvolutionLayer
+
+
+def _stem_space_to_depth(x, W, b, k, pad):
+    """Stride-2 convolution over a few input channels (an RGB stem) rewritten as a stride-1 convolution over a 2x2
+    space-to-depth view: ``y[oh] = sum_kh W[kh] x[2 oh + kh]`` with ``kh = 2 a + bh`` becomes
+    ``sum_a sum_bh W'[bh][a] x'[bh][oh + a]``.  The rewritten problem has 4x the channels (padded to 16) and half the
+    taps per axis, which the tensor-core convolution kernels handle well; the 3-channel original does not."""
+    N, C, H, Wd = x.shape
+    kH, kW = k
+    OH, OW = (H + 2 * pad[0] - kH) // 2 + 1, (Wd + 2 * pad[1] - kW) // 2 + 1
+    KH2, KW2 = (kH + 1) // 2, (kW + 1) // 2
+    Hs, Ws = OH + KH2 - 1, OW + KW2 - 1                    # space-to-depth extent the stride-1 convolution needs
+    eh, ew = 2 * Hs - (H + 2 * pad[0]), 2 * Ws - (Wd + 2 * pad[1])
+    xp = F.pad(x, (pad[1], pad[1] + max(ew, 0), pad[0], pad[0] + max(eh, 0)))[:, :, :2 * Hs, :2 * Ws]
+    xs = xp.reshape(N, C, Hs, 2, Ws, 2).permute(0, 3, 5, 1, 2, 4).reshape(N, 4 * C, Hs, Ws)
+    W8 = F.pad(W, (0, 2 * KW2 - kW, 0, 2 * KH2 - kH))
+    Wsd = W8.reshape(W.shape[0], C, KH2, 2, KW2, 2).permute(0, 3, 5, 1, 2, 4).reshape(W.shape[0], 4 * C, KH2, KW2)
+    cpad = (-4 * C) % 8
+    if cpad:
+        xs = F.pad(xs, (0, 0, 0, 0, 0, cpad))
+        Wsd = F.pad(Wsd, (0, 0, 0, 0, 0, cpad))
+    xs = xs.contiguous(memory_format=torch.channels_last)
+    return F.conv2d(xs, Wsd, b)
 
 
 def nnops_conv2d(x, W, b, stride, pad, dilation, groups=1):

@@ -151,3 +151,17 @@ def test_samediff_defined_layers_match_dense_and_train():
     for _ in range(30):
         net.fit(x, y)
     assert net.score(DataSet(x, y)) < s0
+
+
+def test_stride2_stem_space_to_depth_rewrite_is_exact():
+    """The RGB-stem rewrite used on the GPU path (stride-2 conv -> stride-1 conv over a 2x2 space-to-depth view)."""
+    import torch.nn.functional as F
+    from deeplearning4j_b200.nn.layers.conv import _stem_space_to_depth
+    g = torch.Generator().manual_seed(0)
+    for (H, W, k, p) in [(64, 64, (7, 7), (3, 3)), (33, 31, (3, 3), (1, 1)), (32, 32, (5, 3), (2, 0)), (17, 18, (2, 2), (0, 0))]:
+        x = torch.randn(2, 3, H, W, dtype=torch.float64, generator=g)
+        w = torch.randn(5, 3, *k, dtype=torch.float64, generator=g)
+        b = torch.randn(5, dtype=torch.float64, generator=g)
+        ref = F.conv2d(x, w, b, stride=2, padding=p)
+        got = _stem_space_to_depth(x, w, b, k, p)
+        assert got.shape == ref.shape and float((got - ref).abs().max()) < 1e-10
