@@ -104,6 +104,42 @@ maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const unsigned char* __
   }
 }
 
+// Strided spatial subsampling x[:, ::sH, ::sW, :] (the input side of a strided 1x1 convolution) and its adjoint, which
+// writes the zeros and the scattered gradient in one pass.
+__global__ void __launch_bounds__(PL_THREADS)
+subsample_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, const PoolShape s) {
+  const int cv_n = s.C >> 3;
+  const long long total = (long long)s.N * s.OH * s.OW * cv_n;
+  for (long long g = blockIdx.x * (long long)PL_THREADS + threadIdx.x; g < total; g += (long long)gridDim.x * PL_THREADS) {
+    const int cv = (int)(g % cv_n);
+    long long t = g / cv_n;
+    const int ow = (int)(t % s.OW); t /= s.OW;
+    const int oh = (int)(t % s.OH);
+    const int n = (int)(t / s.OH);
+    reinterpret_cast<uint4*>(y)[g] =
+        __ldg(reinterpret_cast<const uint4*>(x + (((long long)n * s.H + (long long)oh * s.sH) * s.W + (long long)ow * s.sW) * s.C) + cv);
+  }
+}
+
+__global__ void __launch_bounds__(PL_THREADS)
+subsample_bwd_kernel(const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, const PoolShape s) {
+  const int cv_n = s.C >> 3;
+  const long long total = (long long)s.N * s.H * s.W * cv_n;
+  for (long long g = blockIdx.x * (long long)PL_THREADS + threadIdx.x; g < total; g += (long long)gridDim.x * PL_THREADS) {
+    const int cv = (int)(g % cv_n);
+    long long t = g / cv_n;
+    const int iw = (int)(t % s.W); t /= s.W;
+    const int ih = (int)(t % s.H);
+    const int n = (int)(t / s.H);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (ih % s.sH == 0 && iw % s.sW == 0) {
+      const int oh = ih / s.sH, ow = iw / s.sW;
+      if (oh < s.OH && ow < s.OW) v = __ldg(reinterpret_cast<const uint4*>(dy) + ((((long long)n * s.OH + oh) * s.OW + ow) * cv_n + cv));
+    }
+    reinterpret_cast<uint4*>(dx)[g] = v;
+  }
+}
+
 static inline int pl_grid(long long total) {
   long long b = (total + PL_THREADS - 1) / PL_THREADS;
   if (b > 148 * 16) b = 148 * 16;
@@ -137,5 +173,24 @@ DL4J_API int dl4j_maxpool_bwd(const void* dy, const void* idx, void* dx, const i
   const long long total = (long long)s.N * s.H * s.W * (s.C >> 3);
   maxpool_bwd_kernel<<<pl_grid(total), PL_THREADS, 0, (cudaStream_t)stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const unsigned char*>(idx), reinterpret_cast<__nv_bfloat16*>(dx), s);
+  return (int)cudaGetLastError();
+}
+
+// shape as above with kH = kW = 1, pH = pW = 0: OH = ceil(H / sH), OW = ceil(W / sW)
+DL4J_API int dl4j_subsample(const void* in, void* out, const int* shape, int backward, void* stream) {
+  PoolShape s;
+  memcpy(&s, shape, sizeof(s));
+  if (s.N <= 0 || s.H <= 0 || s.W <= 0 || s.C < 8 || s.C % 8 || s.sH < 1 || s.sW < 1 || s.OH != (s.H + s.sH - 1) / s.sH ||
+      s.OW != (s.W + s.sW - 1) / s.sW)
+    return -DL4J_ERR_BAD_ARG;
+  if (backward) {
+    const long long total = (long long)s.N * s.H * s.W * (s.C >> 3);
+    subsample_bwd_kernel<<<pl_grid(total), PL_THREADS, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(in),
+                                                                                 reinterpret_cast<__nv_bfloat16*>(out), s);
+  } else {
+    const long long total = (long long)s.N * s.OH * s.OW * (s.C >> 3);
+    subsample_fwd_kernel<<<pl_grid(total), PL_THREADS, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(in),
+                                                                                 reinterpret_cast<__nv_bfloat16*>(out), s);
+  }
   return (int)cudaGetLastError();
 }

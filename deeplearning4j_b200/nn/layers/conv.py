@@ -175,6 +175,9 @@ def _stem_space_to_depth(x, W, b, k, pad):
 
 
 def nnops_conv2d(x, W, b, stride, pad, dilation, groups=1):
+    if x.is_cuda and not torch.backends.cudnn.benchmark:
+        # the layers' default ``cudnnAlgoMode = PREFER_FASTEST``: let cuDNN time its algorithms once per shape
+        torch.backends.cudnn.benchmark = True
     return F.conv2d(x, W, b, stride=tuple(stride), padding=tuple(pad), dilation=tuple(dilation), groups=groups)
 
 

@@ -65,6 +65,7 @@ def _load():
             "dl4j_add_relu": [vp, vp, vp, i64, vp],
             "dl4j_maxpool_fwd": [vp, vp, vp, vp, vp],
             "dl4j_maxpool_bwd": [vp, vp, vp, vp, vp],
+            "dl4j_subsample": [vp, vp, vp, i32, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
             "dl4j_bind_device": [i32],
@@ -615,6 +616,32 @@ def lstm_seq(zx, rw, h0, c0, reverse=False):
     return _LstmSeqFn.apply(zx, rw, h0, c0, reverse, rw_lp)
 
 
+class _SubsampleFn(torch.autograd.Function):
+    """x[:, :, ::sH, ::sW] of a channels-last bf16 activation as one gather kernel; the gradient is one scatter-with-zeros."""
+
+    @staticmethod
+    def forward(ctx, x, sH, sW):
+        l = require()
+        x = _dense_cl(x)
+        N, C, H, W = x.shape
+        OH, OW = (H + sH - 1) // sH, (W + sW - 1) // sW
+        y = torch.empty((N, C, OH, OW), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        ctx.shape = (N, H, W, C, OH, OW, 1, 1, sH, sW, 0, 0)
+        rc = l.dl4j_subsample(_ptr(x), _ptr(y), (ctypes.c_int * 12)(*ctx.shape), 0, _stream())
+        _check(rc, "dl4j_subsample")
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        l = require()
+        N, H, W, C = ctx.shape[:4]
+        dy = _dense_cl(dy)
+        dx = torch.empty((N, C, H, W), dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+        rc = l.dl4j_subsample(_ptr(dy), _ptr(dx), (ctypes.c_int * 12)(*ctx.shape), 1, _stream())
+        _check(rc, "dl4j_subsample")
+        return dx, None, None
+
+
 def conv1x1(x, W, b, stride=(1, 1)):
     """1x1 convolution over a channels-last activation as one tcgen05 GEMM: [N*H*W, Cin] x [Cin, Cout] (forward, data
     gradient and weight gradient all run on the hand-written kernel).  ``W`` is the [Cout, Cin, 1, 1] parameter; returns
@@ -630,7 +657,7 @@ def conv1x1(x, W, b, stride=(1, 1)):
     if not W_lp.is_contiguous() or W_lp.data_ptr() % 16:
         return None
     if stride[0] != 1 or stride[1] != 1:
-        x = x[:, :, ::stride[0], ::stride[1]]
+        x = _SubsampleFn.apply(x, int(stride[0]), int(stride[1])) if x.dtype == torch.bfloat16 else x[:, :, ::stride[0], ::stride[1]]
     x = _dense_cl(x)
     N, _, H, Wd = x.shape
     x2 = x.permute(0, 2, 3, 1).reshape(N * H * Wd, Cin)
