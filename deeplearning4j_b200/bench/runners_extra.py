@@ -111,6 +111,7 @@ class LstmRunner(_NetRunner):
             self.dev.append((x.to(self.device), y.to(self.device)))
         self.i = 0
         self._attach(net)
+        self._graphs(net)
 
     def work_per_step(self):
         return self.batch * self.T

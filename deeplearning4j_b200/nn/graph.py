@@ -358,10 +358,32 @@ class ComputationGraph(BaseNetwork):
         names = list(ins.keys())
         n_in = len(names)
 
-        def loss_fn(ts):
-            return self._loss(dict(zip(names, ts[:n_in])), list(ts[n_in:]), fm, lm, True, ctx)
-        plain = fm is None and (lm is None or all(m is None for m in lm)) and not ctx
-        self._score = self._loss_backward([ins[n] for n in names] + list(labs), loss_fn, eager_ok=plain)
+        n_lab = len(labs)
+        no_masks = fm is None and (lm is None or all(m is None for m in lm))
+        if ctx and set(ctx.keys()) <= {"rnn_state_in"} and no_masks:
+            # truncated BPTT segment: the carried recurrent state travels as extra inputs / outputs of the step, so the
+            # segment can replay from a CUDA graph like a stateless step
+            st_in = ctx.get("rnn_state_in") or {}
+            keys = sorted(st_in.keys(), key=str)
+            sizes = [len(st_in[k]) for k in keys]
+            aux = {}
+
+            def loss_fn(ts):
+                pos, st = n_in + n_lab, {}
+                for k, n in zip(keys, sizes):
+                    st[k] = tuple(ts[pos:pos + n])
+                    pos += n
+                c = {"rnn_state_in": st}
+                loss = self._loss(dict(zip(names, ts[:n_in])), list(ts[n_in:n_in + n_lab]), None, None, True, c)
+                aux["rnn_state_out"] = c.get("rnn_state_out", {})
+                return loss
+            tensors = [ins[n] for n in names] + list(labs) + [t for k in keys for t in st_in[k]]
+            self._score = self._loss_backward(tensors, loss_fn, aux=aux)
+            ctx["rnn_state_out"] = aux.get("rnn_state_out", {})
+        else:
+            def loss_fn(ts):
+                return self._loss(dict(zip(names, ts[:n_in])), list(ts[n_in:]), fm, lm, True, ctx)
+            self._score = self._loss_backward([ins[n] for n in names] + list(labs), loss_fn, eager_ok=no_masks and not ctx)
         self._last_batch = next(iter(ins.values())).shape[0]
         if self.listeners:
             self._fire("onGradientCalculation")

@@ -289,9 +289,11 @@ class BaseNetwork:
         self._cg = {"on": bool(enabled), "warmup": int(warmup), "entries": {}}
         return self
 
-    def _loss_backward(self, tensors, loss_fn, eager_ok=True):
+    def _loss_backward(self, tensors, loss_fn, eager_ok=True, aux=None):
         """Runs ``loss = loss_fn(tensors); loss.backward()`` either eagerly or through a captured CUDA graph.
-        ``tensors`` is a flat list of input / label tensors; returns the detached loss."""
+        ``tensors`` is a flat list of input / label (/ carried state) tensors; returns the detached loss.  ``aux`` is a
+        dict that ``loss_fn`` fills with side outputs (carried recurrent state); on replay it receives the captured
+        graph's output tensors."""
         cg = getattr(self, "_cg", None)
         if not (cg and cg["on"] and eager_ok and self.flat_params.is_cuda):
             loss = loss_fn(tensors)
@@ -316,11 +318,16 @@ class BaseNetwork:
             e["launches"] = native.LAUNCHES - n0
             native.LAUNCHES = n0                    # capture launched nothing
             e["loss"] = loss.detach()
+            e["aux"] = dict(aux) if aux is not None else None
             e["graph"] = g
         for dst, src in zip(e["static"], tensors):
-            dst.copy_(src, non_blocking=True)
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src, non_blocking=True)
         e["graph"].replay()
         native.LAUNCHES += e["launches"]
+        if aux is not None and e["aux"] is not None:
+            aux.clear()
+            aux.update(e["aux"])
         return e["loss"]
 
     # ------------------------------------------------------------------ step skeleton
