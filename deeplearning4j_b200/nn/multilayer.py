@@ -238,8 +238,28 @@ class MultiLayerNetwork(BaseNetwork):
             self._train_step(x, y, fm, lm)
 
     def _train_step(self, x, y, fm=None, lm=None, ctx=None):
-        self._score = self._loss_backward([x, y], lambda ts: self._loss(ts[0], ts[1], fm, lm, True, ctx),
-                                          eager_ok=fm is None and lm is None and not ctx)
+        no_masks = fm is None and lm is None
+        if ctx and set(ctx.keys()) <= {"rnn_state_in"} and no_masks:
+            # truncated BPTT segment: carried recurrent state becomes extra step inputs / outputs (CUDA-graph friendly)
+            st_in = ctx.get("rnn_state_in") or {}
+            keys = sorted(st_in.keys(), key=str)
+            sizes = [len(st_in[k]) for k in keys]
+            aux = {}
+
+            def loss_fn(ts):
+                pos, st = 2, {}
+                for k, n in zip(keys, sizes):
+                    st[k] = tuple(ts[pos:pos + n])
+                    pos += n
+                c = {"rnn_state_in": st}
+                loss = self._loss(ts[0], ts[1], None, None, True, c)
+                aux["rnn_state_out"] = c.get("rnn_state_out", {})
+                return loss
+            self._score = self._loss_backward([x, y] + [t for k in keys for t in st_in[k]], loss_fn, aux=aux)
+            ctx["rnn_state_out"] = aux.get("rnn_state_out", {})
+        else:
+            self._score = self._loss_backward([x, y], lambda ts: self._loss(ts[0], ts[1], fm, lm, True, ctx),
+                                              eager_ok=no_masks and not ctx)
         self._last_batch = x.shape[0]
         if self.listeners:
             self._fire("onGradientCalculation")
