@@ -8,7 +8,7 @@
 // Work split: CTA j owns hidden units [16 j, 16 j + 16) and keeps their 64 recurrent weight rows
 // (4 gates x 16 units, each row = n bf16 values) resident in shared memory for the whole sequence, so the
 // recurrent weights are read from HBM once per launch instead of once per step.  Per step the CTA streams
-// h_{t-1} ([mb, n] bf16, L2 resident) through a 4-stage TMA ring as the M operand of tcgen05.mma
+// h_{t-1} ([mb, n] bf16, L2 resident) through a multi-stage TMA ring as the M operand of tcgen05.mma
 // (M = 128 batch rows, zero filled beyond mb; N = 64 gate rows; K = n), accumulates in TMEM, and its four
 // epilogue warps (one thread per batch row) apply the cell non-linearities with c_t held in registers across
 // steps, then publish their slice of h_t.  Steps are separated by a grid-wide arrive/wait on a global counter;
@@ -21,8 +21,7 @@ constexpr int LS_UNITS = 16;                 // hidden units per CTA
 constexpr int LS_N = 4 * LS_UNITS;           // MMA N: gate rows per CTA
 constexpr int LS_M = 128;                    // MMA M: batch rows (zero padded)
 constexpr int LS_BK = 64;                    // K elements per stage (128 bytes, SWIZZLE_128B)
-constexpr int LS_STAGES = 4;
-constexpr int LS_A_STAGE = LS_M * LS_BK * 2; // 16 KB
+constexpr int LS_MAX_STAGES = 16;             // ring depth is chosen at launch from the shared memory left beside the weights
 constexpr int LS_B_KB = LS_N * LS_BK * 2;    // 8 KB per k-block of resident weights
 constexpr int LS_THREADS = 192;              // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 
@@ -33,6 +32,7 @@ struct LstmSeqParams {
   float* cs;                 // [T, mb, n]  c_t (time index, not step index)
   __nv_bfloat16* gates;      // [T, mb, 4n] activated gates (for the backward pass)
   int T, mb, n, reverse;
+  int stages, a_stage;       // TMA ring: number of stages and bytes per stage (batch rows rounded up to 8, x 128 B)
   unsigned int* counter;     // zero on entry
   int* status;
 };
@@ -79,11 +79,11 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int kblocks = p.n / LS_BK;
   uint8_t* w_smem = smem;                                   // kblocks x 8 KB, resident
-  uint8_t* a_smem = w_smem + kblocks * LS_B_KB;             // LS_STAGES x 16 KB ring
-  uint64_t* bars = reinterpret_cast<uint64_t*>(a_smem + LS_STAGES * LS_A_STAGE);
-  uint64_t* full_bar = bars;                  // [LS_STAGES]
-  uint64_t* empty_bar = bars + LS_STAGES;     // [LS_STAGES]
-  uint64_t* w_full = bars + 2 * LS_STAGES;
+  uint8_t* a_smem = w_smem + kblocks * LS_B_KB;             // ring of p.stages x p.a_stage bytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_smem + p.stages * p.a_stage);
+  uint64_t* full_bar = bars;                  // [LS_MAX_STAGES]
+  uint64_t* empty_bar = bars + LS_MAX_STAGES;     // [LS_MAX_STAGES]
+  uint64_t* w_full = bars + 2 * LS_MAX_STAGES;
   uint64_t* acc_full = w_full + 1;
   uint64_t* acc_empty = w_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 3);
@@ -95,7 +95,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_h);
     prefetch_tmap(&tmap_w);
-    for (int i = 0; i < LS_STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < p.stages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     mbar_init(w_full, 1);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
@@ -130,9 +130,9 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
         }
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
-          mbar_expect_tx(&full_bar[stage], LS_A_STAGE);
-          tma_load_4d(a_smem + stage * LS_A_STAGE, &tmap_h, &full_bar[stage], kb * LS_BK, 0, s, 0);
-          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+          mbar_expect_tx(&full_bar[stage], (uint32_t)p.a_stage);
+          tma_load_4d(a_smem + stage * p.a_stage, &tmap_h, &full_bar[stage], kb * LS_BK, 0, s, 0);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -149,13 +149,13 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * LS_A_STAGE), 16, 1024);
+          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * p.a_stage), 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LS_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
             umma_f16(tmem_base, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
-          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(acc_full);
       }
@@ -259,6 +259,7 @@ struct LstmSeqBwdParams {
   __nv_bfloat16* dh0;          // [mb, n] or null
   float* dc0;                  // [mb, n] or null
   int T, mb, n, reverse;
+  int stages, a_stage;       // TMA ring: number of stages and bytes per stage (batch rows rounded up to 8, x 128 B)
   unsigned int* counter;
   int* status;
 };
@@ -274,10 +275,10 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
   const int kblocks = 4 * p.n / LS_BK;
   uint8_t* w_smem = smem;
   uint8_t* a_smem = w_smem + kblocks * LB_B_KB;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(a_smem + LS_STAGES * LS_A_STAGE);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_smem + p.stages * p.a_stage);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + LS_STAGES;
-  uint64_t* w_full = bars + 2 * LS_STAGES;
+  uint64_t* empty_bar = bars + LS_MAX_STAGES;
+  uint64_t* w_full = bars + 2 * LS_MAX_STAGES;
   uint64_t* acc_full = w_full + 1;
   uint64_t* acc_empty = w_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 3);
@@ -290,7 +291,7 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_dz);
     prefetch_tmap(&tmap_w);
-    for (int i = 0; i < LS_STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < p.stages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     mbar_init(w_full, 1);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 4);
@@ -321,9 +322,9 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
         fence_proxy_async_all();
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
-          mbar_expect_tx(&full_bar[stage], LS_A_STAGE);
-          tma_load_4d(a_smem + stage * LS_A_STAGE, &tmap_dz, &full_bar[stage], kb * LS_BK, 0, t_src, 0);
-          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+          mbar_expect_tx(&full_bar[stage], (uint32_t)p.a_stage);
+          tma_load_4d(a_smem + stage * p.a_stage, &tmap_dz, &full_bar[stage], kb * LS_BK, 0, t_src, 0);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -340,13 +341,13 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * LS_A_STAGE), 16, 1024);
+          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * p.a_stage), 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LB_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
             umma_f16(tmem_base, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
-          if (++stage == LS_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(acc_full);
       }
@@ -465,6 +466,22 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
 
 using namespace dl4j;
 
+// Shared memory plan: resident weights, then as many ring stages as fit (stage = batch rows rounded up to 8 x 128 B: rows
+// beyond the batch are never loaded, the MMA reads whatever those rows of the tile hold and their accumulator rows are
+// ignored), then the barriers.  Returns the dynamic shared memory size, 0 when fewer than two stages fit.
+static size_t ls_ring(size_t weight_bytes, int mb, int* a_rows, int* stages) {
+  const int rows = (mb + 7) / 8 * 8;
+  // the M = 128 MMA reads a full 16 KB tile from every stage base: keep that much allocated behind the last stage
+  const size_t tail = (size_t)(LS_M - rows) * 128;
+  const size_t stage = (size_t)rows * 128, limit = 227 * 1024, fixed = weight_bytes + 1024 + 512 + tail;
+  if (fixed + 2 * stage > limit) return 0;
+  size_t s = (limit - fixed) / stage;
+  if (s > LS_MAX_STAGES) s = LS_MAX_STAGES;
+  *a_rows = rows;
+  *stages = (int)s;
+  return fixed + s * stage;
+}
+
 static int ls_encode(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t nb1, uint64_t row_stride_bytes,
                      uint64_t sb1_bytes, uint32_t box_inner, uint32_t box_outer) {
   dl4j_PFN_encodeTiled enc = dl4j_get_encode_tiled();
@@ -485,8 +502,9 @@ DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, cons
                                int reverse, unsigned int* counter, void* stream_) {
   if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
   const int kblocks = n / LS_BK;
-  const size_t smem = (size_t)kblocks * LS_B_KB + LS_STAGES * LS_A_STAGE + 1024 + 256;
-  if (smem > 227 * 1024) return -DL4J_ERR_BAD_ARG;
+  int a_rows, stages;
+  const size_t smem = ls_ring((size_t)kblocks * LS_B_KB, mb, &a_rows, &stages);
+  if (!smem) return -DL4J_ERR_BAD_ARG;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -494,7 +512,7 @@ DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, cons
   if (grid > sms) return -DL4J_ERR_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_;
   CUtensorMap th, tw;
-  int r = ls_encode(&th, h_all, (uint64_t)n, (uint64_t)mb, (uint64_t)T + 1, (uint64_t)n * 2, (uint64_t)mb * n * 2, LS_BK, LS_M);
+  int r = ls_encode(&th, h_all, (uint64_t)n, (uint64_t)mb, (uint64_t)T + 1, (uint64_t)n * 2, (uint64_t)mb * n * 2, LS_BK, (uint32_t)a_rows);
   if (r) return -1000 - r;
   r = ls_encode(&tw, rw, (uint64_t)n, (uint64_t)4 * n, 1, (uint64_t)n * 2, (uint64_t)4 * n * n * 2, LS_BK, LS_UNITS);
   if (r) return -1000 - r;
@@ -504,6 +522,7 @@ DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, cons
   p.c0 = c0; p.cs = cs;
   p.gates = reinterpret_cast<__nv_bfloat16*>(gates);
   p.T = T; p.mb = mb; p.n = n; p.reverse = reverse;
+  p.stages = stages; p.a_stage = a_rows * 128;
   p.counter = counter;
   p.status = dl4j_status_word(dev);
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
@@ -522,8 +541,9 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
                                void* stream_) {
   if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
   const int kblocks = 4 * n / LS_BK;
-  const size_t smem = (size_t)kblocks * LB_B_KB + LS_STAGES * LS_A_STAGE + 1024 + 256;
-  if (smem > 227 * 1024) return -DL4J_ERR_BAD_ARG;
+  int a_rows, stages;
+  const size_t smem = ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
+  if (!smem) return -DL4J_ERR_BAD_ARG;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -531,7 +551,7 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   if (grid > sms) return -DL4J_ERR_BAD_ARG;
   cudaStream_t stream = (cudaStream_t)stream_;
   CUtensorMap td, tw;
-  int r = ls_encode(&td, dzx, (uint64_t)4 * n, (uint64_t)mb, (uint64_t)T, (uint64_t)4 * n * 2, (uint64_t)mb * 4 * n * 2, LS_BK, LS_M);
+  int r = ls_encode(&td, dzx, (uint64_t)4 * n, (uint64_t)mb, (uint64_t)T, (uint64_t)4 * n * 2, (uint64_t)mb * 4 * n * 2, LS_BK, (uint32_t)a_rows);
   if (r) return -1000 - r;
   r = ls_encode(&tw, rwt, (uint64_t)4 * n, (uint64_t)n, 1, (uint64_t)4 * n * 2, (uint64_t)4 * n * n * 2, LS_BK, LS_UNITS);
   if (r) return -1000 - r;
@@ -543,6 +563,7 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   p.dh0 = reinterpret_cast<__nv_bfloat16*>(dh0);
   p.dc0 = dc0;
   p.T = T; p.mb = mb; p.n = n; p.reverse = reverse;
+  p.stages = stages; p.a_stage = a_rows * 128;
   p.counter = counter;
   p.status = dl4j_status_word(dev);
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
