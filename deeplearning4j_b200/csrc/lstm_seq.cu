@@ -21,6 +21,8 @@ constexpr int LS_UNITS = 16;                 // hidden units per CTA
 constexpr int LS_N = 4 * LS_UNITS;           // MMA N: gate rows per CTA
 constexpr int LS_M = 128;                    // MMA M: batch rows (zero padded)
 constexpr int LS_BK = 64;                    // K elements per stage (128 bytes, SWIZZLE_128B)
+constexpr int LS_ACCS = 4;                   // independent TMEM accumulators: k-step j of every k-block adds into accumulator j,
+                                             // so consecutive MMAs do not wait on each other; the epilogue sums them
 constexpr int LS_MAX_STAGES = 16;             // ring depth is chosen at launch from the shared memory left beside the weights
 constexpr int LS_B_KB = LS_N * LS_BK * 2;    // 8 KB per k-block of resident weights
 constexpr int LS_THREADS = 192;              // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
@@ -102,7 +104,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, LS_N);
+    tmem_alloc(tmem_slot, LS_ACCS * LS_N);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -153,7 +155,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LS_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
-            umma_f16(tmem_base, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(tmem_base + (uint32_t)(k * LS_N), da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, kb > 0 ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -194,6 +196,18 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       tmem_ld_32x32(taddr, r0);
       tmem_ld_32x32(taddr + 32, r1);
       tmem_ld_wait();
+#pragma unroll
+      for (int j = 1; j < LS_ACCS; ++j) {          // fold the independent partial accumulators
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32(taddr + j * LS_N, t0);
+        tmem_ld_32x32(taddr + j * LS_N + 32, t1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          r0[i] = __float_as_uint(__uint_as_float(r0[i]) + __uint_as_float(t0[i]));
+          r1[i] = __float_as_uint(__uint_as_float(r1[i]) + __uint_as_float(t1[i]));
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty);      // accumulator drained: the next step's MMAs may overwrite it
@@ -238,7 +252,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, LS_N);
+    tmem_dealloc(tmem_base, LS_ACCS * LS_N);
   }
 }
 
@@ -266,7 +280,7 @@ struct LstmSeqBwdParams {
 
 constexpr int LB_N = LS_UNITS;               // MMA N
 constexpr int LB_B_KB = LB_N * LS_BK * 2;    // 2 KB of resident weights per k-block
-constexpr int LB_TMEM_COLS = 32;
+constexpr int LB_TMEM_COLS = 64;           // LS_ACCS partial accumulators of LB_N columns each
 
 __global__ void __launch_bounds__(LS_THREADS, 1)
 lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqBwdParams p) {
@@ -345,7 +359,7 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LB_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
-            umma_f16(tmem_base, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(tmem_base + (uint32_t)(k * LB_N), da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, kb > 0 ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -399,8 +413,13 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
       if (r >= 0) {
         if (!mbar_wait_bounded(acc_full, (uint32_t)(r & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
         tc_fence_after();
+        uint32_t hi[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), acc);
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + 32, hi);
         tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < LS_UNITS; ++u)           // fold the four partial accumulators (columns u, 16 + u, 32 + u, 48 + u)
+          acc[u] = __float_as_uint(__uint_as_float(acc[u]) + __uint_as_float(acc[16 + u]) + __uint_as_float(hi[u]) + __uint_as_float(hi[16 + u]));
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty);
