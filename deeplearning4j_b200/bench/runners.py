@@ -105,6 +105,9 @@ class BertRunner(BaseRunner):
         sd = build_bert_mlm(cfg, self.batch, self.seq, Adam(1e-4), DataType.BFLOAT16)
         sd.to(self.device)
         self.sd = sd
+        import os
+        if not a.library_baseline and os.environ.get("DL4J_CUDA_GRAPHS", "1") != "0":
+            sd.getTrainingConfig().cudaGraphs = True        # forward + backward replay from a captured CUDA graph
         g = torch.Generator().manual_seed(1234 + self.rank)
         n_tok = self.batch * self.seq
         self.n_masked = int(n_tok * 0.15) // 8 * 8

@@ -25,7 +25,8 @@ from .core import SDVariable, VariableType, _tensor
 class TrainingConfig:
     def __init__(self, updater=None, regularization=None, minimize=True, dataSetFeatureMapping=None, dataSetLabelMapping=None,
                  dataSetFeatureMaskMapping=None, dataSetLabelMaskMapping=None, lossVariables=None, computeDataType=None,
-                 iterationCount=0, epochCount=0, trainEvaluations=None, validationEvaluations=None):
+                 iterationCount=0, epochCount=0, trainEvaluations=None, validationEvaluations=None, cudaGraphs=False):
+        self.cudaGraphs = bool(cudaGraphs)      # replay forward + backward from a captured CUDA graph (runtime option, not serialised)
         self.updater = updater or Sgd()
         self.regularization = list(regularization or [])
         self.minimize = minimize
@@ -112,6 +113,7 @@ class _TCBuilder:
     def dataSetLabelMaskMapping(self, *n): self.kw["dataSetLabelMaskMapping"] = list(n[0]) if len(n) == 1 and isinstance(n[0], (list, tuple)) else list(n); return self
     def markLabelsUnused(self): self.kw["dataSetLabelMapping"] = []; return self
     def computeDataType(self, dt): self.kw["computeDataType"] = dt; return self
+    def cudaGraphs(self, on=True): self.kw["cudaGraphs"] = bool(on); return self
     def trainEvaluation(self, var, labelIndex, *evals): self.kw.setdefault("trainEvaluations", {})[getattr(var, "name", var)] = (labelIndex, list(evals)); return self
     def validationEvaluation(self, var, labelIndex, *evals): self.kw.setdefault("validationEvaluations", {})[getattr(var, "name", var)] = (labelIndex, list(evals)); return self
     def skipBuilderValidation(self, b): return self
@@ -232,12 +234,17 @@ class TrainingState:
         losses = sd.lossVariables or tc.lossVariables
         if not losses:
             raise ValueError("no loss variables: call sd.setLossVariables(...)")
-        vals = InferenceSession(sd).run(placeholders, losses, self.values(), training=True)
-        loss = vals[losses[0]].sum() if len(losses) == 1 else sum(vals[l].sum() for l in losses)
-        if not tc.minimize:
-            loss = -loss
-        loss.backward()
-        self.score = loss.detach()
+        def fwd_bwd(ph):
+            vals = InferenceSession(sd).run(ph, losses, self.values(), training=True)
+            loss = vals[losses[0]].sum() if len(losses) == 1 else sum(vals[l].sum() for l in losses)
+            if not tc.minimize:
+                loss = -loss
+            loss.backward()
+            return loss.detach()
+        if tc.cudaGraphs and self.flat_params.is_cuda and not sd.listeners:
+            self.score = self._graphed(placeholders, fwd_bwd)
+        else:
+            self.score = fwd_bwd(placeholders)
         with torch.no_grad():
             if not (self.gradient_hook is not None and self.gradient_hook(self) is True):
                 self.updater.update(tc.iterationCount, tc.epochCount)
@@ -247,6 +254,38 @@ class TrainingState:
                     self.flat_grads.zero_()
         tc.iterationCount += 1
         return self.score
+
+
+    def _graphed(self, placeholders, fwd_bwd, warmup=1):
+        """Forward + backward through a CUDA graph captured per placeholder signature (the updater stays outside, so
+        schedules and the Adam step count keep working).  The first ``warmup`` steps of a signature run eagerly."""
+        from ..ops import native
+        from .core import _tensor
+        dev = self.sd.device
+        names = sorted(k.name if hasattr(k, "name") else k for k in placeholders)
+        src = {(k.name if hasattr(k, "name") else k): v for k, v in placeholders.items()}
+        tensors = [_tensor(src[n]) for n in names]          # host (pinned) tensors are copied straight into the static inputs
+        key = tuple((n, tuple(t.shape), t.dtype) for n, t in zip(names, tensors))
+        cache = self.__dict__.setdefault("_cg_entries", {})
+        e = cache.setdefault(key, {"seen": 0, "graph": None})
+        if e["graph"] is None:
+            e["seen"] += 1
+            if e["seen"] <= warmup:
+                return fwd_bwd({n: (t if t.device == dev else t.to(dev, non_blocking=True)) for n, t in zip(names, tensors)})
+            e["static"] = [t.to(dev, copy=True) for t in tensors]
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = native.LAUNCHES
+            with torch.cuda.graph(g):
+                loss = fwd_bwd(dict(zip(names, e["static"])))
+            e["launches"] = native.LAUNCHES - n0
+            native.LAUNCHES = n0
+            e["loss"], e["graph"] = loss, g
+        for dst, t in zip(e["static"], tensors):
+            dst.copy_(t, non_blocking=True)
+        e["graph"].replay()
+        native.LAUNCHES += e["launches"]
+        return e["loss"]
 
 
 class History:
