@@ -135,3 +135,35 @@ def attention(q, k, v, mask, scale):
         return None
     scale = float(scale) if scale is not None else D ** -0.5
     return _AttentionFn.apply(q, k, v, mask, scale)
+
+
+_LONG3 = ctypes.c_long * 3
+
+
+def flash_supported(q, k, v):
+    return (native.available() and q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[3] == 64 and k.shape[2] in (256, 512)
+            and k.shape[2] == v.shape[2] and q.shape[:2] == k.shape[:2])
+
+
+def flash_forward(q, k, v, key_mask, scale):
+    """Fused attention forward: returns (out [B, Tq, H, 64] bf16, lse [B, H, Tq] fp32).  q, k, v: [B, H, T, 64] views."""
+    l = native.require()
+    if not hasattr(l.dl4j_flash_attn_fwd, "_typed"):
+        vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        lp = ctypes.POINTER(ctypes.c_long)
+        l.dl4j_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, f32, vp]
+        l.dl4j_flash_attn_fwd.restype = ctypes.c_int
+        l.dl4j_flash_attn_fwd._typed = True
+    q, k, v = _prep(q), _prep(k), _prep(v)
+    Bn, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    out = torch.empty((Bn, Tq, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((Bn, H, Tq), dtype=torch.float32, device=q.device)
+    mk = key_mask.to(torch.float32).contiguous() if key_mask is not None else None
+
+    def st(t):
+        return _LONG3(t.stride(0), t.stride(1), t.stride(2))
+    rc = l.dl4j_flash_attn_fwd(native._ptr(q), native._ptr(k), native._ptr(v), native._ptr(out), native._ptr(lse), native._ptr(mk),
+                               Bn, H, Tq, Tk, st(q), st(k), st(v), float(scale), native._stream())
+    native._check(rc, "dl4j_flash_attn_fwd")
+    return out, lse

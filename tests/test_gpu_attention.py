@@ -52,3 +52,32 @@ def test_attention_fwd_bwd(B, H, T, D, packed, use_mask):
     else:
         for a, b in ((q, q2), (k, k2), (v, v2)):
             assert _rel(a.grad, b.grad) < 4e-2
+
+
+@pytest.mark.parametrize("B,H,Tq,Tk,masked", [(2, 3, 512, 512, False), (2, 2, 256, 256, True), (1, 4, 384, 512, True), (1, 1, 100, 256, False)])
+def test_flash_forward_matches_reference(B, H, Tq, Tk, masked):
+    from deeplearning4j_b200.ops import attention_native as an
+    from deeplearning4j_b200.ops import native
+    native.require()
+    g = torch.Generator(device="cuda").manual_seed(B * 100 + H * 10 + Tq)
+    # packed projection buffer [B, T, 3, H, 64] like the multi-head layer produces: q / k / v are strided views
+    qkv = torch.randn(B, max(Tq, Tk), 3, H, 64, device="cuda", generator=g).bfloat16()
+    q = qkv[:, :Tq, 0].permute(0, 2, 1, 3)
+    k = qkv[:, :Tk, 1].permute(0, 2, 1, 3)
+    v = qkv[:, :Tk, 2].permute(0, 2, 1, 3)
+    mask = None
+    if masked:
+        mask = (torch.rand(B, Tk, device="cuda", generator=g) > 0.3).float()
+        mask[:, 0] = 1.0
+    scale = 0.125
+    out, lse = an.flash_forward(q, k, v, mask, scale)
+    torch.cuda.synchronize()
+    native.check_status()
+    s = torch.matmul(q.float(), k.float().transpose(-1, -2)) * scale
+    if mask is not None:
+        s = s.masked_fill(mask[:, None, None, :] == 0, float("-inf"))
+    ref = torch.matmul(torch.softmax(s, -1), v.float())                 # [B, H, Tq, 64]
+    got = out.permute(0, 2, 1, 3).float()
+    assert float((got - ref).abs().max()) < 2e-2 * float(ref.abs().max() + 1e-6) + 2e-2
+    ref_lse = torch.logsumexp(s, -1)
+    assert float((lse - ref_lse).abs().max()) < 2e-2
