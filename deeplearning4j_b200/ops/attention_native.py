@@ -64,6 +64,14 @@ class _AttentionFn(torch.autograd.Function):
         Bn, H, Tq, D = q.shape
         Tk = k.shape[2]
         dt = q.dtype
+        ctx.flash = USE_FLASH and flash_supported(q, k, v)
+        if ctx.flash:
+            # fused kernel: the score matrix stays in tensor memory; only O and the row log-sum-exp are written
+            O, lse = flash_forward(q, k, v, key_mask, scale)
+            mk = key_mask.to(torch.float32).contiguous() if key_mask is not None else None
+            ctx.save_for_backward(q, k, v, O, lse, mk)
+            ctx.scale = scale
+            return O.permute(0, 2, 1, 3)
         P = torch.empty((Bn, H, Tq, Tk), dtype=dt, device=q.device)
         # S = scale * Q K^T
         _bgemm(l, q.data_ptr(), k.data_ptr(), P.data_ptr(), Tq, Tk, D, q.stride(2), k.stride(2), Tk, 0, 0, scale, H, Bn,
@@ -84,6 +92,8 @@ class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dO):
         l = native.require()
+        if ctx.flash:
+            return _flash_backward(ctx, dO)
         q, k, v, P = ctx.saved_tensors
         Bn, H, Tq, D = q.shape
         Tk = k.shape[2]
@@ -138,6 +148,42 @@ def attention(q, k, v, mask, scale):
 
 
 _LONG3 = ctypes.c_long * 3
+USE_FLASH = True      # False: batched GEMMs + separate softmax kernels with a materialised score matrix (cross-check path)
+
+
+def _flash_backward(ctx, dO):
+    l = native.require()
+    if not hasattr(l.dl4j_flash_attn_bwd, "_typed"):
+        vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        lp = ctypes.POINTER(ctypes.c_long)
+        l.dl4j_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, lp, ctypes.c_long, ctypes.c_long, f32, vp]
+        l.dl4j_flash_attn_bwd.restype = ctypes.c_int
+        l.dl4j_flash_attn_bwd._typed = True
+    q, k, v, O, lse, mk = ctx.saved_tensors
+    Bn, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    dO = _prep(dO)                                           # [B, H, Tq, D] view
+    # D_r = sum_d dO * O per query row, laid out like the log-sum-exp
+    dvec = (dO.permute(0, 2, 1, 3).float() * O.float()).sum(-1).permute(0, 2, 1).contiguous()
+    dq_acc = torch.zeros((Bn, H, Tq, D), dtype=torch.float32, device=q.device)
+    same_len = Tq == Tk
+    if same_len:
+        # one packed [B, T, 3, H, D] gradient buffer, so the gradient of the fused q/k/v projection is a plain view
+        dqkv = torch.empty((Bn, Tq, 3, H, D), dtype=q.dtype, device=q.device)
+        dq_t, dk_t, dv_t = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    else:
+        dq_t = torch.empty((Bn, Tq, H, D), dtype=q.dtype, device=q.device)
+        dk_t = torch.empty((Bn, Tk, H, D), dtype=q.dtype, device=q.device)
+        dv_t = torch.empty((Bn, Tk, H, D), dtype=q.dtype, device=q.device)
+
+    def st(t):
+        return _LONG3(t.stride(0), t.stride(1), t.stride(2))
+    rc = l.dl4j_flash_attn_bwd(native._ptr(q), native._ptr(k), native._ptr(v), native._ptr(dO), native._ptr(lse), native._ptr(dvec),
+                               native._ptr(mk), native._ptr(dq_acc), native._ptr(dk_t), native._ptr(dv_t), Bn, H, Tq, Tk,
+                               st(q), st(k), st(v), st(dO), dk_t.stride(0), dk_t.stride(1), float(ctx.scale), native._stream())
+    native._check(rc, "dl4j_flash_attn_bwd")
+    dq_t.copy_(dq_acc.permute(0, 2, 1, 3))
+    return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None
 
 
 def flash_supported(q, k, v):

@@ -16,7 +16,7 @@ def _ref(q, k, v, mask, scale):
     return torch.softmax(s, -1) @ v.float()
 
 
-@pytest.mark.parametrize("B,H,T,D", [(2, 3, 128, 64), (1, 12, 512, 64), (3, 2, 136, 32)])
+@pytest.mark.parametrize("B,H,T,D", [(2, 3, 128, 64), (1, 12, 512, 64), (2, 4, 256, 64), (3, 2, 136, 32)])
 @pytest.mark.parametrize("packed", [True, False])
 @pytest.mark.parametrize("use_mask", [False, True])
 def test_attention_fwd_bwd(B, H, T, D, packed, use_mask):
