@@ -1,0 +1,268 @@
+// Fused scaled-dot-product attention forward for head size 64 (bf16), one CTA per (batch, head, 128-query block), two
+// CTAs resident per SM so that one CTA's softmax overlaps the other's loads and MMAs:
+//     for each block of 128 keys:  S = Q K_j^T (tcgen05, fp32 in TMEM)  ->  online softmax in registers  ->
+//     P_j (bf16) staged in shared memory  ->  P_j V_j (tcgen05, TMEM)  ->  O = O * alpha + P_j V_j in registers
+//     finally: normalise, store O [B, Tq, H, 64] and the row log-sum-exp [B, H, Tq].
+// The score matrix never reaches HBM (AttentionHelper.cpp computes matmul, scale, mask add, softmax over the full
+// score matrix and a second matmul as separate ops).  Warp 0 issues the TMA loads (K / V blocks through a 3-slot
+// ring), warp 1 the MMAs, warps 2-9 do the softmax: two threads per query row, each owning half of the columns.
+#include "flash_common.cuh"
+
+namespace dl4j {
+
+constexpr int FF_BM = 128;                    // queries per CTA
+constexpr int FF_BN = 128;                    // keys per block
+constexpr int FF_THREADS = 64 + 256;
+constexpr int FF_TILE = 128 * FA_D * 2;       // 16 KB: Q tile, one K block or one V block
+constexpr int FF_P_BYTES = FF_BM * FF_BN * 2; // 32 KB
+constexpr int FF_SLOTS = 3;
+constexpr int FF_TMEM_COLS = 256;             // S: 0..127, P V: 128..191
+constexpr uint32_t FF_T_PV = 128;
+
+struct FlashFwdParams {
+  __nv_bfloat16* out;        // [B, Tq, H, 64]
+  float* lse;                // [B, H, Tq]
+  const float* key_mask;     // [B, Tk] (non-zero = keep) or null
+  int B, H, Tq, Tk;
+  float scale;
+  int* status;
+};
+
+__global__ void __launch_bounds__(FF_THREADS, 2)
+flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const FlashFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = q_s + FF_TILE;                    // FF_SLOTS tiles, filled in the order K_0, V_0, K_1, V_1, ...
+  uint8_t* p_s = kv_s + FF_SLOTS * FF_TILE;
+  float* mask_s = reinterpret_cast<float*>(p_s + FF_P_BYTES);         // [128] current key block
+  float* xch = mask_s + FF_BN;                                        // [2][128] per-row exchange between the two column halves
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 2 * FF_BM + 4);     // 4 floats: failure flag + padding
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;          // [FF_SLOTS]
+  uint64_t* kv_empty = kv_full + FF_SLOTS;
+  uint64_t* s_full = kv_empty + FF_SLOTS;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* pv_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_blocks = (p.Tq + FF_BM - 1) / FF_BM;
+  const int qb = blockIdx.x % q_blocks;
+  const int h = (blockIdx.x / q_blocks) % p.H;
+  const int b = blockIdx.x / (q_blocks * p.H);
+  const int nb = p.Tk / FF_BN;
+  const int q0 = qb * FF_BM;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < FF_SLOTS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 8);
+    mbar_init(pv_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, FF_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, FF_TILE);
+      tma_load_4d(q_s, &tmap_q, q_full, 0, q0, h, b);
+      for (int t = 0; t < 2 * nb; ++t) {              // tile t: K block t/2 (even) or V block t/2 (odd)
+        const int slot = t % FF_SLOTS;
+        const uint32_t ph = (uint32_t)((t / FF_SLOTS) & 1);
+        if (!mbar_wait_bounded(&kv_empty[slot], ph ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) break;
+        mbar_expect_tx(&kv_full[slot], FF_TILE);
+        tma_load_4d(kv_s + slot * FF_TILE, (t & 1) ? &tmap_v : &tmap_k, &kv_full[slot], 0, (t >> 1) * FF_BN, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(1, 0, 0, FF_BM, FF_BN);      // S = Q K^T: both operands K-major (K = head dim)
+      const uint32_t idesc_o = make_idesc(1, 0, 1, FF_BM, FA_D);       // P V: V [keys, 64] is MN-major for the B operand
+      const uint64_t dq = make_smem_desc_sw128(smem_u32(q_s), 16, 1024);
+      const uint32_t pp = smem_u32(p_s);
+      bool ok = mbar_wait_bounded(q_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
+      auto issue_s = [&](int j) -> bool {
+        const int t = 2 * j, slot = t % FF_SLOTS;
+        if (!mbar_wait_bounded(&kv_full[slot], (uint32_t)((t / FF_SLOTS) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint64_t dk = make_smem_desc_sw128(smem_u32(kv_s + slot * FF_TILE), 16, 1024);
+#pragma unroll
+        for (int k = 0; k < FA_D / 16; ++k)
+          umma_f16(tmem_base, dq + ((uint64_t)(k * 32) >> 4), dk + ((uint64_t)(k * 32) >> 4), idesc_s, k > 0 ? 1u : 0u);
+        umma_commit(&kv_empty[slot]);
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < nb && ok; ++j) {
+        // P_j is in shared memory (and S_j has been read out of TMEM) once p_full completes
+        if (!mbar_wait_bounded(p_full, (uint32_t)(j & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        const int t = 2 * j + 1, slot = t % FF_SLOTS;
+        if (!mbar_wait_bounded(&kv_full[slot], (uint32_t)((t / FF_SLOTS) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t pv = smem_u32(kv_s + slot * FF_TILE);
+#pragma unroll
+        for (int k = 0; k < FF_BN / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(pp + (k >> 2) * (FF_BM * 128) + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(pv + k * (16 * 128), 64 * 128, 1024);
+          umma_f16(tmem_base + FF_T_PV, da, db, idesc_o, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[slot]);
+        umma_commit(pv_full);
+        if (j + 1 < nb) ok = issue_s(j + 1);        // overlaps the threads' accumulation of P_j V_j
+      }
+    }
+  } else {
+    const int cw = warp - 2;                        // 0..7
+    const int q = cw & 3;                           // TMEM lane quadrant
+    const int ch = cw >> 2;                         // column half owned by this thread
+    const int r = q * 32 + lane;                    // query row within the block
+    const int t = threadIdx.x - 64;                 // 0..255
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const float k2 = p.scale * FA_LOG2E;
+    float run_m = -INFINITY, run_l = 0.f;           // running row maximum (raw scores) and this thread's partial row sum
+    float o[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    volatile int* fail_s = reinterpret_cast<volatile int*>(xch + 2 * FF_BM);    // set by any thread whose bounded wait expired
+    if (t == 0) *fail_s = 0;
+    for (int j = 0; j < nb; ++j) {
+      // key mask of this block -> shared memory; the barrier also orders the reuse of xch / mask_s between blocks
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (t < FF_BN) mask_s[t] = p.key_mask ? p.key_mask[(long)b * p.Tk + j * FF_BN + t] : 1.f;
+      if (!mbar_wait_bounded(s_full, (uint32_t)(j & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) *fail_s = 1;
+      tc_fence_after();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (*fail_s) break;                            // uniform: every thread reads the flag after the same barrier
+      const float* mk = mask_s + ch * 64;
+      float m = -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32];
+        tmem_ld_32x32(taddr + ch * 64 + half * 32, sv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (mk[half * 32 + i] != 0.f) m = fmaxf(m, __uint_as_float(sv[i]));
+      }
+      xch[ch * FF_BM + r] = m;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      m = fmaxf(m, xch[(ch ^ 1) * FF_BM + r]);
+      const float new_m = fmaxf(run_m, m);
+      const float mref = (new_m == -INFINITY) ? 0.f : new_m;
+      const float alpha = (run_m == -INFINITY) ? 0.f : fa_exp2((run_m - mref) * k2);
+      run_m = new_m;
+      const float mk2 = mref * k2;
+      float l = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32];
+        tmem_ld_32x32(taddr + ch * 64 + half * 32, sv);
+        tmem_ld_wait();
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          e[i] = mk[half * 32 + i] != 0.f ? fa_exp2(fmaf(__uint_as_float(sv[i]), k2, -mk2)) : 0.f;
+          l += e[i];
+        }
+        fa_store_row(p_s, r, ch * 64 + half * 32, 32, e);
+      }
+      run_l = fmaf(run_l, alpha, l);
+      tc_fence_before();
+      fence_proxy_async_smem();       // P was written through the generic proxy; the MMA reads it through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      // O = O * alpha + P_j V_j (this thread: 32 of the 64 head-dimension columns)
+      if (!mbar_wait_bounded(pv_full, (uint32_t)(j & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) {
+        *fail_s = 1;                                 // seen by everybody after the next barrier
+      } else {
+        tc_fence_after();
+        uint32_t pv[32];
+        tmem_ld_32x32(taddr + FF_T_PV + ch * 32, pv);
+        tmem_ld_wait();
+        tc_fence_before();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(pv[i]));
+      }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (!*fail_s) {
+      xch[ch * FF_BM + r] = run_l;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float l = run_l + xch[(ch ^ 1) * FF_BM + r];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int tq = q0 + r;
+      if (tq < p.Tq) {
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (((long)b * p.Tq + tq) * p.H + h) * FA_D + ch * 32);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 u;
+          __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) hh[i] = __floats2bfloat162_rn(o[jj * 8 + 2 * i] * inv, o[jj * 8 + 2 * i + 1] * inv);
+          dst[jj] = u;
+        }
+        if (p.lse && ch == 0) {
+          const float mref = (run_m == -INFINITY) ? 0.f : run_m;
+          p.lse[((long)b * p.H + h) * p.Tq + tq] = l > 0.f ? mref * p.scale + __logf(l) : -INFINITY;
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, FF_TMEM_COLS);
+  }
+}
+
+}  // namespace dl4j
+
+using namespace dl4j;
+
+// q / k / v: [B, H, T, 64] bf16 views with element strides {sb, sh, st} (head dimension contiguous, strides multiples of 8,
+// base 16-byte aligned).  out [B, Tq, H, 64] bf16 contiguous, lse [B, H, Tq] fp32, key_mask [B, Tk] fp32 or null.
+// Limits: Tk a multiple of 128.
+DL4J_API int dl4j_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const float* key_mask, int B, int H,
+                                 int Tq, int Tk, const long* q_strides, const long* k_strides, const long* v_strides, float scale,
+                                 void* stream_) {
+  if (B < 1 || H < 1 || Tq < 1 || Tk < FF_BN || Tk % FF_BN) return -DL4J_ERR_BAD_ARG;
+  CUtensorMap tq, tk, tv;
+  int r = fa_encode(&tq, q, B, H, Tq, q_strides[0], q_strides[1], q_strides[2], FF_BM);
+  if (r) return -1000 - r;
+  r = fa_encode(&tk, k, B, H, Tk, k_strides[0], k_strides[1], k_strides[2], FF_BN);
+  if (r) return -1000 - r;
+  r = fa_encode(&tv, v, B, H, Tk, v_strides[0], v_strides[1], v_strides[2], FF_BN);
+  if (r) return -1000 - r;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  FlashFwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.key_mask = key_mask;
+  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
+  p.scale = scale;
+  p.status = dl4j_status_word(dev);
+  const size_t smem = FF_TILE * (1 + FF_SLOTS) + FF_P_BYTES + (FF_BN + 2 * FF_BM + 4) * sizeof(float) + 256 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int q_blocks = (Tq + FF_BM - 1) / FF_BM;
+  flash_attn_fwd_kernel<<<B * H * q_blocks, FF_THREADS, smem, (cudaStream_t)stream_>>>(tq, tk, tv, p);
+  return (int)cudaGetLastError();
+}
