@@ -141,7 +141,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
   } else {
     const int cw = warp - 2;                        // 0..15
-    const int q = cw & 3;                           // TMEM lane quadrant
+    const int q = warp & 3;                         // TMEM lane quadrant this warp may access (warp index modulo 4)
     const int cq = cw >> 2;                         // column quarter (32 columns) owned by this thread
     const int r = q * 32 + lane;
     const int t = threadIdx.x - 64;                 // 0..511

@@ -127,7 +127,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
   } else {
     const int cw = warp - 2;                        // 0..7
-    const int q = cw & 3;                           // TMEM lane quadrant
+    const int q = warp & 3;                         // TMEM lane quadrant this warp may access (warp index modulo 4)
     const int ch = cw >> 2;                         // column half owned by this thread
     const int r = q * 32 + lane;                    // query row within the block
     const int t = threadIdx.x - 64;                 // 0..255
