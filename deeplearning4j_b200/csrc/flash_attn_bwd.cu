@@ -193,9 +193,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (row_ok) {
           float4* dst = reinterpret_cast<float4*>(p.dq + ridx * FA_D + cq * 32);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            atomicAdd(dst + j, make_float4(__uint_as_float(v0[4 * j]), __uint_as_float(v0[4 * j + 1]), __uint_as_float(v0[4 * j + 2]),
-                                           __uint_as_float(v0[4 * j + 3])));
+          for (int j = 0; j < 8; ++j)      // fire-and-forget 16-byte reductions at L2
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(v0[4 * j]), "r"(v0[4 * j + 1]),
+                         "r"(v0[4 * j + 2]), "r"(v0[4 * j + 3])
+                         : "memory");
         }
       }
     }
@@ -259,5 +260,77 @@ DL4J_API int dl4j_flash_attn_bwd(const void* q, const void* k, const void* v, co
   cudaError_t e = cudaFuncSetAttribute(flash_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   flash_attn_bwd_kernel<<<B * H * (Tk / FB_BLK), FB_THREADS, smem, (cudaStream_t)stream_>>>(tq, tk, tv, tdo, p);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------ small helpers of the backward pass
+namespace dl4j {
+
+// dvec[b, h, t] = sum_d dO[b, h, t, d] * O[b, t, h, d]; eight threads per row, 8 elements each
+__global__ void __launch_bounds__(256)
+attn_dvec_kernel(const __nv_bfloat16* __restrict__ dO, long sb, long sh, long st, const __nv_bfloat16* __restrict__ O, float* __restrict__ dvec,
+                 int B, int H, int T) {
+  const long rows = (long)B * H * T;
+  const long g = blockIdx.x * 256L + threadIdx.x;
+  const long row = g >> 3;
+  const int part = (int)(g & 7);
+  float acc = 0.f;
+  if (row < rows) {
+    const int t = (int)(row % T);
+    const int h = (int)((row / T) % H);
+    const int b = (int)(row / ((long)T * H));
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(dO + b * sb + h * sh + t * st) + part);
+    const uint4 c = __ldg(reinterpret_cast<const uint4*>(O + (((long)b * T + t) * H + h) * FA_D) + part);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(ch[i]);
+      acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+    }
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (row < rows && part == 0) dvec[row] = acc;
+}
+
+// dq (bf16, addressed base + b * o_bs + t * o_ts + h * 64) = acc [B, H, T, 64] fp32; the accumulator is cleared for its next use
+__global__ void __launch_bounds__(256)
+attn_dq_finish_kernel(float* __restrict__ acc, __nv_bfloat16* __restrict__ out, long o_bs, long o_ts, int B, int H, int T) {
+  const long n8 = (long)B * H * T * (FA_D / 8);
+  for (long g = blockIdx.x * 256L + threadIdx.x; g < n8; g += (long)gridDim.x * 256) {
+    const int part = (int)(g & 7);
+    const long row = g >> 3;
+    const int t = (int)(row % T);
+    const int h = (int)((row / T) % H);
+    const int b = (int)(row / ((long)T * H));
+    float4* src = reinterpret_cast<float4*>(acc) + 2 * g;
+    const float4 x = src[0], y = src[1];
+    uint4 u;
+    __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&u);
+    hh[0] = __floats2bfloat162_rn(x.x, x.y); hh[1] = __floats2bfloat162_rn(x.z, x.w);
+    hh[2] = __floats2bfloat162_rn(y.x, y.y); hh[3] = __floats2bfloat162_rn(y.z, y.w);
+    reinterpret_cast<uint4*>(out + b * o_bs + t * o_ts + (long)h * FA_D)[part] = u;
+    src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+}  // namespace dl4j
+
+DL4J_API int dl4j_attn_dvec(const void* dout, const long* do_strides, const void* out, float* dvec, int B, int H, int T, void* stream) {
+  const long threads = (long)B * H * T * 8;
+  attn_dvec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dout), do_strides[0], do_strides[1], do_strides[2], reinterpret_cast<const __nv_bfloat16*>(out),
+      dvec, B, H, T);
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_attn_dq_finish(float* acc, void* out, long o_bs, long o_ts, int B, int H, int T, void* stream) {
+  const long n8 = (long)B * H * T * 8;
+  long blocks = (n8 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  attn_dq_finish_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(acc, reinterpret_cast<__nv_bfloat16*>(out), o_bs, o_ts, B, H, T);
   return (int)cudaGetLastError();
 }

@@ -148,6 +148,7 @@ def attention(q, k, v, mask, scale):
 
 
 _LONG3 = ctypes.c_long * 3
+_DQ_ACC = {}
 USE_FLASH = True      # False: batched GEMMs + separate softmax kernels with a materialised score matrix (cross-check path)
 
 
@@ -158,14 +159,26 @@ def _flash_backward(ctx, dO):
         lp = ctypes.POINTER(ctypes.c_long)
         l.dl4j_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, lp, ctypes.c_long, ctypes.c_long, f32, vp]
         l.dl4j_flash_attn_bwd.restype = ctypes.c_int
+        l.dl4j_attn_dvec.argtypes = [vp, lp, vp, vp, i32, i32, i32, vp]
+        l.dl4j_attn_dvec.restype = ctypes.c_int
+        l.dl4j_attn_dq_finish.argtypes = [vp, vp, ctypes.c_long, ctypes.c_long, i32, i32, i32, vp]
+        l.dl4j_attn_dq_finish.restype = ctypes.c_int
         l.dl4j_flash_attn_bwd._typed = True
     q, k, v, O, lse, mk = ctx.saved_tensors
     Bn, H, Tq, D = q.shape
     Tk = k.shape[2]
     dO = _prep(dO)                                           # [B, H, Tq, D] view
+    def st(t):
+        return _LONG3(t.stride(0), t.stride(1), t.stride(2))
     # D_r = sum_d dO * O per query row, laid out like the log-sum-exp
-    dvec = (dO.permute(0, 2, 1, 3).float() * O.float()).sum(-1).permute(0, 2, 1).contiguous()
-    dq_acc = torch.zeros((Bn, H, Tq, D), dtype=torch.float32, device=q.device)
+    dvec = torch.empty((Bn, H, Tq), dtype=torch.float32, device=q.device)
+    rc = l.dl4j_attn_dvec(native._ptr(dO), st(dO), native._ptr(O), native._ptr(dvec), Bn, H, Tq, native._stream())
+    native._check(rc, "dl4j_attn_dvec")
+    # fp32 dQ accumulator: allocated zeroed once per shape, the finishing kernel clears it again after reading it
+    key = (q.device, Bn, H, Tq)
+    dq_acc = _DQ_ACC.get(key)
+    if dq_acc is None:
+        dq_acc = _DQ_ACC[key] = torch.zeros((Bn, H, Tq, D), dtype=torch.float32, device=q.device)
     same_len = Tq == Tk
     if same_len:
         # one packed [B, T, 3, H, D] gradient buffer, so the gradient of the fused q/k/v projection is a plain view
@@ -176,13 +189,12 @@ def _flash_backward(ctx, dO):
         dk_t = torch.empty((Bn, Tk, H, D), dtype=q.dtype, device=q.device)
         dv_t = torch.empty((Bn, Tk, H, D), dtype=q.dtype, device=q.device)
 
-    def st(t):
-        return _LONG3(t.stride(0), t.stride(1), t.stride(2))
     rc = l.dl4j_flash_attn_bwd(native._ptr(q), native._ptr(k), native._ptr(v), native._ptr(dO), native._ptr(lse), native._ptr(dvec),
                                native._ptr(mk), native._ptr(dq_acc), native._ptr(dk_t), native._ptr(dv_t), Bn, H, Tq, Tk,
                                st(q), st(k), st(v), st(dO), dk_t.stride(0), dk_t.stride(1), float(ctx.scale), native._stream())
     native._check(rc, "dl4j_flash_attn_bwd")
-    dq_t.copy_(dq_acc.permute(0, 2, 1, 3))
+    rc = l.dl4j_attn_dq_finish(native._ptr(dq_acc), native._ptr(dq_t), dq_t.stride(0), dq_t.stride(1), Bn, H, Tq, native._stream())
+    native._check(rc, "dl4j_attn_dq_finish")
     return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None
 
 
