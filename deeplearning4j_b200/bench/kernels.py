@@ -144,6 +144,25 @@ def bench_attention(t, small, rows):
     fl = 4.0 * B * H * T * T * D
     rows.append({"kernel": "attention fwd (QK^T, softmax, PV)", "shape": f"B{B} H{H} T{T} D{D}", "ms": ms, "tflops": fl / ms / 1e9,
                  "library_ms": ref, "library_tflops": fl / ref / 1e9})
+    # backward through autograd on a packed [B, T, 3, H, D] projection buffer, as the multi-head layer produces it
+    qkv = (torch.randn(B, T, 3, H, D, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    qq, kk, vv = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    do = torch.randn(B, H, T, D, device="cuda").bfloat16()
+    o = native.attention(qq, kk, vv, None, D ** -0.5)
+
+    def bwd():
+        qkv.grad = None
+        o.backward(do, retain_graph=True)
+    ms_b = t(bwd)
+    q2, k2, v2 = (x.detach().clone().requires_grad_(True) for x in (q, k, v))
+    o2 = torch.nn.functional.scaled_dot_product_attention(q2, k2, v2)
+
+    def bwd_ref():
+        q2.grad = k2.grad = v2.grad = None
+        o2.backward(do, retain_graph=True)
+    ref_b = t(bwd_ref)
+    rows.append({"kernel": "attention bwd (dQ, dK, dV; autograd)", "shape": f"B{B} H{H} T{T} D{D}", "ms": ms_b, "tflops": 2.5 * fl / ms_b / 1e9,
+                 "library_ms": ref_b, "library_tflops": 2.5 * fl / ref_b / 1e9})
 
 
 KERNELS = {"gemm": bench_gemm, "layer_norm": bench_layer_norm, "softmax_xent": bench_softmax_xent, "updater": bench_updater,
