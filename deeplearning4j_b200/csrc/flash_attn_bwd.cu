@@ -105,18 +105,25 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       bool ok = mbar_wait_bounded(kv_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
       const uint32_t ak = smem_u32(k_s), av = smem_u32(v_s), ap = smem_u32(p_s), ads = smem_u32(ds_s);
       const uint64_t dk_k = make_smem_desc_sw128(ak, 16, 1024), dv_k = make_smem_desc_sw128(av, 16, 1024);
-      for (int i = 0; i < nq && ok; ++i) {
+      // S_i = Q_i K_j^T and dP_i = dO_i V_j^T; issued one block ahead so that they overlap the threads' work on block i - 1
+      auto issue_s = [&](int i) -> bool {
         const int st = i & 1;
-        if (!mbar_wait_bounded(&qdo_full[st], (uint32_t)((i >> 1) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        if (!mbar_wait_bounded(&qdo_full[st], (uint32_t)((i >> 1) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint32_t aq = smem_u32(q_s + st * FB_TILE), ado = smem_u32(do_s + st * FB_TILE);
-        const uint64_t dq_k = make_smem_desc_sw128(aq, 16, 1024), ddo_k = make_smem_desc_sw128(ado, 16, 1024);
+        const uint64_t dq_k = make_smem_desc_sw128(smem_u32(q_s + st * FB_TILE), 16, 1024);
+        const uint64_t ddo_k = make_smem_desc_sw128(smem_u32(do_s + st * FB_TILE), 16, 1024);
 #pragma unroll
         for (int k = 0; k < FA_D / 16; ++k) {
           umma_f16(tmem_base + T_S, dq_k + ((uint64_t)(k * 32) >> 4), dk_k + ((uint64_t)(k * 32) >> 4), id_s, k > 0 ? 1u : 0u);
           umma_f16(tmem_base + T_DP, ddo_k + ((uint64_t)(k * 32) >> 4), dv_k + ((uint64_t)(k * 32) >> 4), id_s, k > 0 ? 1u : 0u);
         }
         umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int i = 0; i < nq && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t aq = smem_u32(q_s + st * FB_TILE), ado = smem_u32(do_s + st * FB_TILE);
         if (!mbar_wait_bounded(p_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         if (!mbar_wait_bounded(dq_empty, (uint32_t)((i & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
@@ -136,6 +143,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         umma_commit(&qdo_empty[st]);
         umma_commit(dq_full);
+        // S / dP of block i were read out of tensor memory before p_full(i) completed, so block i + 1 may overwrite them now
+        if (i + 1 < nq) ok = issue_s(i + 1);
       }
       if (ok) umma_commit(fin_full);
     }
@@ -151,12 +160,19 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const float k2 = p.scale * FA_LOG2E;
     const float* mk = mask_s + cq * 32;
     bool ok = true;
+    const long rbase = ((long)b * p.H + h) * p.Tq;
+    // per-row log-sum-exp and D of the next query block are fetched one block ahead (+inf: exp2(-inf) = 0 past the end)
+    float lse_n = r < p.Tq ? p.lse[rbase + r] : INFINITY, dv_n = r < p.Tq ? p.dvec[rbase + r] : 0.f;
     for (int i = 0; i < nq && ok; ++i) {
       const int tq = i * FB_BLK + r;
       const bool row_ok = tq < p.Tq;
-      const long ridx = ((long)b * p.H + h) * p.Tq + tq;
-      const float lse = row_ok ? p.lse[ridx] : INFINITY;          // +inf: exp2(-inf) = 0 for rows past the end
-      const float dv_r = row_ok ? p.dvec[ridx] : 0.f;
+      const long ridx = rbase + tq;
+      const float lse = lse_n, dv_r = dv_n;
+      if (i + 1 < nq) {
+        const int tn = tq + FB_BLK;
+        lse_n = tn < p.Tq ? p.lse[rbase + tn] : INFINITY;
+        dv_n = tn < p.Tq ? p.dvec[rbase + tn] : 0.f;
+      }
       const float lse2 = lse * FA_LOG2E;
       const bool live = lse != -INFINITY;
       if (!mbar_wait_bounded(s_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
