@@ -107,7 +107,7 @@ class LSTM(BaseRecurrentLayer):
         zx = nnops.linear(xt.reshape(T * mb, -1), W, b).reshape(T, mb, 4 * n)
         gate, act = self.gateActivationFn, self.activation
         plain = isinstance(gate, ActivationSigmoid) and isinstance(act, ActivationTanH) and not self.PEEPHOLE
-        if plain and mask is None and c.dtype == torch.float32:
+        if plain and mask is None and c.dtype == torch.float32 and not nnops._FORCE_TORCH:
             from ...ops import native as nat
             if nat.lstm_seq_supported(zx, n, mb) and h.dtype == zx.dtype:
                 # whole sequence in one persistent kernel (recurrent weights resident on chip)
