@@ -79,7 +79,7 @@ class BaseRunner:
         value = work / (per_step / 1e3)
         e2e_value = work / (ms_e2e / a.steps / 1e3)
         cfg = self.config()
-        cfg["l2_policy"] = "inputs+weights+activations per step exceed the 126 MB L2 (no explicit flush)"
+        cfg["l2_policy"] = getattr(self, "l2_policy", "inputs+weights+activations per step exceed the 126 MB L2 (no explicit flush)")
         return {"metric": self.metric, "value": value, "unit": self.unit, "ms_per_step": per_step,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": cfg, "clocks": clocks,
