@@ -42,3 +42,28 @@ def test_single_op_cases_and_coverage():
     assert "differs" in OpValidation.validate(OpTestCase("add", [x, x]).expectedOutput(0, x))
     cov = OpValidation.coverage()
     assert cov["validated"] >= 10 and cov["total"] > 500 and "Op validation coverage" in OpValidation.logCoverageInformation()
+
+
+def test_graph_optimizer_folds_constants_removes_identities_and_unused_ops():
+    import numpy as np
+    from deeplearning4j_b200 import DataType, Nd4j
+    from deeplearning4j_b200.samediff import SameDiff
+    from deeplearning4j_b200.samediff.optimize import GraphOptimizer
+    sd = SameDiff.create()
+    x = sd.placeHolder("x", DataType.FLOAT, -1, 3)
+    c1 = sd.constant("c1", Nd4j.create([1.0, 2.0, 3.0]))
+    c2 = sd.constant("c2", Nd4j.create([10.0, 20.0, 30.0]))
+    folded = c1.mul(c2).add(c1)                       # constants only: becomes one constant
+    y = x.add(0.0).mul(1.0)                          # identities
+    y = sd.math.neg(sd.math.neg(y))
+    out = y.add(folded).rename("out")
+    unused = sd.math.exp(x).rename("unused")          # does not reach the output
+    n_before = len(sd.ops)
+    opt = GraphOptimizer.optimize(sd, "out")
+    assert len(opt.ops) == 1 and opt.ops[0].opName == "add" and len(sd.ops) == n_before      # original untouched
+    assert "unused" not in opt.variables
+    xv = np.random.default_rng(0).normal(size=(4, 3)).astype(np.float32)
+    a = sd.output({"x": Nd4j.create(xv)}, "out")["out"].numpy()
+    b = opt.output({"x": Nd4j.create(xv)}, "out")["out"].numpy()
+    np.testing.assert_allclose(a, b, rtol=1e-6)
+    np.testing.assert_allclose(b, xv + np.array([11.0, 42.0, 93.0], dtype=np.float32), rtol=1e-6)
