@@ -99,3 +99,40 @@ def test_serde_extras_round_trips(tmp_path):
     assert torch.equal(Nd4jBase64.fromNpyBase64(Nd4jBase64.base64StringNumpy(x)).t, x.t)
     assert torch.equal(NDArrayTextSerializer.fromJson(NDArrayTextSerializer.toJson(x)).t, x.t)
     assert torch.equal(ArrowSerde.fromBytes(ArrowSerde.toBytes(x)).t, x.t)
+
+
+def test_common_primitives_lifecycle_tracker_and_parallel_loops():
+    import torch
+    from deeplearning4j_b200.utils.common import AtomicDouble, Counter, CounterMap, Pair, Preconditions, Triple
+    from deeplearning4j_b200.utils.lifecycle import LifecycleTracker
+    from deeplearning4j_b200.utils import threads
+    p = Pair.of(1, "a")
+    assert p.getFirst() == 1 and p.getSecond() == "a" and p == Pair(1, "a") and tuple(Triple.of(1, 2, 3)) == (1, 2, 3)
+    c = Counter()
+    for w in "a b a c a b".split():
+        c.incrementCount(w)
+    assert c.argMax() == "a" and c.totalCount() == 6 and abs(c.getProbability("b") - 1 / 3) < 1e-9 and c.keySetSorted()[0] == "a"
+    cm = CounterMap()
+    cm.incrementCount("x", "y", 2.0)
+    assert cm.getCount("x", "y") == 2.0 and cm.argMax() == Pair("x", "y")
+    ad = AtomicDouble(1.0)
+    assert ad.addAndGet(2.5) == 3.5 and ad.compareAndSet(3.5, 0.0) and ad.get() == 0.0
+    with pytest.raises(ValueError, match="bad 3"):
+        Preconditions.checkArgument(False, "bad %s", 3)
+    tr = LifecycleTracker().enable(capture_stacks=True)
+    keep = [tr.recordAllocation(torch.zeros(100)) for _ in range(3)]
+    tmp = tr.recordAllocation(torch.zeros(10))
+    before = tr.snapshot()
+    del tmp
+    assert tr.liveCount() == 3 and tr.liveBytes() == 3 * 400 and "live objects: 3" in tr.generateLeakReport()
+    keep.append(tr.recordAllocation(torch.zeros(1000)))
+    assert any("+" in line for line in LifecycleTracker.temporalReport(before, tr.snapshot())) or tr.liveCount() == 4
+    out = [0] * 100
+
+    def body(tid, a, b, step):
+        for i in range(a, b, step):
+            out[i] = i * 2
+    threads.parallel_for(body, 0, 100, 1, numThreads=4)
+    assert out == [2 * i for i in range(100)]
+    s = threads.parallel_long(lambda tid, a, b, st: sum(range(a, b, st)), lambda x, y: x + y, 0, 1000, 1, numThreads=8)
+    assert s == sum(range(1000))
