@@ -4,3 +4,4 @@ from .bert_iterator import (BertIterator, BertMaskedLMMasker, CollectionLabeledP
 from .embeddings import (InMemoryLookupTable, ParagraphVectors, SequenceVectors, VocabCache, VocabWord, Word2Vec,  # noqa: F401
                          WordVectorSerializer, build_huffman)
 from .tokenization import *  # noqa: F401,F403
+from .fasttext import FastText  # noqa: F401

@@ -1,4 +1,5 @@
 """Tokenizers, Word2Vec / ParagraphVectors training and serialisation, BertIterator."""
+import numpy as np
 import random
 
 import torch
@@ -107,3 +108,33 @@ def test_bert_iterator_unsupervised_and_classification():
     assert float(m.getLabels(0).sum()) == 5.0
     feats, masks = cls.featurizeSentencePairs([("w1 w2 w3", "w4 w5")])
     assert feats[1][0].tolist()[:7] == [0, 0, 0, 0, 0, 1, 1]
+
+
+def test_fasttext_supervised_and_subword_vectors(tmp_path):
+    from deeplearning4j_b200.nlp.fasttext import FastText
+    rng = np.random.default_rng(0)
+    animals = "cat dog horse cow sheep goat tiger lion".split()
+    tools = "hammer wrench drill saw pliers chisel ruler level".split()
+    lines = []
+    for _ in range(300):
+        if rng.random() < 0.5:
+            lines.append("__label__animal " + " ".join(rng.choice(animals, 5)))
+        else:
+            lines.append("__label__tool " + " ".join(rng.choice(tools, 5)))
+    ft = FastText(supervised=True, dim=16, epochs=20, lr=0.5, minn=2, maxn=4, bucket=2000, iterator=lines, batchSize=64, seed=1).fit()
+    assert set(ft.getLabels()) == {"animal", "tool"}
+    assert ft.predict("the cat and the lion") == "animal" and ft.predict("wrench drill saw") == "tool"
+    lab, p = ft.predictProbability("hammer chisel")
+    assert lab == "tool" and 0.5 < p <= 1.0
+    # an unseen word still gets a vector from its character n-grams, close to a word it shares most n-grams with
+    assert not ft.hasWord("hammers") and np.abs(ft.getWordVector("hammers")).sum() > 0
+    path = str(tmp_path / "ft.zip")
+    ft.saveModel(path)
+    back = FastText.loadModel(path)
+    assert back.predict("goat sheep cow") == "animal"
+    np.testing.assert_allclose(back.getWordVector("cat"), ft.getWordVector("cat"))
+    # skip-gram mode trains word + sub-word vectors; words that share contexts end up closer than unrelated ones
+    corpus = [" ".join(rng.choice(animals, 8)) for _ in range(200)] + [" ".join(rng.choice(tools, 8)) for _ in range(200)]
+    sg = FastText(skipgram=True, dim=24, epochs=8, lr=0.1, minn=0, maxn=0, iterator=corpus, batchSize=512, negativeSamples=5, seed=3).fit()
+    assert sg.similarity("cat", "dog") > sg.similarity("cat", "wrench")
+    assert len(sg.wordsNearest("hammer", 3)) == 3
