@@ -218,3 +218,31 @@ def test_equality_and_distance_helpers():
     assert abs(a.distance2(Nd4j.zeros(3)) - np.sqrt(14.0)) < 1e-5
     assert abs(a.distance1(Nd4j.zeros(3)) - 6.0) < 1e-6
     assert abs(a.squaredDistance(Nd4j.zeros(3)) - 14.0) < 1e-5
+
+
+def test_counter_based_random_generator_matches_scalar_arithmetic():
+    from deeplearning4j_b200.nd.rng import RandomGenerator
+    root, node = 119, 5
+    g = RandomGenerator(root, node)
+    M64, M32 = (1 << 64) - 1, (1 << 32) - 1
+
+    def x32(index):                                   # the stream definition written out with Python integers
+        s0 = root | (((index + 2) * (node + 24243287)) & M64)
+        s1 = node ^ (((index + 2) * (s0 + 723829)) & M64)
+        half = (s1 ^ s0) & M32
+        x = (half * 0x9E3779BB) & M32
+        x = ((x << 5) | (x >> 27)) & M32
+        return (x * 5) & M32
+    idx = np.array([0, 1, 2, 1000, 123456789], dtype=np.uint64)
+    assert g.xoroshiro32(idx).tolist() == [x32(int(i)) for i in idx]
+    f = g.relativeFloat(idx)
+    want = [np.frombuffer(np.uint32(0x3F800000 | (x32(int(i)) >> 9)).tobytes(), dtype=np.float32)[0] - np.float32(1.0) for i in idx]
+    np.testing.assert_array_equal(f, np.array(want, dtype=np.float32))
+    u = g.uniform((20000,), 2.0, 4.0)
+    assert float(u.min()) >= 2.0 and float(u.max()) < 4.0 and abs(float(u.mean()) - 3.0) < 0.05
+    state_after = g.nodeState()
+    g2 = RandomGenerator(root, node)
+    g2.uniform((20000,), 2.0, 4.0)
+    assert g2.nodeState() == state_after != node                       # consuming values advances the node state deterministically
+    d = g.relativeDouble(np.arange(1000, dtype=np.uint64))
+    assert d.min() >= 0.0 and d.max() < 1.0 and 0.4 < d.mean() < 0.6
