@@ -67,3 +67,41 @@ def test_graph_optimizer_folds_constants_removes_identities_and_unused_ops():
     b = opt.output({"x": Nd4j.create(xv)}, "out")["out"].numpy()
     np.testing.assert_allclose(a, b, rtol=1e-6)
     np.testing.assert_allclose(b, xv + np.array([11.0, 42.0, 93.0], dtype=np.float32), rtol=1e-6)
+
+
+def test_op_log_listener_finds_first_divergence(tmp_path):
+    import numpy as np
+    from deeplearning4j_b200 import DataType, Nd4j
+    from deeplearning4j_b200.contrib import OpLogAnalyzer, OpLogListener
+    from deeplearning4j_b200.samediff import SameDiff
+
+    def build(scale):
+        sd = SameDiff.create()
+        x = sd.placeHolder("x", DataType.FLOAT, -1, 3)
+        w = sd.var("w", Nd4j.create(np.eye(3, dtype=np.float32) * scale))
+        h = x.mmul(w).rename("h")
+        sd.math.tanh(h).rename("t").sum().rename("s")
+        return sd
+    xv = Nd4j.create(np.arange(6, dtype=np.float32).reshape(2, 3))
+    paths = []
+    for i, scale in enumerate((1.0, 1.0, 1.5)):
+        p = str(tmp_path / f"log{i}.db")
+        sd = build(scale)
+        lst = OpLogListener(p)
+        sd.addListeners(lst)
+        sd.output({"x": xv}, "s")
+        lst.close()
+        paths.append(p)
+    same = OpLogAnalyzer.compare(paths[0], paths[1])
+    assert same["first_divergence"] is None and not same["missing_in_b"]
+    diff = OpLogAnalyzer.compare(paths[0], paths[2])
+    assert diff["first_divergence"]["op"] in ("matmul", "mmul") and len(diff["diverged"]) == 3
+    assert {op for op, n, ms in OpLogAnalyzer.summary(paths[0])} >= {"tanh", "reduce_sum"}
+
+
+def test_ops_benchmark_suite_runs_on_cpu():
+    from deeplearning4j_b200.bench import ops_suite
+    rows = ops_suite.run("light", "cpu", filt="transform/exp", iters=2, warmup=1)
+    assert len(rows) == 2 and all(r["ms"] > 0 and r["gbs"] > 0 for r in rows)
+    rows = ops_suite.run("light", "cpu", filt="blas/matmul", iters=1, warmup=1)
+    assert rows and "gflops" in rows[0]
