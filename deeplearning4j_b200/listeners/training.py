@@ -252,7 +252,7 @@ class CheckpointListener(TrainingListener):
     ``checkpointInfo.txt`` index; retention keep-all / keep-last-N / keep-last-N-and-every-M."""
 
     def __init__(self, rootDir, saveEveryNIterations=None, saveEveryNEpochs=None, saveEveryMs=None, saveEverySinceLast=True,
-                 keepMode="ALL", keepLast=0, keepEvery=0, logSaving=True, deleteExisting=False, saveUpdater=True):
+                 keepMode="ALL", keepLast=0, keepEvery=0, logSaving=True, deleteExisting=False, saveUpdater=True, continueExisting=False):
         self.rootDir = str(rootDir)
         os.makedirs(self.rootDir, exist_ok=True)
         self.saveEveryNIterations, self.saveEveryNEpochs, self.saveEveryMs = saveEveryNIterations, saveEveryNEpochs, saveEveryMs
@@ -266,10 +266,14 @@ class CheckpointListener(TrainingListener):
                 p = os.path.join(self.rootDir, f)
                 if os.path.exists(p):
                     os.remove(p)
-        elif any(f.endswith(".zip") for f in existing):
+        elif any(f.endswith(".zip") for f in existing) and not continueExisting:
             raise ValueError(f"Checkpoint directory {self.rootDir} already holds checkpoints; use deleteExisting(true) or another directory")
         self.checkpoints = []
         self.lastCheckpointNum = -1
+        if continueExisting and os.path.exists(self.recordFile):
+            # a resumed job keeps numbering (and pruning) where the previous one stopped
+            self.checkpoints = CheckpointListener.availableCheckpoints(self.rootDir)
+            self.lastCheckpointNum = max((c.checkpointNum for c in self.checkpoints), default=-1)
         self.startTime = self.lastSaveTime = None
         self.startIter = None
 
@@ -289,6 +293,7 @@ class CheckpointListener(TrainingListener):
         def logSaving(self, b): self.kw["logSaving"] = b; return self
         def deleteExisting(self, b): self.kw["deleteExisting"] = b; return self
         def saveUpdater(self, b): self.kw["saveUpdater"] = b; return self
+        def continueExisting(self, b=True): self.kw["continueExisting"] = b; return self
         def build(self):
             if not any(self.kw.get(k) for k in ("saveEveryNIterations", "saveEveryNEpochs", "saveEveryMs")):
                 raise ValueError("Cannot construct listener: no models will be saved (must use at least one of: save every N iter, N epochs or time)")
