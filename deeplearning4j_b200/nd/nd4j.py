@@ -340,6 +340,22 @@ class Nd4j:
     def exec(cls, op, *a, **kw):
         return cls.getExecutioner().exec(op, *a, **kw)
 
+    # ------------------------------------------------------------------ op execution trace (Nd4j.toggleTrace / collectTrace)
+    @classmethod
+    def toggleTrace(cls, on=True):
+        from ..ops import registry
+        registry.toggle_trace(on)
+
+    @classmethod
+    def purgeTrace(cls):
+        from ..ops import registry
+        registry.purge_traces()
+
+    @classmethod
+    def listTraces(cls):
+        from ..ops import registry
+        return list(registry.TRACES)
+
     # ------------------------------------------------------------------ serde
     @classmethod
     def write(cls, arr, out):

@@ -62,8 +62,39 @@ def has(name: str) -> bool:
     return name in REGISTRY
 
 
+# ----------------------------------------------------------------------------- execution trace
+# ``NativeOps.toggleOpTrace / listOpTraces / purgeOpTrace`` + ``OpExecTrace``: while tracing is on, every eagerly executed op
+# is recorded with its arguments and the identity of its input / output arrays, from which ``SameDiff.collectTrace`` rebuilds a graph.
+TRACE_ON = False
+TRACES = []
+
+
+class OpExecTrace:
+    def __init__(self, opName, inputs, outputs, args):
+        self.opName, self.inputs, self.outputs, self.args = opName, inputs, outputs, args
+
+    def inputShapes(self): return [tuple(t.shape) if hasattr(t, "shape") else None for t in self.inputs]
+    def outputShapes(self): return [tuple(t.shape) if hasattr(t, "shape") else None for t in self.outputs]
+
+    def __repr__(self):
+        return f"OpExecTrace({self.opName}, in={self.inputShapes()}, out={self.outputShapes()}, args={self.args})"
+
+
+def toggle_trace(on: bool):
+    global TRACE_ON
+    TRACE_ON = bool(on)
+
+
+def purge_traces():
+    TRACES.clear()
+
+
 def execute(name: str, inputs, **kwargs):
-    return get(name).fn(*inputs, **kwargs)
+    res = get(name).fn(*inputs, **kwargs)
+    if TRACE_ON:
+        outs = list(res) if isinstance(res, (tuple, list)) else [res]
+        TRACES.append(OpExecTrace(name, list(inputs), outs, dict(kwargs)))
+    return res
 
 
 def names():

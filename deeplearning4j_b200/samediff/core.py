@@ -486,6 +486,34 @@ class SameDiff:
         self._exec_plan = None
         return outs[0] if n == 1 else outs
 
+    @staticmethod
+    def collectTrace(traces=None):
+        """Rebuild a graph from eagerly executed ops (``SameDiff.collectTrace``): arrays produced by one traced op and consumed by a
+        later one become edges, every other input becomes a constant holding the value it had."""
+        from ..ops import registry as reg
+        traces = list(reg.TRACES) if traces is None else list(traces)
+        sd = SameDiff.create()
+        known = {}                                   # id(tensor) -> SDVariable
+        keep = []                                    # keeps traced tensors alive so ids stay unique
+        for tr in traces:
+            ins = []
+            for t in tr.inputs:
+                if t is None:
+                    ins.append(None)
+                    continue
+                v = known.get(id(t))
+                if v is None:
+                    v = sd.constant(None, t.detach() if isinstance(t, torch.Tensor) else t)
+                    known[id(t)] = v
+                    keep.append(t)
+                ins.append(v)
+            outs = sd._op(tr.opName, ins, n_out=len(tr.outputs), **tr.args)
+            outs = outs if isinstance(outs, list) else [outs]
+            for o, t in zip(outs, tr.outputs):
+                known[id(t)] = o
+                keep.append(t)
+        return sd
+
     def invokeGraphOn(self, other):
         for n, v in self.variables.items():
             if n not in other.variables:

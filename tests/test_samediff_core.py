@@ -132,3 +132,26 @@ def test_convert_constant_variable_and_dup():
     c = sd.dup()
     c.getVariable("w").getArr().addi(1.0)
     assert float(sd.getVariable("w").getArr().sumNumber()) == 4.0
+
+
+def test_execution_trace_is_collected_into_a_graph():
+    from deeplearning4j_b200.ops import registry
+    Nd4j.purgeTrace()
+    Nd4j.toggleTrace(True)
+    try:
+        a = torch.tensor([[1.0, -2.0], [3.0, 4.0]])
+        b = registry.execute("abs", [a])
+        c = registry.execute("matmul", [b, a], transposeY=True)
+        d = registry.execute("reduce_sum", [c], dimensions=[1])
+    finally:
+        Nd4j.toggleTrace(False)
+    traces = Nd4j.listTraces()
+    assert [t.opName for t in traces] == ["abs", "matmul", "reduce_sum"] and traces[1].args == {"transposeY": True}
+    sd = SameDiff.collectTrace()
+    assert [o.opName for o in sd.ops] == ["abs", "matmul", "reduce_sum"]
+    out = sd.output({}, sd.ops[-1].outputs[0])[sd.ops[-1].outputs[0]]
+    np.testing.assert_allclose(out.numpy(), d.numpy())
+    registry.execute("abs", [a])
+    assert len(Nd4j.listTraces()) == 3                   # tracing is off again
+    Nd4j.purgeTrace()
+    assert not Nd4j.listTraces()
