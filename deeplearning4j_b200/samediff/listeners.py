@@ -232,6 +232,8 @@ class ProfilingListener(Listener):
         if cuda:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
+            if getattr(self, "nvtx", True):
+                torch.cuda.nvtx.range_push(f"{op.opName}:{op.name}")        # named range per op for external profilers
         self._open[id(op)] = (ev, time.perf_counter())
 
     def opExecution(self, sd, op, outputs):
@@ -239,6 +241,8 @@ class ProfilingListener(Listener):
         if st is None:
             return
         ev0, t_host = st
+        if ev0 is not None and getattr(self, "nvtx", True):
+            torch.cuda.nvtx.range_pop()
         shapes = [list(o.shape) for o in outputs if isinstance(o, torch.Tensor)]
         args = {"op": op.opName, "inputs": [i for i in op.inputs if i is not None], "outputs": list(op.outputs), "output shapes": shapes}
         if ev0 is not None:
