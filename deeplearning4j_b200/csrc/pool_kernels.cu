@@ -194,3 +194,53 @@ DL4J_API int dl4j_subsample(const void* in, void* out, const int* shape, int bac
   }
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------ convolution weight layouts
+// DL4J keeps convolution kernels as fp32 [O, I, kH, kW] ('c' order); the tensor-core convolution kernels want bf16 [O, kH, kW, I]
+// (channels-last).  Forward: one cast + relayout pass.  Backward: the channels-last bf16 weight gradient is added into the fp32
+// [O, I, kH, kW] gradient buffer in one pass.
+namespace dl4j {
+
+__global__ void __launch_bounds__(256)
+conv_weight_to_cl_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int O, int I, int S) {
+  // out[o][s][i] = w[o][i][s], S = kH * kW
+  const long total = (long)O * I * S;
+  for (long g = blockIdx.x * 256L + threadIdx.x; g < total; g += (long)gridDim.x * 256) {
+    const int i = (int)(g % I);
+    const int s = (int)((g / I) % S);
+    const long o = g / ((long)I * S);
+    out[g] = __float2bfloat16(w[(o * I + i) * S + s]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+conv_wgrad_from_cl_kernel(const __nv_bfloat16* __restrict__ g_cl, float* __restrict__ grad, int O, int I, int S) {
+  // grad[o][i][s] += g_cl[o][s][i]; threads walk the destination so that the read-modify-write is coalesced
+  const long total = (long)O * I * S;
+  for (long g = blockIdx.x * 256L + threadIdx.x; g < total; g += (long)gridDim.x * 256) {
+    const int s = (int)(g % S);
+    const int i = (int)((g / S) % I);
+    const long o = g / ((long)I * S);
+    grad[g] += __bfloat162float(g_cl[(o * S + s) * I + i]);
+  }
+}
+
+}  // namespace dl4j
+
+DL4J_API int dl4j_conv_weight_to_cl(const float* w, void* out, int O, int I, int S, void* stream) {
+  const long total = (long)O * I * S;
+  if (total <= 0) return -DL4J_ERR_BAD_ARG;
+  long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  conv_weight_to_cl_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(w, reinterpret_cast<__nv_bfloat16*>(out), O, I, S);
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_conv_wgrad_from_cl(const void* g_cl, float* grad, int O, int I, int S, void* stream) {
+  const long total = (long)O * I * S;
+  if (total <= 0) return -DL4J_ERR_BAD_ARG;
+  long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  conv_wgrad_from_cl_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(g_cl), grad, O, I, S);
+  return (int)cudaGetLastError();
+}

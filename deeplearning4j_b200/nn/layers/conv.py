@@ -131,7 +131,14 @@ class ConvolutionLayer(FeedForwardLayer):
                 if z is not None:
                     z = self.activation(z, training)
                     return z.permute(0, 2, 3, 1) if nhwc else z
-        W = p["W"].to(x.dtype) if p["W"].dtype != x.dtype else p["W"]
+        W = None
+        if x.is_cuda and x.dtype == torch.bfloat16 and type(self) is ConvolutionLayer:
+            from ...ops import native as nat
+            from ...ops import nnops as _nn
+            if not _nn._FORCE_TORCH:
+                W = nat.conv_weight_cl(p["W"])          # cast + channels-last relayout in one pass, gradient added in place
+        if W is None:
+            W = p["W"].to(x.dtype) if p["W"].dtype != x.dtype else p["W"]
         b = p["b"].reshape(-1).to(x.dtype) if self.hasBias and not skip_bias else None
         x, pad = _pad_for_mode(x, self.kernelSize, self.stride, self.padding, self.dilation, self._mode())
         if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.shape[1] < 8 and x.dim() == 4:

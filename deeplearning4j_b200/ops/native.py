@@ -66,6 +66,8 @@ def _load():
             "dl4j_maxpool_fwd": [vp, vp, vp, vp, vp],
             "dl4j_maxpool_bwd": [vp, vp, vp, vp, vp],
             "dl4j_subsample": [vp, vp, vp, i32, vp],
+            "dl4j_conv_weight_to_cl": [vp, vp, i32, i32, i32, vp],
+            "dl4j_conv_wgrad_from_cl": [vp, vp, i32, i32, i32, vp],
             "dl4j_read_status": [i32],
             "dl4j_num_sms": [],
             "dl4j_bind_device": [i32],
@@ -614,6 +616,41 @@ def lstm_seq(zx, rw, h0, c0, reverse=False):
     if rw_lp is None or rw_lp.dtype != zx.dtype:
         rw_lp = rw.detach() if rw.dtype == zx.dtype else rw.detach().to(zx.dtype)
     return _LstmSeqFn.apply(zx, rw, h0, c0, reverse, rw_lp)
+
+
+class _ConvWeightFn(torch.autograd.Function):
+    """fp32 [O, I, kH, kW] convolution kernel -> bf16 channels-last view for the tensor-core convolution kernels (one cast +
+    relayout pass); the channels-last weight gradient is added straight into the fp32 gradient buffer of the parameter."""
+
+    @staticmethod
+    def forward(ctx, W):
+        l = require()
+        O, I, kH, kW = W.shape
+        buf = torch.empty((O, kH, kW, I), dtype=torch.bfloat16, device=W.device)
+        Wm = getattr(W, "_master", W)
+        rc = l.dl4j_conv_weight_to_cl(_ptr(Wm.detach().contiguous()), _ptr(buf), O, I, kH * kW, _stream())
+        _check(rc, "dl4j_conv_weight_to_cl")
+        ctx.W_ref = Wm
+        return buf.permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dW):
+        l = require()
+        W = ctx.W_ref
+        O, I, kH, kW = W.shape
+        g_cl = dW.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        tgt = W.grad if (W.is_leaf and W.grad is not None and W.grad.dtype == torch.float32 and W.grad.is_contiguous()) else None
+        out = tgt if tgt is not None else torch.zeros(W.shape, dtype=torch.float32, device=W.device)
+        rc = l.dl4j_conv_wgrad_from_cl(_ptr(g_cl), _ptr(out), O, I, kH * kW, _stream())
+        _check(rc, "dl4j_conv_wgrad_from_cl")
+        return None if tgt is not None else out.to(W.dtype)
+
+
+def conv_weight_cl(W):
+    """bf16 channels-last version of an fp32 convolution kernel parameter, or None when not applicable."""
+    if not (available() and W.is_cuda and W.dim() == 4 and W.dtype == torch.float32 and W.is_contiguous()):
+        return None
+    return _ConvWeightFn.apply(W)
 
 
 class _SubsampleFn(torch.autograd.Function):

@@ -77,3 +77,20 @@ def test_rgb_stem_convolution_pads_channels(nat):
     assert _rel(y, ref) < 2e-2
     y.float().sum().backward()
     assert W.grad is not None and W.grad.shape == W.shape and x.grad.shape == x.shape
+
+
+def test_conv_weight_channels_last_relayout_and_gradient(nat):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    W = torch.randn(32, 16, 3, 3, device="cuda", generator=g).requires_grad_(True)
+    W.grad = torch.zeros_like(W)
+    x = torch.randn(4, 16, 10, 10, device="cuda", generator=g).bfloat16().contiguous(memory_format=torch.channels_last)
+    Wc = nat.conv_weight_cl(W)
+    assert Wc.dtype == torch.bfloat16 and Wc.is_contiguous(memory_format=torch.channels_last)
+    assert torch.equal(Wc.float(), W.detach().bfloat16().float())
+    y = F.conv2d(x, Wc, None, padding=1)
+    w = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    (y * w).sum().backward()
+    got = W.grad.clone()
+    Wr = W.detach().clone().requires_grad_(True)
+    (F.conv2d(x.float(), Wr.bfloat16().float(), None, padding=1) * w.float()).sum().backward()
+    assert _rel(got, Wr.grad) < 3e-2
