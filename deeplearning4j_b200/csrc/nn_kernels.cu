@@ -209,6 +209,112 @@ layer_norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
   }
 }
 
+// Split form of the backward for large row counts: a lean per-row dx kernel (no column accumulators, so many warps stay resident)
+// and a column kernel for dgain / dbias that re-reads dy and x (they are L2 resident right after the first kernel when they fit).
+template <typename T, int NV>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+layer_norm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gain,
+                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx, int rows, int C) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nvec = C / 8;
+  for (int row = blockIdx.x * LN_WARPS + wid; row < rows; row += gridDim.x * LN_WARPS) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[NV][8], dg[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        Vec8<T>::load(dy + (long long)row * C + vi * 8, dg[i]);
+        Vec8<T>::load(x + (long long)row * C + vi * 8, xh[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float gn[8];
+        Vec8<float>::load(gain + vi * 8, gn);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          dg[i][j] *= gn[j];
+          s1 += dg[i][j];
+          s2 = fmaf(dg[i][j], xh[i][j], s2);
+        }
+      }
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (dg[i][j] - s1 - xh[i][j] * s2);
+        Vec8<T>::store(dx + (long long)row * C + vi * 8, o);
+      }
+    }
+  }
+}
+
+// dgain[c] += sum_r dy[r, c] * xhat[r, c], dbias[c] += sum_r dy[r, c]; block = 8 column threads (64 columns) x 32 row lanes
+template <typename T>
+__global__ void __launch_bounds__(256)
+layer_norm_bwd_cols_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean_in,
+                           const float* __restrict__ rstd_in, float* __restrict__ dgain, float* __restrict__ dbias, int rows, int C,
+                           int rows_per_block) {
+  __shared__ float red[2][32][64 + 1];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = blockIdx.x * 64 + tx * 8;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(r0 + rows_per_block, rows);
+  float sg[8], sb[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { sg[j] = 0.f; sb[j] = 0.f; }
+  if (col < C) {
+    for (int r = r0 + ty; r < r1; r += 64) {
+      float d[2][8], xv[2][8], mu[2], rs[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int rr = r + u * 32;
+        if (rr < r1) {
+          const long long o = (long long)rr * C + col;
+          Vec8<T>::load(dy + o, d[u]);
+          Vec8<T>::load(x + o, xv[u]);
+          mu[u] = mean_in[rr];
+          rs[u] = rstd_in[rr];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (r + u * 32 < r1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            sb[j] += d[u][j];
+            sg[j] = fmaf(d[u][j], (xv[u][j] - mu[u]) * rs[u], sg[j]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { red[0][ty][tx * 8 + j] = sg[j]; red[1][ty][tx * 8 + j] = sb[j]; }
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int which = threadIdx.x >> 6, cc = threadIdx.x & 63;
+    const int c = blockIdx.x * 64 + cc;
+    float* out = which == 0 ? dgain : dbias;
+    if (c < C && out) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 32; ++w) t += red[which][w][cc];
+      atomicAdd(out + c, t);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- softmax cross entropy
 // One block per row.  labels: dense probabilities (same dtype as logits) or int64 class indices.
 // loss[r] = -sum_j labels_j * log softmax_j ; grad_out (optional) = softmax * sum(labels) - labels.
@@ -376,26 +482,27 @@ bias_act_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __rest
   }
 }
 
-// Vector form for C % 8 == 0: a thread owns 8 adjacent columns (one 16-byte load per row), a warp spans 256 columns,
-// the 8 warps of a block walk rows with four independent row loads in flight per thread.
+// Vector form for C % 8 == 0: a thread owns 8 adjacent columns (one 16-byte load per row), eight threads span a 64-column
+// tile (128 contiguous bytes per row) and the block's 32 row lanes walk a long row slab with four independent row loads in
+// flight per thread; one atomicAdd per column and block at the end (about two blocks per SM, so few atomics per address).
 template <typename T>
 __global__ void __launch_bounds__(256)
 bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restrict__ dz, float* __restrict__ dbias,
                         int rows, int C, int act, int rows_per_block) {
-  __shared__ float red[8][256 + 8];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int col = blockIdx.x * 256 + tx * 8;
+  __shared__ float red[32][64 + 1];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int col = blockIdx.x * 64 + tx * 8;
   const int r0 = blockIdx.y * rows_per_block;
   const int r1 = min(r0 + rows_per_block, rows);
   float s[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) s[j] = 0.f;
   if (col < C) {
-    for (int r = r0 + ty; r < r1; r += 32) {
+    for (int r = r0 + ty; r < r1; r += 128) {
       float d[4][8], zz[4][8];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int rr = r + u * 8;
+        const int rr = r + u * 32;
         if (rr < r1) {
           const long long o = (long long)rr * C + col;
           Vec8<T>::load(dy + o, d[u]);
@@ -404,7 +511,7 @@ bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int rr = r + u * 8;
+        const int rr = r + u * 32;
         if (rr < r1) {
           if (act != 0) {
 #pragma unroll
@@ -420,12 +527,12 @@ bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __
 #pragma unroll
   for (int j = 0; j < 8; ++j) red[ty][tx * 8 + j] = s[j];
   __syncthreads();
-  if (dbias) {
-    const int c = blockIdx.x * 256 + threadIdx.x;
+  if (dbias && threadIdx.x < 64) {
+    const int c = blockIdx.x * 64 + threadIdx.x;
     if (c < C) {
       float t = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+      for (int w = 0; w < 32; ++w) t += red[w][threadIdx.x];
       atomicAdd(dbias + c, t);
     }
   }
@@ -536,9 +643,32 @@ DL4J_API int dl4j_layer_norm_fwd(const void* x, const void* res, const float* ga
 DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gain, const float* mean, const float* rstd,
                                  void* dx, float* dgain, float* dbias, int rows, int C, int dtype, void* stream) {
   if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
+  const int nv = (C + 255) / 256;
+  if (rows >= 2048) {
+    int g1 = (rows + LN_WARPS - 1) / LN_WARPS;
+    if (g1 > 148 * 4) g1 = 148 * 4;
+#define DL4J_LN_DX(NVV)                                                                                           \
+  DL4J_DISPATCH_T(dtype, (layer_norm_bwd_dx_kernel<T, NVV><<<g1, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(       \
+      (const T*)dy, (const T*)x, gain, mean, rstd, (T*)dx, rows, C)))
+    if (nv == 1) { DL4J_LN_DX(1); }
+    else if (nv == 2) { DL4J_LN_DX(2); }
+    else if (nv == 3) { DL4J_LN_DX(3); }
+    else { DL4J_LN_DX(4); }
+#undef DL4J_LN_DX
+    if (dgain || dbias) {
+      const int ct = (C + 63) / 64;
+      int slabs = (148 * 2 + ct - 1) / ct;
+      int rpb = (rows + slabs - 1) / slabs;
+      rpb = (rpb + 63) / 64 * 64;
+      slabs = (rows + rpb - 1) / rpb;
+      dim3 g2(ct, slabs);
+      DL4J_DISPATCH_T(dtype, (layer_norm_bwd_cols_kernel<T><<<g2, 256, 0, (cudaStream_t)stream>>>(
+          (const T*)dy, (const T*)x, mean, rstd, dgain, dbias, rows, C, rpb)));
+    }
+    return (int)cudaGetLastError();
+  }
   int grid = (rows + LN_WARPS - 1) / LN_WARPS;
   if (grid > 148 * 2) grid = 148 * 2;
-  const int nv = (C + 255) / 256;
 #define DL4J_LN_BWD(NVV)                                                                                       \
   DL4J_DISPATCH_T(dtype, (layer_norm_bwd_kernel<T, NVV><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(     \
       (const T*)dy, (const T*)x, gain, mean, rstd, (T*)dx, dgain, dbias, rows, C)))
@@ -583,10 +713,11 @@ DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* d
   if (rows <= 0 || C <= 0) return 0;
   if (dy == nullptr || (act != 0 && z == nullptr)) return -DL4J_ERR_BAD_ARG;
   if (C % 8 == 0) {
-    const int ct = (C + 255) / 256;
-    int slabs = (148 * 6 + ct - 1) / ct;
+    const int ct = (C + 63) / 64;
+    int slabs = (148 * 2 + ct - 1) / ct;
+    if (slabs < 1) slabs = 1;
     int rpb = (rows + slabs - 1) / slabs;
-    rpb = (rpb + 31) / 32 * 32;
+    rpb = (rpb + 127) / 128 * 128;
     slabs = (rows + rpb - 1) / rpb;
     dim3 grid(ct, slabs);
     DL4J_DISPATCH_T(dtype, (bias_act_bwd_vec_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(

@@ -106,8 +106,8 @@ def test_linear_autograd(nat):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_layer_norm(nat, dtype):
-    R, C = 300, 768
+@pytest.mark.parametrize("R,C", [(300, 768), (4100, 768), (2050, 264)])       # small and large row counts take different backward kernels
+def test_layer_norm(nat, dtype, R, C):
     x = torch.randn(R, C, device="cuda").to(dtype).requires_grad_(True)
     g = torch.randn(C, device="cuda").requires_grad_(True)
     b = torch.randn(C, device="cuda").requires_grad_(True)
