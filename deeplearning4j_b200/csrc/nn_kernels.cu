@@ -483,10 +483,10 @@ bias_act_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __rest
 }
 
 // Vector form for C % 8 == 0: a thread owns 8 adjacent columns (one 16-byte load per row), eight threads span a 64-column
-// tile (128 contiguous bytes per row) and the block's 32 row lanes walk a long row slab with four independent row loads in
-// flight per thread; one atomicAdd per column and block at the end (about two blocks per SM, so few atomics per address).
+// tile (128 contiguous bytes per row) and the block's 32 row lanes walk a row slab with two independent row loads in
+// flight per thread; many small blocks keep enough warps resident to hide the load latency; one atomicAdd per column and block.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restrict__ dz, float* __restrict__ dbias,
                         int rows, int C, int act, int rows_per_block) {
   __shared__ float red[32][64 + 1];
@@ -498,10 +498,10 @@ bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __
 #pragma unroll
   for (int j = 0; j < 8; ++j) s[j] = 0.f;
   if (col < C) {
-    for (int r = r0 + ty; r < r1; r += 128) {
-      float d[4][8], zz[4][8];
+    for (int r = r0 + ty; r < r1; r += 64) {
+      float d[2][8], zz[2][8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const int rr = r + u * 32;
         if (rr < r1) {
           const long long o = (long long)rr * C + col;
@@ -510,7 +510,7 @@ bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const int rr = r + u * 32;
         if (rr < r1) {
           if (act != 0) {
@@ -657,7 +657,7 @@ DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gai
 #undef DL4J_LN_DX
     if (dgain || dbias) {
       const int ct = (C + 63) / 64;
-      int slabs = (148 * 2 + ct - 1) / ct;
+      int slabs = (148 * 12 + ct - 1) / ct;
       int rpb = (rows + slabs - 1) / slabs;
       rpb = (rpb + 63) / 64 * 64;
       slabs = (rows + rpb - 1) / rpb;
@@ -714,10 +714,10 @@ DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* d
   if (dy == nullptr || (act != 0 && z == nullptr)) return -DL4J_ERR_BAD_ARG;
   if (C % 8 == 0) {
     const int ct = (C + 63) / 64;
-    int slabs = (148 * 2 + ct - 1) / ct;
+    int slabs = (148 * 16 + ct - 1) / ct;          // many small blocks: the kernel hides latency with resident warps, not with depth
     if (slabs < 1) slabs = 1;
     int rpb = (rows + slabs - 1) / slabs;
-    rpb = (rpb + 127) / 128 * 128;
+    rpb = (rpb + 63) / 64 * 64;
     slabs = (rows + rpb - 1) / rpb;
     dim3 grid(ct, slabs);
     DL4J_DISPATCH_T(dtype, (bias_act_bwd_vec_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
