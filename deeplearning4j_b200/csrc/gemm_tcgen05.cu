@@ -42,6 +42,7 @@ struct GemmParams {
   long c_stride_b1, c_stride_b2;   // output batch strides in elements
   int tma_store;          // epilogue stages tiles in shared memory and writes them with TMA (needs 16-byte aligned C rows)
   int tma_aux;            // same for the auxiliary pre-activation output
+  int bias_mma;           // the bias is added on the tensor core: one extra K=16 step ones[128 x 1] x bias[1 x N] per tile
 };
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
@@ -129,6 +130,7 @@ template <int BLOCK_N, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
+                    const __grid_constant__ CUtensorMap tmap_ones, const __grid_constant__ CUtensorMap tmap_bias,
                     const GemmParams p) {
   using S = GemmSmem<BLOCK_N, A_MN, B_MN>;
   constexpr int STAGES = S::STAGES;
@@ -187,6 +189,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, kb_total);
+        if (p.bias_mma) {
+          // bias stage: both operands MN-major with a single valid K row (row 0 = ones / bias, rows 1..15 zero-filled by
+          // TMA because the maps' K extent is 1); only the 16 K rows of the one MMA step are written (2 KB per 64-column box
+          // at the usual box addresses), so the usual stage layout and descriptors apply
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], (BLOCK_M / 64 + BLOCK_N / 64) * (64 * UMMA_K * 2));
+#pragma unroll
+          for (int i = 0; i < BLOCK_M / 64; ++i)
+            tma_load_4d(sa + i * (64 * BLOCK_K * 2), &tmap_ones, &full_bar[stage], i * 64, 0, 0, 0);
+#pragma unroll
+          for (int i = 0; i < BLOCK_N / 64; ++i)
+            tma_load_4d(sb + i * (64 * BLOCK_K * 2), &tmap_bias, &full_bar[stage], n0 + i * 64, 0, 0, 0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
@@ -232,6 +250,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!mbar_wait_bounded(&tmem_empty[buf], acc_phase ^ 1, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
+        if (p.bias_mma) {
+          // accumulator := ones[128 x 16] * bias[16 x BLOCK_N] (only K row 0 is non-zero): every row starts at the bias
+          if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+          umma_f16(tmem_d, make_smem_desc_sw128(sa, 64 * BLOCK_K * 2, 1024), make_smem_desc_sw128(sb, 64 * BLOCK_K * 2, 1024),
+                   make_idesc(p.fmt, 1, 1, BLOCK_M, BLOCK_N), 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after();
@@ -242,7 +271,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
             umma_f16(tmem_d, da + ((uint64_t)(k * KSTEP_A) >> 4), db + ((uint64_t)(k * KSTEP_B) >> 4), idesc,
-                     (kb > kb0 || k > 0) ? 1u : 0u);
+                     (kb > kb0 || k > 0 || p.bias_mma) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);   // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -267,7 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool lead_split = split == 0;
       // lane L of the warp fetches bias[col0 + L] one 32-column group ahead of its use (first group here, before the
       // wait for the accumulator), and the group is broadcast with shuffles: no load latency inside the tile loop
-      const bool use_bias = p.bias != nullptr && lead_split;
+      const bool use_bias = p.bias != nullptr && lead_split && !p.bias_mma;
       float bias_cur = use_bias ? load_bias(p, n0 + lane) : 0.f;
       if (!mbar_wait_bounded(&tmem_full[buf], acc_phase, p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
@@ -378,7 +407,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = has_k ? __uint_as_float(r[j]) * p.alpha : 0.0f;
         const bool full_chunk = col0 + 32 <= p.N;
-        if (p.bias != nullptr && lead_split) {
+        if (p.bias != nullptr && lead_split && !p.bias_mma) {
           if (p.bias_fp32) {
             const float* b = reinterpret_cast<const float*>(p.bias) + col0;
 #pragma unroll
@@ -498,14 +527,20 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// 128 ones in each operand format: the A operand of the bias step
+#define DL4J_REP8(x) x, x, x, x, x, x, x, x
+#define DL4J_REP128(x) DL4J_REP8(DL4J_REP8(x)), DL4J_REP8(DL4J_REP8(x))
+static __device__ __align__(128) uint16_t g_ones_bf16[128] = {DL4J_REP128(0x3F80)};
+static __device__ __align__(128) uint16_t g_ones_f16[128] = {DL4J_REP128(0x3C00)};
+
 template <int BLOCK_N, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
-                       const GemmParams& p, int grid, cudaStream_t stream) {
+                       const CUtensorMap& tones, const CUtensorMap& tbias, const GemmParams& p, int grid, cudaStream_t stream) {
   using S = GemmSmem<BLOCK_N, A_MN, B_MN>;
   auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   if (e != cudaSuccess) return (int)e;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, tc, tx, p);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(ta, tb, tc, tx, tones, tbias, p);
   return (int)cudaGetLastError();
 }
 
@@ -557,13 +592,27 @@ static int gemm_impl(const void* A, const void* B, void* C, void* aux, const voi
       if (r == 0) p.tma_aux = 1; else p.tma_store = 0;
     }
   }
+  // bias on the tensor core: needs the bias in the operand format, 16-byte aligned, and alpha = 1 (the accumulator then
+  // already holds A.B + bias); the epilogue's per-element broadcast of the bias competes with the MMA operand fetch for
+  // the shared-memory path and costs a quarter of a short-K tile
+  CUtensorMap tones, tbias;
+  memset(&tones, 0, sizeof(tones));
+  memset(&tbias, 0, sizeof(tbias));
+  p.bias_mma = 0;
+  if (bias && !bias_fp32 && alpha == 1.0f && splits == 1 && batch1 == 1 && batch2 == 1 && !(reinterpret_cast<uintptr_t>(bias) & 15)) {
+    void* ones = nullptr;
+    cudaError_t ce = fmt == 1 ? cudaGetSymbolAddress(&ones, g_ones_bf16) : cudaGetSymbolAddress(&ones, g_ones_f16);
+    if (ce == cudaSuccess && encode_2d(&tones, ones, 128, 1, 256, 64, UMMA_K) == 0 &&
+        encode_2d(&tbias, bias, (uint64_t)N, 1, (uint64_t)((N + 7) / 8 * 8) * 2, 64, UMMA_K) == 0)
+      p.bias_mma = 1;
+  }
   const long tiles_l = (long)((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n) * splits * batch1 * batch2;
   if (tiles_l > 0x7fffffffL) return -DL4J_ERR_BAD_ARG;
   const int tiles = (int)tiles_l;
   if (num_sms <= 0) num_sms = 148;
   const int grid = tiles < num_sms ? tiles : num_sms;
 #define DL4J_GEMM_CASE(BN, AM, BM) \
-  if (block_n == BN && a_mn == AM && b_mn == BM) return launch_gemm<BN, AM != 0, BM != 0>(ta, tb, tc, tx, p, grid, stream);
+  if (block_n == BN && a_mn == AM && b_mn == BM) return launch_gemm<BN, AM != 0, BM != 0>(ta, tb, tc, tx, tones, tbias, p, grid, stream);
   DL4J_GEMM_CASE(256, 0, 0) DL4J_GEMM_CASE(256, 0, 1) DL4J_GEMM_CASE(256, 1, 0) DL4J_GEMM_CASE(256, 1, 1)
   DL4J_GEMM_CASE(128, 0, 0) DL4J_GEMM_CASE(128, 0, 1) DL4J_GEMM_CASE(128, 1, 0) DL4J_GEMM_CASE(128, 1, 1)
 #undef DL4J_GEMM_CASE

@@ -315,6 +315,28 @@ layer_norm_bwd_cols_kernel(const T* __restrict__ dy, const T* __restrict__ x, co
   }
 }
 
+// ----------------------------------------------------------------------------- embedding / row-gather gradient
+// grad[idx[r], :] += dy[r, :] accumulated in fp32 with 16-byte vector reductions (the table's master gradient is fp32 while dy
+// is the compute type); an index outside [0, V) is skipped and recorded in the status word.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scatter_add_rows_kernel(const T* __restrict__ dy, const long long* __restrict__ idx, float* __restrict__ grad, long long n,
+                        int C, long long ld_dy, long long V, int* status) {
+  const int c8 = C / 8;
+  const long long total = n * c8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / c8;
+    const int c = (int)(i % c8) * 8;
+    const long long t = idx[r];
+    if (t < 0 || t >= V) { if (status) atomicCAS(status, 0, DL4J_ERR_BOUNDS); continue; }
+    float v[8];
+    Vec8<T>::load(dy + r * ld_dy + c, v);
+    float* o = grad + t * (long long)C + c;
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+  }
+}
+
 // ----------------------------------------------------------------------------- softmax cross entropy
 // One block per row.  labels: dense probabilities (same dtype as logits) or int64 class indices.
 // loss[r] = -sum_j labels_j * log softmax_j ; grad_out (optional) = softmax * sum(labels) - labels.
@@ -375,6 +397,88 @@ softmax_xent_kernel(const T* __restrict__ logits, const T* __restrict__ dense_la
       const float l = dense_labels ? ldf(dense_labels + row * (long long)C + j) : (j == tgt ? 1.f : 0.f);
       stf(g + j, pj * sl - l);
     }
+  }
+}
+
+// Split form used for training: the forward pass makes one online (max, sum) sweep over the row and stores only the loss, the
+// log-sum-exp and the label mass; the backward pass writes grad = (softmax * label_mass - labels) * dloss[row] in one sweep, so
+// the upstream scale needs no pass of its own.  Rows are read in 16-byte vectors when VEC (row pitch and base allow it).
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(SX_THREADS)
+softmax_xent_fwd_kernel(const T* __restrict__ logits, const T* __restrict__ dense_labels, const long long* __restrict__ idx_labels,
+                        float* __restrict__ loss, float* __restrict__ lse_out, float* __restrict__ mass_out, int C, long long ld,
+                        int ignore_index) {
+  __shared__ float sh[SX_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* z = logits + row * ld;
+  const T* lab = dense_labels ? dense_labels + row * (long long)C : nullptr;
+  float mx = -INFINITY, se = 0.f, sl = 0.f, slz = 0.f;
+  auto take = [&](float v, float l) {
+    if (v > mx) { se = se * __expf(mx - v) + 1.f; mx = v; } else if (v != -INFINITY) { se += __expf(v - mx); }
+    sl += l; slz += l * v;
+  };
+  if (VEC) {
+    const int C8 = C & ~7;
+    for (int j = threadIdx.x * 8; j < C8; j += SX_THREADS * 8) {
+      float v[8], l[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      Vec8<T>::load(z + j, v);
+      if (lab) Vec8<T>::load(lab + j, l);
+      float m8 = v[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) m8 = fmaxf(m8, v[i]);
+      if (m8 > mx) { se *= __expf(mx - m8); mx = m8; }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { se += mx == -INFINITY ? 0.f : __expf(v[i] - mx); sl += l[i]; slz += l[i] * v[i]; }
+    }
+    for (int j = C8 + threadIdx.x; j < C; j += SX_THREADS) take(ldf(z + j), lab ? ldf(lab + j) : 0.f);
+  } else {
+    for (int j = threadIdx.x; j < C; j += SX_THREADS) take(ldf(z + j), lab ? ldf(lab + j) : 0.f);
+  }
+  const float gmx = block_reduce(mx, sh, true);
+  se = block_reduce(mx == -INFINITY ? 0.f : se * __expf(mx - gmx), sh, false);
+  const float lse = gmx + __logf(se);
+  if (lab) {
+    sl = block_reduce(sl, sh, false);
+    slz = block_reduce(slz, sh, false);
+  } else {
+    const long long tgt = idx_labels[row];
+    if (tgt == ignore_index || tgt < 0 || tgt >= C) { sl = 0.f; slz = 0.f; }
+    else { sl = 1.f; slz = ldf(z + tgt); }
+  }
+  if (threadIdx.x == 0) { loss[row] = sl * lse - slz; lse_out[row] = lse; mass_out[row] = sl; }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(SX_THREADS)
+softmax_xent_bwd_kernel(const T* __restrict__ logits, const T* __restrict__ dense_labels, const long long* __restrict__ idx_labels,
+                        const float* __restrict__ lse, const float* __restrict__ mass, const float* __restrict__ dloss,
+                        T* __restrict__ grad, int C, long long ld, long long ld_grad, int ignore_index) {
+  const long long row = blockIdx.x;
+  const T* z = logits + row * ld;
+  const T* lab = dense_labels ? dense_labels + row * (long long)C : nullptr;
+  T* g = grad + row * ld_grad;
+  const float l0 = lse[row], sl = mass[row], d = dloss[row];
+  long long tgt = -1;
+  if (!lab) { tgt = idx_labels[row]; if (tgt == ignore_index || tgt < 0 || tgt >= C) tgt = -1; }
+  const float a = sl * d;
+  if (VEC) {
+    const int C8 = C & ~7;
+    for (int j = threadIdx.x * 8; j < C8; j += SX_THREADS * 8) {
+      float v[8], l[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      Vec8<T>::load(z + j, v);
+      if (lab) Vec8<T>::load(lab + j, l);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float li = lab ? l[i] : ((long long)(j + i) == tgt ? 1.f : 0.f);
+        v[i] = __expf(v[i] - l0) * a - li * d;
+      }
+      Vec8<T>::store(g + j, v);
+    }
+    for (int j = C8 + threadIdx.x; j < C; j += SX_THREADS)
+      stf(g + j, __expf(ldf(z + j) - l0) * a - (lab ? ldf(lab + j) : ((long long)j == tgt ? 1.f : 0.f)) * d);
+  } else {
+    for (int j = threadIdx.x; j < C; j += SX_THREADS)
+      stf(g + j, __expf(ldf(z + j) - l0) * a - (lab ? ldf(lab + j) : ((long long)j == tgt ? 1.f : 0.f)) * d);
   }
 }
 
@@ -685,6 +789,57 @@ DL4J_API int dl4j_softmax_xent(const void* logits, const void* dense_labels, con
   if (rows <= 0) return 0;
   DL4J_DISPATCH_T(dtype, (softmax_xent_kernel<T><<<rows, SX_THREADS, 0, (cudaStream_t)stream>>>(
       (const T*)logits, (const T*)dense_labels, idx_labels, loss, (T*)grad_out, C, ld, ignore_index)));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_scatter_add_rows(const void* dy, const long long* idx, float* grad, long long n, int C, long long ld_dy,
+                                   long long V, int dtype, void* stream) {
+  if (n <= 0 || C <= 0) return 0;
+  if (!dy || !idx || !grad || C % 8 != 0 || ((uintptr_t)dy % 16) || ((uintptr_t)grad % 16) || (ld_dy % 8)) return -DL4J_ERR_BAD_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const long long total = n * (C / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  DL4J_DISPATCH_T(dtype, (scatter_add_rows_kernel<T><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const T*)dy, idx, grad, n, C, ld_dy, V, dl4j_status_word(dev))));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_softmax_xent_fwd(const void* logits, const void* dense_labels, const long long* idx_labels, float* loss,
+                                   float* lse, float* mass, int rows, int C, long long ld, int ignore_index, int dtype,
+                                   void* stream) {
+  if (rows <= 0) return 0;
+  if (!logits || !loss || !lse || !mass || (!dense_labels && !idx_labels)) return -DL4J_ERR_BAD_ARG;
+  const int esz = dtype == 2 ? 4 : 2;
+  const bool vec = ((uintptr_t)logits % 16 == 0) && ((ld * esz) % 16 == 0) &&
+                   (!dense_labels || (((uintptr_t)dense_labels % 16 == 0) && (((long long)C * esz) % 16 == 0)));
+  if (vec) {
+    DL4J_DISPATCH_T(dtype, (softmax_xent_fwd_kernel<T, true><<<rows, SX_THREADS, 0, (cudaStream_t)stream>>>(
+        (const T*)logits, (const T*)dense_labels, idx_labels, loss, lse, mass, C, ld, ignore_index)));
+  } else {
+    DL4J_DISPATCH_T(dtype, (softmax_xent_fwd_kernel<T, false><<<rows, SX_THREADS, 0, (cudaStream_t)stream>>>(
+        (const T*)logits, (const T*)dense_labels, idx_labels, loss, lse, mass, C, ld, ignore_index)));
+  }
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_softmax_xent_bwd(const void* logits, const void* dense_labels, const long long* idx_labels, const float* lse,
+                                   const float* mass, const float* dloss, void* grad, int rows, int C, long long ld,
+                                   long long ld_grad, int ignore_index, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  if (!logits || !lse || !mass || !dloss || !grad || (!dense_labels && !idx_labels)) return -DL4J_ERR_BAD_ARG;
+  const int esz = dtype == 2 ? 4 : 2;
+  const bool vec = ((uintptr_t)logits % 16 == 0) && ((ld * esz) % 16 == 0) && ((uintptr_t)grad % 16 == 0) &&
+                   ((ld_grad * esz) % 16 == 0) &&
+                   (!dense_labels || (((uintptr_t)dense_labels % 16 == 0) && (((long long)C * esz) % 16 == 0)));
+  if (vec) {
+    DL4J_DISPATCH_T(dtype, (softmax_xent_bwd_kernel<T, true><<<rows, SX_THREADS, 0, (cudaStream_t)stream>>>(
+        (const T*)logits, (const T*)dense_labels, idx_labels, lse, mass, dloss, (T*)grad, C, ld, ld_grad, ignore_index)));
+  } else {
+    DL4J_DISPATCH_T(dtype, (softmax_xent_bwd_kernel<T, false><<<rows, SX_THREADS, 0, (cudaStream_t)stream>>>(
+        (const T*)logits, (const T*)dense_labels, idx_labels, lse, mass, dloss, (T*)grad, C, ld, ld_grad, ignore_index)));
+  }
   return (int)cudaGetLastError();
 }
 

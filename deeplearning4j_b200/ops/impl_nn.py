@@ -163,7 +163,9 @@ def layer_norm(x, gain, bias=None, dimensions=(-1,), channelsFirst=False, **kw):
     dims = _ints(dimensions) or [-1]
     dims = [d % x.dim() for d in dims]
     if dims == [x.dim() - 1]:
-        return nnops.layer_norm(x, gain.reshape(-1), None if bias is None else bias.reshape(-1), 1e-5)
+        # a 1-D parameter is passed as is: reshape would return a view without the link to its fp32 master
+        flat = lambda t: t if t is None or t.dim() == 1 else t.reshape(-1)
+        return nnops.layer_norm(x, flat(gain), flat(bias), 1e-5)
     mean = x.mean(dims, keepdim=True)
     var = x.var(dims, unbiased=False, keepdim=True)
     shape = [x.shape[d] if d in dims else 1 for d in range(x.dim())]

@@ -234,6 +234,11 @@ def gather(x, indices=None, axis=0, intArgs=None, **kw):
     idx = indices if indices is not None else torch.tensor(intArgs, device=x.device)
     if isinstance(axis, torch.Tensor):
         axis = int(axis)
+    if int(axis) == 0 and x.dim() == 2 and x.is_cuda:
+        from . import native as nat
+        y = nat.gather_rows(x, idx)          # gradient scattered in fp32, straight into the table's master gradient
+        if y is not None:
+            return y.reshape(tuple(idx.shape) + x.shape[1:])
     return torch.index_select(x, int(axis), idx.reshape(-1).long()).reshape(
         x.shape[:int(axis)] + tuple(idx.shape) + x.shape[int(axis) + 1:])
 

@@ -54,6 +54,9 @@ def _load():
             "dl4j_layer_norm_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
             "dl4j_layer_norm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_softmax_xent": [vp, vp, vp, vp, vp, i32, i32, i64, i32, i32, vp],
+            "dl4j_scatter_add_rows": [vp, vp, vp, i64, i32, i64, i64, i32, vp],
+            "dl4j_softmax_xent_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i64, i32, i32, vp],
+            "dl4j_softmax_xent_bwd": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i64, i64, i32, i32, vp],
             "dl4j_lstm_cell_fwd": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_lstm_cell_bwd": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_lstm_seq_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
@@ -280,8 +283,17 @@ class _LinearFn(torch.autograd.Function):
         need_z = act in (2, 3, 4, 5, 6)
         z = torch.empty((x.shape[0], W_lp.shape[1]), dtype=x.dtype, device=x.device) if need_z and any(ctx.needs_input_grad) else None
         W = getattr(W, "_master", W)          # accumulate weight/bias gradients straight into the fp32 masters
+        # the forward GEMM takes the bias in the operand format when there is one (shadow of the master): it is then added
+        # by one extra tensor-core step instead of a per-element broadcast in the epilogue
+        b_fwd = None
+        if b is not None:
+            b_fwd = b if b.dtype == x.dtype else getattr(b, "_lp", None)
+            if b_fwd is not None:
+                b_fwd = b_fwd.detach()
         b = getattr(b, "_master", b) if b is not None else None
-        y = gemm_raw(x, W_lp, bias=None if b is None else b.reshape(-1), act=act, aux=z)
+        if b_fwd is None:
+            b_fwd = b
+        y = gemm_raw(x, W_lp, bias=None if b_fwd is None else b_fwd.reshape(-1), act=act, aux=z)
         ctx.act = act
         ctx.has_bias = b is not None
         ctx.W_ref = W
@@ -437,37 +449,83 @@ def layer_norm(x, gain, bias, eps):
 
 # =========================================================================== softmax cross entropy
 class _SoftmaxXentFn(torch.autograd.Function):
+    """Per-row loss; the forward stores only (loss, log-sum-exp, label mass) and the backward writes the gradient already
+    multiplied by the upstream per-row scale, so neither pass materialises an unscaled gradient."""
+
     @staticmethod
     def forward(ctx, logits, labels, sparse):
         l = require()
-        if not logits.is_contiguous():
+        if logits.stride(1) != 1:
             logits = logits.contiguous()
         rows, C = logits.shape
         loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
-        need_grad = ctx.needs_input_grad[0]
-        grad = torch.empty_like(logits) if need_grad else None
+        stats = torch.empty((2, rows), dtype=torch.float32, device=logits.device)
         if sparse:
-            idx = labels.reshape(-1).to(torch.int64).contiguous()
-            rc = l.dl4j_softmax_xent(_ptr(logits), None, _ptr(idx), _ptr(loss), _ptr(grad), rows, C, logits.stride(0), -100,
-                                     _DT[logits.dtype], _stream())
+            idx, lab = labels.reshape(-1).to(torch.int64).contiguous(), None
         else:
-            lab = labels.to(logits.dtype).contiguous()
-            rc = l.dl4j_softmax_xent(_ptr(logits), _ptr(lab), None, _ptr(loss), _ptr(grad), rows, C, logits.stride(0), -100,
-                                     _DT[logits.dtype], _stream())
-        _check(rc, "dl4j_softmax_xent")
-        ctx.save_for_backward(grad)
+            idx, lab = None, labels.to(logits.dtype).contiguous()
+        rc = l.dl4j_softmax_xent_fwd(_ptr(logits), _ptr(lab), _ptr(idx), _ptr(loss), _ptr(stats[0]), _ptr(stats[1]), rows, C,
+                                     logits.stride(0), -100, _DT[logits.dtype], _stream())
+        _check(rc, "dl4j_softmax_xent_fwd")
+        ctx.save_for_backward(logits, stats, *([idx] if sparse else [lab]))
+        ctx.sparse = sparse
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
-        (grad,) = ctx.saved_tensors
-        return grad * dloss.to(grad.dtype).unsqueeze(1), None, None
+        l = require()
+        logits, stats, lab_or_idx = ctx.saved_tensors
+        rows, C = logits.shape
+        grad = torch.empty((rows, C), dtype=logits.dtype, device=logits.device)
+        d = dloss.reshape(-1).float().contiguous()
+        idx, lab = (lab_or_idx, None) if ctx.sparse else (None, lab_or_idx)
+        rc = l.dl4j_softmax_xent_bwd(_ptr(logits), _ptr(lab), _ptr(idx), _ptr(stats[0]), _ptr(stats[1]), _ptr(d), _ptr(grad), rows, C,
+                                     logits.stride(0), grad.stride(0), -100, _DT[logits.dtype], _stream())
+        _check(rc, "dl4j_softmax_xent_bwd")
+        return grad, None, None
 
 
 def softmax_xent(logits, labels, sparse):
     if not available() or logits.dim() != 2 or logits.dtype not in _DT:
         return None
     return _SoftmaxXentFn.apply(logits, labels, bool(sparse))
+
+
+# =========================================================================== row gather (embedding lookup)
+class _GatherRowsFn(torch.autograd.Function):
+    """``table[idx]`` along dim 0.  The gradient is scattered with fp32 vector reductions: straight into the table's
+    preallocated fp32 gradient when it has one (nothing is returned for the table then), else into a fresh fp32 buffer."""
+
+    @staticmethod
+    def forward(ctx, table, idx):
+        ctx.table_ref = getattr(table, "_master", table)
+        ctx.table_dtype, ctx.V = table.dtype, table.shape[0]
+        ctx.save_for_backward(idx)
+        return torch.index_select(table.detach(), 0, idx)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        l = require()
+        tbl = ctx.table_ref
+        if dy.stride(1) != 1 or dy.stride(0) % 8 or dy.data_ptr() % 16:
+            dy = dy.contiguous()
+        C = dy.shape[1]
+        g = tbl.grad if (tbl.is_leaf and tbl.grad is not None) else None
+        direct = g is not None and g.dtype == torch.float32 and g.is_contiguous() and g.data_ptr() % 16 == 0
+        out = g if direct else torch.zeros((ctx.V, C), dtype=torch.float32, device=dy.device)
+        rc = l.dl4j_scatter_add_rows(_ptr(dy), _ptr(idx), _ptr(out), idx.numel(), C, dy.stride(0), ctx.V, _DT[dy.dtype], _stream())
+        _check(rc, "dl4j_scatter_add_rows")
+        return (None if direct else out.to(ctx.table_dtype)), None
+
+
+def gather_rows(table, idx):
+    """Differentiable ``table[idx]`` (2-D table, 1-D int64 indices) or None when the case is not covered."""
+    if not available() or table.dim() != 2 or table.dtype not in _DT or table.shape[1] % 8 or not table.is_contiguous():
+        return None
+    if not (torch.is_grad_enabled() and table.requires_grad):
+        return None
+    return _GatherRowsFn.apply(table, idx.reshape(-1).to(torch.int64).contiguous())
 
 
 # =========================================================================== LSTM cell

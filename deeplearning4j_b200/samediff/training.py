@@ -141,11 +141,14 @@ class _ShadowParam(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, leaf, shadow):
+        # kernels that accumulate straight into the master gradient return no gradient for the shadow; without this
+        # autograd would hand backward() a zero tensor, which costs a fill, a cast and an accumulate per parameter
+        ctx.set_materialize_grads(False)
         return shadow.view_as(shadow)
 
     @staticmethod
     def backward(ctx, g):
-        return g.float(), None
+        return (None if g is None else g.float()), None
 
 
 class TrainingState:

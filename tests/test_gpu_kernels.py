@@ -58,6 +58,25 @@ def test_gemm_epilogue(nat, act):
     assert _rel(aux, z) < 2e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b_mn", [0, 1])
+@pytest.mark.parametrize("shape,bn", [((384, 520, 192), 256), ((200, 768, 320), 128), ((16384, 768, 768), 256)])
+def test_gemm_bias_in_operand_format_is_added_on_the_tensor_core(nat, dtype, b_mn, shape, bn):
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(N + b_mn)
+    A = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dtype)
+    B = (torch.randn(K, N, device="cuda", generator=g) * 0.1).to(dtype)
+    b = B if b_mn else B.t().contiguous().t()
+    bias = (torch.randn(N, device="cuda", generator=g) * 3).to(dtype)
+    z = A.float() @ B.float() + bias.float()
+    aux = torch.empty(M, N, device="cuda", dtype=dtype)
+    out = nat.gemm_raw(A, b, bias=bias, act=1, aux=aux, block_n=bn)
+    torch.cuda.synchronize()
+    nat.check_status()
+    assert _rel(aux, z) < 1e-2
+    assert _rel(out, torch.relu(z)) < 1e-2
+
+
 def test_gemm_fp32_out_splitk_atomic(nat):
     M, N, K = 256, 512, 4096
     g = torch.Generator(device="cuda").manual_seed(5)
@@ -158,6 +177,43 @@ def test_lstm_cell(nat):
     (hr.sum() + (c2 * c2).sum()).backward()
     assert _rel(h, hr) < 1e-4 and _rel(c, c2) < 1e-4
     assert _rel(z.grad, zr.grad) < 1e-3 and _rel(c0.grad, cr.grad) < 1e-3
+
+
+def test_softmax_xent_bf16_gradient_carries_the_upstream_row_scale(nat):
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rows, C = 96, 30528
+    z = (torch.randn(rows, C, device="cuda", generator=g) * 2).bfloat16().requires_grad_(True)
+    idx = torch.randint(0, C, (rows,), device="cuda", generator=g)
+    w = torch.rand(rows, device="cuda", generator=g)
+    loss = nat.softmax_xent(z, idx, True)
+    (loss * w).sum().backward()
+    z32 = z.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(z32, idx, reduction="none")
+    (ref * w).sum().backward()
+    assert _rel(loss, ref) < 1e-3
+    assert _rel(z.grad, z32.grad) < 1e-2
+
+
+def test_gather_rows_scatters_gradient_into_fp32_master(nat):
+    g = torch.Generator(device="cuda").manual_seed(12)
+    V, C, n = 1000, 768, 4096
+    master = torch.randn(V, C, device="cuda", generator=g).requires_grad_(True)
+    master.grad = torch.full((V, C), 0.5, device="cuda")
+    shadow = master.detach().bfloat16().requires_grad_(True)
+    shadow._master = master
+    idx = torch.randint(0, V, (n,), device="cuda", generator=g)
+    y = nat.gather_rows(shadow, idx)
+    assert torch.equal(y, shadow.detach()[idx])
+    dy = torch.randn(n, C, device="cuda", generator=g).bfloat16()
+    y.backward(dy)
+    ref = torch.full((V, C), 0.5, device="cuda").index_add_(0, idx, dy.float())
+    assert shadow.grad is None                                  # accumulated straight into the master gradient
+    assert _rel(master.grad, ref) < 1e-5
+    # a table without a preallocated gradient gets an ordinary gradient
+    t2 = torch.randn(V, C, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    nat.gather_rows(t2, idx).backward(dy)
+    assert _rel(t2.grad, torch.zeros(V, C, device="cuda").index_add_(0, idx, dy.float())) < 1e-2
+    nat.check_status()
 
 
 @pytest.mark.parametrize("n", [1000, 65536 + 17, 3_000_001])
