@@ -52,6 +52,19 @@ template <> struct Vec8<float> {
   }
 };
 
+// Eight elements as raw 16-byte words (one for 16-bit types, two for float): lets a kernel issue the loads of several rows
+// before converting any of them.
+template <typename T> struct Raw8 { uint4 q[sizeof(T) / 2]; };
+template <typename T> __device__ __forceinline__ Raw8<T> ld_raw8(const T* p) {
+  Raw8<T> r;
+#pragma unroll
+  for (int i = 0; i < (int)(sizeof(T) / 2); ++i) r.q[i] = __ldcs(reinterpret_cast<const uint4*>(p) + i);
+  return r;
+}
+template <typename T> __device__ __forceinline__ void unpack8(const Raw8<T>& r, float (&v)[8]) {
+  Vec8<T>::load(reinterpret_cast<const T*>(&r), v);
+}
+
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
 template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
@@ -67,57 +80,73 @@ template <> __device__ __forceinline__ void stf<__half>(__half* p, float v) { *p
 constexpr int LN_MAXV = 4;
 constexpr int LN_WARPS = 8;
 
-template <typename T>
+template <typename T, int NV>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const float* __restrict__ gain,
                       const float* __restrict__ bias, T* __restrict__ y, T* __restrict__ sum_out,
                       float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int C, float eps) {
+  // One warp per row, rows strided over a fixed grid; the raw 16-byte loads of the next row are issued before the current row's
+  // reductions so that every warp always has a row in flight.
   const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
-  if (row >= rows) return;
   const int nvec = C / 8;
-  float v[LN_MAXV][8];
-  float s = 0.f;
-  const T* xr = x + (long long)row * C;
+  const int stride = gridDim.x * LN_WARPS;
+  int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  Raw8<T> qx[NV], qr[NV];
+  auto fetch = [&](int r) {
 #pragma unroll
-  for (int i = 0; i < LN_MAXV; ++i) {
-    const int vi = lane + i * 32;
-    if (vi < nvec) {
-      Vec8<T>::load(xr + vi * 8, v[i]);
-      if (res) {
-        float r[8];
-        Vec8<T>::load(res + (long long)row * C + vi * 8, r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
-        if (sum_out) Vec8<T>::store(sum_out + (long long)row * C + vi * 8, v[i]);
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        qx[i] = ld_raw8(x + (long long)r * C + vi * 8);
+        if (res) qr[i] = ld_raw8(res + (long long)r * C + vi * 8);
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s += v[i][j];
     }
-  }
-  const float mean = warp_sum(s) / C;
-  float q = 0.f;
+  };
+  if (row < rows) fetch(row);
+  for (; row < rows; row += stride) {
+    float v[NV][8];
+    float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < LN_MAXV; ++i)
-    if (lane + i * 32 < nvec) {
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        unpack8(qx[i], v[i]);
+        if (res) {
+          float r[8];
+          unpack8(qr[i], r);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; q += d * d; }
+          for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+          if (sum_out) Vec8<T>::store(sum_out + (long long)row * C + vi * 8, v[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += v[i][j];
+      }
     }
-  const float rstd = rsqrtf(warp_sum(q) / C + eps);
-  if (lane == 0) {
-    if (mean_out) mean_out[row] = mean;
-    if (rstd_out) rstd_out[row] = rstd;
-  }
+    if (row + stride < rows) fetch(row + stride);
+    const float mean = warp_sum(s) / C;
+    float q = 0.f;
 #pragma unroll
-  for (int i = 0; i < LN_MAXV; ++i) {
-    const int vi = lane + i * 32;
-    if (vi < nvec) {
-      float g[8], b[8], o[8];
-      Vec8<float>::load(gain + vi * 8, g);
-      if (bias) Vec8<float>::load(bias + vi * 8, b);
+    for (int i = 0; i < NV; ++i)
+      if (lane + i * 32 < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + (bias ? b[j] : 0.f);
-      Vec8<T>::store(y + (long long)row * C + vi * 8, o);
+        for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; q += d * d; }
+      }
+    const float rstd = rsqrtf(warp_sum(q) / C + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float g[8], bb[8], o[8];
+        Vec8<float>::load(gain + vi * 8, g);
+        if (bias) Vec8<float>::load(bias + vi * 8, bb);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + (bias ? bb[j] : 0.f);
+        Vec8<T>::store(y + (long long)row * C + vi * 8, o);
+      }
     }
   }
 }
@@ -217,23 +246,34 @@ layer_norm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx, int rows, int C) {
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int nvec = C / 8;
-  for (int row = blockIdx.x * LN_WARPS + wid; row < rows; row += gridDim.x * LN_WARPS) {
-    const float mean = mean_in[row], rstd = rstd_in[row];
+  const int stride = gridDim.x * LN_WARPS;
+  int row = blockIdx.x * LN_WARPS + wid;
+  Raw8<T> qd[NV], qx[NV];
+  float mean_n = 0.f, rstd_n = 0.f;
+  auto fetch = [&](int r) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        qd[i] = ld_raw8(dy + (long long)r * C + vi * 8);
+        qx[i] = ld_raw8(x + (long long)r * C + vi * 8);
+      }
+    }
+    mean_n = mean_in[r];
+    rstd_n = rstd_in[r];
+  };
+  if (row < rows) fetch(row);
+  for (; row < rows; row += stride) {
+    const float mean = mean_n, rstd = rstd_n;
     float xh[NV][8], dg[NV][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = lane + i * 32;
       if (vi < nvec) {
-        Vec8<T>::load(dy + (long long)row * C + vi * 8, dg[i]);
-        Vec8<T>::load(x + (long long)row * C + vi * 8, xh[i]);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = lane + i * 32;
-      if (vi < nvec) {
         float gn[8];
+        unpack8(qd[i], dg[i]);
+        unpack8(qx[i], xh[i]);
         Vec8<float>::load(gain + vi * 8, gn);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -244,6 +284,7 @@ layer_norm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
         }
       }
     }
+    if (row + stride < rows) fetch(row + stride);       // next row in flight during the reductions and the stores
     s1 = warp_sum(s1) / C;
     s2 = warp_sum(s2) / C;
 #pragma unroll
@@ -261,39 +302,44 @@ layer_norm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
 
 // dgain[c] += sum_r dy[r, c] * xhat[r, c], dbias[c] += sum_r dy[r, c]; block = 8 column threads (64 columns) x 32 row lanes
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 layer_norm_bwd_cols_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean_in,
                            const float* __restrict__ rstd_in, float* __restrict__ dgain, float* __restrict__ dbias, int rows, int C,
                            int rows_per_block) {
-  __shared__ float red[2][32][64 + 1];
-  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-  const int col = blockIdx.x * 64 + tx * 8;
+  // Same shape as the bias-gradient kernel: a warp reads 512 contiguous bytes of one row, 8 warps x 4 rows in flight per thread.
+  __shared__ float red[2][8][256 + 8];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + tx * 8;
   const int r0 = blockIdx.y * rows_per_block;
   const int r1 = min(r0 + rows_per_block, rows);
   float sg[8], sb[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { sg[j] = 0.f; sb[j] = 0.f; }
   if (col < C) {
-    for (int r = r0 + ty; r < r1; r += 64) {
-      float d[2][8], xv[2][8], mu[2], rs[2];
+    for (int r = r0 + ty; r < r1; r += 32) {
+      Raw8<T> qd[4], qx[4];
+      float mu[4], rs[4];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int rr = r + u * 32;
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * 8;
         if (rr < r1) {
           const long long o = (long long)rr * C + col;
-          Vec8<T>::load(dy + o, d[u]);
-          Vec8<T>::load(x + o, xv[u]);
+          qd[u] = ld_raw8(dy + o);
+          qx[u] = ld_raw8(x + o);
           mu[u] = mean_in[rr];
           rs[u] = rstd_in[rr];
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (r + u * 32 < r1) {
+      for (int u = 0; u < 4; ++u) {
+        if (r + u * 8 < r1) {
+          float d[8], xv[8];
+          unpack8(qd[u], d);
+          unpack8(qx[u], xv);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            sb[j] += d[u][j];
-            sg[j] = fmaf(d[u][j], (xv[u][j] - mu[u]) * rs[u], sg[j]);
+            sb[j] += d[j];
+            sg[j] = fmaf(d[j], (xv[j] - mu[u]) * rs[u], sg[j]);
           }
         }
       }
@@ -302,16 +348,13 @@ layer_norm_bwd_cols_kernel(const T* __restrict__ dy, const T* __restrict__ x, co
 #pragma unroll
   for (int j = 0; j < 8; ++j) { red[0][ty][tx * 8 + j] = sg[j]; red[1][ty][tx * 8 + j] = sb[j]; }
   __syncthreads();
-  if (threadIdx.x < 128) {
-    const int which = threadIdx.x >> 6, cc = threadIdx.x & 63;
-    const int c = blockIdx.x * 64 + cc;
-    float* out = which == 0 ? dgain : dbias;
-    if (c < C && out) {
-      float t = 0.f;
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < C) {
+    float tg = 0.f, tb = 0.f;
 #pragma unroll
-      for (int w = 0; w < 32; ++w) t += red[which][w][cc];
-      atomicAdd(out + c, t);
-    }
+    for (int w = 0; w < 8; ++w) { tg += red[0][w][threadIdx.x]; tb += red[1][w][threadIdx.x]; }
+    if (dgain) atomicAdd(dgain + c, tg);
+    if (dbias) atomicAdd(dbias + c, tb);
   }
 }
 
@@ -549,6 +592,35 @@ __device__ __forceinline__ float act_grad(float z, int act) {
     default: return 1.f;
   }
 }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+// d[j] *= act'(z[j]) for eight values with the activation dispatched once; the GELU forms use one tanh.approx per value
+// (sigmoid(y) = 0.5 + 0.5 tanh(y / 2)), which keeps the kernel bound by memory rather than by the special-function unit.
+__device__ __forceinline__ void act_grad8(float (&d)[8], const float (&z)[8], int act) {
+  if (act == 6) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = fmaf(0.5f, tanh_approx(0.851f * z[j]), 0.5f);
+      d[j] *= fmaf(1.702f * z[j] * s, 1.f - s, s);
+    }
+  } else if (act == 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] = z[j] > 0.f ? d[j] : 0.f;
+  } else if (act == 3) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float z2 = z[j] * z[j];
+      const float t = tanh_approx(0.7978845608028654f * z[j] * fmaf(0.044715f, z2, 1.f));
+      d[j] *= fmaf(0.5f, t, 0.5f) + 0.5f * z[j] * (1.f - t * t) * 0.7978845608028654f * fmaf(0.134145f, z2, 1.f);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] *= act_grad(z[j], act);
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -590,55 +662,59 @@ bias_act_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __rest
 // tile (128 contiguous bytes per row) and the block's 32 row lanes walk a row slab with two independent row loads in
 // flight per thread; many small blocks keep enough warps resident to hide the load latency; one atomicAdd per column and block.
 template <typename T>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256, 3)
 bias_act_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ z, T* __restrict__ dz, float* __restrict__ dbias,
                         int rows, int C, int act, int rows_per_block) {
-  __shared__ float red[32][64 + 1];
-  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-  const int col = blockIdx.x * 64 + tx * 8;
+  // A warp reads 512 contiguous bytes of one row (32 lanes x 8 elements); the block's 8 warps take 8 rows at a time and every
+  // thread keeps 4 rows in flight (raw 16-byte loads, converted after all of them are issued).
+  __shared__ float red[8][256 + 8];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + tx * 8;
   const int r0 = blockIdx.y * rows_per_block;
   const int r1 = min(r0 + rows_per_block, rows);
   float s[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) s[j] = 0.f;
   if (col < C) {
-    for (int r = r0 + ty; r < r1; r += 64) {
-      float d[2][8], zz[2][8];
+    for (int r = r0 + ty; r < r1; r += 32) {
+      Raw8<T> qd[4], qz[4];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int rr = r + u * 32;
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * 8;
         if (rr < r1) {
           const long long o = (long long)rr * C + col;
-          Vec8<T>::load(dy + o, d[u]);
-          if (act != 0) Vec8<T>::load(z + o, zz[u]);
+          qd[u] = ld_raw8(dy + o);
+          if (act != 0) qz[u] = ld_raw8(z + o);
         }
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int rr = r + u * 32;
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * 8;
         if (rr < r1) {
+          float d[8];
+          unpack8(qd[u], d);
           if (act != 0) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) d[u][j] *= act_grad(zz[u][j], act);
+            float zz[8];
+            unpack8(qz[u], zz);
+            act_grad8(d, zz, act);
           }
-          if (dz) Vec8<T>::store(dz + (long long)rr * C + col, d[u]);
+          if (dz) Vec8<T>::store(dz + (long long)rr * C + col, d);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) s[j] += d[u][j];
+          for (int j = 0; j < 8; ++j) s[j] += d[j];
         }
       }
     }
   }
+  if (!dbias) return;
 #pragma unroll
   for (int j = 0; j < 8; ++j) red[ty][tx * 8 + j] = s[j];
   __syncthreads();
-  if (dbias && threadIdx.x < 64) {
-    const int c = blockIdx.x * 64 + threadIdx.x;
-    if (c < C) {
-      float t = 0.f;
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < C) {
+    float t = 0.f;
 #pragma unroll
-      for (int w = 0; w < 32; ++w) t += red[w][threadIdx.x];
-      atomicAdd(dbias + c, t);
-    }
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    atomicAdd(dbias + c, t);
   }
 }
 
@@ -738,9 +814,17 @@ using namespace dl4j;
 DL4J_API int dl4j_layer_norm_fwd(const void* x, const void* res, const float* gain, const float* bias, void* y,
                                  void* sum_out, float* mean, float* rstd, int rows, int C, float eps, int dtype, void* stream) {
   if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
-  const int grid = (rows + LN_WARPS - 1) / LN_WARPS;
-  DL4J_DISPATCH_T(dtype, (layer_norm_fwd_kernel<T><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(
-      (const T*)x, (const T*)res, gain, bias, (T*)y, (T*)sum_out, mean, rstd, rows, C, eps)));
+  int grid = (rows + LN_WARPS - 1) / LN_WARPS;
+  if (grid > 148 * 4) grid = 148 * 4;
+  const int nvf = (C + 255) / 256;
+#define DL4J_LN_FWD(NVV)                                                                                     \
+  DL4J_DISPATCH_T(dtype, (layer_norm_fwd_kernel<T, NVV><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(   \
+      (const T*)x, (const T*)res, gain, bias, (T*)y, (T*)sum_out, mean, rstd, rows, C, eps)))
+  if (nvf == 1) { DL4J_LN_FWD(1); }
+  else if (nvf == 2) { DL4J_LN_FWD(2); }
+  else if (nvf == 3) { DL4J_LN_FWD(3); }
+  else { DL4J_LN_FWD(4); }
+#undef DL4J_LN_FWD
   return (int)cudaGetLastError();
 }
 
@@ -760,10 +844,11 @@ DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gai
     else { DL4J_LN_DX(4); }
 #undef DL4J_LN_DX
     if (dgain || dbias) {
-      const int ct = (C + 63) / 64;
-      int slabs = (148 * 12 + ct - 1) / ct;
+      const int ct = (C + 255) / 256;
+      int slabs = (148 * 6 + ct - 1) / ct;
+      if (slabs < 1) slabs = 1;
       int rpb = (rows + slabs - 1) / slabs;
-      rpb = (rpb + 63) / 64 * 64;
+      rpb = (rpb + 31) / 32 * 32;
       slabs = (rows + rpb - 1) / rpb;
       dim3 g2(ct, slabs);
       DL4J_DISPATCH_T(dtype, (layer_norm_bwd_cols_kernel<T><<<g2, 256, 0, (cudaStream_t)stream>>>(
@@ -868,11 +953,11 @@ DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* d
   if (rows <= 0 || C <= 0) return 0;
   if (dy == nullptr || (act != 0 && z == nullptr)) return -DL4J_ERR_BAD_ARG;
   if (C % 8 == 0) {
-    const int ct = (C + 63) / 64;
-    int slabs = (148 * 16 + ct - 1) / ct;          // many small blocks: the kernel hides latency with resident warps, not with depth
+    const int ct = (C + 255) / 256;
+    int slabs = (148 * 6 + ct - 1) / ct;           // about two rounds of resident blocks (3 per SM)
     if (slabs < 1) slabs = 1;
     int rpb = (rows + slabs - 1) / slabs;
-    rpb = (rpb + 63) / 64 * 64;
+    rpb = (rpb + 31) / 32 * 32;
     slabs = (rows + rpb - 1) / rpb;
     dim3 grid(ct, slabs);
     DL4J_DISPATCH_T(dtype, (bias_act_bwd_vec_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
