@@ -70,7 +70,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     mbar_init(s_full, 1);
     mbar_init(p_full, 16);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 8);
+    mbar_init(dq_empty, 16);
     mbar_init(fin_full, 1);
     mbar_fence_init();
   }
@@ -105,13 +105,14 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       bool ok = mbar_wait_bounded(kv_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
       const uint32_t ak = smem_u32(k_s), av = smem_u32(v_s), ap = smem_u32(p_s), ads = smem_u32(ds_s);
       const uint64_t dk_k = make_smem_desc_sw128(ak, 16, 1024), dv_k = make_smem_desc_sw128(av, 16, 1024);
+      const uint64_t d_q_k0 = make_smem_desc_sw128(smem_u32(q_s), 16, 1024), d_do_k0 = make_smem_desc_sw128(smem_u32(do_s), 16, 1024);
+      constexpr uint64_t STAGE_STEP_K = (uint64_t)(FB_TILE >> 4);
       // S_i = Q_i K_j^T and dP_i = dO_i V_j^T; issued one block ahead so that they overlap the threads' work on block i - 1
       auto issue_s = [&](int i) -> bool {
         const int st = i & 1;
         if (!mbar_wait_bounded(&qdo_full[st], (uint32_t)((i >> 1) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) return false;
         tc_fence_after();
-        const uint64_t dq_k = make_smem_desc_sw128(smem_u32(q_s + st * FB_TILE), 16, 1024);
-        const uint64_t ddo_k = make_smem_desc_sw128(smem_u32(do_s + st * FB_TILE), 16, 1024);
+        const uint64_t dq_k = d_q_k0 + (st ? STAGE_STEP_K : 0), ddo_k = d_do_k0 + (st ? STAGE_STEP_K : 0);
 #pragma unroll
         for (int k = 0; k < FA_D / 16; ++k) {
           umma_f16(tmem_base + T_S, dq_k + ((uint64_t)(k * 32) >> 4), dk_k + ((uint64_t)(k * 32) >> 4), id_s, k > 0 ? 1u : 0u);
@@ -120,25 +121,29 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         umma_commit(s_full);
         return true;
       };
+      // descriptors are built once; inside the loops they only advance by a constant (one 64-bit add per operand), which keeps
+      // the single issuing thread at a few instructions per MMA
+      const uint64_t d_pt = make_smem_desc_sw128(ap, FB_BLK * 128, 1024), d_dst = make_smem_desc_sw128(ads, FB_BLK * 128, 1024);
+      const uint64_t d_dsk = make_smem_desc_sw128(ads, 16, 1024), d_kmn = make_smem_desc_sw128(ak, FB_BLK * 128, 1024);
+      const uint64_t d_do_mn0 = make_smem_desc_sw128(smem_u32(do_s), FB_BLK * 128, 1024), d_q_mn0 = make_smem_desc_sw128(smem_u32(q_s), FB_BLK * 128, 1024);
+      constexpr uint64_t STAGE_STEP = (uint64_t)(FB_TILE >> 4);     // second Q / dO stage: same descriptor, start address + one tile
       if (ok) ok = issue_s(0);
       for (int i = 0; i < nq && ok; ++i) {
         const int st = i & 1;
-        const uint32_t aq = smem_u32(q_s + st * FB_TILE), ado = smem_u32(do_s + st * FB_TILE);
+        const uint64_t d_do_st = d_do_mn0 + (st ? STAGE_STEP : 0), d_q_st = d_q_mn0 + (st ? STAGE_STEP : 0);
         if (!mbar_wait_bounded(p_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         if (!mbar_wait_bounded(dq_empty, (uint32_t)((i & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < FB_BLK / 16; ++k) {
           // reduction over the 128 query rows: 16 rows (2048 bytes) per step in the MN-major tiles
-          const uint64_t a_pt = make_smem_desc_sw128(ap + k * 2048, FB_BLK * 128, 1024);
-          const uint64_t a_dst = make_smem_desc_sw128(ads + k * 2048, FB_BLK * 128, 1024);
-          const uint64_t b_do = make_smem_desc_sw128(ado + k * 2048, FB_BLK * 128, 1024);
-          const uint64_t b_q = make_smem_desc_sw128(aq + k * 2048, FB_BLK * 128, 1024);
+          const uint64_t a_pt = d_pt + (uint64_t)(k * (2048 >> 4)), a_dst = d_dst + (uint64_t)(k * (2048 >> 4));
+          const uint64_t b_do = d_do_st + (uint64_t)(k * (2048 >> 4)), b_q = d_q_st + (uint64_t)(k * (2048 >> 4));
           umma_f16(tmem_base + T_DV, a_pt, b_do, id_kv, (i > 0 || k > 0) ? 1u : 0u);
           umma_f16(tmem_base + T_DK, a_dst, b_q, id_kv, (i > 0 || k > 0) ? 1u : 0u);
           // reduction over the 128 keys: dS K-major (two 64-key blocks of 16 KB, 32 bytes per step), K_j MN-major
-          const uint64_t a_ds = make_smem_desc_sw128(ads + (k >> 2) * (FB_BLK * 128) + (k & 3) * 32, 16, 1024);
-          const uint64_t b_k = make_smem_desc_sw128(ak + k * 2048, FB_BLK * 128, 1024);
+          const uint64_t a_ds = d_dsk + (uint64_t)(((k >> 2) * (FB_BLK * 128) + (k & 3) * 32) >> 4);
+          const uint64_t b_k = d_kmn + (uint64_t)(k * (2048 >> 4));
           umma_f16(tmem_base + T_DQ, a_ds, b_k, id_dq, k > 0 ? 1u : 0u);
         }
         umma_commit(&qdo_empty[st]);
@@ -158,7 +163,12 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     asm volatile("bar.sync 1, 512;" ::: "memory");
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float k2 = p.scale * FA_LOG2E;
-    const float* mk = mask_s + cq * 32;
+    // key mask of this thread's 32 columns as a bit word; without masked keys the inner loop has no select at all
+    uint32_t mbits = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) mbits |= (mask_s[cq * 32 + j] != 0.f ? 1u : 0u) << j;
+    const bool all_keys = mbits == 0xffffffffu;
+    const float sc = p.scale;
     bool ok = true;
     const long rbase = ((long)b * p.H + h) * p.Tq;
     // per-row log-sum-exp and D of the next query block are fetched one block ahead (+inf: exp2(-inf) = 0 past the end)
@@ -173,8 +183,9 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         lse_n = tn < p.Tq ? p.lse[rbase + tn] : INFINITY;
         dv_n = tn < p.Tq ? p.dvec[rbase + tn] : 0.f;
       }
-      const float lse2 = lse * FA_LOG2E;
-      const bool live = lse != -INFINITY;
+      // a fully masked row (lse = -inf) and rows past the end (+inf) both give exp2(-inf) = 0 for every key
+      const float lse2 = (lse == -INFINITY) ? INFINITY : lse * FA_LOG2E;
+      const float dvs = dv_r * sc;
       if (!mbar_wait_bounded(s_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
       {
@@ -183,11 +194,20 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tmem_ld_32x32(taddr + T_DP + cq * 32, dpv);
         tmem_ld_wait();
         float pe[32], de[32];
+        if (all_keys) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float pv = (live && mk[j] != 0.f) ? fa_exp2(fmaf(__uint_as_float(sv[j]), k2, -lse2)) : 0.f;
-          pe[j] = pv;
-          de[j] = pv * (__uint_as_float(dpv[j]) - dv_r) * p.scale;
+          for (int j = 0; j < 32; ++j) {
+            const float pv = fa_exp2(fmaf(__uint_as_float(sv[j]), k2, -lse2));
+            pe[j] = pv;
+            de[j] = pv * fmaf(__uint_as_float(dpv[j]), sc, -dvs);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float pv = ((mbits >> j) & 1u) ? fa_exp2(fmaf(__uint_as_float(sv[j]), k2, -lse2)) : 0.f;
+            pe[j] = pv;
+            de[j] = pv * fmaf(__uint_as_float(dpv[j]), sc, -dvs);
+          }
         }
         fa_store_row(p_s, r, cq * 32, 32, pe);
         fa_store_row(ds_s, r, cq * 32, 32, de);
@@ -196,20 +216,20 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      if (cq < 2) {
-        // dQ_i: 64 columns per row, 32 per thread of the first two column groups
+      {
+        // dQ_i: 64 columns per row, 16 per thread (all four column groups take part)
         if (!mbar_wait_bounded(dq_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
         tc_fence_after();
-        uint32_t v0[32];
-        tmem_ld_32x32(taddr + T_DQ + cq * 32, v0);
+        uint32_t v0[16];
+        tmem_ld_32x16(taddr + T_DQ + cq * 16, v0);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(dq_empty);
         if (row_ok) {
-          float4* dst = reinterpret_cast<float4*>(p.dq + ridx * FA_D + cq * 32);
+          float4* dst = reinterpret_cast<float4*>(p.dq + ridx * FA_D + cq * 16);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)      // fire-and-forget 16-byte reductions at L2
+          for (int j = 0; j < 4; ++j)      // fire-and-forget 16-byte reductions at L2
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(v0[4 * j]), "r"(v0[4 * j + 1]),
                          "r"(v0[4 * j + 2]), "r"(v0[4 * j + 3])
                          : "memory");
