@@ -132,7 +132,6 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const int st = i & 1;
         const uint64_t d_do_st = d_do_mn0 + (st ? STAGE_STEP : 0), d_q_st = d_q_mn0 + (st ? STAGE_STEP : 0);
         if (!mbar_wait_bounded(p_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
-        if (!mbar_wait_bounded(dq_empty, (uint32_t)((i & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < FB_BLK / 16; ++k) {
@@ -141,12 +140,18 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const uint64_t b_do = d_do_st + (uint64_t)(k * (2048 >> 4)), b_q = d_q_st + (uint64_t)(k * (2048 >> 4));
           umma_f16(tmem_base + T_DV, a_pt, b_do, id_kv, (i > 0 || k > 0) ? 1u : 0u);
           umma_f16(tmem_base + T_DK, a_dst, b_q, id_kv, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&qdo_empty[st]);      // Q_i / dO_i are not read again: their stage can be refilled
+        // dQ_{i-1} must have left tensor memory before dQ_i overwrites it; the threads read it out while dV / dK were issued
+        if (!mbar_wait_bounded(dq_empty, (uint32_t)((i & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < FB_BLK / 16; ++k) {
           // reduction over the 128 keys: dS K-major (two 64-key blocks of 16 KB, 32 bytes per step), K_j MN-major
           const uint64_t a_ds = d_dsk + (uint64_t)(((k >> 2) * (FB_BLK * 128) + (k & 3) * 32) >> 4);
           const uint64_t b_k = d_kmn + (uint64_t)(k * (2048 >> 4));
           umma_f16(tmem_base + T_DQ, a_ds, b_k, id_dq, k > 0 ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[st]);
         umma_commit(dq_full);
         // S / dP of block i were read out of tensor memory before p_full(i) completed, so block i + 1 may overwrite them now
         if (i + 1 < nq) ok = issue_s(i + 1);
@@ -173,10 +178,29 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const long rbase = ((long)b * p.H + h) * p.Tq;
     // per-row log-sum-exp and D of the next query block are fetched one block ahead (+inf: exp2(-inf) = 0 past the end)
     float lse_n = r < p.Tq ? p.lse[rbase + r] : INFINITY, dv_n = r < p.Tq ? p.dvec[rbase + r] : 0.f;
+    auto dq_flush = [&](int blk) -> bool {
+      // dQ_blk: 64 columns per row, 16 per thread (all four column groups take part)
+      if (!mbar_wait_bounded(dq_full, (uint32_t)(blk & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) return false;
+      tc_fence_after();
+      uint32_t v0[16];
+      tmem_ld_32x16(taddr + T_DQ + cq * 16, v0);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
+      const int tqb = blk * FB_BLK + r;
+      if (tqb < p.Tq) {
+        float4* dst = reinterpret_cast<float4*>(p.dq + (rbase + tqb) * FA_D + cq * 16);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)      // fire-and-forget 16-byte reductions at L2
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(v0[4 * j]), "r"(v0[4 * j + 1]),
+                       "r"(v0[4 * j + 2]), "r"(v0[4 * j + 3])
+                       : "memory");
+      }
+      return true;
+    };
     for (int i = 0; i < nq && ok; ++i) {
       const int tq = i * FB_BLK + r;
-      const bool row_ok = tq < p.Tq;
-      const long ridx = rbase + tq;
       const float lse = lse_n, dv_r = dv_n;
       if (i + 1 < nq) {
         const int tn = tq + FB_BLK;
@@ -216,26 +240,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      {
-        // dQ_i: 64 columns per row, 16 per thread (all four column groups take part)
-        if (!mbar_wait_bounded(dq_full, (uint32_t)(i & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
-        tc_fence_after();
-        uint32_t v0[16];
-        tmem_ld_32x16(taddr + T_DQ + cq * 16, v0);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(dq_empty);
-        if (row_ok) {
-          float4* dst = reinterpret_cast<float4*>(p.dq + ridx * FA_D + cq * 16);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)      // fire-and-forget 16-byte reductions at L2
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "r"(v0[4 * j]), "r"(v0[4 * j + 1]),
-                         "r"(v0[4 * j + 2]), "r"(v0[4 * j + 3])
-                         : "memory");
-        }
-      }
+      // dQ of the previous block: read out of tensor memory and reduced into global memory now, while the MMA thread issues
+      // the dV / dK products of this block (the reductions stall their warp on the L2 atomics queue for about a microsecond)
+      if (i > 0 && !dq_flush(i - 1)) { ok = false; break; }
     }
+    if (ok && nq > 0) ok = dq_flush(nq - 1);
     if (ok && mbar_wait_bounded(fin_full, 0, p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) {
       tc_fence_after();
       // accumulator rows are keys here: thread r owns key k0 + r; column groups 0, 1 -> dV, 2, 3 -> dK
