@@ -36,9 +36,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   uint8_t* q_s = smem;
   uint8_t* kv_s = q_s + FF_TILE;                    // FF_SLOTS tiles, filled in the order K_0, V_0, K_1, V_1, ...
   uint8_t* p_s = kv_s + FF_SLOTS * FF_TILE;
-  float* mask_s = reinterpret_cast<float*>(p_s + FF_P_BYTES);         // [128] current key block
-  float* xch = mask_s + FF_BN;                                        // [2][128] per-row exchange between the two column halves
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 2 * FF_BM + 4);     // 4 floats: failure flag + padding
+  float* mask_s = reinterpret_cast<float*>(p_s + FF_P_BYTES);         // [2][128] key mask of the current and the next key block
+  float* xch = mask_s + 2 * FF_BN;                                    // [2][2][128] per-row exchange between the two column halves, by block parity
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 4 * FF_BM + 4);     // 4 floats: failure flag + padding
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;          // [FF_SLOTS]
   uint64_t* kv_empty = kv_full + FF_SLOTS;
@@ -137,30 +137,51 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     float o[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) o[i] = 0.f;
-    volatile int* fail_s = reinterpret_cast<volatile int*>(xch + 2 * FF_BM);    // set by any thread whose bounded wait expired
+    volatile int* fail_s = reinterpret_cast<volatile int*>(xch + 4 * FF_BM);    // set by any thread whose bounded wait expired
     if (t == 0) *fail_s = 0;
+    // Key mask: block 0 is staged here, block j + 1 is fetched into a register at the top of block j and stored at its end, so
+    // no global-memory latency sits between the barriers.  Without a mask the loops below have no select at all.
+    const bool has_mask = p.key_mask != nullptr;
+    if (has_mask && t < FF_BN) mask_s[t] = p.key_mask[(long)b * p.Tk + t];
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     for (int j = 0; j < nb; ++j) {
-      // key mask of this block -> shared memory; the barrier also orders the reuse of xch / mask_s between blocks
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (t < FF_BN) mask_s[t] = p.key_mask ? p.key_mask[(long)b * p.Tk + j * FF_BN + t] : 1.f;
+      float mask_next = 1.f;
+      if (has_mask && j + 1 < nb && t < FF_BN) mask_next = p.key_mask[(long)b * p.Tk + (j + 1) * FF_BN + t];
+      float* xj = xch + (j & 1) * (2 * FF_BM);       // exchange buffer of this block (the other parity may still be read)
       if (!mbar_wait_bounded(s_full, (uint32_t)(j & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) *fail_s = 1;
       tc_fence_after();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (*fail_s) break;                            // uniform: every thread reads the flag after the same barrier
-      const float* mk = mask_s + ch * 64;
+      // this thread's 64 keys as two bit words
+      uint32_t mb0 = 0xffffffffu, mb1 = 0xffffffffu;
+      if (has_mask) {
+        const float* mk = mask_s + (j & 1) * FF_BN + ch * 64;
+        mb0 = 0u; mb1 = 0u;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { mb0 |= (mk[i] != 0.f ? 1u : 0u) << i; mb1 |= (mk[32 + i] != 0.f ? 1u : 0u) << i; }
+      }
+      const bool all_keys = (mb0 & mb1) == 0xffffffffu;
       float m = -INFINITY;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t sv[32];
         tmem_ld_32x32(taddr + ch * 64 + half * 32, sv);
         tmem_ld_wait();
+        const uint32_t mb = half ? mb1 : mb0;
+        if (all_keys) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (mk[half * 32 + i] != 0.f) m = fmaxf(m, __uint_as_float(sv[i]));
+          for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(sv[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((mb >> i) & 1u) m = fmaxf(m, __uint_as_float(sv[i]));
+        }
       }
-      xch[ch * FF_BM + r] = m;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      m = fmaxf(m, xch[(ch ^ 1) * FF_BM + r]);
+      // the next block's mask is published before this block's barrier and read after it (its buffer was last read before
+      // the previous block's barrier)
+      if (has_mask && j + 1 < nb && t < FF_BN) mask_s[((j + 1) & 1) * FF_BN + t] = mask_next;
+      xj[ch * FF_BM + r] = m;
+      asm volatile("bar.sync 1, 256;" ::: "memory");      // the only barrier of the block
+      if (*fail_s) break;                            // uniform: every thread reads the flag after the same barrier
+      m = fmaxf(m, xj[(ch ^ 1) * FF_BM + r]);
       const float new_m = fmaxf(run_m, m);
       const float mref = (new_m == -INFINITY) ? 0.f : new_m;
       const float alpha = (run_m == -INFINITY) ? 0.f : fa_exp2((run_m - mref) * k2);
@@ -173,10 +194,16 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tmem_ld_32x32(taddr + ch * 64 + half * 32, sv);
         tmem_ld_wait();
         float e[32];
+        const uint32_t mb = half ? mb1 : mb0;
+        if (all_keys) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          e[i] = mk[half * 32 + i] != 0.f ? fa_exp2(fmaf(__uint_as_float(sv[i]), k2, -mk2)) : 0.f;
-          l += e[i];
+          for (int i = 0; i < 32; ++i) { e[i] = fa_exp2(fmaf(__uint_as_float(sv[i]), k2, -mk2)); l += e[i]; }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            e[i] = ((mb >> i) & 1u) ? fa_exp2(fmaf(__uint_as_float(sv[i]), k2, -mk2)) : 0.f;
+            l += e[i];
+          }
         }
         fa_store_row(p_s, r, ch * 64 + half * 32, 32, e);
       }
@@ -200,9 +227,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (!*fail_s) {
-      xch[ch * FF_BM + r] = run_l;
+      float* xl = xch + (nb & 1) * (2 * FF_BM);
+      xl[ch * FF_BM + r] = run_l;
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      const float l = run_l + xch[(ch ^ 1) * FF_BM + r];
+      const float l = run_l + xl[(ch ^ 1) * FF_BM + r];
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int tq = q0 + r;
       if (tq < p.Tq) {
@@ -259,7 +287,7 @@ DL4J_API int dl4j_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
   p.scale = scale;
   p.status = dl4j_status_word(dev);
-  const size_t smem = FF_TILE * (1 + FF_SLOTS) + FF_P_BYTES + (FF_BN + 2 * FF_BM + 4) * sizeof(float) + 256 + 1024;
+  const size_t smem = FF_TILE * (1 + FF_SLOTS) + FF_P_BYTES + (2 * FF_BN + 4 * FF_BM + 4) * sizeof(float) + 256 + 1024;
   cudaError_t e = cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int q_blocks = (Tq + FF_BM - 1) / FF_BM;
