@@ -110,6 +110,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       for (int j = 0; j < nb && ok; ++j) {
         // P_j is in shared memory (and S_j has been read out of TMEM) once p_full completes
         if (!mbar_wait_bounded(p_full, (uint32_t)(j & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        // S_{j+1} first: the threads take its row maxima while P_j V_j runs (S_j has been read out, K_{j+1} sits in the ring)
+        if (j + 1 < nb && !(ok = issue_s(j + 1))) break;
         const int t = 2 * j + 1, slot = t % FF_SLOTS;
         if (!mbar_wait_bounded(&kv_full[slot], (uint32_t)((t / FF_SLOTS) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
@@ -122,7 +124,6 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         umma_commit(&kv_empty[slot]);
         umma_commit(pv_full);
-        if (j + 1 < nb) ok = issue_s(j + 1);        // overlaps the threads' accumulation of P_j V_j
       }
     }
   } else {
@@ -137,6 +138,23 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     float o[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    float alpha_prev = 0.f;                         // rescale factor that goes with the pending P V product
+    bool broke = false;
+    // O = O * alpha + P_blk V_blk (this thread: 32 of the 64 head-dimension columns); deferred by one block so that the product
+    // runs on the tensor core while the threads take the next block's row maxima
+    auto o_update = [&](int blk, float a) {
+      if (!mbar_wait_bounded(pv_full, (uint32_t)(blk & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) {
+        *reinterpret_cast<volatile int*>(xch + 4 * FF_BM) = 1;      // seen by everybody after the next barrier
+      } else {
+        tc_fence_after();
+        uint32_t pv[32];
+        tmem_ld_32x32(taddr + FF_T_PV + ch * 32, pv);
+        tmem_ld_wait();
+        tc_fence_before();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], a, __uint_as_float(pv[i]));
+      }
+    };
     volatile int* fail_s = reinterpret_cast<volatile int*>(xch + 4 * FF_BM);    // set by any thread whose bounded wait expired
     if (t == 0) *fail_s = 0;
     // Key mask: block 0 is staged here, block j + 1 is fetched into a register at the top of block j and stored at its end, so
@@ -180,13 +198,15 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (has_mask && j + 1 < nb && t < FF_BN) mask_s[((j + 1) & 1) * FF_BN + t] = mask_next;
       xj[ch * FF_BM + r] = m;
       asm volatile("bar.sync 1, 256;" ::: "memory");      // the only barrier of the block
-      if (*fail_s) break;                            // uniform: every thread reads the flag after the same barrier
+      if (*fail_s) { broke = true; break; }          // uniform: every thread reads the flag after the same barrier
       m = fmaxf(m, xj[(ch ^ 1) * FF_BM + r]);
       const float new_m = fmaxf(run_m, m);
       const float mref = (new_m == -INFINITY) ? 0.f : new_m;
       const float alpha = (run_m == -INFINITY) ? 0.f : fa_exp2((run_m - mref) * k2);
       run_m = new_m;
       const float mk2 = mref * k2;
+      if (j > 0) o_update(j - 1, alpha_prev);         // also: P_{j-1} V_{j-1} has finished reading P before P_j is written below
+      alpha_prev = alpha;
       float l = 0.f;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -212,19 +232,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       fence_proxy_async_smem();       // P was written through the generic proxy; the MMA reads it through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      // O = O * alpha + P_j V_j (this thread: 32 of the 64 head-dimension columns)
-      if (!mbar_wait_bounded(pv_full, (uint32_t)(j & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) {
-        *fail_s = 1;                                 // seen by everybody after the next barrier
-      } else {
-        tc_fence_after();
-        uint32_t pv[32];
-        tmem_ld_32x32(taddr + FF_T_PV + ch * 32, pv);
-        tmem_ld_wait();
-        tc_fence_before();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(pv[i]));
-      }
     }
+    if (!broke && nb > 0) o_update(nb - 1, alpha_prev);
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (!*fail_s) {
       float* xl = xch + (nb & 1) * (2 * FF_BM);
