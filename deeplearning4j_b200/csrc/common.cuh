@@ -261,4 +261,5 @@ typedef CUresult (*dl4j_PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuui
                                          const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                          CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 dl4j_PFN_encodeTiled dl4j_get_encode_tiled();
+int dl4j_launch_grid(const char* name, int fallback);   // blocks per SM from the launch table (GRID_SIZE_<NAME> overrides)
 int* dl4j_status_word(int device);   // device-resident int, zeroed at creation, one per device

@@ -815,7 +815,8 @@ DL4J_API int dl4j_layer_norm_fwd(const void* x, const void* res, const float* ga
                                  void* sum_out, float* mean, float* rstd, int rows, int C, float eps, int dtype, void* stream) {
   if (C % 8 != 0 || C > 32 * 8 * LN_MAXV) return -DL4J_ERR_BAD_ARG;
   int grid = (rows + LN_WARPS - 1) / LN_WARPS;
-  if (grid > 148 * 4) grid = 148 * 4;
+  const int cap_f = 148 * dl4j_launch_grid("LAYER_NORM_FWD", 4);
+  if (grid > cap_f) grid = cap_f;
   const int nvf = (C + 255) / 256;
 #define DL4J_LN_FWD(NVV)                                                                                     \
   DL4J_DISPATCH_T(dtype, (layer_norm_fwd_kernel<T, NVV><<<grid, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(   \
@@ -834,7 +835,8 @@ DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gai
   const int nv = (C + 255) / 256;
   if (rows >= 2048) {
     int g1 = (rows + LN_WARPS - 1) / LN_WARPS;
-    if (g1 > 148 * 4) g1 = 148 * 4;
+    const int cap_dx = 148 * dl4j_launch_grid("LAYER_NORM_BWD_DX", 4);
+    if (g1 > cap_dx) g1 = cap_dx;
 #define DL4J_LN_DX(NVV)                                                                                           \
   DL4J_DISPATCH_T(dtype, (layer_norm_bwd_dx_kernel<T, NVV><<<g1, LN_WARPS * 32, 0, (cudaStream_t)stream>>>(       \
       (const T*)dy, (const T*)x, gain, mean, rstd, (T*)dx, rows, C)))
@@ -845,7 +847,7 @@ DL4J_API int dl4j_layer_norm_bwd(const void* dy, const void* x, const float* gai
 #undef DL4J_LN_DX
     if (dgain || dbias) {
       const int ct = (C + 255) / 256;
-      int slabs = (148 * 6 + ct - 1) / ct;
+      int slabs = (148 * dl4j_launch_grid("LAYER_NORM_BWD_COLS", 6) + ct - 1) / ct;
       if (slabs < 1) slabs = 1;
       int rpb = (rows + slabs - 1) / slabs;
       rpb = (rpb + 31) / 32 * 32;
@@ -885,7 +887,8 @@ DL4J_API int dl4j_scatter_add_rows(const void* dy, const long long* idx, float* 
   cudaGetDevice(&dev);
   const long long total = n * (C / 8);
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const long long cap_s = 148LL * dl4j_launch_grid("SCATTER_ADD_ROWS", 16);
+  if (blocks > cap_s) blocks = cap_s;
   DL4J_DISPATCH_T(dtype, (scatter_add_rows_kernel<T><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const T*)dy, idx, grad, n, C, ld_dy, V, dl4j_status_word(dev))));
   return (int)cudaGetLastError();
@@ -954,7 +957,7 @@ DL4J_API int dl4j_bias_act_bwd(const void* dy, const void* z, void* dz, float* d
   if (dy == nullptr || (act != 0 && z == nullptr)) return -DL4J_ERR_BAD_ARG;
   if (C % 8 == 0) {
     const int ct = (C + 255) / 256;
-    int slabs = (148 * 6 + ct - 1) / ct;           // about two rounds of resident blocks (3 per SM)
+    int slabs = (148 * dl4j_launch_grid("BIAS_ACT_BWD", 6) + ct - 1) / ct;      // default: about two rounds of resident blocks (3 per SM)
     if (slabs < 1) slabs = 1;
     int rpb = (rows + slabs - 1) / slabs;
     rpb = (rpb + 31) / 32 * 32;

@@ -347,3 +347,20 @@ def test_lstm_sequence_kernel(nat, T, mb, n, reverse, persistent_bwd, monkeypatc
     (ref_hs * w).sum().backward()
     for name, a, b in zip(("dzx", "drw", "dh0", "dc0"), got, (zx.grad, rw.grad, h0.grad, c0.grad)):
         assert _rel(a, b) < 6e-2, (name, _rel(a, b))
+
+
+def test_launch_table_override_changes_grid_not_results(nat, monkeypatch):
+    from deeplearning4j_b200.utils.launch import DeviceValidator, LaunchDims
+    x = torch.randn(4100, 768, device="cuda").bfloat16()
+    g, b = torch.randn(768, device="cuda"), torch.randn(768, device="cuda")
+    ref = nat.layer_norm(x, g, b, 1e-5)
+    monkeypatch.setenv("GRID_SIZE_LAYER_NORM_FWD", "1")
+    LaunchDims.reload()
+    try:
+        assert LaunchDims.get("LAYER_NORM_FWD").grid == 1
+        out = nat.layer_norm(x, g, b, 1e-5)
+        assert torch.equal(out, ref)
+    finally:
+        monkeypatch.delenv("GRID_SIZE_LAYER_NORM_FWD")
+        LaunchDims.reload()
+    assert DeviceValidator().validateTable() == {}          # every table entry fits the current device
