@@ -176,6 +176,17 @@ def layer_norm(x, gain, bias=None, dimensions=(-1,), channelsFirst=False, **kw):
 op("layer_norm_bp", n_out=3)(_autobp(layer_norm, 3))
 
 
+@op("add_layer_norm")
+def add_layer_norm(a, b, gain, bias=None, dimensions=(-1,), channelsFirst=False, **kw):
+    """Fused ``layer_norm(a + b)``: produced by the session from ``add`` -> ``layer_norm`` (the residual connections of a
+    transformer block); falls back to the two ops when the operands broadcast or the axis is not the last one."""
+    dims = [d % a.dim() for d in (_ints(dimensions) or [-1])]
+    if a.shape == b.shape and a.dtype == b.dtype and dims == [a.dim() - 1]:
+        flat = lambda t: t if t is None or t.dim() == 1 else t.reshape(-1)
+        return nnops.layer_norm(a, flat(gain), flat(bias), 1e-5, residual=b)
+    return layer_norm(a + b, gain, bias, dimensions=dimensions, channelsFirst=channelsFirst)
+
+
 @op("standardize")
 def standardize(x, dimensions=(-1,), **kw):
     d = [i % x.dim() for i in (_ints(dimensions) or [-1])]

@@ -387,7 +387,7 @@ def linear(x, W, b, activation):
 # =========================================================================== layer norm
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gain, bias, eps):
+    def forward(ctx, x, gain, bias, eps, res=None):
         l = require()
         shp = x.shape
         C = shp[-1]
@@ -402,10 +402,18 @@ class _LayerNormFn(torch.autograd.Function):
         bias = getattr(bias, "_master", bias) if bias is not None else None
         g32 = gain.detach().float().contiguous().reshape(-1)
         b32 = bias.detach().float().contiguous().reshape(-1) if bias is not None else None
-        rc = l.dl4j_layer_norm_fwd(_ptr(x2), None, _ptr(g32), _ptr(b32), _ptr(y), None, _ptr(mean), _ptr(rstd), rows, C,
+        r2 = s2 = None
+        if res is not None:
+            # y = LN(x + res): the kernel adds the residual while loading and writes the sum once (kept for the backward)
+            r2 = res.reshape(-1, C)
+            if not r2.is_contiguous():
+                r2 = r2.contiguous()
+            s2 = torch.empty_like(x2)
+        rc = l.dl4j_layer_norm_fwd(_ptr(x2), _ptr(r2), _ptr(g32), _ptr(b32), _ptr(y), _ptr(s2), _ptr(mean), _ptr(rstd), rows, C,
                                    float(eps), _DT[x.dtype], _stream())
         _check(rc, "dl4j_layer_norm_fwd")
-        ctx.save_for_backward(x2, g32, mean, rstd)
+        ctx.has_res = res is not None
+        ctx.save_for_backward(x2 if s2 is None else s2, g32, mean, rstd)
         ctx.refs = (gain, bias)
         ctx.shape = shp
         return y.reshape(shp)
@@ -437,14 +445,18 @@ class _LayerNormFn(torch.autograd.Function):
             gret = gret.reshape(gain.shape).to(gain.dtype)
         if bret is not None:
             bret = bret.reshape(bias.shape).to(bias.dtype)
-        return dx.reshape(ctx.shape), gret, bret, None
+        dx = dx.reshape(ctx.shape)
+        return dx, gret, bret, None, (dx if ctx.has_res else None)
 
 
-def layer_norm(x, gain, bias, eps):
+def layer_norm(x, gain, bias, eps, residual=None):
+    """LN(x) or, with ``residual`` (same shape and dtype as x), LN(x + residual) in one pass."""
     C = x.shape[-1]
     if not available() or C % 8 != 0 or C > 1024 or x.dtype not in _DT:
         return None
-    return _LayerNormFn.apply(x, gain, bias, eps)
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype):
+        return None
+    return _LayerNormFn.apply(x, gain, bias, eps, residual)
 
 
 # =========================================================================== softmax cross entropy

@@ -53,12 +53,15 @@ def linear(x, W, b=None, activation=None, training=False):
     return activation(z, training) if activation is not None else z
 
 
-def layer_norm(x, gain, bias=None, eps=1e-5):
+def layer_norm(x, gain, bias=None, eps=1e-5, residual=None):
+    """Layer norm over the last axis; with ``residual`` the input is ``x + residual`` (added inside the kernel)."""
     nat = _native_for(x)
     if nat is not None and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and x.shape[-1] % 8 == 0:
-        y = nat.layer_norm(x, gain, bias, eps)
+        y = nat.layer_norm(x, gain, bias, eps, residual)
         if y is not None:
             return y
+    if residual is not None:
+        x = x + residual
     return F.layer_norm(x, (x.shape[-1],), gain.to(x.dtype), None if bias is None else bias.to(x.dtype), eps)
 
 

@@ -32,8 +32,22 @@ def _build_plan(sd, outputs):
                 consumers.setdefault(i, []).append(n)
     out_set = set(outputs)
     skip, plan = set(), []
+    # fusion: add whose only consumer is a layer_norm taking it as its input (residual connection + norm); the fused node sits at
+    # the layer_norm's position, where the gain / bias inputs are certainly available
+    fuse_ln = {}
+    for n in nodes:
+        if n.opName == "add" and len(n.inputs) == 2 and None not in n.inputs and len(n.outputs) == 1 and n.outputs[0] not in out_set:
+            cs = consumers.get(n.outputs[0], [])
+            if len(cs) == 1 and cs[0].opName == "layer_norm" and cs[0].inputs and cs[0].inputs[0] == n.outputs[0] \
+                    and cs[0].inputs.count(n.outputs[0]) == 1:
+                ln = cs[0]
+                fuse_ln[id(ln)] = SameDiffOp(ln.name, "add_layer_norm", list(n.inputs) + list(ln.inputs[1:]), list(ln.outputs), dict(ln.args))
+                skip.add(id(n))
     for n in nodes:
         if id(n) in skip:
+            continue
+        if id(n) in fuse_ln:
+            plan.append((fuse_ln[id(n)], registry.get("add_layer_norm")))
             continue
         # fusion: xw_plus_b whose only consumer is a gelu node
         if n.opName in ("xw_plus_b", "linear") and len(n.outputs) == 1 and n.outputs[0] not in out_set \

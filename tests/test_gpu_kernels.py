@@ -364,3 +364,24 @@ def test_launch_table_override_changes_grid_not_results(nat, monkeypatch):
         monkeypatch.delenv("GRID_SIZE_LAYER_NORM_FWD")
         LaunchDims.reload()
     assert DeviceValidator().validateTable() == {}          # every table entry fits the current device
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layer_norm_with_fused_residual(nat, dtype):
+    R, C = 4100, 768
+    x = torch.randn(R, C, device="cuda").to(dtype).requires_grad_(True)
+    res = torch.randn(R, C, device="cuda").to(dtype).requires_grad_(True)
+    g = torch.randn(C, device="cuda").requires_grad_(True)
+    b = torch.randn(C, device="cuda").requires_grad_(True)
+    y = nat.layer_norm(x, g, b, 1e-5, residual=res)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, rr = x.detach().float().requires_grad_(True), res.detach().float().requires_grad_(True)
+    gr, br = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    s = (xr + rr).to(dtype).float() if dtype == torch.bfloat16 else xr + rr      # the kernel rounds the stored sum to the io type
+    yr = torch.nn.functional.layer_norm(xr + rr, (C,), gr, br, 1e-5)
+    yr.backward(dy.float())
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel(y, yr) < tol
+    assert _rel(x.grad, xr.grad) < tol and _rel(res.grad, rr.grad) < tol
+    assert _rel(g.grad, gr.grad) < tol and _rel(b.grad, br.grad) < tol

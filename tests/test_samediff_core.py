@@ -155,3 +155,39 @@ def test_execution_trace_is_collected_into_a_graph():
     assert len(Nd4j.listTraces()) == 3                   # tracing is off again
     Nd4j.purgeTrace()
     assert not Nd4j.listTraces()
+
+
+def test_residual_add_followed_by_layer_norm_runs_as_one_fused_node():
+    from deeplearning4j_b200.samediff.session import _build_plan
+    sd = SameDiff.create()
+    x = sd.placeHolder("x", DataType.FLOAT, -1, 8)
+    y = sd.placeHolder("y", DataType.FLOAT, -1, 8)
+    gv, bv = np.linspace(0.5, 1.5, 8).astype(np.float32), np.linspace(-1, 1, 8).astype(np.float32)
+    g, b = sd.var("g", Nd4j.create(gv)), sd.var("b", Nd4j.create(bv))
+    h = sd.nn.layerNorm("ln", x.add(y), g, b, False, 1)
+    loss = h.mul(h).sum().rename("loss")
+    sd.setLossVariables("loss")
+    assert [n.opName for n, _ in _build_plan(sd, ["loss"])] == ["add_layer_norm", "multiply", "reduce_sum"]
+    # the sum itself requested as an output: no fusion
+    s_name = sd.getVariable("ln").name_()
+    add_out = [o.outputs[0] for o in sd.ops if o.opName == "add"][0]
+    assert "add" in [n.opName for n, _ in _build_plan(sd, ["loss", add_out])]
+    rng = np.random.default_rng(0)
+    xv, yv = rng.normal(size=(4, 8)).astype(np.float32), rng.normal(size=(4, 8)).astype(np.float32)
+    out = sd.output({"x": Nd4j.create(xv), "y": Nd4j.create(yv)}, "ln")["ln"].numpy()
+    tx, ty = torch.tensor(xv, requires_grad=True), torch.tensor(yv)
+    tg, tb = torch.tensor(gv, requires_grad=True), torch.tensor(bv, requires_grad=True)
+    ref = torch.nn.functional.layer_norm(tx + ty, (8,), tg, tb, 1e-5)
+    np.testing.assert_allclose(out, ref.detach().numpy(), rtol=1e-5, atol=1e-6)
+    (ref * ref).sum().backward()
+    grads = sd.calculateGradients({"x": Nd4j.create(xv), "y": Nd4j.create(yv)}, "g", "b")
+    np.testing.assert_allclose(grads["g"].numpy(), tg.grad.numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(grads["b"].numpy(), tb.grad.numpy(), rtol=1e-4, atol=1e-5)
+    # broadcasting operands keep the two-op semantics inside the fused node
+    sd2 = SameDiff.create()
+    a = sd2.placeHolder("a", DataType.FLOAT, -1, 8)
+    p = sd2.constant("p", Nd4j.create(bv))
+    sd2.nn.layerNorm("ln", a.add(p), sd2.constant("g", Nd4j.create(gv)), sd2.constant("b", Nd4j.create(bv)), False, 1)
+    out2 = sd2.output({"a": Nd4j.create(xv)}, "ln")["ln"].numpy()
+    ref2 = torch.nn.functional.layer_norm(torch.tensor(xv) + torch.tensor(bv), (8,), torch.tensor(gv), torch.tensor(bv), 1e-5)
+    np.testing.assert_allclose(out2, ref2.numpy(), rtol=1e-5, atol=1e-6)
