@@ -244,3 +244,55 @@ DL4J_API int dl4j_conv_wgrad_from_cl(const void* g_cl, float* grad, int O, int I
   conv_wgrad_from_cl_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(g_cl), grad, O, I, S);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------ stem space-to-depth
+// A stride-2 convolution over a few input channels (an RGB stem) runs as a stride-1 convolution over a 2x2 space-to-depth view of the
+// zero-padded input.  This kernel builds that view in one pass: out[n, hs, ws, (bh * 2 + bw) * C + c] = x[n, c, 2 hs + bh - pH,
+// 2 ws + bw - pW] (0 outside the image, 0 in the channels 4 C .. CP - 1), channels-last bf16 / fp16 with CP a multiple of 8, from
+// an input of the same element type with arbitrary strides.  One thread writes one output pixel (CP elements, 16-byte stores).
+namespace dl4j {
+template <int CP>
+__global__ void __launch_bounds__(256)
+stem_s2d_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int N, int C, int H, int W, long long sn, long long sc,
+                long long sh, long long sw, int pH, int pW, int Hs, int Ws) {
+  const long long total = (long long)N * Hs * Ws;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int ws = (int)(i % Ws);
+    const int hs = (int)((i / Ws) % Hs);
+    const long long n = i / ((long long)Ws * Hs);
+    __align__(16) uint16_t v[CP];
+#pragma unroll
+    for (int j = 0; j < CP; ++j) v[j] = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int ih = 2 * hs + (b >> 1) - pH, iw = 2 * ws + (b & 1) - pW;
+      if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+        const uint16_t* src = x + n * sn + ih * sh + iw * sw;
+        for (int c = 0; c < C; ++c)
+          if (b * C + c < CP) v[b * C + c] = __ldg(src + c * sc);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + i * CP);
+#pragma unroll
+    for (int j = 0; j < CP / 8; ++j) dst[j] = reinterpret_cast<const uint4*>(v)[j];
+  }
+}
+}  // namespace dl4j
+
+// x: 16-bit elements (bf16 or fp16) [N, C, H, W] addressed with element strides {sn, sc, sh, sw}; out [N, Hs, Ws, CP] contiguous,
+// CP in {8, 16, 32} and 4 C <= CP.
+DL4J_API int dl4j_stem_space_to_depth(const void* x, void* out, int N, int C, int H, int W, const long long* strides, int pH, int pW,
+                                      int Hs, int Ws, int CP, void* stream) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || Hs <= 0 || Ws <= 0) return 0;
+  if (!x || !out || !strides || 4 * C > CP || ((uintptr_t)out & 15)) return -DL4J_ERR_BAD_ARG;
+  const long long total = (long long)N * Hs * Ws;
+  const int grid = pl_grid(total);
+  const uint16_t* xi = reinterpret_cast<const uint16_t*>(x);
+  uint16_t* o = reinterpret_cast<uint16_t*>(out);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (CP == 8) stem_s2d_kernel<8><<<grid, 256, 0, st>>>(xi, o, N, C, H, W, strides[0], strides[1], strides[2], strides[3], pH, pW, Hs, Ws);
+  else if (CP == 16) stem_s2d_kernel<16><<<grid, 256, 0, st>>>(xi, o, N, C, H, W, strides[0], strides[1], strides[2], strides[3], pH, pW, Hs, Ws);
+  else if (CP == 32) stem_s2d_kernel<32><<<grid, 256, 0, st>>>(xi, o, N, C, H, W, strides[0], strides[1], strides[2], strides[3], pH, pW, Hs, Ws);
+  else return -DL4J_ERR_BAD_ARG;
+  return (int)cudaGetLastError();
+}

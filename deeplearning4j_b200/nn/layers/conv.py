@@ -168,16 +168,22 @@ def _stem_space_to_depth(x, W, b, k, pad):
     OH, OW = (H + 2 * pad[0] - kH) // 2 + 1, (Wd + 2 * pad[1] - kW) // 2 + 1
     KH2, KW2 = (kH + 1) // 2, (kW + 1) // 2
     Hs, Ws = OH + KH2 - 1, OW + KW2 - 1                    # space-to-depth extent the stride-1 convolution needs
-    eh, ew = 2 * Hs - (H + 2 * pad[0]), 2 * Ws - (Wd + 2 * pad[1])
-    xp = F.pad(x, (pad[1], pad[1] + max(ew, 0), pad[0], pad[0] + max(eh, 0)))[:, :, :2 * Hs, :2 * Ws]
-    xs = xp.reshape(N, C, Hs, 2, Ws, 2).permute(0, 3, 5, 1, 2, 4).reshape(N, 4 * C, Hs, Ws)
     W8 = F.pad(W, (0, 2 * KW2 - kW, 0, 2 * KH2 - kH))
     Wsd = W8.reshape(W.shape[0], C, KH2, 2, KW2, 2).permute(0, 3, 5, 1, 2, 4).reshape(W.shape[0], 4 * C, KH2, KW2)
     cpad = (-4 * C) % 8
     if cpad:
-        xs = F.pad(xs, (0, 0, 0, 0, 0, cpad))
         Wsd = F.pad(Wsd, (0, 0, 0, 0, 0, cpad))
-    xs = xs.contiguous(memory_format=torch.channels_last)
+    xs = None
+    if x.is_cuda and not x.requires_grad and not nnops._FORCE_TORCH:
+        from ...ops import native as nat
+        xs = nat.stem_space_to_depth(x, pad, Hs, Ws, 4 * C + cpad)      # one kernel: padded 2x2 view, channels-last, padded channels
+    if xs is None:
+        eh, ew = 2 * Hs - (H + 2 * pad[0]), 2 * Ws - (Wd + 2 * pad[1])
+        xp = F.pad(x, (pad[1], pad[1] + max(ew, 0), pad[0], pad[0] + max(eh, 0)))[:, :, :2 * Hs, :2 * Ws]
+        xs = xp.reshape(N, C, Hs, 2, Ws, 2).permute(0, 3, 5, 1, 2, 4).reshape(N, 4 * C, Hs, Ws)
+        if cpad:
+            xs = F.pad(xs, (0, 0, 0, 0, 0, cpad))
+        xs = xs.contiguous(memory_format=torch.channels_last)
     return F.conv2d(xs, Wsd, b)
 
 

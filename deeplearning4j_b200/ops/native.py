@@ -749,6 +749,28 @@ class _SubsampleFn(torch.autograd.Function):
         return dx, None, None
 
 
+def stem_space_to_depth(x, pad, Hs, Ws, CP):
+    """2x2 space-to-depth view of the zero-padded input ``x`` [N, C, H, W] (16-bit, any strides, no gradient) as a channels-last
+    tensor [N, CP, Hs, Ws] with channel (bh * 2 + bw) * C + c; one pass instead of pad / reshape / permute / pad / contiguous.
+    Returns None when the case is not covered."""
+    if not available() or x.requires_grad or x.dtype not in (torch.bfloat16, torch.float16) or CP not in (8, 16, 32):
+        return None
+    N, C, H, W = x.shape
+    if 4 * C > CP:
+        return None
+    l = require()
+    if not hasattr(l.dl4j_stem_space_to_depth, "_typed"):
+        vp, i32 = ctypes.c_void_p, ctypes.c_int
+        l.dl4j_stem_space_to_depth.argtypes = [vp, vp, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_longlong), i32, i32, i32, i32, i32, vp]
+        l.dl4j_stem_space_to_depth.restype = ctypes.c_int
+        l.dl4j_stem_space_to_depth._typed = True
+    out = torch.empty((N, Hs, Ws, CP), dtype=x.dtype, device=x.device)
+    st = (ctypes.c_longlong * 4)(*x.stride())
+    rc = l.dl4j_stem_space_to_depth(_ptr(x), _ptr(out), N, C, H, W, st, int(pad[0]), int(pad[1]), Hs, Ws, CP, _stream())
+    _check(rc, "dl4j_stem_space_to_depth")
+    return out.permute(0, 3, 1, 2)
+
+
 def conv1x1(x, W, b, stride=(1, 1)):
     """1x1 convolution over a channels-last activation as one tcgen05 GEMM: [N*H*W, Cin] x [Cin, Cout] (forward, data
     gradient and weight gradient all run on the hand-written kernel).  ``W`` is the [Cout, Cin, 1, 1] parameter; returns

@@ -94,3 +94,25 @@ def test_conv_weight_channels_last_relayout_and_gradient(nat):
     Wr = W.detach().clone().requires_grad_(True)
     (F.conv2d(x.float(), Wr.bfloat16().float(), None, padding=1) * w.float()).sum().backward()
     assert _rel(got, Wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("shape,k,pad", [((4, 3, 224, 224), 7, 3), ((3, 3, 37, 41), 7, 3), ((2, 1, 30, 30), 3, 1), ((2, 4, 33, 32), 5, 2)])
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_stem_space_to_depth_kernel_matches_the_torch_construction(shape, k, pad, channels_last):
+    import torch.nn.functional as F
+    from deeplearning4j_b200.ops import native as nat
+    N, C, H, W = shape
+    x = torch.randn(shape, device="cuda").bfloat16()
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
+    OH, OW = (H + 2 * pad - k) // 2 + 1, (W + 2 * pad - k) // 2 + 1
+    K2 = (k + 1) // 2
+    Hs, Ws = OH + K2 - 1, OW + K2 - 1
+    cp = 4 * C + (-4 * C) % 8
+    got = nat.stem_space_to_depth(x, (pad, pad), Hs, Ws, cp)
+    assert got is not None and got.shape == (N, cp, Hs, Ws) and got.is_contiguous(memory_format=torch.channels_last)
+    eh, ew = 2 * Hs - (H + 2 * pad), 2 * Ws - (W + 2 * pad)
+    xp = F.pad(x, (pad, pad + max(ew, 0), pad, pad + max(eh, 0)))[:, :, :2 * Hs, :2 * Ws]
+    ref = xp.reshape(N, C, Hs, 2, Ws, 2).permute(0, 3, 5, 1, 2, 4).reshape(N, 4 * C, Hs, Ws)
+    ref = F.pad(ref, (0, 0, 0, 0, 0, cp - 4 * C))
+    assert torch.equal(got, ref)
