@@ -839,8 +839,11 @@ class BatchNormalization(FeedForwardLayer):
         if not nnops._FORCE_TORCH and x.dim() in (2, 4) and mean.dtype == torch.float32 and nat.bn_supported(x):
             # hand-written channels-last kernels: statistics, running-stat update, normalise (+ add) (+ ReLU)
             if training:
-                y = nat.bn_act_train(x, residual, g, b, mean.detach(), sv.detach(), self.useLogStd, self.decay, self.eps, fuse_relu,
-                                     pre_bias)
+                # the parameter leaves themselves (not reshaped views): the backward kernel then adds dgamma / dbeta straight into
+                # their slices of the flat gradient buffer and autograd launches no accumulation kernels
+                g_leaf, b_leaf = (g, b) if self.lockGammaBeta else (p["gamma"], p["beta"])
+                y = nat.bn_act_train(x, residual, g_leaf, b_leaf, mean.detach(), sv.detach(), self.useLogStd, self.decay, self.eps,
+                                     fuse_relu, pre_bias)
             else:
                 with torch.no_grad():
                     var = torch.pow(10.0, 2.0 * sv) if self.useLogStd else sv

@@ -876,6 +876,7 @@ class _BnActFn(torch.autograd.Function):
         global LAUNCHES
         LAUNCHES += 2
         ctx.relu, ctx.has_res, ctx.has_affine = bool(relu), res is not None, gamma is not None
+        ctx.gb_refs = (gamma, beta)
         ctx.save_for_backward(x, y if (res is not None and relu) else None, save, work)
         return y
 
@@ -887,14 +888,27 @@ class _BnActFn(torch.autograd.Function):
         dy = _dense_cl(dy)
         dx = torch.empty_like(x)
         dres = torch.empty_like(x) if ctx.has_res else None
-        dgb = torch.zeros(2 * C, dtype=torch.float32, device=x.device) if ctx.has_affine else None
+        # the kernel adds dgamma / dbeta to what its targets hold: the parameters' preallocated fp32 gradients when they have
+        # them (nothing is returned then, so autograd launches no accumulation), else a zeroed scratch that is returned
+        def target(p_):
+            if p_ is not None and p_.is_leaf and p_.grad is not None and p_.grad.dtype == torch.float32 and p_.grad.is_contiguous() \
+                    and p_.grad.numel() == C:
+                return p_.grad
+            return None
+        gamma, beta = ctx.gb_refs
+        tg, tb = (target(gamma), target(beta)) if ctx.has_affine else (None, None)
+        dgb = None
+        if ctx.has_affine and (tg is None or tb is None):
+            dgb = torch.zeros(2 * C, dtype=torch.float32, device=x.device)
+        pg = tg if tg is not None else (dgb[:C] if dgb is not None else None)
+        pb = tb if tb is not None else (dgb[C:] if dgb is not None else None)
         rc = l.dl4j_bn_bwd(_ptr(dy), _ptr(x), _ptr(y), _ptr(save), _ptr(save[C:]), _ptr(work), _ptr(dx), _ptr(dres),
-                           _ptr(dgb), _ptr(dgb[C:]) if dgb is not None else None, rows, C, int(ctx.relu), _stream())
+                           _ptr(pg), _ptr(pb), rows, C, int(ctx.relu), _stream())
         _check(rc, "dl4j_bn_bwd")
         global LAUNCHES
         LAUNCHES += 1
-        dg = dgb[:C] if dgb is not None and ctx.needs_input_grad[2] else None
-        db = dgb[C:] if dgb is not None and ctx.needs_input_grad[3] else None
+        dg = pg.reshape(gamma.shape) if (ctx.has_affine and tg is None and ctx.needs_input_grad[2]) else None
+        db = pb.reshape(beta.shape) if (ctx.has_affine and tb is None and ctx.needs_input_grad[3]) else None
         return dx, dres, dg, db, None, None, None, None, None, None, None
 
 
