@@ -975,7 +975,7 @@ def attention(q, k, v, mask, scale):
 # =========================================================================== fused updater
 _SEG_FMT = "<qqqqqfffiii"     # offset, block_start, block_numel, state_off, shadow_off, l1, l2, wd, kernel_id, hyper, pad
 _CHUNK_FMT = "<qii"
-_CHUNK = 16384
+_CHUNK = int(os.environ.get("DL4J_UPDATER_CHUNK", "16384"))     # elements per block of the multi-segment updater launch
 
 
 def _cfg_index(known, cfg):
