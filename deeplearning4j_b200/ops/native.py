@@ -923,8 +923,8 @@ def bn_act_train(x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, ep
     """Fused training-mode batch norm; ``gamma`` / ``beta`` fp32 [C] (or None), running buffers fp32 [C] updated in place.
     ``pre_bias`` (fp32 [C]) is a bias that the producer left out of ``x``: it only enters the running mean."""
     pb = pre_bias.detach().float().reshape(-1).contiguous() if pre_bias is not None else None
-    return _BnActFn.apply(x, res, gamma.reshape(-1) if gamma is not None else None, beta.reshape(-1) if beta is not None else None,
-                          run_mean, run_stat, use_log_std, decay, eps, relu, pb)
+    # gamma / beta go in as they are (any shape with C elements): a reshape would hide a parameter leaf and its gradient slice
+    return _BnActFn.apply(x, res, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, relu, pb)
 
 
 def bn_act_eval(x, res, scale, shift, relu):
