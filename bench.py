@@ -25,7 +25,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def _reference_arm():
     why = ("reference is a JVM/Maven project (no setup.py/pyproject; needs JDK+Maven+JavaCPP and downloads FlatBuffers at "
-           "configure time): pip install of /root/reference found nothing to build")
+           "configure time): pip install of the reference tree found nothing to build")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 

@@ -29,6 +29,11 @@ extern "C" {
 //   accumulate == 0: dgain / dbias are overwritten;  accumulate != 0: the sums are added to their contents.
 //   dtype: 0 = float16, 1 = bfloat16, 2 = float32 (dy, x, dx; the codes every entry point of the library uses); gain, mean, rstd, dgain, dbias are float32.
 //   dgain and dbias may be null (that gradient is then skipped).
+//   Alignment: dy, x, dx and gain must start on a 16-byte boundary (they are moved with 16-byte vector accesses; with
+//   C % 8 == 0 every row then keeps that alignment); mean, rstd, dgain and dbias on a 4-byte boundary.  A pointer that
+//   breaks this is rejected with -6 before anything is launched.
+//   `stream` must belong to the device that is current at the call: the scratch address is looked up for the current
+//   device, and a stream of another device is not supported.
 //
 // Memory: the routine allocates nothing (no cudaMalloc / cudaFree, no allocating library call).  Its
 // scratch (256 B of counters + DL4J_NOALLOC_LN_MAX_BLOCKS * 2 * DL4J_NOALLOC_LN_MAX_C floats, about
@@ -41,7 +46,7 @@ extern "C" {
 // streams, or several host threads) race on it and must be serialised by the caller.
 //
 // Returns 0 on success; -6 for sizes beyond the limits above (C % 8 != 0, C > DL4J_NOALLOC_LN_MAX_C,
-// rows < 1) or a bad dtype / null pointer -- a one-line reason is written to stderr; a positive value
+// rows < 1), a bad dtype, a null or misaligned pointer -- a one-line reason is written to stderr; a positive value
 // is a cudaError_t from set-up or launch.
 int dl4j_layer_norm_bwd_noalloc(const void* dy, const void* x, const float* gain, const float* mean, const float* rstd,
                                 void* dx, float* dgain, float* dbias, long long rows, int C, int dtype, int accumulate,

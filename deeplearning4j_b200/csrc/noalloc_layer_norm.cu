@@ -112,7 +112,9 @@ ln_bwd_scratch_kernel(const T* __restrict__ dy, const T* __restrict__ x, const f
   __shared__ float red[NA_WARPS][32 * 8 + 1];
   __shared__ bool is_last;
   float* mine = partial + (size_t)blockIdx.x * 2 * DL4J_NOALLOC_LN_MAX_C;
-  for (int i = 0; i < NA_MAXV; ++i) {
+#pragma unroll
+  for (int i = 0; i < NA_MAXV; ++i) {            // unrolled: ag / ab are indexed by constants and stay in registers
+#pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
       __syncthreads();
 #pragma unroll
@@ -186,6 +188,13 @@ DL4J_API int dl4j_layer_norm_bwd_noalloc(const void* dy, const void* x, const fl
   if (rows < 1 || rows > DL4J_NOALLOC_LN_MAX_ROWS) return reject("rows out of range", rows, C);
   if (dtype < 0 || dtype > 2) return reject("dtype must be 0 (f16), 1 (bf16) or 2 (f32)", rows, C);
   if (!dy || !x || !gain || !mean || !rstd || !dx) return reject("null input or dx pointer", rows, C);
+  // the kernel moves dy / x / dx / gain with 16-byte vector accesses; rows keep the base's alignment because C % 8 == 0
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) |
+       reinterpret_cast<uintptr_t>(gain)) & 15)
+    return reject("dy, x, dx and gain must be 16-byte aligned", rows, C);
+  if ((reinterpret_cast<uintptr_t>(mean) | reinterpret_cast<uintptr_t>(rstd) | reinterpret_cast<uintptr_t>(dgain) |
+       reinterpret_cast<uintptr_t>(dbias)) & 3)
+    return reject("mean, rstd, dgain and dbias must be 4-byte aligned", rows, C);
   unsigned char* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != 0) return rc;

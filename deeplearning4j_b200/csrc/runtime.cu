@@ -44,6 +44,16 @@ DL4J_API int dl4j_read_status(int reset) {
   return v;
 }
 
+// Queues an asynchronous copy of the status word into `pinned_host` (4 bytes of page-locked memory) on `stream`:
+// the host learns of an expired wait one step later without synchronising the device.
+DL4J_API int dl4j_status_snapshot(void* pinned_host, void* stream) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* p = dl4j_status_word(dev);
+  if (!p || !pinned_host) return -1;
+  return (int)cudaMemcpyAsync(pinned_host, p, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+}
+
 DL4J_API void* dl4j_status_ptr() {
   int dev = 0;
   cudaGetDevice(&dev);

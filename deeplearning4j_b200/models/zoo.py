@@ -93,7 +93,10 @@ class _ZooBuilder:
 
 # ----------------------------------------------------------------------------- ResNet-50
 class ResNet50(ZooModel):
-    DEFAULT_WEIGHT_INIT = WeightInit.get(NormalDistribution(0.0, 0.5)) if False else "RELU"
+    # the reference default is a truncated normal (0, 0.5) (ResNet50.java:55), which diverges without pretrained weights
+    # at the first steps of a from-scratch run; He initialisation ("RELU") is this zoo's default, the reference's is
+    # available through ``weightInit=WeightInitDistribution(TruncatedNormalDistribution(0.0, 0.5))``
+    DEFAULT_WEIGHT_INIT = "RELU"
 
     def default_updater(self):
         return RmsProp(0.1, 0.96, 0.001)

@@ -49,6 +49,7 @@ class BaseNetwork:
         self.gradient_hook = None       # set by ParallelWrapper: called between backward and the updater
         self.flat_shadow = None
         self.shadow_offsets = None
+        self.asyncPrefetch = 2          # depth of the background batch prefetcher used by fit(iterator)
 
     # ------------------------------------------------------------------ to be provided by subclasses
     def _owners(self):
@@ -160,6 +161,10 @@ class BaseNetwork:
             self.updater.params, self.updater.grads = self.flat_params, self.flat_grads
             self.updater.shadow, self.updater.shadow_offsets = self.flat_shadow, self.shadow_offsets
             self.updater._native_tables = None
+        # graphs captured earlier read the old parameter / shadow storage and write the old gradient buffer
+        cg = getattr(self, "_cg", None)
+        if cg is not None:
+            cg["entries"] = {}
 
     def _ensure_updater(self):
         if self.updater is None:
@@ -371,8 +376,9 @@ class BaseNetwork:
             self._fire("onEpochStart")
             t0 = time.perf_counter()
             src = it
-            if getattr(it, "asyncSupported", lambda: False)() and not isinstance(it, AsyncDataSetIterator):
-                src = AsyncDataSetIterator(it, 2, device=self.device)
+            depth = int(getattr(self, "asyncPrefetch", 2))
+            if depth > 0 and getattr(it, "asyncSupported", lambda: False)() and not isinstance(it, AsyncDataSetIterator):
+                src = AsyncDataSetIterator(it, depth, device=self.device)
             for ds in src:
                 self._last_etl_ms = (time.perf_counter() - t0) * 1e3
                 self._fit_batch(ds)

@@ -161,6 +161,14 @@ class ElasticTrainer:
         self.net.setEpochCount(loaded.getEpochCount())
         return last.iteration
 
+    def _check_device_status(self, wait=False):
+        """Outcome of the previous step's fused gradient exchange (a bounded device-side wait that gave up): raises
+        ``PeerFailure`` / ``StepTimeout``; the poller has then cleared the status word and the stale gradients."""
+        hook = getattr(self.net, "gradient_hook", None)
+        poller = getattr(getattr(hook, "fused", None), "status", None)
+        if poller is not None:
+            poller.check(wait=wait)
+
     # ------------------------------------------------------------------ training
     def fit(self, batches, onFailure=None):
         """Runs ``net.fit`` over ``batches`` (iterable of ``(features, labels)`` or DataSets).  Before every step the peers'
@@ -173,6 +181,7 @@ class ElasticTrainer:
                 if self.monitor is not None:
                     self.monitor.beat(it)
                     self.monitor.check()
+                self._check_device_status()
                 if isinstance(b, (tuple, list)):
                     self.net.fit(*b)
                 else:
@@ -180,6 +189,7 @@ class ElasticTrainer:
                 done += 1
                 if self.ckpt is not None:
                     self.ckpt.iterationDone(self.net, self.net.getIterationCount() - 1, self.net.getEpochCount())
+            self._check_device_status(wait=True)
         except PeerFailure:
             if onFailure is not None:
                 onFailure(self)

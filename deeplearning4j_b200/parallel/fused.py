@@ -59,11 +59,70 @@ class SymmetricAllocator:
         return h
 
 
+_STATUS_NAMES = {1: "TMA producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "peer wait", 5: "index out of bounds"}
+
+
+class DeviceStatusPoller:
+    """Surfaces the device status word (bounded waits that gave up) in the training path without a device sync.
+
+    After every fused launch ``snapshot()`` queues a 4-byte copy of the word into pinned memory and records an event;
+    ``check()`` (called before the next launch, and by ``ElasticTrainer`` at heartbeat time) reads the value once the
+    event has completed.  A non-zero value means the kernel skipped its update *and* left the gradients uncleared, so the
+    poller zeroes the gradient buffer, clears the word (it is sticky: every later bounded wait would bail out at once) and
+    raises ``PeerFailure`` (peer wait) or ``StepTimeout`` (any other bounded wait)."""
+
+    def __init__(self, grads=None):
+        self.grads = grads
+        self._pending = None        # (event, pinned tensor)
+        self._pinned = None
+
+    # -- device access, overridable in host-only tests -----------------------------------------------------------
+    def _queue_copy(self):
+        lib = native.require()
+        if self._pinned is None:
+            self._pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+            lib.dl4j_status_snapshot.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+            lib.dl4j_status_snapshot.restype = ctypes.c_int
+        rc = lib.dl4j_status_snapshot(ctypes.c_void_p(self._pinned.data_ptr()), native._stream())
+        native._check(rc, "dl4j_status_snapshot")
+        ev = torch.cuda.Event()
+        ev.record()
+        return ev, self._pinned
+
+    def _clear_word(self):
+        native.require().dl4j_read_status(1)
+
+    # -------------------------------------------------------------------------------------------------------------
+    def snapshot(self):
+        self._pending = self._queue_copy()
+
+    def check(self, wait=False):
+        if self._pending is None:
+            return 0
+        ev, pinned = self._pending
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return 0
+        self._pending = None
+        v = int(pinned[0])
+        if v == 0:
+            return 0
+        self._clear_word()
+        if self.grads is not None:
+            self.grads.zero_()          # the kernel left them uncleared; the next backward must not accumulate onto them
+        from .elastic import PeerFailure, StepTimeout
+        what = _STATUS_NAMES.get(v, str(v))
+        if v == 4:
+            raise PeerFailure(-1, f"device-side {what} expired in the fused gradient exchange; the step was skipped")
+        raise StepTimeout(f"device-side {what} expired; the step was skipped")
+
+
 class FusedSharing:
     """Per-model state for the fused kernels (one instance per training state / network)."""
 
     def __init__(self, params, grads, shadow, updater, alloc: SymmetricAllocator, use_multimem=None, message_ints=0):
-        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.rank, self.world = dist.get_rank(alloc.group), dist.get_world_size(alloc.group)
         if self.world > MAX_RANKS:
             raise ValueError(f"fused gradient sharing supports up to {MAX_RANKS} ranks on one node")
         self.params, self.grads, self.shadow, self.updater = params, grads, shadow, updater
@@ -96,6 +155,7 @@ class FusedSharing:
         self.args = a
         self._handles = (hp, hg, hs, hm)
         self.scratch = torch.zeros(64, dtype=torch.int32, device=dev)
+        self.status = DeviceStatusPoller(grads)
         self.epoch = 0
         self.residual = None
         lib = native.require()
@@ -108,7 +168,7 @@ class FusedSharing:
         lib.dl4j_shadow_refresh.restype = i32
         self.lib = lib
         # signal pads start zeroed; make sure every rank is set up before the first kernel touches a peer
-        dist.barrier()
+        dist.barrier(group=alloc.group)
 
     def allreduce_update(self, iteration, epoch):
         """Dense averaging: mean gradient over ranks -> updater -> new parameters on every rank."""
@@ -116,6 +176,7 @@ class FusedSharing:
         t = native.update_tables(upd, iteration, epoch, upd.shadow_offsets)
         if t is None:
             raise RuntimeError("updater configuration is not supported by the fused kernel")
+        self.status.check()               # outcome of the previous step's launch (raises PeerFailure / StepTimeout)
         self.epoch += 1
         hp = t["hyper"].ctypes.data_as(ctypes.c_void_p)
         st = upd.state
@@ -124,6 +185,7 @@ class FusedSharing:
                                             1.0 / self.world, self.params.numel(), self.epoch, native._ptr(self.scratch),
                                             1 if self.use_multimem else 0, native._stream())
         native._check(rc, "dl4j_allreduce_update")
+        self.status.snapshot()
         upd._fused_zeroes_grads = True
         upd._shadow_fresh = self.shadow is not None
 
@@ -135,6 +197,7 @@ class FusedSharing:
             raise RuntimeError("updater configuration is not supported by the fused kernel")
         if self.residual is None:
             self.residual = torch.zeros_like(self.params)
+        self.status.check()
         self.epoch += 1
         hp = t["hyper"].ctypes.data_as(ctypes.c_void_p)
         st = upd.state
@@ -147,5 +210,6 @@ class FusedSharing:
             rc = self.lib.dl4j_shadow_refresh(native._ptr(self.params), native._ptr(self.shadow), native._ptr(t["chunks"]),
                                               t["n_chunks"], native._ptr(t["segs_dev"]), native._stream())
             native._check(rc, "dl4j_shadow_refresh")
+        self.status.snapshot()
         upd._fused_zeroes_grads = True
         upd._shadow_fresh = self.shadow is not None

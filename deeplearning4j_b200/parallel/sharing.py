@@ -228,6 +228,10 @@ def attach_gradient_sharing(model, mode="averaging", impl="auto", thresholdAlgor
     on_gpu = t.params.is_cuda
     if impl == "auto":
         impl = "fused" if (on_gpu and symmetric_available()) else "host"
+    if impl == "fused" and getattr(t.updater, "needs_pre_apply", lambda: False)():
+        # per-layer gradient normalisation / clipping acts on the reduced gradient before the updater; the fused kernels do not
+        # do that, so such networks take the library collectives, which keep the normalisation
+        impl = "nccl" if mode == "averaging" else "host"
     if impl == "fused":
         alloc = SymmetricAllocator(group)
         _rehome(model, alloc)

@@ -68,7 +68,8 @@ class _ShardedIterator:
 class ParallelWrapper:
     def __init__(self, model, workers=None, prefetchBuffer=2, averagingFrequency=1, averageUpdaters=True,
                  reportScoreAfterAveraging=False, trainingMode=TrainingMode.AVERAGING, thresholdAlgorithm=None,
-                 residualPostProcessor=None, impl="auto", shardData=True, group=None):
+                 residualPostProcessor=None, impl="auto", shardData=True, group=None, workspaceMode=None,
+                 gradientsAccumulator=None):
         init_process_group()
         self.model = model
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -82,7 +83,17 @@ class ParallelWrapper:
             model.init()
         self.sharing = None
         target = self._target()
-        if self.world > 1:
+        if workspaceMode is not None:
+            for setter in ("setTrainingWorkspaceMode", "setInferenceWorkspaceMode"):
+                conf = getattr(model, "conf", None)
+                if conf is not None and hasattr(conf, setter):
+                    getattr(conf, setter)(workspaceMode)
+            self.workspaceMode = workspaceMode
+        if gradientsAccumulator is not None:
+            if trainingMode != TrainingMode.CUSTOM:
+                raise ValueError("gradientsAccumulator needs trainingMode(TrainingMode.CUSTOM)")
+            target.gradient_hook = gradientsAccumulator
+        elif self.world > 1:
             if trainingMode == TrainingMode.SHARED_GRADIENTS:
                 self.sharing = attach_gradient_sharing(target, "shared_gradients", impl, thresholdAlgorithm or AdaptiveThresholdAlgorithm(1e-3),
                                                        residualPostProcessor, group)
@@ -121,6 +132,8 @@ class ParallelWrapper:
 
     def fit(self, iterator, epochs=1):
         it = _ShardedIterator(iterator, self.rank, self.world) if (self.world > 1 and self.shardData) else iterator
+        if hasattr(self.model, "asyncPrefetch"):
+            self.model.asyncPrefetch = int(self.prefetchBuffer or 0)   # depth of the model's background batch prefetcher
         self.model.fit(it, epochs)
         if self.reportScoreAfterAveraging and self.world > 1 and hasattr(self.model, "score"):
             s = torch.tensor([float(self.model.score())], dtype=torch.float64, device=self._target().flat_params.device)
@@ -147,8 +160,17 @@ class ParallelWrapper:
         def trainingMode(self, m): self.kw["trainingMode"] = m; return self
         def thresholdAlgorithm(self, a): self.kw["thresholdAlgorithm"] = a; return self
         def residualPostProcessor(self, p): self.kw["residualPostProcessor"] = p; return self
-        def workspaceMode(self, m): return self
-        def gradientsAccumulator(self, a): return self
+        def workspaceMode(self, m):
+            """Applied to the wrapped model's training/inference workspace mode, as the reference builder does."""
+            self.kw["workspaceMode"] = m
+            return self
+
+        def gradientsAccumulator(self, a):
+            """A custom accumulator object: anything callable as ``hook(target) -> bool`` (TrainingMode.CUSTOM)."""
+            if not callable(a):
+                raise TypeError("gradientsAccumulator expects a callable gradient hook (target) -> handled?")
+            self.kw["gradientsAccumulator"] = a
+            return self
         def impl(self, i): self.kw["impl"] = i; return self
         def build(self): return ParallelWrapper(self.model, **self.kw)
 
@@ -212,7 +234,12 @@ class SharedTrainingMaster:
         def workersPerNode(self, n): self.kw["workersPerNode"] = n; return self
         def thresholdAlgorithm(self, a): self.kw["thresholdAlgorithm"] = a; return self
         def residualPostProcessor(self, p): self.kw["residualPostProcessor"] = p; return self
-        def rddTrainingApproach(self, a): return self
+        def rddTrainingApproach(self, a):
+            """Spark RDD export/direct switch: there is no Spark here, only the in-memory ("Direct") behaviour exists."""
+            if str(a).rsplit(".", 1)[-1] not in ("Direct", "DIRECT"):
+                raise ValueError("only RDDTrainingApproach.Direct is available (no Spark export path in this framework)")
+            self.kw["rddTrainingApproach"] = "Direct"
+            return self
         def build(self): return SharedTrainingMaster(**self.kw)
 
 

@@ -116,3 +116,50 @@ def test_heartbeat_timeout_and_watchdog_without_a_device():
     with pytest.raises(StepTimeout):
         wd.check()
     wd.close()
+
+
+def test_device_status_is_surfaced_through_elastic_trainer(tmp_path):
+    """A bounded device-side wait that gave up is reported one step later: the poller clears the sticky status word, zeroes the
+    gradients the kernel left behind and the trainer raises.  The device access is replaced by a host stand-in (no GPU)."""
+    from deeplearning4j_b200.parallel.elastic import ElasticTrainer, PeerFailure
+    from deeplearning4j_b200.parallel.fused import DeviceStatusPoller
+
+    class FakeEvent:
+        def query(self): return True
+        def synchronize(self): pass
+
+    class FakePoller(DeviceStatusPoller):
+        word = 0
+        cleared = 0
+
+        def _queue_copy(self):
+            return FakeEvent(), torch.tensor([self.word], dtype=torch.int32)
+
+        def _clear_word(self):
+            self.cleared += 1
+            self.word = 0
+
+    net = _net()
+    poller = FakePoller(net.flat_grads)
+
+    class Hook:                        # stands in for FusedAveraging: steps nothing, reports through the poller
+        class fused:
+            status = poller
+
+        def __call__(self, model):
+            poller.check()
+            poller.snapshot()
+            if model.iterationCount == 2:
+                poller.word = 4        # the *next* snapshot sees an expired peer wait
+            return False
+    net.gradient_hook = Hook()
+    trainer = ElasticTrainer(net, str(tmp_path / "ckpt"), checkpointEvery=100)
+    net.flat_grads.fill_(3.0)
+    with pytest.raises(PeerFailure):
+        trainer.fit(_batches(8, 1))
+    assert poller.cleared == 1 and poller.word == 0
+    assert float(net.flat_grads.abs().sum()) == 0.0          # stale gradients were dropped
+    assert net.getIterationCount() < 8
+    # the word is clear again: training continues
+    done = trainer.fit(_batches(2, 2))
+    assert done == 2

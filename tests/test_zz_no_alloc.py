@@ -134,4 +134,10 @@ def test_sizes_beyond_the_scratch_are_rejected(lib, capfd):
     assert lib.dl4j_layer_norm_bwd_noalloc(*args, 8, 100, 2, 0, s) == -6       # not a multiple of 8
     assert lib.dl4j_layer_norm_bwd_noalloc(*args, 0, 1024, 2, 0, s) == -6      # no rows
     assert lib.dl4j_layer_norm_bwd_noalloc(*args, 8, 1024, 9, 0, s) == -6      # unknown dtype
+    # a base pointer that is not 16-byte aligned would make the kernel's vector accesses fault: refused up front
+    off = ctypes.c_void_p(x.data_ptr() + 4)
+    capfd.readouterr()
+    assert lib.dl4j_layer_norm_bwd_noalloc(_p(dy), off, _p(gain), _p(mean), _p(rstd), _p(dx), None, None, 4, 1024, 2, 0, s) == -6
+    assert "16-byte aligned" in capfd.readouterr().err
+    assert lib.dl4j_layer_norm_bwd_noalloc(_p(dy), _p(x), _p(gain), _p(mean), _p(rstd), off, None, None, 4, 1024, 2, 0, s) == -6
     torch.cuda.synchronize()
