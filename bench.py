@@ -7,9 +7,12 @@ GPU) runs W untimed + K timed training steps of the BERT-base-shaped SameDiff gr
 compute with fp32 master weights, synthetic uniform token ids, 15 % masked positions) and prints one
 JSON line.  ``value`` is timed on the device with inputs resident; ``e2e`` times the same steps
 through ``sd.fit`` including the host->device copy of each step's inputs from pinned memory and a
-device->host read of the loss.  ``--config`` selects the other BASELINE configurations
-(``resnet50``, ``lstm``, ``mlp``, ``gradshare``); ``--impl reference`` reports why the reference
-cannot run here.
+device->host read of the loss.  ``--config`` selects one other BASELINE configuration
+(``resnet50``, ``lstm``, ``mlp``, ``gradshare``).  The default run measures the whole headline metric: after BERT it
+times ResNet-50 (same steps / warm-up) and, for N >= 2, the gradient-exchange microbenchmark, and reports them under
+``secondary`` of the same JSON line (``--no-secondary`` skips them).  For N >= 2 every runner also checks that the
+replicas hold bit-identical parameters after the timed region (``replicas_equal``); a mismatch ends the run with a
+non-zero exit code.  ``--impl reference`` reports why the reference cannot run here.
 """
 from __future__ import annotations
 
@@ -86,6 +89,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="layer-count override (debug only; invalidates the number)")
     ap.add_argument("--library-baseline", action="store_true", help="route ops through torch/cuBLAS + NCCL (baseline B1)")
     ap.add_argument("--mode", default="fused", help="gradient exchange for N>1: fused | nccl")
+    ap.add_argument("--no-secondary", action="store_true", help="default run: BERT only (skip ResNet-50 and gradshare)")
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm()
@@ -105,12 +109,38 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    runner = runners.get(args.config)(args, rank, world, torch.device("cuda", local))
+    device = torch.device("cuda", local)
+    runner = runners.get(args.config)(args, rank, world, device)
     sampler = ClockSampler(local)
     result = runner.run(sampler)
+    bad = result.get("replicas_equal") is False
+    if args.config == "bert" and not args.no_secondary and not args.library_baseline and not args.layers and not args.batch:
+        # the other half of the headline metric, measured in the same process right after BERT
+        import gc
+        del runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        secondary = {}
+        keep = ("metric", "value", "unit", "ms_per_step", "e2e", "gpu_launches", "clocks", "config", "replicas_equal", "last_loss",
+                "dtype")
+        r2 = runners.get("resnet50")(args, rank, world, device).run(ClockSampler(local))
+        secondary["resnet50"] = {k: r2[k] for k in keep if k in r2}
+        bad = bad or r2.get("replicas_equal") is False
+        gc.collect()
+        torch.cuda.empty_cache()
+        if world >= 2:
+            r3 = runners.get("gradshare")(args, rank, world, device).run(ClockSampler(local))
+            secondary["gradshare"] = {k: r3[k] for k in ("metric", "value", "unit", "ms_per_step", "rows", "clocks", "config") if k in r3}
+        result["secondary"] = secondary
     if rank == 0:
         result.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "impl": "ours"})
         print(json.dumps(result))
+    if bad:
+        if rank == 0:
+            sys.stderr.write("replicas diverged: parameters differ between ranks after the timed region\n")
+        if world > 1:
+            dist.destroy_process_group()
+        return 3
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

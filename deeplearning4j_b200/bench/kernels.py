@@ -165,7 +165,38 @@ def bench_attention(t, small, rows):
                  "library_ms": ref_b, "library_tflops": 2.5 * fl / ref_b / 1e9})
 
 
-KERNELS = {"gemm": bench_gemm, "layer_norm": bench_layer_norm, "softmax_xent": bench_softmax_xent, "updater": bench_updater,
+def bench_conv(t, small, rows):
+    """3x3 stride-1 convolutions of the ResNet-50 stages (forward; forward + dgrad + wgrad through autograd) against cuDNN."""
+    import torch.nn.functional as F
+    torch.backends.cudnn.benchmark = True
+    shapes = [(64, 64, 55, 64)] if small else [(256, 64, 55, 64), (256, 128, 28, 128), (256, 256, 14, 256), (256, 512, 7, 512)]
+    for N, C, H, O in shapes:
+        x = torch.randn(N, C, H, H, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        W = (torch.randn(O, C, 3, 3, device="cuda") * 0.05).requires_grad_(True)
+        W.grad = torch.zeros_like(W)
+        Wb = W.detach().bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        fl = 2.0 * N * H * H * C * O * 9
+        ms = t(lambda: native.conv2d(x.detach(), W, None, (1, 1), (1, 1)))
+        ref = t(lambda: F.conv2d(x.detach(), Wb.detach(), padding=1))
+        rows.append({"kernel": "conv3x3 fwd (implicit GEMM)", "shape": f"N{N} C{C} H{H} O{O}", "ms": ms, "tflops": fl / ms / 1e9,
+                     "library_ms": ref, "library_tflops": fl / ref / 1e9})
+        y = native.conv2d(x, W, None, (1, 1), (1, 1))
+        dy = torch.randn_like(y)
+
+        def bwd():
+            x.grad = None
+            y.backward(dy, retain_graph=True)
+        yl = F.conv2d(x, Wb, padding=1)
+
+        def bwd_ref():
+            x.grad = Wb.grad = None
+            yl.backward(dy, retain_graph=True)
+        ms_b, ref_b = t(bwd), t(bwd_ref)
+        rows.append({"kernel": "conv3x3 bwd (dgrad + wgrad)", "shape": f"N{N} C{C} H{H} O{O}", "ms": ms_b, "tflops": 2 * fl / ms_b / 1e9,
+                     "library_ms": ref_b, "library_tflops": 2 * fl / ref_b / 1e9})
+
+
+KERNELS = {"conv": bench_conv, "gemm": bench_gemm, "layer_norm": bench_layer_norm, "softmax_xent": bench_softmax_xent, "updater": bench_updater,
            "lstm_cell": bench_lstm_cell, "attention": bench_attention}
 
 

@@ -45,6 +45,23 @@ class BaseRunner:
     def config(self): return {}
     def h2d_bytes(self): return 0
     def d2h_bytes(self): return 4
+    def flat_params(self): return None                      # the replicated fp32 parameter buffer (replica check)
+    def last_loss(self): return getattr(self, "last_loss_value", None)
+
+    def replica_check(self):
+        """After the timed region every data-parallel replica must hold bit-identical parameters: the int32 view of the
+        flat fp32 buffer is summed in int64 (exact) and the sums are compared across ranks."""
+        p = self.flat_params()
+        if self.world == 1 or p is None:
+            return None
+        if isinstance(p, (list, tuple)):
+            p = torch.cat([t.reshape(-1) for t in p])
+        n = p.numel() // 2 * 2
+        words = p.detach()[:n].view(torch.int32).to(torch.int64)
+        mine = torch.stack([words.sum(), (words * (torch.arange(n, device=p.device) % 8191 + 1)).sum()])
+        all_ = [torch.zeros_like(mine) for _ in range(self.world)]
+        dist.all_gather(all_, mine)
+        return all(bool(torch.equal(a, all_[0])) for a in all_)
 
     def _timed(self, fn, steps):
         _barrier(self.world)
@@ -78,6 +95,7 @@ class BaseRunner:
         work = self.work_per_step() * self.world
         value = work / (per_step / 1e3)
         e2e_value = work / (ms_e2e / a.steps / 1e3)
+        equal = self.replica_check()
         cfg = self.config()
         cfg["l2_policy"] = getattr(self, "l2_policy", "inputs+weights+activations per step exceed the 126 MB L2 (no explicit flush)")
         return {"metric": self.metric, "value": value, "unit": self.unit, "ms_per_step": per_step,
@@ -85,7 +103,8 @@ class BaseRunner:
                 "config": cfg, "clocks": clocks,
                 "e2e": {"value": e2e_value, "unit": self.unit, "ms_per_step": ms_e2e / a.steps,
                         "h2d_bytes_per_step": self.h2d_bytes(), "d2h_bytes_per_step": self.d2h_bytes()},
-                "gpu_launches": launches, "library_baseline": bool(a.library_baseline)}
+                "gpu_launches": launches, "library_baseline": bool(a.library_baseline),
+                "replicas_equal": equal, "last_loss": self.last_loss()}
 
 
 class BertRunner(BaseRunner):
@@ -136,7 +155,10 @@ class BertRunner(BaseRunner):
         ph = self.host[self.i % self.n_batches]
         self.i += 1
         hist = self.sd.fit(ph, 1)              # public API: copies inputs H2D, runs the step, reads the loss back
-        self.last_loss = hist.losses[-1][-1]
+        self.last_loss_value = float(hist.losses[-1][-1])
+
+    def flat_params(self):
+        return self.state.flat_params
 
     def work_per_step(self):
         return self.batch * self.seq

@@ -56,6 +56,13 @@ class _NetRunner(BaseRunner):
         y.record_stream(cur)
         self.net.fit(x, y)
         self.last = self.net.score()          # device -> host read of the loss
+        self.last_loss_value = float(self.last)
+
+    def flat_params(self):
+        # every trainable parameter; batch-norm running statistics (kind "state") are local to a replica by design (each
+        # rank normalises with the statistics of the batches it saw), so they are not part of the equality check
+        net = self.net
+        return [net.flat_params[e.offset:e.end] for e in net.entries if e.spec.kind != "state"]
 
     def h2d_bytes(self):
         return sum(t.numel() * t.element_size() for t in self.host[0])
@@ -160,10 +167,12 @@ class GradShareRunner(BaseRunner):
     Reports, per size, the time of one fused dense step (reduce-scatter + SGD + all-gather in one kernel), one
     fused threshold step (updater + encode + exchange + decode + apply) and the NCCL all_reduce + updater baseline,
     with algorithm bandwidth (buffer bytes / time) and the achieved fraction of the NVLink roofline
-    (bytes that must cross the link per GPU / 770 GB/s measured peer-copy bandwidth per direction)."""
+    (bytes that must cross the link per GPU / 900 GB/s nominal per direction; the fraction of the measured 770 GB/s
+    peer-copy bandwidth is reported beside it)."""
     metric = "gradient exchange bandwidth"
     unit = "GB/s"
-    LINK_GBS = 770.0
+    LINK_GBS = 900.0            # nominal NVLink 5 bandwidth per direction and GPU: the roofline denominator
+    LINK_GBS_MEASURED = 770.0   # peer-copy bandwidth measured on this pool, reported beside it
 
     def run(self, sampler):
         from .. import nn
@@ -225,6 +234,7 @@ class GradShareRunner(BaseRunner):
                     # per direction and GPU: reduce-scatter pulls (W-1)/W of the buffer in, all-gather receives the same again
                     link_bytes = 2 * (W - 1) / W * 4 * n
                     res["dense_fused_roofline_frac"] = (link_bytes / (self.LINK_GBS * 1e9)) / (ms / 1e3)
+                    res["dense_fused_frac_of_measured_770"] = (link_bytes / (self.LINK_GBS_MEASURED * 1e9)) / (ms / 1e3)
                     res["dense_fused_multimem"] = bool(s.fused.use_multimem)
                 if key == "threshold_fused":
                     link_bytes = (W - 1) * (n / 16 + 4) * 4

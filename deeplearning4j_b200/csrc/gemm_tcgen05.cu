@@ -43,7 +43,21 @@ struct GemmParams {
   int tma_store;          // epilogue stages tiles in shared memory and writes them with TMA (needs 16-byte aligned C rows)
   int tma_aux;            // same for the auxiliary pre-activation output
   int bias_mma;           // the bias is added on the tensor core: one extra K=16 step ones[128 x 1] x bias[1 x N] per tile
+  int raster_gn;          // tile raster: column-tile groups of this width, column index fastest inside a group
 };
+
+// Tile order.  CTAs that run at the same time take consecutive tile numbers, so the order decides what they share in L2:
+// within a group of `gn` column tiles the column index runs fastest, i.e. the CTAs of one wave cover few row panels of A
+// (each read from DRAM once and hit in L2 by the other column tiles) and at most gn column panels of B.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int gn, int& mt, int& nt) {
+  const int per_group = tiles_m * gn;
+  const int g = tile / per_group;
+  const int n_base = g * gn;
+  const int gw = min(gn, tiles_n - n_base);
+  const int r = tile - g * per_group;
+  mt = r / gw;
+  nt = n_base + (r - mt * gw);
+}
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
 struct GemmSmem {
@@ -186,7 +200,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int batch = w / per_batch, wr = w % per_batch;
         const int b1 = batch % p.batch1, b2 = batch / p.batch1;
         const int tile = wr / p.splits, split = wr % p.splits;
-        const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+        int mt, nt;
+        tile_coords(tile, tiles_m, tiles_n, p.raster_gn, mt, nt);
+        const int m0 = mt * BLOCK_M, n0 = nt * BLOCK_N;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, kb_total);
         if (p.bias_mma) {
@@ -288,7 +304,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int batch = w / per_batch, wr = w % per_batch;
       const long c_off = (long)(batch % p.batch1) * p.c_stride_b1 + (long)(batch / p.batch1) * p.c_stride_b2;
       const int tile = wr / p.splits, split = wr % p.splits;
-      const int m0 = (tile % tiles_m) * BLOCK_M, n0 = (tile / tiles_m) * BLOCK_N;
+      int mt, nt;
+      tile_coords(tile, tiles_m, tiles_n, p.raster_gn, mt, nt);
+      const int m0 = mt * BLOCK_M, n0 = nt * BLOCK_N;
       const int kb0 = split * kb_per_split;
       const bool has_k = kb0 < min(kb0 + kb_per_split, kb_total);
       const int buf = it & 1;
@@ -605,6 +623,10 @@ static int gemm_impl(const void* A, const void* B, void* C, void* aux, const voi
     if (ce == cudaSuccess && encode_2d(&tones, ones, 128, 1, 256, 64, UMMA_K) == 0 &&
         encode_2d(&tbias, bias, (uint64_t)N, 1, (uint64_t)((N + 7) / 8 * 8) * 2, 64, UMMA_K) == 0)
       p.bias_mma = 1;
+  }
+  {
+    const int tn = (N + block_n - 1) / block_n;
+    p.raster_gn = tn < 16 ? tn : 16;
   }
   const long tiles_l = (long)((M + BLOCK_M - 1) / BLOCK_M) * ((N + block_n - 1) / block_n) * splits * batch1 * batch2;
   if (tiles_l > 0x7fffffffL) return -DL4J_ERR_BAD_ARG;

@@ -132,6 +132,17 @@ class ConvolutionLayer(FeedForwardLayer):
                     z = self.activation(z, training)
                     return z.permute(0, 2, 3, 1) if nhwc else z
         W = None
+        if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and type(self) is ConvolutionLayer \
+                and tuple(self.stride) == (1, 1) and x.shape[1] % 8 == 0 and self.nOut % 8 == 0:
+            # stride-1 convolution of any kernel size: tcgen05 implicit GEMM (forward, dgrad, wgrad), no library convolution
+            from ...ops import native as nat
+            from ...ops import nnops as _nn
+            if not _nn._FORCE_TORCH and nat.available():
+                xp, pad = _pad_for_mode(x, self.kernelSize, self.stride, self.padding, self.dilation, self._mode())
+                z = nat.conv2d(xp, p["W"], p["b"] if self.hasBias and not skip_bias else None, pad, self.dilation)
+                if z is not None:
+                    z = self.activation(z, training)
+                    return z.permute(0, 2, 3, 1) if nhwc else z
         if x.is_cuda and x.dtype == torch.bfloat16 and type(self) is ConvolutionLayer:
             from ...ops import native as nat
             from ...ops import nnops as _nn
@@ -184,6 +195,13 @@ def _stem_space_to_depth(x, W, b, k, pad):
         if cpad:
             xs = F.pad(xs, (0, 0, 0, 0, 0, cpad))
         xs = xs.contiguous(memory_format=torch.channels_last)
+    if xs.is_cuda and not nnops._FORCE_TORCH and xs.shape[1] % 8 == 0 and Wsd.shape[0] % 8 == 0:
+        # stride-1 convolution over the space-to-depth view on the native kernels; the KW2 taps of a filter row times the
+        # padded channels are one 64-element run per output pixel, loaded as a single K slice
+        from ...ops import native as nat
+        z = nat.conv2d(xs, Wsd, b, (0, 0), (1, 1), fuse_w=True)
+        if z is not None:
+            return z
     return F.conv2d(xs, Wsd, b)
 
 

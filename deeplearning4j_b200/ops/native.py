@@ -716,6 +716,121 @@ class _ConvWeightFn(torch.autograd.Function):
         return None if tgt is not None else out.to(W.dtype)
 
 
+def _conv_sigs(l):
+    if getattr(l, "_conv_typed", False):
+        return
+    vp, i32 = ctypes.c_void_p, ctypes.c_int
+    l.dl4j_conv2d.argtypes = [i32, vp, vp, vp, vp] + [i32] * 17 + [vp]
+    l.dl4j_conv2d.restype = i32
+    l.dl4j_conv2d_wgrad.argtypes = [vp, vp, vp] + [i32] * 15 + [vp]
+    l.dl4j_conv2d_wgrad.restype = i32
+    l.dl4j_conv_wgrad_f32_from_cl.argtypes = [vp, vp, i32, i32, i32, vp]
+    l.dl4j_conv_wgrad_f32_from_cl.restype = i32
+    l._conv_typed = True
+
+
+class _Conv2dFn(torch.autograd.Function):
+    """Stride-1 2-D convolution on the tcgen05 implicit-GEMM kernels (``csrc/conv_tcgen05.cu``): forward, data gradient
+    and weight gradient.  ``x`` is a channels-last 16-bit activation [N, Cin, H, W].  ``W`` is either the fp32 parameter
+    [Cout, Cin, kH, kW] (it is cast and laid out channels-last here, and its gradient is added straight into the
+    parameter's fp32 gradient buffer when it has one) or an already channels-last 16-bit kernel (its gradient is returned).
+    ``fuse_w``: few-channel stem form, see ``dl4j_conv2d``."""
+
+    @staticmethod
+    def forward(ctx, x, W, bias, pad, dil, fuse_w, path=0):
+        l = require()
+        _conv_sigs(l)
+        x = _dense_cl(x)
+        N, Cin, H, Wd = x.shape
+        Wm = getattr(W, "_master", W)
+        Cout, _, kH, kW = Wm.shape
+        if Wm.dtype == torch.float32:
+            w_cl = torch.empty((Cout, kH, kW, Cin), dtype=x.dtype, device=x.device)
+            if x.dtype == torch.bfloat16 and Wm.is_contiguous():
+                rc = l.dl4j_conv_weight_to_cl(_ptr(Wm.detach()), _ptr(w_cl), Cout, Cin, kH * kW, _stream())
+                _check(rc, "dl4j_conv_weight_to_cl")
+            else:
+                w_cl.copy_(Wm.detach().permute(0, 2, 3, 1))
+            ctx.master = Wm
+        else:
+            w_cl = W.detach().permute(0, 2, 3, 1).contiguous()
+            ctx.master = None
+        OH = H + 2 * pad[0] - (kH - 1) * dil[0]
+        OW = Wd + 2 * pad[1] - (kW - 1) * dil[1]
+        y = torch.empty((N, OH, OW, Cout), dtype=x.dtype, device=x.device)
+        b = None
+        if bias is not None:
+            b = bias.detach().reshape(-1)
+            b = b if b.dtype in (torch.float32, x.dtype) else b.float()
+            b = b.contiguous()
+        ctx.geom = (N, H, Wd, Cin, OH, OW, Cout, kH, kW, int(pad[0]), int(pad[1]), int(dil[0]), int(dil[1]))
+        ctx.fuse_w = int(bool(fuse_w))
+        ctx.path = int(path)          # 0 automatic, 2 per-tap kernel, 4 halo kernel (tests)
+        rc = l.dl4j_conv2d(0, _ptr(x), _ptr(w_cl), _ptr(y), _ptr(b), *ctx.geom, _DT[x.dtype],
+                           1 if (b is not None and b.dtype == torch.float32) else 0, 0, ctx.fuse_w | ctx.path, _stream())
+        _check(rc, "dl4j_conv2d")
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        ctx.bias_shape = tuple(bias.shape) if bias is not None else None
+        ctx.w_dtype = W.dtype
+        ctx.save_for_backward(x, w_cl)
+        return y.permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        l = require()
+        x, w_cl = ctx.saved_tensors
+        N, H, Wd, Cin, OH, OW, Cout, kH, kW, ph, pw, dh, dw_ = ctx.geom
+        dy = _dense_cl(dy)
+        if dy.dtype != x.dtype:
+            dy = dy.to(x.dtype)
+        dx = dW = db = None
+        if ctx.needs_input_grad[0]:
+            dxb = torch.empty((N, H, Wd, Cin), dtype=x.dtype, device=x.device)
+            rc = l.dl4j_conv2d(1, _ptr(dy), _ptr(w_cl), _ptr(dxb), None, *ctx.geom, _DT[x.dtype], 0, 0, ctx.path, _stream())
+            _check(rc, "dl4j_conv2d")
+            dx = dxb.permute(0, 3, 1, 2)
+        if ctx.needs_input_grad[1] or ctx.master is not None:
+            g_cl = torch.zeros((Cout, kH, kW, Cin), dtype=torch.float32, device=x.device)
+            rc = l.dl4j_conv2d_wgrad(_ptr(dy), _ptr(x), _ptr(g_cl), *ctx.geom, _DT[x.dtype], ctx.fuse_w, _stream())
+            _check(rc, "dl4j_conv2d_wgrad")
+            Wm = ctx.master
+            if Wm is not None:
+                tgt = Wm.grad if (Wm.is_leaf and Wm.grad is not None and Wm.grad.dtype == torch.float32 and Wm.grad.is_contiguous()) else None
+                out = tgt if tgt is not None else torch.zeros(Wm.shape, dtype=torch.float32, device=x.device)
+                rc = l.dl4j_conv_wgrad_f32_from_cl(_ptr(g_cl), _ptr(out), Cout, Cin, kH * kW, _stream())
+                _check(rc, "dl4j_conv_wgrad_f32_from_cl")
+                dW = None if tgt is not None else out.to(ctx.w_dtype)
+            else:
+                dW = g_cl.permute(0, 3, 1, 2).to(ctx.w_dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy.float().sum((0, 2, 3)).reshape(ctx.bias_shape).to(ctx.bias_dtype)
+        return dx, dW, db, None, None, None, None
+
+
+def conv2d(x, W, bias, pad, dil, fuse_w=False, path=None):
+    """Stride-1 convolution on the native implicit-GEMM kernels, or None when the case is not covered (the caller then
+    uses the library path): 16-bit CUDA activation, channel counts multiples of 8, non-negative output size."""
+    if not (available() and x.is_cuda and x.dim() == 4 and x.dtype in (torch.bfloat16, torch.float16)):
+        return None
+    Wm = getattr(W, "_master", W)
+    if Wm.dim() != 4 or Wm.shape[1] != x.shape[1] or x.shape[1] % 8 or Wm.shape[0] % 8:
+        return None
+    if Wm.dtype != torch.float32 and Wm.dtype != x.dtype:
+        return None
+    kH, kW = Wm.shape[2], Wm.shape[3]
+    if kH * kW > 64:
+        return None
+    if x.shape[2] + 2 * pad[0] - (kH - 1) * dil[0] < 1 or x.shape[3] + 2 * pad[1] - (kW - 1) * dil[1] < 1:
+        return None
+    if pad[0] < 0 or pad[1] < 0 or pad[0] > 255 or pad[1] > 255:
+        return None
+    if fuse_w and (pad[1] != 0 or dil[1] != 1 or kW * x.shape[1] > 64):
+        fuse_w = False
+    return _Conv2dFn.apply(x, W, bias, (int(pad[0]), int(pad[1])), (int(dil[0]), int(dil[1])), bool(fuse_w),
+                           {None: 0, "tap": 2, "halo": 4}[path])
+
+
 def conv_weight_cl(W):
     """bf16 channels-last version of an fp32 convolution kernel parameter, or None when not applicable."""
     if not (available() and W.is_cuda and W.dim() == 4 and W.dtype == torch.float32 and W.is_contiguous()):

@@ -116,3 +116,91 @@ def test_stem_space_to_depth_kernel_matches_the_torch_construction(shape, k, pad
     ref = xp.reshape(N, C, Hs, 2, Ws, 2).permute(0, 3, 5, 1, 2, 4).reshape(N, 4 * C, Hs, Ws)
     ref = F.pad(ref, (0, 0, 0, 0, 0, cp - 4 * C))
     assert torch.equal(got, ref)
+
+
+def _close(a, b, rtol=2e-2, atol_frac=1e-2):
+    """Element-wise check with a bf16-sized tolerance: |a - b| <= atol + rtol |b| with atol a fraction of b's rms."""
+    a, b = a.detach().float(), b.detach().float()
+    atol = atol_frac * float(b.pow(2).mean().sqrt()) + 1e-6
+    torch.testing.assert_close(a, b, rtol=rtol, atol=atol)
+
+
+@pytest.mark.parametrize("N,C,H,W,O,k,pad,dil", [
+    (4, 64, 14, 14, 64, (3, 3), (1, 1), (1, 1)),        # ResNet stage shape, Same
+    (2, 64, 55, 55, 64, (3, 3), (1, 1), (1, 1)),        # odd extent, boxes overhang the image
+    (3, 512, 7, 7, 512, (3, 3), (1, 1), (1, 1)),        # several images per box, two 256-column tiles
+    (2, 128, 28, 28, 256, (3, 3), (0, 0), (1, 1)),      # Truncate: output smaller than input
+    (2, 32, 17, 13, 48, (7, 7), (3, 3), (1, 1)),        # 7x7, channel counts below one 64-wide slice
+    (1, 8, 9, 11, 8, (1, 7), (0, 3), (1, 1)),           # asymmetric kernel, minimal channels
+    (2, 64, 20, 20, 96, (3, 3), (2, 2), (2, 2)),        # dilation 2
+    (5, 256, 14, 14, 256, (3, 3), (1, 1), (1, 1)),
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("path", ["tap", "halo"])
+def test_conv2d_implicit_gemm_matches_conv2d(nat, N, C, H, W, O, k, pad, dil, dtype, path):
+    """Both forms of the forward / data-gradient kernel (one input fetch per tap; one halo box per channel slice read through
+    shifted descriptors) and the weight-gradient kernel against fp32 ``F.conv2d``."""
+    if dtype == torch.float16 and (C > 64 or path == "halo"):
+        pytest.skip("fp16 covered on the small shapes")
+    g = torch.Generator(device="cuda").manual_seed(N * 1000 + C + H + O)
+    x = torch.randn(N, C, H, W, device="cuda", generator=g).to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    Wt = (torch.randn(O, C, k[0], k[1], device="cuda", generator=g) / (C * k[0] * k[1]) ** 0.5).requires_grad_(True)   # fp32 master
+    Wt.grad = torch.full_like(Wt, 0.5)               # the kernel adds into the preallocated gradient
+    b = torch.randn(1, O, device="cuda", generator=g).requires_grad_(True)
+    y = nat.conv2d(x, Wt, b, pad, dil, path=path)
+    assert y is not None and y.is_contiguous(memory_format=torch.channels_last)
+    wgt = torch.randn(y.shape, device="cuda", generator=g).to(dtype)
+    (y.float() * wgt.float()).sum().backward()
+    torch.cuda.synchronize()
+    nat.check_status()
+    got = (y.detach().clone(), x.grad.clone(), Wt.grad.clone() - 0.5, b.grad.clone())
+    x.grad = None
+    Wt.grad = None
+    b.grad = None
+    xr = x.detach().float().requires_grad_(True)
+    Wr = Wt.detach().to(dtype).float().requires_grad_(True)
+    br = b.detach().reshape(-1).requires_grad_(True)
+    ref = F.conv2d(xr, Wr, br, padding=pad, dilation=dil)
+    (ref * wgt.float()).sum().backward()
+    _close(got[0], ref)
+    _close(got[1], xr.grad)
+    _close(got[2], Wr.grad, rtol=2e-2, atol_frac=2e-2)
+    _close(got[3].reshape(-1), br.grad, rtol=2e-2, atol_frac=2e-2)
+
+
+def test_conv_layer_stride1_uses_native_kernels(nat):
+    """A 3x3 Same convolution layer runs on the implicit-GEMM kernels (launch counter moves, no library convolution needed)."""
+    from deeplearning4j_b200 import nn
+    layer = nn.ConvolutionLayer(kernelSize=(3, 3), stride=(1, 1), convolutionMode="Same", nIn=64, nOut=64, activation="identity",
+                                hasBias=False)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(2, 64, 12, 12, device="cuda", generator=g).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    W = (torch.randn(64, 64, 3, 3, device="cuda", generator=g) * 0.05).requires_grad_(True)
+    n0 = nat.LAUNCHES
+    y = layer.forward({"W": W}, x, True)
+    y.float().sum().backward()
+    assert nat.LAUNCHES - n0 >= 5          # weight relayout, forward, dgrad, wgrad, gradient fold
+    ref = F.conv2d(x.detach().float(), W.detach().bfloat16().float(), padding=1)
+    _close(y, ref)
+
+
+def test_stem_space_to_depth_on_native_conv(nat):
+    """7x7 stride-2 RGB stem: space-to-depth view + stride-1 native convolution with the fused filter-row K slice; input has no
+    gradient (the data), so the one-kernel view builder runs too."""
+    from deeplearning4j_b200 import nn
+    layer = nn.ConvolutionLayer(kernelSize=(7, 7), stride=(2, 2), padding=(3, 3), nIn=3, nOut=64, activation="identity")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(4, 3, 64, 64, device="cuda", generator=g).bfloat16()
+    W = (torch.randn(64, 3, 7, 7, device="cuda", generator=g) * 0.1).requires_grad_(True)
+    b = torch.randn(1, 64, device="cuda", generator=g).requires_grad_(True)
+    y = layer.forward({"W": W, "b": b}, x, True)
+    wgt = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    (y.float() * wgt.float()).sum().backward()
+    got_w, got_b = W.grad.clone(), b.grad.clone()
+    Wr = W.detach().bfloat16().float().requires_grad_(True)
+    br = b.detach().reshape(-1).requires_grad_(True)
+    ref = F.conv2d(x.float(), Wr, br, stride=2, padding=3)
+    (ref * wgt.float()).sum().backward()
+    _close(y, ref)
+    _close(got_w, Wr.grad, rtol=3e-2, atol_frac=3e-2)
+    _close(got_b.reshape(-1), br.grad, rtol=3e-2, atol_frac=3e-2)
