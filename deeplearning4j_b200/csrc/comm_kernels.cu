@@ -123,6 +123,106 @@ __device__ bool grid_barrier(unsigned int* counter, unsigned int target, int* st
   return ok_flag != 0;
 }
 
+// One owned chunk of a dense-averaging step: sum of every rank's gradient (peer loads or one multimem.ld_reduce), the
+// updater on the sum, and the new fp32 parameters written to every rank (peer stores or multimem.st) plus this rank's
+// bf16 shadow.  Shared by the whole-buffer kernel and the per-bucket kernel.
+__device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __restrict__ state, const UpdChunk* __restrict__ chunks,
+                                                    const UpdSegment* __restrict__ segs, const UpdHyperTable& ht, float grad_scale,
+                                                    int use_multimem, int ci) {
+  float* my_params = c.params[c.rank];
+  const UpdChunk ch = chunks[ci];
+  const UpdSegment sg = segs[ch.seg];
+  const UpdHyper h = ht.h[sg.hyper];
+  const long long rel0 = ch.offset - sg.block_start;
+  float* st0 = state + sg.state_off + rel0;
+  float* st1 = st0 + sg.block_numel;
+  float* st2 = st1 + sg.block_numel;
+  const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+  const int ns = upd_n_state(sg.kernel_id);
+  __nv_bfloat16* my_shadow = c.shadow[c.rank];
+  const uintptr_t al = (uintptr_t)(ch.offset & 3) | (ns > 0 ? reinterpret_cast<uintptr_t>(st0) : 0) |
+                       (ns > 1 ? reinterpret_cast<uintptr_t>(st1) : 0) | (ns > 2 ? reinterpret_cast<uintptr_t>(st2) : 0);
+  const bool vec_ok = (al & 15) == 0;
+  const bool sh_vec = ((sh0 & 3) == 0);
+  const int nvec = vec_ok ? ch.count / 4 : 0;
+  // two vectors per thread and iteration: every load of both (peer gradients, parameters, state) is issued
+  // before the first use so that enough bytes are in flight to cover the NVLink round trip
+  constexpr int U = 2;
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += COMM_THREADS * U) {
+    float4 g[U], w[U], a4[U], b4[U], c4[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * COMM_THREADS;
+      g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      w[u] = g[u]; a4[u] = g[u]; b4[u] = g[u]; c4[u] = g[u];
+      if (v < nvec) {
+        const long long i = ch.offset + 4LL * v;
+        if (use_multimem) {
+          g[u] = multimem_ld_reduce_f4(c.mc_grads + i);
+        } else {
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r) {
+            if (r < c.world) {
+              const float4 t = ld_peer_f4(c.grads[(c.rank + r) % c.world] + i);
+              g[u].x += t.x; g[u].y += t.y; g[u].z += t.z; g[u].w += t.w;
+            }
+          }
+        }
+        w[u] = *reinterpret_cast<const float4*>(my_params + i);
+        if (ns > 0) a4[u] = *reinterpret_cast<const float4*>(st0 + 4 * v);
+        if (ns > 1) b4[u] = *reinterpret_cast<const float4*>(st1 + 4 * v);
+        if (ns > 2) c4[u] = *reinterpret_cast<const float4*>(st2 + 4 * v);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * COMM_THREADS;
+      if (v >= nvec) continue;
+      const long long i = ch.offset + 4LL * v;
+      float wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+      if (sg.kernel_id != 9) {
+        float sa[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w}, sb[4] = {b4[u].x, b4[u].y, b4[u].z, b4[u].w},
+              sc[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wv[j] -= updater_step(sg, h, wv[j], gv[j] * grad_scale, sa + j, sb + j, sc + j);
+        if (ns > 0) *reinterpret_cast<float4*>(st0 + 4 * v) = make_float4(sa[0], sa[1], sa[2], sa[3]);
+        if (ns > 1) *reinterpret_cast<float4*>(st1 + 4 * v) = make_float4(sb[0], sb[1], sb[2], sb[3]);
+        if (ns > 2) *reinterpret_cast<float4*>(st2 + 4 * v) = make_float4(sc[0], sc[1], sc[2], sc[3]);
+      }
+      const float4 wn = make_float4(wv[0], wv[1], wv[2], wv[3]);
+      if (use_multimem) {
+        multimem_st_f4(c.mc_params + i, wn);
+      } else {
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < c.world) *reinterpret_cast<float4*>(c.params[(c.rank + r) % c.world] + i) = wn;
+      }
+      // only the fp32 master crosses the link; every rank derives its own bf16 shadow (here for the owned chunks,
+      // in the last phase for the others)
+      if (my_shadow) {
+        __nv_bfloat16* sp = my_shadow + sh0 + 4LL * v;
+        if (sh_vec) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(wv[0], wv[1]), hi = __floats2bfloat162_rn(wv[2], wv[3]);
+          *reinterpret_cast<uint2*>(sp) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) sp[j] = __float2bfloat16(wv[j]);
+        }
+      }
+    }
+  }
+  // scalar tail (and whole chunk when its offset is not 16-byte aligned)
+  for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) {
+    const long long i = ch.offset + e;
+    float g = 0.f;
+    for (int r = 0; r < c.world; ++r) g += ld_peer_f(c.grads[r] + i);
+    float w = my_params[i];
+    if (sg.kernel_id != 9) w -= updater_step(sg, h, w, g * grad_scale, st0 + e, st1 + e, st2 + e);
+    for (int r = 0; r < c.world; ++r) c.params[r][i] = w;
+    if (my_shadow) my_shadow[sh0 + e] = __float2bfloat16(w);
+  }
+    }
+
 // ------------------------------------------------------------------------------------------------ K2
 // scratch[0] = grid barrier counter (zeroed by the host before every launch)
 __global__ void __launch_bounds__(COMM_THREADS)
@@ -138,99 +238,8 @@ allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChu
   if (ok) {
     // ---- phase 1: owned chunks: reduce -> updater -> broadcast
     const int c0 = (int)((long long)n_chunks * c.rank / c.world), c1 = (int)((long long)n_chunks * (c.rank + 1) / c.world);
-    float* my_params = c.params[c.rank];
     for (int ci = c0 + blockIdx.x; ci < c1; ci += gridDim.x) {
-      const UpdChunk ch = chunks[ci];
-      const UpdSegment sg = segs[ch.seg];
-      const UpdHyper h = ht.h[sg.hyper];
-      const long long rel0 = ch.offset - sg.block_start;
-      float* st0 = state + sg.state_off + rel0;
-      float* st1 = st0 + sg.block_numel;
-      float* st2 = st1 + sg.block_numel;
-      const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
-      const int ns = upd_n_state(sg.kernel_id);
-      __nv_bfloat16* my_shadow = c.shadow[c.rank];
-      const uintptr_t al = (uintptr_t)(ch.offset & 3) | (ns > 0 ? reinterpret_cast<uintptr_t>(st0) : 0) |
-                           (ns > 1 ? reinterpret_cast<uintptr_t>(st1) : 0) | (ns > 2 ? reinterpret_cast<uintptr_t>(st2) : 0);
-      const bool vec_ok = (al & 15) == 0;
-      const bool sh_vec = ((sh0 & 3) == 0);
-      const int nvec = vec_ok ? ch.count / 4 : 0;
-      // two vectors per thread and iteration: every load of both (peer gradients, parameters, state) is issued
-      // before the first use so that enough bytes are in flight to cover the NVLink round trip
-      constexpr int U = 2;
-      for (int v0 = threadIdx.x; v0 < nvec; v0 += COMM_THREADS * U) {
-        float4 g[U], w[U], a4[U], b4[U], c4[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int v = v0 + u * COMM_THREADS;
-          g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-          w[u] = g[u]; a4[u] = g[u]; b4[u] = g[u]; c4[u] = g[u];
-          if (v < nvec) {
-            const long long i = ch.offset + 4LL * v;
-            if (use_multimem) {
-              g[u] = multimem_ld_reduce_f4(c.mc_grads + i);
-            } else {
-#pragma unroll
-              for (int r = 0; r < MAX_RANKS; ++r) {
-                if (r < c.world) {
-                  const float4 t = ld_peer_f4(c.grads[(c.rank + r) % c.world] + i);
-                  g[u].x += t.x; g[u].y += t.y; g[u].z += t.z; g[u].w += t.w;
-                }
-              }
-            }
-            w[u] = *reinterpret_cast<const float4*>(my_params + i);
-            if (ns > 0) a4[u] = *reinterpret_cast<const float4*>(st0 + 4 * v);
-            if (ns > 1) b4[u] = *reinterpret_cast<const float4*>(st1 + 4 * v);
-            if (ns > 2) c4[u] = *reinterpret_cast<const float4*>(st2 + 4 * v);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int v = v0 + u * COMM_THREADS;
-          if (v >= nvec) continue;
-          const long long i = ch.offset + 4LL * v;
-          float wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
-          if (sg.kernel_id != 9) {
-            float sa[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w}, sb[4] = {b4[u].x, b4[u].y, b4[u].z, b4[u].w},
-                  sc[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) wv[j] -= updater_step(sg, h, wv[j], gv[j] * grad_scale, sa + j, sb + j, sc + j);
-            if (ns > 0) *reinterpret_cast<float4*>(st0 + 4 * v) = make_float4(sa[0], sa[1], sa[2], sa[3]);
-            if (ns > 1) *reinterpret_cast<float4*>(st1 + 4 * v) = make_float4(sb[0], sb[1], sb[2], sb[3]);
-            if (ns > 2) *reinterpret_cast<float4*>(st2 + 4 * v) = make_float4(sc[0], sc[1], sc[2], sc[3]);
-          }
-          const float4 wn = make_float4(wv[0], wv[1], wv[2], wv[3]);
-          if (use_multimem) {
-            multimem_st_f4(c.mc_params + i, wn);
-          } else {
-#pragma unroll
-            for (int r = 0; r < MAX_RANKS; ++r)
-              if (r < c.world) *reinterpret_cast<float4*>(c.params[(c.rank + r) % c.world] + i) = wn;
-          }
-          // only the fp32 master crosses the link; every rank derives its own bf16 shadow (here for the owned chunks,
-          // in the last phase for the others)
-          if (my_shadow) {
-            __nv_bfloat16* sp = my_shadow + sh0 + 4LL * v;
-            if (sh_vec) {
-              __nv_bfloat162 lo = __floats2bfloat162_rn(wv[0], wv[1]), hi = __floats2bfloat162_rn(wv[2], wv[3]);
-              *reinterpret_cast<uint2*>(sp) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) sp[j] = __float2bfloat16(wv[j]);
-            }
-          }
-        }
-      }
-      // scalar tail (and whole chunk when its offset is not 16-byte aligned)
-      for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) {
-        const long long i = ch.offset + e;
-        float g = 0.f;
-        for (int r = 0; r < c.world; ++r) g += ld_peer_f(c.grads[r] + i);
-        float w = my_params[i];
-        if (sg.kernel_id != 9) w -= updater_step(sg, h, w, g * grad_scale, st0 + e, st1 + e, st2 + e);
-        for (int r = 0; r < c.world; ++r) c.params[r][i] = w;
-        if (my_shadow) my_shadow[sh0 + e] = __float2bfloat16(w);
-      }
+      reduce_update_chunk(c, state, chunks, segs, ht, grad_scale, use_multimem, ci);
     }
     __threadfence_system();
   }
@@ -269,6 +278,140 @@ allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChu
         for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) dst[e] = __float2bfloat16(__ldcg(src + e));
       }
     }
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------ K2, per bucket
+// Dense averaging bucket by bucket, so that the exchange of the layers whose gradients are already final runs while
+// the backward pass of the earlier layers is still computing (the reference steps only once the whole gradient is
+// complete: deeplearning4j-nn/.../optimize/solvers/StochasticGradientDescent.java:47-57).
+//
+// One launch per bucket (a contiguous range of updater chunks) on a side stream, after an event that follows the last
+// kernel writing into the bucket's gradients.  The grid is small (it shares the SMs with the backward GEMMs) and not
+// cooperative: nothing in it waits for another CTA of the same launch -- every CTA polls the peers' "ready" flags
+// itself, and the CTA that takes the last ticket publishes this rank's "done" flag.  The step count, the
+// hyper-parameters and the flag epoch are read from device memory (written by the host before the step), so the
+// launch can sit in a captured CUDA graph.  Gradient clearing and the bf16 shadow of the chunks that other ranks own
+// are left to bucket_finish_kernel, which runs once after the last bucket.
+// Signal-pad slots: 4 + 2 b = ready flag of bucket b, 5 + 2 b = done flag.
+struct StepVars {            // device copy, refreshed by the host before every step
+  UpdHyperTable ht;
+  uint32_t epoch;
+  float grad_scale;
+};
+
+__device__ __forceinline__ bool wait_peer_flags(const CommCtx& c, int slot, uint32_t epoch, int* status) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t* mine = c.signal[c.rank] + slot * MAX_RANKS + threadIdx.x;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && (clock64() - t0 > 2000000000LL || *((volatile int*)status) != 0)) {
+        atomicCAS(status, 0, DL4J_ERR_TIMEOUT_PEER);
+        ok_flag = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+bucket_allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChunk* __restrict__ chunks, int chunk0, int chunk1,
+                               const UpdSegment* __restrict__ segs, const StepVars* __restrict__ vars, int bucket,
+                               unsigned int* tickets, int use_multimem, int* status) {
+  __shared__ UpdHyperTable ht;
+  __shared__ unsigned int my_ticket;
+  const uint32_t epoch = vars->epoch;
+  const float grad_scale = vars->grad_scale;
+  for (int i = threadIdx.x; i < (int)(sizeof(UpdHyperTable) / 4); i += COMM_THREADS)
+    reinterpret_cast<float*>(&ht)[i] = reinterpret_cast<const float*>(&vars->ht)[i];
+  const int slot_ready = 4 + 2 * bucket, slot_done = slot_ready + 1;
+  // this rank's gradients of the bucket are final (the launch is ordered after the kernels that wrote them)
+  if (blockIdx.x == 0 && threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.signal[threadIdx.x] + slot_ready * MAX_RANKS + c.rank, epoch);
+  }
+  bool ok = wait_peer_flags(c, slot_ready, epoch, status) && *((volatile int*)status) == 0;
+  if (ok) {
+    const int n = chunk1 - chunk0;
+    const int c0 = chunk0 + (int)((long long)n * c.rank / c.world), c1 = chunk0 + (int)((long long)n * (c.rank + 1) / c.world);
+    for (int ci = c0 + blockIdx.x; ci < c1; ci += gridDim.x) reduce_update_chunk(c, state, chunks, segs, ht, grad_scale, use_multimem, ci);
+  }
+  // the CTA that finishes last tells every peer that this rank has read their gradients and written their parameters
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) my_ticket = atomicAdd(&tickets[bucket], 1u);
+  __syncthreads();
+  if (my_ticket == gridDim.x - 1) {
+    if (threadIdx.x == 0) tickets[bucket] = 0u;          // ready for the next step (launches of one bucket are stream-ordered)
+    if (ok && threadIdx.x < c.world) {
+      __threadfence_system();
+      st_release_sys(c.signal[threadIdx.x] + slot_done * MAX_RANKS + c.rank, epoch);
+    }
+  }
+}
+
+// After the last bucket: waits until every peer has finished every bucket (their reads of this rank's gradients and their
+// writes of the parameters they own), then clears the local gradients and derives the bf16 shadow of the chunks other ranks own.
+__global__ void __launch_bounds__(COMM_THREADS)
+bucket_finish_kernel(const CommCtx c, const UpdChunk* __restrict__ chunks, const UpdSegment* __restrict__ segs,
+                     const int* __restrict__ bucket_chunk0, int n_buckets, const StepVars* __restrict__ vars, long long n_total,
+                     int* status) {
+  __shared__ int ok_flag;
+  const uint32_t epoch = vars->epoch;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  for (int f = threadIdx.x; f < n_buckets * c.world; f += COMM_THREADS) {
+    const int b = f / c.world, r = f - b * c.world;
+    const uint32_t* flag = c.signal[c.rank] + (5 + 2 * b) * MAX_RANKS + r;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && (clock64() - t0 > 2000000000LL || *((volatile int*)status) != 0)) {
+        atomicCAS(status, 0, DL4J_ERR_TIMEOUT_PEER);
+        ok_flag = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok_flag || *((volatile int*)status) != 0) return;      // gradients stay as they are: the host drops them
+  float4* g4 = reinterpret_cast<float4*>(c.grads[c.rank]);
+  const long long n4 = n_total / 4;
+  for (long long i = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; i < n4; i += (long long)gridDim.x * COMM_THREADS)
+    g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (blockIdx.x == 0)
+    for (long long i = n4 * 4 + threadIdx.x; i < n_total; i += COMM_THREADS) c.grads[c.rank][i] = 0.f;
+  __nv_bfloat16* my_shadow = c.shadow[c.rank];
+  if (!my_shadow) return;
+  const float* my_params = c.params[c.rank];
+  const int total_chunks = bucket_chunk0[n_buckets];
+  for (int ci = blockIdx.x; ci < total_chunks; ci += gridDim.x) {
+    // owner of chunk ci inside its bucket
+    int b = 0;
+    while (b + 1 < n_buckets && bucket_chunk0[b + 1] <= ci) ++b;
+    const int k0 = bucket_chunk0[b], n = bucket_chunk0[b + 1] - k0;
+    const int c0 = k0 + (int)((long long)n * c.rank / c.world), c1 = k0 + (int)((long long)n * (c.rank + 1) / c.world);
+    if (ci >= c0 && ci < c1) continue;                     // own chunks got their shadow in the bucket kernel
+    const UpdChunk ch = chunks[ci];
+    const UpdSegment sg = segs[ch.seg];
+    const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+    const float* src = my_params + ch.offset;
+    __nv_bfloat16* dst = my_shadow + sh0;
+    const bool vec = ((ch.offset & 3) == 0) && ((sh0 & 3) == 0);
+    const int nvec = vec ? ch.count / 4 : 0;
+    for (int v = threadIdx.x; v < nvec; v += COMM_THREADS) {
+      const float4 w = __ldcg(reinterpret_cast<const float4*>(src) + v);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(w.x, w.y), hi = __floats2bfloat162_rn(w.z, w.w);
+      reinterpret_cast<uint2*>(dst)[v] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+    for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) dst[e] = __float2bfloat16(__ldcg(src + e));
   }
 }
 
@@ -456,6 +599,40 @@ DL4J_API int dl4j_allreduce_update(const void* comm_args, float* state, const vo
   cudaError_t e = cudaLaunchCooperativeKernel((void*)allreduce_update_kernel, dim3(grid), dim3(COMM_THREADS), args, 0, stream);
   return (int)e;
 }
+
+
+// Per-bucket dense averaging (see bucket_allreduce_update_kernel).  `vars` is the device StepVars block, `tickets` a zeroed
+// device array of one counter per bucket; `grid` CTAs (small: the launch shares the SMs with the backward pass).
+DL4J_API int dl4j_bucket_allreduce_update(const void* comm_args, float* state, const void* chunks, int chunk0, int chunk1,
+                                          const void* segs, const void* vars, int bucket, void* tickets, int use_multimem,
+                                          int grid, void* stream_) {
+  const HostCommArgs* a = reinterpret_cast<const HostCommArgs*>(comm_args);
+  if (a->world < 1 || a->world > MAX_RANKS || bucket < 0 || bucket >= 64 || chunk1 < chunk0 || grid < 1) return -DL4J_ERR_BAD_ARG;
+  if (use_multimem && (!a->mc_grads || !a->mc_params)) return -DL4J_ERR_BAD_ARG;
+  CommCtx c = make_ctx(a);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bucket_allreduce_update_kernel<<<grid, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
+      c, state, reinterpret_cast<const UpdChunk*>(chunks), chunk0, chunk1, reinterpret_cast<const UpdSegment*>(segs),
+      reinterpret_cast<const StepVars*>(vars), bucket, reinterpret_cast<unsigned int*>(tickets), use_multimem, dl4j_status_word(dev));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_bucket_finish(const void* comm_args, const void* chunks, const void* segs, const int* bucket_chunk0, int n_buckets,
+                                const void* vars, long long n_total, void* stream_) {
+  const HostCommArgs* a = reinterpret_cast<const HostCommArgs*>(comm_args);
+  if (a->world < 1 || a->world > MAX_RANKS || n_buckets < 1 || n_buckets > 64) return -DL4J_ERR_BAD_ARG;
+  CommCtx c = make_ctx(a);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  bucket_finish_kernel<<<sms * 2, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
+      c, reinterpret_cast<const UpdChunk*>(chunks), reinterpret_cast<const UpdSegment*>(segs), bucket_chunk0, n_buckets,
+      reinterpret_cast<const StepVars*>(vars), n_total, dl4j_status_word(dev));
+  return (int)cudaGetLastError();
+}
+
+DL4J_API int dl4j_step_vars_bytes() { return (int)sizeof(StepVars); }
 
 DL4J_API int dl4j_threshold_share(const void* comm_args, float* state, float* residual, const void* chunks, int n_chunks,
                                   const void* segs, const float* hyper, int n_hyper, float grad_scale, float tau,

@@ -1108,7 +1108,9 @@ def _build_tables(upd, shadow_offsets):
     segs = upd.segments(0, 0)
     block_ids = []
     seg_rows, chunks = [], []
+    upd._seg_chunk0 = []                 # first chunk of every segment (bucketed gradient exchange addresses chunk ranges)
     for si, (off, numel, st_off, bn, bs, kid, lr, l1, l2, wd, cfg) in enumerate(segs):
+        upd._seg_chunk0.append(len(chunks))
         hid = _cfg_index(block_ids, cfg)
         seg_rows.append([off, bs, bn, st_off, shadow_offsets[si] if shadow_offsets is not None else 0, l1, l2, wd, kid, hid, 0])
         o = 0
@@ -1116,6 +1118,7 @@ def _build_tables(upd, shadow_offsets):
             c = min(_CHUNK, numel - o)
             chunks.append(struct.pack(_CHUNK_FMT, off + o, c, si))
             o += c
+    upd._seg_chunk0.append(len(chunks))
     return seg_rows, b"".join(chunks), len(chunks), len(block_ids)
 
 

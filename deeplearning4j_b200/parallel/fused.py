@@ -213,3 +213,133 @@ class FusedSharing:
         self.status.snapshot()
         upd._fused_zeroes_grads = True
         upd._shadow_fresh = self.shadow is not None
+
+
+class BucketedAveraging:
+    """Dense gradient averaging overlapped with the backward pass, bucket by bucket.
+
+    The flat parameter buffer is cut into ``n_buckets`` contiguous ranges at parameter boundaries.  A parameter reports
+    "gradient final" from the autograd node that presents its shadow to the graph (``samediff.training._ShadowParam``); when the
+    last parameter of a bucket has reported, an event is recorded on the compute stream and ``bucket_allreduce_update_kernel``
+    for that bucket is launched behind it on a side stream with a small grid, so the reduce-scatter + updater + all-gather of the
+    late layers runs under the backward GEMMs of the early ones (the reference steps once, after the whole gradient is complete:
+    ``optimize/solvers/StochasticGradientDescent.java:47-57``).  After backward the side stream is joined and one
+    ``bucket_finish_kernel`` clears the gradients and derives the shadow of the chunks other ranks own.
+
+    Everything that changes from step to step (Adam's bias correction, learning-rate schedule, the flag epoch) lives in a small
+    device block written by ``pre_step``, so the launches can be part of a captured CUDA graph and replay unchanged.
+    """
+
+    def __init__(self, fused: FusedSharing, state, n_buckets=12, grid=32):
+        self.fused, self.state = fused, state
+        self.lib = fused.lib
+        upd = fused.updater
+        t = native.update_tables(upd, 0, 0, upd.shadow_offsets)
+        if t is None:
+            raise RuntimeError("updater configuration is not supported by the fused kernel")
+        self.tables = t
+        entries = state.entries
+        total = sum(e.spec.numel for e in entries)
+        n_buckets = max(1, min(int(n_buckets), len(entries), 48))
+        target = total / n_buckets
+        # bucket boundaries at parameter boundaries, in buffer order (= forward order); gradients become final back to front
+        self.bucket_of, bounds, acc, b = {}, [0], 0, 0
+        for i, e in enumerate(entries):
+            self.bucket_of[e.spec.name] = b
+            acc += e.spec.numel
+            if acc >= target * (b + 1) and i + 1 < len(entries) and b + 1 < n_buckets:
+                b += 1
+                bounds.append(i + 1)
+        bounds.append(len(entries))
+        self.n_buckets = b + 1
+        self.seg_bounds = bounds
+        sc0 = upd._seg_chunk0
+        self.chunk_bounds = [sc0[i] for i in bounds]
+        dev = fused.params.device
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        self.lib.dl4j_bucket_allreduce_update.argtypes = [vp, vp, vp, i32, i32, vp, vp, i32, vp, i32, i32, vp]
+        self.lib.dl4j_bucket_allreduce_update.restype = i32
+        self.lib.dl4j_bucket_finish.argtypes = [vp, vp, vp, vp, i32, vp, i64, vp]
+        self.lib.dl4j_bucket_finish.restype = i32
+        self.lib.dl4j_step_vars_bytes.restype = i32
+        self.vars_bytes = int(self.lib.dl4j_step_vars_bytes())
+        self.vars_dev = torch.zeros(self.vars_bytes, dtype=torch.uint8, device=dev)
+        self.tickets = torch.zeros(64, dtype=torch.int32, device=dev)
+        self.bounds_dev = torch.tensor(self.chunk_bounds, dtype=torch.int32, device=dev)
+        self.segs_dev = t["segs_dev"].clone()          # own copy with a fixed address (captured launches keep pointing at it)
+        self._segs_key = t["segs_key"]
+        import os
+        self.grid = int(os.environ.get("DL4J_BUCKET_GRID", grid))
+        self.side = torch.cuda.Stream(device=dev, priority=int(os.environ.get("DL4J_BUCKET_PRIO", "0")))
+        self.count = [0] * self.n_buckets
+        for e in entries:
+            self.count[self.bucket_of[e.spec.name]] += 1
+        self.pending, self.fired = list(self.count), [False] * self.n_buckets
+        self.fired_early = [False] * self.n_buckets
+        self.launches = 0
+        for e in entries:
+            leaf = state.views[e.spec.name]
+            leaf._grad_ready = self._ready
+            leaf._bucket = self.bucket_of[e.spec.name]
+
+    # ------------------------------------------------------------------ per step
+    def pre_step(self, iteration, epoch):
+        import numpy as np
+        f = self.fused
+        f.status.check()
+        upd = f.updater
+        t = native.update_tables(upd, iteration, epoch, upd.shadow_offsets)
+        if t["segs_key"] != self._segs_key:            # scheduled regularisation changed: refresh in place
+            self.segs_dev.copy_(t["segs_dev"])
+            self._segs_key = t["segs_key"]
+        f.epoch += 1
+        blob = np.zeros(self.vars_bytes, dtype=np.uint8)
+        blob[:256] = np.frombuffer(t["hyper"].astype(np.float32).tobytes(), dtype=np.uint8)
+        blob[256:260] = np.frombuffer(np.uint32(f.epoch).tobytes(), dtype=np.uint8)
+        blob[260:264] = np.frombuffer(np.float32(1.0 / f.world).tobytes(), dtype=np.uint8)
+        self.vars_dev.copy_(torch.from_numpy(blob))    # pageable source: staged at once, the buffer may be reused
+        self.pending, self.fired = list(self.count), [False] * self.n_buckets
+        self.fired_early = [False] * self.n_buckets     # buckets launched from a parameter's report, i.e. during backward
+
+    def _ready(self, leaf):
+        b = leaf._bucket
+        self.pending[b] -= 1
+        if self.pending[b] == 0 and not self.fired[b]:
+            self.fired_early[b] = True
+            self._fire(b)
+
+    def _fire(self, b):
+        f = self.fused
+        self.fired[b] = True
+        cur = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self.side.wait_event(ev)
+        st = f.updater.state
+        with torch.cuda.stream(self.side):
+            rc = self.lib.dl4j_bucket_allreduce_update(ctypes.byref(f.args), native._ptr(st) if st.numel() else None,
+                                                       native._ptr(self.tables["chunks"]), self.chunk_bounds[b], self.chunk_bounds[b + 1],
+                                                       native._ptr(self.segs_dev), native._ptr(self.vars_dev), b, native._ptr(self.tickets),
+                                                       1 if f.use_multimem else 0, self.grid, native._stream())
+        native._check(rc, "dl4j_bucket_allreduce_update")
+
+    def after_backward(self):
+        f = self.fused
+        for b in range(self.n_buckets - 1, -1, -1):    # whatever did not report (unused parameters): same order on every rank
+            if not self.fired[b]:
+                self._fire(b)
+        cur = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        cur.wait_event(ev)
+        rc = self.lib.dl4j_bucket_finish(ctypes.byref(f.args), native._ptr(self.tables["chunks"]), native._ptr(self.segs_dev),
+                                         native._ptr(self.bounds_dev), self.n_buckets, native._ptr(self.vars_dev), f.params.numel(),
+                                         native._stream())
+        native._check(rc, "dl4j_bucket_finish")
+
+    def __call__(self, model):
+        upd = self.fused.updater
+        upd._fused_zeroes_grads = True
+        upd._shadow_fresh = self.fused.shadow is not None
+        self.fused.status.snapshot()
+        return True

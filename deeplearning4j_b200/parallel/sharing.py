@@ -217,7 +217,7 @@ class FusedThresholdSharing(GradientSharing):
 
 
 def attach_gradient_sharing(model, mode="averaging", impl="auto", thresholdAlgorithm=None, residualPostProcessor=None,
-                            group=None, use_multimem=None):
+                            group=None, use_multimem=None, buckets=None):
     """Install a sharing strategy on ``model`` (a DL4J network or a SameDiff ``TrainingState``).
 
     mode: ``"averaging"`` | ``"shared_gradients"``; impl: ``"fused"`` (NVLink kernels), ``"nccl"`` / ``"host"``
@@ -239,7 +239,20 @@ def attach_gradient_sharing(model, mode="averaging", impl="auto", thresholdAlgor
         n = t.params.numel()
         fused = FusedSharing(t.params, t.grads, t.shadow, t.updater, alloc, use_multimem,
                              message_ints=(4 + (n + 15) // 16) if mode != "averaging" else 0)
-        s = FusedAveraging(model, fused, group) if mode == "averaging" else FusedThresholdSharing(model, fused, thresholdAlgorithm, group)
+        import os
+        if buckets is None:
+            # default: one whole-buffer kernel after backward.  The bucketed form was measured slower on BERT-base (2 GPUs:
+            # 16.9 - 20 ms/step against 16.6): the tcgen05 GEMMs take all shared memory of every SM, so the exchange kernels
+            # cannot co-reside with them and only run between GEMM launches, where they add their own launch and flag latency.
+            buckets = int(os.environ.get("DL4J_EXCHANGE_BUCKETS", "1"))
+        if mode == "averaging" and buckets > 1 and hasattr(model, "tc") and model.flat_shadow is not None:
+            # SameDiff training state with a low-precision shadow: exchange overlapped with backward, bucket by bucket
+            from .fused import BucketedAveraging
+            s = BucketedAveraging(fused, model, n_buckets=buckets)
+            s.t, s.group, s.world, s.rank = t, group, fused.world, fused.rank
+            s.broadcast_parameters = GradientSharing.broadcast_parameters.__get__(s)
+        else:
+            s = FusedAveraging(model, fused, group) if mode == "averaging" else FusedThresholdSharing(model, fused, thresholdAlgorithm, group)
     elif mode == "averaging":
         s = NcclAveraging(model, group)
     else:

@@ -144,11 +144,20 @@ class _ShadowParam(torch.autograd.Function):
         # kernels that accumulate straight into the master gradient return no gradient for the shadow; without this
         # autograd would hand backward() a zero tensor, which costs a fill, a cast and an accumulate per parameter
         ctx.set_materialize_grads(False)
+        ctx.leaf = leaf
         return shadow.view_as(shadow)
 
     @staticmethod
     def backward(ctx, g):
-        return (None if g is None else g.float()), None
+        # this node runs once every consumer of the parameter has run its backward: the parameter's gradient is final
+        leaf = ctx.leaf
+        cb = getattr(leaf, "_grad_ready", None)
+        if cb is None:
+            return (None if g is None else g.float()), None
+        if g is not None:
+            leaf.grad.add_(g)            # accumulate here (not in AccumulateGrad, which runs later) so that "final" holds
+        cb(leaf)
+        return None, None
 
 
 class TrainingState:
@@ -237,12 +246,17 @@ class TrainingState:
         losses = sd.lossVariables or tc.lossVariables
         if not losses:
             raise ValueError("no loss variables: call sd.setLossVariables(...)")
+        hook = self.gradient_hook
+        if hook is not None and hasattr(hook, "pre_step"):
+            hook.pre_step(tc.iterationCount, tc.epochCount)       # per-step device variables of an overlapped exchange
         def fwd_bwd(ph):
             vals = InferenceSession(sd).run(ph, losses, self.values(), training=True)
             loss = vals[losses[0]].sum() if len(losses) == 1 else sum(vals[l].sum() for l in losses)
             if not tc.minimize:
                 loss = -loss
             loss.backward()
+            if hook is not None and hasattr(hook, "after_backward"):
+                hook.after_backward()                             # flush + join of the side stream (inside a graph capture too)
             return loss.detach()
         if tc.cudaGraphs and self.flat_params.is_cuda and not sd.listeners:
             self.score = self._graphed(placeholders, fwd_bwd)

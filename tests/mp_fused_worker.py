@@ -86,6 +86,52 @@ def run_pair(mode, updater_fn, bf16, multimem, steps=6):
     return d
 
 
+def bucketed_case(graphs, updater_fn, buckets=5, steps=7):
+    """SameDiff BERT-shaped model: exchange overlapped with backward bucket by bucket (fused kernels on a side stream, optionally
+    inside the captured CUDA graph) against NCCL all-reduce + the local updater."""
+    from deeplearning4j_b200 import DataType
+    from deeplearning4j_b200.models.bert import BertConfig, build_bert_mlm
+    from deeplearning4j_b200.ops import native
+    from deeplearning4j_b200.parallel.fused import BucketedAveraging
+    from deeplearning4j_b200.parallel.sharing import attach_gradient_sharing
+    from deeplearning4j_b200.samediff.training import _ensure_state
+    rank = dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = BertConfig(vocabSize=512, hidden=128, layers=3, heads=4, ffn=256, maxPositions=64)
+    B, T = 4, 64
+    states = []
+    for impl in ("fused", "nccl"):
+        torch.manual_seed(7)
+        sd = build_bert_mlm(cfg, B, T, updater_fn(), DataType.BFLOAT16).to(dev)
+        sd.getTrainingConfig().cudaGraphs = bool(graphs)
+        st = _ensure_state(sd)
+        hook = attach_gradient_sharing(st, "averaging", impl, buckets=buckets)
+        states.append((sd, st, hook))
+    (sda, a, ha), (sdb, b, hb) = states
+    assert isinstance(ha, BucketedAveraging) and ha.n_buckets >= 3, type(ha)
+    assert torch.equal(a.flat_params, b.flat_params)
+    for step in range(steps):
+        g = torch.Generator().manual_seed(50 * rank + step)
+        tok = torch.randint(0, cfg.vocabSize, (B, T), generator=g)
+        pos = torch.randperm(B * T, generator=g)[:40].sort().values
+        ph = {"tokens": tok.to(dev), "maskedPositions": pos.to(dev), "maskedLabels": tok.reshape(-1)[pos].to(dev)}
+        la = a.step(ph)
+        lb = b.step(ph)
+    torch.cuda.synchronize()
+    native.check_status()
+    d = float((a.flat_params - b.flat_params).abs().max())
+    assert d <= 3e-2, ("bucketed vs nccl", graphs, d)
+    assert abs(float(la) - float(lb)) <= 5e-2 * max(1.0, abs(float(lb))), (float(la), float(lb))
+    assert gather_equal(a.flat_params), "bucketed replicas diverged"
+    assert gather_equal(a.flat_shadow.float())
+    for e, so in zip(a.entries, a.shadow_offsets):
+        sh = a.flat_shadow[so:so + e.spec.numel].float()
+        assert float((sh - a.flat_params[e.offset:e.end]).abs().max()) <= 1e-2, e.spec.name
+    assert float(a.flat_grads.abs().max()) == 0.0
+    early = sum(1 for c in getattr(ha, "fired_early", []) if c)
+    return d, ha.n_buckets, early
+
+
 def timeout_case():
     """Rank 1 skips a step: rank 0's peer wait must expire and report through the status word, leaving the
     context usable."""
@@ -131,6 +177,10 @@ def main():
         for bf16 in (False, True):
             # plain SGD: the update is a smooth function of the gradient, so the two implementations stay comparable
             res[("thr", bf16)] = run_pair("threshold", lambda: nn.Sgd(0.5), bf16, False)
+    if what in ("all", "bucketed"):
+        for graphs in (False, True):
+            for upd in (lambda: nn.Adam(1e-3), lambda: nn.Nesterovs(0.05, 0.9)):
+                res[("bucketed", graphs, upd().JAVA)] = bucketed_case(graphs, upd)
     if what == "timeout":
         timeout_case()
     if dist.get_rank() == 0:

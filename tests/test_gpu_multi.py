@@ -32,5 +32,9 @@ def test_fused_threshold_matches_host_codec():
     _run("threshold", port=29712)
 
 
+def test_bucketed_exchange_overlapped_with_backward_matches_nccl():
+    _run("bucketed", port=29714)
+
+
 def test_bounded_peer_wait_reports_timeout():
     _run("timeout", port=29713, extra_env={"NCCL_NVLS_ENABLE": "0"})
