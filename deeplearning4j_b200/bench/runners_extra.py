@@ -188,8 +188,12 @@ class GradShareRunner(BaseRunner):
             n = side * side
             res = {"bytes": 4 * n}
             default_mm = W >= 4          # FusedSharing's own policy: in-switch reduction pays from four ranks on
+            # threshold "host" = the reference's algorithm as separate launches (baseline B2): updater kernel, encode kernel,
+            # NCCL all-gather of the messages, one decode launch per peer (libnd4j/include/loops/cuda/type_conversions.cu:215-354)
             for mode, impl, mm in (("averaging", "fused", None), ("averaging", "fused", not default_mm), ("averaging", "nccl", None),
-                                   ("shared_gradients", "fused", None)):
+                                   ("shared_gradients", "fused", None), ("shared_gradients", "host", None)):
+                if impl == "host" and n > 4096 * 4096 * 4:
+                    continue
                 conf = (nn.NeuralNetConfiguration.Builder().seed(1).updater(nn.Sgd(0.1)).list()
                         .layer(nn.DenseLayer(nIn=side, nOut=side, hasBias=False, activation="identity"))
                         .layer(nn.LossLayer("MSE", activation="identity")).build())
@@ -239,7 +243,10 @@ class GradShareRunner(BaseRunner):
                 if key == "threshold_fused":
                     link_bytes = (W - 1) * (n / 16 + 4) * 4
                     res["threshold_fused_roofline_frac"] = (link_bytes / (self.LINK_GBS * 1e9)) / (ms / 1e3)
+                    # local traffic: gradient, parameters, residual read + residual, gradient written, then parameters read and written
                     res["threshold_hbm_bound_ms"] = (4 * n * 7) / 6.5475e12 * 1e3
+                    res["threshold_fused_frac_of_hbm_bound"] = res["threshold_hbm_bound_ms"] / ms
+                    res["threshold_fused_form"] = "bitmap" if s.fused.last_form == 1 else "index list"
                 net.gradient_hook = None
                 del net, s, src
                 torch.cuda.empty_cache()

@@ -416,18 +416,90 @@ bucket_finish_kernel(const CommCtx c, const UpdChunk* __restrict__ chunks, const
 }
 
 // ------------------------------------------------------------------------------------------------ K1
-// Threshold ("shared gradients") step.  msg layout per rank: [k, N, bits(tau), 1, words...] (bitmap encoding).
+// Threshold ("shared gradients") step in one launch.
+//
+// Message slot of a rank (int32, double-buffered by step parity):
+//   [0] k = elements sent   [1] N   [2] bits(tau)   [3] form: 1 = bitmap, 0 = index list   [4] number of list segments
+//   [5] capacity of one list segment   [6..63] unused   [64 .. 64 + segments) entries written per segment
+//   payload at thr_payload(segments): bitmap = one word per 16 elements (bit b = |r| >= tau, bit b + 16 = negative; a negative
+//   value in [tau/2, tau) sets only the sign bit and moves by tau/2 -- the reference's bitmap format,
+//   libnd4j/include/loops/cuda/type_conversions.cu:380-500), or index list = one segment per updater chunk holding
+//   +-(index + 1) for every |r| >= tau of that chunk (the reference's primary "flexible" form, type_conversions.cu:215-311,
+//   without its global prefix scan: the segment of a chunk sits at the chunk's own word range, so it holds count / 16
+//   entries, and the CTA working on the chunk appends through a shared-memory cursor; what does not fit stays in the
+//   residual and goes out in a later step, as with the reference's encoding boundary).
+// Phase 1 is a single sweep: updater on the local gradient, add into the residual, encode from registers, write the
+// remainder back, clear the gradient.  Phase 2 sums every rank's message into the parameters and writes the bf16 shadow of what
+// it touched in the same loop (bitmap messages: one word per thread, vector read-modify-write; list messages: atomics,
+// then a pass over the same entries for the shadow).  The form is chosen by the host from the density of the previous step.
+constexpr int THR_HEADER = 64;
+__host__ __device__ __forceinline__ long long thr_payload(int segments) { return THR_HEADER + (segments + 63) / 64 * 64; }
+
+struct EncodeOut {
+  int* words;           // bitmap payload
+  int* seg;             // this CTA's list segment
+  int seg_cap;
+  int form;             // 1 bitmap, 0 list
+};
+
+// Encodes one element held in a register; returns the 2-bit code (bit 0 magnitude, bit 1 sign) for the bitmap form.
+__device__ __forceinline__ int encode_one(float& r, float tau, float half, int form, long long idx, const EncodeOut& eo, int* cursor,
+                                          int& sent) {
+  const float a = fabsf(r);
+  if (a >= tau) {
+    const bool neg = r < 0.f;
+    if (form == 0) {
+      const int pos = atomicAdd(cursor, 1);
+      if (pos >= eo.seg_cap) return 0;                 // segment full: the value stays in the residual
+      eo.seg[pos] = neg ? -(int)(idx + 1) : (int)(idx + 1);
+    }
+    r += neg ? tau : -tau;
+    ++sent;
+    return neg ? 3 : 1;
+  }
+  if (form == 1 && a >= half && r < 0.f) {
+    r += half;
+    ++sent;
+    return 2;
+  }
+  return 0;
+}
+
+__device__ __forceinline__ int find_segment(const UpdSegment* __restrict__ segs, int n_segs, long long idx) {
+  int lo = 0, hi = n_segs - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (segs[mid].offset <= idx) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
 __global__ void __launch_bounds__(COMM_THREADS)
 threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __restrict__ residual,
-                       const UpdChunk* __restrict__ chunks, int n_chunks, const UpdSegment* __restrict__ segs,
+                       const UpdChunk* __restrict__ chunks, int n_chunks, const UpdSegment* __restrict__ segs, int n_segs,
                        const UpdHyperTable ht, float grad_scale, float tau, long long n_total, uint32_t epoch,
-                       unsigned int* scratch, int msg_parity, long long msg_stride_ints, int* status) {
+                       unsigned int* scratch, int msg_parity, long long msg_stride_ints, int form, int* status) {
+  __shared__ int cursor;            // entries appended to this CTA's list segment
+  __shared__ int cta_sent;
   unsigned int bar = 0;
   bool ok = true;
   float* grads = c.grads[c.rank];
   float* params = c.params[c.rank];
   __nv_bfloat16* shadow = c.shadow[c.rank];
-  // ---- phase 1a: updater on the local gradient, accumulated into the residual; gradient cleared
+  int* my_msg = c.msg[c.rank] + (long long)msg_parity * msg_stride_ints;
+  const int n_seg = n_chunks;
+  const long long payload = thr_payload(n_seg);
+  const float half = tau * 0.5f;
+  EncodeOut eo;
+  eo.words = my_msg + payload;
+  eo.seg = eo.words;
+  eo.seg_cap = 0;
+  eo.form = form;
+  if (threadIdx.x == 0) cta_sent = 0;
+  const int lane = threadIdx.x & 31;
+
+  // ---- phase 1: updater -> residual -> encode -> residual remainder, gradient cleared (one sweep)
+  int sent = 0;
   for (int ci = blockIdx.x; ci < n_chunks; ci += gridDim.x) {
     const UpdChunk ch = chunks[ci];
     const UpdSegment sg = segs[ch.seg];
@@ -436,95 +508,222 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
     float* st0 = state + sg.state_off + rel0;
     float* st1 = st0 + sg.block_numel;
     float* st2 = st1 + sg.block_numel;
-    for (int e = threadIdx.x; e < ch.count; e += COMM_THREADS) {
-      const long long i = ch.offset + e;
-      if (sg.kernel_id != 9) residual[i] += updater_step(sg, h, params[i], grads[i] * grad_scale, st0 + e, st1 + e, st2 + e);
-      grads[i] = 0.f;
-    }
-  }
-  ok = grid_barrier(scratch, gridDim.x * (++bar), status);
-  // ---- phase 1b: bitmap-encode the residual into this rank's message slot (residual keeps the remainder)
-  int* my_msg = c.msg[c.rank] + (long long)msg_parity * msg_stride_ints;
-  const long long words = (n_total + 15) / 16;
-  const float half = tau * 0.5f;
-  if (ok) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) { my_msg[1] = (int)n_total; my_msg[2] = __float_as_int(tau); my_msg[3] = 1; }
-    for (long long w = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; w < words; w += (long long)gridDim.x * COMM_THREADS) {
-      const long long base = w * 16;
-      int word = 0;
+    const int ns = upd_n_state(sg.kernel_id);
+    const uintptr_t al = (uintptr_t)(ch.offset & 15) | (ns > 0 ? reinterpret_cast<uintptr_t>(st0) : 0) |
+                         (ns > 1 ? reinterpret_cast<uintptr_t>(st1) : 0) | (ns > 2 ? reinterpret_cast<uintptr_t>(st2) : 0);
+    const bool vec_ok = (al & 15) == 0;               // chunk starts on a word boundary and every array is 16-byte aligned
+    const int nvec = vec_ok ? ch.count / 4 : 0;
+    // this chunk's list segment: the words that lie wholly inside the chunk
+    const long long seg0 = (ch.offset + 15) >> 4;
+    eo.seg = eo.words + seg0;
+    eo.seg_cap = (int)max(0LL, ((ch.offset + ch.count) >> 4) - seg0);
+    __syncthreads();                                  // previous chunk's appends are done
+    if (threadIdx.x == 0) cursor = 0;
+    __syncthreads();
+    // every load of a vector is issued before the first use
+    constexpr int U = 1;      // (two vectors per thread cost a second resident CTA per SM: 117 registers, measured slower)
+    for (int vb = (threadIdx.x & ~31); vb < nvec; vb += COMM_THREADS * U) {
+      float4 g4[U], w4[U], r4[U], a4[U], b4[U], c4[U];
+      bool valid[U];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        float v[4];
-        if (base + 4 * q4 + 4 <= n_total) {
-          const float4 a = *reinterpret_cast<const float4*>(residual + base + 4 * q4);
-          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) v[j] = (base + 4 * q4 + j < n_total) ? residual[base + 4 * q4 + j] : 0.f;
-        }
-        bool touched = false;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int bit = 4 * q4 + j;
-          const float a = fabsf(v[j]);
-          if (a >= tau) {
-            word |= 1 << bit;
-            if (v[j] < 0.f) { word |= 1 << (bit + 16); v[j] += tau; } else { v[j] -= tau; }
-            touched = true;
-          } else if (a >= half && v[j] < 0.f) {
-            word |= 1 << (bit + 16);
-            v[j] += half;
-            touched = true;
+      for (int u = 0; u < U; ++u) {
+        const int v = vb + u * COMM_THREADS + lane;
+        valid[u] = v < nvec;
+        g4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        w4[u] = g4[u]; r4[u] = g4[u]; a4[u] = g4[u]; b4[u] = g4[u]; c4[u] = g4[u];
+        if (valid[u]) {
+          const long long i = ch.offset + 4LL * v;
+          g4[u] = *reinterpret_cast<const float4*>(grads + i);
+          w4[u] = *reinterpret_cast<const float4*>(params + i);
+          r4[u] = *reinterpret_cast<const float4*>(residual + i);
+          if (sg.kernel_id != 9) {
+            if (ns > 0) a4[u] = *reinterpret_cast<const float4*>(st0 + 4 * v);
+            if (ns > 1) b4[u] = *reinterpret_cast<const float4*>(st1 + 4 * v);
+            if (ns > 2) c4[u] = *reinterpret_cast<const float4*>(st2 + 4 * v);
           }
         }
-        if (touched) {
-          if (base + 4 * q4 + 4 <= n_total) *reinterpret_cast<float4*>(residual + base + 4 * q4) = make_float4(v[0], v[1], v[2], v[3]);
-          else
-            for (int j = 0; j < 4; ++j) if (base + 4 * q4 + j < n_total) residual[base + 4 * q4 + j] = v[j];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = vb + u * COMM_THREADS + lane;
+        int part = 0;
+        if (valid[u]) {
+          const long long i = ch.offset + 4LL * v;
+          float gv[4] = {g4[u].x, g4[u].y, g4[u].z, g4[u].w}, wv[4] = {w4[u].x, w4[u].y, w4[u].z, w4[u].w},
+                rv[4] = {r4[u].x, r4[u].y, r4[u].z, r4[u].w};
+          if (sg.kernel_id != 9) {
+            float sa[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w}, sb[4] = {b4[u].x, b4[u].y, b4[u].z, b4[u].w},
+                  sc[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) rv[j] += updater_step(sg, h, wv[j], gv[j] * grad_scale, sa + j, sb + j, sc + j);
+            if (ns > 0) *reinterpret_cast<float4*>(st0 + 4 * v) = make_float4(sa[0], sa[1], sa[2], sa[3]);
+            if (ns > 1) *reinterpret_cast<float4*>(st1 + 4 * v) = make_float4(sb[0], sb[1], sb[2], sb[3]);
+            if (ns > 2) *reinterpret_cast<float4*>(st2 + 4 * v) = make_float4(sc[0], sc[1], sc[2], sc[3]);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int code = encode_one(rv[j], tau, half, form, i + j, eo, &cursor, sent);
+            part |= ((code & 1) << (4 * (lane & 3) + j)) | (((code >> 1) & 1) << (16 + 4 * (lane & 3) + j));
+          }
+          *reinterpret_cast<float4*>(residual + i) = make_float4(rv[0], rv[1], rv[2], rv[3]);
+          *reinterpret_cast<float4*>(grads + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (form == 1 && vb + u * COMM_THREADS < nvec) {          // warp-uniform
+          // four neighbouring lanes hold the four nibbles of one word
+          part |= __shfl_xor_sync(0xffffffffu, part, 1);
+          part |= __shfl_xor_sync(0xffffffffu, part, 2);
+          if (valid[u] && (lane & 3) == 0) {
+            const long long wi = (ch.offset + 4LL * v) >> 4;
+            if (4 * (v + 4) <= ch.count) eo.words[wi] = part;            // whole word inside the chunk
+            else if (part) atomicOr(eo.words + wi, part);                  // shared with the next chunk
+          }
         }
       }
-      my_msg[4 + w] = word;
     }
+    // scalar tail (and whole chunk when it is not aligned): bits go in with atomics (the payload was zeroed before the launch)
+    for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) {
+      const long long i = ch.offset + e;
+      float r = residual[i];
+      if (sg.kernel_id != 9) r += updater_step(sg, h, params[i], grads[i] * grad_scale, st0 + e, st1 + e, st2 + e);
+      const int code = encode_one(r, tau, half, form, i, eo, &cursor, sent);
+      if (form == 1 && code) atomicOr(eo.words + (i >> 4), ((code & 1) << (i & 15)) | (((code >> 1) & 1) << (16 + (i & 15))));
+      residual[i] = r;
+      grads[i] = 0.f;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) my_msg[THR_HEADER + ci] = min(cursor, eo.seg_cap);
+  }
+  // element count of this CTA -> header
+  for (int o = 16; o > 0; o >>= 1) sent += __shfl_xor_sync(0xffffffffu, sent, o);
+  if (lane == 0 && sent) atomicAdd(&cta_sent, sent);
+  __syncthreads();
+  if (threadIdx.x == 0 && cta_sent) atomicAdd(reinterpret_cast<int*>(scratch) + 1, cta_sent);
+  __threadfence_system();
+  // ---- exchange: every rank's message is complete
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && ok) {
+    my_msg[0] = *((volatile int*)scratch + 1);
+    my_msg[1] = (int)n_total; my_msg[2] = __float_as_int(tau); my_msg[3] = form; my_msg[4] = n_seg; my_msg[5] = 0;
     __threadfence_system();
   }
-  // ---- exchange: every rank's message is complete
-  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok;
   if (blockIdx.x == 0 && ok) ok = peer_barrier(c, 2, epoch, status);
   ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok && *((volatile int*)status) == 0;
-  // ---- phase 2: decode the sum of all ranks' messages and apply it to the local parameters
-  if (ok) {
-    const float ntau = tau, nhalf = half;
-    for (long long w = blockIdx.x * (long long)COMM_THREADS + threadIdx.x; w < words; w += (long long)gridDim.x * COMM_THREADS) {
-      int wr[MAX_RANKS];
-      int any = 0;
-#pragma unroll
-      for (int r = 0; r < MAX_RANKS; ++r) {
-        wr[r] = 0;
-        if (r < c.world) {
-          wr[r] = ld_peer_i(c.msg[r] + (long long)msg_parity * msg_stride_ints + 4 + w);
-          any |= wr[r];
-        }
-      }
-      if (!any) continue;
-      const long long base = w * 16;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (base + j >= n_total) break;
-        float d = 0.f;
+  if (!ok) return;
+
+  // ---- phase 2a: bitmap messages, chunk by chunk (a word per thread; vector read-modify-write; shadow written in the same loop)
+  __shared__ int peer_form[MAX_RANKS], peer_segs[MAX_RANKS];
+  if (threadIdx.x < c.world) {
+    const int* pm = c.msg[threadIdx.x] + (long long)msg_parity * msg_stride_ints;
+    peer_form[threadIdx.x] = ld_peer_i(pm + 3);
+    peer_segs[threadIdx.x] = ld_peer_i(pm + 4);
+  }
+  __syncthreads();
+  bool any_bitmap = false, any_list = false;
+  for (int r = 0; r < c.world; ++r) { any_bitmap |= peer_form[r] == 1; any_list |= peer_form[r] == 0; }
+  if (any_bitmap) {
+    for (int ci = blockIdx.x; ci < n_chunks; ci += gridDim.x) {
+      const UpdChunk ch = chunks[ci];
+      const UpdSegment sg = segs[ch.seg];
+      const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+      const bool vec = ((ch.offset & 15) == 0);
+      const int nvec = vec ? ch.count / 4 : 0;
+      // a float4 per thread: four neighbouring lanes read the same word of every bitmap peer and take one nibble each
+      for (int vb = (threadIdx.x & ~31); vb < nvec; vb += COMM_THREADS) {
+        const int v = vb + lane;
+        const bool valid = v < nvec;
+        const long long i = ch.offset + 4LL * (valid ? v : 0);
+        const long long w = i >> 4;
+        const int sh = (int)(i & 15);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        int any = 0;
 #pragma unroll
         for (int r = 0; r < MAX_RANKS; ++r) {
-          const bool bit = wr[r] & (1 << j), sign = wr[r] & (1 << (j + 16));
-          if (bit) d += sign ? -ntau : ntau;
-          else if (sign) d -= nhalf;
+          if (r < c.world && peer_form[r] == 1) {
+            // one lane of four fetches the word (a word crosses the link once), the others get it by shuffle
+            int wr = 0;
+            if ((lane & 3) == 0 && valid) wr = ld_peer_i(c.msg[r] + (long long)msg_parity * msg_stride_ints + thr_payload(peer_segs[r]) + w);
+            wr = __shfl_sync(0xffffffffu, wr, lane & ~3);
+            const int mag = (wr >> sh) & 15, sgn = (wr >> (16 + sh)) & 15;
+            any |= mag | sgn;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const bool bit = mag & (1 << j), sign = sgn & (1 << j);
+              if (bit) d[j] += sign ? -tau : tau;
+              else if (sign) d[j] -= half;
+            }
+          }
         }
-        if (d != 0.f) {
-          const float nw = params[base + j] - d;
-          params[base + j] = nw;
+        if (!any || !valid) continue;
+        float4* pp = reinterpret_cast<float4*>(params + i);
+        float4 pv = *pp;
+        pv.x -= d[0]; pv.y -= d[1]; pv.z -= d[2]; pv.w -= d[3];
+        *pp = pv;
+        if (shadow) {
+          __nv_bfloat16* sp = shadow + sh0 + 4LL * v;
+          if ((reinterpret_cast<uintptr_t>(sp) & 7) == 0) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(pv.x, pv.y), hi = __floats2bfloat162_rn(pv.z, pv.w);
+            *reinterpret_cast<uint2*>(sp) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          } else {
+            sp[0] = __float2bfloat16(pv.x); sp[1] = __float2bfloat16(pv.y); sp[2] = __float2bfloat16(pv.z); sp[3] = __float2bfloat16(pv.w);
+          }
         }
+      }
+      // scalar tail (and whole chunk when it does not start on a word boundary)
+      for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) {
+        const long long i = ch.offset + e;
+        float dj = 0.f;
+        for (int r = 0; r < c.world; ++r) {
+          if (peer_form[r] != 1) continue;
+          const int wr = ld_peer_i(c.msg[r] + (long long)msg_parity * msg_stride_ints + thr_payload(peer_segs[r]) + (i >> 4));
+          const bool bit = wr & (1 << (i & 15)), sign = wr & (1 << ((i & 15) + 16));
+          if (bit) dj += sign ? -tau : tau;
+          else if (sign) dj -= half;
+        }
+        if (dj == 0.f) continue;
+        const float nw = params[i] - dj;
+        params[i] = nw;
+        if (shadow) shadow[sh0 + e] = __float2bfloat16(nw);
       }
     }
   }
-  (void)shadow;
+  if (!any_list) return;                       // uniform over the grid: every CTA read the same headers
+  // ---- phase 2b: index-list messages (after the bitmap pass: both write the parameters)
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status);
+  if (!ok) return;
+  for (int r = 0; r < c.world; ++r) {
+    if (peer_form[r] != 0) continue;
+    const int* pm = c.msg[r] + (long long)msg_parity * msg_stride_ints;
+    const int* pl = pm + thr_payload(peer_segs[r]);
+    for (int sgm = blockIdx.x; sgm < min(peer_segs[r], n_chunks); sgm += gridDim.x) {
+      const long long seg0 = (chunks[sgm].offset + 15) >> 4;
+      const int cnt = ld_peer_i(pm + THR_HEADER + sgm);
+      for (int e = threadIdx.x; e < cnt; e += COMM_THREADS) {
+        const int code = ld_peer_i(pl + seg0 + e);
+        const long long idx = (code < 0 ? -code : code) - 1;
+        if (idx >= 0 && idx < n_total) atomicAdd(params + idx, code < 0 ? tau : -tau);
+      }
+    }
+  }
+  if (!shadow) return;
+  // ---- phase 2c: shadow of the touched elements from the final parameter values
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status);
+  if (!ok) return;
+  for (int r = 0; r < c.world; ++r) {
+    if (peer_form[r] != 0) continue;
+    const int* pm = c.msg[r] + (long long)msg_parity * msg_stride_ints;
+    const int* pl = pm + thr_payload(peer_segs[r]);
+    for (int sgm = blockIdx.x; sgm < min(peer_segs[r], n_chunks); sgm += gridDim.x) {
+      const long long seg0 = (chunks[sgm].offset + 15) >> 4;
+      const int cnt = ld_peer_i(pm + THR_HEADER + sgm);
+      for (int e = threadIdx.x; e < cnt; e += COMM_THREADS) {
+        const int code = ld_peer_i(pl + seg0 + e);
+        const long long idx = (code < 0 ? -code : code) - 1;
+        if (idx < 0 || idx >= n_total) continue;
+        const UpdSegment sg = segs[find_segment(segs, n_segs, idx)];
+        shadow[sg.shadow_off + (idx - sg.offset)] = __float2bfloat16(__ldcg(params + idx));
+      }
+    }
+  }
 }
 
 // Refreshes the bf16 shadow from the fp32 parameters following the segment table (used after a
@@ -635,12 +834,12 @@ DL4J_API int dl4j_bucket_finish(const void* comm_args, const void* chunks, const
 DL4J_API int dl4j_step_vars_bytes() { return (int)sizeof(StepVars); }
 
 DL4J_API int dl4j_threshold_share(const void* comm_args, float* state, float* residual, const void* chunks, int n_chunks,
-                                  const void* segs, const float* hyper, int n_hyper, float grad_scale, float tau,
+                                  const void* segs, int n_segs, const float* hyper, int n_hyper, float grad_scale, float tau,
                                   long long n_total, unsigned int epoch, void* scratch, int msg_parity,
-                                  long long msg_stride_ints, void* stream_) {
+                                  long long msg_stride_ints, int form, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   const HostCommArgs* a = reinterpret_cast<const HostCommArgs*>(comm_args);
-  if (a->world < 1 || a->world > MAX_RANKS || n_hyper > UPD_MAX_HYPER || n_total >= 2147483647LL) return -DL4J_ERR_BAD_ARG;
+  if (a->world < 1 || a->world > MAX_RANKS || n_hyper > UPD_MAX_HYPER || n_total >= 2147483647LL || n_segs < 1) return -DL4J_ERR_BAD_ARG;
   CommCtx c = make_ctx(a);
   UpdHyperTable ht;
   memset(&ht, 0, sizeof(ht));
@@ -650,16 +849,25 @@ DL4J_API int dl4j_threshold_share(const void* comm_args, float* state, float* re
   int* status = dl4j_status_word(dev);
   const int grid = coop_grid(threshold_share_kernel, COMM_THREADS);
   if (grid < 1) return -DL4J_ERR_BAD_ARG;
+  const long long words = (n_total + 15) / 16;
+  if (thr_payload(n_chunks) + words > msg_stride_ints) return -DL4J_ERR_BAD_ARG;
   cudaMemsetAsync(scratch, 0, 16, stream);
+  // bitmap bits of chunk edges and unaligned chunks are OR-ed in: this step's payload starts from zero
+  if (form == 1)
+    cudaMemsetAsync(reinterpret_cast<int*>(a->msg[a->rank]) + (long long)msg_parity * msg_stride_ints + thr_payload(n_chunks), 0,
+                    (size_t)words * 4, stream);
   const UpdChunk* ch = reinterpret_cast<const UpdChunk*>(chunks);
   const UpdSegment* sg = reinterpret_cast<const UpdSegment*>(segs);
   unsigned int* sc = reinterpret_cast<unsigned int*>(scratch);
-  void* args[] = {(void*)&c, (void*)&state, (void*)&residual, (void*)&ch, (void*)&n_chunks, (void*)&sg, (void*)&ht,
+  void* args[] = {(void*)&c, (void*)&state, (void*)&residual, (void*)&ch, (void*)&n_chunks, (void*)&sg, (void*)&n_segs, (void*)&ht,
                   (void*)&grad_scale, (void*)&tau, (void*)&n_total, (void*)&epoch, (void*)&sc, (void*)&msg_parity,
-                  (void*)&msg_stride_ints, (void*)&status};
+                  (void*)&msg_stride_ints, (void*)&form, (void*)&status};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)threshold_share_kernel, dim3(grid), dim3(COMM_THREADS), args, 0, stream);
   return (int)e;
 }
+
+// Ints a message slot must hold for a buffer of n_total elements (header + segment table + payload), for any grid this library uses.
+DL4J_API long long dl4j_threshold_msg_ints(long long n_total, int n_chunks) { return thr_payload(n_chunks) + (n_total + 15) / 16 + 64; }
 
 DL4J_API int dl4j_shadow_refresh(const float* params, void* shadow, const void* chunks, int n_chunks, const void* segs, void* stream) {
   if (n_chunks <= 0) return 0;

@@ -133,6 +133,13 @@ class FusedSharing:
         self.msg = None
         hm = None
         if message_ints:
+            lib0 = native.require()
+            lib0.dl4j_threshold_msg_ints.argtypes = [ctypes.c_longlong, ctypes.c_int]
+            lib0.dl4j_threshold_msg_ints.restype = ctypes.c_longlong
+            t0 = native.update_tables(updater, 0, 0, updater.shadow_offsets)
+            if t0 is None:
+                raise RuntimeError("updater configuration is not supported by the fused kernel")
+            message_ints = max(int(message_ints), int(lib0.dl4j_threshold_msg_ints(params.numel(), t0["n_chunks"])))
             self.msg_stride = (int(message_ints) + 63) // 64 * 64
             self.msg = alloc.empty(2 * self.msg_stride, torch.int32, dev)
             hm = alloc.handle(self.msg)
@@ -162,7 +169,7 @@ class FusedSharing:
         vp, i32, i64, u32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint, ctypes.c_float
         lib.dl4j_allreduce_update.argtypes = [vp, vp, vp, i32, vp, vp, i32, f32, i64, u32, vp, i32, vp]
         lib.dl4j_allreduce_update.restype = i32
-        lib.dl4j_threshold_share.argtypes = [vp, vp, vp, vp, i32, vp, vp, i32, f32, f32, i64, u32, vp, i32, i64, vp]
+        lib.dl4j_threshold_share.argtypes = [vp, vp, vp, vp, i32, vp, i32, vp, i32, f32, f32, i64, u32, vp, i32, i64, i32, vp]
         lib.dl4j_threshold_share.restype = i32
         lib.dl4j_shadow_refresh.argtypes = [vp, vp, vp, i32, vp, vp]
         lib.dl4j_shadow_refresh.restype = i32
@@ -189,8 +196,10 @@ class FusedSharing:
         upd._fused_zeroes_grads = True
         upd._shadow_fresh = self.shadow is not None
 
-    def threshold_share(self, iteration, epoch, tau):
-        """Shared gradients: updater -> residual -> bitmap encode -> exchange -> decode sum -> apply."""
+    def threshold_share(self, iteration, epoch, tau, form=None):
+        """Shared gradients in one launch: updater -> residual -> encode -> exchange -> decode sum -> apply (+ bf16 shadow).
+        ``form``: 1 = bitmap, 0 = index list, None = chosen from the density the previous step reported (list when at most one
+        element in 32 was sent: the list then is at most half the size of the bitmap)."""
         upd = self.updater
         t = native.update_tables(upd, iteration, epoch, upd.shadow_offsets)
         if t is None:
@@ -198,21 +207,47 @@ class FusedSharing:
         if self.residual is None:
             self.residual = torch.zeros_like(self.params)
         self.status.check()
+        self._poll_sent()
+        if form is None:
+            form = 0 if (self.last_sparsity is not None and self.last_sparsity <= 1.0 / 32.0) else 1
+        self.last_form = int(form)
         self.epoch += 1
+        parity = self.epoch & 1
         hp = t["hyper"].ctypes.data_as(ctypes.c_void_p)
         st = upd.state
         rc = self.lib.dl4j_threshold_share(ctypes.byref(self.args), native._ptr(st) if st.numel() else None,
                                            native._ptr(self.residual), native._ptr(t["chunks"]), t["n_chunks"],
-                                           native._ptr(t["segs_dev"]), hp, t["n_hyper"], 1.0, float(tau), self.params.numel(),
-                                           self.epoch, native._ptr(self.scratch), self.epoch & 1, self.msg_stride, native._stream())
+                                           native._ptr(t["segs_dev"]), len(t["seg_rows"]), hp, t["n_hyper"], 1.0, float(tau),
+                                           self.params.numel(), self.epoch, native._ptr(self.scratch), parity, self.msg_stride,
+                                           int(form), native._stream())
         native._check(rc, "dl4j_threshold_share")
-        if self.shadow is not None:
-            rc = self.lib.dl4j_shadow_refresh(native._ptr(self.params), native._ptr(self.shadow), native._ptr(t["chunks"]),
-                                              t["n_chunks"], native._ptr(t["segs_dev"]), native._stream())
-            native._check(rc, "dl4j_shadow_refresh")
+        # the header's element count comes back one step late (pinned copy + event, no synchronisation)
+        if self._k_pinned is None:
+            self._k_pinned = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._k_pinned[parity].copy_(self.msg[parity * self.msg_stride:parity * self.msg_stride + 1], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._k_event = (ev, parity)
         self.status.snapshot()
         upd._fused_zeroes_grads = True
         upd._shadow_fresh = self.shadow is not None
+
+    _k_pinned = None
+    _k_event = None
+    last_sparsity = None
+    last_form = 1
+
+    def _poll_sent(self, wait=False):
+        """Fraction of elements the last finished step sent (None until one has finished)."""
+        if self._k_event is None:
+            return self.last_sparsity
+        ev, parity = self._k_event
+        if wait:
+            ev.synchronize()
+        if ev.query():
+            self.last_sparsity = int(self._k_pinned[parity][0]) / max(self.params.numel(), 1)
+            self._k_event = None
+        return self.last_sparsity
 
 
 class BucketedAveraging:

@@ -210,10 +210,15 @@ class FusedThresholdSharing(GradientSharing):
 
     def __call__(self, model):
         it, ep = self.t.counters()
-        tau = self.algo.calculateThreshold(it, ep, self.lastThreshold, True, None, None)
+        f = self.fused
+        # density and form of the last finished step (read back without a synchronisation, so one step late)
+        sparsity = f._poll_sent()
+        tau = self.algo.calculateThreshold(it, ep, self.lastThreshold, f.last_form == 1, sparsity, None)
         self.lastThreshold = tau
-        self.fused.threshold_share(it, ep, tau)
+        f.threshold_share(it, ep, tau, self.encoding)
         return True
+
+    encoding = None       # None = by density; codec.BITMAP_ENCODING / codec.FLEXIBLE_ENCODING force a form
 
 
 def attach_gradient_sharing(model, mode="averaging", impl="auto", thresholdAlgorithm=None, residualPostProcessor=None,
