@@ -275,3 +275,59 @@ def decode_bitmap(x, encoded, **kw):
     out = x.clone().float()
     codec.bitmap_decode(encoded, out)
     return out.to(x.dtype)
+
+
+# ----------------------------------------------------------------------------- TensorFlow-style TensorArray ops
+# Graphs imported from TensorFlow (and the reference's .fb files made from them) thread a scalar "flow" value through the
+# TensorArray ops to order them: write / scatter / split return the flow, read / gather / size / concat take it as their last input
+# (libnd4j/include/ops/declarable/generic/list/*.cpp under their tensorarray*v3 synonyms).
+def _flow():
+    return torch.zeros((), dtype=torch.float32)
+
+
+@op("tf_list_create", n_out=2, differentiable=False)
+def tf_list_create(size=None, **kw):
+    n = int(torch.as_tensor(size).reshape(-1)[0]) if size is not None else 0
+    return NDArrayList(max(n, 0)), _flow()
+
+
+@op("tf_list_write", differentiable=False)
+def tf_list_write(lst, idx, v, flow=None, **kw):
+    lst.write(int(torch.as_tensor(idx).reshape(-1)[0]), v)
+    return _flow()
+
+
+@op("tf_list_read")
+def tf_list_read(lst, idx, flow=None, **kw):
+    return lst.read(int(torch.as_tensor(idx).reshape(-1)[0]))
+
+
+@op("tf_list_gather")
+def tf_list_gather(lst, idx, flow=None, **kw):
+    return torch.stack([lst.read(int(i)) for i in torch.as_tensor(idx).reshape(-1).tolist()])
+
+
+@op("tf_list_scatter", differentiable=False)
+def tf_list_scatter(lst, idx, x, flow=None, **kw):
+    for k, i in enumerate(torch.as_tensor(idx).reshape(-1).tolist()):
+        lst.write(int(i), x[k])
+    return _flow()
+
+
+@op("tf_list_split", differentiable=False)
+def tf_list_split(lst, x, sizes, flow=None, **kw):
+    pos = 0
+    for k, n in enumerate(torch.as_tensor(sizes).reshape(-1).tolist()):
+        lst.write(k, x[pos:pos + int(n)])
+        pos += int(n)
+    return _flow()
+
+
+@op("tf_list_size", differentiable=False)
+def tf_list_size(lst, flow=None, **kw):
+    return torch.tensor(lst.size, dtype=torch.int64)
+
+
+@op("tf_list_concat")
+def tf_list_concat(lst, flow=None, **kw):
+    return torch.cat([lst.read(i) for i in range(lst.size)], 0)

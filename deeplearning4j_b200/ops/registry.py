@@ -12,7 +12,7 @@ from dataclasses import dataclass, field
 from typing import Callable
 
 _IMPL_MODULES = ("impl_elementwise", "impl_reduce", "impl_shape", "impl_nn", "impl_conv", "impl_loss", "impl_rnn",
-                 "impl_linalg", "impl_random", "impl_image", "impl_misc", "impl_updaters")
+                 "impl_linalg", "impl_random", "impl_image", "impl_misc", "impl_updaters", "impl_legacy")
 
 
 @dataclass

@@ -529,21 +529,22 @@ class SameDiff:
 
     # ------------------------------------------------------------------ control flow
     def ifCond(self, *a):
-        """``ifCond([outputName, ifName,] cond_fn, true_fn, false_fn)``: lambdas build sub-graphs over this instance."""
+        """``ifCond([outputName, ifName,] cond_fn, true_fn, false_fn)`` (``ControlFlow.java:139``): the lambdas build sub-graphs over
+        this instance; the result is a ``merge`` of the two branches, each gated by ``switch`` nodes on the predicate, so only the
+        taken branch executes and the construct is part of the serialised graph."""
+        from .controlflow import build_if
         fns = [f for f in a if callable(f)]
         names = [n for n in a if isinstance(n, str) or n is None]
         cond, tb, fb = fns
-        c = cond(self)
-        t, f = tb(self), fb(self)
-        return self._op("select", [c, t, f], name=names[0] if names and names[0] else None)
+        return build_if(self, cond, tb, fb, name=names[0] if names and names[0] else None)
 
     def whileLoop(self, *a):
         """``whileLoop([outputNames, loopName,] loopVars, cond, body)`` (``SameDiff.java`` ``whileLoop``).
 
-        ``cond`` / ``body`` are either SameDiff lambdas ``(sd, SDVariable[]) -> SDVariable | SDVariable[]`` that
-        define ops on this instance (captured once and replayed per iteration; they may read outer variables), or
-        plain callables over torch tensors ``(*tensors) -> tensor(s)``.  Both run eagerly inside one
-        ``while_loop`` node."""
+        ``cond`` / ``body`` are either SameDiff lambdas ``(sd, SDVariable[]) -> SDVariable | SDVariable[]`` that define ops on
+        this instance -- the loop then becomes an ``enter / merge / loop_cond / switch / exit / next_iteration`` frame in the
+        graph (``ControlFlow.java:505``), which serialises and runs on the frame-aware executor -- or plain callables over
+        torch tensors ``(*tensors) -> tensor(s)``, which run eagerly inside one opaque ``while_loop`` node."""
         import inspect
         loop_vars = list(next(x for x in a if isinstance(x, (list, tuple)) and x and isinstance(x[0], SDVariable)))
         fns = [f for f in a if callable(f)]
@@ -556,28 +557,9 @@ class SameDiff:
             sub = (self, cond_fn, body_fn, len(loop_vars))
             outs = self._op("while_loop", loop_vars, n_out=len(loop_vars), body=sub)
             return outs if isinstance(outs, list) else [outs]
-        loop_name = next((x for x in a if isinstance(x, str)), None) or self._unique("while")
-        phs = [self._add_var(self._unique(f"{loop_name}/in{i}"), VariableType.ARRAY, v.dataType(), v.getShape())
-               for i, v in enumerate(loop_vars)]
-        mark = len(self.ops)
-        c = cond_fn(self, phs)
-        cond_ops = self.ops[mark:]
-        del self.ops[mark:]
-        r = body_fn(self, phs)
-        r = list(r) if isinstance(r, (list, tuple)) else [r]
-        body_ops = self.ops[mark:]
-        del self.ops[mark:]
-        if len(r) != len(loop_vars):
-            raise ValueError(f"loop body returned {len(r)} variables for {len(loop_vars)} loop variables")
-        produced = {o for op in cond_ops + body_ops for o in op.outputs} | {p.name for p in phs}
-        extra = []
-        for op in cond_ops + body_ops:
-            for i in op.inputs:
-                if i is not None and i not in produced and i not in extra and self.variables[i].variableType == VariableType.ARRAY:
-                    extra.append(i)
-        sub = ("graph", [p.name for p in phs], c.name, cond_ops, [v.name for v in r], body_ops, extra)
-        outs = self._op("while_loop", loop_vars + [self.variables[e] for e in extra], n_out=len(loop_vars), body=sub)
-        return outs if isinstance(outs, list) else [outs]
+        from .controlflow import build_while
+        loop_name = next((x for x in a if isinstance(x, str)), None)
+        return build_while(self, loop_vars, cond_fn, body_fn, name=loop_name)
 
     # ------------------------------------------------------------------ loss / training config
     def setLossVariables(self, *names):

@@ -73,6 +73,18 @@ class InferenceSession:
         key = (tuple(outputs), bool(training))
         if sd._exec_plan is None:
             sd._exec_plan = {}
+        logic = sd._exec_plan.get("__logic__")
+        if logic is None:
+            from .controlflow import has_logic_ops
+            logic = sd._exec_plan["__logic__"] = has_logic_ops(sd)
+        if logic:
+            # graphs with enter / exit / switch / merge / next_iteration nodes have cycles: the frame-aware executor runs them
+            from .controlflow import DataflowExecutor
+            vals = DataflowExecutor(sd, training).run(placeholders, values)
+            for o in outputs:
+                if o not in vals:
+                    raise ValueError(f"requested output '{o}' was not produced (its branch was not taken, or an input is missing)")
+            return vals
         plan = sd._exec_plan.get(key)
         if plan is None:
             plan = _build_plan(sd, outputs)
