@@ -189,8 +189,21 @@ def _pick_block_n(M, N, splits=1):
     return best
 
 
+_PAIR_MODE = os.environ.get("DL4J_GEMM_PAIR", "0")     # 0 | 1: 256x256 tiles on CTA pairs (cta_group::2) for large problems
+
+
+def _use_pair(M, N, K, splits):
+    """Whether a GEMM runs on CTA pairs (``csrc/gemm_pair_tcgen05.cu``).  Off unless requested: measured on the BERT-base shapes
+    the pair kernel ties the single-CTA kernel (30 / 75 / 71 / 58 us against 30 / 71 / 71 / 54 us for out / ffn1 / ffn2 / qkv) and
+    loses on 8192^3 (1058 against 790 us): the kernels are bound by the depth of the shared-memory ring over the load latency,
+    not by the shared-memory bandwidth a pair saves, and the pair's "stage landed" hand-off between the CTAs adds to that latency."""
+    if _PAIR_MODE != "1":
+        return False
+    return M >= 2048 and N >= 512 and ((M + 255) // 256) * ((N + 255) // 256) * max(splits, 1) >= 74
+
+
 def gemm_raw(a, b, out=None, bias=None, act=0, aux=None, residual=None, out_dtype=None, atomic=False, splits=1,
-             alpha=1.0, block_n=None):
+             alpha=1.0, block_n=None, pair=None):
     """out[M,N] = act(alpha * a @ b + bias) + residual with a logical [M,K], b logical [K,N]."""
     l = require()
     oa, ob = _operand_a(a), _operand_b(b)
@@ -216,6 +229,21 @@ def gemm_raw(a, b, out=None, bias=None, act=0, aux=None, residual=None, out_dtyp
         bias = bias.to(a.dtype)
     if bias is not None and not bias.is_contiguous():
         bias = bias.contiguous()
+    if pair is None:
+        pair = block_n is None and _use_pair(M, N, K, splits)
+    if pair:
+        if not getattr(l, "_pair_typed", False):
+            vp, i32, lng, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+            l.dl4j_gemm_pair.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, lng, lng, lng, lng, lng, i32, i32, i32, i32, i32, i32,
+                                         i32, i32, f32, i32, vp]
+            l.dl4j_gemm_pair.restype = i32
+            l._pair_typed = True
+        rc = l.dl4j_gemm_pair(_ptr(oa[0]), _ptr(ob[0]), _ptr(out), _ptr(aux), _ptr(bias), _ptr(residual), M, N, K, oa[2], ob[2],
+                              out.stride(0), 0 if aux is None else aux.stride(0), 0 if residual is None else residual.stride(0),
+                              oa[1], ob[1], _DT[a.dtype], bias_fp32, out_fp32, int(act), 1 if atomic else 0, splits, float(alpha),
+                              num_sms(), _stream())
+        _check(rc, "dl4j_gemm_pair")
+        return out
     rc = l.dl4j_gemm(_ptr(oa[0]), _ptr(ob[0]), _ptr(out), _ptr(aux), _ptr(bias), _ptr(residual), M, N, K, oa[2], ob[2],
                      out.stride(0), 0 if aux is None else aux.stride(0), 0 if residual is None else residual.stride(0),
                      oa[1], ob[1], _DT[a.dtype], bias_fp32, out_fp32, int(act), 1 if atomic else 0, splits, float(alpha),

@@ -17,7 +17,11 @@ def nat():
 
 
 def _rel(a, b):
-    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+    """Worst element-wise error in units of (|reference element| + rms of the reference): ``_rel(a, b) < t`` is
+    ``allclose(a, b, rtol=t, atol=t * rms(b))`` -- a region of small values that is wrong fails, which a max-norm ratio would hide."""
+    a, b = a.detach().float(), b.detach().float()
+    rms = float(b.pow(2).mean().sqrt()) + 1e-12
+    return float(((a - b).abs() / (b.abs() + rms)).max())
 
 
 def _ref(x, res, gamma, beta, eps, relu):

@@ -16,7 +16,11 @@ def nat():
 
 
 def _rel(a, b):
-    return float((a.detach().float() - b.detach().float()).abs().max() / (b.detach().float().abs().max() + 1e-6))
+    """Worst element-wise error in units of (|reference element| + rms of the reference): ``_rel(a, b) < t`` is
+    ``allclose(a, b, rtol=t, atol=t * rms(b))`` -- a region of small values that is wrong fails, which a max-norm ratio would hide."""
+    a, b = a.detach().float(), b.detach().float()
+    rms = float(b.pow(2).mean().sqrt()) + 1e-12
+    return float(((a - b).abs() / (b.abs() + rms)).max())
 
 
 @pytest.mark.parametrize("shape,cout,stride", [((4, 64, 14, 14), 256, (1, 1)), ((2, 256, 9, 7), 64, (1, 1)), ((3, 128, 14, 14), 512, (2, 2))])

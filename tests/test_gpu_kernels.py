@@ -17,7 +17,11 @@ def nat():
 
 
 def _rel(a, b):
-    return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+    """Worst element-wise error in units of (|reference element| + rms of the reference): ``_rel(a, b) < t`` is
+    ``allclose(a, b, rtol=t, atol=t * rms(b))`` -- a region of small values that is wrong fails, which a max-norm ratio would hide."""
+    a, b = a.detach().float(), b.detach().float()
+    rms = float(b.pow(2).mean().sqrt()) + 1e-12
+    return float(((a - b).abs() / (b.abs() + rms)).max())
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
@@ -385,3 +389,26 @@ def test_layer_norm_with_fused_residual(nat, dtype):
     assert _rel(y, yr) < tol
     assert _rel(x.grad, xr.grad) < tol and _rel(res.grad, rr.grad) < tol
     assert _rel(g.grad, gr.grad) < tol and _rel(b.grad, br.grad) < tol
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (300, 200, 72), (1024, 768, 768), (257, 768, 520)])
+def test_gemm_on_cta_pairs_matches_fp32(nat, M, N, K):
+    """cta_group::2 GEMM (256 x 256 tile per SM pair): forward, MN-major dgrad, split-K wgrad with TMA reduce-add and the
+    bias-by-MMA + ReLU epilogue against fp32 matmul, including row / column tails and a K tail."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    W = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    dY = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g).bfloat16()
+    ref = A.float() @ W.float().t()
+    tol = dict(rtol=2e-2, atol=2e-2 * float(ref.abs().mean()))
+    torch.testing.assert_close(nat.gemm_raw(A, W.t(), pair=True).float(), ref, **tol)
+    torch.testing.assert_close(nat.gemm_raw(A, W.t(), bias=b, act=1, pair=True).float(), torch.relu(ref + b.float()), **tol)
+    rd = dY.float() @ W.float()
+    torch.testing.assert_close(nat.gemm_raw(dY, W, pair=True).float(), rd, rtol=2e-2, atol=2e-2 * float(rd.abs().mean()))
+    out32 = torch.full((N, K), 0.25, device="cuda")
+    nat.gemm_raw(dY.t(), A, out=out32, atomic=True, splits=2, pair=True)
+    rw = dY.float().t() @ A.float() + 0.25
+    torch.testing.assert_close(out32, rw, rtol=1e-3, atol=1e-3 * float(rw.abs().mean()))
+    torch.cuda.synchronize()
+    nat.check_status()
