@@ -627,44 +627,54 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
       const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
       const bool vec = ((ch.offset & 15) == 0);
       const int nvec = vec ? ch.count / 4 : 0;
-      // a float4 per thread: four neighbouring lanes read the same word of every bitmap peer and take one nibble each
-      for (int vb = (threadIdx.x & ~31); vb < nvec; vb += COMM_THREADS) {
-        const int v = vb + lane;
-        const bool valid = v < nvec;
-        const long long i = ch.offset + 4LL * (valid ? v : 0);
-        const long long w = i >> 4;
-        const int sh = (int)(i & 15);
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-        int any = 0;
+      // A warp covers 128 consecutive float4 (32 message words) per iteration: lane L fetches word L of every bitmap peer -- one
+      // full 128-byte request per peer, which is what keeps the NVLink loads efficient at eight ranks -- and the float4 with
+      // index 32 j + L takes its nibble from the word held by lane 8 j + L / 4.
+      const int n_iter = (nvec + 127) / 128;
+      for (int itw = (threadIdx.x >> 5); itw < n_iter; itw += COMM_THREADS / 32) {
+        const int v_base = itw * 128;
+        const long long w_base = (ch.offset >> 4) + (v_base >> 2);
+        int wr[MAX_RANKS];
 #pragma unroll
         for (int r = 0; r < MAX_RANKS; ++r) {
-          if (r < c.world && peer_form[r] == 1) {
-            // one lane of four fetches the word (a word crosses the link once), the others get it by shuffle
-            int wr = 0;
-            if ((lane & 3) == 0 && valid) wr = ld_peer_i(c.msg[r] + (long long)msg_parity * msg_stride_ints + thr_payload(peer_segs[r]) + w);
-            wr = __shfl_sync(0xffffffffu, wr, lane & ~3);
-            const int mag = (wr >> sh) & 15, sgn = (wr >> (16 + sh)) & 15;
-            any |= mag | sgn;
+          wr[r] = 0;
+          if (r < c.world && peer_form[r] == 1 && v_base + 4 * lane < nvec)
+            wr[r] = ld_peer_i(c.msg[r] + (long long)msg_parity * msg_stride_ints + thr_payload(peer_segs[r]) + w_base + lane);
+        }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const bool bit = mag & (1 << j), sign = sgn & (1 << j);
-              if (bit) d[j] += sign ? -tau : tau;
-              else if (sign) d[j] -= half;
+        for (int j = 0; j < 4; ++j) {
+          const int v = v_base + 32 * j + lane;
+          const int src = 8 * j + (lane >> 2), sh = 4 * (lane & 3);
+          float d[4] = {0.f, 0.f, 0.f, 0.f};
+          int any = 0;
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r) {
+            if (r < c.world && peer_form[r] == 1) {          // uniform: the shuffle is executed by the whole warp
+              const int w = __shfl_sync(0xffffffffu, wr[r], src);
+              const int mag = (w >> sh) & 15, sgn = (w >> (16 + sh)) & 15;
+              any |= mag | sgn;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const bool bit = mag & (1 << e), sign = sgn & (1 << e);
+                if (bit) d[e] += sign ? -tau : tau;
+                else if (sign) d[e] -= half;
+              }
             }
           }
-        }
-        if (!any || !valid) continue;
-        float4* pp = reinterpret_cast<float4*>(params + i);
-        float4 pv = *pp;
-        pv.x -= d[0]; pv.y -= d[1]; pv.z -= d[2]; pv.w -= d[3];
-        *pp = pv;
-        if (shadow) {
-          __nv_bfloat16* sp = shadow + sh0 + 4LL * v;
-          if ((reinterpret_cast<uintptr_t>(sp) & 7) == 0) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(pv.x, pv.y), hi = __floats2bfloat162_rn(pv.z, pv.w);
-            *reinterpret_cast<uint2*>(sp) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-          } else {
-            sp[0] = __float2bfloat16(pv.x); sp[1] = __float2bfloat16(pv.y); sp[2] = __float2bfloat16(pv.z); sp[3] = __float2bfloat16(pv.w);
+          if (!any || v >= nvec) continue;
+          const long long i = ch.offset + 4LL * v;
+          float4* pp = reinterpret_cast<float4*>(params + i);
+          float4 pv = *pp;
+          pv.x -= d[0]; pv.y -= d[1]; pv.z -= d[2]; pv.w -= d[3];
+          *pp = pv;
+          if (shadow) {
+            __nv_bfloat16* sp = shadow + sh0 + 4LL * v;
+            if ((reinterpret_cast<uintptr_t>(sp) & 7) == 0) {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(pv.x, pv.y), hi = __floats2bfloat162_rn(pv.z, pv.w);
+              *reinterpret_cast<uint2*>(sp) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+              sp[0] = __float2bfloat16(pv.x); sp[1] = __float2bfloat16(pv.y); sp[2] = __float2bfloat16(pv.z); sp[3] = __float2bfloat16(pv.w);
+            }
           }
         }
       }
@@ -687,11 +697,13 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
     }
   }
   if (!any_list) return;                       // uniform over the grid: every CTA read the same headers
-  // ---- phase 2b: index-list messages (after the bitmap pass: both write the parameters)
-  ok = grid_barrier(scratch, gridDim.x * (++bar), status);
-  if (!ok) return;
+  // ---- phase 2b: index-list messages, after the bitmap pass (both write the parameters).  One peer at a time in rank order with a
+  // grid barrier in between: within one message an index occurs once, so plain read-modify-writes do, and every rank adds the
+  // same terms in the same order -- the replicas stay bit-identical (atomics would add them in arrival order).
   for (int r = 0; r < c.world; ++r) {
-    if (peer_form[r] != 0) continue;
+    if (peer_form[r] != 0) continue;                 // uniform: every CTA read the same headers
+    ok = grid_barrier(scratch, gridDim.x * (++bar), status);
+    if (!ok) return;
     const int* pm = c.msg[r] + (long long)msg_parity * msg_stride_ints;
     const int* pl = pm + thr_payload(peer_segs[r]);
     for (int sgm = blockIdx.x; sgm < min(peer_segs[r], n_chunks); sgm += gridDim.x) {
@@ -700,7 +712,7 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
       for (int e = threadIdx.x; e < cnt; e += COMM_THREADS) {
         const int code = ld_peer_i(pl + seg0 + e);
         const long long idx = (code < 0 ? -code : code) - 1;
-        if (idx >= 0 && idx < n_total) atomicAdd(params + idx, code < 0 ? tau : -tau);
+        if (idx >= 0 && idx < n_total) params[idx] += code < 0 ? tau : -tau;
       }
     }
   }
