@@ -37,7 +37,7 @@ def _conv2d(i, t, b, extra):
     if len(i) > 9:
         kw["dataFormat"] = int(i[9])            # 0 NCHW, 1 NHWC
     if len(i) > 10:
-        kw["weightsFormat"] = int(i[10])        # 0 [kH,kW,iC,oC], 1 [oC,iC,kH,kW], 2 [oC,kH,kW,iC]
+        kw["wFormat"] = int(i[10])        # 0 [kH,kW,iC,oC], 1 [oC,iC,kH,kW], 2 [oC,kH,kW,iC]
     return kw
 
 

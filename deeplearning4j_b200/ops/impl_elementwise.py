@@ -119,7 +119,7 @@ _binary("squaredsubtract", lambda x, y: (x - y) ** 2)
 _binary("maximum", torch.maximum, "max_pairwise")
 _binary("minimum", torch.minimum, "min_pairwise")
 _binary("floormod", lambda x, y: torch.remainder(x, y))
-_binary("mod", lambda x, y: torch.fmod(x, y))
+_binary("mod", lambda x, y: torch.remainder(x, y))      # simdOps::Mod is d1 - floor(d1 / d2) * d2 (ops.h:1708), not C fmod
 _binary("reversemod", lambda x, y: torch.fmod(y, x))
 _binary("floordiv", lambda x, y: torch.floor_divide(x, y))
 _binary("realdiv", lambda x, y: x / y)

@@ -55,7 +55,17 @@ op("rank", differentiable=False)(lambda x, **kw: torch.tensor(x.dim(), dtype=tor
 op("order")(lambda x, order="c", **kw: x.contiguous())
 op("flatten_2d")(lambda x, axis=1, **kw: x.reshape(int(torch.tensor(x.shape[:int(axis)]).prod()) if axis else 1, -1))
 op("broadcast_to")(lambda x, shape, **kw: x.expand(*_ints(shape)))
-op("tile_to_shape")(lambda x, shape=None, **kw: x.expand(*_ints(shape)).clone())
+def _tile_to_shape(x, shape=None, **kw):
+    """``tile_to_shape``: repeat ``x`` along every axis until it has ``shape`` (each target extent a multiple of the source's;
+    libnd4j/include/ops/declarable/generic/shape/tile_to_shape.cpp)."""
+    tgt = _ints(shape)
+    src = [1] * (len(tgt) - x.dim()) + list(x.shape)
+    if any(t % s for t, s in zip(tgt, src)):
+        raise ValueError(f"tile_to_shape: {tuple(x.shape)} does not tile to {tuple(tgt)}")
+    return x.reshape(src).repeat(*[t // s for t, s in zip(tgt, src)])
+
+
+op("tile_to_shape")(_tile_to_shape)
 op("tile_to_shape_bp")(lambda x, g, **kw: g.sum_to_size(x.shape))
 op("evaluate_reduction_shape", differentiable=False)(
     lambda shape, dims, keepDims=False, **kw: torch.tensor(

@@ -37,7 +37,7 @@ def _worker(rank, world, port, out_dir, fail_at):
     from deeplearning4j_b200.parallel.wrapper import ParallelWrapper, TrainingMode
     net = _net()
     ParallelWrapper.Builder(net).workers(world).trainingMode(TrainingMode.AVERAGING).averagingFrequency(1).build()
-    trainer = ElasticTrainer(net, os.path.join(out_dir, "ckpt"), checkpointEvery=4, heartbeatTimeout=3.0)
+    trainer = ElasticTrainer(net, os.path.join(out_dir, "ckpt"), checkpointEvery=4, heartbeatTimeout=30.0)     # the failure is announced, not timed out
     batches = _batches(40, 11 + rank)
     result = {"rank": rank}
 
