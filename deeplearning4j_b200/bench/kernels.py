@@ -169,7 +169,7 @@ def bench_conv(t, small, rows):
     """3x3 stride-1 convolutions of the ResNet-50 stages (forward; forward + dgrad + wgrad through autograd) against cuDNN."""
     import torch.nn.functional as F
     torch.backends.cudnn.benchmark = True
-    shapes = [(64, 64, 55, 64)] if small else [(256, 64, 55, 64), (256, 128, 28, 128), (256, 256, 14, 256), (256, 512, 7, 512)]
+    shapes = [(256, 64, 55, 64)] if small else [(256, 64, 55, 64), (256, 128, 28, 128), (256, 256, 14, 256), (256, 512, 7, 512)]
     for N, C, H, O in shapes:
         x = torch.randn(N, C, H, H, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
         W = (torch.randn(O, C, 3, 3, device="cuda") * 0.05).requires_grad_(True)

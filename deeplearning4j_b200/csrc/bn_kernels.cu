@@ -64,7 +64,8 @@ bn_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ sums, l
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const long long rr = r + (long long)u * step;
-      v[u] = rr < r1 ? __ldg(reinterpret_cast<const uint4*>(base + rr * C)) : make_uint4(0u, 0u, 0u, 0u);
+      v[u] = rr < r1 && DL4J_IN_BOUNDS(rr * C + cv * 8 + 7, rows * (long long)C)
+                 ? __ldg(reinterpret_cast<const uint4*>(base + rr * C)) : make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {

@@ -30,9 +30,26 @@ def _stale(out, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
+DEBUG_LIB = os.path.join(HERE, "libdl4j_b200_dbg.so")
+ASAN_LIB = os.path.join(HERE, "libdl4j_b200_asan.so")
+
+
+def build(verbose: bool = False, force: bool = False, debug_bounds: bool = False, asan: bool = False) -> str:
+    """Default: the optimised library.  ``debug_bounds``: a second library with ``-DDL4J_DEBUG_BOUNDS`` (kernels check the element
+    offsets they wrap in ``DL4J_IN_BOUNDS``, record the first violation and skip the access; relocatable device code so that
+    every translation unit shares one record).  ``asan``: a third library whose *host* code is instrumented with
+    AddressSanitizer + UndefinedBehaviorSanitizer; load it in a process started with ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``."""
     headers = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".cuh", ".h"))]
-    objdir = os.path.join(HERE, "build")
+    global_flags = list(FLAGS)
+    lib, objname = LIB, "build"
+    if debug_bounds:
+        global_flags += ["-DDL4J_DEBUG_BOUNDS", "-rdc=true"]
+        lib, objname = DEBUG_LIB, "build_dbg"
+    elif asan:
+        global_flags = [f for f in global_flags if f != "-O3"] + ["-O1", "-Xcompiler", "-fsanitize=address", "-Xcompiler", "-fsanitize=undefined",
+                                                                   "-Xcompiler", "-fno-omit-frame-pointer"]
+        lib, objname = ASAN_LIB, "build_asan"
+    objdir = os.path.join(HERE, objname)
     os.makedirs(objdir, exist_ok=True)
     jobs = []
     for s in sources():
@@ -43,7 +60,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
     def compile_one(job):
         src, obj = job
-        cmd = [NVCC] + ARCH + FLAGS + ["-c", src, "-o", obj]
+        cmd = [NVCC] + ARCH + global_flags + ["-c", src, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         return src, r
 
@@ -55,14 +72,16 @@ def build(verbose: bool = False, force: bool = False) -> str:
                 if r.returncode != 0:
                     raise RuntimeError(f"nvcc failed for {src}")
     objs = [os.path.join(objdir, s[:-3] + ".o") for s in sources()]
-    if force or jobs or _stale(LIB, objs):
-        cmd = [NVCC] + ARCH + ["-shared", "-o", LIB] + objs + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+    if force or jobs or _stale(lib, objs):
+        cmd = [NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+        if asan:
+            cmd += ["-Xcompiler", "-fsanitize=address", "-Xcompiler", "-fsanitize=undefined"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, debug_bounds="--debug-bounds" in sys.argv, asan="--asan" in sys.argv))

@@ -22,6 +22,28 @@ enum : int {
   DL4J_ERR_BAD_ARG = 6,
 };
 
+// Debug-build bounds checks (-DDL4J_DEBUG_BOUNDS, built as a second library by `build.py --debug-bounds`): a kernel wraps an
+// element offset it is about to touch in DL4J_IN_BOUNDS(offset, extent).  Out of range, the first failure records its source line,
+// the offset and the extent in `dl4j_dbg_bounds`, the access is skipped and the kernel carries on; nothing traps.  In the normal
+// build the macro is the constant `true` and costs nothing.
+#ifdef DL4J_DEBUG_BOUNDS
+extern __device__ unsigned long long dl4j_dbg_bounds[4];      // [0] failures, [1] line, [2] offset, [3] extent of the first one
+namespace dl4j {
+__device__ __forceinline__ bool bounds_ok(long long i, long long n, int line) {
+  if (i >= 0 && i < n) return true;
+  if (atomicAdd(&dl4j_dbg_bounds[0], 1ULL) == 0ULL) {
+    dl4j_dbg_bounds[1] = (unsigned long long)line;
+    dl4j_dbg_bounds[2] = (unsigned long long)i;
+    dl4j_dbg_bounds[3] = (unsigned long long)n;
+  }
+  return false;
+}
+}  // namespace dl4j
+#define DL4J_IN_BOUNDS(i, n) dl4j::bounds_ok((long long)(i), (long long)(n), __LINE__)
+#else
+#define DL4J_IN_BOUNDS(i, n) true
+#endif
+
 namespace dl4j {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -96,7 +96,7 @@ layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const 
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int vi = lane + i * 32;
-      if (vi < nvec) {
+      if (vi < nvec && DL4J_IN_BOUNDS((long long)r * C + vi * 8 + 7, (long long)rows * C)) {
         qx[i] = ld_raw8(x + (long long)r * C + vi * 8);
         if (res) qr[i] = ld_raw8(res + (long long)r * C + vi * 8);
       }
@@ -428,6 +428,7 @@ softmax_xent_kernel(const T* __restrict__ logits, const T* __restrict__ dense_la
     slz = block_reduce(slz, sh, false);
   } else {
     tgt = idx_labels[row];
+    if (tgt != ignore_index) (void)DL4J_IN_BOUNDS(tgt, C);          // debug build: a label outside [0, C) is recorded, then ignored
     if (tgt == ignore_index || tgt < 0 || tgt >= C) { tgt = -1; sl = 0.f; slz = 0.f; }
     else { sl = 1.f; slz = ldf(z + tgt); }
   }
@@ -485,6 +486,7 @@ softmax_xent_fwd_kernel(const T* __restrict__ logits, const T* __restrict__ dens
     slz = block_reduce(slz, sh, false);
   } else {
     const long long tgt = idx_labels[row];
+    if (tgt != ignore_index) (void)DL4J_IN_BOUNDS(tgt, C);
     if (tgt == ignore_index || tgt < 0 || tgt >= C) { sl = 0.f; slz = 0.f; }
     else { sl = 1.f; slz = ldf(z + tgt); }
   }

@@ -48,7 +48,9 @@ maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
         const int iw = iw0 + kw;
         if (iw < 0 || iw >= s.W) continue;
         float v[8];
-        pl_unpack8(__ldg(reinterpret_cast<const uint4*>(x + (((long long)n * s.H + ih) * s.W + iw) * s.C) + cv), v);
+        const long long xo = (((long long)n * s.H + ih) * s.W + iw) * cv_n + cv;      // in 16-byte groups
+        if (!DL4J_IN_BOUNDS(xo, (long long)s.N * s.H * s.W * cv_n)) continue;
+        pl_unpack8(__ldg(reinterpret_cast<const uint4*>(x) + xo), v);
         const unsigned char pos = (unsigned char)(kh * s.kW + kw);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -90,6 +92,7 @@ maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const unsigned char* __
         const int kw = wp - ow * s.sW;
         const unsigned pos = (unsigned)(kh * s.kW + kw);
         const long long o = (((long long)n * s.OH + oh) * s.OW + ow) * cv_n + cv;
+        if (!DL4J_IN_BOUNDS(o, (long long)s.N * s.OH * s.OW * cv_n)) continue;
         const uint2 p = __ldg(reinterpret_cast<const uint2*>(idx) + o);
         float d[8];
         pl_unpack8(__ldg(reinterpret_cast<const uint4*>(dy) + o), d);
@@ -116,8 +119,9 @@ subsample_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restr
     const int ow = (int)(t % s.OW); t /= s.OW;
     const int oh = (int)(t % s.OH);
     const int n = (int)(t / s.OH);
-    reinterpret_cast<uint4*>(y)[g] =
-        __ldg(reinterpret_cast<const uint4*>(x + (((long long)n * s.H + (long long)oh * s.sH) * s.W + (long long)ow * s.sW) * s.C) + cv);
+    const long long xo = (((long long)n * s.H + (long long)oh * s.sH) * s.W + (long long)ow * s.sW) * cv_n + cv;
+    if (!DL4J_IN_BOUNDS(xo, (long long)s.N * s.H * s.W * cv_n)) continue;
+    reinterpret_cast<uint4*>(y)[g] = __ldg(reinterpret_cast<const uint4*>(x) + xo);
   }
 }
 
@@ -134,7 +138,8 @@ subsample_bwd_kernel(const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __rest
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (ih % s.sH == 0 && iw % s.sW == 0) {
       const int oh = ih / s.sH, ow = iw / s.sW;
-      if (oh < s.OH && ow < s.OW) v = __ldg(reinterpret_cast<const uint4*>(dy) + ((((long long)n * s.OH + oh) * s.OW + ow) * cv_n + cv));
+      const long long yo = (((long long)n * s.OH + oh) * s.OW + ow) * cv_n + cv;
+      if (oh < s.OH && ow < s.OW && DL4J_IN_BOUNDS(yo, (long long)s.N * s.OH * s.OW * cv_n)) v = __ldg(reinterpret_cast<const uint4*>(dy) + yo);
     }
     reinterpret_cast<uint4*>(dx)[g] = v;
   }

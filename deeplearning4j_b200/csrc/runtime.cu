@@ -69,6 +69,26 @@ DL4J_API int dl4j_num_sms() {
 
 DL4J_API int dl4j_abi_version() { return 1; }
 
+#ifdef DL4J_DEBUG_BOUNDS
+__device__ unsigned long long dl4j_dbg_bounds[4] = {0ULL, 0ULL, 0ULL, 0ULL};
+#endif
+
+// Debug-bounds build only: copies {failures, source line, offset, extent of the first failure} into out[4] (synchronises) and
+// clears the record when `reset` is set.  Returns 0, or -1 in a build without the checks.
+DL4J_API int dl4j_debug_bounds(unsigned long long* out, int reset) {
+#ifdef DL4J_DEBUG_BOUNDS
+  if (cudaMemcpyFromSymbol(out, dl4j_dbg_bounds, 4 * sizeof(unsigned long long)) != cudaSuccess) return -2;
+  if (reset && out[0] != 0ULL) {
+    const unsigned long long z[4] = {0ULL, 0ULL, 0ULL, 0ULL};
+    if (cudaMemcpyToSymbol(dl4j_dbg_bounds, z, sizeof(z)) != cudaSuccess) return -2;
+  }
+  return 0;
+#else
+  (void)out; (void)reset;
+  return -1;
+#endif
+}
+
 // Binds `device`'s primary context to the calling thread for this library's runtime instance.  The
 // library is linked against its own (static) CUDA runtime; a thread that has only used another runtime
 // instance so far (e.g. an autograd worker thread) may have no context bound yet, and driver entry

@@ -19,7 +19,11 @@ import torch
 _LIB = None
 _LIB_ERR = None
 _LOCK = threading.Lock()
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc", "libdl4j_b200.so")
+# DL4J_DEBUG_BOUNDS=1 loads the build whose kernels check their element offsets (``csrc/build.py --debug-bounds``), DL4J_ASAN=1 the
+# build whose host code runs under AddressSanitizer / UBSan (``--asan``; the process needs libasan preloaded).
+_LIB_FLAVOUR = "dbg" if os.environ.get("DL4J_DEBUG_BOUNDS", "0") == "1" else "asan" if os.environ.get("DL4J_ASAN", "0") == "1" else ""
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc",
+                         "libdl4j_b200" + ("_" + _LIB_FLAVOUR if _LIB_FLAVOUR else "") + ".so")
 
 LAUNCHES = 0     # number of native kernel launches issued by this process (bench.py reports it)
 
@@ -133,10 +137,30 @@ def check_status(reset=True):
     if l is None:
         return 0
     v = l.dl4j_read_status(1 if reset else 0)
+    if _LIB_FLAVOUR == "dbg":
+        rec = debug_bounds(reset)
+        if rec["failures"]:
+            raise RuntimeError(f"debug bounds check failed {rec['failures']} time(s); first: source line {rec['line']}, "
+                               f"offset {rec['offset']}, extent {rec['extent']}")
     if v != 0:
         names = {1: "TMA producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "peer wait", 5: "index out of bounds"}
         raise RuntimeError(f"device-side bounded wait/ check failed: {names.get(v, v)}")
     return v
+
+
+def debug_bounds(reset=True):
+    """The debug-bounds build's record: number of out-of-range offsets the kernels skipped since the last reset, and the source
+    line, offset and extent of the first (synchronises).  ``None`` in the normal build."""
+    l = require()
+    if l is None:
+        return None
+    out = (ctypes.c_ulonglong * 4)()
+    l.dl4j_debug_bounds.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    l.dl4j_debug_bounds.restype = ctypes.c_int
+    if l.dl4j_debug_bounds(out, 1 if reset else 0) != 0:
+        return None
+    off = out[2] - (1 << 64) if out[2] >= (1 << 63) else out[2]
+    return {"failures": int(out[0]), "line": int(out[1]), "offset": int(off), "extent": int(out[3])}
 
 
 _DT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}

@@ -21,8 +21,8 @@ _LIB = None
 def _lib():
     global _LIB
     if _LIB is None:
-        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc", "libdl4j_b200.so")
-        lib = ctypes.CDLL(os.path.abspath(path))
+        from ..ops import native          # the same file the kernels come from (normal, debug-bounds or sanitizer build)
+        lib = ctypes.CDLL(os.path.abspath(native._LIB_PATH))
         lib.dl4j_launch_dims.argtypes = [ctypes.c_char_p, ctypes.c_void_p]
         lib.dl4j_launch_dims.restype = ctypes.c_int
         lib.dl4j_launch_dims_name.argtypes = [ctypes.c_int]
