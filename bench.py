@@ -89,6 +89,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="layer-count override (debug only; invalidates the number)")
     ap.add_argument("--library-baseline", action="store_true", help="route ops through torch/cuBLAS + NCCL (baseline B1)")
     ap.add_argument("--mode", default="fused", help="gradient exchange for N>1: fused | nccl")
+    ap.add_argument("--no-library-graphs", action="store_true", help="library baseline without CUDA-graph replay (eager launches)")
     ap.add_argument("--no-secondary", action="store_true", help="default run: BERT only (skip ResNet-50 and gradshare)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -125,8 +125,10 @@ class BertRunner(BaseRunner):
         sd.to(self.device)
         self.sd = sd
         import os
-        if not a.library_baseline and os.environ.get("DL4J_CUDA_GRAPHS", "1") != "0":
-            sd.getTrainingConfig().cudaGraphs = True        # forward + backward replay from a captured CUDA graph
+        if os.environ.get("DL4J_CUDA_GRAPHS", "1") != "0" and not (a.library_baseline and a.no_library_graphs):
+            # forward + backward replay from a captured CUDA graph; the library baseline gets the same treatment so that the
+            # comparison isolates the kernels from the launch overhead
+            sd.getTrainingConfig().cudaGraphs = True
         g = torch.Generator().manual_seed(1234 + self.rank)
         n_tok = self.batch * self.seq
         self.n_masked = int(n_tok * 0.15) // 8 * 8

@@ -21,9 +21,10 @@ class _NetRunner(BaseRunner):
             attach_gradient_sharing(net, self.sharing_mode, impl, FixedThresholdAlgorithm(1e-3))
 
     def _graphs(self, net):
-        """Launch-bound networks replay their forward + backward pass from a CUDA graph (off for the library baseline)."""
+        """Launch-bound networks replay their forward + backward pass from a CUDA graph (the library baseline too, unless
+        ``--no-library-graphs``)."""
         import os
-        if not self.args.library_baseline and os.environ.get("DL4J_CUDA_GRAPHS", "1") != "0":
+        if os.environ.get("DL4J_CUDA_GRAPHS", "1") != "0" and not (self.args.library_baseline and self.args.no_library_graphs):
             net.setCudaGraphs(True)
 
     def device_step(self):

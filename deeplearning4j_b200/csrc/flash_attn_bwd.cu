@@ -29,8 +29,12 @@ struct FlashBwdParams {
   int B, H, Tq, Tk;
   float scale;
   int* status;
+  const unsigned long long* seed;   // dropout seed of the forward pass (device memory), read when drop_thr != 0
+  uint32_t drop_thr;
+  float inv_keep;
 };
 
+template <bool DROP>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -174,6 +178,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int j = 0; j < 32; ++j) mbits |= (mask_s[cq * 32 + j] != 0.f ? 1u : 0u) << j;
     const bool all_keys = mbits == 0xffffffffu;
     const float sc = p.scale;
+    constexpr bool drop = DROP;
+    uint32_t seed_lo = 0u, seed_hi = 0u;
+    if (drop) { const unsigned long long sd = *p.seed; seed_lo = (uint32_t)sd; seed_hi = (uint32_t)(sd >> 32); }
+    const uint32_t bh = (uint32_t)(b * p.H + h);
     bool ok = true;
     const long rbase = ((long)b * p.H + h) * p.Tq;
     // per-row log-sum-exp and D of the next query block are fetched one block ahead (+inf: exp2(-inf) = 0 past the end)
@@ -218,7 +226,18 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tmem_ld_32x32(taddr + T_DP + cq * 32, dpv);
         tmem_ld_wait();
         float pe[32], de[32];
-        if (all_keys) {
+        if constexpr (DROP) {
+          // the forward's mask, regenerated: dV takes the dropped weights, dS = P * (mask / keep * dP - D) * scale
+          const uint32_t kw = fa_keep32(seed_lo, seed_hi, bh, (uint32_t)tq, (uint32_t)(k0 + cq * 32), p.drop_thr);
+          const float ik = p.inv_keep;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float pv = ((mbits >> j) & 1u) ? fa_exp2(fmaf(__uint_as_float(sv[j]), k2, -lse2)) : 0.f;
+            const float mk = ((kw >> j) & 1u) ? ik : 0.f;
+            pe[j] = pv * mk;
+            de[j] = pv * fmaf(__uint_as_float(dpv[j]) * mk, sc, -dvs);
+          }
+        } else if (all_keys) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float pv = fa_exp2(fmaf(__uint_as_float(sv[j]), k2, -lse2));
@@ -279,8 +298,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 // zeroed by the caller; dk, dv bf16 addressed as base + b * o_bs + key * o_ts + head * 64.  Limits: Tk a multiple of 128.
 DL4J_API int dl4j_flash_attn_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* dvec,
                                  const float* key_mask, float* dq, void* dk, void* dv, int B, int H, int Tq, int Tk, const long* q_strides,
-                                 const long* k_strides, const long* v_strides, const long* do_strides, long o_bs, long o_ts, float scale, void* stream_) {
+                                 const long* k_strides, const long* v_strides, const long* do_strides, long o_bs, long o_ts, float scale,
+                                 float dropout_p, const void* seed, void* stream_) {
   if (B < 1 || H < 1 || Tq < 1 || Tk < FB_BLK || Tk % FB_BLK) return -DL4J_ERR_BAD_ARG;
+  if (dropout_p < 0.f || dropout_p >= 1.f || (dropout_p > 0.f && !seed)) return -DL4J_ERR_BAD_ARG;
   CUtensorMap tq, tk, tv, tdo;
   int r = fa_encode(&tq, q, B, H, Tq, q_strides[0], q_strides[1], q_strides[2], FB_BLK);
   if (r) return -1000 - r;
@@ -301,10 +322,14 @@ DL4J_API int dl4j_flash_attn_bwd(const void* q, const void* k, const void* v, co
   p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
   p.scale = scale;
   p.status = dl4j_status_word(dev);
+  p.seed = reinterpret_cast<const unsigned long long*>(seed);
+  p.drop_thr = dropout_p > 0.f ? (uint32_t)(dropout_p * 65536.f + 0.5f) : 0u;
+  p.inv_keep = p.drop_thr ? 65536.f / (65536.f - (float)p.drop_thr) : 1.f;
   const size_t smem = 6 * FB_TILE + 2 * FB_PS + FB_BLK * sizeof(float) + 256 + 1024;
-  cudaError_t e = cudaFuncSetAttribute(flash_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kern = p.drop_thr ? flash_attn_bwd_kernel<true> : flash_attn_bwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  flash_attn_bwd_kernel<<<B * H * (Tk / FB_BLK), FB_THREADS, smem, (cudaStream_t)stream_>>>(tq, tk, tv, tdo, p);
+  kern<<<B * H * (Tk / FB_BLK), FB_THREADS, smem, (cudaStream_t)stream_>>>(tq, tk, tv, tdo, p);
   return (int)cudaGetLastError();
 }
 

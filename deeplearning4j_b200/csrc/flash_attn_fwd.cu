@@ -26,8 +26,12 @@ struct FlashFwdParams {
   int B, H, Tq, Tk;
   float scale;
   int* status;
+  const unsigned long long* seed;   // device-resident dropout seed (read when drop_thr != 0)
+  uint32_t drop_thr;                // round(p * 65536); 0 = no dropout
+  float inv_keep;                   // 1 / (1 - p)
 };
 
+template <bool DROP>
 __global__ void __launch_bounds__(FF_THREADS, 2)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const FlashFwdParams p) {
@@ -134,6 +138,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int t = threadIdx.x - 64;                 // 0..255
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float k2 = p.scale * FA_LOG2E;
+    constexpr bool drop = DROP;
+    uint32_t seed_lo = 0u, seed_hi = 0u;
+    if (drop) { const unsigned long long sd = *p.seed; seed_lo = (uint32_t)sd; seed_hi = (uint32_t)(sd >> 32); }
+    const uint32_t bh = (uint32_t)(b * p.H + h);
     float run_m = -INFINITY, run_l = 0.f;           // running row maximum (raw scores) and this thread's partial row sum
     float o[32];
 #pragma unroll
@@ -225,6 +233,11 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             l += e[i];
           }
         }
+        if constexpr (DROP) {       // the row sum above is the undropped one: O = (P o mask / keep) V / l
+          const uint32_t kw = fa_keep32(seed_lo, seed_hi, bh, (uint32_t)(q0 + r), (uint32_t)(j * FF_BN + ch * 64 + half * 32), p.drop_thr);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) e[i] = ((kw >> i) & 1u) ? e[i] * p.inv_keep : 0.f;
+        }
         fa_store_row(p_s, r, ch * 64 + half * 32, 32, e);
       }
       run_l = fmaf(run_l, alpha, l);
@@ -275,11 +288,13 @@ using namespace dl4j;
 
 // q / k / v: [B, H, T, 64] bf16 views with element strides {sb, sh, st} (head dimension contiguous, strides multiples of 8,
 // base 16-byte aligned).  out [B, Tq, H, 64] bf16 contiguous, lse [B, H, Tq] fp32, key_mask [B, Tk] fp32 or null.
-// Limits: Tk a multiple of 128.
+// Limits: Tk a multiple of 128.  dropout_p > 0: `seed` points to a 64-bit seed in device memory; pass the same seed and
+// probability to the backward pass.
 DL4J_API int dl4j_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const float* key_mask, int B, int H,
                                  int Tq, int Tk, const long* q_strides, const long* k_strides, const long* v_strides, float scale,
-                                 void* stream_) {
+                                 float dropout_p, const void* seed, void* stream_) {
   if (B < 1 || H < 1 || Tq < 1 || Tk < FF_BN || Tk % FF_BN) return -DL4J_ERR_BAD_ARG;
+  if (dropout_p < 0.f || dropout_p >= 1.f || (dropout_p > 0.f && !seed)) return -DL4J_ERR_BAD_ARG;
   CUtensorMap tq, tk, tv;
   int r = fa_encode(&tq, q, B, H, Tq, q_strides[0], q_strides[1], q_strides[2], FF_BM);
   if (r) return -1000 - r;
@@ -296,10 +311,14 @@ DL4J_API int dl4j_flash_attn_fwd(const void* q, const void* k, const void* v, vo
   p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
   p.scale = scale;
   p.status = dl4j_status_word(dev);
+  p.seed = reinterpret_cast<const unsigned long long*>(seed);
+  p.drop_thr = dropout_p > 0.f ? (uint32_t)(dropout_p * 65536.f + 0.5f) : 0u;
+  p.inv_keep = p.drop_thr ? 65536.f / (65536.f - (float)p.drop_thr) : 1.f;
   const size_t smem = FF_TILE * (1 + FF_SLOTS) + FF_P_BYTES + (2 * FF_BN + 4 * FF_BM + 4) * sizeof(float) + 256 + 1024;
-  cudaError_t e = cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kern = p.drop_thr ? flash_attn_fwd_kernel<true> : flash_attn_fwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int q_blocks = (Tq + FF_BM - 1) / FF_BM;
-  flash_attn_fwd_kernel<<<B * H * q_blocks, FF_THREADS, smem, (cudaStream_t)stream_>>>(tq, tk, tv, p);
+  kern<<<B * H * q_blocks, FF_THREADS, smem, (cudaStream_t)stream_>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }

@@ -29,6 +29,34 @@ __device__ __forceinline__ void fa_store_row(uint8_t* tile, int r, int col0, int
   }
 }
 
+// Dropout on the attention weights (AttentionHelper.cpp applies it to the softmax output): the keep decision of element
+// (batch*head, query row, key column) is a pure function of a 64-bit seed and those three indices, so the backward pass
+// regenerates the forward's mask instead of storing it.  One Philox4x32-7 block yields 8 x 16 bits = the decisions of 8
+// consecutive key columns; an element is dropped when its 16-bit value is below `thr` = round(p * 65536).
+__device__ __forceinline__ uint32_t fa_keep8(uint32_t seed_lo, uint32_t seed_hi, uint32_t bh, uint32_t row, uint32_t col8, uint32_t thr) {
+  uint32_t c0 = col8, c1 = row, c2 = bh, c3 = 0x5eed5eedu, k0 = seed_lo, k1 = seed_hi;
+#pragma unroll
+  for (int r = 0; r < 7; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0; c1 = lo1; c2 = hi0 ^ c3 ^ k1; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  const uint32_t w[4] = {c0, c1, c2, c3};
+  uint32_t keep = 0;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) keep |= (((w[e >> 1] >> (16 * (e & 1))) & 0xffffu) >= thr ? 1u : 0u) << e;
+  return keep;
+}
+
+// keep bits of 32 consecutive key columns starting at col0 (a multiple of 8)
+__device__ __forceinline__ uint32_t fa_keep32(uint32_t seed_lo, uint32_t seed_hi, uint32_t bh, uint32_t row, uint32_t col0, uint32_t thr) {
+  uint32_t k = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) k |= fa_keep8(seed_lo, seed_hi, bh, row, (col0 >> 3) + g, thr) << (8 * g);
+  return k;
+}
+
 }  // namespace dl4j
 
 // Tensor map over a [B, H, T, 64] bf16 view given by its element strides (unit stride along the head dimension)

@@ -256,6 +256,40 @@ class SequenceVectors:
             _scatter_add(lt.syn1Neg, tg.reshape(-1), (g.unsqueeze(-1) * h.unsqueeze(1)).reshape(-1, h.shape[1]))
         return dh
 
+    def _native_tables(self):
+        """Index tables in the form the batch kernel takes (``csrc/nlp_kernels.cu``), or None when the tables are not fp32 CUDA
+        tensors: Huffman points with -1 padding, int8 codes, and a unigram^0.75 sample table of 2^20 entries."""
+        lt = self.lookupTable
+        if not (lt.syn0.is_cuda and lt.syn0.dtype == torch.float32) or getattr(self, "useTorchKernels", False):
+            return None
+        from ..ops import native
+        if not native.available():
+            return None
+        t = getattr(self, "_native_tab", None)
+        if t is None:
+            t = {}
+            if self.useHierarchicSoftmax:
+                codes, points, mask = self._hs
+                t["points"] = torch.where(mask > 0, points, torch.full_like(points, -1)).to(torch.int32)
+                t["codes"] = codes.to(torch.int8)
+            if self.negativeSample > 0:
+                cdf = torch.cumsum(self._neg.double(), 0)
+                u = (torch.arange(1 << 20, device=cdf.device, dtype=torch.float64) + 0.5) / float(1 << 20)
+                t["neg"] = torch.searchsorted(cdf, u).clamp(max=cdf.numel() - 1).to(torch.int32)
+            self._native_tab = t
+        return t
+
+    def _native_step(self, tab, rows_in, center, context, lr, gen):
+        """One kernel launch for a batch: skip-gram (``rows_in`` = input rows of syn0, ``context`` None) or CBOW (``context`` [B, W])."""
+        from ..ops import native
+        lt = self.lookupTable
+        hs, ns = self.useHierarchicSoftmax, self.negativeSample > 0
+        rnd = torch.randint(0, 1 << 62, (center.numel(),), device=center.device, generator=gen)
+        return native.w2v_batch(lt.syn0, lt.syn1 if hs else None, lt.syn1Neg if ns else None, tab.get("neg"), rows_in,
+                                center if ns else None, tab["points"][center] if hs else None, tab["codes"][center] if hs else None,
+                                context, torch.tensor([lr], dtype=torch.float32, device=center.device), rnd,
+                                int(self.negativeSample) if ns else 0, True)
+
     def _pairs(self, ids, sent, gen):
         """(center position, context position) pairs with per-center dynamic windows and subsampling."""
         n = ids.numel()
@@ -284,6 +318,7 @@ class SequenceVectors:
 
     def _train_elements(self, ids, sent, gen, lr_fn, progress):
         lt = self.lookupTable
+        tab = self._native_tables()
         for _ in range(max(self.iterations, 1)):
             ids_k, sent_k, c, x = self._pairs(ids, sent, gen)
             if c.numel() == 0:
@@ -302,6 +337,9 @@ class SequenceVectors:
                 for s in range(0, perm.numel(), self.batchSize):
                     rows = perm[s:s + self.batchSize]
                     cm = ctx[rows]
+                    if tab is not None and self._native_step(tab, ids_k[rows], ids_k[rows], cm, lr_fn(progress[0]), gen):
+                        progress[0] += rows.numel()
+                        continue
                     msk = (cm >= 0).to(lt.syn0.dtype)
                     vecs = lt.syn0[cm.clamp(min=0)] * msk.unsqueeze(-1)
                     cnt = msk.sum(1, keepdim=True).clamp(min=1)
@@ -317,6 +355,9 @@ class SequenceVectors:
                     sel = perm[s:s + self.batchSize]
                     center, context = ids_k[c[sel]], ids_k[x[sel]]
                     # skip-gram as in word2vec.c: the context word's vector is the input, the centre word the target
+                    if tab is not None and self._native_step(tab, context, center, None, lr_fn(progress[0]), gen):
+                        progress[0] += sel.numel() / (2.0 * self.windowSize)
+                        continue
                     h = lt.syn0[context]
                     lr = lr_fn(progress[0])
                     dh = self._output_step(h, center, lr, gen)
@@ -330,6 +371,7 @@ class SequenceVectors:
         gen = torch.Generator(device=self.device).manual_seed(int(self.seed))
         if self.useHierarchicSoftmax:
             self._hs = self._hs_tables()
+            self._native_tab = None
         if self.negativeSample > 0:
             self._neg = self._neg_table()
         total = max(ids.numel() * self.epochs * max(self.iterations, 1), 1)
@@ -493,6 +535,7 @@ class ParagraphVectors(SequenceVectors):
         saved = (None if lt.syn1 is None else lt.syn1.clone(), None if lt.syn1Neg is None else lt.syn1Neg.clone())
         if self.useHierarchicSoftmax and not hasattr(self, "_hs"):
             self._hs = self._hs_tables()
+            self._native_tab = None
         if self.negativeSample > 0 and not hasattr(self, "_neg"):
             self._neg = self._neg_table()
         for it in range(iterations):

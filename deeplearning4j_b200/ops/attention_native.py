@@ -57,21 +57,24 @@ def _typed_softmax(l):
 
 class _AttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, key_mask, scale):
+    def forward(ctx, q, k, v, key_mask, scale, dropout_p=0.0):
         l = native.require()
         _typed_softmax(l)
         q, k, v = _prep(q), _prep(k), _prep(v)
         Bn, H, Tq, D = q.shape
         Tk = k.shape[2]
         dt = q.dtype
-        ctx.flash = USE_FLASH and flash_supported(q, k, v)
+        ctx.flash = (USE_FLASH or dropout_p > 0.0) and flash_supported(q, k, v)
         if ctx.flash:
             # fused kernel: the score matrix stays in tensor memory; only O and the row log-sum-exp are written
-            O, lse = flash_forward(q, k, v, key_mask, scale)
+            seed = _next_dropout_seed(q.device) if dropout_p > 0.0 else None
+            O, lse = flash_forward(q, k, v, key_mask, scale, dropout_p, seed)
             mk = key_mask.to(torch.float32).contiguous() if key_mask is not None else None
-            ctx.save_for_backward(q, k, v, O, lse, mk)
-            ctx.scale = scale
+            ctx.save_for_backward(q, k, v, O, lse, mk, seed)
+            ctx.scale, ctx.dropout_p = scale, float(dropout_p)
             return O.permute(0, 2, 1, 3)
+        if dropout_p > 0.0:
+            raise RuntimeError("attention dropout needs the fused kernels (head size 64, key length a multiple of 128)")
         P = torch.empty((Bn, H, Tq, Tk), dtype=dt, device=q.device)
         # S = scale * Q K^T
         _bgemm(l, q.data_ptr(), k.data_ptr(), P.data_ptr(), Tq, Tk, D, q.stride(2), k.stride(2), Tk, 0, 0, scale, H, Bn,
@@ -131,20 +134,53 @@ class _AttentionFn(torch.autograd.Function):
         cbs, ldc = obs(dk_t)
         _bgemm(l, dP.data_ptr(), q.data_ptr(), dk_t.data_ptr(), Tk, D, Tq, Tk, q.stride(2), ldc, 1, 1, 1.0, H, Bn,
                pbs, (q.stride(1), q.stride(0)), cbs, dt)
-        return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None
+        return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None, None
 
 
-def attention(q, k, v, mask, scale):
-    """q, k, v: [B, H, T, D]; ``mask``: None or a [B, Tk] key mask (non-zero = attend)."""
+def attention(q, k, v, mask, scale, dropout_p=0.0):
+    """q, k, v: [B, H, T, D]; ``mask``: None or a [B, Tk] key mask (non-zero = attend); ``dropout_p``: probability of dropping an
+    attention weight (training).  Returns None when the case is not covered by the native kernels.
+
+    Head sizes below 64 run on the fused head-size-64 kernels with zero-padded heads (Q K^T is unchanged by zero columns, the
+    padded columns of V give output columns that are sliced away), so no score matrix is materialised for them either."""
     if not native.available() or q.dim() != 4 or q.dtype not in (torch.bfloat16, torch.float16):
         return None
     if mask is not None and (mask.dim() != 2 or mask.shape[0] != q.shape[0] or mask.shape[1] != k.shape[2]):
         return None
     D, Tk, Tq = q.shape[3], k.shape[2], q.shape[2]
-    if D % 8 or Tk % 8 or Tq % 8 or Tk > 1024:
-        return None
     scale = float(scale) if scale is not None else D ** -0.5
-    return _AttentionFn.apply(q, k, v, mask, scale)
+    if D < 64 and D % 8 == 0 and q.dtype == torch.bfloat16 and Tk % 128 == 0 and Tk == v.shape[2] and q.shape[:2] == k.shape[:2]:
+        pad = (0, 64 - D)
+        qp, kp, vp = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+        return _AttentionFn.apply(qp, kp, vp, mask, scale, float(dropout_p))[..., :D]
+    fused = flash_supported(q, k, v)
+    if dropout_p > 0.0 and not fused:
+        return None
+    if D % 8 or Tk % 8 or Tq % 8 or (Tk > 1024 and not fused):
+        return None
+    return _AttentionFn.apply(q, k, v, mask, scale, float(dropout_p))
+
+
+# Dropout seeds live on the device: every fused forward call with dropout takes a private copy of the running seed and
+# advances it, both with device-side operations, so a captured CUDA graph draws a new mask at every replay; the backward pass
+# reads the forward's copy.
+_DROPOUT_SEED = {}
+
+
+def set_dropout_seed(seed, device=None):
+    """(Re)starts the attention-dropout seed sequence of ``device`` (default: the current CUDA device)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _DROPOUT_SEED[device] = torch.tensor([int(seed) & 0x7fffffffffffffff], dtype=torch.int64, device=device)
+
+
+def _next_dropout_seed(device):
+    state = _DROPOUT_SEED.get(device)
+    if state is None:
+        set_dropout_seed(torch.initial_seed(), device)
+        state = _DROPOUT_SEED[device]
+    mine = state.clone()
+    state.add_(0x9E3779B97F4A7C15 & 0x3fffffffffffffff)      # any odd stride: consecutive calls never share a Philox key
+    return mine
 
 
 _LONG3 = ctypes.c_long * 3
@@ -157,14 +193,15 @@ def _flash_backward(ctx, dO):
     if not hasattr(l.dl4j_flash_attn_bwd, "_typed"):
         vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         lp = ctypes.POINTER(ctypes.c_long)
-        l.dl4j_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, lp, ctypes.c_long, ctypes.c_long, f32, vp]
+        l.dl4j_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, lp, ctypes.c_long, ctypes.c_long, f32,
+                                          f32, vp, vp]
         l.dl4j_flash_attn_bwd.restype = ctypes.c_int
         l.dl4j_attn_dvec.argtypes = [vp, lp, vp, vp, i32, i32, i32, vp]
         l.dl4j_attn_dvec.restype = ctypes.c_int
         l.dl4j_attn_dq_finish.argtypes = [vp, vp, ctypes.c_long, ctypes.c_long, i32, i32, i32, vp]
         l.dl4j_attn_dq_finish.restype = ctypes.c_int
         l.dl4j_flash_attn_bwd._typed = True
-    q, k, v, O, lse, mk = ctx.saved_tensors
+    q, k, v, O, lse, mk, seed = ctx.saved_tensors
     Bn, H, Tq, D = q.shape
     Tk = k.shape[2]
     dO = _prep(dO)                                           # [B, H, Tq, D] view
@@ -191,25 +228,26 @@ def _flash_backward(ctx, dO):
 
     rc = l.dl4j_flash_attn_bwd(native._ptr(q), native._ptr(k), native._ptr(v), native._ptr(dO), native._ptr(lse), native._ptr(dvec),
                                native._ptr(mk), native._ptr(dq_acc), native._ptr(dk_t), native._ptr(dv_t), Bn, H, Tq, Tk,
-                               st(q), st(k), st(v), st(dO), dk_t.stride(0), dk_t.stride(1), float(ctx.scale), native._stream())
+                               st(q), st(k), st(v), st(dO), dk_t.stride(0), dk_t.stride(1), float(ctx.scale), float(ctx.dropout_p),
+                               native._ptr(seed), native._stream())
     native._check(rc, "dl4j_flash_attn_bwd")
     rc = l.dl4j_attn_dq_finish(native._ptr(dq_acc), native._ptr(dq_t), dq_t.stride(0), dq_t.stride(1), Bn, H, Tq, native._stream())
     native._check(rc, "dl4j_attn_dq_finish")
-    return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None
+    return dq_t.permute(0, 2, 1, 3), dk_t.permute(0, 2, 1, 3), dv_t.permute(0, 2, 1, 3), None, None, None
 
 
 def flash_supported(q, k, v):
-    return (native.available() and q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[3] == 64 and k.shape[2] in (256, 512)
-            and k.shape[2] == v.shape[2] and q.shape[:2] == k.shape[:2])
+    return (native.available() and q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[3] == 64 and k.shape[2] >= 128
+            and k.shape[2] % 128 == 0 and k.shape[2] == v.shape[2] and q.shape[:2] == k.shape[:2] and v.shape[3] == 64)
 
 
-def flash_forward(q, k, v, key_mask, scale):
+def flash_forward(q, k, v, key_mask, scale, dropout_p=0.0, seed=None):
     """Fused attention forward: returns (out [B, Tq, H, 64] bf16, lse [B, H, Tq] fp32).  q, k, v: [B, H, T, 64] views."""
     l = native.require()
     if not hasattr(l.dl4j_flash_attn_fwd, "_typed"):
         vp, i32, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         lp = ctypes.POINTER(ctypes.c_long)
-        l.dl4j_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, f32, vp]
+        l.dl4j_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, lp, lp, lp, f32, f32, vp, vp]
         l.dl4j_flash_attn_fwd.restype = ctypes.c_int
         l.dl4j_flash_attn_fwd._typed = True
     q, k, v = _prep(q), _prep(k), _prep(v)
@@ -222,6 +260,6 @@ def flash_forward(q, k, v, key_mask, scale):
     def st(t):
         return _LONG3(t.stride(0), t.stride(1), t.stride(2))
     rc = l.dl4j_flash_attn_fwd(native._ptr(q), native._ptr(k), native._ptr(v), native._ptr(out), native._ptr(lse), native._ptr(mk),
-                               Bn, H, Tq, Tk, st(q), st(k), st(v), float(scale), native._stream())
+                               Bn, H, Tq, Tk, st(q), st(k), st(v), float(scale), float(dropout_p), native._ptr(seed), native._stream())
     native._check(rc, "dl4j_flash_attn_fwd")
     return out, lse

@@ -4,6 +4,8 @@ helpers (``headers/BarnesHutTsne.h``), string / compat / util / test ops, and th
 compression ops (``encode_threshold`` / ``decode_threshold`` / ``encode_bitmap`` / ``decode_bitmap``)."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .registry import op
@@ -69,34 +71,59 @@ def split_list(lst, x, sizes, **kw):
 
 
 # ----------------------------------------------------------------------------- word2vec
+_MAX_EXP = 6.0      # HS_MAX_EXP of helpers/cuda/sg_cb.cu
+
+
+def _native_w2v(syn0, syn1, syn1neg, negTable, target, ngStarter, indices, codes, context, alpha, randomValue, nsRounds, trainWords=True):
+    """The whole batch in one kernel launch when the tables are fp32 CUDA tensors."""
+    if not (isinstance(syn0, torch.Tensor) and syn0.is_cuda and syn0.dtype == torch.float32):
+        return False
+    from . import native
+    if not native.available():
+        return False
+    s1 = syn1 if syn1 is not None and syn1.numel() else None
+    s1n = syn1neg if syn1neg is not None and syn1neg.numel() else None
+    pts = indices if indices is not None and indices.numel() and s1 is not None else None
+    ng = ngStarter if ngStarter is not None and ngStarter.numel() else None
+    return native.w2v_batch(syn0, s1, s1n, negTable, target, ng, pts, codes if pts is not None else None, context, alpha, randomValue,
+                            nsRounds if ng is not None else 0, trainWords)
+
+
 def _sg_rows(syn0, syn1, syn1neg, expTable, target, codes, points, ngStarter, negTable, alpha, nsRounds, nextRandom, vec=None, train_vec=True):
-    """One skip-gram style update of row ``target`` of syn0 (or of ``vec`` in inference mode)."""
-    l1 = vec if vec is not None else syn0[target]
+    """One skip-gram style update of row ``target`` of syn0 (or of ``vec`` in inference mode).  Output rows are visited one after
+    the other, each seeing the updates of the ones before it, as ``helpers/cuda/sg_cb.cu`` does (hSoftmax_ / nSampling_ per row)."""
+    l1 = (vec if vec is not None else syn0[target]).clone()
     neu1e = torch.zeros_like(l1)
-    if points is not None and len(points):
-        rows = syn1[points]
-        f = torch.sigmoid(rows @ l1)
-        g = (1.0 - codes.to(f.dtype) - f) * alpha
-        neu1e += g @ rows
-        syn1.index_add_(0, points, g.unsqueeze(1) * l1.unsqueeze(0))
-    if nsRounds > 0 and syn1neg is not None:
-        tgt = [int(ngStarter)]
-        r = int(nextRandom)
+
+    def row_step(table, r, code, hierarchic):
+        row = table[r]
+        dot = float(row @ l1)
+        if hierarchic:
+            if dot < -_MAX_EXP or dot >= _MAX_EXP:          # saturated node: skipped
+                return
+            g = (1.0 - code - 1.0 / (1.0 + math.exp(-dot))) * alpha
+        elif dot > _MAX_EXP:
+            g = (code - 1.0) * alpha
+        elif dot < -_MAX_EXP:
+            g = code * alpha
+        else:
+            g = (code - 1.0 / (1.0 + math.exp(-dot))) * alpha
+        neu1e.add_(row, alpha=g)
+        table[r] = row + g * l1
+
+    if points is not None and len(points) and syn1 is not None:
+        for p_, c_ in zip(points.tolist(), codes.tolist()):
+            row_step(syn1, int(p_), float(c_), True)
+    if nsRounds > 0 and syn1neg is not None and int(ngStarter) >= 0:
+        r = int(nextRandom) & 0xFFFFFFFFFFFFFFFF
         nt = negTable
+        row_step(syn1neg, int(ngStarter), 1.0, False)
         for _ in range(int(nsRounds)):
             r = (r * 25214903917 + 11) & 0xFFFFFFFFFFFFFFFF
             t = int(nt[(r >> 16) % nt.numel()]) if nt is not None and nt.numel() else (r >> 16) % syn1neg.shape[0]
             if t == int(ngStarter):
                 continue
-            tgt.append(t)
-        idx = torch.tensor(tgt, dtype=torch.long, device=syn0.device)
-        lab = torch.zeros(len(tgt), dtype=l1.dtype, device=syn0.device)
-        lab[0] = 1.0
-        rows = syn1neg[idx]
-        f = torch.sigmoid(rows @ l1)
-        g = (lab - f) * alpha
-        neu1e += g @ rows
-        syn1neg.index_add_(0, idx, g.unsqueeze(1) * l1.unsqueeze(0))
+            row_step(syn1neg, t, 0.0, False)
     if train_vec:
         if vec is not None:
             vec += neu1e
@@ -108,6 +135,9 @@ def _sg_rows(syn0, syn1, syn1neg, expTable, target, codes, points, ngStarter, ne
 @op("skipgram", differentiable=False, n_out=-1)
 def skipgram(target, ngStarter, indices, codes, syn0, syn1, syn1neg, expTable, negTable, alpha, randomValue, inferenceVector=None,
              nsRounds=0, isInference=False, isPreciseMode=False, numWorkers=1, **kw):
+    if not isInference and inferenceVector is None and _native_w2v(syn0, syn1, syn1neg, negTable, target, ngStarter, indices, codes, None,
+                                                                     alpha, randomValue, nsRounds):
+        return (syn0, syn1, syn1neg)
     tg = target.reshape(-1).tolist()
     al = alpha.reshape(-1).tolist()
     rv = randomValue.reshape(-1).tolist()
@@ -131,6 +161,10 @@ op("skipgram_inference", differentiable=False, n_out=-1)(lambda *a, **kw: skipgr
 @op("cbow", differentiable=False, n_out=-1)
 def cbow(target, ngStarter, context, lockedWords, indices, codes, syn0, syn1, syn1neg, expTable, negTable, alpha, randomValue,
          numLabels=None, inferenceVector=None, nsRounds=0, trainWords=True, isInference=False, **kw):
+    if not isInference and inferenceVector is None and target.numel() >= 1 and context.numel() % target.numel() == 0 \
+            and _native_w2v(syn0, syn1, syn1neg, negTable, target, ngStarter, indices, codes, context.reshape(target.numel(), -1), alpha,
+                            randomValue, nsRounds, trainWords):
+        return (syn0, syn1, syn1neg)
     ctx = context.reshape(-1)
     ctx = ctx[ctx >= 0].long()
     if ctx.numel() == 0 and inferenceVector is None:
@@ -169,6 +203,11 @@ def barnes_gains(gains, gradX, epsilon, **kw):
 @op("barnes_edge_forces")
 def barnes_edge_forces(rowP, colP, valP, dataP, N=None, **kw):
     n = int(N) if N is not None else dataP.shape[0]
+    if dataP.is_cuda and dataP.dtype == torch.float32 and n == dataP.shape[0]:
+        from . import native
+        r = native.barnes_edge_forces(rowP, colP, valP, dataP) if native.available() else None
+        if r is not None:
+            return r
     out = torch.zeros_like(dataP)
     rp = rowP.long().tolist()
     for i in range(n):

@@ -1134,9 +1134,9 @@ def add_relu(a, b):
     return _AddReluFn.apply(a, b)
 
 
-def attention(q, k, v, mask, scale):
+def attention(q, k, v, mask, scale, dropout_p=0.0):
     from . import attention_native
-    return attention_native.attention(q, k, v, mask, scale)
+    return attention_native.attention(q, k, v, mask, scale, dropout_p)
 
 
 # =========================================================================== fused updater
@@ -1280,3 +1280,72 @@ def bitmap_decode(msg, target, scale=1.0):
     rc = l.dl4j_bitmap_decode(_ptr(msg), _ptr(target), target.numel(), float(scale), _stream())
     _check(rc, "dl4j_bitmap_decode")
     return target
+
+
+# =========================================================================== word2vec / t-SNE
+def w2v_batch(syn0, syn1, syn1neg, neg_table, target, ng_starter, points, codes, context, alpha, random, ns_rounds, train_words=True):
+    """One launch of the skip-gram (``context`` None) or CBOW output-layer update for a batch of examples, in place on the fp32
+    tables.  ``target`` / ``ng_starter`` [B], ``points`` / ``codes`` [B, L] (-1 padded) or None, ``context`` [B, W] (-1 padded) or
+    None, ``alpha`` fp32 [B] or [1], ``random`` int64 [B] or [1].  Returns False when the case is not covered."""
+    l = lib()
+    if l is None or not syn0.is_cuda or syn0.dtype != torch.float32 or not syn0.is_contiguous() or syn0.dim() != 2:
+        return False
+    for t in (syn1, syn1neg):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.shape[1] != syn0.shape[1]):
+            return False
+    dev = syn0.device
+    V, D = int(syn0.shape[0]), int(syn0.shape[1])
+    if D > 4096:
+        return False
+
+    def i32(t):
+        return None if t is None else t.to(device=dev, dtype=torch.int32).contiguous()
+    target = i32(target.reshape(-1))
+    B = int(target.numel())
+    if B == 0:
+        return True
+    ng_starter = i32(ng_starter.reshape(-1)) if ng_starter is not None else None
+    L = W = 0
+    if points is not None and syn1 is not None:
+        points = i32(points.reshape(B, -1))
+        codes = codes.reshape(B, -1).to(device=dev, dtype=torch.int8).contiguous()
+        L = int(points.shape[1])
+    else:
+        points = codes = None
+    if context is not None:
+        context = i32(context.reshape(B, -1))
+        W = int(context.shape[1])
+    neg_table = i32(neg_table.reshape(-1)) if neg_table is not None and neg_table.numel() else None
+    alpha = alpha.to(device=dev, dtype=torch.float32).reshape(-1).contiguous()
+    random = random.to(device=dev, dtype=torch.int64).reshape(-1).contiguous()
+    if not hasattr(l.dl4j_w2v_batch, "_typed"):
+        vp, i32c, i64c = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        l.dl4j_w2v_batch.argtypes = [vp, vp, vp, vp, i64c, vp, vp, vp, vp, vp, vp, i32c, vp, i32c, i32c, i32c, i32c, i32c, i32c, i32c, i32c, vp]
+        l.dl4j_w2v_batch.restype = ctypes.c_int
+        l.dl4j_w2v_batch._typed = True
+    rc = l.dl4j_w2v_batch(_ptr(syn0), _ptr(syn1), _ptr(syn1neg), _ptr(neg_table), 0 if neg_table is None else int(neg_table.numel()),
+                          _ptr(target), _ptr(ng_starter), _ptr(points), _ptr(codes), _ptr(context), _ptr(alpha), int(alpha.numel()),
+                          _ptr(random), int(random.numel()), B, L, W, D, V, int(ns_rounds), 1 if train_words else 0, _stream())
+    _check(rc, "dl4j_w2v_batch")
+    return True
+
+
+def barnes_edge_forces(row_p, col_p, val_p, y):
+    """Attractive t-SNE forces over a CSR matrix; ``y`` fp32 [N, D <= 8].  None when the case is not covered."""
+    l = lib()
+    if l is None or not y.is_cuda or y.dtype != torch.float32 or y.dim() != 2 or y.shape[1] > 8:
+        return None
+    N, D = int(y.shape[0]), int(y.shape[1])
+    row_p = row_p.to(device=y.device, dtype=torch.int32).contiguous()
+    col_p = col_p.to(device=y.device, dtype=torch.int32).contiguous()
+    val_p = val_p.to(device=y.device, dtype=torch.float32).contiguous()
+    y = y.contiguous()
+    out = torch.empty_like(y)
+    if not hasattr(l.dl4j_barnes_edge_forces, "_typed"):
+        vp, i32c = ctypes.c_void_p, ctypes.c_int
+        l.dl4j_barnes_edge_forces.argtypes = [vp, vp, vp, vp, vp, i32c, i32c, vp]
+        l.dl4j_barnes_edge_forces.restype = ctypes.c_int
+        l.dl4j_barnes_edge_forces._typed = True
+    rc = l.dl4j_barnes_edge_forces(_ptr(row_p), _ptr(col_p), _ptr(val_p), _ptr(y), _ptr(out), N, D, _stream())
+    _check(rc, "dl4j_barnes_edge_forces")
+    return out

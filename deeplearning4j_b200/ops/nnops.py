@@ -87,8 +87,8 @@ def gelu(x, approximate="none"):
 def attention(q, k, v, mask=None, scale=None, dropout_p=0.0, training=False):
     """Scaled dot-product attention over [B, H, T, D] tensors; ``mask`` is [B, Tk] (1 = keep)."""
     nat = _native_for(q)
-    if nat is not None and q.dtype in (torch.bfloat16, torch.float16) and (dropout_p == 0.0 or not training):
-        y = nat.attention(q, k, v, mask, scale)
+    if nat is not None and q.dtype in (torch.bfloat16, torch.float16):
+        y = nat.attention(q, k, v, mask, scale, dropout_p if training else 0.0)      # dropout inside the fused kernels
         if y is not None:
             return y
     d = q.shape[-1]

@@ -85,3 +85,132 @@ def test_flash_forward_matches_reference(B, H, Tq, Tk, masked):
     assert float((got - ref).abs().max()) < 2e-2 * float(ref.abs().max() + 1e-6) + 2e-2
     ref_lse = torch.logsumexp(s, -1)
     assert float((lse - ref_lse).abs().max()) < 2e-2
+
+
+def _dropout_mask(an, B, H, T, p, seed):
+    """The keep mask the fused kernels apply for a given seed, read back through the kernels themselves: with q = k = 0 every
+    attention weight is 1 / T, and with V = 64 one-hot key selectors the output columns are the dropped weights of those keys."""
+    q = torch.zeros(B, H, T, 64, device="cuda", dtype=torch.bfloat16)
+    keep = torch.zeros(B, H, T, T, device="cuda", dtype=torch.bool)
+    for c0 in range(0, T, 64):
+        v = torch.zeros(B, H, T, 64, device="cuda", dtype=torch.bfloat16)
+        v[:, :, c0:c0 + 64] = torch.eye(64, device="cuda", dtype=torch.bfloat16)
+        an.set_dropout_seed(seed)
+        o = an.attention(q, q, v, None, 0.125, p)
+        keep[:, :, :, c0:c0 + 64] = o != 0
+    return keep
+
+
+@pytest.mark.parametrize("p", [0.1, 0.5])
+def test_fused_attention_dropout_mask_statistics_and_reproducibility(p):
+    from deeplearning4j_b200.ops import attention_native as an
+    from deeplearning4j_b200.ops import native
+    native.require()
+    B, H, T = 2, 3, 256
+    keep = _dropout_mask(an, B, H, T, p, seed=1234)
+    torch.cuda.synchronize()
+    native.check_status()
+    n = keep.numel()
+    frac = float(keep.float().mean())
+    assert abs(frac - (1 - p)) < 5 * (p * (1 - p) / n) ** 0.5 + 1e-4, frac          # five standard errors
+    # no structure along rows, columns, heads: every marginal is close to 1 - p
+    for dim in ((0, 1, 2), (0, 1, 3), (0, 2, 3), (1, 2, 3)):
+        m = keep.float().mean(dim)
+        se = (p * (1 - p) / (n / m.numel())) ** 0.5
+        assert float((m - (1 - p)).abs().max()) < 6 * se, (dim, float((m - (1 - p)).abs().max()), se)
+    # neighbouring elements are uncorrelated
+    a, b = keep[..., :-1].float() - (1 - p), keep[..., 1:].float() - (1 - p)
+    assert abs(float((a * b).mean()) / (p * (1 - p))) < 0.01
+    assert torch.equal(keep, _dropout_mask(an, B, H, T, p, seed=1234))               # same seed, same mask
+    other = _dropout_mask(an, B, H, T, p, seed=1235)
+    assert abs(float((keep == other).float().mean()) - (p * p + (1 - p) * (1 - p))) < 0.01      # another seed: independent
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_fused_attention_dropout_forward_backward_against_fp32_with_the_same_mask(masked):
+    from deeplearning4j_b200.ops import attention_native as an
+    from deeplearning4j_b200.ops import native
+    native.require()
+    B, H, T, p = 2, 2, 256, 0.2
+    g = torch.Generator(device="cuda").manual_seed(77)
+    keep = _dropout_mask(an, B, H, T, p, seed=99).float()
+    q, k, v = ((torch.randn(B, H, T, 64, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True) for _ in range(3))
+    mask = None
+    if masked:
+        mask = (torch.rand(B, T, device="cuda", generator=g) > 0.3).float()
+        mask[:, 0] = 1
+    an.set_dropout_seed(99)
+    o = an.attention(q, k, v, mask, 0.125, p)
+    do = torch.randn(B, H, T, 64, device="cuda", generator=g).bfloat16()
+    o.backward(do)
+    torch.cuda.synchronize()
+    native.check_status()
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    s = (q2 @ k2.transpose(-1, -2)) * 0.125
+    if mask is not None:
+        s = s.masked_fill(mask[:, None, None, :] == 0, float("-inf"))
+    thr = round(p * 65536)
+    w = torch.softmax(s, -1) * keep * (65536.0 / (65536 - thr))
+    ref = w @ v2
+    ref.backward(do.float())
+    assert _rel(o, ref) < 3e-2
+    for a, b in ((q, q2), (k, k2), (v, v2)):
+        assert _rel(a.grad, b.grad) < 4e-2
+
+
+def test_dropout_seed_advances_on_the_device_between_calls():
+    from deeplearning4j_b200.ops import attention_native as an
+    q = torch.zeros(1, 1, 128, 64, device="cuda", dtype=torch.bfloat16)
+    v = torch.zeros(1, 1, 128, 64, device="cuda", dtype=torch.bfloat16)
+    v[:, :, :64] = torch.eye(64, device="cuda", dtype=torch.bfloat16)
+    an.set_dropout_seed(5)
+    a = an.attention(q, q, v, None, 0.125, 0.5) != 0
+    b = an.attention(q, q, v, None, 0.125, 0.5) != 0
+    assert not torch.equal(a, b)
+
+
+@pytest.mark.parametrize("D,T", [(32, 256), (16, 128), (48, 384)])
+def test_small_head_sizes_run_on_the_fused_kernels(D, T):
+    from deeplearning4j_b200.ops import attention_native as an
+    from deeplearning4j_b200.ops import native
+    native.require()
+    B, H = 2, 3
+    g = torch.Generator(device="cuda").manual_seed(D + T)
+    q, k, v = ((torch.randn(B, H, T, D, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True) for _ in range(3))
+    mask = (torch.rand(B, T, device="cuda", generator=g) > 0.2).float()
+    mask[:, 0] = 1
+    before = native.LAUNCHES
+    o = an.attention(q, k, v, mask, None)
+    assert o is not None and o.shape == (B, H, T, D)
+    do = torch.randn(B, H, T, D, device="cuda", generator=g).bfloat16()
+    o.backward(do)
+    torch.cuda.synchronize()
+    native.check_status()
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = _ref(q2, k2, v2, mask, D ** -0.5)
+    ref.backward(do.float())
+    assert _rel(o, ref) < 3e-2
+    for a, b in ((q, q2), (k, k2), (v, v2)):
+        assert _rel(a.grad, b.grad) < 4e-2
+
+
+@pytest.mark.parametrize("T", [128, 1024, 2048])
+def test_fused_attention_sequence_lengths(T):
+    from deeplearning4j_b200.ops import attention_native as an
+    from deeplearning4j_b200.ops import native
+    native.require()
+    B, H = 1, 2
+    g = torch.Generator(device="cuda").manual_seed(T)
+    q, k, v = ((torch.randn(B, H, T, 64, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True) for _ in range(3))
+    assert an.flash_supported(q, k, v)
+    o = an.attention(q, k, v, None, 0.125)
+    do = torch.randn(B, H, T, 64, device="cuda", generator=g).bfloat16()
+    o.backward(do)
+    torch.cuda.synchronize()
+    native.check_status()
+    q2, k2, v2 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = _ref(q2, k2, v2, None, 0.125)
+    ref.backward(do.float())
+    assert _rel(o, ref) < 3e-2
+    for a, b in ((q, q2), (k, k2), (v, v2)):
+        assert _rel(a.grad, b.grad) < 4e-2

@@ -246,3 +246,25 @@ def test_counter_based_random_generator_matches_scalar_arithmetic():
     assert g2.nodeState() == state_after != node                       # consuming values advances the node state deterministically
     d = g.relativeDouble(np.arange(1000, dtype=np.uint64))
     assert d.min() >= 0.0 and d.max() < 1.0 and 0.4 < d.mean() < 0.6
+
+
+def test_counter_based_random_generator_golden_values():
+    """Literal values obtained by evaluating the stream definition of ``libnd4j/include/graph/RandomGenerator.h`` (``xoroshiro32``
+    :374-385, ``xoroshiro64`` :387-393, ``relativeT<float>`` / ``<double>`` :141-156, ``rewindH`` :395-404) with plain C integer
+    arithmetic (uint64 / uint32 wrap-around, the low 32 bits of ``s1 ^ s0`` taken as ``int``), independently of this package."""
+    from deeplearning4j_b200.nd.rng import RandomGenerator
+    g = RandomGenerator(119, 5)
+    idx = np.array([0, 1, 2, 1000, 123456789], dtype=np.uint64)
+    assert g.xoroshiro32(idx).tolist() == [3752294361, 3177379693, 1663668732, 1377381342, 3039950299]
+    assert g.xoroshiro64(idx).tolist() == [16115981569212512217, 13646741872161814489, 7145402799070083033, 5915807821762885593,
+                                           13056487119422715865]
+    np.testing.assert_array_equal(g.relativeFloat(idx), np.array([0.873649001, 0.739791274, 0.387352943, 0.320696473, 0.707793474],
+                                                                 dtype=np.float32))
+    np.testing.assert_array_equal(g.relativeDouble(idx), np.array([0.87364911145382762, 0.73979135925733686, 0.38735306190178931,
+                                                                   0.32069658461810291, 0.70779358499535561]))
+    g.rewindH(20000)
+    assert g.nodeState() == 175925260843722
+    g.rewindH(7)
+    assert g.nodeState() == -6099745996984563767
+    # default node seed (a zero node seed selects 1298567341)
+    assert RandomGenerator(0x123456789ABCDEF, 0).xoroshiro32(np.arange(3)).tolist() == [3946914084, 4080556201, 4230060595]
