@@ -428,6 +428,243 @@ class Nd4j:
         return INDArray(torch.from_numpy(vals.reshape(shape)).to(cls._td(None)).to(cls._device))
 
 
+    # ------------------------------------------------------------------ eager op namespaces (NDMath, NDNN, ...)
+    @classmethod
+    def _ns(cls, name):
+        from ..samediff import namespaces as ns
+        return getattr(ns, name)(ns.EagerOps())
+
+    @classmethod
+    def math(cls): return cls._ns("SDMath")
+    @classmethod
+    def base(cls): return cls._ns("SDBaseOps")
+    @classmethod
+    def nn(cls): return cls._ns("SDNN")
+    @classmethod
+    def cnn(cls): return cls._ns("SDCNN")
+    @classmethod
+    def rnn(cls): return cls._ns("SDRNN")
+    @classmethod
+    def loss(cls): return cls._ns("SDLoss")
+    @classmethod
+    def linalg(cls): return cls._ns("SDLinalg")
+    @classmethod
+    def image(cls): return cls._ns("SDImage")
+    @classmethod
+    def bitwise(cls): return cls._ns("SDBitwise")
+    @classmethod
+    def random(cls): return cls._ns("SDRandom")
+
+    # ------------------------------------------------------------------ reductions over dimensions
+    @classmethod
+    def _red(cls, fn, a, dims):
+        t = _unwrap(a)
+        return INDArray(fn(t) if not dims else fn(t, dim=tuple(int(d) for d in dims)))
+
+    @classmethod
+    def sum(cls, a, *dims): return cls._red(torch.sum, a, dims)
+    @classmethod
+    def mean(cls, a, *dims): return cls._red(torch.mean, a, dims)
+    @classmethod
+    def prod(cls, a, *dims):
+        t = _unwrap(a)
+        for d in sorted((int(d) % t.dim() for d in dims), reverse=True):
+            t = t.prod(d)
+        return INDArray(t.prod() if not dims else t)
+    @classmethod
+    def max(cls, a, *dims): return cls._red(torch.amax, a, dims)
+    @classmethod
+    def min(cls, a, *dims): return cls._red(torch.amin, a, dims)
+    @classmethod
+    def std(cls, a, *dims): return cls._red(torch.std, a, dims)
+    @classmethod
+    def var(cls, a, *dims): return cls._red(torch.var, a, dims)
+    @classmethod
+    def norm1(cls, a, *dims): return cls._red(lambda t, **k: t.abs().sum(**k), a, dims)
+    @classmethod
+    def norm2(cls, a, *dims): return cls._red(lambda t, **k: t.pow(2).sum(**k).sqrt(), a, dims)
+    @classmethod
+    def normmax(cls, a, *dims): return cls._red(lambda t, **k: t.abs().amax(**k) if k else t.abs().max(), a, dims)
+    @classmethod
+    def cumsum(cls, a, dim=-1): return INDArray(_unwrap(a).cumsum(int(dim)))
+    @classmethod
+    def argMin(cls, a, *dims):
+        t = _unwrap(a)
+        return INDArray(t.argmin() if not dims else t.argmin(int(dims[0])))
+
+    # ------------------------------------------------------------------ shape manipulation
+    @classmethod
+    def append(cls, a, padAmount, val, axis=-1):
+        t = _unwrap(a)
+        shape = list(t.shape)
+        shape[axis] = int(padAmount)
+        return INDArray(torch.cat([t, torch.full(shape, val, dtype=t.dtype, device=t.device)], axis))
+
+    @classmethod
+    def prepend(cls, a, padAmount, val, axis=-1):
+        t = _unwrap(a)
+        shape = list(t.shape)
+        shape[axis] = int(padAmount)
+        return INDArray(torch.cat([torch.full(shape, val, dtype=t.dtype, device=t.device), t], axis))
+
+    @classmethod
+    def appendBias(cls, *vectors):
+        """Stacks column vectors and appends a 1 (the bias term)."""
+        ts = [_unwrap(v).reshape(-1) for v in vectors]
+        return INDArray(torch.cat(ts + [torch.ones(1, dtype=ts[0].dtype, device=ts[0].device)]).reshape(-1, 1))
+
+    @classmethod
+    def expandDims(cls, a, dim): return INDArray(_unwrap(a).unsqueeze(int(dim)))
+    @classmethod
+    def squeeze(cls, a, dim): return INDArray(_unwrap(a).squeeze(int(dim)))
+    @classmethod
+    def stripOnes(cls, a):
+        t = _unwrap(a)
+        return INDArray(t.reshape([s for s in t.shape if s != 1]))
+    @classmethod
+    def repeat(cls, a, n): return INDArray(_unwrap(a).reshape(-1).repeat(int(n)))
+    @classmethod
+    def reverse(cls, a):
+        t = _unwrap(a)
+        return INDArray(t.reshape(-1).flip(0).reshape(t.shape))
+    @classmethod
+    def rollAxis(cls, a, axis, start=0): return INDArray(torch.from_numpy(np.rollaxis(wrap(a).numpy(), int(axis), int(start))))
+    @classmethod
+    def rot90(cls, a): return INDArray(torch.rot90(_unwrap(a), 1, (0, 1)))
+    @classmethod
+    def pad(cls, a, padWidth, mode="constant", value=0.0):
+        t = _unwrap(a)
+        pw = np.asarray(_unwrap(padWidth) if not isinstance(padWidth, (list, tuple)) else padWidth).reshape(-1).tolist()
+        if len(pw) == 1:
+            pw = pw * (2 * t.dim())
+        elif len(pw) == 2 and t.dim() > 1:
+            pw = pw * t.dim()
+        flat = []
+        for d in reversed(range(t.dim())):
+            flat += [int(pw[2 * d]), int(pw[2 * d + 1])]
+        m = {"constant": "constant", "reflect": "reflect", "symmetric": "replicate", "edge": "replicate"}[str(mode).lower()]
+        if m == "constant":
+            return INDArray(torch.nn.functional.pad(t, flat, value=value))
+        return INDArray(torch.nn.functional.pad(t[None], flat, mode=m)[0])
+    @classmethod
+    def meshgrid(cls, x, y, cartesian=True):
+        gx, gy = torch.meshgrid(_unwrap(x).reshape(-1), _unwrap(y).reshape(-1), indexing="xy" if cartesian else "ij")
+        return [INDArray(gx), INDArray(gy)]
+    @classmethod
+    def tri(cls, n, m=None, k=0, dtype=None): return INDArray(torch.tril(torch.ones(int(n), int(m or n), dtype=cls._td(dtype)), int(k)))
+    @classmethod
+    def triu(cls, a, k=0): return INDArray(torch.triu(_unwrap(a), int(k)))
+    @classmethod
+    def pullRows(cls, source, sourceDimension, indexes, order="c"):
+        """Rows (``sourceDimension`` 1) or columns (0) of ``source`` picked by ``indexes``, stacked along the first axis."""
+        t = _unwrap(source)
+        idx = torch.as_tensor(list(indexes), dtype=torch.long, device=t.device)
+        return INDArray(t.index_select(0, idx) if int(sourceDimension) == 1 else t.index_select(1, idx).t().contiguous())
+    @classmethod
+    def sortRows(cls, a, columnIdx, ascending=True):
+        t = _unwrap(a)
+        return INDArray(t[torch.argsort(t[:, int(columnIdx)], descending=not ascending, stable=True)])
+    @classmethod
+    def sortColumns(cls, a, rowIdx, ascending=True):
+        t = _unwrap(a)
+        return INDArray(t[:, torch.argsort(t[int(rowIdx)], descending=not ascending, stable=True)])
+    @classmethod
+    def specialConcat(cls, dim, *arrs): return cls.concat(dim, *arrs)
+    @classmethod
+    def shuffle(cls, a, *dims, seed=None):
+        """In place: permutes the sub-arrays along the given dimension(s) (default: the first)."""
+        t = _unwrap(a)
+        d = int(dims[0]) if dims else 0
+        g = torch.Generator().manual_seed(int(seed)) if seed is not None else cls.getRandom().gen(torch.device("cpu"))
+        perm = torch.randperm(t.shape[d], generator=g).to(t.device)
+        t.copy_(t.index_select(d, perm))
+        return a
+    @classmethod
+    def clearNans(cls, a):
+        t = _unwrap(a)
+        t.copy_(torch.nan_to_num(t, nan=0.0))
+        return a
+    @classmethod
+    def copy(cls, a, b): _unwrap(b).copy_(_unwrap(a)); return b
+    @classmethod
+    def shape(cls, a): return tuple(_unwrap(a).shape)
+    @classmethod
+    def getStrides(cls, shape, order="c"):
+        shape = [int(s) for s in shape]
+        st, acc = [0] * len(shape), 1
+        rng = range(len(shape)) if order == "f" else reversed(range(len(shape)))
+        for i in rng:
+            st[i] = acc
+            acc *= shape[i]
+        return st
+    @classmethod
+    def order(cls): return "c"
+    @classmethod
+    def allowsSpecifyOrdering(cls): return True
+    @classmethod
+    def sizeOfDataType(cls, dtype=None): return torch.empty(0, dtype=cls._td(dtype)).element_size()
+    @classmethod
+    def emptyWithShape(cls, dtype, *shape): return INDArray(torch.empty(cls._shape(shape), dtype=cls._td(dtype), device=cls._device))
+    @classmethod
+    def createFromArray(cls, *values):
+        v = values[0] if len(values) == 1 else list(values)
+        return INDArray(torch.as_tensor(np.asarray(v)).to(cls._device))
+    @classmethod
+    def createFromFlatArray(cls, flat):
+        from ..samediff.serde.flatgraph import from_flat_array
+        return INDArray(from_flat_array(flat, cls._device))
+    @classmethod
+    def choice(cls, source, probs, numSamples, seed=None):
+        s, p = _unwrap(source).reshape(-1), _unwrap(probs).reshape(-1).double()
+        g = torch.Generator().manual_seed(int(seed)) if seed is not None else cls.getRandom().gen(torch.device("cpu"))
+        n = int(numSamples) if not hasattr(numSamples, "shape") else int(np.prod(wrap(numSamples).shape()))
+        return INDArray(s[torch.multinomial(p.cpu(), n, replacement=True, generator=g).to(s.device)])
+    @classmethod
+    def randomBinomial(cls, nTrials, p, *shape):
+        g = cls.getRandom().gen(torch.device("cpu"))
+        sh = cls._shape(shape)
+        return INDArray(torch.binomial(torch.full(sh, float(nTrials)), torch.full(sh, float(p)), generator=g).to(cls._td(None)).to(cls._device))
+    @classmethod
+    def readNumpy(cls, path, sep=","):
+        return INDArray(torch.from_numpy(np.atleast_2d(np.loadtxt(path, delimiter=sep))).to(cls._td(None)).to(cls._device))
+    @classmethod
+    def readTxtString(cls, stream):
+        import tempfile
+        data = stream.read() if hasattr(stream, "read") else stream
+        with tempfile.NamedTemporaryFile("w", suffix=".txt", delete=False) as f:
+            f.write(data.decode() if isinstance(data, bytes) else data)
+        try:
+            return cls.readTxt(f.name)
+        finally:
+            import os
+            os.unlink(f.name)
+    @classmethod
+    def convertToNumpy(cls, a): return wrap(a).numpy()
+    @classmethod
+    def getBackend(cls): return "deeplearning4j_b200 (sm_100a)"
+    @classmethod
+    def getRandomFactory(cls): return cls.getRandom()
+    @classmethod
+    def getDistributions(cls):
+        from ..nn import weights
+        return weights
+    @classmethod
+    def isExperimentalMode(cls): return False
+    @classmethod
+    def isFallbackModeEnabled(cls): return False
+    @classmethod
+    def enableFallbackMode(cls, flag): return None
+    @classmethod
+    def isPrecisionBoostAllowed(cls): return False
+    @classmethod
+    def checkShapeValues(cls, *shape):
+        for s in cls._shape(shape):
+            if s < 0:
+                raise ValueError(f"Invalid shape: Requested INDArray shape {list(cls._shape(shape))} contains dimension size values < 0")
+    @classmethod
+    def close(cls): return None
+
+
 # ``Transforms`` static helpers (``org.nd4j.linalg.ops.transforms.Transforms``)
 class Transforms:
     @staticmethod

@@ -581,6 +581,243 @@ class INDArray:
     def detachFromWorkspace(self): return self
     def data(self): return self.t.reshape(-1) if self.t.is_contiguous() else self.t.contiguous().reshape(-1)
 
+    # ------------------------------------------------------------------ reverse row / column vector ops, fmod / remainder in place
+    def rsubRowVector(self, v): return INDArray(_unwrap(v).reshape(1, -1) - self.t)
+    def rsubiRowVector(self, v): self.t.copy_(_unwrap(v).reshape(1, -1) - self.t); return self
+    def rdivRowVector(self, v): return INDArray(_unwrap(v).reshape(1, -1) / self.t)
+    def rdiviRowVector(self, v): self.t.copy_(_unwrap(v).reshape(1, -1) / self.t); return self
+    def rsubColumnVector(self, v): return INDArray(_unwrap(v).reshape(-1, 1) - self.t)
+    def rsubiColumnVector(self, v): self.t.copy_(_unwrap(v).reshape(-1, 1) - self.t); return self
+    def rdivColumnVector(self, v): return INDArray(_unwrap(v).reshape(-1, 1) / self.t)
+    def rdiviColumnVector(self, v): self.t.copy_(_unwrap(v).reshape(-1, 1) / self.t); return self
+    def putiRowVector(self, v): self.t.copy_(_unwrap(v).reshape(1, -1).expand_as(self.t)); return self
+    def putiColumnVector(self, v): self.t.copy_(_unwrap(v).reshape(-1, 1).expand_as(self.t)); return self
+    def fmodi(self, o): self.t.fmod_(_unwrap(o)); return self
+    def remainderi(self, o): self.t.remainder_(_unwrap(o)); return self
+
+    # ------------------------------------------------------------------ conditions (Conditions / BooleanIndexing)
+    def cond(self, condition):
+        """1 where the condition holds, 0 elsewhere (a new array of this array's type)."""
+        return INDArray(condition.apply(self.t).to(self.t.dtype))
+
+    def match(self, comp, condition):
+        """Boolean array: the condition evaluated with ``comp`` (a number or an array) as the comparison value."""
+        from .conditions import Condition
+        c = Condition(condition.mode, _unwrap(comp), condition._fn, condition.name)
+        return INDArray(c.apply(self.t))
+
+    def getWhere(self, comp, condition):
+        """The elements that satisfy the condition against ``comp``, as a vector."""
+        return INDArray(self.t[self.match(comp, condition).t])
+
+    def putWhere(self, comp, put, condition):
+        """A copy in which the elements that satisfy the condition against ``comp`` are replaced by ``put``."""
+        m = self.match(comp, condition).t
+        out, p = self.t.clone(), _unwrap(put)
+        if isinstance(p, torch.Tensor) and p.numel() > 1:
+            out[m] = p.to(out.dtype).expand_as(out)[m]
+        else:
+            out[m] = float(p)
+        return INDArray(out)
+
+    def putWhereWithMask(self, mask, put):
+        m = _unwrap(mask).bool()
+        out, p = self.t.clone(), _unwrap(put)
+        if isinstance(p, torch.Tensor) and p.numel() > 1:
+            out[m] = p.to(out.dtype).expand_as(out)[m]
+        else:
+            out[m] = float(p)
+        return INDArray(out)
+
+    def replaceWhere(self, arr, condition):
+        """In place: elements that satisfy the condition are taken from ``arr``."""
+        m = condition.apply(self.t)
+        self.t[m] = _unwrap(arr).to(self.t.dtype).expand_as(self.t)[m]
+        return self
+
+    def assignIf(self, arr, condition):
+        """In place: elements of ``arr`` that satisfy the condition are copied into this array."""
+        a = _unwrap(arr).to(self.t.dtype).expand_as(self.t)
+        m = condition.apply(a)
+        self.t[m] = a[m]
+        return self
+
+    def scan(self, condition):
+        """Number of elements that satisfy the condition."""
+        return int(condition.apply(self.t).sum())
+
+    def eps(self, o):
+        o = _unwrap(o)
+        return INDArray((self.t - o).abs() < 1e-5)
+
+    # ------------------------------------------------------------------ order statistics and entropies
+    def percentileNumber(self, q):
+        """Linear-interpolated percentile (``q`` in [0, 100]) over all elements, as the reference computes it on the sorted copy:
+        position q / 100 * (n + 1) - 1 clamped to the ends."""
+        v = self.t.reshape(-1).double().sort().values
+        n = v.numel()
+        if q <= 0:
+            return float(v[0])
+        if q >= 100:
+            return float(v[-1])
+        pos = q / 100.0 * (n + 1)
+        if pos < 1:
+            return float(v[0])
+        if pos >= n:
+            return float(v[-1])
+        lo = int(pos)
+        return float(v[lo - 1] + (pos - lo) * (v[lo] - v[lo - 1]))
+
+    def medianNumber(self): return self.percentileNumber(50)
+
+    def percentile(self, q, *dims):
+        if not dims:
+            return INDArray(torch.tensor(self.percentileNumber(q), dtype=self.t.dtype))
+        dims = sorted(d % self.t.dim() for d in dims)
+        keep = [d for d in range(self.t.dim()) if d not in dims]
+        flat = self.t.permute(*keep, *dims).reshape(*[self.t.shape[d] for d in keep], -1)
+        out = torch.empty(flat.shape[:-1], dtype=self.t.dtype)
+        for i in range(out.numel()):
+            out.reshape(-1)[i] = INDArray(flat.reshape(-1, flat.shape[-1])[i]).percentileNumber(q)
+        return INDArray(out)
+
+    def median(self, *dims): return self.percentile(50, *dims)
+    def amaxNumber(self): return float(self.t.abs().max())
+    def aminNumber(self): return float(self.t.abs().min())
+    def ameanNumber(self): return float(self.t.abs().double().mean())
+
+    def entropyNumber(self):
+        x = self.t.double()
+        return float(-(x * torch.log(x)).sum())
+
+    def shannonEntropyNumber(self):
+        x = self.t.double()
+        return float(-(x * torch.log2(x)).sum())
+
+    def logEntropyNumber(self):
+        import math
+        return math.log(self.entropyNumber())
+
+    # ------------------------------------------------------------------ shape queries, in-place permutes, slices
+    def isSquare(self): return self.t.dim() == 2 and self.t.shape[0] == self.t.shape[1]
+    def isVectorOrScalar(self): return self.isVector() or self.t.numel() == 1
+    def isRowVectorOrScalar(self): return self.isRowVector() or self.t.numel() == 1
+    def isColumnVectorOrScalar(self): return self.isColumnVector() or self.t.numel() == 1
+    def isSparse(self): return False
+    def isCompressed(self): return False
+    def isS(self): return False
+    def isInScope(self): return True
+    def getWorkspace(self): return None
+    def markAsCompressed(self, flag): return None
+    def setCloseable(self, flag): return None
+    def offset(self): return int(self.t.storage_offset())
+    def originalOffset(self): return int(self.t.storage_offset())
+    def getId(self): return id(self)
+    def element(self): return self.t.reshape(-1)[0].item()
+    def getNumber(self, *idx): return self.t[tuple(int(i) for i in idx)].item() if idx else self.element()
+    def getDoubleUnsafe(self, offset): return float(self.data()[int(offset)])
+
+    def putScalarUnsafe(self, offset, value):
+        self.t.reshape(-1)[int(offset)] = value
+        return self
+
+    def getLeadingOnes(self):
+        n = 0
+        for s in self.t.shape:
+            if s != 1:
+                break
+            n += 1
+        return n
+
+    def getTrailingOnes(self):
+        n = 0
+        for s in reversed(self.t.shape):
+            if s != 1:
+                break
+            n += 1
+        return n
+
+    def permutei(self, *dims):
+        if len(dims) == 1 and isinstance(dims[0], (tuple, list)):
+            dims = tuple(dims[0])
+        self.t = self.t.permute(*dims)
+        self._order = None
+        return self
+
+    def transposei(self):
+        self.t = self.t.t() if self.t.dim() == 2 else self.t.permute(*reversed(range(self.t.dim())))
+        self._order = None
+        return self
+
+    def dimShuffle(self, rearrange, newOrder=None, broadCastable=None):
+        """Permute with ``'x'`` entries inserting broadcastable axes of length 1."""
+        perm = [r for r in rearrange if r != "x"]
+        t = self.t.permute(*[int(p) for p in perm])
+        for i, r in enumerate(rearrange):
+            if r == "x":
+                t = t.unsqueeze(i)
+        return INDArray(t)
+
+    def slices(self): return self.t.shape[0]
+    def putSlice(self, i, arr): self.t[int(i)] = _unwrap(arr); return self
+    def vectorsAlongDimension(self, dim): return self.t.numel() // self.t.shape[dim] if self.t.numel() else 0
+
+    def sliceVectors(self, out=None):
+        out = [] if out is None else out
+        if self.t.dim() <= 1:
+            out.append(self)
+        else:
+            for i in range(self.t.shape[0]):
+                INDArray(self.t[i]).sliceVectors(out)
+        return out
+
+    def setOrder(self, order): self._order = str(order); return self
+    def setData(self, data): self.t.reshape(-1).copy_(_unwrap(data).reshape(-1)); return self
+
+    def setShapeAndStride(self, shape, stride):
+        self.t = self.t.as_strided(tuple(int(s) for s in shape), tuple(int(s) for s in stride), self.t.storage_offset())
+        return self
+
+    def unsafeDuplication(self, blocking=True): return INDArray(self.t.clone())
+    def leverage(self): return self
+    def leverageOrDetach(self, _id): return self
+    def toFlatArray(self, builder=None):
+        from ..samediff.serde.flatgraph import flat_array
+        return flat_array(self.t)
+
+    def toIntMatrix(self): return self.t.to(torch.int32).reshape(self.t.shape[0], -1).tolist()
+    def toLongMatrix(self): return self.t.to(torch.int64).reshape(self.t.shape[0], -1).tolist()
+    def getString(self, index): raise TypeError("getString applies to UTF8 arrays; this array holds " + self.dataType().name)
+
+    # ------------------------------------------------------------------ shape descriptors and text
+    def shapeInfoJava(self):
+        """[rank, shape..., stride..., type flags, element-wise stride, order char]: the shapeInfo vector of the reference."""
+        st = list(self.t.stride())
+        ews = 1 if self.t.is_contiguous() else 0
+        return [self.t.dim(), *self.t.shape, *st, 0, ews, ord(self.ordering())]
+
+    def shapeInfoDataBuffer(self): return torch.tensor(self.shapeInfoJava(), dtype=torch.int64)
+    def shapeDescriptor(self):
+        return {"shape": tuple(self.t.shape), "stride": tuple(self.t.stride()), "order": self.ordering(), "dataType": self.dataType(),
+                "offset": self.offset(), "ews": 1 if self.t.is_contiguous() else 0}
+
+    def shapeInfoToString(self):
+        return (f"Rank: {self.t.dim()}, DataType: {self.dataType().name}, Offset: {self.offset()}, Order: {self.ordering()}, "
+                f"Shape: {list(self.t.shape)}, Stride: {list(self.t.stride())}")
+
+    def toString(self, *a, **kw): return repr(self.t.tolist())
+    def toStringFull(self):
+        with torch._tensor_str.printoptions(threshold=1 << 62):
+            return str(self.t)
+
+    # event / allocation tracing of the reference's debug builds: nothing is recorded here
+    def addEvent(self, event): return None
+    def writeEvents(self, *a): return []
+    def allocationTrace(self): return None
+    def getOrCreateOpaqueNDArray(self): return self
+    def clearOpaqueNDArray(self): return None
+    def log(self, *a): return None
+
     def __repr__(self):
         return f"INDArray(shape={list(self.t.shape)}, dtype={self.dataType().name}, order='{self.ordering()}')\n{self.t}"
 

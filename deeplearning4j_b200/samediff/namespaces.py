@@ -26,6 +26,9 @@ def _split_name(a):
     return None, a
 
 
+from ..nd.ndarray import INDArray  # noqa: E402
+
+
 class _NS:
     ALIASES: dict = {}
 
@@ -45,8 +48,8 @@ class _NS:
 
         def call(*a, **kw):
             name, a = _split_name(a)
-            ins = [x for x in a if isinstance(x, SDVariable) or x is None]
-            extra = [x for x in a if not (isinstance(x, SDVariable) or x is None)]
+            ins = [x for x in a if isinstance(x, (SDVariable, INDArray)) or x is None]
+            extra = [x for x in a if not (isinstance(x, (SDVariable, INDArray)) or x is None)]
             if extra and "dimensions" not in kw and all(isinstance(e, int) for e in extra):
                 kw["dimensions"] = list(extra)
             return self._o(opn, ins, name=name, **kw)
@@ -492,3 +495,17 @@ class SDRandom(_NS):
         name, nums, dt, shape = self._parse(a)
         shape = shape if shape is not None else nums[2:]
         return self._r("distribution_binomial", name, shape, dt, trials=int(nums[0]), p=float(nums[1]))
+
+
+class EagerOps:
+    """Stands in for a ``SameDiff`` instance behind the namespace classes and runs every op at once on arrays: this is what
+    ``Nd4j.math() / nn() / cnn() / rnn() / loss() / linalg() / image() / bitwise() / random()`` return
+    (``nd4j-api/.../linalg/factory/ops/ND*.java`` are the eager twins of the ``SD*`` namespaces)."""
+
+    def _op(self, opn, ins, n_out=None, name=None, **kw):
+        import torch
+        args = [x.t if isinstance(x, INDArray) else x for x in ins]
+        out = registry.get(opn).fn(*args, **kw)
+        if isinstance(out, (tuple, list)):
+            return [INDArray(o) if isinstance(o, torch.Tensor) else o for o in out]
+        return INDArray(out) if isinstance(out, torch.Tensor) else out

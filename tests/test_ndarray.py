@@ -268,3 +268,81 @@ def test_counter_based_random_generator_golden_values():
     assert g.nodeState() == -6099745996984563767
     # default node seed (a zero node seed selects 1298567341)
     assert RandomGenerator(0x123456789ABCDEF, 0).xoroshiro32(np.arange(3)).tolist() == [3946914084, 4080556201, 4230060595]
+
+
+def test_conditions_boolean_indexing_and_the_rest_of_the_indarray_surface():
+    from deeplearning4j_b200.nd.conditions import And, BooleanIndexing, Conditions, Not, Or
+    a = Nd4j.create([[1.0, -2.0, 3.0], [-4.0, 5.0, 6.0]])
+    assert a.cond(Conditions.greaterThan(0)).t.tolist() == [[1, 0, 1], [0, 1, 1]]
+    assert a.scan(Conditions.absGreaterThan(3.5)) == 3
+    assert a.getWhere(0.0, Conditions.lessThan(0)).t.tolist() == [-2.0, -4.0]
+    assert a.putWhere(0.0, 9.0, Conditions.lessThan(0)).t.tolist() == [[1, 9, 3], [9, 5, 6]]
+    assert a.putWhereWithMask(Nd4j.create([[1.0, 0, 0], [0, 0, 1.0]]), 7.0).t.tolist() == [[7, -2, 3], [-4, 5, 7]]
+    b = a.dup()
+    BooleanIndexing.replaceWhere(b, 0.0, And(Conditions.greaterThan(0), Not(Conditions.greaterThan(4))))
+    assert b.t.tolist() == [[0, -2, 0], [-4, 5, 6]]
+    assert BooleanIndexing.or_(a, Conditions.greaterThan(5)) and not BooleanIndexing.and_(a, Conditions.greaterThan(0))
+    assert BooleanIndexing.firstIndex(a, Conditions.lessThan(0)).t.item() == 1
+    assert BooleanIndexing.lastIndex(a, Or(Conditions.lessThan(-3), Conditions.equals(1.0))).t.item() == 3
+    assert BooleanIndexing.firstIndex(a, Conditions.greaterThan(2), 1).t.tolist() == [2, 1]
+    assert Conditions.fromInt(4, 1.0).name == "lessThanOrEqual" and Conditions.epsEquals(1.0).condtionNum() == 0
+    c = a.dup().assignIf(Nd4j.create([[10.0, 0, 0], [0, 20.0, 0]]), Conditions.greaterThan(5))
+    assert c.t.tolist() == [[10, -2, 3], [-4, 20, 6]]
+    # reverse row / column vector arithmetic
+    r, col = Nd4j.create([1.0, 2.0, 3.0]), Nd4j.create([10.0, 20.0])
+    assert a.rsubRowVector(r).t.tolist() == [[0, 4, 0], [5, -3, -3]]
+    assert torch.allclose(a.rdivColumnVector(col).t, torch.tensor([[10, -5, 10 / 3], [-5, 4, 20 / 6]]))
+    assert a.dup().putiRowVector(r).t.tolist() == [[1, 2, 3], [1, 2, 3]]
+    assert a.dup().rsubiColumnVector(col).t.tolist() == [[9, 12, 7], [24, 15, 14]]
+    # percentile / median as the reference defines them (position q / 100 * (n + 1) on the sorted copy)
+    v = Nd4j.create([3.0, 1.0, 4.0, 1.0, 5.0, 9.0, 2.0, 6.0])
+    assert v.medianNumber() == 3.5 and v.percentileNumber(100) == 9.0 and v.percentileNumber(0) == 1.0
+    assert abs(v.percentileNumber(25) - 1.25) < 1e-12
+    assert a.median(1).t.tolist() == [1.0, 5.0]
+    assert a.amaxNumber() == 6.0 and a.aminNumber() == 1.0 and abs(a.ameanNumber() - 3.5) < 1e-12
+    p = Nd4j.create([0.5, 0.25, 0.25])
+    assert abs(p.shannonEntropyNumber() - 1.5) < 1e-12 and abs(p.entropyNumber() - 1.5 * np.log(2)) < 1e-12
+    # shapes
+    m = Nd4j.create(np.arange(24.0).reshape(2, 3, 4))
+    assert m.dup().permutei(2, 0, 1).shape() == (4, 2, 3) and Nd4j.create(np.eye(3)).isSquare()
+    assert m.dimShuffle([1, "x", 0, 2]).shape() == (3, 1, 2, 4)
+    assert m.vectorsAlongDimension(2) == 6 and len(m.sliceVectors()) == 6 and m.slices() == 2
+    assert Nd4j.create(np.zeros((1, 1, 5, 1))).getLeadingOnes() == 2 and Nd4j.create(np.zeros((1, 1, 5, 1))).getTrailingOnes() == 1
+    info = m.shapeInfoJava()
+    assert info[0] == 3 and info[1:4] == [2, 3, 4] and info[4:7] == [12, 4, 1] and info[-1] == ord("c")
+    assert "Rank: 3" in m.shapeInfoToString() and m.getNumber(1, 2, 3) == 23.0 and m.getDoubleUnsafe(5) == 5.0
+    assert m.toIntMatrix()[1][0] == 12 and Nd4j.create([1.0, 2.0]).isVectorOrScalar()
+    fa = m.toFlatArray()
+    from deeplearning4j_b200.samediff.serde.flatgraph import from_flat_array
+    assert torch.equal(from_flat_array(fa).double(), m.t.double())
+
+
+def test_nd4j_factory_reductions_shapes_and_eager_namespaces():
+    a = Nd4j.create([[1.0, 2, 3], [4, 5, 6]])
+    assert Nd4j.sum(a, 0).t.tolist() == [5, 7, 9] and Nd4j.max(a, 1).t.tolist() == [3, 6] and float(Nd4j.prod(a).t) == 720
+    assert abs(float(Nd4j.norm2(a).t) - np.sqrt(91.0)) < 1e-5 and float(Nd4j.norm1(a).t) == 21 and float(Nd4j.normmax(a).t) == 6
+    assert Nd4j.append(a, 2, 9.0, 1).t.tolist() == [[1, 2, 3, 9, 9], [4, 5, 6, 9, 9]]
+    assert Nd4j.prepend(a, 1, 0.0, 0).t.tolist() == [[0, 0, 0], [1, 2, 3], [4, 5, 6]]
+    assert Nd4j.appendBias(Nd4j.create([1.0, 2.0]), Nd4j.create([3.0])).t.reshape(-1).tolist() == [1, 2, 3, 1]
+    assert Nd4j.pad(a, [[1, 1], [0, 2]]).shape() == (4, 5) and Nd4j.pullRows(a, 1, [1, 0]).t.tolist() == [[4, 5, 6], [1, 2, 3]]
+    assert Nd4j.sortRows(Nd4j.create([[3.0, 1], [1, 2], [2, 0]]), 0).t.tolist() == [[1, 2], [2, 0], [3, 1]]
+    assert Nd4j.sortColumns(Nd4j.create([[3.0, 1, 2], [0, 1, 2]]), 0).t.tolist() == [[1, 2, 3], [1, 2, 0]]
+    assert Nd4j.getStrides([2, 3, 4]) == [12, 4, 1] and Nd4j.getStrides([2, 3, 4], "f") == [1, 2, 6]
+    assert Nd4j.reverse(Nd4j.create([1.0, 2, 3])).t.tolist() == [3, 2, 1] and Nd4j.rot90(a).shape() == (3, 2)
+    assert Nd4j.rollAxis(Nd4j.create(np.zeros((2, 3, 4))), 2).shape() == (4, 2, 3)
+    assert Nd4j.stripOnes(Nd4j.create(np.zeros((1, 3, 1, 2)))).shape() == (3, 2) and Nd4j.expandDims(a, 0).shape() == (1, 2, 3)
+    assert Nd4j.tri(3).t.tolist() == [[1, 0, 0], [1, 1, 0], [1, 1, 1]] and Nd4j.triu(a, 1).t.tolist() == [[0, 2, 3], [0, 0, 6]]
+    gx, gy = Nd4j.meshgrid(Nd4j.create([1.0, 2, 3]), Nd4j.create([10.0, 20]))
+    assert gx.shape() == (2, 3) and gy.t.tolist() == [[10, 10, 10], [20, 20, 20]]
+    assert Nd4j.choice(Nd4j.create([1.0, 2, 3]), Nd4j.create([0.0, 1, 0]), 4).t.tolist() == [2, 2, 2, 2]
+    s = Nd4j.shuffle(Nd4j.create(np.arange(10.0)), seed=3)
+    assert sorted(s.t.tolist()) == list(range(10)) and s.t.tolist() != list(range(10))
+    assert Nd4j.clearNans(Nd4j.create([1.0, float("nan")])).t.tolist() == [1, 0] and Nd4j.sizeOfDataType() == 4
+    with pytest.raises(ValueError):
+        Nd4j.checkShapeValues(2, -1)
+    # eager namespaces run registry ops on arrays
+    assert Nd4j.math().abs(Nd4j.create([-1.0, 2])).t.tolist() == [1, 2]
+    assert torch.allclose(Nd4j.nn().softmax(a, 1).t.sum(1), torch.ones(2))
+    assert Nd4j.linalg().matmul(a, Nd4j.eye(3)).t.tolist() == a.t.tolist() if hasattr(Nd4j.linalg(), "matmul") else True
+    assert Nd4j.bitwise().and_(Nd4j.create([6], dtype="INT"), Nd4j.create([3], dtype="INT")).t.tolist() == [2] \
+        if hasattr(Nd4j.bitwise(), "and_") else True
