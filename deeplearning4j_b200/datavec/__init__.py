@@ -5,3 +5,13 @@ from .transform import (AnalyzeLocal, BooleanCondition, CategoricalColumnConditi
                         ConditionOp, DataAnalysis, DoubleColumnCondition, IntegerColumnCondition, InvalidValueColumnCondition,
                         LocalTransformExecutor, MathFunction, MathOp, NullWritableColumnCondition, ReduceOp, Reducer, Schema,
                         StringColumnCondition, TransformProcess)
+from .extra import (ArrowConverter, ArrowRecordReader, ArrowRecordWriter, BoxImageTransform, ColorConversionTransform,  # noqa: F401
+                    CropImageTransform, DataQualityAnalysis, EqualizeHistTransform, ExcelRecordReader, ExcelRecordWriter,
+                    FlipImageTransform, ImageTransform, JDBCRecordReader, Join, JoinType, MultiImageTransform, NativeImageLoader,
+                    PipelineImageTransform, RandomCropTransform, ResizeImageTransform, RotateImageTransform, ScaleImageTransform,
+                    analyzeQuality, convertFromSequence, executeJoin, reduceSequence, sequenceDifference,
+                    sequenceMovingWindowReduce, splitSequenceMaxLength, splitSequenceTimeSeparation, trimSequence,
+                    trimSequenceToLength)
+
+LocalTransformExecutor.executeJoin = staticmethod(executeJoin)
+AnalyzeLocal.analyzeQuality = staticmethod(analyzeQuality)
