@@ -5,6 +5,8 @@ graph inputs become placeholders, and each node is mapped by an entry of ``OP_MA
 list of unsupported op types, as the reference's importer does."""
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -212,6 +214,308 @@ OP_MAPPERS = {
 }
 
 
+# ----------------------------------------------------------------------------- generic rules: ONNX semantics written once on tensors
+def _ints(t):
+    return [int(v) for v in (t.reshape(-1).tolist() if isinstance(t, torch.Tensor) else t)]
+
+
+def _onnx_ops():
+    """ONNX op type -> (function(inputs..., **attributes), number of outputs; -1 = one per declared output).  Inputs that ONNX passes
+    as tensors (axes, shapes, pads, k, ...) stay tensor inputs of the graph node, so they may be computed at run time."""
+    import torch.nn.functional as F
+
+    def variadic(fn):
+        def f(*xs, **kw):
+            out = xs[0]
+            for x in xs[1:]:
+                out = fn(out, x)
+            return out
+        return f
+
+    def red(fn):
+        def f(x, axes_t=None, axes=None, keepdims=1, noop_with_empty_axes=0, **kw):
+            ax = _ints(axes_t) if axes_t is not None else (list(axes) if axes is not None else None)
+            if not ax:
+                if noop_with_empty_axes and axes_t is not None:
+                    return x
+                ax = list(range(x.dim()))
+            return fn(x, tuple(ax), bool(keepdims))
+        return f
+
+    def split(x, split_t=None, axis=0, split=None, num_outputs=None, **kw):
+        sizes = _ints(split_t) if split_t is not None else (list(split) if split is not None else None)
+        if sizes is None:
+            k = int(num_outputs)
+            step = -(-x.shape[axis] // k)
+            return tuple(x.split(step, axis))
+        return tuple(x.split(sizes, axis))
+
+    def topk(x, k, axis=-1, largest=1, sorted=1, **kw):
+        v, i = torch.topk(x, int(k.reshape(-1)[0]), dim=axis, largest=bool(largest), sorted=True)
+        return v, i
+
+    def pad(x, pads, value=None, axes=None, mode="constant", **kw):
+        p = _ints(pads)
+        ax = _ints(axes) if axes is not None else list(range(x.dim()))
+        n = len(ax)
+        lo, hi = [0] * x.dim(), [0] * x.dim()
+        for j, a in enumerate(ax):
+            lo[a % x.dim()], hi[a % x.dim()] = p[j], p[n + j]
+        if mode == "constant":
+            flat = []
+            for d in reversed(range(x.dim())):
+                flat += [lo[d], hi[d]]
+            return F.pad(x, flat, value=float(value.reshape(-1)[0]) if value is not None and value.numel() else 0.0)
+        y = x
+        for d in range(x.dim()):
+            if not (lo[d] or hi[d]):
+                continue
+            nd = y.shape[d]
+            if mode == "reflect":
+                front, back = y.narrow(d, 1, lo[d]).flip(d), y.narrow(d, nd - hi[d] - 1, hi[d]).flip(d)
+            else:                                          # edge
+                front = y.narrow(d, 0, 1).expand(*[lo[d] if k == d else s for k, s in enumerate(y.shape)])
+                back = y.narrow(d, nd - 1, 1).expand(*[hi[d] if k == d else s for k, s in enumerate(y.shape)])
+            y = torch.cat([front, y, back], d)
+        return y
+
+    def resize(x, roi=None, scales=None, sizes=None, mode="nearest", coordinate_transformation_mode="half_pixel", nearest_mode="round_prefer_floor", **kw):
+        if sizes is not None and sizes.numel():
+            out = _ints(sizes)[2:]
+        else:
+            sc = scales.reshape(-1).tolist()[2:]
+            out = [int(math.floor(s * f)) for s, f in zip(x.shape[2:], sc)]
+        if mode == "nearest":
+            if coordinate_transformation_mode == "asymmetric" and nearest_mode == "floor":
+                idx = [(torch.arange(o, device=x.device) * (s / o)).floor().long().clamp(max=s - 1) for o, s in zip(out, x.shape[2:])]
+                y = x
+                for d, i in enumerate(idx):
+                    y = y.index_select(2 + d, i)
+                return y
+            return F.interpolate(x, size=out, mode="nearest-exact" if coordinate_transformation_mode in ("half_pixel", "pytorch_half_pixel") else "nearest")
+        m = {1: "linear", 2: "bilinear", 3: "trilinear"}[len(out)] if mode == "linear" else "bicubic"
+        return F.interpolate(x, size=out, mode=m, align_corners=coordinate_transformation_mode == "align_corners")
+
+    def conv_t(x, w, b=None, strides=None, dilations=None, pads=None, output_padding=None, group=1, output_shape=None, auto_pad="NOTSET", **kw):
+        nd = x.dim() - 2
+        st, dl = list(strides or [1] * nd), list(dilations or [1] * nd)
+        op_ = list(output_padding or [0] * nd)
+        pd = list(pads or [0] * (2 * nd))
+        fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[nd]
+        y = fn(x, w.to(x.dtype), None if b is None else b.to(x.dtype), st, 0, op_, group, dl)
+        if output_shape is not None or auto_pad in ("SAME_UPPER", "SAME_LOWER"):
+            tgt = list(output_shape) if output_shape is not None else [s * k for s, k in zip(x.shape[2:], st)]
+            for d in range(nd):
+                extra = y.shape[2 + d] - tgt[d]
+                lo = extra // 2 if auto_pad != "SAME_LOWER" else extra - extra // 2
+                y = y.narrow(2 + d, lo, tgt[d])
+            return y
+        for d in range(nd):
+            y = y.narrow(2 + d, pd[d], y.shape[2 + d] - pd[d] - pd[nd + d])
+        return y
+
+    def inorm(x, scale, bias, epsilon=1e-5, **kw):
+        return F.instance_norm(x, weight=scale, bias=bias, eps=float(epsilon))
+
+    def lrn(x, size=5, alpha=1e-4, beta=0.75, bias=1.0, **kw):
+        return F.local_response_norm(x, int(size), float(alpha), float(beta), float(bias))
+
+    def d2s(x, blocksize=2, mode="DCR", **kw):
+        n, c, h, w = x.shape
+        b = int(blocksize)
+        if mode == "DCR":
+            return x.reshape(n, b, b, c // (b * b), h, w).permute(0, 3, 4, 1, 5, 2).reshape(n, c // (b * b), h * b, w * b)
+        return x.reshape(n, c // (b * b), b, b, h, w).permute(0, 1, 4, 2, 5, 3).reshape(n, c // (b * b), h * b, w * b)
+
+    def s2d(x, blocksize=2, **kw):
+        n, c, h, w = x.shape
+        b = int(blocksize)
+        return x.reshape(n, c, h // b, b, w // b, b).permute(0, 3, 5, 1, 2, 4).reshape(n, c * b * b, h // b, w // b)
+
+    def scatter_el(x, idx, upd, axis=0, reduction="none", **kw):
+        idx = torch.where(idx < 0, idx + x.shape[axis], idx).long()
+        if reduction == "none":
+            return x.scatter(axis, idx, upd)
+        return x.scatter_reduce(axis, idx, upd, {"add": "sum", "mul": "prod", "max": "amax", "min": "amin"}[reduction])
+
+    def scatter_nd(x, idx, upd, reduction="none", **kw):
+        y = x.clone()
+        ix = tuple(idx.long()[..., i] for i in range(idx.shape[-1]))
+        if reduction == "add":
+            y.index_put_(ix, upd, accumulate=True)
+        else:
+            y[ix] = upd
+        return y
+
+    def gather_nd(x, idx, batch_dims=0, **kw):
+        idx = idx.long()
+        if batch_dims:
+            return torch.stack([gather_nd(xb, ib, batch_dims - 1) for xb, ib in zip(x, idx)])
+        return x[tuple(idx[..., i] for i in range(idx.shape[-1]))]
+
+    def onehot(idx, depth, values, axis=-1, **kw):
+        d = int(depth.reshape(-1)[0])
+        i = idx.long()
+        i = torch.where(i < 0, i + d, i)
+        oh = F.one_hot(i.clamp(0, d - 1), d).bool() & ((i >= 0) & (i < d)).unsqueeze(-1)
+        y = torch.where(oh, values[1], values[0])
+        return y if axis in (-1, idx.dim()) else y.movedim(-1, axis)
+
+    def cumsum(x, axis, exclusive=0, reverse=0, **kw):
+        a = int(axis.reshape(-1)[0])
+        if reverse:
+            x = x.flip(a)
+        y = x.cumsum(a)
+        if exclusive:
+            y = y - x
+        return y.flip(a) if reverse else y
+
+    def arg(fn):
+        def f(x, axis=0, keepdims=1, select_last_index=0, **kw):
+            if select_last_index:
+                r = x.shape[axis] - 1 - fn(x.flip(axis), axis, bool(keepdims))
+                return r
+            return fn(x, axis, bool(keepdims))
+        return f
+
+    def lstm(X, W, R, B=None, seq_lens=None, h0=None, c0=None, P=None, hidden_size=None, direction="forward", **kw):
+        """ONNX LSTM (gate order i, o, f, c; layout 0): X [T, N, I] -> Y [T, D, N, H], Y_h, Y_c [D, N, H]."""
+        T, N, _ = X.shape
+        D, H = W.shape[0], R.shape[2]
+        ys, hs, cs = [], [], []
+        for d in range(D):
+            w, r = W[d], R[d]
+            b = (B[d][:4 * H] + B[d][4 * H:]) if B is not None else X.new_zeros(4 * H)
+            h = h0[d] if h0 is not None else X.new_zeros(N, H)
+            c = c0[d] if c0 is not None else X.new_zeros(N, H)
+            steps = range(T - 1, -1, -1) if (direction == "reverse" or d == 1) else range(T)
+            out = [None] * T
+            for t in steps:
+                z = X[t] @ w.t() + h @ r.t() + b
+                i, o, f, g = z[:, :H], z[:, H:2 * H], z[:, 2 * H:3 * H], z[:, 3 * H:]
+                if P is not None:
+                    i, f = i + P[d][:H] * c, f + P[d][2 * H:] * c
+                i, f = torch.sigmoid(i), torch.sigmoid(f)
+                c = f * c + i * torch.tanh(g)
+                if P is not None:
+                    o = o + P[d][H:2 * H] * c
+                h = torch.sigmoid(o) * torch.tanh(c)
+                out[t] = h
+            ys.append(torch.stack(out))
+            hs.append(h)
+            cs.append(c)
+        return torch.stack(ys, 1), torch.stack(hs), torch.stack(cs)
+
+    def gru(X, W, R, B=None, seq_lens=None, h0=None, hidden_size=None, direction="forward", linear_before_reset=0, **kw):
+        """ONNX GRU (gate order z, r, h): X [T, N, I] -> Y [T, D, N, H], Y_h [D, N, H]."""
+        T, N, _ = X.shape
+        D, H = W.shape[0], R.shape[2]
+        ys, hs = [], []
+        for d in range(D):
+            w, r = W[d], R[d]
+            wb = B[d][:3 * H] if B is not None else X.new_zeros(3 * H)
+            rb = B[d][3 * H:] if B is not None else X.new_zeros(3 * H)
+            h = h0[d] if h0 is not None else X.new_zeros(N, H)
+            steps = range(T - 1, -1, -1) if (direction == "reverse" or d == 1) else range(T)
+            out = [None] * T
+            for t in steps:
+                xz = X[t] @ w.t() + wb
+                z = torch.sigmoid(xz[:, :H] + h @ r[:H].t() + rb[:H])
+                rr = torch.sigmoid(xz[:, H:2 * H] + h @ r[H:2 * H].t() + rb[H:2 * H])
+                if linear_before_reset:
+                    hh = torch.tanh(xz[:, 2 * H:] + rr * (h @ r[2 * H:].t() + rb[2 * H:]))
+                else:
+                    hh = torch.tanh(xz[:, 2 * H:] + (rr * h) @ r[2 * H:].t() + rb[2 * H:])
+                h = (1 - z) * hh + z * h
+                out[t] = h
+            ys.append(torch.stack(out))
+            hs.append(h)
+        return torch.stack(ys, 1), torch.stack(hs)
+
+    T = {
+        "Less": (lambda a, b, **k: a < b, 1), "LessOrEqual": (lambda a, b, **k: a <= b, 1), "Greater": (lambda a, b, **k: a > b, 1),
+        "GreaterOrEqual": (lambda a, b, **k: a >= b, 1), "Equal": (lambda a, b, **k: a == b, 1), "Not": (lambda a, **k: ~a, 1),
+        "And": (lambda a, b, **k: a & b, 1), "Or": (lambda a, b, **k: a | b, 1), "Xor": (lambda a, b, **k: a ^ b, 1),
+        "Where": (lambda c, a, b, **k: torch.where(c, a, b), 1),
+        "Max": (variadic(torch.maximum), 1), "Min": (variadic(torch.minimum), 1), "Sum": (variadic(torch.add), 1),
+        "Mean": (lambda *xs, **k: variadic(torch.add)(*xs) / len(xs), 1),
+        "Sin": (lambda x, **k: x.sin(), 1), "Cos": (lambda x, **k: x.cos(), 1), "Tan": (lambda x, **k: x.tan(), 1), "Asin": (lambda x, **k: x.asin(), 1),
+        "Acos": (lambda x, **k: x.acos(), 1), "Atan": (lambda x, **k: x.atan(), 1), "Sinh": (lambda x, **k: x.sinh(), 1), "Cosh": (lambda x, **k: x.cosh(), 1),
+        "Asinh": (lambda x, **k: x.asinh(), 1), "Acosh": (lambda x, **k: x.acosh(), 1), "Atanh": (lambda x, **k: x.atanh(), 1),
+        "Round": (lambda x, **k: x.round(), 1), "Sign": (lambda x, **k: x.sign(), 1), "Softsign": (lambda x, **k: x / (1 + x.abs()), 1),
+        "Selu": (lambda x, alpha=1.6732632423543772, gamma=1.0507009873554805, **k: gamma * torch.where(x > 0, x, alpha * x.expm1()), 1),
+        "HardSigmoid": (lambda x, alpha=0.2, beta=0.5, **k: (alpha * x + beta).clamp(0, 1), 1),
+        "HardSwish": (lambda x, **k: x * (x / 6 + 0.5).clamp(0, 1), 1), "PRelu": (lambda x, s, **k: torch.where(x >= 0, x, x * s), 1),
+        "ThresholdedRelu": (lambda x, alpha=1.0, **k: torch.where(x > alpha, x, torch.zeros_like(x)), 1),
+        "Mish": (lambda x, **k: x * torch.tanh(F.softplus(x)), 1), "Celu": (lambda x, alpha=1.0, **k: F.celu(x, alpha), 1),
+        "IsNaN": (lambda x, **k: x.isnan(), 1), "IsInf": (lambda x, detect_negative=1, detect_positive=1, **k:
+                                                          (x.isposinf() if detect_positive else torch.zeros_like(x, dtype=torch.bool)) |
+                                                          (x.isneginf() if detect_negative else torch.zeros_like(x, dtype=torch.bool)), 1),
+        "Expand": (lambda x, sh, **k: x.broadcast_to(torch.broadcast_shapes(tuple(x.shape), tuple(_ints(sh)))), 1),
+        "Tile": (lambda x, r, **k: x.repeat(*_ints(r)), 1),
+        "Range": (lambda a, b, c, **k: torch.arange(a.item(), b.item(), c.item(), dtype=a.dtype, device=a.device), 1),
+        "ConstantOfShape": (lambda sh, value=None, **k: torch.full(_ints(sh), (value.reshape(-1)[0].item() if value is not None else 0.0),
+                                                                  dtype=value.dtype if value is not None else torch.float32), 1),
+        "Split": (split, -1), "TopK": (topk, 2),
+        "ArgMax": (arg(lambda x, a, kd: x.argmax(a, kd)), 1), "ArgMin": (arg(lambda x, a, kd: x.argmin(a, kd)), 1),
+        "CumSum": (cumsum, 1), "OneHot": (onehot, 1),
+        "GatherElements": (lambda x, i, axis=0, **k: x.gather(axis, torch.where(i < 0, i + x.shape[axis], i).long()), 1),
+        "GatherND": (gather_nd, 1), "ScatterElements": (scatter_el, 1), "Scatter": (scatter_el, 1), "ScatterND": (scatter_nd, 1),
+        "Pad": (pad, 1), "Resize": (resize, 1), "Upsample": (lambda x, scales, mode="nearest", **k: resize(x, None, scales, None, mode, "asymmetric", "floor"), 1),
+        "DepthToSpace": (d2s, 1), "SpaceToDepth": (s2d, 1), "ConvTranspose": (conv_t, 1), "InstanceNormalization": (inorm, 1), "LRN": (lrn, 1),
+        "ReduceProd": (red(lambda x, ax, kd: [x := x.prod(d, keepdim=True) for d in ax][-1] if kd else
+                           [x := x.prod(d) for d in sorted((a % x.dim() for a in ax), reverse=True)][-1]), 1),
+        "ReduceL1": (red(lambda x, ax, kd: x.abs().sum(ax, kd)), 1), "ReduceL2": (red(lambda x, ax, kd: x.pow(2).sum(ax, kd).sqrt()), 1),
+        "ReduceLogSumExp": (red(lambda x, ax, kd: x.logsumexp(ax, kd)), 1), "ReduceSumSquare": (red(lambda x, ax, kd: x.pow(2).sum(ax, kd)), 1),
+        "ReduceLogSum": (red(lambda x, ax, kd: x.sum(ax, kd).log()), 1),
+        "Einsum": (lambda *xs, equation="", **k: torch.einsum(equation, *xs), 1), "NonZero": (lambda x, **k: x.nonzero().t(), 1),
+        "Size": (lambda x, **k: torch.tensor(x.numel(), dtype=torch.int64), 1),
+        "Trilu": (lambda x, kk=None, upper=1, **k: (torch.triu if upper else torch.tril)(x, int(kk.reshape(-1)[0]) if kk is not None else 0), 1),
+        "Mod": (lambda a, b, fmod=0, **k: torch.fmod(a, b) if fmod else torch.remainder(a, b), 1),
+        "BitShift": (lambda a, b, direction="LEFT", **k: a << b if direction == "LEFT" else a >> b, 1),
+        "EyeLike": (lambda x, k=0, **kw: torch.eye(x.shape[0], x.shape[1], dtype=x.dtype).roll(int(k), 1) if not k else torch.diag(torch.ones(min(x.shape[0], x.shape[1] - k) if k > 0 else min(x.shape[0] + k, x.shape[1]), dtype=x.dtype), int(k))[:x.shape[0], :x.shape[1]], 1),
+        "Hardmax": (lambda x, axis=-1, **k: F.one_hot(x.argmax(axis), x.shape[axis]).to(x.dtype).movedim(-1, axis), 1),
+        "LpNormalization": (lambda x, axis=-1, p=2, **k: x / x.norm(p=p, dim=axis, keepdim=True), 1),
+        "MeanVarianceNormalization": (lambda x, axes=(0, 2, 3), **k: (x - x.mean(tuple(axes), keepdim=True)) / x.var(tuple(axes), unbiased=False, keepdim=True).sqrt(), 1),
+        "GlobalLpPool": (lambda x, p=2, **k: x.norm(p=p, dim=tuple(range(2, x.dim())), keepdim=True), 1),
+        "Sqrt": (lambda x, **k: x.sqrt(), 1),
+        "LSTM": (lstm, 3), "GRU": (gru, 2),
+    }
+    return T
+
+
+def _register_onnx_ops():
+    from ..ops.registry import has, op
+    if has("onnx.Less"):
+        return
+    for name, (fn, n_out) in _onnx_ops().items():
+        op("onnx." + name, n_out=n_out, group="onnx_import")(fn)
+
+
+def _generic(opname):
+    def f(sd, ctx, n, x):
+        fn, n_out = _GENERIC[opname]
+        k = len([o for o in n["outputs"]]) if n_out == -1 else n_out
+        attrs = {a: (list(v) if isinstance(v, (list, tuple)) else v) for a, v in n["attrs"].items() if not isinstance(v, (torch.Tensor, dict))}
+        tens = {a: v for a, v in n["attrs"].items() if isinstance(v, torch.Tensor)}
+        ins = list(x)
+        while ins and ins[-1] is None:
+            ins.pop()
+        if opname == "Split":
+            attrs["num_outputs"] = k
+        if tens:                                     # tensor-valued attributes (ConstantOfShape.value) become constants of the graph
+            for a, t in tens.items():
+                attrs[a] = t
+        return sd._op("onnx." + opname, ins, n_out=k, **attrs)
+    return f
+
+
+_GENERIC = _onnx_ops()
+
+for _name in _GENERIC:
+    OP_MAPPERS.setdefault(_name, _generic(_name))
+
+
 # helper ops with ONNX semantics (NCHW, explicit begin/end pads) registered in the op registry
 def _register_helpers():
     import torch.nn.functional as F
@@ -305,6 +609,7 @@ class OnnxFrameworkImporter:
 
     def runImport(self, path_or_bytes, dynamicVariables=None, suggestDynamicVariables=False):
         _register_helpers()
+        _register_onnx_ops()
         if isinstance(path_or_bytes, (bytes, bytearray, memoryview)):
             data = path_or_bytes
         else:
@@ -333,6 +638,9 @@ class OnnxFrameworkImporter:
             dt = {1: DataType.FLOAT, 6: DataType.INT, 7: DataType.LONG, 10: DataType.HALF, 11: DataType.DOUBLE, 9: DataType.BOOL}.get(elem, DataType.FLOAT)
             vars_[name] = sd.placeHolder(name, dt, *(shape or []))
         for n in model["nodes"]:
+            for i in n["inputs"]:                       # an initializer that some rule consumed at import time and another reads as data
+                if i and i not in vars_ and i in ctx["consts"] and n["op"] in _GENERIC:
+                    vars_[i] = sd.constant(i, ctx["consts"][i].clone())
             ins = [vars_.get(i) if i else None for i in n["inputs"]]
             out = OP_MAPPERS[n["op"]](sd, ctx, n, ins)
             outs = out if isinstance(out, (list, tuple)) else [out]

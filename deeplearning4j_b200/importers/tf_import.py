@@ -147,6 +147,229 @@ def _register_helpers():
         return (x - mean.reshape(shp)) * (scale.reshape(shp) * torch.rsqrt(var.reshape(shp) + epsilon)) + offset.reshape(shp)
 
 
+def _ints(t):
+    return [int(v) for v in (t.reshape(-1).tolist() if isinstance(t, torch.Tensor) else t)]
+
+
+def _tf_ops():
+    """TensorFlow op type -> (function(inputs..., **attrs), number of outputs; -1 = variable).  Arguments that TensorFlow passes as
+    tensors (shapes, axes, paddings, ...) stay tensor inputs, so they may be computed inside the graph."""
+    import torch.nn.functional as F
+
+    def strided(x, begin, end, strides, begin_mask=0, end_mask=0, ellipsis_mask=0, new_axis_mask=0, shrink_axis_mask=0, **kw):
+        b, e, st = _ints(begin), _ints(end), _ints(strides)
+        idx, dim = [], 0
+        for i in range(len(b)):
+            if ellipsis_mask >> i & 1:
+                idx.append(Ellipsis)
+                dim = x.dim() - (len(b) - i - 1 - sum((new_axis_mask >> j) & 1 for j in range(i + 1, len(b))))
+                continue
+            if new_axis_mask >> i & 1:
+                idx.append(None)
+                continue
+            if shrink_axis_mask >> i & 1:
+                idx.append(b[i])
+                dim += 1
+                continue
+            lo = None if begin_mask >> i & 1 else b[i]
+            hi = None if end_mask >> i & 1 else e[i]
+            if st[i] < 0:                      # torch has no negative steps: flip the axis and mirror the bounds
+                n = x.shape[dim]
+                lo2 = 0 if lo is None else n - 1 - (lo if lo >= 0 else n + lo)
+                hi2 = n if hi is None else n - 1 - (hi if hi >= 0 else n + hi)
+                x = x.flip(dim)
+                idx.append(slice(lo2, hi2, -st[i]))
+            else:
+                idx.append(slice(lo, hi, st[i]))
+            dim += 1
+        return x[tuple(idx)]
+
+    def resize(x, size, mode, align_corners=False, half_pixel_centers=False, **kw):
+        h, w = _ints(size)
+        y = x.permute(0, 3, 1, 2).float()
+        if mode == "nearest":
+            if half_pixel_centers or align_corners:
+                y = F.interpolate(y, size=(h, w), mode="nearest-exact" if half_pixel_centers else "nearest")
+            else:
+                ih = (torch.arange(h, device=x.device) * (x.shape[1] / h)).floor().long().clamp(max=x.shape[1] - 1)
+                iw = (torch.arange(w, device=x.device) * (x.shape[2] / w)).floor().long().clamp(max=x.shape[2] - 1)
+                y = y[:, :, ih][:, :, :, iw]
+        elif align_corners:
+            y = F.interpolate(y, size=(h, w), mode="bilinear", align_corners=True)
+        elif half_pixel_centers:
+            y = F.interpolate(y, size=(h, w), mode="bilinear", align_corners=False)
+        else:                                  # TensorFlow 1.x default: source = destination * scale, no half-pixel offset
+            sy, sx = x.shape[1] / h, x.shape[2] / w
+            fy, fx = torch.arange(h, device=x.device) * sy, torch.arange(w, device=x.device) * sx
+            y0, x0 = fy.floor().long().clamp(max=x.shape[1] - 1), fx.floor().long().clamp(max=x.shape[2] - 1)
+            y1, x1 = (y0 + 1).clamp(max=x.shape[1] - 1), (x0 + 1).clamp(max=x.shape[2] - 1)
+            wy, wx = (fy - y0).reshape(1, 1, -1, 1), (fx - x0).reshape(1, 1, 1, -1)
+            top = y[:, :, y0][:, :, :, x0] * (1 - wx) + y[:, :, y0][:, :, :, x1] * wx
+            bot = y[:, :, y1][:, :, :, x0] * (1 - wx) + y[:, :, y1][:, :, :, x1] * wx
+            y = top * (1 - wy) + bot * wy
+        return y.permute(0, 2, 3, 1).to(x.dtype if mode == "nearest" else torch.float32)
+
+    def conv_t(out_shape, w, dy, strides=(1, 1, 1, 1), padding="SAME", data_format="NHWC", **kw):
+        nhwc = data_format == "NHWC"
+        g = dy.permute(0, 3, 1, 2) if nhwc else dy
+        s = (strides[1], strides[2]) if nhwc else (strides[2], strides[3])
+        osz = _ints(out_shape)
+        oh, ow = (osz[1], osz[2]) if nhwc else (osz[2], osz[3])
+        wt = w.permute(3, 2, 0, 1)                   # HWIO (I = output channels of the transpose) -> [in=O, out=I, kh, kw]
+        kh, kw_ = wt.shape[2:]
+        if padding == "SAME":
+            ph = max((g.shape[2] - 1) * s[0] + kh - oh, 0)
+            pw_ = max((g.shape[3] - 1) * s[1] + kw_ - ow, 0)
+            y = F.conv_transpose2d(g, wt.to(g.dtype), None, s, 0)
+            y = y[:, :, ph // 2:ph // 2 + oh, pw_ // 2:pw_ // 2 + ow]
+        else:
+            y = F.conv_transpose2d(g, wt.to(g.dtype), None, s, 0)
+            y = F.pad(y, (0, ow - y.shape[3], 0, oh - y.shape[2]))
+        return y.permute(0, 2, 3, 1) if nhwc else y
+
+    def sd_(x, bs, to_depth, data_format="NHWC", **kw):
+        y = x.permute(0, 3, 1, 2) if data_format == "NHWC" else x
+        if to_depth:                                 # TensorFlow's channel order: (block row, block column, channel)
+            n, c, h, w = y.shape
+            y = y.reshape(n, c, h // bs, bs, w // bs, bs).permute(0, 3, 5, 1, 2, 4).reshape(n, c * bs * bs, h // bs, w // bs)
+        else:
+            n, c, h, w = y.shape
+            y = y.reshape(n, bs, bs, c // (bs * bs), h, w).permute(0, 3, 4, 1, 5, 2).reshape(n, c // (bs * bs), h * bs, w * bs)
+        return y.permute(0, 2, 3, 1) if data_format == "NHWC" else y
+
+    def xent_sparse(logits, labels, **kw):
+        ls = torch.log_softmax(logits.float(), -1)
+        loss = -ls.gather(-1, labels.long().unsqueeze(-1)).squeeze(-1)
+        return loss, torch.softmax(logits.float(), -1) - F.one_hot(labels.long(), logits.shape[-1]).float()
+
+    def xent(logits, labels, **kw):
+        ls = torch.log_softmax(logits.float(), -1)
+        return -(labels * ls).sum(-1), torch.softmax(logits.float(), -1) - labels
+
+    def lrn(x, depth_radius=5, bias=1.0, alpha=1.0, beta=0.5, **kw):
+        sq = (x * x).permute(0, 3, 1, 2)
+        pad = F.pad(sq, (0, 0, 0, 0, depth_radius, depth_radius))
+        win = sum(pad[:, i:i + sq.shape[1]] for i in range(2 * depth_radius + 1))
+        return x / (bias + alpha * win.permute(0, 2, 3, 1)) ** beta
+
+    def gather(x, idx, axis=0, batch_dims=0, **kw):
+        axis = int(axis) % x.dim()
+        if batch_dims:
+            return torch.stack([gather(xb, ib, axis - 1, batch_dims - 1) for xb, ib in zip(x, idx)])
+        return x.index_select(axis, idx.reshape(-1).long()).reshape(*x.shape[:axis], *idx.shape, *x.shape[axis + 1:])
+
+    def gather_nd(x, idx, **kw):
+        idx = idx.long()
+        return x[tuple(idx[..., i] for i in range(idx.shape[-1]))]
+
+    def one_hot(idx, depth, on, off, axis=-1, **kw):
+        d = int(depth)
+        oh = F.one_hot(idx.long().clamp(0, max(d - 1, 0)), d).bool() & ((idx >= 0) & (idx < d)).unsqueeze(-1)
+        y = torch.where(oh, on, off)
+        return y if axis in (-1, idx.dim()) else y.movedim(-1, int(axis))
+
+    def cumsum(x, axis, exclusive=False, reverse=False, **kw):
+        a = int(axis)
+        if reverse:
+            x = x.flip(a)
+        y = x.cumsum(a)
+        if exclusive:
+            y = y - x
+        return y.flip(a) if reverse else y
+
+    def red(fn):
+        def f(x, axis, keep_dims=False, **kw):
+            ax = tuple(_ints(axis))
+            if not ax and isinstance(axis, torch.Tensor) and axis.numel() == 0:
+                return x
+            return fn(x, ax, bool(keep_dims))
+        return f
+
+    def unpack(x, axis=0, num=None, **kw): return tuple(x.unbind(int(axis)))
+    def split(axis, x, num_split=1, **kw): return tuple(x.chunk(int(num_split), int(axis)))
+    def split_v(x, sizes, axis, num_split=None, **kw):
+        sz = _ints(sizes)
+        if -1 in sz:
+            sz[sz.index(-1)] = x.shape[int(axis)] - sum(v for v in sz if v >= 0)
+        return tuple(x.split(sz, int(axis)))
+
+    def pad(x, paddings, value=0.0, mode="constant"):
+        p = paddings.reshape(-1, 2).tolist()
+        if mode == "constant":
+            flat = []
+            for lo, hi in reversed(p):
+                flat += [int(lo), int(hi)]
+            return F.pad(x, flat, value=float(value))
+        y = x
+        for d, (lo, hi) in enumerate(p):           # REFLECT excludes the border element, SYMMETRIC repeats it
+            lo, hi, n = int(lo), int(hi), y.shape[d]
+            off = 1 if mode == "reflect" else 0
+            front = y.narrow(d, off, lo).flip(d) if lo else None
+            back = y.narrow(d, n - hi - off, hi).flip(d) if hi else None
+            y = torch.cat([t for t in (front, y, back) if t is not None], d)
+        return y
+
+    def bmm(x, y, adj_x=False, adj_y=False, **kw):
+        return torch.matmul(x.transpose(-1, -2) if adj_x else x, y.transpose(-1, -2) if adj_y else y)
+
+    T = {
+        "Less": (lambda a, b, **k: a < b, 1), "LessEqual": (lambda a, b, **k: a <= b, 1), "Greater": (lambda a, b, **k: a > b, 1),
+        "GreaterEqual": (lambda a, b, **k: a >= b, 1), "Equal": (lambda a, b, **k: a == b, 1), "NotEqual": (lambda a, b, **k: a != b, 1),
+        "LogicalAnd": (lambda a, b, **k: a & b, 1), "LogicalOr": (lambda a, b, **k: a | b, 1), "LogicalNot": (lambda a, **k: ~a, 1),
+        "Select": (lambda c, a, b, **k: torch.where(c.reshape(list(c.shape) + [1] * (a.dim() - c.dim())) if c.dim() < a.dim() else c, a, b), 1),
+        "SelectV2": (lambda c, a, b, **k: torch.where(c, a, b), 1),
+        "FloorDiv": (lambda a, b, **k: torch.div(a, b, rounding_mode="floor"), 1), "FloorMod": (lambda a, b, **k: torch.remainder(a, b), 1),
+        "Mod": (lambda a, b, **k: torch.fmod(a, b), 1), "TruncateDiv": (lambda a, b, **k: torch.div(a, b, rounding_mode="trunc"), 1),
+        "Range": (lambda a, b, c, **k: torch.arange(a.item(), b.item(), c.item(), dtype=a.dtype, device=a.device), 1),
+        "Fill": (lambda sh, v, **k: torch.full(_ints(sh), v.item(), dtype=v.dtype, device=v.device), 1),
+        "ZerosLike": (lambda x, **k: torch.zeros_like(x), 1), "OnesLike": (lambda x, **k: torch.ones_like(x), 1),
+        "Tile": (lambda x, m, **k: x.repeat(*_ints(m)), 1),
+        "Slice": (lambda x, b, sz, **k: x[tuple(slice(bi, None if si < 0 else bi + si) for bi, si in zip(_ints(b), _ints(sz)))], 1),
+        "StridedSlice": (strided, 1), "Split": (split, -1), "SplitV": (split_v, -1), "Unpack": (unpack, -1),
+        "Gather": (lambda x, i, **k: gather(x, i, 0), 1), "GatherV2": (lambda x, i, ax, batch_dims=0, **k: gather(x, i, int(ax), batch_dims), 1),
+        "GatherNd": (gather_nd, 1), "OneHot": (one_hot, 1),
+        "TopKV2": (lambda x, kk, sorted=True, **k: tuple(t if j == 0 else t.to(torch.int32) for j, t in enumerate(torch.topk(x, int(kk), sorted=True))), 2),
+        "Cumsum": (cumsum, 1), "Cumprod": (lambda x, ax, **k: x.cumprod(int(ax)), 1),
+        "Sin": (lambda x, **k: x.sin(), 1), "Cos": (lambda x, **k: x.cos(), 1), "Tan": (lambda x, **k: x.tan(), 1),
+        "Asin": (lambda x, **k: x.asin(), 1), "Acos": (lambda x, **k: x.acos(), 1), "Atan": (lambda x, **k: x.atan(), 1),
+        "Sinh": (lambda x, **k: x.sinh(), 1), "Cosh": (lambda x, **k: x.cosh(), 1), "Atan2": (lambda a, b, **k: torch.atan2(a, b), 1),
+        "Ceil": (lambda x, **k: x.ceil(), 1), "Round": (lambda x, **k: x.round(), 1), "Rint": (lambda x, **k: x.round(), 1),
+        "Sign": (lambda x, **k: x.sign(), 1), "Reciprocal": (lambda x, **k: 1.0 / x, 1), "Inv": (lambda x, **k: 1.0 / x, 1),
+        "Log1p": (lambda x, **k: x.log1p(), 1), "Expm1": (lambda x, **k: x.expm1(), 1), "Softsign": (lambda x, **k: x / (1 + x.abs()), 1),
+        "IsNan": (lambda x, **k: x.isnan(), 1), "IsInf": (lambda x, **k: x.isinf(), 1), "IsFinite": (lambda x, **k: x.isfinite(), 1),
+        "Size": (lambda x, **k: torch.tensor(x.numel(), dtype=torch.int32), 1), "Rank": (lambda x, **k: torch.tensor(x.dim(), dtype=torch.int32), 1),
+        "ArgMin": (lambda x, ax, **k: x.argmin(int(ax)), 1),
+        "All": (red(lambda x, ax, kd: x.all(ax[0], kd) if len(ax) == 1 else x.float().amin(ax, kd).bool()), 1),
+        "Any": (red(lambda x, ax, kd: x.any(ax[0], kd) if len(ax) == 1 else x.float().amax(ax, kd).bool()), 1),
+        "BatchMatMul": (bmm, 1), "BatchMatMulV2": (bmm, 1), "AddN": (lambda *xs, **k: torch.stack(xs).sum(0), 1),
+        "Conv2DBackpropInput": (conv_t, 1),
+        "ResizeBilinear": (lambda x, sz, **k: resize(x, sz, "bilinear", **k), 1),
+        "ResizeNearestNeighbor": (lambda x, sz, **k: resize(x, sz, "nearest", **k), 1),
+        "SpaceToDepth": (lambda x, block_size=2, data_format="NHWC", **k: sd_(x, int(block_size), True, data_format), 1),
+        "DepthToSpace": (lambda x, block_size=2, data_format="NHWC", **k: sd_(x, int(block_size), False, data_format), 1),
+        "PadV2": (lambda x, p, v, **k: pad(x, p, v.item()), 1),
+        "MirrorPad": (lambda x, p, mode="REFLECT", **k: pad(x, p, mode=mode.lower()), 1),
+        "ReverseV2": (lambda x, ax, **k: x.flip(_ints(ax)), 1),
+        "ClipByValue": (lambda x, lo, hi, **k: torch.minimum(torch.maximum(x, lo), hi), 1),
+        "L2Loss": (lambda x, **k: (x * x).sum() / 2, 1), "LRN": (lrn, 1),
+        "IdentityN": (lambda *xs, **k: tuple(xs), -1), "Snapshot": (lambda x, **k: x, 1), "PreventGradient": (lambda x, **k: x.detach(), 1),
+        "SparseSoftmaxCrossEntropyWithLogits": (xent_sparse, 2), "SoftmaxCrossEntropyWithLogits": (xent, 2),
+        "Where": (lambda c, **k: c.nonzero(), 1), "Swish": (lambda x, **k: x * torch.sigmoid(x), 1),
+        "BroadcastTo": (lambda x, sh, **k: x.broadcast_to(_ints(sh)), 1), "Einsum": (lambda *xs, equation="", **k: torch.einsum(equation, *xs), 1),
+        "MatrixDiag": (lambda x, **k: torch.diag_embed(x), 1), "MatrixDiagPart": (lambda x, **k: torch.diagonal(x, dim1=-2, dim2=-1), 1),
+        "Tanh": (lambda x, **k: x.tanh(), 1),
+    }
+    return T
+
+
+def _register_tf_ops():
+    from ..ops.registry import has, op
+    if has("tf.Less"):
+        return
+    for name, (fn, n_out) in _tf_ops().items():
+        op("tf." + name, n_out=n_out, group="tf_import")(fn)
+
+
 def _base(name):
     name = name[1:] if name.startswith("^") else name
     return name.split(":")[0], int(name.split(":")[1]) if ":" in name else 0
@@ -163,32 +386,75 @@ class TensorflowFrameworkImporter:
     def __init__(self, trainable=False):
         self.trainable = trainable
 
+    # ops with dedicated rules below (they map onto the framework's own ops so that its fusions and kernels apply)
+    _DIRECT = {"Const", "Placeholder", "PlaceholderWithDefault", "MatMul", "BiasAdd", "Conv2D", "DepthwiseConv2dNative", "MaxPool", "AvgPool", "Reshape",
+               "Softmax", "LogSoftmax", "Squeeze", "ExpandDims", "ConcatV2", "Transpose", "FusedBatchNorm", "FusedBatchNormV3", "Pad", "Cast", "LeakyRelu",
+               "NoOp", "Shape", "Pack", "ArgMax"}
+    # TensorFlow 1.x control flow: the same dataflow primitives the SameDiff executor runs (frames, dead branches)
+    _CONTROL = {"Enter": "enter", "RefEnter": "enter", "Exit": "exit", "RefExit": "exit", "Switch": "switch", "RefSwitch": "switch",
+                "Merge": "merge", "RefMerge": "merge", "NextIteration": "next_iteration", "RefNextIteration": "next_iteration", "LoopCond": "loop_cond"}
+    # TensorArray ops -> the list ops of the framework
+    _TENSOR_ARRAY = {"TensorArrayV3": "tensorarrayv3", "TensorArrayWriteV3": "tensorarraywritev3", "TensorArrayReadV3": "tensorarrayreadv3",
+                     "TensorArrayGatherV3": "tensorarraygatherv3", "TensorArrayScatterV3": "tensorarrayscatterv3", "TensorArraySizeV3": "tensorarraysizev3",
+                     "TensorArrayConcatV3": "tensorarrayconcatv3", "TensorArraySplitV3": "tensorarraysplitv3"}
+
+    @classmethod
+    def supportedOps(cls):
+        from ..ops import registry
+        ta = {k for k, v in cls._TENSOR_ARRAY.items() if registry.has(v)}
+        return sorted(set(cls.UNARY) | set(cls.BINARY) | set(cls.REDUCE) | cls._DIRECT | set(cls._CONTROL) | ta | set(_tf_ops()))
+
     def runImport(self, path_or_bytes, dynamicVariables=None):
         _register_helpers()
+        _register_tf_ops()
+        from ..ops import registry
         if isinstance(path_or_bytes, (bytes, bytearray, memoryview)):
             data = path_or_bytes
         else:
             with open(path_or_bytes, "rb") as f:
                 data = f.read()
         nodes = parse_graphdef(data)
-        known = set(self.UNARY) | set(self.BINARY) | set(self.REDUCE) | {"Const", "Placeholder", "PlaceholderWithDefault", "MatMul", "BiasAdd", "Conv2D", "DepthwiseConv2dNative", "MaxPool", "AvgPool", "Reshape", "Softmax",
-                                                                           "LogSoftmax", "Squeeze", "ExpandDims", "ConcatV2", "Transpose", "FusedBatchNorm", "FusedBatchNormV3", "Pad", "Cast",
-                                                                           "LeakyRelu", "NoOp", "Shape", "Pack", "StridedSlice", "GatherV2", "ArgMax"}
+        known = set(self.supportedOps())
         unsupported = sorted({n["op"] for n in nodes if n["op"] not in known})
         if unsupported:
             raise NotImplementedError(f"TensorFlow import: no mapping rule for op types {unsupported}")
+        generic = _tf_ops()
         sd = SameDiff.create()
-        vars_, consts = {}, {}
+        vars_, consts, patches = {}, {}, []          # vars_: (node name, output index) -> SDVariable
+
+        def put(name, out):
+            outs = list(out) if isinstance(out, (list, tuple)) else [out]
+            for k, v in enumerate(outs):
+                vars_[(name, k)] = v
+
+        def ref(s):
+            nm, idx = _base(s)
+            return vars_.get((nm, idx))
 
         def inp(n, i):
-            nm, idx = _base(n["inputs"][i])
-            return vars_[nm]
+            v = ref(n["inputs"][i])
+            if v is None:
+                raise ValueError(f"TensorFlow import: input {n['inputs'][i]!r} of {n['name']} is produced later in the file and is not a loop back edge")
+            return v
 
         def cval(n, i):
             nm, _ = _base(n["inputs"][i])
             if nm not in consts:
                 raise ValueError(f"TensorFlow import: input {i} of {n['name']} ({n['op']}) must be a constant")
             return consts[nm]
+
+        def plain(a):
+            out = {}
+            for k, v in a.items():
+                if k in ("T", "Tidx", "Tshape", "Tparams", "Tindices", "Tperm", "Tpaddings", "TI", "Taxis", "Index", "out_type", "_output_shapes", "_class",
+                         "Tlen", "Tmultiples", "Tlabels", "output_type", "N", "dtype", "element_shape", "clear_after_read", "dynamic_size",
+                         "identical_element_shapes", "tensor_array_name", "parallel_iterations", "validate_indices", "use_cudnn_on_gpu",
+                         "explicit_paddings", "U", "is_training", "exponential_avg_factor"):
+                    continue
+                if isinstance(v, tuple) or isinstance(v, torch.Tensor) or v is None:
+                    continue
+                out[k] = list(v) if isinstance(v, list) else v
+            return out
         for n in nodes:
             op_, a, name = n["op"], n["attrs"], n["name"]
             data_in = [i for i in n["inputs"] if not i.startswith("^")]
@@ -198,62 +464,102 @@ class TensorflowFrameworkImporter:
             if op_ == "Const":
                 t = a["value"]
                 consts[name] = t
-                vars_[name] = sd.var(name, t.clone()) if (self.trainable and t.is_floating_point() and t.dim() >= 1) else sd.constant(name, t.clone())
+                put(name, sd.var(name, t.clone()) if (self.trainable and t.is_floating_point() and t.dim() >= 1) else sd.constant(name, t.clone()))
             elif op_ in ("Placeholder", "PlaceholderWithDefault"):
                 dt = _TF_TO_DT.get(a.get("dtype", ("dtype", 1))[1], DataType.FLOAT)
                 shp = a.get("shape", ("shape", None))[1]
-                vars_[name] = sd.placeHolder(name, dt, *(shp or []))
+                put(name, sd.placeHolder(name, dt, *(shp or [])))
+            elif op_ in self._CONTROL:
+                kind = self._CONTROL[op_]
+                if kind == "enter":
+                    put(name, sd._op("enter", [inp(n, 0)], name=name, frameName=a.get("frame_name", "frame"), isConstant=bool(a.get("is_constant", False))))
+                elif kind == "merge":
+                    have = [ref(i) for i in n["inputs"]]
+                    first = next(v for v in have if v is not None)
+                    m = sd._op("merge", [v if v is not None else first for v in have], name=name)
+                    node = sd._producer[m.name]
+                    for k, v in enumerate(have):
+                        if v is None:
+                            patches.append((node, k, n["inputs"][k]))           # the back edge: filled in once NextIteration exists
+                    put(name, m)
+                elif kind == "switch":
+                    put(name, sd._op("switch", [inp(n, 0), inp(n, 1)], name=name))
+                else:
+                    put(name, sd._op(kind, [inp(n, 0)], name=name))
+            elif op_ in self._TENSOR_ARRAY:
+                target = self._TENSOR_ARRAY[op_]
+                put(name, sd._op(target, [inp(n, i) for i in range(len(n["inputs"]))], name=name, n_out=registry.get(target).n_out))
             elif op_ in self.UNARY:
-                vars_[name] = sd._op(self.UNARY[op_], [inp(n, 0)], name=name)
+                put(name, sd._op(self.UNARY[op_], [inp(n, 0)], name=name))
             elif op_ in self.BINARY:
-                vars_[name] = sd._op(self.BINARY[op_], [inp(n, 0), inp(n, 1)], name=name)
-            elif op_ in self.REDUCE:
+                put(name, sd._op(self.BINARY[op_], [inp(n, 0), inp(n, 1)], name=name))
+            elif op_ in self.REDUCE and _base(n["inputs"][1])[0] in consts:
                 ax = cval(n, 1).reshape(-1).tolist()
-                vars_[name] = sd._op(self.REDUCE[op_], [inp(n, 0)], name=name, dimensions=[int(v) for v in ax], keepDims=bool(a.get("keep_dims", False)))
+                put(name, sd._op(self.REDUCE[op_], [inp(n, 0)], name=name, dimensions=[int(v) for v in ax], keepDims=bool(a.get("keep_dims", False))))
             elif op_ == "MatMul":
-                vars_[name] = sd._op("matmul", [inp(n, 0), inp(n, 1)], name=name, transposeX=bool(a.get("transpose_a", False)), transposeY=bool(a.get("transpose_b", False)))
+                put(name, sd._op("matmul", [inp(n, 0), inp(n, 1)], name=name, transposeX=bool(a.get("transpose_a", False)), transposeY=bool(a.get("transpose_b", False))))
             elif op_ == "BiasAdd":
-                vars_[name] = sd._op("tf_bias_add", [inp(n, 0), inp(n, 1)], name=name, data_format=a.get("data_format", "NHWC"))
+                put(name, sd._op("tf_bias_add", [inp(n, 0), inp(n, 1)], name=name, data_format=a.get("data_format", "NHWC")))
             elif op_ in ("Conv2D", "DepthwiseConv2dNative"):
-                vars_[name] = sd._op("tf_conv2d", [inp(n, 0), inp(n, 1)], name=name, strides=list(a.get("strides", [1, 1, 1, 1])), padding=a.get("padding", "SAME"),
-                                     dilations=list(a.get("dilations", [1, 1, 1, 1])), data_format=a.get("data_format", "NHWC"), depthwise=op_ != "Conv2D")
+                put(name, sd._op("tf_conv2d", [inp(n, 0), inp(n, 1)], name=name, strides=list(a.get("strides", [1, 1, 1, 1])), padding=a.get("padding", "SAME"),
+                                 dilations=list(a.get("dilations", [1, 1, 1, 1])), data_format=a.get("data_format", "NHWC"), depthwise=op_ != "Conv2D"))
             elif op_ in ("MaxPool", "AvgPool"):
-                vars_[name] = sd._op("tf_pool", [inp(n, 0)], name=name, kind="max" if op_ == "MaxPool" else "avg", ksize=list(a["ksize"]), strides=list(a["strides"]),
-                                     padding=a.get("padding", "VALID"), data_format=a.get("data_format", "NHWC"))
+                put(name, sd._op("tf_pool", [inp(n, 0)], name=name, kind="max" if op_ == "MaxPool" else "avg", ksize=list(a["ksize"]), strides=list(a["strides"]),
+                                 padding=a.get("padding", "VALID"), data_format=a.get("data_format", "NHWC")))
+            elif op_ == "Reshape" and _base(n["inputs"][1])[0] in consts:
+                put(name, sd._op("reshape", [inp(n, 0)], name=name, shape=[int(v) for v in cval(n, 1).reshape(-1).tolist()]))
             elif op_ == "Reshape":
-                vars_[name] = sd._op("reshape", [inp(n, 0)], name=name, shape=[int(v) for v in cval(n, 1).reshape(-1).tolist()])
+                put(name, sd._op("reshape", [inp(n, 0), inp(n, 1)], name=name))
             elif op_ in ("Softmax", "LogSoftmax"):
-                vars_[name] = sd._op("softmax" if op_ == "Softmax" else "log_softmax", [inp(n, 0)], name=name, dimension=-1)
+                put(name, sd._op("softmax" if op_ == "Softmax" else "log_softmax", [inp(n, 0)], name=name, dimension=-1))
             elif op_ == "Squeeze":
                 dims = a.get("squeeze_dims") or None
-                vars_[name] = sd._op("squeeze", [inp(n, 0)], name=name, dimensions=None if not dims else [int(v) for v in dims])
+                put(name, sd._op("squeeze", [inp(n, 0)], name=name, dimensions=None if not dims else [int(v) for v in dims]))
             elif op_ == "ExpandDims":
-                vars_[name] = sd._op("expand_dims", [inp(n, 0)], name=name, axis=int(cval(n, 1)))
+                put(name, sd._op("expand_dims", [inp(n, 0)], name=name, axis=int(cval(n, 1))))
             elif op_ == "ConcatV2":
-                vars_[name] = sd._op("concat", [inp(n, i) for i in range(len(n["inputs"]) - 1)], name=name, concatDimension=int(cval(n, len(n["inputs"]) - 1)))
+                put(name, sd._op("concat", [inp(n, i) for i in range(len(n["inputs"]) - 1)], name=name, concatDimension=int(cval(n, len(n["inputs"]) - 1))))
             elif op_ == "Pack":
-                vars_[name] = sd._op("stack", [inp(n, i) for i in range(len(n["inputs"]))], name=name, axis=int(a.get("axis", 0)))
+                put(name, sd._op("stack", [inp(n, i) for i in range(len(n["inputs"]))], name=name, axis=int(a.get("axis", 0))))
             elif op_ == "Transpose":
-                vars_[name] = sd._op("permute", [inp(n, 0)], name=name, dimensions=[int(v) for v in cval(n, 1).tolist()])
+                put(name, sd._op("permute", [inp(n, 0)], name=name, dimensions=[int(v) for v in cval(n, 1).tolist()]))
             elif op_ in ("FusedBatchNorm", "FusedBatchNormV3"):
-                vars_[name] = sd._op("tf_fused_batchnorm", [inp(n, i) for i in range(5)], name=name, epsilon=float(a.get("epsilon", 1e-3)), data_format=a.get("data_format", "NHWC"))
+                put(name, sd._op("tf_fused_batchnorm", [inp(n, i) for i in range(5)], name=name, epsilon=float(a.get("epsilon", 1e-3)), data_format=a.get("data_format", "NHWC")))
             elif op_ == "Pad":
-                vars_[name] = sd._op("pad", [inp(n, 0)], name=name, paddings=cval(n, 1).tolist(), mode="CONSTANT", constant=0.0)
+                put(name, sd._op("pad", [inp(n, 0)], name=name, paddings=cval(n, 1).tolist(), mode="CONSTANT", constant=0.0))
             elif op_ == "Cast":
-                vars_[name] = sd._op("cast", [inp(n, 0)], name=name, dtype=int(_TF_TO_DT.get(a["DstT"][1], DataType.FLOAT)))
+                put(name, sd._op("cast", [inp(n, 0)], name=name, dtype=int(_TF_TO_DT.get(a["DstT"][1], DataType.FLOAT))))
             elif op_ == "LeakyRelu":
-                vars_[name] = sd._op("leakyrelu", [inp(n, 0)], name=name, alpha=float(a.get("alpha", 0.2)))
+                put(name, sd._op("leakyrelu", [inp(n, 0)], name=name, alpha=float(a.get("alpha", 0.2))))
             elif op_ == "Shape":
-                vars_[name] = sd._op("shape_of", [inp(n, 0)], name=name)
-            elif op_ == "GatherV2":
-                vars_[name] = sd._op("gather", [inp(n, 0), inp(n, 1)], name=name, axis=int(cval(n, 2)))
+                put(name, sd._op("shape_of", [inp(n, 0)], name=name))
             elif op_ == "ArgMax":
-                vars_[name] = sd._op("argmax", [inp(n, 0)], name=name, dimensions=[int(cval(n, 1))])
-            elif op_ == "StridedSlice":
-                b, e, s = (cval(n, i).reshape(-1).tolist() for i in (1, 2, 3))
-                vars_[name] = sd._op("strided_slice", [inp(n, 0)], name=name, begin=[int(v) for v in b], end=[int(v) for v in e], strides=[int(v) for v in s],
-                                     beginMask=int(a.get("begin_mask", 0)), endMask=int(a.get("end_mask", 0)), ellipsisMask=int(a.get("ellipsis_mask", 0)),
-                                     newAxisMask=int(a.get("new_axis_mask", 0)), shrinkAxisMask=int(a.get("shrink_axis_mask", 0)))
+                put(name, sd._op("argmax", [inp(n, 0)], name=name, dimensions=[int(cval(n, 1))]))
+            elif op_ in self.REDUCE:              # reduction whose axes are computed in the graph
+                fn = {"Mean": "mean", "Sum": "sum", "Max": "amax", "Min": "amin", "Prod": "prod"}[op_]
+                if not registry.has("tf.Reduce" + fn):
+                    def mk(fn=fn):
+                        def f(x, axis, keep_dims=False, **kw):
+                            ax = tuple(_ints(axis))
+                            if fn == "prod":
+                                for d in sorted((v % x.dim() for v in ax), reverse=True):
+                                    x = x.prod(d, keepdim=bool(keep_dims))
+                                return x
+                            return getattr(x, fn)(ax, keepdim=bool(keep_dims))
+                        return f
+                    registry.op("tf.Reduce" + fn, group="tf_import")(mk())
+                put(name, sd._op("tf.Reduce" + fn, [inp(n, 0), inp(n, 1)], name=name, keep_dims=bool(a.get("keep_dims", False))))
+            else:
+                fn, n_out = generic[op_]
+                if n_out == -1:
+                    n_out = int(a.get("num_split") or a.get("num") or len(n["inputs"]))
+                put(name, sd._op("tf." + op_, [inp(n, i) for i in range(len(n["inputs"]))], name=name, n_out=n_out, **plain(a)))
+        for node, k, src in patches:
+            v = ref(src)
+            if v is None:
+                raise ValueError(f"TensorFlow import: merge input {src!r} is never produced")
+            node.inputs[k] = v.name
+        sd._exec_plan = None
         consumed = {_base(i)[0] for n in nodes for i in n["inputs"]}
         self.outputs = [n["name"] for n in nodes if n["name"] not in consumed and n["op"] not in ("Const", "Placeholder", "NoOp")]
         return sd

@@ -88,3 +88,81 @@ def test_elementwise_shape_ops_and_unsupported():
         assert False
     except NotImplementedError as e:
         assert "NonMaxSuppressionXYZ" in str(e)
+
+
+def test_generic_rules_against_torch():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 4, 6, 6, generator=g)
+    Wt = torch.randn(4, 3, 3, 3, generator=g) * 0.2
+    i64 = np.int64
+    nodes = [
+        node("Less", ["x", "zero"], ["lt"]), node("Where", ["lt", "zero", "x"], ["relu_like"]),
+        node("ReduceL2", ["x"], ["l2"], axes=[1], keepdims=0), node("ReduceLogSumExp", ["x", "ax23"], ["lse"], keepdims=1),
+        node("TopK", ["x", "k"], ["tv", "ti"], axis=3, largest=1), node("Split", ["x", "sizes"], ["s0", "s1"], axis=1),
+        node("Pad", ["x", "pads"], ["pd"], mode="reflect"), node("DepthToSpace", ["x"], ["d2s"], blocksize=2, mode="CRD"),
+        node("SpaceToDepth", ["x"], ["s2d"], blocksize=2), node("ConvTranspose", ["x", "Wt"], ["ct"], strides=[2, 2], pads=[1, 1, 1, 1], output_padding=[1, 1]),
+        node("InstanceNormalization", ["x", "isc", "ibi"], ["inn"], epsilon=1e-5), node("CumSum", ["x", "ax3"], ["cs"], reverse=1),
+        node("Expand", ["isc", "eshape"], ["ex"]), node("HardSwish", ["x"], ["hs"]), node("Mod", ["x", "two"], ["md"], fmod=1),
+        node("Resize", ["x", "", "scales"], ["rz"], mode="nearest", coordinate_transformation_mode="asymmetric", nearest_mode="floor"),
+        node("ArgMax", ["x"], ["am"], axis=1, keepdims=0), node("GatherElements", ["x", "gidx"], ["ge"], axis=3),
+        node("Max", ["x", "zero", "isc4"], ["mx"]), node("Trilu", ["x"], ["tri"], upper=0),
+    ]
+    inits = [tensor("zero", np.zeros((), np.float32)), tensor("ax23", np.asarray([2, 3], i64)), tensor("k", np.asarray([2], i64)),
+             tensor("sizes", np.asarray([1, 3], i64)), tensor("pads", np.asarray([0, 0, 1, 2, 0, 0, 2, 1], i64)), tensor("Wt", Wt.numpy()),
+             tensor("isc", np.asarray([1.0, 2.0, 0.5, -1.0], np.float32)), tensor("ibi", np.asarray([0.0, 1.0, -1.0, 0.5], np.float32)),
+             tensor("ax3", np.asarray(3, i64)), tensor("eshape", np.asarray([2, 3, 1], i64)), tensor("two", np.asarray(2.0, np.float32)),
+             tensor("scales", np.asarray([1.0, 1.0, 2.0, 2.0], np.float32)), tensor("gidx", np.asarray(np.random.RandomState(0).randint(-6, 6, (2, 4, 6, 2)), i64)),
+             tensor("isc4", np.asarray([1.0, 2.0, 0.5, -1.0], np.float32).reshape(4, 1, 1))]
+    outs = ["relu_like", "l2", "lse", "tv", "ti", "s0", "s1", "pd", "d2s", "s2d", "ct", "inn", "cs", "ex", "hs", "md", "rz", "am", "ge", "mx", "tri"]
+    raw = model(nodes, inits, [("x", [2, 4, 6, 6])], [(o, []) for o in outs])
+    sd = OnnxFrameworkImporter(trainable=False).runImport(raw)
+    r = {k: v.t for k, v in sd.output({"x": x}, *outs).items()}
+    assert torch.equal(r["relu_like"], torch.where(x < 0, torch.zeros(()), x))
+    assert torch.allclose(r["l2"], x.pow(2).sum(1).sqrt()) and torch.allclose(r["lse"], x.logsumexp((2, 3), keepdim=True))
+    tv, ti = torch.topk(x, 2, dim=3)
+    assert torch.equal(r["tv"], tv) and torch.equal(r["ti"], ti)
+    assert torch.equal(r["s0"], x[:, :1]) and torch.equal(r["s1"], x[:, 1:])
+    assert torch.equal(r["pd"], F.pad(x, (2, 1, 1, 2), mode="reflect"))
+    assert torch.equal(r["d2s"], F.pixel_shuffle(x, 2)) and torch.equal(F.pixel_shuffle(r["s2d"].reshape(2, 2, 2, 4, 3, 3).permute(0, 3, 1, 2, 4, 5).reshape(2, 16, 3, 3), 2), x)
+    assert torch.allclose(r["ct"], F.conv_transpose2d(x, Wt, stride=2, padding=1, output_padding=1), atol=1e-5)
+    isc, ibi = torch.tensor([1.0, 2.0, 0.5, -1.0]), torch.tensor([0.0, 1.0, -1.0, 0.5])
+    assert torch.allclose(r["inn"], F.instance_norm(x, weight=isc, bias=ibi, eps=1e-5), atol=1e-5)
+    assert torch.allclose(r["cs"], x.flip(3).cumsum(3).flip(3), atol=1e-6)
+    assert tuple(r["ex"].shape) == (2, 3, 4) and torch.equal(r["ex"][1, 2], isc)
+    assert torch.allclose(r["hs"], F.hardswish(x), atol=1e-6) and torch.allclose(r["md"], torch.fmod(x, 2.0))
+    assert torch.equal(r["rz"], x.repeat_interleave(2, 2).repeat_interleave(2, 3))
+    assert torch.equal(r["am"], x.argmax(1))
+    gi = torch.from_numpy(np.random.RandomState(0).randint(-6, 6, (2, 4, 6, 2)))
+    assert torch.equal(r["ge"], x.gather(3, torch.where(gi < 0, gi + 6, gi)))
+    assert torch.equal(r["mx"], torch.maximum(x.clamp_min(0), isc.reshape(4, 1, 1))) and torch.equal(r["tri"], torch.tril(x))
+
+
+def test_lstm_and_gru_nodes_match_torch_modules():
+    torch.manual_seed(0)
+    T, N, I, H = 5, 3, 4, 6
+    x = torch.randn(T, N, I)
+    lstm = torch.nn.LSTM(I, H, bidirectional=True)
+    gru = torch.nn.GRU(I, H)
+
+    def reorder(w, order):            # torch gate blocks -> ONNX gate blocks along dim 0
+        blocks = w.detach().chunk(len(order), 0)
+        return torch.cat([blocks[i] for i in order], 0)
+    io = [0, 3, 1, 2]                 # torch (i, f, g, o) -> ONNX (i, o, f, c)
+    W = torch.stack([reorder(lstm.weight_ih_l0, io), reorder(lstm.weight_ih_l0_reverse, io)])
+    R = torch.stack([reorder(lstm.weight_hh_l0, io), reorder(lstm.weight_hh_l0_reverse, io)])
+    B = torch.stack([torch.cat([reorder(lstm.bias_ih_l0, io), reorder(lstm.bias_hh_l0, io)]),
+                     torch.cat([reorder(lstm.bias_ih_l0_reverse, io), reorder(lstm.bias_hh_l0_reverse, io)])])
+    go = [1, 0, 2]                    # torch (r, z, n) -> ONNX (z, r, h)
+    Wg, Rg = reorder(gru.weight_ih_l0, go).unsqueeze(0), reorder(gru.weight_hh_l0, go).unsqueeze(0)
+    Bg = torch.cat([reorder(gru.bias_ih_l0, go), reorder(gru.bias_hh_l0, go)]).unsqueeze(0)
+    nodes = [node("LSTM", ["x", "W", "R", "B"], ["Y", "Yh", "Yc"], hidden_size=H, direction="bidirectional"),
+             node("GRU", ["x", "Wg", "Rg", "Bg"], ["G", "Gh"], hidden_size=H, linear_before_reset=1)]
+    inits = [tensor(n, t.numpy()) for n, t in (("W", W), ("R", R), ("B", B), ("Wg", Wg), ("Rg", Rg), ("Bg", Bg))]
+    raw = model(nodes, inits, [("x", [T, N, I])], [("Y", []), ("Yh", []), ("Yc", []), ("G", []), ("Gh", [])])
+    sd = OnnxFrameworkImporter(trainable=False).runImport(raw)
+    r = {k: v.t for k, v in sd.output({"x": x}, "Y", "Yh", "Yc", "G", "Gh").items()}
+    y, (h, c) = lstm(x)
+    assert torch.allclose(r["Y"].permute(0, 2, 1, 3).reshape(T, N, 2 * H), y, atol=1e-5)
+    assert torch.allclose(r["Yh"], h, atol=1e-5) and torch.allclose(r["Yc"], c, atol=1e-5)
+    yg, hg = gru(x)
+    assert torch.allclose(r["G"][:, 0], yg, atol=1e-5) and torch.allclose(r["Gh"], hg, atol=1e-5)

@@ -26,6 +26,10 @@ def tf_attr(v):
         return pw.field_varint(5, int(v))
     if isinstance(v, str):
         return pw.field_bytes(2, v.encode())
+    if isinstance(v, int):
+        return pw.field_varint(3, v)
+    if isinstance(v, float):
+        return pw.field_float(4, v)
     if isinstance(v, list):
         return pw.field_bytes(1, pw.field_packed_varints(3, v))
     if isinstance(v, tuple) and v[0] == "dtype":
@@ -143,3 +147,104 @@ def test_keras_functional_residual_and_errors():
         KerasModelImport.importKerasSequentialModelAndWeights(_seq_json([{"class_name": "Lambda", "config": {"name": "l", "batch_input_shape": [None, 3]}}]))
     with pytest.raises(UnsupportedKerasConfigurationException, match="h5py"):
         KerasModelImport.importKerasSequentialModelAndWeights(_seq_json([{"class_name": "Dense", "config": {"name": "d", "units": 2, "batch_input_shape": [None, 3]}}]), "weights.h5")
+
+
+def _c(name, arr):
+    return tf_node(name, "Const", value=np.asarray(arr))
+
+
+def test_tensorflow_while_loop_control_flow_import():
+    """A TensorFlow 1.x while loop (Enter / Merge / LoopCond / Switch / Identity / NextIteration / Exit, with the back edge
+    referring to a node that comes later in the file):  i = 0, acc = x;  while i < n: acc = acc * 2 + i; i += 1."""
+    f32, i32 = np.float32, np.int32
+    graph = b"".join([
+        tf_node("x", "Placeholder", dtype=("dtype", 1), shape=("shape", [3])),
+        _c("zero", np.asarray(0, i32)), _c("n", np.asarray(5, i32)), _c("one", np.asarray(1, i32)), _c("two", np.asarray(2.0, f32)),
+        tf_node("while/Enter", "Enter", ["zero"], frame_name="while/ctx", is_constant=False),
+        tf_node("while/Enter_1", "Enter", ["x"], frame_name="while/ctx", is_constant=False),
+        tf_node("while/n", "Enter", ["n"], frame_name="while/ctx", is_constant=True),
+        tf_node("while/one", "Enter", ["one"], frame_name="while/ctx", is_constant=True),
+        tf_node("while/two", "Enter", ["two"], frame_name="while/ctx", is_constant=True),
+        tf_node("while/Merge", "Merge", ["while/Enter", "while/NextIteration"]),
+        tf_node("while/Merge_1", "Merge", ["while/Enter_1", "while/NextIteration_1"]),
+        tf_node("while/Less", "Less", ["while/Merge", "while/n"]),
+        tf_node("while/LoopCond", "LoopCond", ["while/Less"]),
+        tf_node("while/Switch", "Switch", ["while/Merge", "while/LoopCond"]),
+        tf_node("while/Switch_1", "Switch", ["while/Merge_1", "while/LoopCond"]),
+        tf_node("while/Identity", "Identity", ["while/Switch:1"]),
+        tf_node("while/Identity_1", "Identity", ["while/Switch_1:1"]),
+        tf_node("while/mul", "Mul", ["while/Identity_1", "while/two"]),
+        tf_node("while/cast", "Cast", ["while/Identity"], DstT=("dtype", 1)),
+        tf_node("while/acc", "AddV2", ["while/mul", "while/cast"]),
+        tf_node("while/inc", "AddV2", ["while/Identity", "while/one"]),
+        tf_node("while/NextIteration", "NextIteration", ["while/inc"]),
+        tf_node("while/NextIteration_1", "NextIteration", ["while/acc"]),
+        tf_node("while/Exit", "Exit", ["while/Switch"]),
+        tf_node("while/Exit_1", "Exit", ["while/Switch_1:0"]),
+        tf_node("out", "Identity", ["while/Exit_1"])])
+    imp = TensorflowFrameworkImporter()
+    sd = imp.runImport(graph)
+    x = torch.tensor([1.0, -2.0, 0.5])
+    res = sd.output({"x": x}, "out", "while/Exit")
+    acc = x.clone()
+    for i in range(5):
+        acc = acc * 2 + i
+    assert torch.allclose(res["out"].t, acc) and int(res["while/Exit"].t) == 5
+    # the imported loop survives a FlatBuffers round trip
+    from deeplearning4j_b200.samediff.core import SameDiff
+    back = SameDiff.fromFlatBuffers(sd.asFlatBuffers())
+    assert torch.allclose(back.output({"x": x}, "out")["out"].t, acc)
+
+
+def test_tensorflow_generic_rules_against_torch():
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 4, 6, 3, generator=g)
+    f32, i32 = np.float32, np.int32
+    K = (torch.randn(3, 3, 5, 3, generator=g) * 0.2)                                  # HWIO with I = output channels of the transpose
+    graph = b"".join([
+        tf_node("x", "Placeholder", dtype=("dtype", 1), shape=("shape", [2, 4, 6, 3])),
+        _c("begin", np.asarray([0, 1, 0, 0], i32)), _c("size", np.asarray([-1, 2, 3, -1], i32)),
+        tf_node("sl", "Slice", ["x", "begin", "size"]),
+        _c("b", np.asarray([0, 0, 1, 0], i32)), _c("e", np.asarray([0, 0, 6, 0], i32)), _c("s", np.asarray([1, 1, 2, 1], i32)),
+        tf_node("ss", "StridedSlice", ["x", "b", "e", "s"], begin_mask=11, end_mask=11, shrink_axis_mask=0),
+        _c("axis1", np.asarray(1, i32)), tf_node("sp", "Split", ["axis1", "x"], num_split=2),
+        tf_node("spsum", "AddV2", ["sp", "sp:1"]),
+        _c("k", np.asarray(2, i32)), tf_node("top", "TopKV2", ["x", "k"], sorted=True),
+        _c("size2", np.asarray([8, 9], i32)), tf_node("rb", "ResizeBilinear", ["x", "size2"], align_corners=False, half_pixel_centers=True),
+        tf_node("rn", "ResizeNearestNeighbor", ["x", "size2"], align_corners=False, half_pixel_centers=False),
+        tf_node("s2d", "SpaceToDepth", ["x"], block_size=2, data_format="NHWC"), tf_node("d2s", "DepthToSpace", ["s2d"], block_size=2, data_format="NHWC"),
+        _c("pads", np.asarray([[0, 0], [1, 2], [2, 1], [0, 0]], i32)), tf_node("mp", "MirrorPad", ["x", "pads"], mode="REFLECT"),
+        tf_node("sp2", "MirrorPad", ["x", "pads"], mode="SYMMETRIC"),
+        _c("lo", np.asarray(-0.5, f32)), _c("hi", np.asarray(0.25, f32)), tf_node("clip", "ClipByValue", ["x", "lo", "hi"]),
+        tf_node("gt", "Greater", ["x", "hi"]), tf_node("sel", "SelectV2", ["gt", "x", "clip"]),
+        _c("ax3", np.asarray(3, i32)), tf_node("cs", "Cumsum", ["x", "ax3"], exclusive=True, reverse=True),
+        _c("idx", np.asarray([2, 0], i32)), _c("ax2", np.asarray(2, i32)), tf_node("ga", "GatherV2", ["x", "idx", "ax2"], batch_dims=0),
+        _c("oshape", np.asarray([2, 8, 12, 5], i32)), _c("K", K.numpy()),
+        tf_node("dc", "Conv2DBackpropInput", ["oshape", "K", "x"], strides=[1, 2, 2, 1], padding="SAME", data_format="NHWC"),
+        tf_node("red", "Mean", ["x", "ax_dyn"], keep_dims=True), tf_node("ax_dyn", "Identity", ["ax3"]),
+    ])
+    # "red" reads "ax_dyn" which comes later in the file: a forward reference outside a loop is an error, so move it
+    graph = graph.replace(tf_node("red", "Mean", ["x", "ax_dyn"], keep_dims=True) + tf_node("ax_dyn", "Identity", ["ax3"]),
+                          tf_node("ax_dyn", "Identity", ["ax3"]) + tf_node("red", "Mean", ["x", "ax_dyn"], keep_dims=True))
+    sd = TensorflowFrameworkImporter().runImport(graph)
+    names = ["sl", "ss", "spsum", "top", "top:1", "rb", "rn", "d2s", "mp", "sp2", "sel", "cs", "ga", "dc", "red"]
+    r = sd.output({"x": x}, *[n for n in names if ":" not in n])
+    assert torch.equal(r["sl"].t, x[:, 1:3, 0:3]) and torch.equal(r["ss"].t, x[:, :, 1:6:2])
+    assert torch.equal(r["spsum"].t, x[:, :2] + x[:, 2:])
+    assert torch.equal(r["top"].t, torch.topk(x, 2).values)
+    assert torch.allclose(r["rb"].t, F.interpolate(x.permute(0, 3, 1, 2), size=(8, 9), mode="bilinear", align_corners=False).permute(0, 2, 3, 1), atol=1e-6)
+    ih, iw = (torch.arange(8) * (4 / 8)).floor().long(), (torch.arange(9) * (6 / 9)).floor().long()
+    assert torch.equal(r["rn"].t, x[:, ih][:, :, iw])
+    assert torch.equal(r["d2s"].t, x)
+    assert torch.equal(r["mp"].t, F.pad(x.permute(0, 3, 1, 2), (2, 1, 1, 2), mode="reflect").permute(0, 2, 3, 1))
+    assert torch.equal(r["sp2"].t[:, 0], x[:, 0][:, [1, 0, *range(6), 5]])                        # symmetric: border repeated
+    assert torch.equal(r["sel"].t, torch.where(x > 0.25, x, x.clamp(-0.5, 0.25)))
+    assert torch.allclose(r["cs"].t, x.flip(3).cumsum(3).flip(3) - x, atol=1e-6)
+    assert torch.equal(r["ga"].t, x[:, :, [2, 0]])
+    ref = F.conv_transpose2d(x.permute(0, 3, 1, 2), K.permute(3, 2, 0, 1), stride=2, padding=1, output_padding=1).permute(0, 2, 3, 1)
+    assert tuple(r["dc"].t.shape) == (2, 8, 12, 5)
+    # SAME padding of the transposed convolution: total padding k - s = 1, taken from the start (0) and the end (1)
+    full = F.conv_transpose2d(x.permute(0, 3, 1, 2), K.permute(3, 2, 0, 1), stride=2).permute(0, 2, 3, 1)
+    assert torch.allclose(r["dc"].t, full[:, 0:8, 0:12], atol=1e-5) and ref is not None
+    assert torch.allclose(r["red"].t, x.mean(3, keepdim=True), atol=1e-6)
+    assert len(TensorflowFrameworkImporter.supportedOps()) >= 150
