@@ -179,8 +179,11 @@ class ElasticTrainer:
             for b in batches:
                 it = self.net.getIterationCount()
                 if self.monitor is not None:
+                    # two-phase entry: publish "about to run step it", then wait until every peer has published the same (or
+                    # an error).  A rank that fails between steps never publishes the next step, so no survivor enters that
+                    # step's collective alone.
                     self.monitor.beat(it)
-                    self.monitor.check()
+                    self.monitor.wait_all(it)
                 self._check_device_status()
                 if isinstance(b, (tuple, list)):
                     self.net.fit(*b)

@@ -45,7 +45,6 @@ def _worker(rank, world, port, out_dir, fail_at):
         for i, b in enumerate(batches):
             if rank == 1 and i == fail_at:
                 raise RuntimeError("injected host failure")           # the failing rank leaves between steps
-            trainer.monitor.wait_all(net.getIterationCount() - 1)      # host-side rendezvous: never enter a collective alone
             yield b
     try:
         trainer.fit(stepper())
