@@ -44,6 +44,8 @@ struct GemmParams {
   int tma_aux;            // same for the auxiliary pre-activation output
   int bias_mma;           // the bias is added on the tensor core: one extra K=16 step ones[128 x 1] x bias[1 x N] per tile
   int raster_gn;          // tile raster: column-tile groups of this width, column index fastest inside a group
+  int res_act;            // != 0: `residual` holds pre-activations z and the result is multiplied by act'(z) instead of added to
+                          // (the data-gradient GEMM of a layer that feeds an activation writes dz directly)
 };
 
 // Tile order.  CTAs that run at the same time take consecutive tile numbers, so the order decides what they share in L2:
@@ -78,6 +80,29 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case 4: return sigmoidf_(v);
     case 5: return tanhf(v);
     case 6: return gelu_sigmoid(v);
+    default: return v;
+  }
+}
+
+// v *= act'(z): the activation-gradient factor applied in the epilogue of a data-gradient GEMM.  The GELU forms use one
+// tanh.approx per value (sigmoid(y) = 0.5 + 0.5 tanh(y / 2)).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+__device__ __forceinline__ float mul_act_grad(float v, float z, int act) {
+  switch (act) {
+    case 1: return z > 0.f ? v : 0.f;
+    case 2: return v * (0.5f * (1.f + erff(z * 0.70710678118654752f)) + z * 0.3989422804014327f * __expf(-0.5f * z * z));
+    case 3: {
+      const float z2 = z * z;
+      const float t = tanh_fast(0.7978845608028654f * z * fmaf(0.044715f, z2, 1.f));
+      return v * (fmaf(0.5f, t, 0.5f) + 0.5f * z * (1.f - t * t) * 0.7978845608028654f * fmaf(0.134145f, z2, 1.f));
+    }
+    case 4: { const float sg = fmaf(0.5f, tanh_fast(0.5f * z), 0.5f); return v * sg * (1.f - sg); }
+    case 5: { const float t = tanh_fast(z); return v * (1.f - t * t); }
+    case 6: { const float sg = fmaf(0.5f, tanh_fast(0.851f * z), 0.5f); return v * fmaf(1.702f * z * sg, 1.f - sg, sg); }
     default: return v;
   }
 }
@@ -372,14 +397,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                   const uint4 u = *reinterpret_cast<const uint4*>(rs + j);
-                  v[j] += unpack_lo(u.x, p.fmt); v[j + 1] += unpack_hi(u.x, p.fmt);
-                  v[j + 2] += unpack_lo(u.y, p.fmt); v[j + 3] += unpack_hi(u.y, p.fmt);
-                  v[j + 4] += unpack_lo(u.z, p.fmt); v[j + 5] += unpack_hi(u.z, p.fmt);
-                  v[j + 6] += unpack_lo(u.w, p.fmt); v[j + 7] += unpack_hi(u.w, p.fmt);
+                  const float z8[8] = {unpack_lo(u.x, p.fmt), unpack_hi(u.x, p.fmt), unpack_lo(u.y, p.fmt), unpack_hi(u.y, p.fmt),
+                                       unpack_lo(u.z, p.fmt), unpack_hi(u.z, p.fmt), unpack_lo(u.w, p.fmt), unpack_hi(u.w, p.fmt)};
+                  if (p.res_act) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j + e] = mul_act_grad(v[j + e], z8[e], p.res_act);
+                  } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j + e] += z8[e];
+                  }
                 }
               } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) if (col0 + j < p.N) v[j] += unpack_lo((uint32_t)rs[j], p.fmt);
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) {
+                    const float z = unpack_lo((uint32_t)rs[j], p.fmt);
+                    v[j] = p.res_act ? mul_act_grad(v[j], z, p.res_act) : v[j] + z;
+                  }
               }
             }
             if (p.out_fp32) {
@@ -464,13 +498,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 const uint4 u = *reinterpret_cast<const uint4*>(rs + j);
-                v[j] += unpack_lo(u.x, p.fmt); v[j + 1] += unpack_hi(u.x, p.fmt);
-                v[j + 2] += unpack_lo(u.y, p.fmt); v[j + 3] += unpack_hi(u.y, p.fmt);
-                v[j + 4] += unpack_lo(u.z, p.fmt); v[j + 5] += unpack_hi(u.z, p.fmt);
-                v[j + 6] += unpack_lo(u.w, p.fmt); v[j + 7] += unpack_hi(u.w, p.fmt);
+                const float z8[8] = {unpack_lo(u.x, p.fmt), unpack_hi(u.x, p.fmt), unpack_lo(u.y, p.fmt), unpack_hi(u.y, p.fmt),
+                                     unpack_lo(u.z, p.fmt), unpack_hi(u.z, p.fmt), unpack_lo(u.w, p.fmt), unpack_hi(u.w, p.fmt)};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[j + e] = p.res_act ? mul_act_grad(v[j + e], z8[e], p.res_act) : v[j + e] + z8[e];
               }
             } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) v[j] += unpack_lo((uint32_t)rs[j], p.fmt);
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                const float z = unpack_lo((uint32_t)rs[j], p.fmt);
+                v[j] = p.res_act ? mul_act_grad(v[j], z, p.res_act) : v[j] + z;
+              }
             }
           }
           if (p.out_fp32) {
@@ -580,7 +617,11 @@ static int gemm_impl(const void* A, const void* B, void* C, void* aux, const voi
   cudaGetDevice(&dev);
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ld_aux = ld_aux; p.ld_res = ld_res; p.C = C; p.aux = aux; p.bias = bias;
-  p.residual = residual; p.bias_fp32 = bias_fp32; p.out_fp32 = out_fp32; p.act = act; p.atomic_out = atomic_out;
+  // `act` carries two ids: bits 0-7 the forward activation applied to the result, bits 8-15 an activation whose derivative at
+  // `residual` multiplies the result (then `residual` is not added)
+  p.residual = residual; p.bias_fp32 = bias_fp32; p.out_fp32 = out_fp32; p.act = act & 0xff; p.res_act = (act >> 8) & 0xff;
+  if (p.res_act && (!residual || p.act)) return -DL4J_ERR_BAD_ARG;
+  p.atomic_out = atomic_out;
   p.splits = splits; p.fmt = fmt; p.alpha = alpha; p.status = dl4j_status_word(dev);
   p.batch1 = batch1; p.batch2 = batch2; p.c_stride_b1 = c_bs[0]; p.c_stride_b2 = c_bs[1];
   if ((a_bs[0] & 7) || (a_bs[1] & 7) || (b_bs[0] & 7) || (b_bs[1] & 7)) return -DL4J_ERR_BAD_ARG;

@@ -116,12 +116,12 @@ w2v_batch_kernel(const W2vParams p) {
     // the accumulated error goes to the trained input rows
     if (p.context) {
       if (p.train_words) {
-        const float inv = 1.f / (float)n_ctx;        // the mean's derivative: every context row gets err / n
+        // as in the original algorithm (and cbow_ of helpers/cuda/sg_cb.cu) every context row receives the whole error
         for (int w = 0; w < p.W; ++w) {
           const int c = p.context[(long long)b * p.W + w];
           if (c < 0 || c >= p.V) continue;
           float* r = p.syn0 + (long long)c * p.D;
-          for (int d = lane; d < p.D; d += 32) atomicAdd(r + d, err[d] * inv);
+          for (int d = lane; d < p.D; d += 32) atomicAdd(r + d, err[d]);
         }
       }
     } else {
@@ -164,7 +164,7 @@ barnes_edge_forces_kernel(const int* __restrict__ row_p, const int* __restrict__
 using namespace dl4j;
 
 // One launch for a batch of word2vec examples.  `context` null: skip-gram (row target[b] of syn0 is the input and receives the
-// error); non-null [B, W]: CBOW (the mean of the context rows is the input; with train_words the error / n goes back to each).
+// error); non-null [B, W]: CBOW (the mean of the context rows is the input; with train_words the error goes back to each of them).
 // Tables are fp32; index arrays int32; codes int8; alpha fp32 [n_alpha]; random int64 [n_random].
 DL4J_API int dl4j_w2v_batch(float* syn0, float* syn1, float* syn1neg, const int* neg_table, long long neg_table_len, const int* target,
                             const int* ng_starter, const int* points, const signed char* codes, const int* context, const float* alpha,

@@ -161,7 +161,8 @@ class MultiLayerUpdater:
         if self.needs_pre_apply():
             self._pre_apply()
         if use_fused is None:
-            use_fused = self.params.is_cuda
+            from ..ops import nnops
+            use_fused = self.params.is_cuda and not nnops._FORCE_TORCH        # the library-only baseline also updates with torch ops
         self._shadow_fresh = False
         if use_fused and apply_step and self._fused_update(iteration, epoch):
             self._shadow_fresh = self.shadow is not None

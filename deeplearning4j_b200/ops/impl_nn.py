@@ -144,6 +144,21 @@ def linear_gelu(x, w, b=None, precise=False, **kw):
     return nnops.linear(x.reshape(-1, x.shape[-1]), w, b, ActivationGELU(precise)).reshape(*lead, w.shape[1])
 
 
+@op("mlp_gelu")
+def mlp_gelu(x, w1, b1, w2, b2=None, precise=False, **kw):
+    """Fused ``gelu(x @ w1 + b1) @ w2 + b2``: produced by the graph optimizer from ``xw_plus_b -> gelu -> xw_plus_b``; on the native
+    path the GELU gradient is applied inside the second layer's data-gradient GEMM."""
+    from ..nn.activations import ActivationGELU
+    act = ActivationGELU(precise)
+    lead = x.shape[:-1]
+    x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+    nat = nnops._native_for(x2)
+    y = nat.mlp(x2, w1, b1, w2, b2, act) if nat is not None and x2.dtype in (torch.bfloat16, torch.float16) else None
+    if y is None:
+        y = nnops.linear(nnops.linear(x2, w1, b1, act), w2, b2, None)
+    return y if x.dim() == 2 else y.reshape(*lead, w2.shape[1])
+
+
 @op("biasadd")
 def biasadd(x, b, nchw=False, **kw):
     if nchw and x.dim() > 2:

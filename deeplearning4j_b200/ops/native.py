@@ -227,9 +227,15 @@ def _use_pair(M, N, K, splits):
 
 
 def gemm_raw(a, b, out=None, bias=None, act=0, aux=None, residual=None, out_dtype=None, atomic=False, splits=1,
-             alpha=1.0, block_n=None, pair=None):
-    """out[M,N] = act(alpha * a @ b + bias) + residual with a logical [M,K], b logical [K,N]."""
+             alpha=1.0, block_n=None, pair=None, res_act=0):
+    """out[M,N] = act(alpha * a @ b + bias) + residual with a logical [M,K], b logical [K,N].  With ``res_act`` (an activation id)
+    ``residual`` holds pre-activations z and the result is multiplied by act'(z) instead: a data-gradient GEMM that writes dz."""
     l = require()
+    if res_act:
+        if residual is None or act:
+            raise ValueError("res_act needs the pre-activations as `residual` and no forward activation")
+        act = int(res_act) << 8
+        pair = False
     oa, ob = _operand_a(a), _operand_b(b)
     if oa is None or ob is None:
         raise ValueError("operand layout not addressable by TMA (need unit stride in one dim, 16-byte alignment)")
@@ -322,6 +328,127 @@ def _wgrad_splits(n_out_tiles, K):
     if n_out_tiles >= sms:
         return 1
     return max(1, min((K + 63) // 64, (2 * sms) // max(n_out_tiles, 1), 32))
+
+
+def _bias_grad_buffer(b, needed, N, device):
+    """(accumulator, returned gradient): the bias' own fp32 ``.grad`` when the kernels may add into it, else a fresh buffer."""
+    if b is None or not needed:
+        return None, None
+    if b.is_leaf and b.grad is not None and b.grad.dtype == torch.float32 and b.grad.is_contiguous():
+        return b.grad, None
+    acc = torch.zeros(N, dtype=torch.float32, device=device)
+    return acc, acc
+
+
+def _weight_grad(W, x, dz):
+    """dW of ``y = x @ W`` accumulated into ``W.grad`` when its layout allows (returns None), else returned in W's layout."""
+    M, N = dz.shape
+    nIn = x.shape[1]
+    tiles = ((N + 127) // 128) * ((nIn + 255) // 256)
+    splits = _wgrad_splits(tiles, M)
+    g = W.grad if (W.is_leaf and W.grad is not None) else None
+    if g is not None and g.dim() == 4 and g.shape[2] == 1 and g.shape[3] == 1 and g.is_contiguous():
+        g = g.view(g.shape[0], g.shape[1]).t()      # 1x1 convolution kernel [nOut, nIn, 1, 1]: same memory as an 'f' dense weight
+    if g is not None and g.dtype == torch.float32 and g.dim() == 2 and g.stride(0) == 1 and g.stride(1) == nIn \
+            and g.data_ptr() % 16 == 0 and nIn % 4 == 0:
+        gemm_raw(dz.t(), x, out=g.t(), atomic=True, splits=splits)
+        return None
+    if g is not None and g.dtype == torch.float32 and g.dim() == 2 and g.is_contiguous() and g.data_ptr() % 16 == 0 and N % 4 == 0:
+        # row-major [nIn, nOut] master (SameDiff variables): dW = x^T dz accumulated in place
+        tiles2 = ((nIn + 127) // 128) * ((N + 255) // 256)
+        gemm_raw(x.t(), dz, out=g, atomic=True, splits=_wgrad_splits(tiles2, M))
+        return None
+    dWt = gemm_raw(dz.t(), x, out_dtype=torch.float32, atomic=True, splits=splits)
+    return dWt.reshape(W.shape).to(W.dtype) if W.dim() == 4 else dWt.t().to(W.dtype)
+
+
+def _fwd_bias(b, dtype):
+    """(bias operand for the forward GEMM, master the gradient goes to)."""
+    if b is None:
+        return None, None
+    b_fwd = b if b.dtype == dtype else getattr(b, "_lp", None)
+    if b_fwd is not None:
+        b_fwd = b_fwd.detach()
+    master = getattr(b, "_master", b)
+    if b_fwd is None:
+        b_fwd = master
+    return b_fwd.reshape(-1), master
+
+
+class _MlpFn(torch.autograd.Function):
+    """y = act(x @ W1 + b1) @ W2 + b2 as one autograd node.  Forward: two GEMMs (the first saves its pre-activation z1 from the
+    epilogue).  Backward: the data-gradient GEMM of the second layer multiplies by act'(z1) in its epilogue and writes dz1
+    directly, so the separate pass that read dy1 and z1 and wrote dz1 disappears; the bias gradient of the first layer is a
+    column sum over dz1 alone."""
+
+    @staticmethod
+    def forward(ctx, x, W1, b1, W2, b2, act, W1_lp, W2_lp):
+        z1 = torch.empty((x.shape[0], W1_lp.shape[1]), dtype=x.dtype, device=x.device)
+        b1_fwd, b1_m = _fwd_bias(b1, x.dtype)
+        b2_fwd, b2_m = _fwd_bias(b2, x.dtype)
+        y1 = gemm_raw(x, W1_lp, bias=b1_fwd, act=act, aux=z1)
+        y2 = gemm_raw(y1, W2_lp, bias=b2_fwd)
+        ctx.act = act
+        ctx.refs = (getattr(W1, "_master", W1), b1_m, getattr(W2, "_master", W2), b2_m)
+        ctx.save_for_backward(x, W1_lp, W2_lp, z1, y1)
+        return y2
+
+    @staticmethod
+    def backward(ctx, dy2):
+        x, W1_lp, W2_lp, z1, y1 = ctx.saved_tensors
+        W1, b1, W2, b2 = ctx.refs
+        l = require()
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        M, N2 = dy2.shape
+        N1 = z1.shape[1]
+        need = ctx.needs_input_grad
+        acc2, db2 = _bias_grad_buffer(b2, need[4], N2, dy2.device)
+        if acc2 is not None:
+            _check(l.dl4j_bias_act_bwd(_ptr(dy2), None, None, _ptr(acc2), M, N2, 0, _DT[dy2.dtype], _stream()), "dl4j_bias_act_bwd")
+        dW2 = _weight_grad(W2, y1, dy2) if need[3] else None
+        # dz1 = (dy2 @ W2^T) * act'(z1): one GEMM
+        dz1 = gemm_raw(dy2, W2_lp.t(), residual=z1, res_act=ctx.act)
+        acc1, db1 = _bias_grad_buffer(b1, need[2], N1, dy2.device)
+        if acc1 is not None:
+            _check(l.dl4j_bias_act_bwd(_ptr(dz1), None, None, _ptr(acc1), M, N1, 0, _DT[dz1.dtype], _stream()), "dl4j_bias_act_bwd")
+        dW1 = _weight_grad(W1, x, dz1) if need[1] else None
+        dx = gemm_raw(dz1, W1_lp.t()) if need[0] else None
+        if db1 is not None:
+            db1 = db1.reshape(b1.shape).to(b1.dtype)
+        if db2 is not None:
+            db2 = db2.reshape(b2.shape).to(b2.dtype)
+        return dx, dW1, db1, dW2, db2, None, None, None
+
+
+def _lp_weight(W, dtype):
+    W_lp = getattr(W, "_lp", None)
+    if W_lp is None:
+        if W.stride(0) != 1 and W.stride(1) != 1:
+            return None
+        W_lp = W.detach() if W.dtype == dtype else W.detach().to(dtype)
+    return W_lp if W_lp.dtype == dtype else None
+
+
+def mlp(x, W1, b1, W2, b2, activation):
+    """``act(x @ W1 + b1) @ W2 + b2`` with the activation gradient folded into the second layer's data-gradient GEMM; returns None
+    when the case is not covered (then the two layers run separately)."""
+    if not available() or x.dim() != 2 or x.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    act = _act_id(activation)
+    if act not in (1, 2, 3, 4, 5, 6):
+        return None
+    W1_lp, W2_lp = _lp_weight(W1, x.dtype), _lp_weight(W2, x.dtype)
+    if W1_lp is None or W2_lp is None or W1_lp.shape[1] != W2_lp.shape[0]:
+        return None
+    if not x.is_contiguous():
+        x = x.contiguous()
+    for w in (W1_lp, W2_lp):
+        if _operand_b(w) is None or _operand_b(w.t()) is None or w.shape[0] % 8 or w.shape[1] % 8:
+            return None
+    if _operand_a(x) is None:
+        return None
+    return _MlpFn.apply(x, W1, b1, W2, b2, act, W1_lp, W2_lp)
 
 
 class _LinearFn(torch.autograd.Function):

@@ -9,6 +9,8 @@ and runs it.  The plan is cached per (outputs, training) pair.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import registry
@@ -34,7 +36,7 @@ def _build_plan(sd, outputs):
     skip, plan = set(), []
     # fusion: add whose only consumer is a layer_norm taking it as its input (residual connection + norm); the fused node sits at
     # the layer_norm's position, where the gain / bias inputs are certainly available
-    fuse_ln = {}
+    fuse_ln, fuse_mlp = {}, {}
     for n in nodes:
         if n.opName == "add" and len(n.inputs) == 2 and None not in n.inputs and len(n.outputs) == 1 and n.outputs[0] not in out_set:
             cs = consumers.get(n.outputs[0], [])
@@ -49,12 +51,26 @@ def _build_plan(sd, outputs):
         if id(n) in fuse_ln:
             plan.append((fuse_ln[id(n)], registry.get("add_layer_norm")))
             continue
+        if id(n) in fuse_mlp:
+            plan.append((fuse_mlp[id(n)], registry.get("mlp_gelu")))
+            continue
         # fusion: xw_plus_b whose only consumer is a gelu node
         if n.opName in ("xw_plus_b", "linear") and len(n.outputs) == 1 and n.outputs[0] not in out_set \
                 and not n.args.get("transposeW") and not n.args.get("aTranspose"):
             cs = consumers.get(n.outputs[0], [])
             if len(cs) == 1 and cs[0].opName in ("gelu", "precise_gelu") and len(cs[0].inputs) == 1:
                 g = cs[0]
+                # ... and a second linear layer as the gelu's only consumer: the whole feed-forward block is one node, placed where
+                # the second layer stood (its weights are certainly available there)
+                cs2 = consumers.get(g.outputs[0], []) if len(g.outputs) == 1 and g.outputs[0] not in out_set else []
+                m = cs2[0] if len(cs2) == 1 else None
+                if m is not None and m.opName in ("xw_plus_b", "linear") and m.inputs and m.inputs[0] == g.outputs[0] \
+                        and m.inputs.count(g.outputs[0]) == 1 and not m.args.get("transposeW") and not m.args.get("aTranspose") \
+                        and len(n.inputs) == 3 and len(m.inputs) in (2, 3) and os.environ.get("DL4J_FUSE_MLP", "1") != "0":
+                    fuse_mlp[id(m)] = SameDiffOp(m.name, "mlp_gelu", list(n.inputs) + list(m.inputs[1:]), list(m.outputs),
+                                                 {"precise": g.opName == "precise_gelu"})
+                    skip.add(id(g))
+                    continue
                 fused = SameDiffOp(n.name, "linear_gelu", list(n.inputs), list(g.outputs), {"precise": g.opName == "precise_gelu"})
                 plan.append((fused, registry.get("linear_gelu")))
                 skip.add(id(g))

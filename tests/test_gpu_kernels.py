@@ -412,3 +412,67 @@ def test_gemm_on_cta_pairs_matches_fp32(nat, M, N, K):
     torch.testing.assert_close(out32, rw, rtol=1e-3, atol=1e-3 * float(rw.abs().mean()))
     torch.cuda.synchronize()
     nat.check_status()
+
+
+@pytest.mark.parametrize("act_id,fn", [(6, lambda z: z * torch.sigmoid(1.702 * z)), (3, lambda z: torch.nn.functional.gelu(z, approximate="tanh")),
+                                       (1, torch.relu), (5, torch.tanh)])
+def test_gemm_epilogue_multiplies_by_the_activation_gradient(act_id, fn):
+    """``gemm_raw(..., residual=z, res_act=id)`` = (a @ b) * act'(z), the data-gradient GEMM that writes dz directly."""
+    from deeplearning4j_b200.ops import native
+    native.require()
+    g = torch.Generator(device="cuda").manual_seed(act_id)
+    M, K, N = 300, 192, 264
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.3).bfloat16()
+    b = (torch.randn(K, N, device="cuda", generator=g) * 0.3).bfloat16()
+    z = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    got = native.gemm_raw(a, b, residual=z, res_act=act_id)
+    zf = z.float().requires_grad_(True)
+    fn(zf).sum().backward()
+    ref = (a.float() @ b.float()) * zf.grad
+    assert _rel(got, ref) < 3e-2
+    with pytest.raises(ValueError):
+        native.gemm_raw(a, b, res_act=act_id)
+
+
+@pytest.mark.parametrize("precise", [False, True])
+def test_fused_mlp_block_matches_fp32_and_the_two_layer_path(precise):
+    from deeplearning4j_b200.nn.activations import ActivationGELU
+    from deeplearning4j_b200.ops import native
+    native.require()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    M, H, F_ = 384, 128, 512
+    x = (torch.randn(M, H, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+
+    def params():
+        gg = torch.Generator(device="cuda").manual_seed(12)
+        W1 = (torch.randn(H, F_, device="cuda", generator=gg) * 0.1).requires_grad_(True)
+        b1 = (torch.randn(F_, device="cuda", generator=gg) * 0.1).requires_grad_(True)
+        W2 = (torch.randn(F_, H, device="cuda", generator=gg) * 0.1).requires_grad_(True)
+        b2 = (torch.randn(H, device="cuda", generator=gg) * 0.1).requires_grad_(True)
+        for p in (W1, b1, W2, b2):
+            p.grad = torch.zeros_like(p)            # the kernels accumulate into existing fp32 gradients
+        return W1, b1, W2, b2
+    act = ActivationGELU(precise)
+    dy = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+    W1, b1, W2, b2 = params()
+    y = native.mlp(x, W1, b1, W2, b2, act)
+    assert y is not None
+    y.backward(dy)
+    dx_fused, x.grad = x.grad.clone(), None
+    V1, c1, V2, c2 = params()
+    y_sep = native.linear(native.linear(x, V1, c1, act), V2, c2, None)
+    y_sep.backward(dy)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert _rel(y, y_sep) < 1e-2 and _rel(dx_fused, x.grad) < 2e-2
+    for a, b in ((W1, V1), (b1, c1), (W2, V2), (b2, c2)):
+        assert _rel(a.grad, b.grad) < 2e-2
+    # fp32 formulation
+    xf = x.detach().float().requires_grad_(True)
+    R1, r1, R2, r2 = (p.detach().clone().requires_grad_(True) for p in (V1, c1, V2, c2))
+    z = xf @ R1 + r1
+    h = torch.nn.functional.gelu(z, approximate="tanh") if precise else z * torch.sigmoid(1.702 * z)
+    (h @ R2 + r2).backward(dy.float())
+    assert _rel(dx_fused, xf.grad) < 4e-2
+    for a, b in ((W1, R1), (b1, r1), (W2, R2), (b2, r2)):
+        assert _rel(a.grad, b.grad) < 4e-2
