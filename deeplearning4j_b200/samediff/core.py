@@ -414,6 +414,8 @@ class SameDiff:
 
     def getArrForVarName(self, name):
         t = self.arrays.get(name)
+        if t is None:
+            t = self.__dict__.get("_eager_arrays", {}).get(name)
         return None if t is None else INDArray(t)
 
     def setArrayForVariable(self, name, arr):
@@ -484,7 +486,46 @@ class SameDiff:
         for o in outs:
             self._producer[o.name] = node
         self._exec_plan = None
+        if getattr(self, "_eager", False):
+            self._eager_run(node, d)
         return outs[0] if n == 1 else outs
+
+    # ------------------------------------------------------------------ eager mode (SameDiff.enableEagerMode)
+    def enableEagerMode(self):
+        """Every op added from now on is also executed at once when the arrays of all its inputs are known (variables, constants,
+        placeholders that were given an array with ``setArray``, results of earlier eager ops); ``SDVariable.getArr`` then returns
+        the value while the graph is still being defined."""
+        self._eager = True
+        self.__dict__.setdefault("_eager_arrays", {})
+        return self
+
+    def isEagerMode(self):
+        return bool(getattr(self, "_eager", False))
+
+    def _eager_run(self, node, d):
+        vals = []
+        for i in node.inputs:
+            if i is None:
+                vals.append(None)
+                continue
+            t = self.arrays.get(i)
+            if t is None:
+                t = self._eager_arrays.get(i)
+            if t is None:
+                return                                  # an input without a value yet (a placeholder): the op stays symbolic
+            vals.append(t)
+        with torch.no_grad():
+            out = d.fn(*vals, **node.args)
+        outs = list(out) if isinstance(out, (tuple, list)) else [out]
+        for name, t in zip(node.outputs, outs):
+            if isinstance(t, torch.Tensor):
+                self._eager_arrays[name] = t
+
+    def doUdf(self, udf, *inputs, name=None):
+        """Adds a user-defined op (``ops.executioner.UserDefinedCustomOp``) to the graph (``SameDiff.doUdf``)."""
+        udf.register()
+        udf.configureWithSameDiff(self)
+        return self._op(udf.opName(), list(inputs), n_out=udf.numOutputs(), name=name)
 
     @staticmethod
     def collectTrace(traces=None):
