@@ -216,6 +216,9 @@ def max_pool_with_argmax(x, kH=2, kW=2, sH=2, sW=2, pH=0, pW=0, dH=1, dW=1, isSa
     xc = x.permute(0, 3, 1, 2) if nhwc else x
     xc, pad = _prep(xc, (kH, kW), (sH, sW), (pH, pW), (dH, dW), bool(isSameMode), float("-inf"))
     y, idx = F.max_pool2d(xc, (kH, kW), (sH, sW), tuple(pad), (dH, dW), return_indices=True)
+    # flattened position inside one example as the reference (and TensorFlow) count it: ((row * W) + column) * C + channel
+    C = xc.shape[1]
+    idx = idx * C + torch.arange(C, device=idx.device).reshape(1, C, 1, 1)
     return (y.permute(0, 2, 3, 1), idx.permute(0, 2, 3, 1)) if nhwc else (y, idx)
 
 

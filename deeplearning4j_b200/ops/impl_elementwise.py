@@ -122,6 +122,9 @@ _binary("floormod", lambda x, y: torch.remainder(x, y))
 _binary("mod", lambda x, y: torch.remainder(x, y))      # simdOps::Mod is d1 - floor(d1 / d2) * d2 (ops.h:1708), not C fmod
 _binary("reversemod", lambda x, y: torch.fmod(y, x))
 _binary("floordiv", lambda x, y: torch.floor_divide(x, y))
+# piecewise constant: both gradients are zero (floordiv.cpp: floordiv_bp assigns 0 to gradX and gradY)
+op("floordiv_bp", n_out=2)(lambda x, y, g, **kw: (torch.zeros_like(x), torch.zeros_like(_t(y, x)).expand_as(torch.broadcast_tensors(x, _t(y, x))[1]).clone()
+                                                  if not isinstance(y, torch.Tensor) else torch.zeros_like(y)))
 _binary("realdiv", lambda x, y: x / y)
 _binary("Pow", lambda x, y: torch.pow(x, y), "pow_pairwise")
 _binary("assign", lambda x, y: y.expand_as(x).clone() if y.shape != x.shape else y.clone())

@@ -148,7 +148,7 @@ def weighted_cross_entropy_with_logits(targets, logits, weights, **kw):
 @op("ctc_loss")
 def ctc_loss(targetLabels, logitInput, targetLabelLengths, logitInputLengths, blankIndex=0, **kw):
     """logitInput [B, T, C] (batch-major, as the native op); returns the per-example loss [B]."""
-    lp = F.log_softmax(logitInput.float(), -1).permute(1, 0, 2)
+    lp = F.log_softmax(logitInput if logitInput.dtype == torch.float64 else logitInput.float(), -1).permute(1, 0, 2)
     return F.ctc_loss(lp, targetLabels.long(), logitInputLengths.long(), targetLabelLengths.long(), blank=int(blankIndex),
                       reduction="none", zero_infinity=False)
 

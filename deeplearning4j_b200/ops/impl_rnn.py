@@ -183,7 +183,18 @@ def gruCell(x, hLast, Wru, Wc, bru, bc, **kw):
     return r, u, c, u * hLast + (1 - u) * c
 
 
-op("gruCell_bp", n_out=-1)(_autobp(lambda *a, **kw: gruCell(*a, **kw)[3], 6))
+@op("gruCell_bp", n_out=6)
+def gruCell_bp(x, hLast, Wru, Wc, bru, bc, dLdr, dLdu=None, dLdc=None, dLdh=None, **kw):
+    """Gradients of (x, hLast, Wru, Wc, bru, bc) given the gradients of the four outputs (r, u, c, h), in the reference's input
+    order (``generic/nn/recurrent/gruCell.cpp:134-150``); with one gradient only it is taken as dL/dh."""
+    if dLdu is None and dLdc is None and dLdh is None:
+        dLdr, dLdh = None, dLdr
+    with torch.enable_grad():
+        leaves = [t.detach().clone().requires_grad_(True) for t in (x, hLast, Wru, Wc, bru, bc)]
+        outs = gruCell(*leaves)
+        pairs = [(o, g) for o, g in zip(outs, (dLdr, dLdu, dLdc, dLdh)) if g is not None]
+        grads = torch.autograd.grad([o for o, _ in pairs], leaves, [g for _, g in pairs], allow_unused=True)
+    return tuple(torch.zeros_like(l) if g is None else g for l, g in zip(leaves, grads))
 
 
 @op("gru")
@@ -265,6 +276,8 @@ def _simple_rnn(x, Wx, Wh, b, h0, seqLen=None, reverse=False):
     n = Wh.shape[0]
     h = h0 if h0 is not None else torch.zeros(B, n, dtype=x.dtype, device=x.device)
     hs = [None] * T
+    if b is not None and b.numel() == 2 * n:           # [2 * units]: input-to-hidden and hidden-to-hidden biases (helpers/impl/rnn.cpp:41)
+        b = b.reshape(-1)[:n] + b.reshape(-1)[n:]
     for t in (range(T - 1, -1, -1) if reverse else range(T)):
         hn = torch.tanh(x[t] @ Wx + h @ Wh + b)
         if seqLen is not None:

@@ -145,7 +145,14 @@ def _unstack(x, dimension=0, num=None, **kw):
 
 
 op("unstack", n_out=-1)(_unstack)
-op("tear", n_out=-1)(lambda x, dimensions=(0,), **kw: tuple(torch.unbind(x, dim=_ints(dimensions)[0])))
+@op("tear", n_out=-1)
+def tear(x, dimensions=(0,), **kw):
+    """All sub-arrays that span ``dimensions`` (the tensors-along-dimension of ``tear.cpp``): for a [3, 4] array and dimension 1,
+    three arrays of shape [4]."""
+    dims = sorted(d % x.dim() for d in _ints(dimensions))
+    rest = [d for d in range(x.dim()) if d not in dims]
+    y = x.permute(*rest, *dims).reshape(-1, *[x.shape[d] for d in dims])
+    return tuple(y.unbind(0))
 
 
 @op("split", n_out=-1)

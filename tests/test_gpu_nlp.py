@@ -81,11 +81,13 @@ def test_batched_examples_update_shared_rows_without_losing_updates():
     target = torch.arange(B, dtype=torch.int32).cuda() % V
     starter = torch.full((B,), 7, dtype=torch.int32).cuda()
     s0 = syn0.clone()
-    ok = native.w2v_batch(syn0, None, syn1n, None, target, starter, None, None, None, torch.tensor([0.01]), torch.arange(B), 0, True)
+    # every negative sample is drawn from a table that only holds the positive word, so it is skipped and only the positive pair trains
+    neg = torch.full((16,), 7, dtype=torch.int32).cuda()
+    ok = native.w2v_batch(syn0, None, syn1n, neg, target, starter, None, None, None, torch.tensor([0.01]), torch.arange(B), 3, True)
     assert ok
     torch.cuda.synchronize()
-    # ns_rounds = 0 still trains the positive pair: row 7 of syn1neg = sum_b alpha * (1 - sigmoid(0)) * syn0[b]  (the row starts at 0
-    # and the dot products stay tiny, so staleness is second order)
+    # row 7 of syn1neg = sum_b alpha * (1 - sigmoid(0)) * syn0[b]  (the row starts at 0 and the dot products stay tiny, so staleness is
+    # second order)
     expect = 0.01 * 0.5 * s0[:B].sum(0)
     torch.testing.assert_close(syn1n[7], expect, rtol=2e-2, atol=1e-5)
     assert float(syn1n[torch.arange(V).cuda() != 7].abs().max()) == 0.0
