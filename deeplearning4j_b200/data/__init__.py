@@ -10,3 +10,4 @@ from .normalizers import (CompositeDataSetPreProcessor, DataNormalization, Image
                           NormalizerSerializer, NormalizerStandardize, VGG16ImagePreProcessor)
 from .fetchers import (Cifar10DataSetIterator, EmnistDataSetIterator, IrisDataSetIterator, LFWDataSetIterator, MnistDataSetIterator,
                        SvhnDataSetIterator, TinyImageNetDataSetIterator, UciSequenceDataSetIterator)
+from .iterators_extra import *  # noqa: F401,F403,E402
