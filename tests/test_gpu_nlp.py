@@ -89,7 +89,7 @@ def test_batched_examples_update_shared_rows_without_losing_updates():
     # row 7 of syn1neg = sum_b alpha * (1 - sigmoid(0)) * syn0[b]  (the row starts at 0 and the dot products stay tiny, so staleness is
     # second order)
     expect = 0.01 * 0.5 * s0[:B].sum(0)
-    torch.testing.assert_close(syn1n[7], expect, rtol=2e-2, atol=1e-5)
+    torch.testing.assert_close(syn1n[7], expect, rtol=2e-2, atol=5e-4)        # elements near zero: the staleness term dominates them
     assert float(syn1n[torch.arange(V).cuda() != 7].abs().max()) == 0.0
 
 
