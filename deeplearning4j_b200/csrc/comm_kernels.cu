@@ -130,6 +130,7 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
                                                     const UpdSegment* __restrict__ segs, const UpdHyperTable& ht, float grad_scale,
                                                     int use_multimem, int ci) {
   float* my_params = c.params[c.rank];
+  const int NT = (int)blockDim.x;          // 512 in the whole-buffer kernel, 128 in the per-bucket kernel (which shares SMs with GEMM CTAs)
   const UpdChunk ch = chunks[ci];
   const UpdSegment sg = segs[ch.seg];
   const UpdHyper h = ht.h[sg.hyper];
@@ -148,11 +149,11 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
   // two vectors per thread and iteration: every load of both (peer gradients, parameters, state) is issued
   // before the first use so that enough bytes are in flight to cover the NVLink round trip
   constexpr int U = 2;
-  for (int v0 = threadIdx.x; v0 < nvec; v0 += COMM_THREADS * U) {
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += NT * U) {
     float4 g[U], w[U], a4[U], b4[U], c4[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int v = v0 + u * COMM_THREADS;
+      const int v = v0 + u * NT;
       g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       w[u] = g[u]; a4[u] = g[u]; b4[u] = g[u]; c4[u] = g[u];
       if (v < nvec) {
@@ -176,7 +177,7 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int v = v0 + u * COMM_THREADS;
+      const int v = v0 + u * NT;
       if (v >= nvec) continue;
       const long long i = ch.offset + 4LL * v;
       float wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
@@ -212,7 +213,7 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
     }
   }
   // scalar tail (and whole chunk when its offset is not 16-byte aligned)
-  for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += COMM_THREADS) {
+  for (int e = nvec * 4 + threadIdx.x; e < ch.count; e += NT) {
     const long long i = ch.offset + e;
     float g = 0.f;
     for (int r = 0; r < c.world; ++r) g += ld_peer_f(c.grads[r] + i);
@@ -321,7 +322,12 @@ __device__ __forceinline__ bool wait_peer_flags(const CommCtx& c, int slot, uint
   return ok_flag != 0;
 }
 
-__global__ void __launch_bounds__(COMM_THREADS)
+// The CTAs are small on purpose (BUCKET_THREADS threads, about 12 K registers, 264 bytes of shared memory): one of them fits next to
+// a resident tcgen05 GEMM CTA (192 threads x 232 registers, all but about 1.7 KB of the shared memory), so the exchange proceeds
+// while the backward pass keeps every SM busy.  With the 512-thread form the launches could only run between GEMMs.
+constexpr int BUCKET_THREADS = 128;
+
+__global__ void __launch_bounds__(BUCKET_THREADS, 5)
 bucket_allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChunk* __restrict__ chunks, int chunk0, int chunk1,
                                const UpdSegment* __restrict__ segs, const StepVars* __restrict__ vars, int bucket,
                                unsigned int* tickets, int use_multimem, int* status) {
@@ -329,7 +335,7 @@ bucket_allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const
   __shared__ unsigned int my_ticket;
   const uint32_t epoch = vars->epoch;
   const float grad_scale = vars->grad_scale;
-  for (int i = threadIdx.x; i < (int)(sizeof(UpdHyperTable) / 4); i += COMM_THREADS)
+  for (int i = threadIdx.x; i < (int)(sizeof(UpdHyperTable) / 4); i += BUCKET_THREADS)
     reinterpret_cast<float*>(&ht)[i] = reinterpret_cast<const float*>(&vars->ht)[i];
   const int slot_ready = 4 + 2 * bucket, slot_done = slot_ready + 1;
   // this rank's gradients of the bucket are final (the launch is ordered after the kernels that wrote them)
@@ -823,7 +829,7 @@ DL4J_API int dl4j_bucket_allreduce_update(const void* comm_args, float* state, c
   CommCtx c = make_ctx(a);
   int dev = 0;
   cudaGetDevice(&dev);
-  bucket_allreduce_update_kernel<<<grid, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
+  bucket_allreduce_update_kernel<<<grid, BUCKET_THREADS, 0, (cudaStream_t)stream_>>>(
       c, state, reinterpret_cast<const UpdChunk*>(chunks), chunk0, chunk1, reinterpret_cast<const UpdSegment*>(segs),
       reinterpret_cast<const StepVars*>(vars), bucket, reinterpret_cast<unsigned int*>(tickets), use_multimem, dl4j_status_word(dev));
   return (int)cudaGetLastError();
