@@ -303,6 +303,12 @@ class UIServer:
             self.storages.remove(storage)
 
     def isAttached(self, storage): return storage in self.storages
+
+    def registerModule(self, module):
+        """Adds a module's routes (``ui/modules.py``: t-SNE, convolutional activations, SameDiff graph)."""
+        self.__dict__.setdefault("modules", []).append(module)
+        self.__dict__.setdefault("_routes", {}).update(module.routes())
+        return self
     def getStatsStorageInstances(self): return list(self.storages)
 
     def enableRemoteListener(self, storage=None, attach=True):
@@ -364,11 +370,22 @@ class UIServer:
                 q = {k: v[0] for k, v in parse_qs(u.query).items()}
                 if u.path in ("/", "/train", "/train/overview.html"):
                     return self._send(200, _PAGE.encode(), "text/html; charset=utf-8")
+                route = server.__dict__.get("_routes", {}).get(("GET", u.path))
+                if route is not None:
+                    code, ctype, body = route(q, b"")
+                    return self._send(code, body, ctype)
                 return self._send(200, json.dumps(server._json(u.path, q)).encode(), "application/json")
 
             def do_POST(self):
+                from urllib.parse import parse_qs, urlparse
                 n = int(self.headers.get("Content-Length", 0))
-                body = json.loads(self.rfile.read(n) or b"{}")
+                raw = self.rfile.read(n)
+                u = urlparse(self.path)
+                route = server.__dict__.get("_routes", {}).get(("POST", u.path))
+                if route is not None:
+                    code, ctype, out = route({k: v[0] for k, v in parse_qs(u.query).items()}, raw)
+                    return self._send(code, out, ctype)
+                body = json.loads(raw or b"{}")
                 if self.path != "/remoteReceive" or server.remote is None:
                     return self._send(403, b'{"error": "remote listener disabled"}', "application/json")
                 kind, rec = body.get("type"), body.get("record")
@@ -388,3 +405,8 @@ class UIServer:
             self._httpd = None
         if UIServer._instance is self:
             UIServer._instance = None
+
+
+from .modules import (ChartHistogram, ChartHorizontalBar, ChartLine, ChartScatter, ChartStackedArea, ChartTimeline, Component,  # noqa: E402,F401
+                      ComponentDiv, ComponentTable, ComponentText, ConvolutionalIterationListener, ConvolutionalListenerModule,
+                      DecoratorAccordion, SameDiffModule, StaticPageUtil, TsneModule, UIModule, decode_stats, encode_stats)
