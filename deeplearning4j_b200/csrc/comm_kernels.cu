@@ -130,7 +130,7 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
                                                     const UpdSegment* __restrict__ segs, const UpdHyperTable& ht, float grad_scale,
                                                     int use_multimem, int ci) {
   float* my_params = c.params[c.rank];
-  const int NT = (int)blockDim.x;          // 512 in the whole-buffer kernel, 128 in the per-bucket kernel (which shares SMs with GEMM CTAs)
+  const int NT = (int)blockDim.x;
   const UpdChunk ch = chunks[ci];
   const UpdSegment sg = segs[ch.seg];
   const UpdHyper h = ht.h[sg.hyper];
@@ -322,12 +322,14 @@ __device__ __forceinline__ bool wait_peer_flags(const CommCtx& c, int slot, uint
   return ok_flag != 0;
 }
 
-// The CTAs are small on purpose (BUCKET_THREADS threads, about 12 K registers, 264 bytes of shared memory): one of them fits next to
-// a resident tcgen05 GEMM CTA (192 threads x 232 registers, all but about 1.7 KB of the shared memory), so the exchange proceeds
-// while the backward pass keeps every SM busy.  With the 512-thread form the launches could only run between GEMMs.
-constexpr int BUCKET_THREADS = 128;
+// Block size of the per-bucket kernel.  Two forms were measured on BERT-base at 2 GPUs against the whole-buffer kernel after backward
+// (16.7 ms per step): 512-thread CTAs (17.4 ms; they cannot share an SM with a GEMM CTA, whose 192 threads x 232 registers leave
+// room for about 12 K registers, so they run between GEMM launches) and 128-thread CTAs that do fit next to a GEMM CTA (20.2 ms
+// with 148 CTAs, 25.1 with 64, 34.3 with 32: with so few threads too few bytes are in flight to cover the NVLink round trip, and
+// the exchange outlasts the backward pass).  The 512-thread form stays; the bucketed exchange stays off by default.
+constexpr int BUCKET_THREADS = COMM_THREADS;
 
-__global__ void __launch_bounds__(BUCKET_THREADS, 5)
+__global__ void __launch_bounds__(BUCKET_THREADS)
 bucket_allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChunk* __restrict__ chunks, int chunk0, int chunk1,
                                const UpdSegment* __restrict__ segs, const StepVars* __restrict__ vars, int bucket,
                                unsigned int* tickets, int use_multimem, int* status) {

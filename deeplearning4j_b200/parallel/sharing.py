@@ -247,8 +247,9 @@ def attach_gradient_sharing(model, mode="averaging", impl="auto", thresholdAlgor
         import os
         if buckets is None:
             # default: one whole-buffer kernel after backward.  The bucketed form was measured slower on BERT-base (2 GPUs:
-            # 16.9 - 20 ms/step against 16.6): the tcgen05 GEMMs take all shared memory of every SM, so the exchange kernels
-            # cannot co-reside with them and only run between GEMM launches, where they add their own launch and flag latency.
+            # 17.4 ms/step against 16.7): a tcgen05 GEMM CTA leaves room for about 12 K registers and 1.7 KB of shared memory on its
+            # SM, so the 512-thread exchange CTAs only run between GEMM launches, where they add their own launch and flag latency;
+            # 128-thread CTAs that do fit next to a GEMM CTA keep too few bytes in flight over NVLink (20.2 - 34.3 ms/step).
             buckets = int(os.environ.get("DL4J_EXCHANGE_BUCKETS", "1"))
         if mode == "averaging" and buckets > 1 and hasattr(model, "tc") and model.flat_shadow is not None:
             # SameDiff training state with a low-precision shadow: exchange overlapped with backward, bucket by bucket
