@@ -283,6 +283,69 @@ allreduce_update_kernel(const CommCtx c, float* __restrict__ state, const UpdChu
 }
 
 
+// ------------------------------------------------------------------------------------------------ parameter averaging
+// ParallelWrapper's classic mode with averagingFrequency > 1: every rank trained on its own for k steps, now the replicas'
+// parameters are replaced by their mean.  Rank r averages the r-th slice (sum of every replica's values by peer loads or one
+// multimem.ld_reduce, times 1 / W) and writes it into every replica (peer stores or multimem.st); after the closing barrier each
+// rank derives its own bf16 shadow from the fp32 values it now holds.
+__global__ void __launch_bounds__(COMM_THREADS)
+param_average_kernel(const CommCtx c, const UpdChunk* __restrict__ chunks, int n_chunks, const UpdSegment* __restrict__ segs,
+                     long long n_total, uint32_t epoch, unsigned int* scratch, int use_multimem, int* status) {
+  unsigned int bar = 0;
+  bool ok = true;
+  if (blockIdx.x == 0) ok = peer_barrier(c, 0, epoch, status);           // every replica's parameters are final
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok && *((volatile int*)status) == 0;
+  if (ok) {
+    const float inv = 1.f / (float)c.world;
+    const long long n4 = n_total / 4;
+    const long long lo = n4 * c.rank / c.world, hi = n4 * (c.rank + 1) / c.world;
+    for (long long v = lo + blockIdx.x * (long long)COMM_THREADS + threadIdx.x; v < hi; v += (long long)gridDim.x * COMM_THREADS) {
+      const long long i = 4 * v;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (use_multimem) {
+        a = multimem_ld_reduce_f4(c.mc_params + i);
+      } else {
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < c.world) {
+            const float4 t = ld_peer_f4(c.params[(c.rank + r) % c.world] + i);
+            a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+          }
+      }
+      a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+      if (use_multimem) {
+        multimem_st_f4(c.mc_params + i, a);
+      } else {
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < c.world) *reinterpret_cast<float4*>(c.params[(c.rank + r) % c.world] + i) = a;
+      }
+    }
+    if (c.rank == c.world - 1 && blockIdx.x == 0)                          // the tail that is not a multiple of four elements
+      for (long long i = n4 * 4 + threadIdx.x; i < n_total; i += COMM_THREADS) {
+        float a = 0.f;
+        for (int r = 0; r < c.world; ++r) a += ld_peer_f(c.params[r] + i);
+        a *= inv;
+        for (int r = 0; r < c.world; ++r) c.params[r][i] = a;
+      }
+    __threadfence_system();
+  }
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok;
+  if (blockIdx.x == 0 && ok) ok = peer_barrier(c, 1, epoch, status);      // every replica holds every slice
+  ok = grid_barrier(scratch, gridDim.x * (++bar), status) && ok && *((volatile int*)status) == 0;
+  __nv_bfloat16* my_shadow = c.shadow[c.rank];
+  if (ok && my_shadow) {
+    const float* my_params = c.params[c.rank];
+    for (int ci = blockIdx.x; ci < n_chunks; ci += gridDim.x) {
+      const UpdChunk ch = chunks[ci];
+      const UpdSegment sg = segs[ch.seg];
+      const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
+      for (int e = threadIdx.x; e < ch.count; e += COMM_THREADS) my_shadow[sh0 + e] = __float2bfloat16(__ldcg(my_params + ch.offset + e));
+    }
+  }
+}
+
+
 // ------------------------------------------------------------------------------------------------ K2, per bucket
 // Dense averaging bucket by bucket, so that the exchange of the layers whose gradients are already final runs while
 // the backward pass of the earlier layers is still computing (the reference steps only once the whole gradient is
@@ -817,6 +880,29 @@ DL4J_API int dl4j_allreduce_update(const void* comm_args, float* state, const vo
                   (void*)&n_total, (void*)&epoch, (void*)&sc, (void*)&use_multimem, (void*)&status};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)allreduce_update_kernel, dim3(grid), dim3(COMM_THREADS), args, 0, stream);
   return (int)e;
+}
+
+
+// Mean of the replicas' parameters written into every replica (+ this rank's bf16 shadow); cooperative launch, bounded waits.
+DL4J_API int dl4j_param_average(const void* comm_args, const void* chunks, int n_chunks, const void* segs, long long n_total,
+                                unsigned int epoch, void* scratch, int use_multimem, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const HostCommArgs* a = reinterpret_cast<const HostCommArgs*>(comm_args);
+  if (a->world < 1 || a->world > MAX_RANKS || n_total < 0) return -DL4J_ERR_BAD_ARG;
+  if (use_multimem && !a->mc_params) return -DL4J_ERR_BAD_ARG;
+  CommCtx c = make_ctx(a);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* status = dl4j_status_word(dev);
+  const int grid = coop_grid(param_average_kernel, COMM_THREADS);
+  if (grid < 1) return -DL4J_ERR_BAD_ARG;
+  cudaMemsetAsync(scratch, 0, 16, stream);
+  const UpdChunk* ch = reinterpret_cast<const UpdChunk*>(chunks);
+  const UpdSegment* sg = reinterpret_cast<const UpdSegment*>(segs);
+  unsigned int* sc = reinterpret_cast<unsigned int*>(scratch);
+  void* args[] = {(void*)&c, (void*)&ch, (void*)&n_chunks, (void*)&sg, (void*)&n_total, (void*)&epoch, (void*)&sc, (void*)&use_multimem,
+                  (void*)&status};
+  return (int)cudaLaunchCooperativeKernel((void*)param_average_kernel, dim3(grid), dim3(COMM_THREADS), args, 0, stream);
 }
 
 

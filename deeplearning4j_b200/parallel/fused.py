@@ -196,6 +196,27 @@ class FusedSharing:
         upd._fused_zeroes_grads = True
         upd._shadow_fresh = self.shadow is not None
 
+    def average_parameters(self):
+        """Classic parameter averaging (``averagingFrequency > 1``): every replica's parameters become the mean over the replicas,
+        in one cooperative launch over peer memory; the bf16 shadow follows in the same kernel."""
+        upd = self.updater
+        t = native.update_tables(upd, 0, 0, upd.shadow_offsets)
+        if t is None:
+            raise RuntimeError("updater configuration is not supported by the fused kernel")
+        if not hasattr(self.lib.dl4j_param_average, "_typed"):
+            vp, i32, i64, u32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint
+            self.lib.dl4j_param_average.argtypes = [vp, vp, i32, vp, i64, u32, vp, i32, vp]
+            self.lib.dl4j_param_average.restype = i32
+            self.lib.dl4j_param_average._typed = True
+        self.status.check()
+        self.epoch += 1
+        rc = self.lib.dl4j_param_average(ctypes.byref(self.args), native._ptr(t["chunks"]), t["n_chunks"], native._ptr(t["segs_dev"]),
+                                         self.params.numel(), self.epoch, native._ptr(self.scratch), 1 if self.use_multimem else 0,
+                                         native._stream())
+        native._check(rc, "dl4j_param_average")
+        self.status.snapshot()
+        upd._shadow_fresh = self.shadow is not None
+
     def threshold_share(self, iteration, epoch, tau, form=None):
         """Shared gradients in one launch: updater -> residual -> encode -> exchange -> decode sum -> apply (+ bf16 shadow).
         ``form``: 1 = bitmap, 0 = index list, None = chosen from the density the previous step reported (list when at most one

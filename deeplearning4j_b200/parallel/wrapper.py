@@ -100,7 +100,16 @@ class ParallelWrapper:
             elif self.averagingFrequency <= 1:
                 self.sharing = attach_gradient_sharing(target, "averaging", impl, group=group)
             else:
-                from .sharing import GradientSharing
+                from .sharing import GradientSharing, _Target, _rehome
+                from .fused import FusedSharing, SymmetricAllocator, symmetric_available
+                self._fused_avg = None
+                if impl in ("auto", "fused") and _Target(target).params.is_cuda and symmetric_available():
+                    # parameters (and gradients, shadow) move into symmetric memory so that the averaging is one kernel over
+                    # peer memory instead of a library all-reduce followed by a divide and a shadow refresh
+                    alloc = SymmetricAllocator(group)
+                    _rehome(target, alloc)
+                    tt = _Target(target)
+                    self._fused_avg = FusedSharing(tt.params, tt.grads, tt.shadow, tt.updater, alloc)
                 GradientSharing(target, group).broadcast_parameters(0)
                 target.gradient_hook = self._param_averaging_hook
         self._local_iter = 0
@@ -120,12 +129,16 @@ class ParallelWrapper:
         t.updater.update(it, ep)
         self._local_iter += 1
         if self._local_iter % self.averagingFrequency == 0:
-            dist.all_reduce(t.params, group=self.group)
-            t.params.div_(self.world)
+            if getattr(self, "_fused_avg", None) is not None:
+                self._fused_avg.average_parameters()
+            else:
+                dist.all_reduce(t.params, group=self.group)
+                t.params.div_(self.world)
             if self.averageUpdaters and t.updater.state.numel():
                 dist.all_reduce(t.updater.state, group=self.group)
                 t.updater.state.div_(self.world)
-            t.refresh_shadow()
+            if getattr(self, "_fused_avg", None) is None:
+                t.refresh_shadow()
         if not getattr(t.updater, "_fused_zeroes_grads", False) or not t.params.is_cuda:
             t.grads.zero_()
         return True

@@ -156,6 +156,42 @@ def bucketed_case(graphs, updater_fn, buckets=5, steps=7):
     return d, ha.n_buckets, early
 
 
+def param_average_case(bf16, steps=7, freq=3):
+    """ParallelWrapper AVERAGING with averagingFrequency 3: the fused parameter-averaging kernel against the library all-reduce path
+    (same data per rank, so the two wrappers must stay equal up to summation order) and equal replicas after an averaging step."""
+    from deeplearning4j_b200 import nn
+    from deeplearning4j_b200.ops import native
+    from deeplearning4j_b200.parallel.wrapper import ParallelWrapper, TrainingMode
+    rank = dist.get_rank()
+    a, b = make_net(rank, nn.Adam(1e-3), bf16), make_net(rank, nn.Adam(1e-3), bf16)
+    wa = ParallelWrapper.Builder(a).workers(dist.get_world_size()).trainingMode(TrainingMode.AVERAGING).averagingFrequency(freq).build()
+    wb = ParallelWrapper(b, workers=dist.get_world_size(), trainingMode=TrainingMode.AVERAGING, averagingFrequency=freq, impl="nccl") \
+        if "impl" in ParallelWrapper.__init__.__code__.co_varnames else None
+    assert getattr(wa, "_fused_avg", None) is not None, "the fused averaging path was not taken"
+    if wb is not None:
+        assert getattr(wb, "_fused_avg", None) is None
+        assert torch.equal(a.flat_params, b.flat_params)
+    worst = 0.0
+    for step in range(steps):
+        x, y = data(rank, step)
+        a.fit(x, y)
+        if wb is not None:
+            b.fit(x, y)
+            worst = max(worst, float((a.flat_params - b.flat_params).abs().max()))
+        if (step + 1) % freq == 0:
+            torch.cuda.synchronize()
+            assert gather_equal(a.flat_params), f"replicas differ after the averaging step {step}"
+            if a.flat_shadow is not None:
+                ref = a.flat_shadow.float()
+                assert gather_equal(ref)
+        elif step % freq == 0 and step > 0:
+            assert not gather_equal(a.flat_params), "replicas should drift between averaging steps (different data per rank)"
+    torch.cuda.synchronize()
+    native.check_status()
+    assert worst < 2e-6, worst
+    return worst
+
+
 def timeout_case():
     """Rank 1 skips a step: rank 0's peer wait must expire and report through the status word, leaving the
     context usable."""
@@ -209,6 +245,9 @@ def main():
         for graphs in (False, True):
             for upd in (lambda: nn.Adam(1e-3), lambda: nn.Nesterovs(0.05, 0.9)):
                 res[("bucketed", graphs, upd().JAVA)] = bucketed_case(graphs, upd)
+    if what in ("all", "paramavg"):
+        for bf16 in (False, True):
+            res[("paramavg", bf16)] = param_average_case(bf16)
     if what == "timeout":
         timeout_case()
     if dist.get_rank() == 0:

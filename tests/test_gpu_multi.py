@@ -36,5 +36,9 @@ def test_bucketed_exchange_overlapped_with_backward_matches_nccl():
     _run("bucketed", port=29714)
 
 
+def test_fused_parameter_averaging_matches_the_library_path():
+    _run("paramavg", port=29715)
+
+
 def test_bounded_peer_wait_reports_timeout():
     _run("timeout", port=29713, extra_env={"NCCL_NVLS_ENABLE": "0"})
