@@ -658,7 +658,9 @@ static int gemm_impl(const void* A, const void* B, void* C, void* aux, const voi
     r = encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * esz, out_fp32 ? 32 : 64, 32, nb1, nb2, c_bs[0] * esz,
                   c_bs[1] * esz, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
     if (r == 0) p.tma_store = 1;
-    static const int aux_by_tma = [] { const char* e = getenv("DL4J_GEMM_AUX_TMA"); return e ? atoi(e) : 0; }();
+    // DL4J_GEMM_AUX_TMA=0: the pre-activation is written straight from registers instead of through a staging slab; measured 4 %
+    // slower on the BERT-base step (18.26 against 17.58 ms on the same box), so the staged form is the default
+    static const int aux_by_tma = [] { const char* e = getenv("DL4J_GEMM_AUX_TMA"); return e ? atoi(e) : 1; }();
     if (r == 0 && aux && aux_by_tma) {
       r = encode_2d(&tx, aux, (uint64_t)N, (uint64_t)M, (uint64_t)ld_aux * 2, 64, 32, 1, 1, 0, 0);
       if (r == 0) p.tma_aux = 1; else p.tma_store = 0;

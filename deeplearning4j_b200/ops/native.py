@@ -564,6 +564,9 @@ def linear(x, W, b, activation):
 
 
 # =========================================================================== layer norm
+_LN_ONE_PASS = os.environ.get("DL4J_LN_BWD_ONEPASS", "0") == "1"
+
+
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gain, bias, eps, res=None):
@@ -617,9 +620,21 @@ class _LayerNormFn(torch.autograd.Function):
             return t, t
         gacc, gret = acc_for(gain)
         bacc, bret = acc_for(bias)
-        rc = l.dl4j_layer_norm_bwd(_ptr(dy2), _ptr(x2), _ptr(g32), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(gacc), _ptr(bacc),
-                                   rows, C, _DT[x2.dtype], _stream())
-        _check(rc, "dl4j_layer_norm_bwd")
+        if _LN_ONE_PASS and C <= 1024 and C % 8 == 0 and all(t is None or t.data_ptr() % 16 == 0 for t in (dy2, x2, dx, g32)):
+            # one kernel: dx and the per-block partial sums of dgain / dbias from a single read of dy and x, summed in block order
+            if not hasattr(l.dl4j_layer_norm_bwd_noalloc, "_typed"):
+                vp = ctypes.c_void_p
+                l.dl4j_layer_norm_bwd_noalloc.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                                          ctypes.c_int, vp]
+                l.dl4j_layer_norm_bwd_noalloc.restype = ctypes.c_int
+                l.dl4j_layer_norm_bwd_noalloc._typed = True
+            rc = l.dl4j_layer_norm_bwd_noalloc(_ptr(dy2), _ptr(x2), _ptr(g32), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(gacc), _ptr(bacc),
+                                               rows, C, _DT[x2.dtype], 1, _stream())
+            _check(rc, "dl4j_layer_norm_bwd_noalloc")
+        else:
+            rc = l.dl4j_layer_norm_bwd(_ptr(dy2), _ptr(x2), _ptr(g32), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(gacc), _ptr(bacc),
+                                       rows, C, _DT[x2.dtype], _stream())
+            _check(rc, "dl4j_layer_norm_bwd")
         if gret is not None:
             gret = gret.reshape(gain.shape).to(gain.dtype)
         if bret is not None:
