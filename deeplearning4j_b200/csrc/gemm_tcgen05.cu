@@ -389,18 +389,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                            pack2(v[8 * j + 4], v[8 * j + 5], p.fmt), pack2(v[8 * j + 6], v[8 * j + 7], p.fmt));
                 *reinterpret_cast<uint4*>(slab_aux + (((hf * 4 + j) ^ sw) << 4)) = u;
               }
-            } else if (p.aux != nullptr && row_ok) {
-              // pre-activation straight from registers: each thread writes the 64 contiguous bytes of its own row, which leaves
-              // both staging slabs to the result so that one TMA store is always in flight while the next slab fills
-              uint16_t* a = reinterpret_cast<uint16_t*>(p.aux) + (long)row * p.ld_aux + col0;
-              if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  reinterpret_cast<uint4*>(a)[j] = make_uint4(pack2(v[8 * j], v[8 * j + 1], p.fmt), pack2(v[8 * j + 2], v[8 * j + 3], p.fmt),
-                                                              pack2(v[8 * j + 4], v[8 * j + 5], p.fmt), pack2(v[8 * j + 6], v[8 * j + 7], p.fmt));
-              } else {
-                for (int j = 0; j < 32 && col0 + j < p.N; ++j) a[j] = (uint16_t)(pack2(v[j], 0.f, p.fmt) & 0xffff);
-              }
             }
             if (p.act != 0) apply_act32(v, p.act);
             if (p.residual != nullptr && lead_split && row_ok) {
@@ -658,10 +646,7 @@ static int gemm_impl(const void* A, const void* B, void* C, void* aux, const voi
     r = encode_2d(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * esz, out_fp32 ? 32 : 64, 32, nb1, nb2, c_bs[0] * esz,
                   c_bs[1] * esz, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
     if (r == 0) p.tma_store = 1;
-    // DL4J_GEMM_AUX_TMA=0: the pre-activation is written straight from registers instead of through a staging slab; measured 4 %
-    // slower on the BERT-base step (18.26 against 17.58 ms on the same box), so the staged form is the default
-    static const int aux_by_tma = [] { const char* e = getenv("DL4J_GEMM_AUX_TMA"); return e ? atoi(e) : 1; }();
-    if (r == 0 && aux && aux_by_tma) {
+    if (r == 0 && aux) {
       r = encode_2d(&tx, aux, (uint64_t)N, (uint64_t)M, (uint64_t)ld_aux * 2, 64, 32, 1, 1, 0, 0);
       if (r == 0) p.tma_aux = 1; else p.tma_store = 0;
     }
