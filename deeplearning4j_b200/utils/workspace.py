@@ -221,6 +221,67 @@ class MemoryWorkspace:
         return a <= t.data_ptr() < b
 
 
+class NativeMemoryWorkspace(MemoryWorkspace):
+    """The same policies over the native arena (``csrc/arena.cu`` through ``utils/arena.py``): the slab, the bump pointer, the
+    spill blocks and the learned high-water mark live in the library; tensors are zero-copy views of arena addresses.  Chosen by
+    ``Nd4j.getWorkspaceManager().createNewWorkspace(..., native=True)`` or ``DL4J_NATIVE_WORKSPACES=1``."""
+
+    def __init__(self, configuration=None, id="default", device=None):
+        from .arena import DEVICE, HOST, PINNED, NativeArena
+        dev = torch.device(device) if device is not None else torch.device("cpu")
+        conf = configuration or WorkspaceConfiguration()
+        kind = DEVICE if dev.type == "cuda" else (PINNED if conf.policyLocation == "MMAP" else HOST)
+        self.arena = NativeArena(kind, 0)
+        super().__init__(conf, id, dev)
+
+    def getCurrentSize(self): return self.arena.stats()["capacity"]
+    def getCurrentOffset(self): return self.arena.stats()["offset"]
+    def getSpilledSize(self): return self.arena.stats()["spilledBytes"]
+
+    def _allocate(self, nbytes):
+        nbytes = int(nbytes)
+        if self.conf.maxSize and nbytes > self.conf.maxSize:
+            nbytes = self.conf.maxSize
+        self.arena.resize(max(nbytes, _ALIGN))
+        self.slab = True                 # marks "initialised" for the base class's spill-policy check
+
+    def alloc(self, shape, dtype=torch.float32, initialize=False):
+        dtype = dtype.to_torch() if isinstance(dtype, DataType) else dtype
+        numel = 1
+        for s_ in shape:
+            numel *= int(s_)
+        padded = (numel * torch.empty(0, dtype=dtype).element_size() + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.cycle_allocations += padded
+        allow = not (self.conf.policySpill == SpillPolicy.FAIL and self.slab is not None)
+        try:
+            return self.arena.tensor(tuple(shape), dtype, allowSpill=allow, zero=initialize)
+        except MemoryError as e:
+            raise MemoryError(f"workspace '{self.id}': {e}") from None
+
+    def notifyScopeLeft(self):
+        last = self._open == 1
+        super().notifyScopeLeft()        # learning policy may call _allocate -> arena.resize, which needs the cycle closed first
+        return self
+
+    def notifyScopeEntered(self):
+        if self._open == 0:
+            self.arena.reset()
+        return super().notifyScopeEntered()
+
+    def initializeWorkspace(self):
+        self.arena.reset()
+        super().initializeWorkspace()
+
+    def destroyWorkspace(self, extended=True):
+        self.arena.reset()
+        self.arena.resize(0)
+        self.slab = None
+        self.offset = self.cycle_allocations = 0
+
+    __enter__ = notifyScopeEntered
+    close = notifyScopeLeft
+
+
 class _TLS(threading.local):
     current = None
 
@@ -252,8 +313,12 @@ class BasicWorkspaceManager:
 
     def setDefaultWorkspaceConfiguration(self, c): self.defaultConfiguration = c
 
-    def createNewWorkspace(self, configuration=None, id=None, device=None):
-        ws = MemoryWorkspace(configuration or self.defaultConfiguration, id or f"ws-{len(self._map())}", device)
+    def createNewWorkspace(self, configuration=None, id=None, device=None, native=None):
+        import os
+        if native is None:
+            native = os.environ.get("DL4J_NATIVE_WORKSPACES", "0") == "1"
+        cls = NativeMemoryWorkspace if native else MemoryWorkspace
+        ws = cls(configuration or self.defaultConfiguration, id or f"ws-{len(self._map())}", device)
         self._map()[ws.id] = ws
         return ws
 
