@@ -60,6 +60,8 @@ def parse_attribute(buf):
         return name, pw.packed_varints(a.get(8, []))
     if typ == 8:
         return name, [pw.string(s) for s in a.get(9, [])]
+    if typ == 5 or (typ == 0 and 6 in a):                            # GRAPH: the body of an If / Loop node
+        return name, {"__graph__": parse_graph(a[6][0])}
     return name, None
 
 
@@ -78,6 +80,18 @@ def parse_value_info(buf):
                     dd = pw.decode(d)
                     shape.append(pw.signed(dd[1][0]) if 1 in dd else -1)
     return name, shape, elem
+
+
+def parse_graph(buf):
+    g = pw.decode(buf)
+    nodes = []
+    for nb in g.get(1, []):
+        n = pw.decode(nb)
+        nodes.append({"inputs": [pw.string(s) for s in n.get(1, [])], "outputs": [pw.string(s) for s in n.get(2, [])],
+                      "name": pw.string(n[3][0]) if 3 in n else "", "op": pw.string(n[4][0]),
+                      "attrs": dict(parse_attribute(a) for a in n.get(5, []))})
+    return {"nodes": nodes, "initializers": dict(parse_tensor(t) for t in g.get(5, [])), "inputs": [parse_value_info(v) for v in g.get(11, [])],
+            "outputs": [parse_value_info(v)[0] for v in g.get(12, [])], "opset": 13}
 
 
 def parse_model(data):
@@ -212,6 +226,103 @@ OP_MAPPERS = {
     "Gelu": lambda sd, ctx, n, x: sd._op("precise_gelu" if n["attrs"].get("approximate", "none") == "tanh" else "gelu_erf", [x[0]]),
     "Shape": lambda sd, ctx, n, x: sd._op("shape_of", [x[0]]),
 }
+
+
+# ----------------------------------------------------------------------------- control flow: If / Loop with sub-graphs
+class _SubGraph:
+    """A body graph of an If / Loop node imported into its own SameDiff.  Names that the body reads from the enclosing graph
+    (ONNX sub-graphs see the outer scope) become placeholders and are handed in at every call."""
+
+    def __init__(self, graph, trainable=False):
+        produced = set(graph["initializers"]) | {i[0] for i in graph["inputs"]}
+        for n in graph["nodes"]:
+            produced.update(o for o in n["outputs"] if o)
+        self.captured = []
+        for n in graph["nodes"]:
+            for i in _node_reads(n):
+                if i and i not in produced and i not in self.captured:
+                    self.captured.append(i)
+        self.inputs = [i[0] for i in graph["inputs"] if i[0] not in graph["initializers"]]
+        self.outputs = list(graph["outputs"])
+        g = dict(graph)
+        g["inputs"] = list(graph["inputs"]) + [(c, None, 1) for c in self.captured]
+        self.sd = OnnxFrameworkImporter(trainable=False)._build(g)
+
+    def run(self, inputs, captured):
+        ph = dict(zip(self.inputs, inputs))
+        ph.update(zip(self.captured, captured))
+        known = {k: v for k, v in ph.items()}
+        out = self.sd.output(known, *self.outputs)
+        return [out[o].t if hasattr(out[o], "t") else out[o] for o in self.outputs]
+
+
+def _node_reads(n):
+    """Names a node reads, including what its own sub-graphs read from outside themselves."""
+    reads = [i for i in n["inputs"] if i]
+    for v in n["attrs"].values():
+        if isinstance(v, dict) and "__graph__" in v:
+            g = v["__graph__"]
+            inner = set(g["initializers"]) | {i[0] for i in g["inputs"]}
+            for m in g["nodes"]:
+                inner.update(o for o in m["outputs"] if o)
+            for m in g["nodes"]:
+                reads += [i for i in _node_reads(m) if i not in inner]
+    return reads
+
+
+def _register_control_flow():
+    from ..ops.registry import has, op
+    if has("onnx.If"):
+        return
+
+    @op("onnx.If", n_out=-1, group="onnx_import")
+    def onnx_if(cond, *captured, then_branch=None, else_branch=None, n_then=0, **kw):
+        taken, caps = (then_branch, captured[:n_then]) if bool(cond.reshape(-1)[0]) else (else_branch, captured[n_then:])
+        return tuple(taken.run([], caps))
+
+    @op("onnx.Loop", n_out=-1, group="onnx_import")
+    def onnx_loop(*args, body=None, n_carried=0, has_trip=True, has_cond=True, **kw):
+        k = 0
+        trip = None
+        cond = True
+        if has_trip:
+            trip, k = int(args[0].reshape(-1)[0]), 1
+        if has_cond:
+            cond, k = bool(args[k].reshape(-1)[0]), k + 1
+        carried = list(args[k:k + n_carried])
+        captured = list(args[k + n_carried:])
+        n_scan = len(body.outputs) - 1 - n_carried
+        scans = [[] for _ in range(n_scan)]
+        it = 0
+        while cond and (trip is None or it < trip):
+            outs = body.run([torch.tensor(it, dtype=torch.int64), torch.tensor(cond)] + carried, captured)
+            cond = bool(outs[0].reshape(-1)[0])
+            carried = list(outs[1:1 + n_carried])
+            for s_, o in zip(scans, outs[1 + n_carried:]):
+                s_.append(o)
+            it += 1
+            if it > 1_000_000:
+                raise RuntimeError("onnx Loop: more than 1e6 iterations")
+        return tuple(carried) + tuple(torch.stack(s_) if s_ else torch.zeros(0) for s_ in scans)
+
+
+def _if(sd, ctx, n, x):
+    tb, eb = _SubGraph(n["attrs"]["then_branch"]["__graph__"]), _SubGraph(n["attrs"]["else_branch"]["__graph__"])
+    caps = [ctx["lookup"](c) for c in tb.captured] + [ctx["lookup"](c) for c in eb.captured]
+    return sd._op("onnx.If", [x[0]] + caps, n_out=len(n["outputs"]), then_branch=tb, else_branch=eb, n_then=len(tb.captured))
+
+
+def _loop(sd, ctx, n, x):
+    body = _SubGraph(n["attrs"]["body"]["__graph__"])
+    has_trip, has_cond = bool(n["inputs"][0]), len(n["inputs"]) > 1 and bool(n["inputs"][1])
+    head = ([x[0]] if has_trip else []) + ([x[1]] if has_cond else [])
+    carried = [v for v in x[2:]]
+    caps = [ctx["lookup"](c) for c in body.captured]
+    return sd._op("onnx.Loop", head + carried + caps, n_out=len(n["outputs"]), body=body, n_carried=len(carried), has_trip=has_trip, has_cond=has_cond)
+
+
+OP_MAPPERS["If"] = _if
+OP_MAPPERS["Loop"] = _loop
 
 
 # ----------------------------------------------------------------------------- generic rules: ONNX semantics written once on tensors
@@ -616,11 +727,28 @@ class OnnxFrameworkImporter:
             with open(path_or_bytes, "rb") as f:
                 data = f.read()
         model = parse_model(data)
+        sd = self._build(model)
+        sd.metadata["onnx.outputs"] = ",".join(model["outputs"])
+        sd.metadata["onnx.opset"] = str(model["opset"])
+        self.outputs = model["outputs"]
+        return sd
+
+    def _build(self, model):
+        """A SameDiff for one graph (the model's main graph, or the body of an If / Loop node)."""
+        _register_helpers()
+        _register_onnx_ops()
+        _register_control_flow()
         unsupported = sorted({n["op"] for n in model["nodes"] if n["op"] not in OP_MAPPERS})
         if unsupported:
             raise NotImplementedError(f"ONNX import: no mapping rule for op types {unsupported}")
         sd = SameDiff.create()
         vars_, ctx = {}, {"consts": dict(model["initializers"])}
+
+        def lookup(name):
+            if name not in vars_ and name in ctx["consts"]:
+                vars_[name] = sd.constant(name, ctx["consts"][name].clone())
+            return vars_[name]
+        ctx["lookup"] = lookup
         consumed_as_const = set()
         for n in model["nodes"]:
             if n["op"] in ("Reshape", "Slice", "Squeeze", "Unsqueeze", "ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin", "Clip"):
@@ -648,9 +776,10 @@ class OnnxFrameworkImporter:
                 if name and v.name != name:
                     v = sd.renameVariable(v.name, name) or sd.getVariable(name)
                 vars_[name] = sd.getVariable(name) if sd.hasVariable(name) else v
-        sd.metadata["onnx.outputs"] = ",".join(model["outputs"])
-        sd.metadata["onnx.opset"] = str(model["opset"])
-        self.outputs = model["outputs"]
+        for o in model["outputs"]:                  # a graph output that is a plain input or initializer (Loop bodies pass values through)
+            if o not in vars_ or not sd.hasVariable(o):
+                if o in ctx["consts"]:
+                    lookup(o)
         return sd
 
 

@@ -23,6 +23,8 @@ def attr(name, v):
         return b + pw.field_bytes(4, v.encode()) + pw.field_varint(20, 3)
     if isinstance(v, (list, tuple)):
         return b + pw.field_packed_varints(8, v) + pw.field_varint(20, 7)
+    if isinstance(v, bytes):                              # an encoded GraphProto
+        return b + pw.field_bytes(6, v) + pw.field_varint(20, 5)
     raise TypeError(v)
 
 
@@ -37,9 +39,13 @@ def value_info(name, shape):
     return pw.field_string(1, name) + pw.field_bytes(2, pw.field_bytes(1, tt))
 
 
-def model(nodes, inits, inputs, outputs):
+def graph(nodes, inits, inputs, outputs):
     g = b"".join(pw.field_bytes(1, n) for n in nodes) + pw.field_string(2, "g") + b"".join(pw.field_bytes(5, t) for t in inits)
-    g += b"".join(pw.field_bytes(11, value_info(n, s)) for n, s in inputs) + b"".join(pw.field_bytes(12, value_info(n, s)) for n, s in outputs)
+    return g + b"".join(pw.field_bytes(11, value_info(n, s)) for n, s in inputs) + b"".join(pw.field_bytes(12, value_info(n, s)) for n, s in outputs)
+
+
+def model(nodes, inits, inputs, outputs):
+    g = graph(nodes, inits, inputs, outputs)
     return pw.field_varint(1, 8) + pw.field_bytes(7, g) + pw.field_bytes(8, pw.field_string(1, "") + pw.field_varint(2, 13))
 
 
@@ -166,3 +172,22 @@ def test_lstm_and_gru_nodes_match_torch_modules():
     assert torch.allclose(r["Yh"], h, atol=1e-5) and torch.allclose(r["Yc"], c, atol=1e-5)
     yg, hg = gru(x)
     assert torch.allclose(r["G"][:, 0], yg, atol=1e-5) and torch.allclose(r["Gh"], hg, atol=1e-5)
+
+
+def test_if_and_loop_nodes_with_sub_graphs_that_read_the_outer_scope():
+    then_g = graph([node("Mul", ["x", "two"], ["t_out"])], [tensor("two", np.asarray(2.0, np.float32))], [], [("t_out", [])])
+    else_g = graph([node("Sub", ["x", "one"], ["e_out"])], [], [], [("e_out", [])])            # "one" and "x" come from the outer graph
+    body = graph([node("Cast", ["it"], ["it_f"], to=1), node("Mul", ["x", "it_f"], ["term"]), node("Add", ["acc", "term"], ["acc_out"]),
+                  node("Identity", ["cond_in"], ["cond_out"])],
+                 [], [("it", []), ("cond_in", []), ("acc", [3])], [("cond_out", []), ("acc_out", [3]), ("term", [3])])
+    nodes = [node("ReduceSum", ["x"], ["sx"], keepdims=0), node("Greater", ["sx", "zero"], ["pos"]),
+             node("If", ["pos"], ["branch"], then_branch=then_g, else_branch=else_g),
+             node("Loop", ["trip", "", "acc0"], ["acc_final", "terms"], body=body)]
+    inits = [tensor("zero", np.asarray(0.0, np.float32)), tensor("one", np.asarray(1.0, np.float32)), tensor("trip", np.asarray(4, np.int64)),
+             tensor("acc0", np.zeros(3, np.float32))]
+    raw = model(nodes, inits, [("x", [3])], [("branch", [3]), ("acc_final", [3]), ("terms", [4, 3])])
+    sd = OnnxFrameworkImporter(trainable=False).runImport(raw)
+    for x in (torch.tensor([1.0, 2.0, 3.0]), torch.tensor([-1.0, -2.0, 0.5])):
+        r = {k: v.t for k, v in sd.output({"x": x}, "branch", "acc_final", "terms").items()}
+        assert torch.equal(r["branch"], x * 2 if float(x.sum()) > 0 else x - 1)
+        assert torch.equal(r["acc_final"], x * (0 + 1 + 2 + 3)) and tuple(r["terms"].shape) == (4, 3) and torch.equal(r["terms"][2], x * 2)
