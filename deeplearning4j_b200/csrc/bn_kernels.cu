@@ -46,10 +46,41 @@ __device__ __forceinline__ void bn_block_reduce(const float* s, const float* q, 
   }
 }
 
+struct BnFinalize {
+  const float* gamma; const float* beta; float* run_mean; float* run_stat; int use_log_std; float decay, eps, inv_rows;
+  float* save_mean; float* save_invstd; float* scale; float* shift; const float* pre_bias;
+};
+
+__device__ __forceinline__ void bn_finalize_channel(const float* sums, const BnFinalize& f, int c, int C) {
+  const float* gamma = f.gamma; const float* beta = f.beta; float* run_mean = f.run_mean; float* run_stat = f.run_stat;
+  const int use_log_std = f.use_log_std; const float decay = f.decay, eps = f.eps, inv_rows = f.inv_rows;
+  float* save_mean = f.save_mean; float* save_invstd = f.save_invstd; float* scale = f.scale; float* shift = f.shift;
+  const float* pre_bias = f.pre_bias;
+  const float mean = __ldcg(sums + c) * inv_rows;
+  const float var = fmaxf(__ldcg(sums + C + c) * inv_rows - mean * mean, 0.f);
+  const float invstd = rsqrtf(var + eps);
+  const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
+  save_mean[c] = mean;
+  save_invstd[c] = invstd;
+  scale[c] = g * invstd;
+  shift[c] = b - mean * g * invstd;
+  // pre_bias: bias of the producing convolution, left out of x because the batch mean cancels it; the running mean
+  // (used at inference, where it does not cancel) still has to see it
+  if (run_mean) run_mean[c] = decay * run_mean[c] + (1.f - decay) * (mean + (pre_bias ? pre_bias[c] : 0.f));
+  if (run_stat) {
+    const float old_var = use_log_std ? exp10f(2.f * run_stat[c]) : run_stat[c];
+    const float nv = decay * old_var + (1.f - decay) * var;
+    run_stat[c] = use_log_std ? 0.5f * log10f(fmaxf(nv, 1e-30f)) : nv;
+  }
+}
+
 // sums[c] = sum_r x[r, c], sums[C + c] = sum_r x[r, c]^2.  C / 8 is a power of two <= 256, so a thread keeps one channel
 // vector for its whole row range and accumulates in registers.
+// With `ticket` the block that finishes last also turns the sums into mean / invstd / scale / shift and updates the running
+// statistics (one launch less per batch-norm layer than a separate per-channel kernel).
 __global__ void __launch_bounds__(BN_THREADS)
-bn_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ sums, long long rows, int C, long long rows_per_block) {
+bn_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ sums, long long rows, int C, long long rows_per_block,
+                unsigned int* ticket, const BnFinalize fin) {
   const int cv_n = C >> 3;
   const int cv = threadIdx.x & (cv_n - 1), rl = threadIdx.x / cv_n;
   const int step = BN_THREADS / cv_n;
@@ -76,35 +107,20 @@ bn_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ sums, l
     }
   }
   bn_block_reduce(s, q, sums, C, cv_n);
+  if (ticket == nullptr) return;
+  __shared__ unsigned int my_ticket;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) my_ticket = atomicAdd(ticket, 1u);
+  __syncthreads();
+  if (my_ticket != gridDim.x - 1) return;
+  __threadfence();
+  for (int c = threadIdx.x; c < C; c += BN_THREADS) bn_finalize_channel(sums, fin, c, C);
 }
 
 // Per channel: batch mean / biased variance -> invstd, scale, shift; running statistics updated in place with
 // DL4J's rule  global = decay * global + (1 - decay) * batch  (the variance kept as log10 of the standard deviation
 // when use_log_std is set).
-__global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                   float* __restrict__ run_mean, float* __restrict__ run_stat, int use_log_std, float decay, float eps,
-                                   float inv_rows, float* __restrict__ save_mean, float* __restrict__ save_invstd,
-                                   float* __restrict__ scale, float* __restrict__ shift, const float* __restrict__ pre_bias, int C) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  const float mean = sums[c] * inv_rows;
-  const float var = fmaxf(sums[C + c] * inv_rows - mean * mean, 0.f);
-  const float invstd = rsqrtf(var + eps);
-  const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
-  save_mean[c] = mean;
-  save_invstd[c] = invstd;
-  scale[c] = g * invstd;
-  shift[c] = b - mean * g * invstd;
-  // pre_bias: bias of the producing convolution, left out of x because the batch mean cancels it; the running mean
-  // (used at inference, where it does not cancel) still has to see it
-  if (run_mean) run_mean[c] = decay * run_mean[c] + (1.f - decay) * (mean + (pre_bias ? pre_bias[c] : 0.f));
-  if (run_stat) {
-    const float old_var = use_log_std ? exp10f(2.f * run_stat[c]) : run_stat[c];
-    const float nv = decay * old_var + (1.f - decay) * var;
-    run_stat[c] = use_log_std ? 0.5f * log10f(fmaxf(nv, 1e-30f)) : nv;
-  }
-}
-
 // y = act(x * scale + shift [+ res])
 __global__ void __launch_bounds__(BN_THREADS)
 bn_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res, const float* __restrict__ scale,
@@ -261,7 +277,7 @@ static inline int bn_grid_elems(long long n_vec) {
 
 using namespace dl4j;
 
-// Training forward.  work: 4 * C floats of scratch laid out as [sums(2C) | scale(C) | shift(C)]; scale / shift and
+// Training forward.  work: 4 * C + 8 floats of scratch laid out as [sums(2C) | ticket(8) | scale(C) | shift(C)]; scale / shift and
 // save_mean / save_invstd are kept by the caller for the backward pass.  run_mean / run_stat may be null.
 DL4J_API int dl4j_bn_fwd_train(const void* x, const void* res, const float* gamma, const float* beta, float* run_mean, float* run_stat,
                                int use_log_std, float decay, float eps, int relu, void* y, float* save_mean, float* save_invstd,
@@ -269,14 +285,17 @@ DL4J_API int dl4j_bn_fwd_train(const void* x, const void* res, const float* gamm
   if (!bn_shape_ok(rows, C)) return -DL4J_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream_;
   float* sums = work;
-  float* scale = work + 2 * C;
-  float* shift = work + 3 * C;
-  cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st);
+  float* scale = work + 2 * C + 8;
+  float* shift = work + 3 * C + 8;
+  cudaMemsetAsync(sums, 0, sizeof(float) * (2 * C + 8), st);          // the sums and the ticket of the statistics kernel
   long long rpb;
   const int g1 = bn_grid_rows(rows, C, &rpb);
-  bn_stats_kernel<<<g1, BN_THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), sums, rows, C, rpb);
-  bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, gamma, beta, run_mean, run_stat, use_log_std, decay, eps, 1.0f / (float)rows,
-                                                      save_mean, save_invstd, scale, shift, pre_bias, C);
+  BnFinalize fin;
+  fin.gamma = gamma; fin.beta = beta; fin.run_mean = run_mean; fin.run_stat = run_stat; fin.use_log_std = use_log_std;
+  fin.decay = decay; fin.eps = eps; fin.inv_rows = 1.0f / (float)rows; fin.save_mean = save_mean; fin.save_invstd = save_invstd;
+  fin.scale = scale; fin.shift = shift; fin.pre_bias = pre_bias;
+  bn_stats_kernel<<<g1, BN_THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), sums, rows, C, rpb,
+                                             reinterpret_cast<unsigned int*>(work + 2 * C), fin);
   const long long n_vec = rows * (C >> 3);
   bn_apply_kernel<<<bn_grid_elems(n_vec), BN_THREADS, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                                                 reinterpret_cast<const __nv_bfloat16*>(res), scale, shift,
@@ -302,8 +321,8 @@ DL4J_API int dl4j_bn_bwd(const void* dy, const void* x, const void* y, const flo
   if (!bn_shape_ok(rows, C)) return -DL4J_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream_;
   float* sums = work;
-  const float* scale = work + 2 * C;
-  const float* shift = work + 3 * C;
+  const float* scale = work + 2 * C + 8;
+  const float* shift = work + 3 * C + 8;
   cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st);
   long long rpb;
   int g1 = bn_grid_rows(rows, C, &rpb);

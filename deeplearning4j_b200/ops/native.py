@@ -1175,7 +1175,7 @@ class _BnActFn(torch.autograd.Function):
         rows, C = _rows_c(x)
         y = torch.empty_like(x)
         save = torch.empty(2 * C, dtype=torch.float32, device=x.device)
-        work = torch.empty(4 * C, dtype=torch.float32, device=x.device)
+        work = torch.empty(4 * C + 8, dtype=torch.float32, device=x.device)      # [sums | ticket | scale | shift]
         g = gamma.detach().float().contiguous() if gamma is not None else None
         b = beta.detach().float().contiguous() if beta is not None else None
         rc = l.dl4j_bn_fwd_train(_ptr(x), _ptr(res), _ptr(g), _ptr(b), _ptr(run_mean), _ptr(run_stat), int(bool(use_log_std)),
