@@ -16,6 +16,7 @@ from .network import BaseNetwork, _as_tensor
 
 
 from .conf.graphconf import ElementWiseVertex
+from ..utils.crash import guard_fit
 
 
 class _VertexOwner:
@@ -323,6 +324,7 @@ class ComputationGraph(BaseNetwork):
         return float(loss + (reg if reg is not None else 0.0))
 
     # ------------------------------------------------------------------ fit
+    @guard_fit
     def fit(self, *args, **kw):
         if not self._initialized:
             self.init()

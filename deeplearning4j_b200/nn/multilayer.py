@@ -16,6 +16,7 @@ from ..nd.ndarray import INDArray, wrap
 from .conf.base import BackpropType
 from .conf.neuralnet import MultiLayerConfiguration
 from .network import BaseNetwork, _as_tensor
+from ..utils.crash import guard_fit
 
 
 class MultiLayerNetwork(BaseNetwork):
@@ -209,6 +210,7 @@ class MultiLayerNetwork(BaseNetwork):
     def clearLayerMaskArrays(self):
         self.mask_features = self.mask_labels = None
 
+    @guard_fit
     def fit(self, *args, **kw):
         """``fit(DataSetIterator[, epochs])``, ``fit(DataSet)``, ``fit(features, labels[, fmask, lmask])``."""
         if not self._initialized:
