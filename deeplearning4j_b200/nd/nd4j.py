@@ -392,7 +392,11 @@ class Nd4j:
         np.save(path, wrap(arr).numpy())
 
     @classmethod
-    def createFromNpyFile(cls, path):
+    def createFromNpyFile(cls, path, mmap=False):
+        """``mmap=True`` maps the file's data section instead of reading it (host arrays only; writes go back to the file)."""
+        if mmap:
+            from ..utils.mmap import createFromNpyFileMapped
+            return INDArray(createFromNpyFileMapped(path))
         return INDArray(torch.from_numpy(np.load(path)).to(cls._device))
 
     @classmethod
