@@ -4,7 +4,8 @@
 The reference binds each vendor runtime through JavaCPP and feeds it INDArrays.  None of those runtimes is available here, so the
 ONNX and TensorFlow runners execute the model through this framework's own importers (protobuf wire reader -> SameDiff graph ->
 native kernels); the API (construct from a path or bytes, ``exec`` / ``run`` a name -> array map, ``close``) is the reference's.
-TFLite flatbuffers and TVM compiled modules have no importer and raise on construction."""
+TFLite flatbuffers go through ``importers/tflite_import.py`` the same way.  TVM compiled modules (machine code for another
+runtime) have no importer and raise on construction."""
 from __future__ import annotations
 
 from ..nd.ndarray import INDArray
@@ -92,8 +93,39 @@ class _Unavailable:
                                   f"OnnxRuntimeRunner / GraphRunner")
 
 
-class TensorFlowLiteRunner(_Unavailable):
-    RUNTIME = "TensorFlow Lite"
+class TensorFlowLiteRunner:
+    """``TensorFlowLiteRunner.builder().modelUri(path).build()``; ``exec`` maps input tensor names to arrays and returns the model's
+    output tensors by name (``nd4j-tensorflow-lite/.../runner/TensorFlowLiteRunner.java``)."""
+
+    def __init__(self, modelUri=None, modelBytes=None):
+        from ..importers.tflite_import import TFLiteImporter
+        imp = TFLiteImporter(trainable=False)
+        self.sd = imp.runImport(modelBytes if modelBytes is not None else _read(modelUri))
+        self.inputs, self.outputs = list(imp.inputs), list(imp.outputs)
+
+    builder = staticmethod(lambda: _UriBuilder(TensorFlowLiteRunner))
+
+    def getInputs(self): return list(self.inputs)
+    def getOutputs(self): return list(self.outputs)
+
+    def exec(self, inputs: dict) -> dict:
+        res = self.sd.output(inputs, *self.outputs)
+        return {k: (v if isinstance(v, INDArray) else INDArray(v)) for k, v in res.items()}
+
+    run = exec
+
+    def close(self):
+        self.sd = None
+
+    def __enter__(self): return self
+    def __exit__(self, *a): self.close()
+
+
+class _UriBuilder:
+    def __init__(self, cls): self.cls, self.kw = cls, {}
+    def modelUri(self, u): self.kw["modelUri"] = u; return self
+    def modelBytes(self, b): self.kw["modelBytes"] = b; return self
+    def build(self): return self.cls(**self.kw)
 
 
 class TvmRunner(_Unavailable):

@@ -74,9 +74,16 @@ def _is_scalar(t):
     return isinstance(t, str) and t in _SCALARS
 
 
+def union(type_field, members):
+    """A union field: ``type_field`` names the ubyte field (declared just before it) holding the member id, ``members`` maps
+    member ids to table names."""
+    return ("union", type_field, members)
+
+
 class _Writer:
-    def __init__(self):
+    def __init__(self, schema=None):
         self.buf = bytearray()
+        self.schema = SCHEMA if schema is None else schema
 
     def pad_to(self, align, bias=0):
         """Pad so that (len(buf) + bias) is a multiple of ``align``."""
@@ -123,14 +130,17 @@ class _Writer:
         return pos
 
     def write_table(self, name, obj):
-        fields = SCHEMA[name]
+        fields = self.schema[name]
         present = []          # (field id, type, value)
-        for fid, (fname, ftype) in enumerate(fields):
+        for fid, f in enumerate(fields):
+            fname, ftype = f[0], f[1]
             v = obj.get(fname)
             if v is None:
                 continue
-            if _is_scalar(ftype) and (v == 0 or v is False):
+            if _is_scalar(ftype) and v == (f[2] if len(f) > 2 else 0):
                 continue                                     # defaults are not stored
+            if not _is_scalar(ftype) and ftype != "string" and ftype[0] == "union":
+                ftype = table(ftype[2][obj[ftype[1]]])        # the member the type field selects
             present.append((fid, ftype, v))
         # inline layout: soffset, then fields largest first
         def fsize(t):
@@ -173,16 +183,21 @@ class _Writer:
         return tpos
 
 
-def encode(root_table: str, obj: dict) -> bytes:
-    w = _Writer()
+def encode(root_table: str, obj: dict, schema=None, identifier=None) -> bytes:
+    """``schema`` defaults to the ND4J graph schema; ``identifier`` is the optional 4-byte file identifier after the root offset."""
+    w = _Writer(schema)
     w.buf.extend(b"\0\0\0\0")
+    if identifier is not None:
+        assert len(identifier) == 4
+        w.buf.extend(identifier)
     root = w.write_table(root_table, obj)
     w.patch_offset(0, root)
     return bytes(w.buf)
 
 
 class _Reader:
-    def __init__(self, data):
+    def __init__(self, data, schema=None):
+        self.schema = SCHEMA if schema is None else schema
         self.mv = memoryview(data).cast("B") if not isinstance(data, memoryview) else data
         self.data = data
 
@@ -212,15 +227,19 @@ class _Reader:
         return out
 
     def table(self, name, tpos, raw_bytes):
-        fields = SCHEMA[name]
+        fields = self.schema[name]
         vpos = tpos - struct.unpack_from("<i", self.mv, tpos)[0]
         vtsize = struct.unpack_from("<H", self.mv, vpos)[0]
         nf = (vtsize - 4) // 2
         out = {}
-        for fid, (fname, ftype) in enumerate(fields):
+        for fid, f in enumerate(fields):
+            fname, ftype = f[0], f[1]
             slot = struct.unpack_from("<H", self.mv, vpos + 4 + 2 * fid)[0] if fid < nf else 0
             if slot == 0:
-                out[fname] = (False if ftype == "bool" else 0) if _is_scalar(ftype) else None
+                if _is_scalar(ftype):
+                    out[fname] = f[2] if len(f) > 2 else (False if ftype == "bool" else 0)
+                else:
+                    out[fname] = None
                 continue
             at = tpos + slot
             if _is_scalar(ftype):
@@ -229,13 +248,16 @@ class _Reader:
                 out[fname] = self.string(self.indirect(at))
             elif ftype[0] == "table":
                 out[fname] = self.table(ftype[1], self.indirect(at), raw_bytes)
+            elif ftype[0] == "union":
+                member = ftype[2].get(out.get(ftype[1], 0))
+                out[fname] = self.table(member, self.indirect(at), raw_bytes) if member is not None else None
             else:
                 out[fname] = self.vector(ftype[1], self.indirect(at), raw_bytes)
         return out
 
 
-def decode(root_table: str, data, raw_bytes=True) -> dict:
+def decode(root_table: str, data, raw_bytes=True, schema=None) -> dict:
     """Decode ``data`` into nested dicts.  With ``raw_bytes`` byte vectors come back as zero-copy
     memoryviews and other scalar vectors as numpy arrays; otherwise everything is plain lists."""
-    r = _Reader(data)
+    r = _Reader(data, schema)
     return r.table(root_table, r.indirect(0), raw_bytes)

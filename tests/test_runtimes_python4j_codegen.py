@@ -43,8 +43,8 @@ def test_foreign_runners():
                 assert r.getInputs() and r.getOutputs()
         except TypeError:
             pass
-    with pytest.raises(NotImplementedError):
-        TensorFlowLiteRunner("model.tflite")
+    with pytest.raises(ValueError):
+        TensorFlowLiteRunner(modelBytes=b"not a flatbuffer")
     with pytest.raises(NotImplementedError):
         TvmRunner("model.so")
     assert callable(GraphRunner.builder) and pw is not None
