@@ -9,7 +9,8 @@
 // (4 gates x 16 units, each row = n bf16 values) resident in shared memory for the whole sequence, so the
 // recurrent weights are read from HBM once per launch instead of once per step.  Per step the CTA streams
 // h_{t-1} ([mb, n] bf16, L2 resident) through a multi-stage TMA ring as the M operand of tcgen05.mma
-// (M = 128 batch rows, zero filled beyond mb; N = 64 gate rows; K = n), accumulates in TMEM, and its four
+// (M = 128 batch rows, zero filled beyond mb; N = 64 gate rows; K = n) issued by three warps that take every third
+// k-block each (a single thread cannot issue MMAs fast enough for N this small), accumulates in TMEM, and its four
 // epilogue warps (one thread per batch row) apply the cell non-linearities with c_t held in registers across
 // steps, then publish their slice of h_t.  Steps are separated by a grid-wide arrive/wait on a global counter;
 // every wait is bounded and reports through the status word.
@@ -21,11 +22,20 @@ constexpr int LS_UNITS = 16;                 // hidden units per CTA
 constexpr int LS_N = 4 * LS_UNITS;           // MMA N: gate rows per CTA
 constexpr int LS_M = 128;                    // MMA M: batch rows (zero padded)
 constexpr int LS_BK = 64;                    // K elements per stage (128 bytes, SWIZZLE_128B)
-constexpr int LS_ACCS = 4;                   // independent TMEM accumulators: k-step j of every k-block adds into accumulator j,
-                                             // so consecutive MMAs do not wait on each other; the epilogue sums them
+constexpr int LS_ISSUERS = 3;                // MMA-issuing warps.  One thread gets at most one tcgen05.mma into the pipe per ~150 clocks
+                                             // whatever the instruction's shape (measured: 150 clk for N = 8 .. 256), while an
+                                             // M 128 x N 64 x K 16 instruction occupies the tensor core for ~48 clocks and N = 16 for
+                                             // less; three issuers, each with every third k-block, bring an N = 64 instruction down to ~50 clocks, and
+                                             // with the producer warp and four epilogue warps the CTA stays at 256 threads (a ninth warp
+                                             // would cut the register budget to 168 and spill the epilogue).
+constexpr int LS_ACCS = LS_ISSUERS;          // one TMEM accumulator per issuer (MMAs of different threads never share one); the
+                                             // epilogue sums them
+constexpr int LS_TMEM_COLS = 256;            // allocation sizes are powers of two >= 32: LS_ACCS x LS_N = 192 columns used
+static_assert(LS_ACCS * LS_N <= LS_TMEM_COLS, "forward accumulators exceed the TMEM allocation");
 constexpr int LS_MAX_STAGES = 16;             // ring depth is chosen at launch from the shared memory left beside the weights
 constexpr int LS_B_KB = LS_N * LS_BK * 2;    // 8 KB per k-block of resident weights
-constexpr int LS_THREADS = 192;              // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int LS_EPI_WARP0 = 1 + LS_ISSUERS; // warp 0 TMA, warps 1..3 MMA issuers, warps 4-7 epilogue
+constexpr int LS_THREADS = 32 * (LS_EPI_WARP0 + 4);
 
 struct LstmSeqParams {
   const __nv_bfloat16* zx;   // [T, mb, 4n]
@@ -37,6 +47,7 @@ struct LstmSeqParams {
   int stages, a_stage;       // TMA ring: number of stages and bytes per stage (batch rows rounded up to 8, x 128 B)
   unsigned int* counter;     // zero on entry
   int* status;
+  long long* trace;          // optional [T][32] clock64 stamps written by the middle CTA (null = off); see dl4j_lstm_set_trace
 };
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -52,6 +63,14 @@ __device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsign
     }
   }
   return true;
+}
+
+// Timeline of one CTA: slot `i` of step `s` receives this SM's clock.  Slots: 0 producer saw the step's grid barrier open,
+// 1 producer issued the step's last load, 2..17 MMA thread saw k-block (slot - 2) land (first 16 k-blocks), 18 MMA thread
+// committed the accumulator, 19 epilogue saw the accumulator, 20 after the TMEM loads, 21 after the global stores, 22 after the
+// fences, 23 after the barrier arrive.
+__device__ __forceinline__ void ls_stamp(long long* trace, int s, int slot) {
+  if (trace != nullptr && blockIdx.x == gridDim.x / 2) trace[s * 32 + slot] = clock64();
 }
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -99,12 +118,12 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
     prefetch_tmap(&tmap_w);
     for (int i = 0; i < p.stages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     mbar_init(w_full, 1);
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, (uint32_t)min(LS_ISSUERS, kblocks));      // one commit per issuer that has k-blocks
     mbar_init(acc_empty, 4);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, LS_ACCS * LS_N);
+    tmem_alloc(tmem_slot, LS_TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -130,36 +149,42 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
           __threadfence();
           fence_proxy_async_all();       // generic-proxy stores of other CTAs -> async-proxy (TMA) reads below
         }
+        ls_stamp(p.trace, s, 0);
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], (uint32_t)p.a_stage);
           tma_load_4d(a_smem + stage * p.a_stage, &tmap_h, &full_bar[stage], kb * LS_BK, 0, s, 0);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
+        ls_stamp(p.trace, s, 1);
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
+  } else if (warp < LS_EPI_WARP0) {
+    const int me = warp - 1;                      // issuer index: k-blocks me, me + LS_ISSUERS, ... of every step
+    if (lane == 0 && me < kblocks) {
       const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LS_N);
+      const uint32_t acc = tmem_base + (uint32_t)(me * LS_N);
       bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
       tc_fence_after();
-      int stage = 0;
-      uint32_t phase = 0;
       for (int s = 0; s < p.T && ok; ++s) {
         if (!mbar_wait_bounded(acc_empty, (uint32_t)((s & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = me; kb < kblocks; kb += LS_ISSUERS) {
+          const int g = s * kblocks + kb;         // position of this k-block in the producer's load sequence
+          const int stage = g % p.stages;
+          const uint32_t phase = (uint32_t)((g / p.stages) & 1);
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          if (kb < 16) ls_stamp(p.trace, s, 2 + kb);
           tc_fence_after();
           const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * p.a_stage), 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LS_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
-            umma_f16(tmem_base + (uint32_t)(k * LS_N), da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, kb > 0 ? 1u : 0u);
+            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > me || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(acc_full);
+        if (me == 0) ls_stamp(p.trace, s, 18);
       }
     }
   } else {
@@ -190,6 +215,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
         }
       }
       if (!mbar_wait_bounded(acc_full, (uint32_t)(s & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 19);
       tc_fence_after();
       uint32_t r0[32], r1[32];
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -197,7 +223,8 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       tmem_ld_32x32(taddr + 32, r1);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 1; j < LS_ACCS; ++j) {          // fold the independent partial accumulators
+      for (int j = 1; j < LS_ACCS; ++j) {          // fold the issuers' partial accumulators
+        if (j >= kblocks) break;
         uint32_t t0[32], t1[32];
         tmem_ld_32x32(taddr + j * LS_N, t0);
         tmem_ld_32x32(taddr + j * LS_N + 32, t1);
@@ -211,6 +238,8 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty);      // accumulator drained: the next step's MMAs may overwrite it
+      if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 20);
+      uint4 gp[8];                                 // activated gates, packed: stored after h_t has been published
       if (row_ok) {
         float za[16], zf[16], zo[16], zg[16];
         unpack8(zraw[0], za); unpack8(zraw[1], za + 8);
@@ -228,23 +257,31 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
           h[u] = o * tanh_fast(c[u]);
           za[u] = a; zf[u] = f; zo[u] = o; zg[u] = g;
         }
-        __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
-        uint4* gd;
-        gd = reinterpret_cast<uint4*>(grow);               gd[0] = pack8(za); gd[1] = pack8(za + 8);
-        gd = reinterpret_cast<uint4*>(grow + (long)p.n);     gd[0] = pack8(zf); gd[1] = pack8(zf + 8);
-        gd = reinterpret_cast<uint4*>(grow + 2L * p.n);      gd[0] = pack8(zo); gd[1] = pack8(zo + 8);
-        gd = reinterpret_cast<uint4*>(grow + 3L * p.n);      gd[0] = pack8(zg); gd[1] = pack8(zg + 8);
-        float4* cd = reinterpret_cast<float4*>(p.cs + ((long)t * p.mb + b) * p.n + unit0);
-#pragma unroll
-        for (int i = 0; i < LS_UNITS / 4; ++i) cd[i] = make_float4(c[4 * i], c[4 * i + 1], c[4 * i + 2], c[4 * i + 3]);
+        gp[0] = pack8(za); gp[1] = pack8(za + 8); gp[2] = pack8(zf); gp[3] = pack8(zf + 8);
+        gp[4] = pack8(zo); gp[5] = pack8(zo + 8); gp[6] = pack8(zg); gp[7] = pack8(zg + 8);
+        // h_t is what the other CTAs wait for: publish it first, then write what only the backward pass reads
         uint4* hd = reinterpret_cast<uint4*>(p.h_all + ((long)(s + 1) * p.mb + b) * p.n + unit0);
         hd[0] = pack8(h);
         hd[1] = pack8(h + 8);
       }
+      if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 21);
       __threadfence();
       fence_proxy_async_all();
       __syncwarp();
+      if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 22);
       if (lane == 0) atomicAdd(p.counter, 1u);
+      if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 23);
+      if (row_ok) {
+        __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
+        uint4* gd;
+        gd = reinterpret_cast<uint4*>(grow);               gd[0] = gp[0]; gd[1] = gp[1];
+        gd = reinterpret_cast<uint4*>(grow + (long)p.n);     gd[0] = gp[2]; gd[1] = gp[3];
+        gd = reinterpret_cast<uint4*>(grow + 2L * p.n);      gd[0] = gp[4]; gd[1] = gp[5];
+        gd = reinterpret_cast<uint4*>(grow + 3L * p.n);      gd[0] = gp[6]; gd[1] = gp[7];
+        float4* cd = reinterpret_cast<float4*>(p.cs + ((long)t * p.mb + b) * p.n + unit0);
+#pragma unroll
+        for (int i = 0; i < LS_UNITS / 4; ++i) cd[i] = make_float4(c[4 * i], c[4 * i + 1], c[4 * i + 2], c[4 * i + 3]);
+      }
     }
   }
 
@@ -252,7 +289,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, LS_ACCS * LS_N);
+    tmem_dealloc(tmem_base, LS_TMEM_COLS);
   }
 }
 
@@ -276,11 +313,13 @@ struct LstmSeqBwdParams {
   int stages, a_stage;       // TMA ring: number of stages and bytes per stage (batch rows rounded up to 8, x 128 B)
   unsigned int* counter;
   int* status;
+  long long* trace;
 };
 
 constexpr int LB_N = LS_UNITS;               // MMA N
 constexpr int LB_B_KB = LB_N * LS_BK * 2;    // 2 KB of resident weights per k-block
-constexpr int LB_TMEM_COLS = 64;           // LS_ACCS partial accumulators of LB_N columns each
+static_assert(LS_ISSUERS >= 2 && LS_ISSUERS <= 4, "the backward epilogue folds two to four accumulators out of 64 TMEM columns");
+constexpr int LB_TMEM_COLS = 64;           // LS_ACCS partial accumulators (one per issuer) of LB_N columns each
 
 __global__ void __launch_bounds__(LS_THREADS, 1)
 lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqBwdParams p) {
@@ -307,7 +346,7 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
     prefetch_tmap(&tmap_w);
     for (int i = 0; i < p.stages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     mbar_init(w_full, 1);
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, LS_ISSUERS);             // 4n / 64 >= 4 k-blocks: every issuer has work in every round
     mbar_init(acc_empty, 4);
     mbar_fence_init();
   }
@@ -334,36 +373,42 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
         if (!ok) break;
         __threadfence();
         fence_proxy_async_all();
+        ls_stamp(p.trace, r, 0);
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
           mbar_expect_tx(&full_bar[stage], (uint32_t)p.a_stage);
           tma_load_4d(a_smem + stage * p.a_stage, &tmap_dz, &full_bar[stage], kb * LS_BK, 0, t_src, 0);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
+        ls_stamp(p.trace, r, 1);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp < LS_EPI_WARP0) {
+    const int me = warp - 1;                      // issuer index: k-blocks me, me + LS_ISSUERS, ... of every round
     if (lane == 0) {
       const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LB_N);
+      const uint32_t acc = tmem_base + (uint32_t)(me * LB_N);
       bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
       tc_fence_after();
-      int stage = 0;
-      uint32_t phase = 0;
       for (int r = 0; r < rounds && ok; ++r) {
         if (!mbar_wait_bounded(acc_empty, (uint32_t)((r & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = me; kb < kblocks; kb += LS_ISSUERS) {
+          const int g = r * kblocks + kb;
+          const int stage = g % p.stages;
+          const uint32_t phase = (uint32_t)((g / p.stages) & 1);
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          if (me == 0 && (kb & 3) == 0 && kb < 64) ls_stamp(p.trace, r, 2 + (kb >> 2));       // every fourth k-block
           tc_fence_after();
           const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * p.a_stage), 16, 1024);
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LB_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
-            umma_f16(tmem_base + (uint32_t)(k * LB_N), da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, kb > 0 ? 1u : 0u);
+            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > me || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(acc_full);
+        if (me == 0) ls_stamp(p.trace, r, 18);
       }
     }
   } else {
@@ -412,14 +457,19 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
       for (int i = 0; i < 32; ++i) acc[i] = 0u;
       if (r >= 0) {
         if (!mbar_wait_bounded(acc_full, (uint32_t)(r & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, r, 19);
         tc_fence_after();
         uint32_t hi[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), acc);
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + 32, hi);
         tmem_ld_wait();
 #pragma unroll
-        for (int u = 0; u < LS_UNITS; ++u)           // fold the four partial accumulators (columns u, 16 + u, 32 + u, 48 + u)
-          acc[u] = __float_as_uint(__uint_as_float(acc[u]) + __uint_as_float(acc[16 + u]) + __uint_as_float(hi[u]) + __uint_as_float(hi[16 + u]));
+        for (int u = 0; u < LS_UNITS; ++u) {         // fold the issuers' accumulators (columns u, 16 + u, 32 + u, 48 + u)
+          float v = __uint_as_float(acc[u]) + __uint_as_float(acc[16 + u]);
+          if (LS_ISSUERS > 2) v += __uint_as_float(hi[u]);
+          if (LS_ISSUERS > 3) v += __uint_as_float(hi[16 + u]);
+          acc[u] = __float_as_uint(v);
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty);
@@ -461,9 +511,11 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
         gd = reinterpret_cast<uint4*>(drow + 2L * p.n);      gd[0] = pack8(go); gd[1] = pack8(go + 8);
         gd = reinterpret_cast<uint4*>(drow + 3L * p.n);      gd[0] = pack8(gg); gd[1] = pack8(gg + 8);
       }
+      if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 21);
       __threadfence();
       fence_proxy_async_all();
       __syncwarp();
+      if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 22);
       if (lane == 0) atomicAdd(p.counter, 1u);
     }
     if (row_ok && p.dc0) {
@@ -484,6 +536,10 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
 }  // namespace dl4j
 
 using namespace dl4j;
+
+// Device buffer of at least T x 32 int64 that the next launches' middle CTA fills with its timeline (null switches it off).
+static long long* g_lstm_trace = nullptr;
+DL4J_API void dl4j_lstm_set_trace(void* buf) { g_lstm_trace = reinterpret_cast<long long*>(buf); }
 
 // Shared memory plan: resident weights, then as many ring stages as fit (stage = batch rows rounded up to 8 x 128 B: rows
 // beyond the batch are never loaded, the MMA reads whatever those rows of the tile hold and their accumulator rows are
@@ -544,6 +600,7 @@ DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, cons
   p.stages = stages; p.a_stage = a_rows * 128;
   p.counter = counter;
   p.status = dl4j_status_word(dev);
+  p.trace = g_lstm_trace;
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return (int)e;
   e = cudaFuncSetAttribute(lstm_seq_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -585,6 +642,7 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   p.stages = stages; p.a_stage = a_rows * 128;
   p.counter = counter;
   p.status = dl4j_status_word(dev);
+  p.trace = g_lstm_trace;
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return (int)e;
   e = cudaFuncSetAttribute(lstm_seq_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
