@@ -50,6 +50,9 @@ struct LstmSeqParams {
   long long* trace;          // optional [T][32] clock64 stamps written by the middle CTA (null = off); see dl4j_lstm_set_trace
 };
 
+// Named barrier over the four epilogue warps (barrier 0 is __syncthreads).
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 __device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, int* status) {
@@ -111,7 +114,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit0 = blockIdx.x * LS_UNITS;
-  const unsigned int arrivals_per_step = 4u * gridDim.x;    // one arrive per epilogue warp per CTA
+  const unsigned int arrivals_per_step = gridDim.x;         // one arrive per CTA
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_h);
@@ -267,9 +270,9 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 21);
       __threadfence();
       fence_proxy_async_all();
-      __syncwarp();
+      epilogue_bar_sync();                         // every epilogue thread's stores are fenced: one arrive per CTA
       if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 22);
-      if (lane == 0) atomicAdd(p.counter, 1u);
+      if (threadIdx.x == 32 * LS_EPI_WARP0) atomicAdd(p.counter, 1u);
       if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 23);
       if (row_ok) {
         __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
@@ -338,7 +341,7 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit0 = blockIdx.x * LS_UNITS;
-  const unsigned int arrivals_per_step = 4u * gridDim.x;
+  const unsigned int arrivals_per_step = gridDim.x;
   const int rounds = p.T - 1 + (p.dh0 ? 1 : 0);     // MMA rounds: one per step except the last one in time, plus dh0
 
   if (threadIdx.x == 0) {
@@ -514,9 +517,9 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
       if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 21);
       __threadfence();
       fence_proxy_async_all();
-      __syncwarp();
+      epilogue_bar_sync();
       if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 22);
-      if (lane == 0) atomicAdd(p.counter, 1u);
+      if (threadIdx.x == 32 * LS_EPI_WARP0) atomicAdd(p.counter, 1u);
     }
     if (row_ok && p.dc0) {
       float4* cd = reinterpret_cast<float4*>(p.dc0 + (long)b * p.n + unit0);
