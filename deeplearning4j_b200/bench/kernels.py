@@ -196,7 +196,26 @@ def bench_conv(t, small, rows):
                      "library_ms": ref_b, "library_tflops": 2 * fl / ref_b / 1e9})
 
 
-KERNELS = {"conv": bench_conv, "gemm": bench_gemm, "layer_norm": bench_layer_norm, "softmax_xent": bench_softmax_xent, "updater": bench_updater,
+def bench_mma_issue(t, small, rows):
+    """Clocks per tcgen05.mma seen by one issuing thread, for one to four issuing warps (``csrc/mma_issue_probe.cu``).  Prints its
+    own table: the figures are clock counts, not rates against a roofline."""
+    import ctypes
+    l = native.require()
+    l.dl4j_mma_issue_probe.argtypes = [ctypes.c_int] * 6 + [ctypes.c_void_p]
+    l.dl4j_mma_issue_probe.restype = ctypes.c_int
+    out = (ctypes.c_longlong * 2)()
+    iters = 256
+    print("tcgen05.mma issue probe (M 128, bf16, K 16): clocks per instruction for each issuing thread")
+    for n, issuers, mn in ((16, 1, 0), (64, 1, 0), (128, 1, 0), (256, 1, 0), (16, 4, 0), (64, 2, 0), (64, 4, 0), (128, 2, 0), (128, 4, 0),
+                           (256, 2, 0), (64, 1, 1), (128, 1, 1), (256, 1, 1), (64, 4, 1), (256, 2, 1)):
+        rc = l.dl4j_mma_issue_probe(128, n, iters, 1, issuers, mn, out)
+        if rc != 0 or out[1] < 0:
+            raise RuntimeError(f"dl4j_mma_issue_probe failed: rc {rc}, completion {out[1]}")
+        per = out[1] / iters
+        print(f"  N {n:3d}  {'MN' if mn else 'K '}-major  issuers {issuers}:  issue {out[0] / iters:6.1f}  complete {per:6.1f}  ->  {per / issuers:6.1f} clocks per instruction overall", flush=True)
+
+
+KERNELS = {"conv": bench_conv, "mma_issue": bench_mma_issue, "gemm": bench_gemm, "layer_norm": bench_layer_norm, "softmax_xent": bench_softmax_xent, "updater": bench_updater,
            "lstm_cell": bench_lstm_cell, "attention": bench_attention}
 
 
