@@ -27,6 +27,7 @@
 namespace dl4j {
 
 constexpr int CV_THREADS = 192;
+constexpr int CV_HALO_THREADS = 192 + 96;    // conv_halo_kernel: three more MMA-issuing warps behind the four epilogue warps
 constexpr int CV_BLOCK_K = 64;
 constexpr int CV_UMMA_K = 16;
 constexpr int CV_MAX_TAPS = 64;
@@ -304,17 +305,18 @@ struct HaloParams {
   const void* bias;
   int bias_fp32, fmt;
   int sa_stages, sb_stages, b_resident;
+  int issuers, nacc;        // MMA-issuing warps (1 .. 4) and accumulator buffers in use (a multiple of issuers, <= 512 / BLOCK_N)
   int* status;
 };
 
 template <int BLOCK_N>
-__global__ void __launch_bounds__(CV_THREADS, 1)
+__global__ void __launch_bounds__(CV_HALO_THREADS, 1)
 conv_halo_kernel(const __grid_constant__ CUtensorMap tmap_a,     // activation {C, W, H, N}, box {64, PW, HR, 1}
                  const __grid_constant__ CUtensorMap tmap_b,     // weights {Cin, taps, Cout}, box {64, 1, 64}
                  const __grid_constant__ CUtensorMap tmap_c,     // output {C, W, H, N}, box {64, 8, 16, 1}
                  const HaloParams p) {
   constexpr int B_BYTES = BLOCK_N * 128;
-  constexpr int NACC = 512 / BLOCK_N;
+  const int NACC = p.nacc;                  // accumulator buffers in use (a multiple of the number of issuing warps)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int a_bytes = p.HR * p.PW * 128;
@@ -340,7 +342,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmap_a,     // activation {
   const int num_work = m_tiles * p.tiles_n;
   const int taps = p.taps_h * p.taps_w;
   const int kc = (p.k_ch + CV_BLOCK_K - 1) / CV_BLOCK_K;
-  for (int t = threadIdx.x; t < taps; t += CV_THREADS) {
+  for (int t = threadIdx.x; t < taps; t += CV_HALO_THREADS) {
     const int r = t / p.taps_w, s = t - r * p.taps_w;
     const int oh = p.mode == 0 ? r * p.dil_h : (p.taps_h - 1 - r) * p.dil_h;
     const int ow = p.mode == 0 ? s * p.dil_w : (p.taps_w - 1 - s) * p.dil_w;
@@ -354,7 +356,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmap_a,     // activation {
     prefetch_tmap(&tmap_c);
     for (int i = 0; i < SA; ++i) { mbar_init(&full_a[i], 1); mbar_init(&empty_a[i], 1); }
     for (int i = 0; i < SB; ++i) { mbar_init(&full_b[i], 1); mbar_init(&empty_b[i], 1); }
-    for (int i = 0; i < NACC; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 4); }
+    for (int i = 0; i < CV_MAX_ACC; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 4); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -396,6 +398,58 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmap_a,     // activation {
             if (++sb == SB) { sb = 0; pb ^= 1; }
           }
         }
+        first = false;
+      }
+    }
+  } else if ((warp == 1 || warp >= 6) && p.issuers > 1) {
+    // Several issuing warps (resident weights only): one thread gets at most one tcgen05.mma into the pipe per ~147 clocks
+    // whatever its shape, an N = 64 instruction occupies the tensor core for ~48.  Warp j takes the tiles j, j + NI, ... of this
+    // CTA, each into an accumulator buffer of its own.  NACC and the number of A stages are multiples of NI (x slices per tile),
+    // so a buffer or a stage always falls to the same warp and that warp sees every phase of its barriers in order.
+    const int me = warp == 1 ? 0 : warp - 5;
+    const int NI = p.issuers;
+    if (lane == 0 && me < NI) {
+      const int b_mn = p.mode == 0 ? 0 : 1;
+      const uint32_t idesc = make_idesc(p.fmt, 0, b_mn, 128, BLOCK_N);
+      const uint32_t lbo_b = b_mn ? 8192u : 16u;
+      const uint32_t kstep_b = b_mn ? CV_UMMA_K * 128 : CV_UMMA_K * 2;
+      const uint64_t desc_a_hi = make_smem_desc_sw128(0, 16, (uint32_t)p.PW * 128u);
+      const uint64_t desc_b_hi = make_smem_desc_sw128(0, lbo_b, 1024);
+      const uint32_t kb16 = kstep_b >> 4;
+      const uint32_t a_base0 = smem_u32(smem), b_base0 = smem_u32(smem_b);
+      bool ok = true, first = true;
+      int it = me;
+      for (long w = (long)blockIdx.x + (long)me * gridDim.x; w < num_work && ok; w += (long)NI * gridDim.x, it += NI) {
+        const int buf = it % NACC;
+        const uint32_t acc_phase = (uint32_t)((it / NACC) & 1);
+        if (!mbar_wait_bounded(&tmem_empty[buf], acc_phase ^ 1, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
+        uint32_t acc = 0;
+        for (int c = 0; c < kc && ok; ++c) {
+          const long ga = (long)it * kc + c;             // position of this slice in the producer's sequence of A loads
+          const int sa = (int)(ga % SA);
+          if (!mbar_wait_bounded(&full_a[sa], (uint32_t)((ga / SA) & 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = a_base0 + (uint32_t)(sa * a_bytes);
+#pragma unroll 1
+          for (int t = 0; t < taps; ++t) {
+            const int sb = c * taps + t;                 // resident weights: one slot per (slice, tap), filled once
+            if (first) {
+              if (!mbar_wait_bounded(&full_b[sb], 0, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+              tc_fence_after();
+            }
+            const uint64_t da = desc_a_hi | (uint64_t)((a_base + tap_off[t]) >> 4);
+            const uint64_t db = desc_b_hi | (uint64_t)((b_base0 + (uint32_t)(sb * B_BYTES)) >> 4);
+            umma_f16(tmem_d, da, db, idesc, acc);
+            umma_f16(tmem_d, da + 2, db + kb16, idesc, 1u);
+            umma_f16(tmem_d, da + 4, db + 2 * kb16, idesc, 1u);
+            umma_f16(tmem_d, da + 6, db + 3 * kb16, idesc, 1u);
+            acc = 1u;
+          }
+          umma_commit(&empty_a[sa]);
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
         first = false;
       }
     }
@@ -451,7 +505,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmap_a,     // activation {
         first = false;
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const int sw = row & 7;
@@ -798,14 +852,19 @@ static int launch_halo(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   auto kern = conv_halo_kernel<BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
-  kern<<<grid, CV_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
+  kern<<<grid, CV_HALO_THREADS, smem_bytes, stream>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
+}
+
+static bool conv_halo_auto() {
+  static const bool on = [] { const char* e = getenv("DL4J_CONV_HALO_AUTO"); return !(e && e[0] == '0'); }();
+  return on;
 }
 
 // Halo form of forward / dgrad; returns 1 when the case is left to the per-tap kernel (small images, no room in shared memory).
 static int try_conv_halo(int mode, const void* in, const void* w_cl, void* out, const void* bias, int N, int in_c, int in_w, int in_h,
                          int out_c, int out_w, int out_h, int Cin, int Cout, int kH, int kW, int pad_h, int pad_w, int dil_h,
-                         int dil_w, int fmt, int bias_fp32, int act, bool force, cudaStream_t stream) {
+                         int dil_w, int fmt, int bias_fp32, int act, bool force, bool multi_only, cudaStream_t stream) {
   const int PW = (8 + (kW - 1) * dil_w + 7) / 8 * 8, HR = 16 + (kH - 1) * dil_h;
   if (PW > 256 || HR > 256) return 1;
   const int tiles_w = (out_w + 7) / 8, tiles_h = (out_h + 15) / 16;
@@ -830,6 +889,19 @@ static int try_conv_halo(int mode, const void* in, const void* w_cl, void* out, 
     if (p.sb_stages < 2) return 1;
     if (p.sb_stages >= 4 && budget - p.sb_stages * b_bytes >= 3 * a_bytes) p.sa_stages = 3;
   }
+  p.issuers = 1;
+  p.nacc = 512 / bn;
+  if (p.b_resident) {
+    // several issuing warps: accumulator buffers and A stages in multiples of the warp count (x slices per tile)
+    const int sa_max = (budget - p.sb_stages * b_bytes) / a_bytes;
+    for (int ni = 4; ni >= 2; --ni) {
+      const int unit = ni * kc;
+      const int nacc = (512 / bn) / ni * ni;
+      const int sa = std::min(sa_max, 2 * unit) / unit * unit;
+      if (nacc >= ni && sa >= unit) { p.issuers = ni; p.nacc = nacc; p.sa_stages = sa; break; }
+    }
+  }
+  if (multi_only && p.issuers < 2) return 1;
   const int smem_bytes = p.sa_stages * a_bytes + p.sb_stages * b_bytes + 2 * 128 * 128 + 1024 + 1536;
   if (smem_bytes > 227 * 1024 || (2 * (p.sa_stages + p.sb_stages) + 2 * CV_MAX_ACC + 2) * 8 > 1536) return 1;
   int dev = 0;
@@ -896,7 +968,13 @@ DL4J_API int dl4j_conv2d(int mode, const void* in, const void* w_cl, void* out, 
     // halo form on request (flag 4): one input fetch per channel slice instead of one per tap.  It moves a quarter of the
     // bytes of the per-tap kernel but measured 20-40 % slower on the ResNet-50 shapes, so the per-tap kernel is the default.
     const int hr = try_conv_halo(mode, in, w_cl, out, bias, N, in_c, in_w, in_h, out_c, out_w, out_h, Cin, Cout, kH, kW, pad_h,
-                                 pad_w, dil_h, dil_w, fmt, bias_fp32, act, true, stream);
+                                 pad_w, dil_h, dil_w, fmt, bias_fp32, act, true, false, stream);
+    if (hr != 1) return hr;
+  } else if (!(fuse_w & 1) && conv_halo_auto()) {
+    // automatic: only where the halo kernel can keep its weights resident and issue from several warps (few input channels);
+    // there it is tensor-bound while the per-tap kernel is bound by its nine-fold input traffic
+    const int hr = try_conv_halo(mode, in, w_cl, out, bias, N, in_c, in_w, in_h, out_c, out_w, out_h, Cin, Cout, kH, kW, pad_h,
+                                 pad_w, dil_h, dil_w, fmt, bias_fp32, act, false, true, stream);
     if (hr != 1) return hr;
   }
   fuse_w &= 1;

@@ -164,7 +164,7 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
     }
   } else if (warp < LS_EPI_WARP0) {
     const int me = warp - 1;                      // issuer index: k-blocks me, me + LS_ISSUERS, ... of every step
-    if (lane == 0 && me < kblocks) {
+    if (lane == 0) {
       const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LS_N);
       const uint32_t acc = tmem_base + (uint32_t)(me * LS_N);
       bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
@@ -172,8 +172,13 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       for (int s = 0; s < p.T && ok; ++s) {
         if (!mbar_wait_bounded(acc_empty, (uint32_t)((s & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = me; kb < kblocks; kb += LS_ISSUERS) {
-          const int g = s * kblocks + kb;         // position of this k-block in the producer's load sequence
+        // Sequence position g of a k-block decides its issuer (g mod LS_ISSUERS) and its ring stage (g mod stages); the ring depth
+        // is a multiple of LS_ISSUERS, so a stage always belongs to the same issuer, which therefore sees every phase of that
+        // stage's barrier in order (a thread that skipped a phase could mistake the previous completion for the one it waits for).
+        const int g0 = s * kblocks;
+        const int kb_first = (me + LS_ISSUERS - g0 % LS_ISSUERS) % LS_ISSUERS;
+        for (int kb = kb_first; kb < kblocks; kb += LS_ISSUERS) {
+          const int g = g0 + kb;
           const int stage = g % p.stages;
           const uint32_t phase = (uint32_t)((g / p.stages) & 1);
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
@@ -183,10 +188,10 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LS_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
-            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > me || k > 0) ? 1u : 0u);
+            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > kb_first || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
         }
-        if (ok) umma_commit(acc_full);
+        if (ok && kb_first < kblocks) umma_commit(acc_full);
         if (me == 0) ls_stamp(p.trace, s, 18);
       }
     }
@@ -222,12 +227,13 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       tc_fence_after();
       uint32_t r0[32], r1[32];
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-      tmem_ld_32x32(taddr, r0);
-      tmem_ld_32x32(taddr + 32, r1);
-      tmem_ld_wait();
 #pragma unroll
-      for (int j = 1; j < LS_ACCS; ++j) {          // fold the issuers' partial accumulators
-        if (j >= kblocks) break;
+      for (int i = 0; i < 32; ++i) { r0[i] = 0u; r1[i] = 0u; }
+      const int g0m = (s * kblocks) % LS_ISSUERS;
+#pragma unroll
+      for (int j = 0; j < LS_ACCS; ++j) {          // fold the issuers' partial accumulators
+        // issuer j wrote its accumulator in this step only if one of the step's k-blocks fell to it (always, once n >= 192)
+        if ((j + LS_ISSUERS - g0m) % LS_ISSUERS >= kblocks) continue;
         uint32_t t0[32], t1[32];
         tmem_ld_32x32(taddr + j * LS_N, t0);
         tmem_ld_32x32(taddr + j * LS_N + 32, t1);
@@ -396,8 +402,10 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
       for (int r = 0; r < rounds && ok; ++r) {
         if (!mbar_wait_bounded(acc_empty, (uint32_t)((r & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = me; kb < kblocks; kb += LS_ISSUERS) {
-          const int g = r * kblocks + kb;
+        const int g0 = r * kblocks;                  // issuer and stage by sequence position, as in the forward kernel
+        const int kb_first = (me + LS_ISSUERS - g0 % LS_ISSUERS) % LS_ISSUERS;
+        for (int kb = kb_first; kb < kblocks; kb += LS_ISSUERS) {
+          const int g = g0 + kb;
           const int stage = g % p.stages;
           const uint32_t phase = (uint32_t)((g / p.stages) & 1);
           if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
@@ -407,7 +415,7 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
           const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LB_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
-            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > me || k > 0) ? 1u : 0u);
+            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > kb_first || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[stage]);
         }
         if (ok) umma_commit(acc_full);
@@ -555,6 +563,8 @@ static size_t ls_ring(size_t weight_bytes, int mb, int* a_rows, int* stages) {
   if (fixed + 2 * stage > limit) return 0;
   size_t s = (limit - fixed) / stage;
   if (s > LS_MAX_STAGES) s = LS_MAX_STAGES;
+  s -= s % LS_ISSUERS;                 // a stage must always fall to the same issuing warp (see the kernels)
+  if (s < (size_t)LS_ISSUERS) return 0;
   *a_rows = rows;
   *stages = (int)s;
   return fixed + s * stage;
