@@ -56,17 +56,62 @@ def test_omnihub_cache_layout(tmp_path, monkeypatch):
     monkeypatch.setenv("OMNIHUB_HOME", str(tmp_path))
     p = OmniHubUtils.modelPath("dl4j", "tiny.zip")
     assert p == os.path.join(str(tmp_path), "dl4j", "tiny.zip")
-    with pytest.raises(IOError, match="cannot be downloaded"):
+    monkeypatch.setenv("OMNIHUB_URL", "file://" + str(tmp_path / "nowhere"))
+    with pytest.raises(IOError, match="could not be fetched"):
         OmniHubUtils.downloadAndLoadFromZoo("dl4j", "tiny.zip")
+    assert not os.path.exists(p + ".part")
     conf = (nn.NeuralNetConfiguration.Builder().seed(1).list().layer(nn.DenseLayer(nIn=3, nOut=2, activation="relu"))
             .layer(nn.OutputLayer("MSE", nIn=2, nOut=1, activation="identity")).build())
     net = nn.MultiLayerNetwork(conf)
     net.init()
-    os.makedirs(os.path.dirname(p))
+    os.makedirs(os.path.dirname(p), exist_ok=True)
     nn.ModelSerializer.writeModel(net, p, False)
     assert OmniHubUtils.loadNetwork("tiny.zip").numParams() == net.numParams()
     with pytest.raises(ValueError):
         OmniHubUtils.modelPath("caffe", "x")
+
+
+def test_omnihub_download_convert_and_namespaces(tmp_path, monkeypatch):
+    """The hub is a ``file://`` folder: fetch into the cache, convert an ONNX and a TFLite model to SameDiff .fb files, and reach the
+    results through the generated-style namespaces (``OmniHubUtils.java:128-150``, ``BootstrapFromLocal.java``)."""
+    import torch
+    from deeplearning4j_b200.omnihub import (BootstrapFromLocal, Framework, ModelNamespaceGenerator, OmniHubUtils, Pretrained, clearCache)
+    import tests.test_import_tflite as t_tfl
+    hub, home = tmp_path / "hub", tmp_path / "home"
+    monkeypatch.setenv("OMNIHUB_HOME", str(home))
+    monkeypatch.setenv("OMNIHUB_URL", "file://" + str(hub))
+    b = t_tfl.ModelBuilder()
+    x = b.tensor("x", [2, 3])
+    y = b.tensor("y", [2, 3]); b.op("TANH", [x], [y])
+    os.makedirs(hub / "tensorflow")
+    (hub / "tensorflow" / "tiny-tanh.tflite").write_bytes(b.build([x], [y]))
+    seen = []
+    p = OmniHubUtils.downloadAndLoadFromZoo("tensorflow", "tiny-tanh.tflite", progress=lambda done, total: seen.append((done, total)))
+    assert p == str(home / "tensorflow" / "tiny-tanh.tflite") and os.path.getsize(p) == seen[-1][0]
+    (hub / "tensorflow" / "tiny-tanh.tflite").unlink()                      # cached: the hub is not asked again
+    assert OmniHubUtils.downloadAndLoadFromZoo("tensorflow", "tiny-tanh.tflite") == p
+    (home / "onnx").mkdir()
+    (home / "onnx" / "broken.onnx").write_bytes(b"\x00\x01not a model")
+    res = BootstrapFromLocal.run()
+    out = res[p]
+    assert out == str(home / "samediff" / "tiny-tanh.fb") and os.path.exists(out)
+    assert isinstance(res[str(home / "onnx" / "broken.onnx")], Exception)
+    ns = Pretrained.samediff()
+    assert ns.models() == ["tinyTanh"] and "tinyTanh" in dir(ns)
+    sd = ns.tinyTanh()
+    xin = torch.tensor([[0.5, -1.0, 2.0], [0.0, 1.0, -2.0]])
+    got = sd.output({"x": xin}, "y")["y"]
+    torch.testing.assert_close(got.t if hasattr(got, "t") else got, torch.tanh(xin))
+    with pytest.raises(KeyError):
+        ns.load("resnet18")
+    src = ModelNamespaceGenerator.generate(Framework.SAMEDIFF)
+    assert "class SameDiffModels:" in src and "def tinyTanh(self, forceDownload=False):" in src
+    compile(src, "generated", "exec")
+    assert Framework.outputFrameworkFor(Framework.KERAS) == Framework.DL4J and Framework.isOutput(Framework.SAMEDIFF)
+    with pytest.raises(ValueError):
+        Framework.outputFrameworkFor(Framework.DL4J)
+    clearCache(Framework.SAMEDIFF)
+    assert Pretrained.samediff().models() == []
 
 
 def test_codegen_emits_working_namespaces(tmp_path):
