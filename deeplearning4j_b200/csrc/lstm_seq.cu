@@ -544,9 +544,320 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
   }
 }
 
+constexpr int LP_N = 2 * LS_UNITS;             // pair kernel: MMA N = the pair's 32 units
+constexpr int LP_B_KB = LP_N * LS_BK * 2;      // 4 KB of resident weights per k-block
+constexpr int LP_TMEM_COLS = 128;              // LS_ISSUERS accumulators of LP_N columns (96 used)
+static_assert(LS_ISSUERS * LP_N <= LP_TMEM_COLS, "pair kernel accumulators exceed the TMEM allocation");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_cluster(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// release at cluster scope: the stores above are visible to the peer thread that observes this arrival with an acquire
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0x3ff) == 0 && (clock64() - t0 > 4000000000LL || *((volatile int*)status) != 0)) {
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+// every thread of both CTAs
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Pair form of the backward kernel: the two CTAs of a cluster own 32 hidden units together and split the reduction over the 4n
+// gate columns.  CTA `rank` keeps RW[32 units, its half of the columns] resident (the same 128 KB as 16 units x all columns),
+// streams only its half of dz per step (the L2 -> SM stream is what bounds the single-CTA form), and issues N = 32 instructions.
+// Each CTA finishes 16 of the 32 units: it sends the other 16 columns of its partial sums into the peer's shared memory
+// (st.shared::cluster), arrives on the peer's mbarrier and waits for the peer's half to land in its own.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(LS_THREADS, 1)
+lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int kblocks = 4 * p.n / LS_BK / 2;          // this CTA's half of the reduction
+  const uint32_t rank = cluster_ctarank();         // 0 / 1 inside the pair
+  const int kb_base = (int)rank * kblocks;
+  uint8_t* w_smem = smem;
+  uint8_t* a_smem = w_smem + kblocks * LP_B_KB;
+  float* xbuf = reinterpret_cast<float*>(a_smem + p.stages * p.a_stage);      // [2][128 rows][16]: the peer's partial sums, by round parity
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xbuf + 2 * LS_M * LS_UNITS);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + LS_MAX_STAGES;
+  uint64_t* w_full = bars + 2 * LS_MAX_STAGES;
+  uint64_t* acc_full = w_full + 1;
+  uint64_t* acc_empty = w_full + 2;
+  uint64_t* x_full = w_full + 3;               // [2]: the peer's four epilogue warps have written xbuf[parity]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 5);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit0 = blockIdx.x * LS_UNITS;                 // the 16 units this CTA finishes
+  const int pair_unit0 = (blockIdx.x & ~1) * LS_UNITS;     // the pair's 32 units (MMA N)
+  const unsigned int arrivals_per_step = gridDim.x;
+  const int rounds = p.T - 1 + (p.dh0 ? 1 : 0);     // MMA rounds: one per step except the last one in time, plus dh0
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_dz);
+    prefetch_tmap(&tmap_w);
+    for (int i = 0; i < p.stages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    mbar_init(w_full, 1);
+    mbar_init(acc_full, LS_ISSUERS);             // 4n / 64 >= 4 k-blocks: every issuer has work in every round
+    mbar_init(acc_empty, 4);
+    mbar_init(&x_full[0], 4);
+    mbar_init(&x_full[1], 4);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, LP_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(w_full, (uint32_t)(kblocks * LP_B_KB));
+      for (int kb = 0; kb < kblocks; ++kb) tma_load_4d(w_smem + kb * LP_B_KB, &tmap_w, w_full, (kb_base + kb) * LS_BK, pair_unit0, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int r = 0; r < rounds && ok; ++r) {
+        const int s_src = p.T - 1 - r;                         // step whose dz feeds this round
+        const int t_src = p.reverse ? p.T - 1 - s_src : s_src;
+        ok = wait_counter(p.counter, arrivals_per_step * (unsigned)(r + 1), p.status);
+        if (!ok) break;
+        __threadfence();
+        fence_proxy_async_all();
+        ls_stamp(p.trace, r, 0);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, p.status, DL4J_ERR_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[stage], (uint32_t)p.a_stage);
+          tma_load_4d(a_smem + stage * p.a_stage, &tmap_dz, &full_bar[stage], (kb_base + kb) * LS_BK, 0, t_src, 0);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        ls_stamp(p.trace, r, 1);
+      }
+    }
+  } else if (warp < LS_EPI_WARP0) {
+    const int me = warp - 1;                      // issuer index: k-blocks me, me + LS_ISSUERS, ... of every round
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LP_N);
+      const uint32_t acc = tmem_base + (uint32_t)(me * LP_N);
+      bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
+      tc_fence_after();
+      for (int r = 0; r < rounds && ok; ++r) {
+        if (!mbar_wait_bounded(acc_empty, (uint32_t)((r & 1) ^ 1), p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const int g0 = r * kblocks;                  // issuer and stage by sequence position, as in the forward kernel
+        const int kb_first = (me + LS_ISSUERS - g0 % LS_ISSUERS) % LS_ISSUERS;
+        for (int kb = kb_first; kb < kblocks; kb += LS_ISSUERS) {
+          const int g = g0 + kb;
+          const int stage = g % p.stages;
+          const uint32_t phase = (uint32_t)((g / p.stages) & 1);
+          if (!mbar_wait_bounded(&full_bar[stage], phase, p.status, DL4J_ERR_TIMEOUT_MMA)) { ok = false; break; }
+          if (me == 0 && (kb & 3) == 0 && kb < 64) ls_stamp(p.trace, r, 2 + (kb >> 2));       // every fourth k-block
+          tc_fence_after();
+          const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * p.a_stage), 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LP_B_KB), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < LS_BK / 16; ++k)
+            umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > kb_first || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+        }
+        if (ok) umma_commit(acc_full);
+        if (me == 0) ls_stamp(p.trace, r, 18);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int b = q * 32 + lane;
+    const bool row_ok = b < p.mb;
+    const long n4 = 4L * p.n;
+    float dc[LS_UNITS];
+#pragma unroll
+    for (int u = 0; u < LS_UNITS; ++u) dc[u] = 0.f;
+    if (row_ok && p.dc_last) {
+      const float4* cp = reinterpret_cast<const float4*>(p.dc_last + (long)b * p.n + unit0);
+#pragma unroll
+      for (int i = 0; i < LS_UNITS / 4; ++i) { const float4 v = cp[i]; dc[4 * i] = v.x; dc[4 * i + 1] = v.y; dc[4 * i + 2] = v.z; dc[4 * i + 3] = v.w; }
+    }
+    bool ok = true;
+    for (int s = p.T - 1; s >= -1 && ok; --s) {
+      if (s < 0 && !p.dh0) break;
+      const int r = p.T - 2 - s;                     // MMA round that produced this step's recurrent gradient (none for s = T-1)
+      const int t = p.reverse ? p.T - 1 - s : s;
+      uint4 graw[8], draw[2];
+      float ct[LS_UNITS], cp_[LS_UNITS];
+      if (row_ok && s >= 0) {
+        const __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint4* src = reinterpret_cast<const uint4*>(grow + (long)g * p.n);
+          graw[2 * g] = __ldg(src);
+          graw[2 * g + 1] = __ldg(src + 1);
+        }
+        const uint4* dsrc = reinterpret_cast<const uint4*>(p.dout + ((long)t * p.mb + b) * p.n + unit0);
+        draw[0] = __ldg(dsrc);
+        draw[1] = __ldg(dsrc + 1);
+        const float4* c4 = reinterpret_cast<const float4*>(p.cs + ((long)t * p.mb + b) * p.n + unit0);
+        const int tp = p.reverse ? t + 1 : t - 1;
+        const float4* p4 = reinterpret_cast<const float4*>((s > 0 ? p.cs + ((long)tp * p.mb + b) * p.n : p.c0 + (long)b * p.n) + unit0);
+#pragma unroll
+        for (int i = 0; i < LS_UNITS / 4; ++i) {
+          const float4 v = __ldg(c4 + i), w = __ldg(p4 + i);
+          ct[4 * i] = v.x; ct[4 * i + 1] = v.y; ct[4 * i + 2] = v.z; ct[4 * i + 3] = v.w;
+          cp_[4 * i] = w.x; cp_[4 * i + 1] = w.y; cp_[4 * i + 2] = w.z; cp_[4 * i + 3] = w.w;
+        }
+      }
+      uint32_t acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = 0u;
+      if (r >= 0) {
+        if (!mbar_wait_bounded(acc_full, (uint32_t)(r & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, r, 19);
+        tc_fence_after();
+        // partial sums over this CTA's half of the gate columns for the pair's 32 units: one accumulator of 32 columns per issuer
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), acc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 1; j < LS_ISSUERS; ++j) {
+          uint32_t t2[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + j * LP_N, t2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __uint_as_float(t2[i]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);       // accumulators drained: the next round's MMAs may start
+        // columns [16 rank, 16 rank + 16) are this CTA's units; the other 16 go to the peer
+        {
+          const int par = r & 1;
+          // (selects with constant indices: a rank-dependent index would push the array into local memory)
+          const bool hi_mine = rank != 0;
+          uint32_t keep[LS_UNITS], send[LS_UNITS];
+#pragma unroll
+          for (int i = 0; i < LS_UNITS; ++i) {
+            keep[i] = hi_mine ? acc[LS_UNITS + i] : acc[i];
+            send[i] = hi_mine ? acc[i] : acc[LS_UNITS + i];
+          }
+          const uint32_t remote = mapa_cluster(smem_u32(xbuf + ((size_t)par * LS_M + b) * LS_UNITS), rank ^ 1u);
+#pragma unroll
+          for (int j = 0; j < LS_UNITS / 4; ++j)
+            st_cluster_v4(remote + 16u * j, send[4 * j], send[4 * j + 1], send[4 * j + 2], send[4 * j + 3]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&x_full[par]), rank ^ 1u));
+          if (!mbar_wait_bounded_cluster(&x_full[par], (uint32_t)((r >> 1) & 1), p.status, DL4J_ERR_TIMEOUT_PEER)) { ok = false; break; }
+          const float4* in = reinterpret_cast<const float4*>(xbuf + ((size_t)par * LS_M + b) * LS_UNITS);
+#pragma unroll
+          for (int j = 0; j < LS_UNITS / 4; ++j) {
+            const float4 v = in[j];
+            acc[4 * j] = __float_as_uint(__uint_as_float(keep[4 * j]) + v.x);
+            acc[4 * j + 1] = __float_as_uint(__uint_as_float(keep[4 * j + 1]) + v.y);
+            acc[4 * j + 2] = __float_as_uint(__uint_as_float(keep[4 * j + 2]) + v.z);
+            acc[4 * j + 3] = __float_as_uint(__uint_as_float(keep[4 * j + 3]) + v.w);
+          }
+        }
+      }
+      if (s < 0) {
+        if (row_ok) {
+          float h[16];
+#pragma unroll
+          for (int u = 0; u < LS_UNITS; ++u) h[u] = __uint_as_float(acc[u]);
+          uint4* hd = reinterpret_cast<uint4*>(p.dh0 + (long)b * p.n + unit0);
+          hd[0] = pack8(h);
+          hd[1] = pack8(h + 8);
+        }
+        break;
+      }
+      if (row_ok) {
+        float ga[16], gf[16], go[16], gg[16], dh[16];
+        unpack8(graw[0], ga); unpack8(graw[1], ga + 8);
+        unpack8(graw[2], gf); unpack8(graw[3], gf + 8);
+        unpack8(graw[4], go); unpack8(graw[5], go + 8);
+        unpack8(graw[6], gg); unpack8(graw[7], gg + 8);
+        unpack8(draw[0], dh); unpack8(draw[1], dh + 8);
+#pragma unroll
+        for (int u = 0; u < LS_UNITS; ++u) {
+          const float a = ga[u], f = gf[u], o = go[u], g = gg[u];
+          const float dhv = dh[u] + __uint_as_float(acc[u]);
+          const float tc = tanh_fast(ct[u]);
+          const float dcv = dc[u] + dhv * o * (1.f - tc * tc);
+          ga[u] = dcv * g * (1.f - a * a);
+          gf[u] = dcv * cp_[u] * f * (1.f - f);
+          go[u] = dhv * tc * o * (1.f - o);
+          gg[u] = dcv * a * g * (1.f - g);
+          dc[u] = dcv * f;
+        }
+        __nv_bfloat16* drow = p.dzx + ((long)t * p.mb + b) * n4 + unit0;
+        uint4* gd;
+        gd = reinterpret_cast<uint4*>(drow);               gd[0] = pack8(ga); gd[1] = pack8(ga + 8);
+        gd = reinterpret_cast<uint4*>(drow + (long)p.n);     gd[0] = pack8(gf); gd[1] = pack8(gf + 8);
+        gd = reinterpret_cast<uint4*>(drow + 2L * p.n);      gd[0] = pack8(go); gd[1] = pack8(go + 8);
+        gd = reinterpret_cast<uint4*>(drow + 3L * p.n);      gd[0] = pack8(gg); gd[1] = pack8(gg + 8);
+      }
+      if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 21);
+      __threadfence();
+      fence_proxy_async_all();
+      epilogue_bar_sync();
+      if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 22);
+      if (threadIdx.x == 32 * LS_EPI_WARP0) atomicAdd(p.counter, 1u);
+    }
+    if (row_ok && p.dc0) {
+      float4* cd = reinterpret_cast<float4*>(p.dc0 + (long)b * p.n + unit0);
+#pragma unroll
+      for (int i = 0; i < LS_UNITS / 4; ++i) cd[i] = make_float4(dc[4 * i], dc[4 * i + 1], dc[4 * i + 2], dc[4 * i + 3]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, LP_TMEM_COLS);
+  }
+  cluster_sync_all();                               // neither CTA leaves while the other may still write into it
+}
+
 }  // namespace dl4j
 
 using namespace dl4j;
+
+static bool lstm_pair_enabled() {
+  static const bool on = [] { const char* e = getenv("DL4J_LSTM_PAIR"); return !(e && e[0] == '0'); }();
+  return on;
+}
 
 // Device buffer of at least T x 32 int64 that the next launches' middle CTA fills with its timeline (null switches it off).
 static long long* g_lstm_trace = nullptr;
@@ -631,7 +942,11 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
   const int kblocks = 4 * n / LS_BK;
   int a_rows, stages;
-  const size_t smem = ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
+  // pair form (two CTAs share 32 units and split the gate columns): same resident bytes, half the L2 -> SM stream per CTA
+  const bool pair = lstm_pair_enabled() && n % (2 * LS_UNITS) == 0 && kblocks % 2 == 0 && kblocks / 2 >= LS_ISSUERS;   // every issuer needs a k-block per round
+  const size_t xbuf_bytes = 2 * LS_M * LS_UNITS * sizeof(float);
+  const size_t smem = pair ? ls_ring((size_t)(kblocks / 2) * LP_B_KB + xbuf_bytes, mb, &a_rows, &stages)
+                           : ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
   if (!smem) return -DL4J_ERR_BAD_ARG;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -642,7 +957,7 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   CUtensorMap td, tw;
   int r = ls_encode(&td, dzx, (uint64_t)4 * n, (uint64_t)mb, (uint64_t)T, (uint64_t)4 * n * 2, (uint64_t)mb * 4 * n * 2, LS_BK, (uint32_t)a_rows);
   if (r) return -1000 - r;
-  r = ls_encode(&tw, rwt, (uint64_t)4 * n, (uint64_t)n, 1, (uint64_t)4 * n * 2, (uint64_t)4 * n * n * 2, LS_BK, LS_UNITS);
+  r = ls_encode(&tw, rwt, (uint64_t)4 * n, (uint64_t)n, 1, (uint64_t)4 * n * 2, (uint64_t)4 * n * n * 2, LS_BK, pair ? LP_N : LS_UNITS);
   if (r) return -1000 - r;
   LstmSeqBwdParams p;
   p.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
@@ -658,9 +973,10 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   p.trace = g_lstm_trace;
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return (int)e;
-  e = cudaFuncSetAttribute(lstm_seq_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  void* kern = pair ? (void*)lstm_seq_bwd_pair_kernel : (void*)lstm_seq_bwd_kernel;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)&td, (void*)&tw, (void*)&p};
-  e = cudaLaunchCooperativeKernel((void*)lstm_seq_bwd_kernel, dim3(grid), dim3(LS_THREADS), args, smem, stream);
+  e = cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(LS_THREADS), args, smem, stream);
   return (int)e;
 }
