@@ -274,11 +274,13 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
         hd[1] = pack8(h + 8);
       }
       if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 21);
-      __threadfence();
       fence_proxy_async_all();
-      epilogue_bar_sync();                         // every epilogue thread's stores are fenced: one arrive per CTA
-      if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 22);
-      if (threadIdx.x == 32 * LS_EPI_WARP0) atomicAdd(p.counter, 1u);
+      epilogue_bar_sync();                         // every epilogue thread's stores precede the barrier; the one fence below is cumulative
+      if (threadIdx.x == 32 * LS_EPI_WARP0) {
+        __threadfence();
+        ls_stamp(p.trace, s, 22);
+        atomicAdd(p.counter, 1u);                  // one arrive per CTA
+      }
       if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 23);
       if (row_ok) {
         __nv_bfloat16* grow = p.gates + ((long)t * p.mb + b) * n4 + unit0;
@@ -523,11 +525,13 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
         gd = reinterpret_cast<uint4*>(drow + 3L * p.n);      gd[0] = pack8(gg); gd[1] = pack8(gg + 8);
       }
       if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 21);
-      __threadfence();
       fence_proxy_async_all();
       epilogue_bar_sync();
-      if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 22);
-      if (threadIdx.x == 32 * LS_EPI_WARP0) atomicAdd(p.counter, 1u);
+      if (threadIdx.x == 32 * LS_EPI_WARP0) {
+        __threadfence();
+        if (r >= 0) ls_stamp(p.trace, r, 22);
+        atomicAdd(p.counter, 1u);
+      }
     }
     if (row_ok && p.dc0) {
       float4* cd = reinterpret_cast<float4*>(p.dc0 + (long)b * p.n + unit0);
@@ -543,11 +547,6 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
     tmem_dealloc(tmem_base, LB_TMEM_COLS);
   }
 }
-
-constexpr int LP_N = 2 * LS_UNITS;             // pair kernel: MMA N = the pair's 32 units
-constexpr int LP_B_KB = LP_N * LS_BK * 2;      // 4 KB of resident weights per k-block
-constexpr int LP_TMEM_COLS = 128;              // LS_ISSUERS accumulators of LP_N columns (96 used)
-static_assert(LS_ISSUERS * LP_N <= LP_TMEM_COLS, "pair kernel accumulators exceed the TMEM allocation");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -589,38 +588,52 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_
   }
   return true;
 }
-// every thread of both CTAs
+// shared memory of this CTA -> shared memory of a CTA of the cluster; the bytes are counted on that CTA's mbarrier
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_cluster), "r"(src_cta),
+               "r"(bytes), "r"(bar_cluster)
+               : "memory");
+}
+// every thread of every CTA of the cluster
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Pair form of the backward kernel: the two CTAs of a cluster own 32 hidden units together and split the reduction over the 4n
-// gate columns.  CTA `rank` keeps RW[32 units, its half of the columns] resident (the same 128 KB as 16 units x all columns),
-// streams only its half of dz per step (the L2 -> SM stream is what bounds the single-CTA form), and issues N = 32 instructions.
-// Each CTA finishes 16 of the 32 units: it sends the other 16 columns of its partial sums into the peer's shared memory
-// (st.shared::cluster), arrives on the peer's mbarrier and waits for the peer's half to land in its own.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(LS_THREADS, 1)
-lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqBwdParams p) {
+// Cluster form of the backward kernel: the CS (2 or 4) CTAs of a cluster own 16 CS hidden units together and split the reduction
+// over the 4n gate columns.  CTA `rank` keeps RW[16 CS units, its 1/CS of the columns] resident (the same 128 KB as 16 units x all
+// columns), streams only its share of dz per step (the L2 -> SM stream is what bounds the single-CTA form) and issues N = 16 CS
+// instructions.  Each CTA finishes 16 of the units: the other columns of its partial sums are staged in shared memory and copied
+// into the owners' shared memory by bulk copies that complete on the owner's mbarrier (cp.async.bulk.shared::cluster), and it waits
+// for the CS - 1 slices that the peers send to it.
+template <int CS>
+__global__ void __launch_bounds__(LS_THREADS, 1)
+lstm_seq_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_constant__ CUtensorMap tmap_w, const LstmSeqBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int kblocks = 4 * p.n / LS_BK / 2;          // this CTA's half of the reduction
-  const uint32_t rank = cluster_ctarank();         // 0 / 1 inside the pair
+  constexpr int GN = CS * LS_UNITS;                 // MMA N: the cluster's units
+  constexpr int G_B_KB = GN * LS_BK * 2;            // resident weights per k-block
+  constexpr int G_TMEM = CS == 2 ? 128 : 256;       // LS_ISSUERS accumulators of GN columns, rounded up to a power of two
+  static_assert(LS_ISSUERS * GN <= G_TMEM, "accumulators exceed the TMEM allocation");
+  const int kblocks = 4 * p.n / LS_BK / CS;         // this CTA's share of the reduction
+  const uint32_t rank = cluster_ctarank();
+  const int rows_x = p.a_stage / 128;               // batch rows (rounded up to 8) that take part in the exchange
   const int kb_base = (int)rank * kblocks;
   uint8_t* w_smem = smem;
-  uint8_t* a_smem = w_smem + kblocks * LP_B_KB;
-  float* xbuf = reinterpret_cast<float*>(a_smem + p.stages * p.a_stage);      // [2][128 rows][16]: the peer's partial sums, by round parity
-  uint64_t* bars = reinterpret_cast<uint64_t*>(xbuf + 2 * LS_M * LS_UNITS);
+  uint8_t* a_smem = w_smem + kblocks * G_B_KB;
+  float* xbuf = reinterpret_cast<float*>(a_smem + p.stages * p.a_stage);      // [2 parities][CS - 1 senders][rows_x][16]: the peers' partial sums
+  float* sbuf = xbuf + 2 * (CS - 1) * rows_x * LS_UNITS;                       // [CS - 1 receivers][rows_x][16]: staging of what this CTA sends
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sbuf + (CS - 1) * rows_x * LS_UNITS);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + LS_MAX_STAGES;
   uint64_t* w_full = bars + 2 * LS_MAX_STAGES;
   uint64_t* acc_full = w_full + 1;
   uint64_t* acc_empty = w_full + 2;
-  uint64_t* x_full = w_full + 3;               // [2]: the peer's four epilogue warps have written xbuf[parity]
+  uint64_t* x_full = w_full + 3;               // [2]: the peers' slices have landed in xbuf[parity]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 5);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int unit0 = blockIdx.x * LS_UNITS;                 // the 16 units this CTA finishes
-  const int pair_unit0 = (blockIdx.x & ~1) * LS_UNITS;     // the pair's 32 units (MMA N)
+  const int grp_unit0 = (int)(blockIdx.x / CS) * CS * LS_UNITS;     // the cluster's units (MMA N)
   const unsigned int arrivals_per_step = gridDim.x;
   const int rounds = p.T - 1 + (p.dh0 ? 1 : 0);     // MMA rounds: one per step except the last one in time, plus dh0
 
@@ -631,12 +644,12 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
     mbar_init(w_full, 1);
     mbar_init(acc_full, LS_ISSUERS);             // 4n / 64 >= 4 k-blocks: every issuer has work in every round
     mbar_init(acc_empty, 4);
-    mbar_init(&x_full[0], 4);
-    mbar_init(&x_full[1], 4);
+    mbar_init(&x_full[0], 1);                    // one local arrive with the expected byte count per round
+    mbar_init(&x_full[1], 1);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, LP_TMEM_COLS);
+    tmem_alloc(tmem_slot, G_TMEM);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -647,8 +660,8 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(w_full, (uint32_t)(kblocks * LP_B_KB));
-      for (int kb = 0; kb < kblocks; ++kb) tma_load_4d(w_smem + kb * LP_B_KB, &tmap_w, w_full, (kb_base + kb) * LS_BK, pair_unit0, 0, 0);
+      mbar_expect_tx(w_full, (uint32_t)(kblocks * G_B_KB));
+      for (int kb = 0; kb < kblocks; ++kb) tma_load_4d(w_smem + kb * G_B_KB, &tmap_w, w_full, (kb_base + kb) * LS_BK, grp_unit0, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -672,8 +685,8 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
   } else if (warp < LS_EPI_WARP0) {
     const int me = warp - 1;                      // issuer index: k-blocks me, me + LS_ISSUERS, ... of every round
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(1, 0, 0, LS_M, LP_N);
-      const uint32_t acc = tmem_base + (uint32_t)(me * LP_N);
+      const uint32_t idesc = make_idesc(1, 0, 0, LS_M, GN);
+      const uint32_t acc = tmem_base + (uint32_t)(me * GN);
       bool ok = mbar_wait_bounded(w_full, 0, p.status, DL4J_ERR_TIMEOUT_MMA);
       tc_fence_after();
       for (int r = 0; r < rounds && ok; ++r) {
@@ -689,7 +702,7 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
           if (me == 0 && (kb & 3) == 0 && kb < 64) ls_stamp(p.trace, r, 2 + (kb >> 2));       // every fourth k-block
           tc_fence_after();
           const uint64_t da = make_smem_desc_sw128(smem_u32(a_smem + stage * p.a_stage), 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * LP_B_KB), 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_u32(w_smem + kb * G_B_KB), 16, 1024);
 #pragma unroll
           for (int k = 0; k < LS_BK / 16; ++k)
             umma_f16(acc, da + ((uint64_t)(k * 32) >> 4), db + ((uint64_t)(k * 32) >> 4), idesc, (kb > kb_first || k > 0) ? 1u : 0u);
@@ -744,49 +757,80 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
 #pragma unroll
       for (int i = 0; i < 32; ++i) acc[i] = 0u;
       if (r >= 0) {
+        if (threadIdx.x == 32 * LS_EPI_WARP0)        // this round's slices from the CS - 1 peers
+          mbar_expect_tx(&x_full[r & 1], (uint32_t)((CS - 1) * rows_x * LS_UNITS * 4));
         if (!mbar_wait_bounded(acc_full, (uint32_t)(r & 1), p.status, DL4J_ERR_TIMEOUT_EPILOGUE)) { ok = false; break; }
         if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, r, 19);
         tc_fence_after();
-        // partial sums over this CTA's half of the gate columns for the pair's 32 units: one accumulator of 32 columns per issuer
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), acc);
-        tmem_ld_wait();
+        // Partial sums over this CTA's share of the gate columns for the cluster's units (one accumulator per issuer), 32 columns
+        // at a time: the 16 columns of this CTA's own units stay in registers, the others are staged for their owners.
+        const int par = r & 1;
+        if (lane == 0) bulk_wait_read<0>();          // the previous round's copies have read the staging buffer
+        __syncwarp();
+        uint32_t keep[LS_UNITS];
 #pragma unroll
-        for (int j = 1; j < LS_ISSUERS; ++j) {
-          uint32_t t2[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + j * LP_N, t2);
+        for (int i = 0; i < LS_UNITS; ++i) keep[i] = 0u;
+#pragma unroll
+        for (int half = 0; half < GN / 32; ++half) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + half * 32, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __uint_as_float(t2[i]));
+          for (int j = 1; j < LS_ISSUERS; ++j) {
+            uint32_t t2[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + j * GN + half * 32, t2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(t2[i]));
+          }
+#pragma unroll
+          for (int gg = 0; gg < 2; ++gg) {
+            const int g = half * 2 + gg;             // 16-column group = rank of the CTA that finishes these units
+            if (g == (int)rank) {
+#pragma unroll
+              for (int i = 0; i < LS_UNITS; ++i) keep[i] = v[16 * gg + i];
+            } else if (b < rows_x) {
+              const int d = (g - (int)rank + CS) % CS;                       // 1 .. CS - 1
+              uint4* dst = reinterpret_cast<uint4*>(sbuf + ((size_t)(d - 1) * rows_x + b) * LS_UNITS);
+#pragma unroll
+              for (int j = 0; j < LS_UNITS / 4; ++j)
+                dst[j] = make_uint4(v[16 * gg + 4 * j], v[16 * gg + 4 * j + 1], v[16 * gg + 4 * j + 2], v[16 * gg + 4 * j + 3]);
+            }
+          }
         }
         tc_fence_before();
+        fence_proxy_async_smem();                    // staging stores -> the bulk copies below
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty);       // accumulators drained: the next round's MMAs may start
-        // columns [16 rank, 16 rank + 16) are this CTA's units; the other 16 go to the peer
-        {
-          const int par = r & 1;
-          // (selects with constant indices: a rank-dependent index would push the array into local memory)
-          const bool hi_mine = rank != 0;
-          uint32_t keep[LS_UNITS], send[LS_UNITS];
+        if (lane == 0) {
+          mbar_arrive(acc_empty);                    // accumulators drained: the next round's MMAs may start
+          const int nrows = min(32, rows_x - q * 32);
+          if (nrows > 0) {
 #pragma unroll
-          for (int i = 0; i < LS_UNITS; ++i) {
-            keep[i] = hi_mine ? acc[LS_UNITS + i] : acc[i];
-            send[i] = hi_mine ? acc[i] : acc[LS_UNITS + i];
+            for (int d = 1; d < CS; ++d) {
+              const uint32_t peer = (rank + (uint32_t)d) % CS;
+              const int slot = CS - d - 1;           // at the receiver, slot j holds the slice of rank (receiver + j + 1) % CS
+              const uint32_t src = smem_u32(sbuf + ((size_t)(d - 1) * rows_x + q * 32) * LS_UNITS);
+              const uint32_t dst = mapa_cluster(smem_u32(xbuf + ((size_t)(par * (CS - 1) + slot) * rows_x + q * 32) * LS_UNITS), peer);
+              bulk_copy_to_cluster(dst, src, (uint32_t)nrows * LS_UNITS * 4u, mapa_cluster(smem_u32(&x_full[par]), peer));
+            }
+            bulk_commit();
           }
-          const uint32_t remote = mapa_cluster(smem_u32(xbuf + ((size_t)par * LS_M + b) * LS_UNITS), rank ^ 1u);
+        }
+        if (!mbar_wait_bounded(&x_full[par], (uint32_t)((r >> 1) & 1), p.status, DL4J_ERR_TIMEOUT_PEER)) { ok = false; break; }
 #pragma unroll
-          for (int j = 0; j < LS_UNITS / 4; ++j)
-            st_cluster_v4(remote + 16u * j, send[4 * j], send[4 * j + 1], send[4 * j + 2], send[4 * j + 3]);
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&x_full[par]), rank ^ 1u));
-          if (!mbar_wait_bounded_cluster(&x_full[par], (uint32_t)((r >> 1) & 1), p.status, DL4J_ERR_TIMEOUT_PEER)) { ok = false; break; }
-          const float4* in = reinterpret_cast<const float4*>(xbuf + ((size_t)par * LS_M + b) * LS_UNITS);
+        for (int i = 0; i < LS_UNITS; ++i) acc[i] = keep[i];
+        if (b < rows_x) {
 #pragma unroll
-          for (int j = 0; j < LS_UNITS / 4; ++j) {
-            const float4 v = in[j];
-            acc[4 * j] = __float_as_uint(__uint_as_float(keep[4 * j]) + v.x);
-            acc[4 * j + 1] = __float_as_uint(__uint_as_float(keep[4 * j + 1]) + v.y);
-            acc[4 * j + 2] = __float_as_uint(__uint_as_float(keep[4 * j + 2]) + v.z);
-            acc[4 * j + 3] = __float_as_uint(__uint_as_float(keep[4 * j + 3]) + v.w);
+          for (int sl = 0; sl < CS - 1; ++sl) {
+            const float4* in = reinterpret_cast<const float4*>(xbuf + ((size_t)(par * (CS - 1) + sl) * rows_x + b) * LS_UNITS);
+#pragma unroll
+            for (int j = 0; j < LS_UNITS / 4; ++j) {
+              const float4 x4 = in[j];
+              acc[4 * j] = __float_as_uint(__uint_as_float(acc[4 * j]) + x4.x);
+              acc[4 * j + 1] = __float_as_uint(__uint_as_float(acc[4 * j + 1]) + x4.y);
+              acc[4 * j + 2] = __float_as_uint(__uint_as_float(acc[4 * j + 2]) + x4.z);
+              acc[4 * j + 3] = __float_as_uint(__uint_as_float(acc[4 * j + 3]) + x4.w);
+            }
           }
         }
       }
@@ -828,11 +872,13 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
         gd = reinterpret_cast<uint4*>(drow + 3L * p.n);      gd[0] = pack8(gg); gd[1] = pack8(gg + 8);
       }
       if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 21);
-      __threadfence();
       fence_proxy_async_all();
       epilogue_bar_sync();
-      if (threadIdx.x == 32 * LS_EPI_WARP0 && r >= 0) ls_stamp(p.trace, r, 22);
-      if (threadIdx.x == 32 * LS_EPI_WARP0) atomicAdd(p.counter, 1u);
+      if (threadIdx.x == 32 * LS_EPI_WARP0) {
+        __threadfence();
+        if (r >= 0) ls_stamp(p.trace, r, 22);
+        atomicAdd(p.counter, 1u);
+      }
     }
     if (row_ok && p.dc0) {
       float4* cd = reinterpret_cast<float4*>(p.dc0 + (long)b * p.n + unit0);
@@ -841,11 +887,12 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
     }
   }
 
+  if (warp >= LS_EPI_WARP0 && lane == 0) bulk_wait<0>();     // this CTA's copies have completed before it may exit
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, LP_TMEM_COLS);
+    tmem_dealloc(tmem_base, G_TMEM);
   }
   cluster_sync_all();                               // neither CTA leaves while the other may still write into it
 }
@@ -854,9 +901,10 @@ lstm_seq_bwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __gr
 
 using namespace dl4j;
 
-static bool lstm_pair_enabled() {
-  static const bool on = [] { const char* e = getenv("DL4J_LSTM_PAIR"); return !(e && e[0] == '0'); }();
-  return on;
+// CTAs per cluster in the backward kernel: 4 unless DL4J_LSTM_CLUSTER says 1 (single-CTA form) or 2
+static int lstm_cluster_size() {
+  static const int cs = [] { const char* e = getenv("DL4J_LSTM_CLUSTER"); const int v = e ? atoi(e) : 4; return v >= 4 ? 4 : (v >= 2 ? 2 : 1); }();
+  return cs;
 }
 
 // Device buffer of at least T x 32 int64 that the next launches' middle CTA fills with its timeline (null switches it off).
@@ -942,11 +990,18 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
   const int kblocks = 4 * n / LS_BK;
   int a_rows, stages;
-  // pair form (two CTAs share 32 units and split the gate columns): same resident bytes, half the L2 -> SM stream per CTA
-  const bool pair = lstm_pair_enabled() && n % (2 * LS_UNITS) == 0 && kblocks % 2 == 0 && kblocks / 2 >= LS_ISSUERS;   // every issuer needs a k-block per round
-  const size_t xbuf_bytes = 2 * LS_M * LS_UNITS * sizeof(float);
-  const size_t smem = pair ? ls_ring((size_t)(kblocks / 2) * LP_B_KB + xbuf_bytes, mb, &a_rows, &stages)
-                           : ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
+  // cluster form (CS CTAs share 16 CS units and split the gate columns): same resident bytes, 1 / CS of the L2 -> SM stream per CTA
+  int csz = lstm_cluster_size();
+  while (csz > 1 && !((n / LS_UNITS) % csz == 0 && kblocks % csz == 0 && kblocks / csz >= LS_ISSUERS)) csz /= 2;   // every issuer needs a k-block per round
+  const int rows8 = (mb + 7) / 8 * 8;
+  size_t smem = 0;
+  while (csz > 1) {                   // a smaller cluster when the exchange buffers leave no room for the ring
+    const size_t xchg_bytes = (size_t)3 * (csz - 1) * rows8 * LS_UNITS * sizeof(float);     // two receive parities + one staging buffer
+    smem = ls_ring((size_t)(kblocks / csz) * (csz * LS_UNITS * LS_BK * 2) + xchg_bytes, mb, &a_rows, &stages);
+    if (smem) break;
+    csz /= 2;
+  }
+  if (csz == 1) smem = ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
   if (!smem) return -DL4J_ERR_BAD_ARG;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
@@ -957,7 +1012,7 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   CUtensorMap td, tw;
   int r = ls_encode(&td, dzx, (uint64_t)4 * n, (uint64_t)mb, (uint64_t)T, (uint64_t)4 * n * 2, (uint64_t)mb * 4 * n * 2, LS_BK, (uint32_t)a_rows);
   if (r) return -1000 - r;
-  r = ls_encode(&tw, rwt, (uint64_t)4 * n, (uint64_t)n, 1, (uint64_t)4 * n * 2, (uint64_t)4 * n * n * 2, LS_BK, pair ? LP_N : LS_UNITS);
+  r = ls_encode(&tw, rwt, (uint64_t)4 * n, (uint64_t)n, 1, (uint64_t)4 * n * 2, (uint64_t)4 * n * n * 2, LS_BK, (uint32_t)(csz * LS_UNITS));
   if (r) return -1000 - r;
   LstmSeqBwdParams p;
   p.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
@@ -973,10 +1028,22 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   p.trace = g_lstm_trace;
   cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return (int)e;
-  void* kern = pair ? (void*)lstm_seq_bwd_pair_kernel : (void*)lstm_seq_bwd_kernel;
+  void* kern = csz == 4 ? (void*)lstm_seq_bwd_cluster_kernel<4> : csz == 2 ? (void*)lstm_seq_bwd_cluster_kernel<2> : (void*)lstm_seq_bwd_kernel;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)&td, (void*)&tw, (void*)&p};
-  e = cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(LS_THREADS), args, smem, stream);
+  if (csz == 1) {
+    e = cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(LS_THREADS), args, smem, stream);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LS_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = (unsigned)csz; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeCooperative;
+    attrs[1].val.cooperative = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 2;
+    e = cudaLaunchKernelExC(&cfg, kern, args);
+  }
   return (int)e;
 }
