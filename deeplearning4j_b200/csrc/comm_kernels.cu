@@ -141,9 +141,11 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
   const long long sh0 = sg.shadow_off + (ch.offset - sg.offset);
   const int ns = upd_n_state(sg.kernel_id);
   __nv_bfloat16* my_shadow = c.shadow[c.rank];
-  const uintptr_t al = (uintptr_t)(ch.offset & 3) | (ns > 0 ? reinterpret_cast<uintptr_t>(st0) : 0) |
-                       (ns > 1 ? reinterpret_cast<uintptr_t>(st1) : 0) | (ns > 2 ? reinterpret_cast<uintptr_t>(st2) : 0);
-  const bool vec_ok = (al & 15) == 0;
+  // gradients and parameters (peer or multicast accesses) need the 16-byte grid; the state slots sit block_numel elements apart
+  // (DL4J's [m | v] layout) and are moved with four 4-byte accesses when they are off it
+  const bool vec_ok = (ch.offset & 3) == 0;
+  const bool a_al = (reinterpret_cast<uintptr_t>(st0) & 15) == 0, b_al = (reinterpret_cast<uintptr_t>(st1) & 15) == 0,
+             c_al = (reinterpret_cast<uintptr_t>(st2) & 15) == 0;
   const bool sh_vec = ((sh0 & 3) == 0);
   const int nvec = vec_ok ? ch.count / 4 : 0;
   // two vectors per thread and iteration: every load of both (peer gradients, parameters, state) is issued
@@ -170,9 +172,9 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
           }
         }
         w[u] = *reinterpret_cast<const float4*>(my_params + i);
-        if (ns > 0) a4[u] = *reinterpret_cast<const float4*>(st0 + 4 * v);
-        if (ns > 1) b4[u] = *reinterpret_cast<const float4*>(st1 + 4 * v);
-        if (ns > 2) c4[u] = *reinterpret_cast<const float4*>(st2 + 4 * v);
+        if (ns > 0) a4[u] = upd_ld4(st0 + 4 * v, a_al);
+        if (ns > 1) b4[u] = upd_ld4(st1 + 4 * v, b_al);
+        if (ns > 2) c4[u] = upd_ld4(st2 + 4 * v, c_al);
       }
     }
 #pragma unroll
@@ -186,9 +188,9 @@ __device__ __forceinline__ void reduce_update_chunk(const CommCtx& c, float* __r
               sc[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) wv[j] -= updater_step(sg, h, wv[j], gv[j] * grad_scale, sa + j, sb + j, sc + j);
-        if (ns > 0) *reinterpret_cast<float4*>(st0 + 4 * v) = make_float4(sa[0], sa[1], sa[2], sa[3]);
-        if (ns > 1) *reinterpret_cast<float4*>(st1 + 4 * v) = make_float4(sb[0], sb[1], sb[2], sb[3]);
-        if (ns > 2) *reinterpret_cast<float4*>(st2 + 4 * v) = make_float4(sc[0], sc[1], sc[2], sc[3]);
+        if (ns > 0) upd_st4(st0 + 4 * v, make_float4(sa[0], sa[1], sa[2], sa[3]), a_al);
+        if (ns > 1) upd_st4(st1 + 4 * v, make_float4(sb[0], sb[1], sb[2], sb[3]), b_al);
+        if (ns > 2) upd_st4(st2 + 4 * v, make_float4(sc[0], sc[1], sc[2], sc[3]), c_al);
       }
       const float4 wn = make_float4(wv[0], wv[1], wv[2], wv[3]);
       if (use_multimem) {
@@ -580,9 +582,9 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
     float* st1 = st0 + sg.block_numel;
     float* st2 = st1 + sg.block_numel;
     const int ns = upd_n_state(sg.kernel_id);
-    const uintptr_t al = (uintptr_t)(ch.offset & 15) | (ns > 0 ? reinterpret_cast<uintptr_t>(st0) : 0) |
-                         (ns > 1 ? reinterpret_cast<uintptr_t>(st1) : 0) | (ns > 2 ? reinterpret_cast<uintptr_t>(st2) : 0);
-    const bool vec_ok = (al & 15) == 0;               // chunk starts on a word boundary and every array is 16-byte aligned
+    const bool vec_ok = (ch.offset & 15) == 0;        // chunk starts on a word boundary; state slots off the 16-byte grid use 4-byte accesses
+    const bool a_al = (reinterpret_cast<uintptr_t>(st0) & 15) == 0, b_al = (reinterpret_cast<uintptr_t>(st1) & 15) == 0,
+               c_al = (reinterpret_cast<uintptr_t>(st2) & 15) == 0;
     const int nvec = vec_ok ? ch.count / 4 : 0;
     // this chunk's list segment: the words that lie wholly inside the chunk
     const long long seg0 = (ch.offset + 15) >> 4;
@@ -608,9 +610,9 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
           w4[u] = *reinterpret_cast<const float4*>(params + i);
           r4[u] = *reinterpret_cast<const float4*>(residual + i);
           if (sg.kernel_id != 9) {
-            if (ns > 0) a4[u] = *reinterpret_cast<const float4*>(st0 + 4 * v);
-            if (ns > 1) b4[u] = *reinterpret_cast<const float4*>(st1 + 4 * v);
-            if (ns > 2) c4[u] = *reinterpret_cast<const float4*>(st2 + 4 * v);
+            if (ns > 0) a4[u] = upd_ld4(st0 + 4 * v, a_al);
+            if (ns > 1) b4[u] = upd_ld4(st1 + 4 * v, b_al);
+            if (ns > 2) c4[u] = upd_ld4(st2 + 4 * v, c_al);
           }
         }
       }
@@ -627,9 +629,9 @@ threshold_share_kernel(const CommCtx c, float* __restrict__ state, float* __rest
                   sc[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) rv[j] += updater_step(sg, h, wv[j], gv[j] * grad_scale, sa + j, sb + j, sc + j);
-            if (ns > 0) *reinterpret_cast<float4*>(st0 + 4 * v) = make_float4(sa[0], sa[1], sa[2], sa[3]);
-            if (ns > 1) *reinterpret_cast<float4*>(st1 + 4 * v) = make_float4(sb[0], sb[1], sb[2], sb[3]);
-            if (ns > 2) *reinterpret_cast<float4*>(st2 + 4 * v) = make_float4(sc[0], sc[1], sc[2], sc[3]);
+            if (ns > 0) upd_st4(st0 + 4 * v, make_float4(sa[0], sa[1], sa[2], sa[3]), a_al);
+            if (ns > 1) upd_st4(st1 + 4 * v, make_float4(sb[0], sb[1], sb[2], sb[3]), b_al);
+            if (ns > 2) upd_st4(st2 + 4 * v, make_float4(sc[0], sc[1], sc[2], sc[3]), c_al);
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {

@@ -38,48 +38,54 @@ fused_update_kernel(float* __restrict__ params, float* __restrict__ grads, float
   }
   float* res = residual ? residual + ch.offset : nullptr;
   __nv_bfloat16* sh = shadow ? shadow + sg.shadow_off + (ch.offset - sg.offset) : nullptr;
-  // scalar head up to a 16-byte boundary of the parameter pointer, then 4 elements per thread when every
-  // stream (params, grads, state slots, residual, shadow) is aligned at that point, scalar otherwise
+  // Scalar head up to a 16-byte boundary of the parameter pointer, then 4 elements per thread.  Parameters and gradients share
+  // their offsets; the state slots sit block_numel elements apart (DL4J's [m | v] layout), the shadow and the residual have
+  // offsets of their own, so any of those streams may be off the 16-byte grid at that point: each stream is moved with one
+  // 16-byte access when it is aligned and with four 4-byte accesses otherwise (the warp still covers a contiguous 512 bytes).
   int head = (int)((4 - ((reinterpret_cast<uintptr_t>(p) >> 2) & 3)) & 3);
   if (head > ch.count) head = ch.count;
   const int ns = upd_n_state(sg.kernel_id);
-  const uintptr_t al = reinterpret_cast<uintptr_t>(p + head) | reinterpret_cast<uintptr_t>(g + head) |
-                       (ns > 0 ? reinterpret_cast<uintptr_t>(st0 + head) : 0) | (ns > 1 ? reinterpret_cast<uintptr_t>(st1 + head) : 0) |
-                       (ns > 2 ? reinterpret_cast<uintptr_t>(st2 + head) : 0) | (res ? reinterpret_cast<uintptr_t>(res + head) : 0) |
-                       (sh ? (reinterpret_cast<uintptr_t>(sh + head) << 1) : 0);
-  const bool vec = (al & 15) == 0;
-  const int nvec = vec ? (ch.count - head) / 4 : 0;
+  const bool pg_ok = ((reinterpret_cast<uintptr_t>(p + head) | reinterpret_cast<uintptr_t>(g + head)) & 15) == 0;
+  const bool a_al = (reinterpret_cast<uintptr_t>(st0 + head) & 15) == 0, b_al = (reinterpret_cast<uintptr_t>(st1 + head) & 15) == 0;
+  const bool c_al = (reinterpret_cast<uintptr_t>(st2 + head) & 15) == 0;
+  const bool r_al = res && (reinterpret_cast<uintptr_t>(res + head) & 15) == 0;
+  const bool s_al = sh && (reinterpret_cast<uintptr_t>(sh + head) & 7) == 0;
+  const int nvec = pg_ok ? (ch.count - head) / 4 : 0;
   for (int q = threadIdx.x; q < nvec; q += UPD_THREADS) {
     const int i = head + 4 * q;
     const float4 w4 = *reinterpret_cast<const float4*>(p + i);
     const float4 g4 = *reinterpret_cast<const float4*>(g + i);
     float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = a4, c4 = a4;
-    if (ns > 0) a4 = *reinterpret_cast<const float4*>(st0 + i);
-    if (ns > 1) b4 = *reinterpret_cast<const float4*>(st1 + i);
-    if (ns > 2) c4 = *reinterpret_cast<const float4*>(st2 + i);
+    if (ns > 0) a4 = upd_ld4(st0 + i, a_al);
+    if (ns > 1) b4 = upd_ld4(st1 + i, b_al);
+    if (ns > 2) c4 = upd_ld4(st2 + i, c_al);
     float w[4] = {w4.x, w4.y, w4.z, w4.w}, gr[4] = {g4.x, g4.y, g4.z, g4.w};
     float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w}, c[4] = {c4.x, c4.y, c4.z, c4.w}, u[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) u[j] = updater_step(sg, h, w[j], gr[j] * grad_scale, a + j, b + j, c + j);
-    if (ns > 0) *reinterpret_cast<float4*>(st0 + i) = make_float4(a[0], a[1], a[2], a[3]);
-    if (ns > 1) *reinterpret_cast<float4*>(st1 + i) = make_float4(b[0], b[1], b[2], b[3]);
-    if (ns > 2) *reinterpret_cast<float4*>(st2 + i) = make_float4(c[0], c[1], c[2], c[3]);
+    if (ns > 0) upd_st4(st0 + i, make_float4(a[0], a[1], a[2], a[3]), a_al);
+    if (ns > 1) upd_st4(st1 + i, make_float4(b[0], b[1], b[2], b[3]), b_al);
+    if (ns > 2) upd_st4(st2 + i, make_float4(c[0], c[1], c[2], c[3]), c_al);
     if (res) {
-      float4 r4 = *reinterpret_cast<const float4*>(res + i);
+      float4 r4 = upd_ld4(res + i, r_al);
       r4.x += u[0]; r4.y += u[1]; r4.z += u[2]; r4.w += u[3];
-      *reinterpret_cast<float4*>(res + i) = r4;
+      upd_st4(res + i, r4, r_al);
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) w[j] -= u[j];
       *reinterpret_cast<float4*>(p + i) = make_float4(w[0], w[1], w[2], w[3]);
       if (sh) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(w[0], w[1]), hi = __floats2bfloat162_rn(w[2], w[3]);
-        *reinterpret_cast<uint2*>(sh + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        if (s_al) {
+          *reinterpret_cast<uint2*>(sh + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else {
+          sh[i] = lo.x; sh[i + 1] = lo.y; sh[i + 2] = hi.x; sh[i + 3] = hi.y;
+        }
       }
     }
     if (zero_grads) *reinterpret_cast<float4*>(g + i) = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  // scalar head and tail (everything when the streams are not mutually aligned)
+  // scalar head and tail
   const int tail0 = head + 4 * nvec;
   for (int k = threadIdx.x; k < head + (ch.count - tail0); k += UPD_THREADS) {
     const int i = k < head ? k : tail0 + (k - head);

@@ -109,4 +109,15 @@ __device__ __forceinline__ float updater_step(const UpdSegment& sg, const UpdHyp
   return u;
 }
 
+// four consecutive floats: one 16-byte access when the address allows it
+__device__ __forceinline__ float4 upd_ld4(const float* q, bool aligned) {
+  if (aligned) return *reinterpret_cast<const float4*>(q);
+  return make_float4(q[0], q[1], q[2], q[3]);
+}
+__device__ __forceinline__ void upd_st4(float* q, const float4 v, bool aligned) {
+  if (aligned) { *reinterpret_cast<float4*>(q) = v; return; }
+  q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
+}
+
+
 }  // namespace dl4j
