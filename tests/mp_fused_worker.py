@@ -9,6 +9,10 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+# classes of the test network; 16 gives a parameter count on the 16-byte grid, 10 puts Adam's second state half 8 bytes off it
+N_OUT = int(os.environ.get("DL4J_TEST_NOUT", "16"))
+
+
 def make_net(rank, updater, bf16):
     from deeplearning4j_b200 import nn, DataType
     b = nn.NeuralNetConfiguration.Builder().seed(100 + rank).updater(updater).l2(1e-4)
@@ -16,7 +20,7 @@ def make_net(rank, updater, bf16):
         b.computeDataType(DataType.BFLOAT16)
     conf = (b.list().layer(nn.DenseLayer(nIn=256, nOut=512, activation="relu"))
             .layer(nn.DenseLayer(nIn=512, nOut=264, activation="tanh"))
-            .layer(nn.OutputLayer("MCXENT", nIn=264, nOut=16, activation="softmax")).build())
+            .layer(nn.OutputLayer("MCXENT", nIn=264, nOut=N_OUT, activation="softmax")).build())
     net = nn.MultiLayerNetwork(conf)
     net.device = torch.device("cuda", torch.cuda.current_device())
     return net.init()
@@ -25,7 +29,7 @@ def make_net(rank, updater, bf16):
 def data(rank, step):
     g = torch.Generator().manual_seed(1000 * rank + step)
     x = torch.rand(64, 256, generator=g).cuda()
-    y = torch.nn.functional.one_hot(torch.randint(0, 16, (64,), generator=g), 16).float().cuda()
+    y = torch.nn.functional.one_hot(torch.randint(0, N_OUT, (64,), generator=g), N_OUT).float().cuda()
     return x, y
 
 

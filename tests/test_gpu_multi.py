@@ -40,5 +40,11 @@ def test_fused_parameter_averaging_matches_the_library_path():
     _run("paramavg", port=29715)
 
 
+def test_fused_paths_with_state_slots_off_the_vector_grid():
+    """269,682 parameters: the second Adam state half starts 8 bytes off the 16-byte grid (the kernels move it with 4-byte accesses)."""
+    _run("averaging", port=29716, extra_env={"DL4J_TEST_NOUT": "10"})
+    _run("threshold", port=29717, extra_env={"DL4J_TEST_NOUT": "10"})
+
+
 def test_bounded_peer_wait_reports_timeout():
     _run("timeout", port=29713, extra_env={"NCCL_NVLS_ENABLE": "0"})
