@@ -1,8 +1,8 @@
 """Keras model import (``deeplearning4j-modelimport``: ``KerasModelImport``, ``KerasSequentialModel``, ``KerasModel``
 and the ``Keras*`` layer mappers).  A model is its architecture JSON (``model.to_json()`` / the ``model_config``
 attribute of an HDF5 file) plus weights.  Weights come from a ``{layer name: [arrays]}`` dict, an ``.npz`` file
-with ``<layer>/<index>`` keys, or an HDF5 file when ``h5py`` is installed (it is optional: without it the HDF5
-entry points raise with that explanation).  Sequential models become a ``MultiLayerNetwork``, functional models a
+with ``<layer>/<index>`` keys, or an HDF5 file read by ``importers/hdf5.py`` (no HDF5 library is needed); a full-model ``.h5``
+file passed as the first argument supplies both.  Sequential models become a ``MultiLayerNetwork``, functional models a
 ``ComputationGraph``; Keras channels-last tensors map onto the NCHW layers by permuting kernels at import time and
 inserting the flatten order fix for ``Flatten`` -> ``Dense``."""
 from __future__ import annotations
@@ -239,25 +239,44 @@ def _load_weights(weights):
         for k in sorted(z.files, key=lambda s: (s.rsplit("/", 1)[0], int(s.rsplit("/", 1)[1]))):
             out.setdefault(k.rsplit("/", 1)[0], []).append(z[k])
         return out
-    try:
-        import h5py
-    except ImportError as e:
-        raise UnsupportedKerasConfigurationException("reading Keras HDF5 weights needs h5py, which is not installed; export the weights with "
-                                                     "numpy.savez(path, **{'<layer>/<i>': array}) instead") from e
+    # HDF5: the importer's own reader (importers/hdf5.py) - Keras stores, under /model_weights (or at the root of a weights-only
+    # file), one group per layer with a weight_names attribute listing its datasets
+    from .hdf5 import Hdf5Archive
     out = {}
-    with h5py.File(path, "r") as f:
-        g = f["model_weights"] if "model_weights" in f else f
-        for lname in g.attrs.get("layer_names", list(g.keys())):
-            lname = lname.decode() if isinstance(lname, bytes) else lname
-            names = [n.decode() if isinstance(n, bytes) else n for n in g[lname].attrs.get("weight_names", [])]
-            out[lname] = [np.asarray(g[lname][n]) for n in names]
+    with Hdf5Archive(path) as ar:
+        root = ("model_weights",) if "model_weights" in ar.getGroups() else ()
+        layer_names = ar.readAttributeAsStringList("layer_names", *root) or ar.getGroups(*root)
+        for lname in layer_names:
+            names = ar.readAttributeAsStringList("weight_names", *root, lname)
+            out[lname] = [ar.readDataSet(n, *root, lname) for n in names]
     return out
+
+
+def _is_hdf5(path):
+    try:
+        with open(path, "rb") as f:
+            return f.read(8) == b"\x89HDF\r\n\x1a\n"
+    except (OSError, TypeError, ValueError):
+        return False
 
 
 class KerasModelImport:
     @staticmethod
     def _config(model_json):
-        cfg = json.loads(model_json) if isinstance(model_json, str) and model_json.lstrip().startswith("{") else json.load(open(model_json))
+        if isinstance(model_json, str) and model_json.lstrip().startswith("{"):
+            cfg = json.loads(model_json)
+        elif _is_hdf5(model_json):
+            # a full-model .h5 file: architecture and training configuration are JSON attributes of the root group
+            from .hdf5 import Hdf5Archive
+            with Hdf5Archive(model_json) as ar:
+                if not ar.hasAttribute("model_config"):
+                    raise InvalidKerasConfigurationException("the HDF5 file has no model_config attribute (a weights-only file: pass the "
+                                                             "architecture JSON as the first argument and this file as weights)")
+                cfg = ar.readAttributeAsJson("model_config")
+                if ar.hasAttribute("training_config") and "training_config" not in cfg:
+                    cfg["training_config"] = ar.readAttributeAsJson("training_config")
+        else:
+            cfg = json.load(open(model_json))
         loss = None
         tc = cfg.get("training_config") or {}
         l = tc.get("loss")
@@ -310,6 +329,8 @@ class KerasModelImport:
             idx += 1
         lb.setInputType(it).validateOutputLayerConfig(False)
         net = nn.MultiLayerNetwork(lb.build()).init()
+        if weights is None and not (isinstance(model_json, str) and model_json.lstrip().startswith("{")) and _is_hdf5(model_json):
+            weights = model_json                      # full-model file: the weights sit beside the configuration
         w = _load_weights(weights)
         for i, kname, layer, ff in mapped:
             if kname in w and w[kname]:
@@ -371,6 +392,8 @@ class KerasModelImport:
         conf = gb.build()
         from ..nn.graph import ComputationGraph
         net = ComputationGraph(conf).init()
+        if weights is None and not (isinstance(model_json, str) and model_json.lstrip().startswith("{")) and _is_hdf5(model_json):
+            weights = model_json                      # full-model file: the weights sit beside the configuration
         w = _load_weights(weights)
         for name, layer, srcs in mapped:
             if name in w and w[name]:
