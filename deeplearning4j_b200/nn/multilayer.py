@@ -17,6 +17,7 @@ from .conf.base import BackpropType
 from .conf.neuralnet import MultiLayerConfiguration
 from .network import BaseNetwork, _as_tensor
 from ..utils.crash import guard_fit
+from ..utils import nvtx as _nvtx
 
 
 class MultiLayerNetwork(BaseNetwork):
@@ -104,7 +105,11 @@ class MultiLayerNetwork(BaseNetwork):
                 x = pps[i].preProcess(x, ctx["minibatch"], ctx)
                 mask = pps[i].feed_forward_mask(mask, ctx["minibatch"])
             p = self.param_views.get(str(i), {})
-            x = l.forward(p, x, training, mask, ctx)
+            if _nvtx._on:
+                with _nvtx.range(f"layer {i} {type(l).__name__}"):
+                    x = l.forward(p, x, training, mask, ctx)
+            else:
+                x = l.forward(p, x, training, mask, ctx)
             mask = l.feed_forward_mask(mask)
             if collect is not None:
                 collect.append(x)

@@ -17,6 +17,7 @@ from ..nd.dtype import DataType
 from ..nd.ndarray import INDArray, wrap, _unwrap
 from .conf.base import ParamSpec, flat_view
 from .updater import MultiLayerUpdater, ParamEntry
+from ..utils import nvtx as _nvtx
 
 
 def _as_tensor(x, device=None, dtype=None):
@@ -337,6 +338,10 @@ class BaseNetwork:
 
     # ------------------------------------------------------------------ step skeleton
     def _apply_update(self):
+        with _nvtx.range("updater"):
+            return self._apply_update_impl()
+
+    def _apply_update_impl(self):
         """updater -> step (-> constraints), between backward and ``iterationDone``."""
         if self.gradient_hook is not None:
             if self.gradient_hook(self) is True:   # hook consumed the gradient and stepped the params
