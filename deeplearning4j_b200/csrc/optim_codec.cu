@@ -51,39 +51,57 @@ fused_update_kernel(float* __restrict__ params, float* __restrict__ grads, float
   const bool r_al = res && (reinterpret_cast<uintptr_t>(res + head) & 15) == 0;
   const bool s_al = sh && (reinterpret_cast<uintptr_t>(sh + head) & 7) == 0;
   const int nvec = pg_ok ? (ch.count - head) / 4 : 0;
-  for (int q = threadIdx.x; q < nvec; q += UPD_THREADS) {
-    const int i = head + 4 * q;
-    const float4 w4 = *reinterpret_cast<const float4*>(p + i);
-    const float4 g4 = *reinterpret_cast<const float4*>(g + i);
-    float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = a4, c4 = a4;
-    if (ns > 0) a4 = upd_ld4(st0 + i, a_al);
-    if (ns > 1) b4 = upd_ld4(st1 + i, b_al);
-    if (ns > 2) c4 = upd_ld4(st2 + i, c_al);
-    float w[4] = {w4.x, w4.y, w4.z, w4.w}, gr[4] = {g4.x, g4.y, g4.z, g4.w};
-    float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w}, c[4] = {c4.x, c4.y, c4.z, c4.w}, u[4];
+  // vectors per thread and iteration, every load issued before the first use.  Measured on 105 M parameters (Adam, fp32): one
+  // vector 0.469 ms (0.96 of the copy bandwidth), two vectors 0.575 ms (124 registers: fewer resident warps outweigh the extra
+  // bytes in flight per thread)
+  constexpr int U = 1;
+  for (int q0 = threadIdx.x; q0 < nvec; q0 += U * UPD_THREADS) {
+    float4 w4[U], g4[U], a4[U], b4[U], c4[U], r4[U];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) u[j] = updater_step(sg, h, w[j], gr[j] * grad_scale, a + j, b + j, c + j);
-    if (ns > 0) upd_st4(st0 + i, make_float4(a[0], a[1], a[2], a[3]), a_al);
-    if (ns > 1) upd_st4(st1 + i, make_float4(b[0], b[1], b[2], b[3]), b_al);
-    if (ns > 2) upd_st4(st2 + i, make_float4(c[0], c[1], c[2], c[3]), c_al);
-    if (res) {
-      float4 r4 = upd_ld4(res + i, r_al);
-      r4.x += u[0]; r4.y += u[1]; r4.z += u[2]; r4.w += u[3];
-      upd_st4(res + i, r4, r_al);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) w[j] -= u[j];
-      *reinterpret_cast<float4*>(p + i) = make_float4(w[0], w[1], w[2], w[3]);
-      if (sh) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(w[0], w[1]), hi = __floats2bfloat162_rn(w[2], w[3]);
-        if (s_al) {
-          *reinterpret_cast<uint2*>(sh + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-        } else {
-          sh[i] = lo.x; sh[i + 1] = lo.y; sh[i + 2] = hi.x; sh[i + 3] = hi.y;
-        }
+    for (int t = 0; t < U; ++t) {
+      const int q = q0 + t * UPD_THREADS;
+      w4[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+      g4[t] = w4[t]; a4[t] = w4[t]; b4[t] = w4[t]; c4[t] = w4[t]; r4[t] = w4[t];
+      if (q < nvec) {
+        const int i = head + 4 * q;
+        w4[t] = *reinterpret_cast<const float4*>(p + i);
+        g4[t] = *reinterpret_cast<const float4*>(g + i);
+        if (ns > 0) a4[t] = upd_ld4(st0 + i, a_al);
+        if (ns > 1) b4[t] = upd_ld4(st1 + i, b_al);
+        if (ns > 2) c4[t] = upd_ld4(st2 + i, c_al);
+        if (res) r4[t] = upd_ld4(res + i, r_al);
       }
     }
-    if (zero_grads) *reinterpret_cast<float4*>(g + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < U; ++t) {
+      const int q = q0 + t * UPD_THREADS;
+      if (q >= nvec) continue;
+      const int i = head + 4 * q;
+      float w[4] = {w4[t].x, w4[t].y, w4[t].z, w4[t].w}, gr[4] = {g4[t].x, g4[t].y, g4[t].z, g4[t].w};
+      float a[4] = {a4[t].x, a4[t].y, a4[t].z, a4[t].w}, b[4] = {b4[t].x, b4[t].y, b4[t].z, b4[t].w},
+            c[4] = {c4[t].x, c4[t].y, c4[t].z, c4[t].w}, u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) u[j] = updater_step(sg, h, w[j], gr[j] * grad_scale, a + j, b + j, c + j);
+      if (ns > 0) upd_st4(st0 + i, make_float4(a[0], a[1], a[2], a[3]), a_al);
+      if (ns > 1) upd_st4(st1 + i, make_float4(b[0], b[1], b[2], b[3]), b_al);
+      if (ns > 2) upd_st4(st2 + i, make_float4(c[0], c[1], c[2], c[3]), c_al);
+      if (res) {
+        upd_st4(res + i, make_float4(r4[t].x + u[0], r4[t].y + u[1], r4[t].z + u[2], r4[t].w + u[3]), r_al);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] -= u[j];
+        *reinterpret_cast<float4*>(p + i) = make_float4(w[0], w[1], w[2], w[3]);
+        if (sh) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(w[0], w[1]), hi = __floats2bfloat162_rn(w[2], w[3]);
+          if (s_al) {
+            *reinterpret_cast<uint2*>(sh + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          } else {
+            sh[i] = lo.x; sh[i + 1] = lo.y; sh[i + 2] = hi.x; sh[i + 3] = hi.y;
+          }
+        }
+      }
+      if (zero_grads) *reinterpret_cast<float4*>(g + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   // scalar head and tail
   const int tail0 = head + 4 * nvec;
