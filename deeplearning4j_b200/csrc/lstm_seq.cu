@@ -55,11 +55,18 @@ __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// Acquire loads: once the target is seen, the other CTAs' stores that preceded their (fenced) arrivals are visible to this thread;
+// no separate fence is needed after the wait.
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, int* status) {
-  if (*((volatile const unsigned int*)counter) >= target) return true;
+  if (ld_acquire_gpu(counter) >= target) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
-  while (*((volatile const unsigned int*)counter) < target) {
+  while (ld_acquire_gpu(counter) < target) {
     if ((++spins & 0xff) == 0 && (clock64() - t0 > 4000000000LL || *((volatile int*)status) != 0)) {
       atomicCAS(status, 0, DL4J_ERR_TIMEOUT_PEER);
       return false;
@@ -149,7 +156,6 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
         if (s > 0) {
           ok = wait_counter(p.counter, arrivals_per_step * (unsigned)s, p.status);   // every CTA published h of step s-1
           if (!ok) break;
-          __threadfence();
           fence_proxy_async_all();       // generic-proxy stores of other CTAs -> async-proxy (TMA) reads below
         }
         ls_stamp(p.trace, s, 0);
@@ -382,7 +388,6 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
         const int t_src = p.reverse ? p.T - 1 - s_src : s_src;
         ok = wait_counter(p.counter, arrivals_per_step * (unsigned)(r + 1), p.status);
         if (!ok) break;
-        __threadfence();
         fence_proxy_async_all();
         ls_stamp(p.trace, r, 0);
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -670,7 +675,6 @@ lstm_seq_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmap_dz, const _
         const int t_src = p.reverse ? p.T - 1 - s_src : s_src;
         ok = wait_counter(p.counter, arrivals_per_step * (unsigned)(r + 1), p.status);
         if (!ok) break;
-        __threadfence();
         fence_proxy_async_all();
         ls_stamp(p.trace, r, 0);
         for (int kb = 0; kb < kblocks; ++kb) {
