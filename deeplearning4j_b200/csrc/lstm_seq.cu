@@ -62,6 +62,9 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void red_release_add(unsigned int* p) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
 __device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, int* status) {
   if (ld_acquire_gpu(counter) >= target) return true;
   const long long t0 = clock64();
@@ -283,9 +286,9 @@ lstm_seq_fwd_kernel(const __grid_constant__ CUtensorMap tmap_h, const __grid_con
       fence_proxy_async_all();
       epilogue_bar_sync();                         // every epilogue thread's stores precede the barrier; the one fence below is cumulative
       if (threadIdx.x == 32 * LS_EPI_WARP0) {
-        __threadfence();
         ls_stamp(p.trace, s, 22);
-        atomicAdd(p.counter, 1u);                  // one arrive per CTA
+        red_release_add(p.counter);                // one arrive per CTA; the release orders every epilogue thread's stores
+                                                   // (they precede the barrier above) before the increment becomes visible
       }
       if (threadIdx.x == 32 * LS_EPI_WARP0) ls_stamp(p.trace, s, 23);
       if (row_ok) {
@@ -533,9 +536,8 @@ lstm_seq_bwd_kernel(const __grid_constant__ CUtensorMap tmap_dz, const __grid_co
       fence_proxy_async_all();
       epilogue_bar_sync();
       if (threadIdx.x == 32 * LS_EPI_WARP0) {
-        __threadfence();
         if (r >= 0) ls_stamp(p.trace, r, 22);
-        atomicAdd(p.counter, 1u);
+        red_release_add(p.counter);
       }
     }
     if (row_ok && p.dc0) {
@@ -879,9 +881,8 @@ lstm_seq_bwd_cluster_kernel(const __grid_constant__ CUtensorMap tmap_dz, const _
       fence_proxy_async_all();
       epilogue_bar_sync();
       if (threadIdx.x == 32 * LS_EPI_WARP0) {
-        __threadfence();
         if (r >= 0) ls_stamp(p.trace, r, 22);
-        atomicAdd(p.counter, 1u);
+        red_release_add(p.counter);
       }
     }
     if (row_ok && p.dc0) {
