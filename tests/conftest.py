@@ -18,3 +18,13 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _crash_dumps_into_tmp(tmp_path_factory):
+    """Tests that make ``fit`` fail with an out-of-memory error (fault-injection listeners, the crash-dump tests) would drop their
+    memory dumps into the working directory; send them to a scratch folder instead."""
+    from deeplearning4j_b200.utils.crash import CrashReportingUtil
+    CrashReportingUtil.crashDumpOutputDirectory(str(tmp_path_factory.getbasetemp()))
+    yield
+    CrashReportingUtil.crashDumpOutputDirectory(None)
