@@ -408,7 +408,7 @@ class Hdf5Writer:
                 raw = n.encode("utf-8") + b"\0"
                 heap_data.extend(raw + b"\0" * (_pad8(len(raw)) - len(raw)))
             seg = alloc(bytes(heap_data))
-            heap = alloc(struct.pack("<4sB3xQQQ", b"HEAP", 0, len(heap_data), UNDEF, seg))
+            heap = alloc(struct.pack("<4sB3xQQQ", b"HEAP", 0, len(heap_data), 1, seg))        # free-list head 1 = "no free block" (H5HL_FREE_NULL)
             snod = struct.pack("<4sBBH", b"SNOD", 1, 0, len(names))
             for n in names:
                 snod += struct.pack("<QQII16x", offs[n], child_hdrs[n], 0, 0)
