@@ -5,9 +5,9 @@
 Supported subset of the file format (HDF5 File Format Specification, the structures that h5py / the HDF5 1.8+ library write by
 default): superblock versions 0 and 1, version-1 object headers with continuation blocks, old-style groups (symbol-table message,
 version-1 B-tree, ``SNOD`` nodes, local heap), dataspace messages v1 / v2, datatype classes fixed-point, floating-point, string and
-variable-length string, contiguous and compact data layouts (message versions 1 - 3), attribute messages v1 - v3, global heap
-collections for variable-length data.  New-style groups (link messages, fractal heaps: ``libver='latest'``), chunked or filtered
-datasets and superblock versions 2 / 3 raise ``Hdf5FormatError`` with the name of the unsupported structure.
+variable-length string, contiguous, compact and chunked data layouts (B-tree-indexed chunks with the deflate, shuffle and fletcher32
+filters), attribute messages v1 - v3, global heap collections for variable-length data.  New-style groups (link messages, fractal
+heaps: ``libver='latest'``), other filters and superblock versions 2 / 3 raise ``Hdf5FormatError`` with the name of the unsupported structure.
 """
 from __future__ import annotations
 
@@ -82,6 +82,39 @@ def _pad8(n):
     return (n + 7) & ~7
 
 
+def _decode_filters(m):
+    """Filter pipeline message (0x000B) -> [(filter id, client data)]; versions 1 and 2."""
+    ver, nf = m[0], m[1]
+    p = 8 if ver == 1 else 2
+    out = []
+    for _ in range(nf):
+        fid = struct.unpack_from("<H", m, p)[0]
+        if ver == 1 or fid >= 256:
+            name_len = struct.unpack_from("<H", m, p + 2)[0]
+            flags, ncd = struct.unpack_from("<HH", m, p + 4)
+            p += 8 + (_pad8(name_len) if ver == 1 else name_len)
+        else:
+            flags, ncd = struct.unpack_from("<HH", m, p + 2)
+            p += 6
+        cd = [struct.unpack_from("<I", m, p + 4 * i)[0] for i in range(ncd)]
+        p += 4 * ncd + (4 if ver == 1 and ncd % 2 else 0)
+        out.append((fid, cd))
+    return tuple(out)
+
+
+def _unfilter(fid, cd, raw, elem_size):
+    if fid == 1:                                            # deflate
+        import zlib
+        return zlib.decompress(raw)
+    if fid == 2:                                            # shuffle: byte planes back to elements
+        n = len(raw) // elem_size
+        a = np.frombuffer(raw, dtype=np.uint8, count=n * elem_size).reshape(elem_size, n)
+        return a.T.tobytes() + raw[n * elem_size:]
+    if fid == 3:                                            # fletcher32: four checksum bytes behind the data
+        return raw[:-4]
+    raise Hdf5FormatError(f"filter {fid} (only deflate, shuffle and fletcher32 are supported)")
+
+
 # ----------------------------------------------------------------------------- reader
 class _Node:
     def __init__(self, f, addr, name):
@@ -135,6 +168,31 @@ class Hdf5Group(_Node):
 
 
 class Hdf5Dataset(_Node):
+    _filters = ()
+
+    def _read_chunked(self, lay, shape, size, n):
+        """Layout class 2: chunks of a fixed shape indexed by a version-1 B-tree whose keys carry the chunk's offset in the dataset."""
+        if lay[0] != 3:
+            raise Hdf5FormatError(f"chunked layout message version {lay[0]}")
+        rank1 = lay[2]                                       # dataset rank + 1 (the last "dimension" is the element size)
+        btree = struct.unpack_from("<Q", lay, 3)[0]
+        cdims = [struct.unpack_from("<I", lay, 11 + 4 * i)[0] for i in range(rank1)]
+        chunk_shape, rank = tuple(cdims[:-1]), rank1 - 1
+        out = bytearray(n * size)
+        arr = np.frombuffer(out, dtype=np.uint8).reshape(tuple(shape) + (size,)) if shape else None
+        if btree == UNDEF:
+            return bytes(out)
+        for offsets, addr, nbytes, mask in self.f._chunk_entries(btree, rank1):
+            raw = self.f._read(addr, nbytes)
+            for k, (fid, cd) in enumerate(reversed(self._filters)):       # undo the pipeline back to front
+                if mask & (1 << (len(self._filters) - 1 - k)):
+                    continue                                          # this filter was skipped for this chunk
+                raw = _unfilter(fid, cd, raw, size)
+            chunk = np.frombuffer(raw, dtype=np.uint8, count=int(np.prod(chunk_shape)) * size).reshape(chunk_shape + (size,))
+            sel = tuple(slice(o, min(o + c, s)) for o, c, s in zip(offsets, chunk_shape, shape))
+            arr[sel] = chunk[tuple(slice(0, e.stop - e.start) for e in sel)]
+        return bytes(out)
+
     def _meta(self):
         shape = dtype = layout = None
         for t, m in self.messages():
@@ -145,7 +203,7 @@ class Hdf5Dataset(_Node):
             elif t == 0x0008:
                 layout = m
             elif t == 0x000B:
-                raise Hdf5FormatError("filtered (compressed) datasets")
+                self._filters = _decode_filters(m)
         return shape, dtype, layout
 
     @property
@@ -171,7 +229,7 @@ class Hdf5Dataset(_Node):
                 nbytes = struct.unpack_from("<H", lay, 2)[0]
                 raw = bytes(lay[4:4 + nbytes])
             else:
-                raise Hdf5FormatError("chunked datasets")
+                raw = self._read_chunked(lay, shape, size, n)
         elif ver in (1, 2):
             rank, cls = lay[1], lay[2]
             if cls == 1:
@@ -274,6 +332,24 @@ class Hdf5File(Hdf5Group):
             yield from self._group_entries(child, heap_addr)
             p += 16
 
+    def _chunk_entries(self, btree_addr, rank1):
+        """(chunk offsets in the dataset, address, stored size, filter mask) of every chunk under a version-1 B-tree of type 1."""
+        d, a = self.data, self.base + btree_addr
+        if d[a:a + 4] != b"TREE" or d[a + 4] != 1:
+            raise Hdf5FormatError("chunk B-tree node")
+        level, used = d[a + 5], struct.unpack_from("<H", d, a + 6)[0]
+        key_size = 8 + 8 * rank1
+        p = a + 24
+        for _ in range(used):
+            nbytes, mask = struct.unpack_from("<II", d, p)
+            offs = [struct.unpack_from("<Q", d, p + 8 + 8 * i)[0] for i in range(rank1 - 1)]
+            child = struct.unpack_from("<Q", d, p + key_size)[0]
+            if level == 0:
+                yield offs, child, nbytes, mask
+            else:
+                yield from self._chunk_entries(child, rank1)
+            p += key_size + 8
+
     def _global_heap_object(self, coll_addr, index):
         d, a = self.data, self.base + coll_addr
         if d[a:a + 4] != b"GCOL":
@@ -345,9 +421,13 @@ class Hdf5Writer:
         self._node(path)
         return path
 
-    def dataset(self, path, array):
+    def dataset(self, path, array, chunks=None, compression=None, shuffle=False):
+        """``chunks``: chunk shape (chunked layout); ``compression="gzip"`` and ``shuffle`` add the filters h5py would."""
         n = self._node(path)
         n["data"] = np.ascontiguousarray(array)
+        if chunks is not None or compression or shuffle:
+            n["chunks"] = tuple(chunks) if chunks is not None else tuple(max(1, d) for d in n["data"].shape)
+            n["filters"] = ([2] if shuffle else []) + ([1] if compression else [])
         return path
 
     def attr(self, path, name, value):
@@ -394,6 +474,38 @@ class Hdf5Writer:
 
         def write_node(node):
             msgs = [attr_message(k, v) for k, v in node["attrs"].items()]
+            if "data" in node and "chunks" in node:
+                arr, cs, filters = node["data"], node["chunks"], node["filters"]
+                esz, rank = arr.dtype.itemsize, arr.ndim
+                entries = []
+                import itertools
+                import zlib
+                for idx in itertools.product(*[range(0, max(s, 1), c) for s, c in zip(arr.shape, cs)]):
+                    chunk = np.zeros(cs, dtype=arr.dtype)
+                    sel = tuple(slice(o, min(o + c, s)) for o, c, s in zip(idx, cs, arr.shape))
+                    chunk[tuple(slice(0, e.stop - e.start) for e in sel)] = arr[sel]
+                    raw = chunk.tobytes()
+                    for fid in filters:
+                        if fid == 2:
+                            raw = np.frombuffer(raw, dtype=np.uint8).reshape(-1, esz).T.tobytes()
+                        elif fid == 1:
+                            raw = zlib.compress(raw, 4)
+                    entries.append((idx, alloc(raw), len(raw)))
+                key = lambda offs, nbytes: struct.pack("<II", nbytes, 0) + b"".join(struct.pack("<Q", o) for o in offs) + struct.pack("<Q", 0)
+                tree = struct.pack("<4sBBHQQ", b"TREE", 1, 0, len(entries), UNDEF, UNDEF)
+                for idx, addr, nbytes in entries:
+                    tree += key(idx, nbytes) + struct.pack("<Q", addr)
+                tree += key(tuple(s for s in arr.shape), 0)                      # closing key: one past the last chunk
+                btree = alloc(tree)
+                layout = struct.pack("<BBBQ", 3, 2, rank + 1, btree) + b"".join(struct.pack("<I", c) for c in cs) + struct.pack("<I", esz)
+                dmsgs = [(0x0001, _encode_dataspace(arr.shape)), (0x0003, _encode_datatype(arr.dtype)), (0x0008, layout)]
+                if filters:
+                    fm = struct.pack("<BB6x", 1, len(filters))
+                    for fid in filters:
+                        cd = [4] if fid == 1 else [esz]
+                        fm += struct.pack("<HHHH", fid, 0, 1 if fid == 2 else 0, len(cd)) + b"".join(struct.pack("<I", c) for c in cd) + b"\0" * 4
+                    dmsgs.append((0x000B, fm))
+                return header(dmsgs + msgs), None
             if "data" in node:
                 arr = node["data"]
                 addr = alloc(arr.tobytes()) if arr.size else UNDEF

@@ -119,3 +119,17 @@ def test_keras_json_plus_weights_only_file(tmp_path):
     out = net.output(x)
     ref = torch.softmax(torch.tanh(torch.tensor(b1)) @ torch.tensor(k2) + torch.tensor(b2), -1).expand(2, 3)
     torch.testing.assert_close(out.t if hasattr(out, "t") else out, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_chunked_and_compressed_datasets():
+    g = np.random.default_rng(3)
+    a = g.standard_normal((37, 21)).astype(np.float32)
+    b = np.arange(1000, dtype=np.int32)
+    w = Hdf5Writer()
+    w.dataset("plain_chunks", a, chunks=(16, 8))                        # edge chunks are partly outside the dataset
+    w.dataset("gzip", a, chunks=(10, 21), compression="gzip")
+    w.dataset("shuffle_gzip", b, chunks=(256,), compression="gzip", shuffle=True)
+    f = Hdf5File(w.tobytes())
+    np.testing.assert_array_equal(np.asarray(f["plain_chunks"]), a)
+    np.testing.assert_array_equal(np.asarray(f["gzip"]), a)
+    np.testing.assert_array_equal(np.asarray(f["shuffle_gzip"]), b)
