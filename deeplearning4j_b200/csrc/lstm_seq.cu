@@ -989,31 +989,22 @@ DL4J_API int dl4j_lstm_seq_fwd(const void* zx, const void* rw, void* h_all, cons
 
 // dout [T, mb, n] bf16; gates [T, mb, 4n] bf16; cs [T, mb, n] fp32; c0 [mb, n] fp32; rwt [n, 4n] bf16 row-major (row j = weights
 // from unit j into every gate column); dzx [T, mb, 4n] bf16 out; dc_last / dh0 / dc0 optional.  Same limits as the forward entry.
-DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float* cs, const float* c0, const void* rwt, void* dzx,
-                               const float* dc_last, void* dh0, float* dc0, int T, int mb, int n, int reverse, unsigned int* counter,
-                               void* stream_) {
-  if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
+// One attempt with `csz` CTAs per cluster (1 = the single-CTA form).  Returns 1 when this form cannot be set up for the problem
+// (shape, shared memory), a CUDA error code when the launch itself was refused, 0 when the kernel is in the stream.
+static int lstm_bwd_launch(int csz, const void* dout, const void* gates, const float* cs, const float* c0, const void* rwt, void* dzx,
+                           const float* dc_last, void* dh0, float* dc0, int T, int mb, int n, int reverse, unsigned int* counter,
+                           cudaStream_t stream) {
   const int kblocks = 4 * n / LS_BK;
-  int a_rows, stages;
-  // cluster form (CS CTAs share 16 CS units and split the gate columns): same resident bytes, 1 / CS of the L2 -> SM stream per CTA
-  int csz = lstm_cluster_size();
-  while (csz > 1 && !((n / LS_UNITS) % csz == 0 && kblocks % csz == 0 && kblocks / csz >= LS_ISSUERS)) csz /= 2;   // every issuer needs a k-block per round
+  if (csz > 1 && !((n / LS_UNITS) % csz == 0 && kblocks % csz == 0 && kblocks / csz >= LS_ISSUERS)) return 1;   // every issuer needs a k-block per round
+  int a_rows = 0, stages = 0;
   const int rows8 = (mb + 7) / 8 * 8;
-  size_t smem = 0;
-  while (csz > 1) {                   // a smaller cluster when the exchange buffers leave no room for the ring
-    const size_t xchg_bytes = (size_t)3 * (csz - 1) * rows8 * LS_UNITS * sizeof(float);     // two receive parities + one staging buffer
-    smem = ls_ring((size_t)(kblocks / csz) * (csz * LS_UNITS * LS_BK * 2) + xchg_bytes, mb, &a_rows, &stages);
-    if (smem) break;
-    csz /= 2;
-  }
-  if (csz == 1) smem = ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
-  if (!smem) return -DL4J_ERR_BAD_ARG;
-  int dev = 0, sms = 0;
+  const size_t xchg_bytes = (size_t)3 * (csz - 1) * rows8 * LS_UNITS * sizeof(float);     // two receive parities + one staging buffer
+  const size_t smem = csz > 1 ? ls_ring((size_t)(kblocks / csz) * (csz * LS_UNITS * LS_BK * 2) + xchg_bytes, mb, &a_rows, &stages)
+                              : ls_ring((size_t)kblocks * LB_B_KB, mb, &a_rows, &stages);
+  if (!smem) return 1;
+  int dev = 0;
   cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = n / LS_UNITS;
-  if (grid > sms) return -DL4J_ERR_BAD_ARG;
-  cudaStream_t stream = (cudaStream_t)stream_;
   CUtensorMap td, tw;
   int r = ls_encode(&td, dzx, (uint64_t)4 * n, (uint64_t)mb, (uint64_t)T, (uint64_t)4 * n * 2, (uint64_t)mb * 4 * n * 2, LS_BK, (uint32_t)a_rows);
   if (r) return -1000 - r;
@@ -1031,24 +1022,42 @@ DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float*
   p.counter = counter;
   p.status = dl4j_status_word(dev);
   p.trace = g_lstm_trace;
-  cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) return (int)e;
   void* kern = csz == 4 ? (void*)lstm_seq_bwd_cluster_kernel<4> : csz == 2 ? (void*)lstm_seq_bwd_cluster_kernel<2> : (void*)lstm_seq_bwd_kernel;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)&td, (void*)&tw, (void*)&p};
-  if (csz == 1) {
-    e = cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(LS_THREADS), args, smem, stream);
-  } else {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LS_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-    cudaLaunchAttribute attrs[2];
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = (unsigned)csz; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
-    attrs[1].id = cudaLaunchAttributeCooperative;
-    attrs[1].val.cooperative = 1;
-    cfg.attrs = attrs; cfg.numAttrs = 2;
-    e = cudaLaunchKernelExC(&cfg, kern, args);
+  if (csz == 1) return (int)cudaLaunchCooperativeKernel(kern, dim3(grid), dim3(LS_THREADS), args, smem, stream);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LS_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = (unsigned)csz; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeCooperative;
+  attrs[1].val.cooperative = 1;
+  cfg.attrs = attrs; cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelExC(&cfg, kern, args);
+}
+
+DL4J_API int dl4j_lstm_seq_bwd(const void* dout, const void* gates, const float* cs, const float* c0, const void* rwt, void* dzx,
+                               const float* dc_last, void* dh0, float* dc0, int T, int mb, int n, int reverse, unsigned int* counter,
+                               void* stream_) {
+  if (T < 1 || mb < 1 || mb > LS_M || n < 64 || n % 64 != 0) return -DL4J_ERR_BAD_ARG;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (n / LS_UNITS > sms) return -DL4J_ERR_BAD_ARG;
+  // Cluster form first (CS CTAs share 16 CS units and split the gate columns: the same resident bytes, 1 / CS of the L2 -> SM stream
+  // per CTA); a form that does not fit the problem, or whose launch the driver refuses (a cooperative launch needs every cluster
+  // resident at once, which a partly occupied device or a profiler may not grant), gives way to the next smaller one.
+  int rc = 1;
+  for (int csz = lstm_cluster_size(); csz >= 1; csz /= 2) {
+    rc = lstm_bwd_launch(csz, dout, gates, cs, c0, rwt, dzx, dc_last, dh0, dc0, T, mb, n, reverse, counter, (cudaStream_t)stream_);
+    if (rc == 0) return 0;
+    if (rc < 0) return rc;                       // tensor-map encoding failed: not a matter of the form
+    if (rc != 1) (void)cudaGetLastError();       // a refused launch leaves a (non-sticky) error behind
+    if (csz == 1) break;
   }
-  return (int)e;
+  return rc == 1 ? -DL4J_ERR_BAD_ARG : rc;
 }
