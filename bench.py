@@ -9,7 +9,7 @@ JSON line.  ``value`` is timed on the device with inputs resident; ``e2e`` times
 through ``sd.fit`` including the host->device copy of each step's inputs from pinned memory and a
 device->host read of the loss.  ``--config`` selects one other BASELINE configuration
 (``resnet50``, ``lstm``, ``mlp``, ``gradshare``).  The default run measures the whole headline metric: after BERT it
-times ResNet-50 (same steps / warm-up) and, for N >= 2, the gradient-exchange microbenchmark, and reports them under
+times ResNet-50, the char-LSTM and the MLP (same steps / warm-up) and, for N >= 2, the gradient-exchange microbenchmark, and reports them under
 ``secondary`` of the same JSON line (``--no-secondary`` skips them).  For N >= 2 every runner also checks that the
 replicas hold bit-identical parameters after the timed region (``replicas_equal``); a mismatch ends the run with a
 non-zero exit code.  ``--impl reference`` reports why the reference cannot run here.
@@ -90,7 +90,7 @@ def main():
     ap.add_argument("--library-baseline", action="store_true", help="route ops through torch/cuBLAS + NCCL (baseline B1)")
     ap.add_argument("--mode", default="fused", help="gradient exchange for N>1: fused | nccl")
     ap.add_argument("--no-library-graphs", action="store_true", help="library baseline without CUDA-graph replay (eager launches)")
-    ap.add_argument("--no-secondary", action="store_true", help="default run: BERT only (skip ResNet-50 and gradshare)")
+    ap.add_argument("--no-secondary", action="store_true", help="default run: BERT only (skip ResNet-50, char-LSTM, MLP and gradshare)")
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm()
@@ -129,6 +129,14 @@ def main():
         bad = bad or r2.get("replicas_equal") is False
         gc.collect()
         torch.cuda.empty_cache()
+        # the recurrent and the small dense configuration (a step is one full tBPTT sequence / one minibatch): same steps and warm-up
+        for name in ("lstm", "mlp"):
+            rr = runners.get(name)(args, rank, world, device).run(ClockSampler(local))
+            secondary[name] = {k: rr[k] for k in keep if k in rr}
+            bad = bad or rr.get("replicas_equal") is False
+            del rr
+            gc.collect()
+            torch.cuda.empty_cache()
         if world >= 2:
             r3 = runners.get("gradshare")(args, rank, world, device).run(ClockSampler(local))
             secondary["gradshare"] = {k: r3[k] for k in ("metric", "value", "unit", "ms_per_step", "rows", "clocks", "config") if k in r3}
