@@ -555,12 +555,34 @@ def linear(x, W, b, activation):
         return None
     if not x.is_contiguous():
         x = x.contiguous()
+    if ((W.shape[1] % 8) or (x.shape[1] % 8)) and _PAD_ODD_WIDTHS and x.shape[0] >= 256:
+        return _linear_padded(x, W, b, act)
     if _operand_a(x) is None or _operand_b(W_lp) is None or _operand_b(W_lp.t()) is None:
         return None
     # wgrad needs x as an MN-major operand: row stride multiple of 8 elements, and dz^T likewise
     if (W_lp.shape[1] % 8) or (x.shape[1] % 8):
         return None
     return _LinearFn.apply(x, W, b, act, W_lp)
+
+
+def _linear_padded(x, W, b, act):
+    """Layer widths that are not multiples of 8 (a 77-symbol alphabet, ten classes): the operands are zero-padded to the next
+    multiple with differentiable ops and the fused path runs on the padded problem; the padding columns produce zeros that the
+    final slice drops, and their gradients vanish in the slice's backward."""
+    import torch.nn.functional as F
+    K, N = x.shape[1], W.shape[1]
+    Kp, Np = (K + 7) // 8 * 8, (N + 7) // 8 * 8
+    xp = F.pad(x, (0, Kp - K)) if Kp != K else x
+    Wp = F.pad(W, (0, Np - N, 0, Kp - K))                    # [Kp, Np], row-major copy in the parameter's precision
+    bp = None if b is None else F.pad(b.reshape(-1), (0, Np - N))
+    Wp_lp = Wp.detach().to(x.dtype)
+    if _operand_a(xp) is None or _operand_b(Wp_lp) is None or _operand_b(Wp_lp.t()) is None:
+        return None
+    y = _LinearFn.apply(xp, Wp, bp, act, Wp_lp)
+    return y[:, :N] if Np != N else y
+
+
+_PAD_ODD_WIDTHS = os.environ.get("DL4J_PAD_ODD_WIDTHS", "1") != "0"
 
 
 # =========================================================================== layer norm

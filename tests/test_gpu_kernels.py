@@ -128,6 +128,35 @@ def test_linear_autograd(nat):
         assert _rel(b.grad, br.grad) < 3e-2, name
 
 
+@pytest.mark.parametrize("nIn,nOut", [(77, 256), (256, 77), (77, 10)])
+def test_linear_with_widths_off_the_vector_grid(nat, nIn, nOut):
+    """Widths that are not multiples of 8 run on the fused path through zero padding; values and all three gradients must match."""
+    from deeplearning4j_b200.nn.activations import Activation
+    M = 512
+    g = torch.Generator(device="cuda").manual_seed(nIn * 1000 + nOut)
+    x = torch.randn(M, nIn, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    W = (torch.randn(nOut, nIn, device="cuda", generator=g) * 0.1).t().detach().requires_grad_(True)   # logical [nIn, nOut], 'f' layout
+    b = torch.randn(1, nOut, device="cuda", generator=g).requires_grad_(True)
+    for name in ("IDENTITY", "TANH"):
+        act = Activation.get(name)
+        x.grad = W.grad = b.grad = None
+        before = nat.LAUNCHES
+        y = nat.linear(x, W, b, act)
+        assert y is not None and y.shape == (M, nOut) and nat.LAUNCHES > before
+        dy = torch.randn(M, nOut, device="cuda", generator=g).bfloat16()
+        y.backward(dy)
+        xr = x.detach().float().requires_grad_(True)
+        Wr = W.detach().float().bfloat16().float().requires_grad_(True)
+        br = b.detach().clone().requires_grad_(True)
+        yr = act(xr @ Wr + br)
+        yr.backward(dy.float())
+        torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+        # sums over 512 rows of O(1) products: magnitudes around 20, bf16 rounding of the result alone is about 0.1
+        torch.testing.assert_close(W.grad.float(), Wr.grad, rtol=3e-2, atol=0.3)
+        torch.testing.assert_close(b.grad.float(), br.grad, rtol=3e-2, atol=0.3)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("R,C", [(300, 768), (4100, 768), (2050, 264)])       # small and large row counts take different backward kernels
 def test_layer_norm(nat, dtype, R, C):
