@@ -999,3 +999,44 @@ DL4J_API int dl4j_attn_softmax_bwd(const void* P, void* dP, long long rows, int 
       (const T*)P, (T*)dP, rows, Tk, scale)));
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------ 16-bit matrix transpose
+// out[c, r] = in[r, c] for a row-major [rows, cols] matrix of 2-byte elements (both even).  64 x 64 tiles through shared memory:
+// the loads read 128 contiguous bytes per row, the stores write 128 contiguous bytes per output row (the generic strided copy of
+// the tensor library reaches about 0.8 TB/s on this shape of problem; the recurrent weights are transposed once per tBPTT segment).
+namespace dl4j {
+
+__global__ void __launch_bounds__(256) transpose16_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int rows, int cols) {
+  __shared__ uint16_t tile[64][64 + 2];
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;        // 32 x 8 threads, two adjacent elements per thread
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + ty + 8 * i, c = c0 + 2 * tx;
+    uint32_t v = 0;
+    if (r < rows && c < cols) v = *reinterpret_cast<const uint32_t*>(in + (size_t)r * cols + c);
+    tile[ty + 8 * i][2 * tx] = (uint16_t)(v & 0xffffu);
+    tile[ty + 8 * i][2 * tx + 1] = (uint16_t)(v >> 16);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = c0 + ty + 8 * i, r = r0 + 2 * tx;             // output row c, output columns r, r + 1
+    if (c < cols && r < rows) {
+      const uint32_t v = (uint32_t)tile[2 * tx][ty + 8 * i] | ((uint32_t)tile[2 * tx + 1][ty + 8 * i] << 16);
+      *reinterpret_cast<uint32_t*>(out + (size_t)c * rows + r) = v;
+    }
+  }
+}
+
+}  // namespace dl4j
+
+// in [rows, cols] -> out [cols, rows], both dense row-major 16-bit matrices with even extents and 4-byte aligned bases.
+DL4J_API int dl4j_transpose16(const void* in, void* out, int rows, int cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((rows & 1) || (cols & 1) || (reinterpret_cast<uintptr_t>(in) & 3) || (reinterpret_cast<uintptr_t>(out) & 3)) return -DL4J_ERR_BAD_ARG;
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+  dl4j::transpose16_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint16_t*>(in), reinterpret_cast<uint16_t*>(out),
+                                                                    rows, cols);
+  return (int)cudaGetLastError();
+}

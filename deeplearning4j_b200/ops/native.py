@@ -65,6 +65,7 @@ def _load():
             "dl4j_lstm_cell_bwd": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
             "dl4j_lstm_seq_fwd": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
             "dl4j_lstm_seq_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp],
+            "dl4j_transpose16": [vp, vp, i32, i32, vp],
             "dl4j_bias_act_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
             "dl4j_bn_fwd_train": [vp, vp, vp, vp, vp, vp, i32, f32, f32, i32, vp, vp, vp, vp, vp, i64, i32, vp],
             "dl4j_bn_apply": [vp, vp, vp, vp, i32, vp, i64, i32, vp],
@@ -848,7 +849,7 @@ class _LstmSeqFn(torch.autograd.Function):
             if dh_rec is not None:
                 dout = dout.clone()
                 dout[0 if rev else T - 1] += dh_rec
-            rwt = rw_t.t().contiguous()
+            rwt = transpose16(rw_t)
             need_h0, need_c0 = ctx.needs_input_grad[2], ctx.needs_input_grad[3]
             dh0 = torch.empty((mb, n), dtype=torch.bfloat16, device=cs.device) if need_h0 else None
             dc0 = torch.empty_like(c0) if need_c0 else None
@@ -889,6 +890,16 @@ class _LstmSeqFn(torch.autograd.Function):
                 drw_t = torch.mm(a, b).to(ctx.rw_dtype)
             drw = drw_t.t()
         return dzx, drw, dh_rec, (dc if ctx.needs_input_grad[3] else None), None, None
+
+
+def transpose16(m):
+    """Dense 2-D bf16 / fp16 matrix -> its transpose as a new dense matrix (tiled kernel; falls back to the strided copy)."""
+    if m.dim() == 2 and m.is_contiguous() and m.is_cuda and m.element_size() == 2 and m.shape[0] % 2 == 0 and m.shape[1] % 2 == 0:
+        out = torch.empty((m.shape[1], m.shape[0]), dtype=m.dtype, device=m.device)
+        rc = require().dl4j_transpose16(_ptr(m), _ptr(out), m.shape[0], m.shape[1], _stream())
+        _check(rc, "dl4j_transpose16")
+        return out
+    return m.t().contiguous()
 
 
 def lstm_seq_supported(zx, n, mb):

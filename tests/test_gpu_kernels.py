@@ -505,3 +505,12 @@ def test_fused_mlp_block_matches_fp32_and_the_two_layer_path(precise):
     assert _rel(dx_fused, xf.grad) < 4e-2
     for a, b in ((W1, R1), (b1, r1), (W2, R2), (b2, r2)):
         assert _rel(a.grad, b.grad) < 4e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 1024), (130, 70), (2, 2), (64, 4096)])
+def test_transpose16(nat, rows, cols):
+    for dt in (torch.bfloat16, torch.float16):
+        m = torch.randn(rows, cols, device="cuda").to(dt)
+        out = nat.transpose16(m)
+        assert out.shape == (cols, rows) and out.is_contiguous()
+        assert torch.equal(out, m.t().contiguous())
