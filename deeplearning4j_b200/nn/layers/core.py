@@ -121,33 +121,51 @@ class RnnOutputLayer(BaseOutputLayer):
     def output_type(self, it):
         return InputType.recurrent(self.nOut, getattr(it, "timeSeriesLength", -1), self.rnnDataFormat)
 
-    def _to2d(self, x):
-        if self.rnnDataFormat == RNNFormat.NCW:
+    def _to2d(self, x, time_major=False):
+        """[mb, n, T] (or [mb, T, n]) -> rows.  Row order is (example, time) unless ``time_major``: the recurrent kernels store their
+        output time-major, and taking the rows in (time, example) order then needs no copy (the loss is a sum over rows)."""
+        if time_major:
+            x = x.permute(2, 0, 1) if self.rnnDataFormat == RNNFormat.NCW else x.permute(1, 0, 2)
+        elif self.rnnDataFormat == RNNFormat.NCW:
             x = x.permute(0, 2, 1)
         return x.reshape(-1, x.shape[2])
+
+    def _is_time_major(self, x):
+        if x.dim() != 3:
+            return False
+        return (x.permute(2, 0, 1) if self.rnnDataFormat == RNNFormat.NCW else x.permute(1, 0, 2)).is_contiguous() and not x.is_contiguous()
 
     def pre_output(self, p, x, training):
         x = self.apply_dropout(x, training)
         mb = x.shape[0]
-        z = nnops.linear(self._to2d(x), p["W"], p.get("b"))
+        tm = self._is_time_major(x)
+        z = nnops.linear(self._to2d(x, tm), p["W"], p.get("b"))
+        z._rows_time_major = tm                   # read back by forward / score_from_preout for the same row order
         return z, mb
 
     def forward(self, p, x, training, mask=None, ctx=None):
         z, mb = self.pre_output(p, x, training)
         if ctx is not None:
             ctx["preout"] = z
-        a = self.activation(z, training).reshape(mb, -1, self.nOut)
+        a = self.activation(z, training)
+        if getattr(z, "_rows_time_major", False):
+            a = a.reshape(-1, mb, self.nOut)                                       # [T, mb, nOut]
+            return a.permute(1, 2, 0) if self.rnnDataFormat == RNNFormat.NCW else a.permute(1, 0, 2)
+        a = a.reshape(mb, -1, self.nOut)
         return a.permute(0, 2, 1) if self.rnnDataFormat == RNNFormat.NCW else a
 
-    def labels2d(self, labels):
+    def labels2d(self, labels, time_major=False):
         if labels.dim() == 3:
-            return self._to2d(labels)
-        return labels.reshape(-1, 1) if labels.dim() == 2 and isinstance(self.lossFunction, LossSparseMCXENT) else labels
+            return self._to2d(labels, time_major)
+        if labels.dim() == 2 and isinstance(self.lossFunction, LossSparseMCXENT):
+            return (labels.t() if time_major else labels).reshape(-1, 1)
+        return labels
 
     def score_from_preout(self, preout, labels, mask=None, average=True, minibatch=None):
         mb = minibatch or labels.shape[0]
-        l2 = self.labels2d(labels)
-        m2 = mask.reshape(-1) if mask is not None else None
+        tm = getattr(preout, "_rows_time_major", False)
+        l2 = self.labels2d(labels, tm)
+        m2 = (mask.t() if tm and mask.dim() == 2 else mask).reshape(-1) if mask is not None else None
         if isinstance(self.lossFunction, LossSparseMCXENT):
             l2 = l2.reshape(-1)
         s = BaseOutputLayer.score_from_preout(self, preout, l2, m2, average=False)
