@@ -543,6 +543,148 @@ def _onnx_ops():
             hs.append(h)
         return torch.stack(ys, 1), torch.stack(hs)
 
+    def rnn(x, w, r, b=None, seq_lens=None, h0=None, hidden_size=None, direction="forward", activations=None, **kw):
+        """Elman RNN: h_t = f(x_t W^T + h_{t-1} R^T + Wb + Rb); Y [T, dirs, N, H], Y_h [dirs, N, H]."""
+        T_, N = x.shape[0], x.shape[1]
+        dirs = w.shape[0]
+        H = w.shape[1]
+        acts = [a.decode() if isinstance(a, bytes) else a for a in (activations or ["Tanh"] * dirs)]
+        fmap = {"Tanh": torch.tanh, "Relu": torch.relu, "Sigmoid": torch.sigmoid}
+        ys, hs = [], []
+        for d in range(dirs):
+            f = fmap[acts[d] if d < len(acts) else acts[0]]
+            h = h0[d] if h0 is not None else x.new_zeros(N, H)
+            bias = (b[d, :H] + b[d, H:]) if b is not None else 0
+            order = range(T_ - 1, -1, -1) if (direction == "reverse" or d == 1) else range(T_)
+            out = [None] * T_
+            for t in order:
+                h = f(x[t] @ w[d].t() + h @ r[d].t() + bias)
+                out[t] = h
+            ys.append(torch.stack(out, 0))
+            hs.append(h)
+        return torch.stack(ys, 1), torch.stack(hs, 0)
+
+    def _bcast_axis(t, like, axis):
+        if t.dim() == 0 or t.numel() == 1:
+            return t.reshape(())
+        shp = [1] * like.dim()
+        shp[axis] = -1
+        return t.reshape(shp)
+
+    def quantize_linear(x, scale, zp=None, axis=1, saturate=1, **kw):
+        dt = zp.dtype if zp is not None else torch.uint8
+        lo, hi = (0, 255) if dt == torch.uint8 else (-128, 127)
+        z = _bcast_axis(zp, x, axis).to(x.dtype) if zp is not None else 0
+        return (torch.round(x / _bcast_axis(scale, x, axis)) + z).clamp(lo, hi).to(dt)
+
+    def dequantize_linear(x, scale, zp=None, axis=1, **kw):
+        z = _bcast_axis(zp, x, axis).to(scale.dtype) if zp is not None else 0
+        return (x.to(scale.dtype) - z) * _bcast_axis(scale, x, axis)
+
+    def reverse_sequence(x, lens, batch_axis=1, time_axis=0, **kw):
+        y = x.clone()
+        for bi, L in enumerate(_ints(lens)):
+            sl = [slice(None)] * x.dim()
+            sl[batch_axis] = bi
+            sl[time_axis] = slice(0, L)
+            seg = x[tuple(sl)]
+            ax = time_axis - (1 if batch_axis < time_axis else 0)
+            y[tuple(sl)] = seg.flip(ax)
+        return y
+
+    def unique(x, axis=None, sorted=1, **kw):
+        """Y, first indices, inverse indices, counts (sorted order; ONNX's unsorted order = first occurrence, restored below)."""
+        flat = x.reshape(-1) if axis is None else x
+        y, inv, cnt = torch.unique(flat, sorted=True, return_inverse=True, return_counts=True, dim=None if axis is None else axis)
+        n = y.shape[0] if axis is None else y.shape[axis]
+        inv1 = inv.reshape(-1)
+        first = torch.full((n,), inv1.numel(), dtype=torch.int64)
+        first.scatter_reduce_(0, inv1, torch.arange(inv1.numel()), reduce="amin")
+        if not sorted:
+            order = first.argsort()
+            y = y.index_select(0 if axis is None else axis, order)
+            rank = torch.empty_like(order)
+            rank[order] = torch.arange(n)
+            inv, cnt, first = rank[inv], cnt[order], first[order]
+        return y, first, inv, cnt
+
+    def nms(boxes, scores, max_out=None, iou_thr=None, score_thr=None, center_point_box=0, **kw):
+        """[num_selected, 3] rows (batch, class, box index), greedy per batch and class in order of decreasing score."""
+        m = int(max_out.reshape(-1)[0]) if max_out is not None and max_out.numel() else 0
+        it = float(iou_thr.reshape(-1)[0]) if iou_thr is not None and iou_thr.numel() else 0.0
+        st = float(score_thr.reshape(-1)[0]) if score_thr is not None and score_thr.numel() else None
+        sel = []
+        if m == 0:
+            return torch.zeros((0, 3), dtype=torch.int64)
+        for bi in range(boxes.shape[0]):
+            bx = boxes[bi]
+            if center_point_box:
+                cx, cy, w_, h_ = bx.unbind(1)
+                x1, y1, x2, y2 = cx - w_ / 2, cy - h_ / 2, cx + w_ / 2, cy + h_ / 2
+            else:
+                y1, x1, y2, x2 = bx.unbind(1)
+                x1, x2 = torch.minimum(x1, x2), torch.maximum(x1, x2)
+                y1, y2 = torch.minimum(y1, y2), torch.maximum(y1, y2)
+            area = (x2 - x1) * (y2 - y1)
+            for ci in range(scores.shape[1]):
+                sc = scores[bi, ci]
+                order = sc.argsort(descending=True).tolist()
+                keep = []
+                for i in order:
+                    if st is not None and float(sc[i]) <= st:
+                        break
+                    ok = True
+                    for j in keep:
+                        iw = (torch.minimum(x2[i], x2[j]) - torch.maximum(x1[i], x1[j])).clamp(min=0)
+                        ih = (torch.minimum(y2[i], y2[j]) - torch.maximum(y1[i], y1[j])).clamp(min=0)
+                        inter = iw * ih
+                        union = area[i] + area[j] - inter
+                        if float(union) > 0 and float(inter / union) > it:
+                            ok = False
+                            break
+                    if ok:
+                        keep.append(i)
+                        sel.append([bi, ci, i])
+                        if len(keep) >= m:
+                            break
+        return torch.tensor(sel, dtype=torch.int64).reshape(-1, 3)
+
+    def roi_align(x, rois, batch_idx, mode="avg", output_height=1, output_width=1, sampling_ratio=0, spatial_scale=1.0,
+                  coordinate_transformation_mode="half_pixel", **kw):
+        mode = mode.decode() if isinstance(mode, bytes) else mode
+        ctm = coordinate_transformation_mode.decode() if isinstance(coordinate_transformation_mode, bytes) else coordinate_transformation_mode
+        off = 0.5 if ctm == "half_pixel" else 0.0
+        N, C, H, W = x.shape
+        out = x.new_zeros(rois.shape[0], C, output_height, output_width)
+        for r in range(rois.shape[0]):
+            x1, y1, x2, y2 = [float(v) * spatial_scale - off for v in rois[r].tolist()]
+            rw, rh = x2 - x1, y2 - y1
+            if ctm != "half_pixel":
+                rw, rh = max(rw, 1.0), max(rh, 1.0)
+            bw, bh = rw / output_width, rh / output_height
+            sx = sampling_ratio if sampling_ratio > 0 else max(1, int(-(-rw // output_width)))
+            sy = sampling_ratio if sampling_ratio > 0 else max(1, int(-(-rh // output_height)))
+            img = x[int(batch_idx[r])]
+            for ph in range(output_height):
+                for pw_ in range(output_width):
+                    vals = []
+                    for iy in range(sy):
+                        yy = y1 + ph * bh + (iy + 0.5) * bh / sy
+                        for ix in range(sx):
+                            xx = x1 + pw_ * bw + (ix + 0.5) * bw / sx
+                            if yy < -1.0 or yy > H or xx < -1.0 or xx > W:
+                                vals.append(x.new_zeros(C))
+                                continue
+                            yc, xc = min(max(yy, 0.0), H - 1), min(max(xx, 0.0), W - 1)
+                            y0, x0 = int(yc), int(xc)
+                            y1i, x1i = min(y0 + 1, H - 1), min(x0 + 1, W - 1)
+                            ly, lx = yc - y0, xc - x0
+                            vals.append(img[:, y0, x0] * (1 - ly) * (1 - lx) + img[:, y0, x1i] * (1 - ly) * lx
+                                        + img[:, y1i, x0] * ly * (1 - lx) + img[:, y1i, x1i] * ly * lx)
+                    v = torch.stack(vals, 0)
+                    out[r, :, ph, pw_] = v.mean(0) if mode == "avg" else v.max(0).values
+        return out
+
     T = {
         "Less": (lambda a, b, **k: a < b, 1), "LessOrEqual": (lambda a, b, **k: a <= b, 1), "Greater": (lambda a, b, **k: a > b, 1),
         "GreaterOrEqual": (lambda a, b, **k: a >= b, 1), "Equal": (lambda a, b, **k: a == b, 1), "Not": (lambda a, **k: ~a, 1),
@@ -590,7 +732,17 @@ def _onnx_ops():
         "MeanVarianceNormalization": (lambda x, axes=(0, 2, 3), **k: (x - x.mean(tuple(axes), keepdim=True)) / x.var(tuple(axes), unbiased=False, keepdim=True).sqrt(), 1),
         "GlobalLpPool": (lambda x, p=2, **k: x.norm(p=p, dim=tuple(range(2, x.dim())), keepdim=True), 1),
         "Sqrt": (lambda x, **k: x.sqrt(), 1),
-        "LSTM": (lstm, 3), "GRU": (gru, 2),
+        "LSTM": (lstm, 3), "GRU": (gru, 2), "RNN": (rnn, 2),
+        "Compress": (lambda x, cond, axis=None, **k: (x.reshape(-1)[:cond.numel()][cond.reshape(-1).bool()] if axis is None
+                                                     else x.index_select(axis, cond.reshape(-1).bool().nonzero().reshape(-1))), 1),
+        "Det": (lambda x, **k: torch.linalg.det(x), 1),
+        "Shrink": (lambda x, bias=0.0, lambd=0.5, **k: torch.where(x < -lambd, x + bias, torch.where(x > lambd, x - bias, torch.zeros_like(x))), 1),
+        "GroupNormalization": (lambda x, scale, b, num_groups=1, epsilon=1e-5, **k: F.group_norm(
+            x, int(num_groups), scale if scale.numel() == x.shape[1] else scale.repeat_interleave(x.shape[1] // scale.numel()),
+            b if b.numel() == x.shape[1] else b.repeat_interleave(x.shape[1] // b.numel()), epsilon), 1),
+        "QuantizeLinear": (quantize_linear, 1), "DequantizeLinear": (dequantize_linear, 1),
+        "ReverseSequence": (reverse_sequence, 1), "Unique": (unique, 4),
+        "NonMaxSuppression": (nms, 1), "RoiAlign": (roi_align, 1),
     }
     return T
 

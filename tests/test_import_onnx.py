@@ -191,3 +191,53 @@ def test_if_and_loop_nodes_with_sub_graphs_that_read_the_outer_scope():
         r = {k: v.t for k, v in sd.output({"x": x}, "branch", "acc_final", "terms").items()}
         assert torch.equal(r["branch"], x * 2 if float(x.sum()) > 0 else x - 1)
         assert torch.equal(r["acc_final"], x * (0 + 1 + 2 + 3)) and tuple(r["terms"].shape) == (4, 3) and torch.equal(r["terms"][2], x * 2)
+
+
+def test_remaining_standard_operators_by_their_definitions():
+    """Compress, Det, Shrink, GroupNormalization, Quantize / DequantizeLinear, ReverseSequence, Unique, RNN, NonMaxSuppression and
+    RoiAlign: each rule against the operator's definition written out with plain torch."""
+    from deeplearning4j_b200.importers.onnx_import import _onnx_ops
+    T = {k: v[0] for k, v in _onnx_ops().items()}
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 4, generator=g)
+    assert torch.equal(T["Compress"](x, torch.tensor([0, 1, 1]), axis=0), x[1:3])
+    assert torch.equal(T["Compress"](x, torch.tensor([0, 1, 0, 0, 1])), x.reshape(-1)[[1, 4]])
+    m = torch.randn(2, 3, 3, generator=g)
+    torch.testing.assert_close(T["Det"](m), torch.stack([torch.det(m[0]), torch.det(m[1])]))
+    s = T["Shrink"](torch.tensor([-2.0, -0.3, 0.0, 0.4, 3.0]), bias=1.0, lambd=0.5)
+    assert s.tolist() == [-1.0, 0.0, 0.0, 0.0, 2.0]
+    xg = torch.randn(2, 6, 5, generator=g)
+    sc, b = torch.rand(6, generator=g) + 0.5, torch.randn(6, generator=g)
+    torch.testing.assert_close(T["GroupNormalization"](xg, sc, b, num_groups=3, epsilon=1e-5), F.group_norm(xg, 3, sc, b, 1e-5))
+    q = T["QuantizeLinear"](torch.tensor([[0.0, 1.0, 300.0], [-1.0, 2.49, 2.51]]), torch.tensor(2.0), torch.tensor(3, dtype=torch.uint8))
+    assert q.dtype == torch.uint8 and q.tolist() == [[3, 3, 153], [3, 4, 4]]        # x / 2 rounded half to even (0.5 -> 0, -0.5 -> -0), plus 3
+    d = T["DequantizeLinear"](torch.tensor([[0, 10], [20, 30]], dtype=torch.int8), torch.tensor([0.5, 2.0]), torch.tensor([0, 10], dtype=torch.int8), axis=1)
+    assert d.tolist() == [[0.0, 0.0], [10.0, 40.0]]
+    seq = torch.arange(12.0).reshape(4, 3)                                         # [time, batch]
+    r = T["ReverseSequence"](seq, torch.tensor([4, 2, 1]), batch_axis=1, time_axis=0)
+    assert r[:, 0].tolist() == [9.0, 6.0, 3.0, 0.0] and r[:, 1].tolist() == [4.0, 1.0, 7.0, 10.0] and r[:, 2].tolist() == [2.0, 5.0, 8.0, 11.0]
+    y, first, inv, cnt = T["Unique"](torch.tensor([2.0, 1.0, 1.0, 3.0, 4.0, 3.0]), sorted=1)
+    assert y.tolist() == [1.0, 2.0, 3.0, 4.0] and first.tolist() == [1, 0, 3, 4] and inv.tolist() == [1, 0, 0, 2, 3, 2] and cnt.tolist() == [2, 1, 2, 1]
+    y, first, inv, cnt = T["Unique"](torch.tensor([2.0, 1.0, 1.0, 3.0, 4.0, 3.0]), sorted=0)
+    assert y.tolist() == [2.0, 1.0, 3.0, 4.0] and first.tolist() == [0, 1, 3, 4] and inv.tolist() == [0, 1, 1, 2, 3, 2] and cnt.tolist() == [1, 2, 2, 1]
+    # RNN against torch.nn.RNN
+    rnn = torch.nn.RNN(3, 4, nonlinearity="tanh")
+    xs = torch.randn(5, 2, 3, generator=g)
+    ref_y, ref_h = rnn(xs)
+    W, R = rnn.weight_ih_l0.detach()[None], rnn.weight_hh_l0.detach()[None]
+    B = torch.cat([rnn.bias_ih_l0.detach(), rnn.bias_hh_l0.detach()])[None]
+    Y, Yh = T["RNN"](xs, W, R, B, hidden_size=4)
+    torch.testing.assert_close(Y[:, 0], ref_y.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(Yh, ref_h.detach(), rtol=1e-5, atol=1e-6)
+    # NonMaxSuppression: the second box overlaps the first (IoU 0.68) and is suppressed, the third is far away
+    boxes = torch.tensor([[[0.0, 0.0, 1.0, 1.0], [0.0, 0.1, 1.0, 1.1], [0.0, 2.0, 1.0, 3.0]]])
+    scores = torch.tensor([[[0.9, 0.8, 0.7]]])
+    sel = T["NonMaxSuppression"](boxes, scores, torch.tensor([3]), torch.tensor([0.5]), torch.tensor([0.0]))
+    assert sel.tolist() == [[0, 0, 0], [0, 0, 2]]
+    # RoiAlign: a roi covering one whole 4x4 image pooled to 2x2 with one sample per bin reads the bin centres
+    img = torch.arange(16.0).reshape(1, 1, 4, 4)
+    ra = T["RoiAlign"](img, torch.tensor([[0.0, 0.0, 4.0, 4.0]]), torch.tensor([0]), output_height=2, output_width=2, sampling_ratio=1,
+                       coordinate_transformation_mode="output_half_pixel")
+    # bin centres (1, 1), (1, 3), (3, 1), (3, 3) in input coordinates fall exactly on pixels
+    ref = torch.tensor([[img[0, 0, 1, 1], img[0, 0, 1, 3]], [img[0, 0, 3, 1], img[0, 0, 3, 3]]])
+    torch.testing.assert_close(ra[0, 0], ref)
