@@ -312,6 +312,116 @@ def _tf_ops():
     def bmm(x, y, adj_x=False, adj_y=False, **kw):
         return torch.matmul(x.transpose(-1, -2) if adj_x else x, y.transpose(-1, -2) if adj_y else y)
 
+    def band_part(x, lower, upper, **kw):
+        lo, up = int(lower), int(upper)
+        r = torch.arange(x.shape[-2], device=x.device)[:, None]
+        c = torch.arange(x.shape[-1], device=x.device)[None, :]
+        keep = ((lo < 0) | (r - c <= lo)) & ((up < 0) | (c - r <= up))
+        return x * keep.to(x.dtype)
+
+    def scatter_nd(indices, updates, shape, **kw):
+        out = torch.zeros(_ints(shape), dtype=updates.dtype, device=updates.device)
+        k = indices.shape[-1]
+        idx = tuple(indices[..., j].long() for j in range(k))
+        return out.index_put(idx, updates, accumulate=True)               # duplicate indices add up, as in TensorFlow
+
+    def space_to_batch_nd(x, block_shape, paddings, **kw):
+        bs, pd = _ints(block_shape), paddings.reshape(-1, 2).tolist()
+        m = len(bs)
+        flat = []
+        for d in reversed(range(x.dim())):
+            lo, hi = (pd[d - 1] if 1 <= d <= m else (0, 0))
+            flat += [int(lo), int(hi)]
+        x = F.pad(x, flat)
+        n = x.shape[0]
+        shp = [n]
+        for i in range(m):
+            shp += [x.shape[1 + i] // bs[i], bs[i]]
+        rest = list(x.shape[1 + m:])
+        x = x.reshape(shp + rest)
+        perm = [2 + 2 * i for i in range(m)] + [0] + [1 + 2 * i for i in range(m)] + list(range(1 + 2 * m, 1 + 2 * m + len(rest)))
+        x = x.permute(perm)
+        return x.reshape([n * int(np.prod(bs))] + [shp[1 + 2 * i] for i in range(m)] + rest)
+
+    def batch_to_space_nd(x, block_shape, crops, **kw):
+        bs, cr = _ints(block_shape), crops.reshape(-1, 2).tolist()
+        m = len(bs)
+        n = x.shape[0] // int(np.prod(bs))
+        rest = list(x.shape[1 + m:])
+        x = x.reshape(bs + [n] + list(x.shape[1:1 + m]) + rest)
+        perm = [m]
+        for i in range(m):
+            perm += [m + 1 + i, i]
+        perm += list(range(2 * m + 1, 2 * m + 1 + len(rest)))
+        x = x.permute(perm)
+        x = x.reshape([n] + [x.shape[1 + 2 * i] * x.shape[2 + 2 * i] for i in range(m)] + rest)
+        idx = [slice(None)] + [slice(int(cr[i][0]), x.shape[1 + i] - int(cr[i][1])) for i in range(m)]
+        return x[tuple(idx)]
+
+    def _same3(size, k, st, dl):
+        eff = (k - 1) * dl + 1
+        total = max((-(-size // st) - 1) * st + eff - size, 0)
+        return total // 2, total - total // 2
+
+    def conv3d(x, w, strides=(1, 1, 1, 1, 1), padding="VALID", dilations=(1, 1, 1, 1, 1), data_format="NDHWC", **kw):
+        padding = padding.decode() if isinstance(padding, bytes) else padding
+        cl = (data_format.decode() if isinstance(data_format, bytes) else data_format) == "NDHWC"
+        xn = x.permute(0, 4, 1, 2, 3) if cl else x
+        st = list(strides[1:4]) if cl else list(strides[2:5])
+        dl = list(dilations[1:4]) if cl else list(dilations[2:5])
+        wk = w.permute(4, 3, 0, 1, 2)                                        # DHWIO -> OIDHW
+        if padding == "SAME":
+            flat = []
+            for d in (2, 1, 0):
+                lo, hi = _same3(xn.shape[2 + d], wk.shape[2 + d], st[d], dl[d])
+                flat += [lo, hi]
+            xn = F.pad(xn, flat)
+        y = F.conv3d(xn, wk, None, st, 0, dl)
+        return y.permute(0, 2, 3, 4, 1) if cl else y
+
+    def pool3d(x, kind, ksize=(1, 1, 1, 1, 1), strides=(1, 1, 1, 1, 1), padding="VALID", data_format="NDHWC", **kw):
+        padding = padding.decode() if isinstance(padding, bytes) else padding
+        cl = (data_format.decode() if isinstance(data_format, bytes) else data_format) == "NDHWC"
+        xn = x.permute(0, 4, 1, 2, 3) if cl else x
+        k = list(ksize[1:4]) if cl else list(ksize[2:5])
+        st = list(strides[1:4]) if cl else list(strides[2:5])
+        if padding == "SAME":
+            flat = []
+            for d in (2, 1, 0):
+                lo, hi = _same3(xn.shape[2 + d], k[d], st[d], 1)
+                flat += [lo, hi]
+            if kind == "max":
+                xn = F.pad(xn, flat, value=float("-inf"))
+                y = F.max_pool3d(xn, k, st)
+            else:
+                ones = F.avg_pool3d(F.pad(torch.ones_like(xn[:1, :1]), flat), k, st)
+                y = F.avg_pool3d(F.pad(xn, flat), k, st) / ones
+        else:
+            y = F.max_pool3d(xn, k, st) if kind == "max" else F.avg_pool3d(xn, k, st)
+        return y.permute(0, 2, 3, 4, 1) if cl else y
+
+    def nms_v3(boxes, scores, max_output_size, iou_threshold, score_threshold, **kw):
+        m, it, stt = int(max_output_size), float(iou_threshold), float(score_threshold)
+        y1, x1, y2, x2 = boxes.unbind(1)
+        x1, x2 = torch.minimum(x1, x2), torch.maximum(x1, x2)
+        y1, y2 = torch.minimum(y1, y2), torch.maximum(y1, y2)
+        area = (x2 - x1) * (y2 - y1)
+        keep = []
+        for i in scores.argsort(descending=True).tolist():
+            if float(scores[i]) <= stt or len(keep) >= m:
+                break
+            ok = True
+            for j in keep:
+                inter = (torch.minimum(x2[i], x2[j]) - torch.maximum(x1[i], x1[j])).clamp(min=0) * \
+                        (torch.minimum(y2[i], y2[j]) - torch.maximum(y1[i], y1[j])).clamp(min=0)
+                union = area[i] + area[j] - inter
+                if float(union) > 0 and float(inter / union) > it:
+                    ok = False
+                    break
+            if ok:
+                keep.append(i)
+        return torch.tensor(keep, dtype=torch.int32)
+
     T = {
         "Less": (lambda a, b, **k: a < b, 1), "LessEqual": (lambda a, b, **k: a <= b, 1), "Greater": (lambda a, b, **k: a > b, 1),
         "GreaterEqual": (lambda a, b, **k: a >= b, 1), "Equal": (lambda a, b, **k: a == b, 1), "NotEqual": (lambda a, b, **k: a != b, 1),
@@ -358,6 +468,13 @@ def _tf_ops():
         "BroadcastTo": (lambda x, sh, **k: x.broadcast_to(_ints(sh)), 1), "Einsum": (lambda *xs, equation="", **k: torch.einsum(equation, *xs), 1),
         "MatrixDiag": (lambda x, **k: torch.diag_embed(x), 1), "MatrixDiagPart": (lambda x, **k: torch.diagonal(x, dim1=-2, dim2=-1), 1),
         "Tanh": (lambda x, **k: x.tanh(), 1),
+        "Assert": (lambda cond, *data, **k: cond, 1),                       # checked at import time only when constant; a no-op at run time
+        "ShapeN": (lambda *xs, out_type=None, **k: tuple(torch.tensor(list(x.shape), dtype=torch.int32) for x in xs), -1),
+        "MatrixBandPart": (band_part, 1), "ScatterNd": (scatter_nd, 1),
+        "SpaceToBatchND": (space_to_batch_nd, 1), "BatchToSpaceND": (batch_to_space_nd, 1),
+        "Conv3D": (conv3d, 1), "MaxPool3D": (lambda x, **k: pool3d(x, "max", **k), 1), "AvgPool3D": (lambda x, **k: pool3d(x, "avg", **k), 1),
+        "RandomUniform": (lambda shape, dtype=None, seed=0, seed2=0, **k: torch.rand(_ints(shape)), 1),
+        "NonMaxSuppressionV3": (nms_v3, 1),
     }
     return T
 

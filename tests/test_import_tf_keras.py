@@ -248,3 +248,71 @@ def test_tensorflow_generic_rules_against_torch():
     assert torch.allclose(r["dc"].t, full[:, 0:8, 0:12], atol=1e-5) and ref is not None
     assert torch.allclose(r["red"].t, x.mean(3, keepdim=True), atol=1e-6)
     assert len(TensorflowFrameworkImporter.supportedOps()) >= 150
+
+
+def test_tensorflow_spatial_scatter_and_3d_rules_by_their_definitions():
+    """Rules added for the less common GraphDef ops, each checked against the TensorFlow definition of the op
+    written out in plain torch (tensorflow/core/ops: array_ops.cc, nn_ops.cc, image_ops.cc)."""
+    from deeplearning4j_b200.importers.tf_import import _tf_ops
+    T = {k: v[0] for k, v in _tf_ops().items()}
+    g = torch.Generator().manual_seed(5)
+
+    x = torch.randn(5, 6, generator=g)
+    got = T["MatrixBandPart"](x, torch.tensor(1), torch.tensor(-1))
+    assert torch.equal(got, torch.triu(x, -1))
+    got = T["MatrixBandPart"](x, torch.tensor(0), torch.tensor(2))
+    assert torch.equal(got, torch.triu(x) - torch.triu(x, 3))
+
+    idx = torch.tensor([[0, 1], [2, 3], [0, 1]])
+    upd = torch.tensor([1.0, 2.0, 4.0])
+    out = T["ScatterNd"](idx, upd, torch.tensor([3, 4]))
+    ref = torch.zeros(3, 4); ref[0, 1] = 5.0; ref[2, 3] = 2.0
+    assert torch.equal(out, ref)
+    rows = T["ScatterNd"](torch.tensor([[1]]), torch.ones(1, 4), torch.tensor([3, 4]))
+    assert torch.equal(rows[1], torch.ones(4)) and rows.sum() == 4
+
+    # space-to-batch with block 2 is the inverse pixel shuffle with the block index moved into the batch
+    x = torch.arange(1 * 4 * 6 * 2, dtype=torch.float32).reshape(1, 4, 6, 2)
+    y = T["SpaceToBatchND"](x, torch.tensor([2, 2]), torch.zeros(2, 2, dtype=torch.int64))
+    assert tuple(y.shape) == (4, 2, 3, 2)
+    for bi in range(2):
+        for bj in range(2):
+            assert torch.equal(y[bi * 2 + bj, :, :, :], x[0, bi::2, bj::2, :])
+    back = T["BatchToSpaceND"](y, torch.tensor([2, 2]), torch.zeros(2, 2, dtype=torch.int64))
+    assert torch.equal(back, x)
+    # padding on the way in, the same crops on the way out
+    x = torch.randn(2, 3, 5, 1, generator=g)
+    pad = torch.tensor([[1, 0], [0, 1]])
+    y = T["SpaceToBatchND"](x, torch.tensor([2, 2]), pad)
+    assert tuple(y.shape) == (8, 2, 3, 1)
+    assert torch.equal(T["BatchToSpaceND"](y, torch.tensor([2, 2]), pad), x)
+
+    x = torch.randn(2, 5, 6, 7, 3, generator=g)
+    w = torch.randn(3, 3, 3, 3, 4, generator=g)
+    y = T["Conv3D"](x, w, strides=[1, 1, 1, 1, 1], padding=b"SAME")
+    ref = F.conv3d(x.permute(0, 4, 1, 2, 3), w.permute(4, 3, 0, 1, 2), padding=1).permute(0, 2, 3, 4, 1)
+    assert torch.allclose(y, ref, atol=1e-5)
+    y = T["Conv3D"](x, w, strides=[1, 2, 2, 2, 1], padding=b"VALID")
+    ref = F.conv3d(x.permute(0, 4, 1, 2, 3), w.permute(4, 3, 0, 1, 2), stride=2).permute(0, 2, 3, 4, 1)
+    assert torch.allclose(y, ref, atol=1e-5)
+    y = T["MaxPool3D"](x, ksize=[1, 2, 2, 2, 1], strides=[1, 2, 2, 2, 1], padding=b"VALID")
+    assert torch.equal(y, F.max_pool3d(x.permute(0, 4, 1, 2, 3), 2, 2).permute(0, 2, 3, 4, 1))
+    y = T["MaxPool3D"](x, ksize=[1, 2, 2, 2, 1], strides=[1, 2, 2, 2, 1], padding=b"SAME")
+    assert tuple(y.shape) == (2, 3, 3, 4, 3)
+    assert torch.equal(y[:, 2, :, 3, :], x[:, 4, :, 6, :].reshape(2, 3, 2, 3).amax(2))   # the ragged corner sees only real elements
+    y = T["AvgPool3D"](x, ksize=[1, 2, 2, 2, 1], strides=[1, 2, 2, 2, 1], padding=b"SAME")
+    assert torch.allclose(y[:, 2, :, 3, :], x[:, 4, :, 6, :].reshape(2, 3, 2, 3).mean(2), atol=1e-6)
+
+    a, b = T["ShapeN"](torch.zeros(2, 3), torch.zeros(4))
+    assert a.tolist() == [2, 3] and b.tolist() == [4]
+    r = T["RandomUniform"](torch.tensor([3, 5]))
+    assert tuple(r.shape) == (3, 5) and float(r.min()) >= 0 and float(r.max()) < 1
+    c = torch.tensor(True)
+    assert T["Assert"](c, torch.zeros(1)) is c
+
+    boxes = torch.tensor([[0, 0, 1, 1], [0, 0.1, 1, 1.1], [0, -0.1, 1, 0.9], [0, 10, 1, 11], [0, 10.1, 1, 11.1], [0, 100, 1, 101]], dtype=torch.float32)
+    scores = torch.tensor([0.9, 0.75, 0.6, 0.95, 0.5, 0.3])
+    sel = T["NonMaxSuppressionV3"](boxes, scores, torch.tensor(3), torch.tensor(0.5), torch.tensor(0.0))
+    assert sel.tolist() == [3, 0, 5]
+    sel = T["NonMaxSuppressionV3"](boxes, scores, torch.tensor(6), torch.tensor(0.5), torch.tensor(0.4))
+    assert sel.tolist() == [3, 0]
