@@ -14,7 +14,11 @@ import torch
 
 from .. import nn
 from ..nn.conf.graphconf import ElementWiseVertex, MergeVertex
-from ..nn.conf.preprocessors import CnnToFeedForwardPreProcessor
+from ..nn.conf.graphconf import PreprocessorVertex
+from ..nn.conf.preprocessors import CnnToFeedForwardPreProcessor, ComposableInputPreProcessor, PermutePreprocessor, ReshapePreprocessor
+
+_LAMBDA_LAYERS = {}          # Keras Lambda layer name -> layer (KerasLayer.registerLambdaLayer)
+_CUSTOM_LAYERS = {}          # Keras class name -> callable(config) -> layer (KerasLayer.registerCustomLayer)
 
 _ACT = {"relu": "RELU", "sigmoid": "SIGMOID", "tanh": "TANH", "softmax": "SOFTMAX", "linear": "IDENTITY", None: "IDENTITY", "elu": "ELU", "selu": "SELU",
         "softplus": "SOFTPLUS", "softsign": "SOFTSIGN", "hard_sigmoid": "HARDSIGMOID", "swish": "SWISH", "gelu": "GELU", "leaky_relu": "LEAKYRELU", "relu6": "RELU6"}
@@ -42,6 +46,20 @@ def _act(cfg):
 
 def _pair(v):
     return [int(v), int(v)] if isinstance(v, int) else [int(x) for x in v]
+
+
+def _triple(v):
+    return [int(v)] * 3 if isinstance(v, int) else [int(x) for x in v]
+
+
+def _sides(v, n):
+    """Keras padding / cropping argument -> flat [before, after] * n."""
+    if isinstance(v, int):
+        return [int(v)] * (2 * n)
+    out = []
+    for e in v:
+        out += [int(e), int(e)] if isinstance(e, int) else [int(e[0]), int(e[1])]
+    return out
 
 
 def _mode(cfg):
@@ -87,8 +105,16 @@ def _map_layer(cls, cfg, is_last, loss):
         return nn.GlobalPoolingLayer("AVG" if "Average" in cls else "MAX", layerName=name), "layer"
     if cls == "Flatten":
         return None, "flatten"
-    if cls in ("Dropout", "SpatialDropout2D", "SpatialDropout1D", "GaussianDropout", "AlphaDropout"):
+    if cls == "Dropout":
         return nn.DropoutLayer(1.0 - float(cfg.get("rate", 0.5)), layerName=name), "layer"        # DL4J stores the retain probability
+    if cls in ("SpatialDropout1D", "SpatialDropout2D", "SpatialDropout3D"):
+        return nn.DropoutLayer(nn.SpatialDropout(1.0 - float(cfg.get("rate", 0.5))), layerName=name), "layer"
+    if cls == "AlphaDropout":
+        return nn.DropoutLayer(nn.AlphaDropout(1.0 - float(cfg.get("rate", 0.5))), layerName=name), "layer"
+    if cls == "GaussianDropout":
+        return nn.DropoutLayer(nn.GaussianDropout(float(cfg.get("rate", 0.5))), layerName=name), "layer"
+    if cls == "GaussianNoise":
+        return nn.DropoutLayer(nn.GaussianNoise(float(cfg.get("stddev", 0.1))), layerName=name), "layer"
     if cls == "Activation":
         return nn.ActivationLayer(_act(cfg), layerName=name), "layer"
     if cls == "LeakyReLU":
@@ -117,6 +143,94 @@ def _map_layer(cls, cfg, is_last, loss):
         return nn.Cropping2D(*[int(v) for v in p], layerName=name), "layer"
     if cls == "UpSampling2D":
         return nn.Upsampling2D(_pair(cfg.get("size", 2)), layerName=name), "layer"
+    if cls in ("Conv3D", "Convolution3D"):
+        return nn.Convolution3D(kernelSize=_triple(cfg["kernel_size"]), stride=_triple(cfg.get("strides", 1)), nOut=cfg["filters"], activation=_act(cfg),
+                                convolutionMode=_mode(cfg), dilation=_triple(cfg.get("dilation_rate", 1)), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls in ("Conv3DTranspose", "Deconvolution3D"):
+        return nn.Deconvolution3D(kernelSize=_triple(cfg["kernel_size"]), stride=_triple(cfg.get("strides", 1)), nOut=cfg["filters"], activation=_act(cfg),
+                                  convolutionMode=_mode(cfg), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls in ("MaxPooling3D", "AveragePooling3D"):
+        ps = _triple(cfg.get("pool_size", 2))
+        return nn.Subsampling3DLayer("MAX" if cls.startswith("Max") else "AVG", kernelSize=ps, stride=_triple(cfg.get("strides") or ps), convolutionMode=_mode(cfg),
+                                     layerName=name), "layer"
+    if cls in ("GlobalAveragePooling3D", "GlobalMaxPooling3D"):
+        return nn.GlobalPoolingLayer("AVG" if "Average" in cls else "MAX", layerName=name), "layer"
+    if cls in ("AtrousConvolution2D", "AtrousConv2D"):                                        # Keras 1: the dilation is called atrous_rate
+        return nn.ConvolutionLayer([cfg["nb_row"], cfg["nb_col"]], _pair(cfg.get("subsample", 1)), nOut=cfg["nb_filter"], activation=_act(cfg),
+                                   convolutionMode="Same" if cfg.get("border_mode") == "same" else "Truncate", dilation=_pair(cfg.get("atrous_rate", 1)),
+                                   hasBias=cfg.get("bias", True), layerName=name), "layer"
+    if cls == "ZeroPadding1D":
+        p = cfg.get("padding", 1)
+        return nn.ZeroPadding1DLayer(*([int(p)] * 2 if isinstance(p, int) else [int(v) for v in p]), layerName=name), "layer"
+    if cls == "ZeroPadding3D":
+        return nn.ZeroPadding3DLayer(*_sides(cfg.get("padding", 1), 3), layerName=name), "layer"
+    if cls == "Cropping1D":
+        p = cfg.get("cropping", 1)
+        return nn.Cropping1D(*([int(p)] * 2 if isinstance(p, int) else [int(v) for v in p]), layerName=name), "layer"
+    if cls == "Cropping3D":
+        return nn.Cropping3D(*_sides(cfg.get("cropping", 1), 3), layerName=name), "layer"
+    if cls == "UpSampling1D":
+        sz = cfg.get("size", 2)
+        return nn.Upsampling1D(int(sz[0] if isinstance(sz, (list, tuple)) else sz), layerName=name), "layer"
+    if cls == "UpSampling3D":
+        return nn.Upsampling3D(_triple(cfg.get("size", 2)), layerName=name), "layer"
+    if cls == "SpaceToDepth":
+        return nn.SpaceToDepthLayer(int(cfg.get("block_size", 2)), layerName=name), "layer"
+    if cls in ("LRN", "LRN2D"):
+        return nn.LocalResponseNormalization(n=float(cfg.get("n", 5)), k=float(cfg.get("k", 2)), alpha=float(cfg.get("alpha", 1e-4)), beta=float(cfg.get("beta", 0.75)),
+                                             layerName=name), "layer"
+    if cls == "PoolHelper":
+        from ..nn.conf.graphconf import PoolHelperVertex
+        return PoolHelperVertex(), "vertex"
+    if cls == "PReLU":
+        shared = cfg.get("shared_axes")
+        return nn.PReLULayer(layerName=name, sharedAxesChannelsLast=[int(a) for a in shared] if shared else None), "layer"
+    if cls == "ELU":
+        return nn.ActivationLayer(nn.activations.ActivationELU(alpha=float(cfg.get("alpha", 1.0))), layerName=name), "layer"
+    if cls == "ThresholdedReLU":
+        return nn.ActivationLayer(nn.activations.ActivationThresholdedReLU(theta=float(cfg.get("theta", 1.0))), layerName=name), "layer"
+    if cls == "RepeatVector":
+        return nn.RepeatVector(int(cfg["n"]), layerName=name), "layer"
+    if cls == "Reshape":
+        return ReshapePreprocessor(cfg["target_shape"]), "preprocessor"
+    if cls == "Permute":
+        return PermutePreprocessor(cfg["dims"]), "preprocessor"
+    if cls == "Masking":
+        return float(cfg.get("mask_value", 0.0)), "masking"
+    if cls == "Bidirectional":
+        inner = cfg["layer"]
+        icfg = dict(inner["config"])
+        seq = icfg.get("return_sequences", False)
+        icfg["return_sequences"] = True
+        l, _ = _map_layer(inner["class_name"], icfg, False, None)
+        mode = {"concat": "CONCAT", "sum": "ADD", "mul": "MUL", "ave": "AVERAGE"}.get(cfg.get("merge_mode", "concat"))
+        if mode is None:
+            raise UnsupportedKerasConfigurationException(f"Unsupported Bidirectional merge mode {cfg.get('merge_mode')}")
+        b = nn.Bidirectional(mode, l, layerName=name)
+        return (b if seq else nn.LastTimeStep(b)), "layer"
+    if cls == "TimeDistributed":
+        inner = cfg["layer"]
+        l, what = _map_layer(inner["class_name"], dict(inner["config"], name=name), is_last, loss)
+        if what != "layer":
+            raise UnsupportedKerasConfigurationException(f"TimeDistributed around {inner['class_name']}")
+        if type(l).__name__ == "OutputLayer":                                             # a per-step output layer is the recurrent output layer
+            return nn.RnnOutputLayer(loss, nOut=l.nOut, activation=_act(inner["config"]), hasBias=l.hasBias, layerName=name), "layer"
+        return nn.TimeDistributed(l, layerName=name), "layer"
+    if cls == "LocallyConnected2D":
+        return nn.LocallyConnected2D(nOut=cfg["filters"], kernel=_pair(cfg["kernel_size"]), stride=_pair(cfg.get("strides", 1)), activation=_act(cfg),
+                                     convolutionMode=_mode(cfg), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls == "LocallyConnected1D":
+        k = cfg["kernel_size"]
+        st = cfg.get("strides", 1)
+        return nn.LocallyConnected1D(nOut=cfg["filters"], kernel=int(k[0] if isinstance(k, (list, tuple)) else k), stride=int(st[0] if isinstance(st, (list, tuple)) else st),
+                                     activation=_act(cfg), convolutionMode=_mode(cfg), hasBias=cfg.get("use_bias", True), layerName=name), "layer"
+    if cls == "Lambda":
+        if name not in _LAMBDA_LAYERS:
+            raise UnsupportedKerasConfigurationException(f"No SameDiff Lambda layer found for Lambda layer {name}. You can register a SameDiff Lambda layer using "
+                                                         f"KerasLayer.registerLambdaLayer(lambdaLayerName, sameDiffLambdaLayer)")
+        return _LAMBDA_LAYERS[name], "layer"
+    if cls in _CUSTOM_LAYERS:
+        return _CUSTOM_LAYERS[cls](cfg), "layer"
     if cls == "Add":
         return ElementWiseVertex("Add"), "vertex"
     if cls == "Multiply":
@@ -134,6 +248,8 @@ def _map_layer(cls, cfg, is_last, loss):
 
 def _input_type(shape):
     shape = [s for s in shape[1:]]
+    if len(shape) == 4:
+        return nn.InputType.convolutional3D(shape[0], shape[1], shape[2], shape[3]), "cnn3d"   # NDHWC -> d, h, w, c
     if len(shape) == 3:
         return nn.InputType.convolutional(shape[0], shape[1], shape[2]), "cnn"           # NHWC -> h, w, c
     if len(shape) == 2:
@@ -145,13 +261,57 @@ def _convert_weights(layer, arrays, flatten_from=None):
     """Keras arrays -> {param name: tensor} for a DL4J layer."""
     t = [torch.from_numpy(np.asarray(a, dtype=np.float32)) for a in arrays]
     cls = type(layer).__name__
-    if cls == "LastTimeStep":
+    if cls in ("LastTimeStep", "MaskZeroLayer", "TimeDistributed"):
         return _convert_weights(layer.underlying, arrays)
+    if cls == "Bidirectional":
+        half = len(arrays) // 2                                                        # forward copy's arrays, then the backward copy's
+        out = {"f" + k: v for k, v in _convert_weights(layer.fwd, arrays[:half]).items()}
+        out.update({"b" + k: v for k, v in _convert_weights(layer.bwd, arrays[half:]).items()})
+        return out
+    if cls == "RnnOutputLayer":
+        out = {"W": t[0]}
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "Convolution3D":
+        out = {"W": t[0].permute(4, 3, 0, 1, 2)}                                       # DHWIO -> OIDHW
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "Deconvolution3D":
+        out = {"W": t[0].permute(4, 3, 0, 1, 2)}                                       # [kd, kh, kw, out, in] -> [in, out, kd, kh, kw]
+        if len(t) > 1:
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "PReLULayer":
+        a = t[0]
+        return {"W": a.permute(a.dim() - 1, *range(a.dim() - 1)) if a.dim() > 1 else a}   # channels last -> channels first
+    if cls == "LocallyConnected2D":
+        kh, kw = layer.kernel
+        W = t[0]                                                                       # [positions, kh*kw*in, out], features in (kh, kw, in) order
+        W = W.reshape(W.shape[0], kh, kw, -1, W.shape[-1]).permute(0, 3, 1, 2, 4).reshape(W.shape[0], -1, W.shape[-1])
+        out = {"W": W}
+        if len(t) > 1:
+            if t[1].numel() != layer.nOut:
+                raise UnsupportedKerasConfigurationException("LocallyConnected2D with one bias per output position (the layer here shares the bias over positions)")
+            out["b"] = t[1].reshape(1, -1)
+        return out
+    if cls == "LocallyConnected1D":
+        k = layer.kernel
+        W = t[0]                                                                       # [steps, k*in, out], features in (k, in) order
+        W = W.reshape(W.shape[0], k, -1, W.shape[-1]).permute(0, 2, 1, 3).reshape(W.shape[0], -1, W.shape[-1])
+        out = {"W": W}
+        if len(t) > 1:
+            if t[1].numel() != layer.nOut:
+                raise UnsupportedKerasConfigurationException("LocallyConnected1D with one bias per output step (the layer here shares the bias over steps)")
+            out["b"] = t[1].reshape(1, -1)
+        return out
     if cls in ("DenseLayer", "OutputLayer"):
         W = t[0]
         if flatten_from is not None:                                                   # rows are in (h, w, c) order; DL4J flattens (c, h, w)
-            h, w, c = flatten_from
-            W = W.reshape(h, w, c, -1).permute(2, 0, 1, 3).reshape(h * w * c, -1)
+            dims = list(flatten_from)                                                  # spatial extents ..., channels
+            n = len(dims)
+            W = W.reshape(*dims, -1).permute(n - 1, *range(n - 1), n).reshape(int(np.prod(dims)), -1)
         out = {"W": W}
         if len(t) > 1:
             out["b"] = t[1].reshape(1, -1)
@@ -306,17 +466,47 @@ class KerasModelImport:
         lb = nn.NeuralNetConfiguration.Builder().list()
         mapped = []                      # (dl4j index, keras name, layer, flatten_from)
         idx, cur, pending_flatten = 0, it, None
+        pending_pp, pending_mask = [], None
         real = [lc for lc in layers_cfg if lc["class_name"] != "InputLayer"]
         for k, lc in enumerate(real):
             layer, what = _map_layer(lc["class_name"], lc["config"], k == len(real) - 1, loss)
             if what == "flatten":
                 if cur.kind == nn.InputType.CNN:
                     pending_flatten = (cur.height, cur.width, cur.channels)
+                elif cur.kind == nn.InputType.CNN3D:
+                    pending_flatten = (cur.depth, cur.height, cur.width, cur.channels)
+                elif cur.kind == nn.InputType.RNN and cur.timeSeriesLength and cur.timeSeriesLength > 0:
+                    pending_flatten = (cur.timeSeriesLength, cur.size)
                 continue
             if what in ("input", "skip"):
                 continue
             if what == "vertex":
                 raise InvalidKerasConfigurationException("merge layers need the functional API: use importKerasModelAndWeights")
+            if what == "masking":
+                pending_mask = layer
+                continue
+            if what == "preprocessor":
+                pending_pp.append(layer)
+                cur = layer.output_type(cur)
+                if k == len(real) - 1:                                                 # nothing follows to carry it: an identity layer does
+                    layer, what = nn.ActivationLayer("IDENTITY", layerName=lc["config"].get("name")), "layer"
+                else:
+                    continue
+            if pending_mask is not None and (getattr(layer, "IS_RECURRENT", False) or type(layer).__name__ == "LastTimeStep"):
+                layer = nn.MaskZeroLayer(underlying=layer, maskingValue=pending_mask, layerName=lc["config"].get("name"))
+                pending_mask = None
+            if pending_pp:
+                auto = layer.preprocessor_for(cur)
+                lb.inputPreProcessor(idx, ComposableInputPreProcessor(pending_pp + ([auto] if auto is not None else [])) if (auto is not None or len(pending_pp) > 1) else pending_pp[0])
+                if auto is not None:
+                    cur = auto.output_type(cur)
+                pending_pp = []
+                lb.layer(idx, layer)
+                mapped.append((idx, lc["config"]["name"], layer, None))
+                layer.setNIn(cur, True)
+                cur = layer.output_type(cur)
+                idx += 1
+                continue
             lb.layer(idx, layer)
             mapped.append((idx, lc["config"]["name"], layer, pending_flatten if type(layer).__name__ in ("DenseLayer", "OutputLayer") else None))
             if pending_flatten is not None and type(layer).__name__ in ("DenseLayer", "OutputLayer"):
@@ -335,7 +525,7 @@ class KerasModelImport:
         for i, kname, layer, ff in mapped:
             if kname in w and w[kname]:
                 _set_params(net, str(i), net.conf.layers()[i], w[kname], ff)
-        net.kerasInputLayout = "NHWC" if kind == "cnn" else ("NWC" if kind == "rnn" else "NC")
+        net.kerasInputLayout = {"cnn": "NHWC", "cnn3d": "NDHWC", "rnn": "NWC"}.get(kind, "NC")
         return net
 
     @staticmethod
@@ -356,7 +546,7 @@ class KerasModelImport:
             sh = by_name[n]["config"].get("batch_input_shape") or by_name[n]["config"].get("batch_shape")
             its.append(_input_type(sh)[0])
         gb.setInputTypes(*its)
-        alias = {}
+        alias, mask_of = {}, {}
         for lc in c["layers"]:
             name = lc.get("name") or lc["config"]["name"]
             if lc["class_name"] == "InputLayer":
@@ -382,6 +572,17 @@ class KerasModelImport:
                 alias[name] = srcs[0]
                 flatten_of[name] = srcs[0]
                 continue
+            if what == "masking":
+                alias[name] = srcs[0]
+                mask_of[name] = layer
+                continue
+            if what == "preprocessor":
+                gb.addVertex(name, PreprocessorVertex(layer), *srcs)
+                continue
+            raw = [s[0] for s in inbound[0]] if inbound and not isinstance(inbound[0], dict) else []
+            masked = [mask_of[r] for r in raw if r in mask_of]
+            if masked and what == "layer" and (getattr(layer, "IS_RECURRENT", False) or type(layer).__name__ == "LastTimeStep"):
+                layer = nn.MaskZeroLayer(underlying=layer, maskingValue=masked[0], layerName=name)
             if what == "vertex":
                 gb.addVertex(name, layer, *srcs)
             else:
@@ -401,8 +602,24 @@ class KerasModelImport:
                 src_t = types.get(srcs[0]) if srcs else None
                 if type(layer).__name__ in ("DenseLayer", "OutputLayer") and src_t is not None and src_t.kind == nn.InputType.CNN:
                     ff = (src_t.height, src_t.width, src_t.channels)
+                elif type(layer).__name__ in ("DenseLayer", "OutputLayer") and src_t is not None and src_t.kind == nn.InputType.CNN3D:
+                    ff = (src_t.depth, src_t.height, src_t.width, src_t.channels)
                 _set_params(net, name, conf.vertices[name].layer, w[name], ff)
         return net
+
+    @staticmethod
+    def registerLambdaLayer(lambdaLayerName, sameDiffLambdaLayer):
+        """``KerasLayer.registerLambdaLayer``: the layer that stands for the Keras ``Lambda`` layer of that name."""
+        _LAMBDA_LAYERS[lambdaLayerName] = sameDiffLambdaLayer
+
+    @staticmethod
+    def clearLambdaLayers():
+        _LAMBDA_LAYERS.clear()
+
+    @staticmethod
+    def registerCustomLayer(layerName, factory):
+        """``KerasLayer.registerCustomLayer``: ``factory(keras config dict) -> layer`` for a Keras class this importer does not know."""
+        _CUSTOM_LAYERS[layerName] = factory
 
     @staticmethod
     def importKerasModelConfiguration(model_json):

@@ -151,7 +151,80 @@ class ComposableInputPreProcessor(InputPreProcessor):
         return {"@class": _P + self.JAVA, "inputPreProcessors": [p.to_json() for p in self.inputPreProcessors]}
 
 
-PREPROCESSORS = {c.JAVA: c for c in (CnnToFeedForwardPreProcessor, FeedForwardToCnnPreProcessor,
+def _to_channels_last(x):
+    return x.permute(0, *range(2, x.dim()), 1) if x.dim() > 2 else x
+
+
+def _to_channels_first(x):
+    return x.permute(0, x.dim() - 1, *range(1, x.dim() - 1)) if x.dim() > 2 else x
+
+
+def _type_of_channels_last(shape):
+    """InputType of an activation whose Keras (channels-last, no batch axis) shape is ``shape``."""
+    s = [int(v) for v in shape]
+    if len(s) == 1:
+        return InputType.feedForward(s[0])
+    if len(s) == 2:
+        return InputType.recurrent(s[1], s[0])
+    if len(s) == 3:
+        return InputType.convolutional(s[0], s[1], s[2])
+    if len(s) == 4:
+        return InputType.convolutional3D(s[0], s[1], s[2], s[3])
+    raise ValueError(f"no input type for a rank-{len(s) + 1} activation")
+
+
+def _channels_last_shape(it):
+    if it.kind == InputType.CNN:
+        return [it.height, it.width, it.channels]
+    if it.kind == InputType.RNN:
+        return [it.timeSeriesLength, it.size]
+    if it.kind == InputType.CNN3D:
+        return [it.depth, it.height, it.width, it.channels]
+    return [it.size]
+
+
+class ReshapePreprocessor(InputPreProcessor):
+    """Keras ``Reshape`` (``deeplearning4j-modelimport/.../keras/preprocessors/ReshapePreprocessor.java``).
+    ``targetShape`` is the Keras one: channels last, without the batch axis, at most one ``-1``.  The network
+    keeps activations channels first, so the activation is put into the Keras order, reshaped, and put back."""
+    JAVA = "ReshapePreprocessor"; FIELDS = ("targetShape",)
+    def __init__(self, targetShape):
+        self.targetShape = [int(v) for v in targetShape]
+    def preProcess(self, x, minibatch=None, ctx=None):
+        y = _to_channels_last(x).reshape([x.shape[0]] + self.targetShape)
+        return _to_channels_first(y).contiguous()
+    def output_type(self, it):
+        src = _channels_last_shape(it)
+        tgt = list(self.targetShape)
+        if -1 in tgt:
+            total, known = 1, 1
+            for v in src:
+                total *= v
+            for v in tgt:
+                known *= v if v != -1 else 1
+            tgt[tgt.index(-1)] = total // known
+        return _type_of_channels_last(tgt)
+    def to_json(self):
+        return {"@class": "org.deeplearning4j.nn.modelimport.keras.preprocessors." + self.JAVA, "targetShape": self.targetShape}
+
+
+class PermutePreprocessor(InputPreProcessor):
+    """Keras ``Permute`` (``.../keras/preprocessors/PermutePreprocessor.java``): ``dims`` are the 1-based Keras axes
+    (channels last) in their new order."""
+    JAVA = "PermutePreprocessor"; FIELDS = ("permutationIndices",)
+    def __init__(self, permutationIndices):
+        self.permutationIndices = [int(v) for v in permutationIndices]
+    def preProcess(self, x, minibatch=None, ctx=None):
+        y = _to_channels_last(x).permute(0, *self.permutationIndices)
+        return _to_channels_first(y).contiguous()
+    def output_type(self, it):
+        src = _channels_last_shape(it)
+        return _type_of_channels_last([src[i - 1] for i in self.permutationIndices])
+    def to_json(self):
+        return {"@class": "org.deeplearning4j.nn.modelimport.keras.preprocessors." + self.JAVA, "permutationIndices": self.permutationIndices}
+
+
+PREPROCESSORS = {c.JAVA: c for c in (ReshapePreprocessor, PermutePreprocessor, CnnToFeedForwardPreProcessor, FeedForwardToCnnPreProcessor,
                                      Cnn3DToFeedForwardPreProcessor, FeedForwardToCnn3DPreProcessor,
                                      RnnToFeedForwardPreProcessor, FeedForwardToRnnPreProcessor,
                                      CnnToRnnPreProcessor, RnnToCnnPreProcessor, ComposableInputPreProcessor)}

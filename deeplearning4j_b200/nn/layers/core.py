@@ -367,11 +367,16 @@ class EmbeddingSequenceLayer(FeedForwardLayer):
 
 class PReLULayer(BaseLayer):
     JAVA_CLASS = _L + "PReLULayer"
-    DEFAULTS = {"inputShape": None, "sharedAxes": None}
+    DEFAULTS = {"inputShape": None, "sharedAxes": None, "sharedAxesChannelsLast": None}
+    JSON_SKIP = ("sharedAxesChannelsLast",)
 
     def setNIn(self, input_type, override):
         if self.inputShape is None:
             self.inputShape = input_type.getShape()
+        if self.sharedAxesChannelsLast and self.sharedAxes is None:
+            # axes given for a channels-last activation (the Keras convention): the last one is the channel axis, which sits first here
+            n = len(self.inputShape)
+            self.sharedAxes = sorted(1 if a == n else a + 1 for a in self.sharedAxesChannelsLast)
 
     def _alpha_shape(self):
         shp = list(self.inputShape)
