@@ -231,6 +231,13 @@ def _map_layer(cls, cfg, is_last, loss):
         return _LAMBDA_LAYERS[name], "layer"
     if cls in _CUSTOM_LAYERS:
         return _CUSTOM_LAYERS[cls](cfg), "layer"
+    if cls == "Attention":
+        if cfg.get("score_mode", "dot") != "dot":
+            raise InvalidKerasConfigurationException(f"Invalid score mode {cfg.get('score_mode')}")
+        from ..nn.conf.graphconf import DotProductAttentionVertex
+        v = DotProductAttentionVertex(scaleFactor=1.0, dropoutProbability=float(cfg.get("dropout", 0.0)), useCausalMask=bool(cfg.get("causal", False)))
+        v._keras_use_scale = bool(cfg.get("use_scale", False))          # the learned scalar arrives with the weights
+        return v, "attention"
     if cls == "Add":
         return ElementWiseVertex("Add"), "vertex"
     if cls == "Multiply":
@@ -480,7 +487,7 @@ class KerasModelImport:
                 continue
             if what in ("input", "skip"):
                 continue
-            if what == "vertex":
+            if what in ("vertex", "attention"):
                 raise InvalidKerasConfigurationException("merge layers need the functional API: use importKerasModelAndWeights")
             if what == "masking":
                 pending_mask = layer
@@ -546,7 +553,7 @@ class KerasModelImport:
             sh = by_name[n]["config"].get("batch_input_shape") or by_name[n]["config"].get("batch_shape")
             its.append(_input_type(sh)[0])
         gb.setInputTypes(*its)
-        alias, mask_of = {}, {}
+        alias, mask_of, scaled = {}, {}, []
         for lc in c["layers"]:
             name = lc.get("name") or lc["config"]["name"]
             if lc["class_name"] == "InputLayer":
@@ -583,6 +590,12 @@ class KerasModelImport:
             masked = [mask_of[r] for r in raw if r in mask_of]
             if masked and what == "layer" and (getattr(layer, "IS_RECURRENT", False) or type(layer).__name__ == "LastTimeStep"):
                 layer = nn.MaskZeroLayer(underlying=layer, maskingValue=masked[0], layerName=name)
+            if what == "attention":
+                if len(srcs) == 3:
+                    srcs = [srcs[0], srcs[2], srcs[1]]                                 # Keras passes [query, value, key]
+                gb.addVertex(name, layer, *srcs)
+                scaled.append((name, layer))
+                continue
             if what == "vertex":
                 gb.addVertex(name, layer, *srcs)
             else:
@@ -596,6 +609,9 @@ class KerasModelImport:
         if weights is None and not (isinstance(model_json, str) and model_json.lstrip().startswith("{")) and _is_hdf5(model_json):
             weights = model_json                      # full-model file: the weights sit beside the configuration
         w = _load_weights(weights)
+        for name, vertex in scaled:
+            if vertex._keras_use_scale and w.get(name):
+                vertex.scaleFactor = float(np.asarray(w[name][0]).reshape(-1)[0])
         for name, layer, srcs in mapped:
             if name in w and w[name]:
                 ff = None

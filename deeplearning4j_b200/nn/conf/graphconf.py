@@ -257,6 +257,12 @@ class DotProductAttentionVertex(GraphVertex):
         q, k, v = (inputs + inputs[-1:] * 3)[:3]
         qq, kk, vv = (t.permute(0, 2, 1).unsqueeze(1) for t in (q, k, v))
         m = masks[1] if masks and len(masks) > 1 else None
+        if self.useCausalMask:                       # query step t sees key steps <= t; folded with the key mask into one additive mask
+            import torch
+            add = torch.full((qq.shape[2], kk.shape[2]), float("-inf"), device=qq.device, dtype=torch.float32).triu(1)[None, None]
+            if m is not None:
+                add = add.masked_fill(m[:, None, None, :] == 0, float("-inf"))
+            m = add
         o = nnops.attention(qq, kk, vv, m, self.scaleFactor, self.dropoutProbability, training)
         return o.squeeze(1).permute(0, 2, 1)
     def output_type(self, *its):

@@ -246,3 +246,29 @@ def test_functional_graph_with_reshape_vertex_and_masking():
             h = (x[e].reshape(3, 2)[s] @ W + h @ U + b).tanh()
         ref.append(h @ t(w["out"][0]) + t(w["out"][1]))
     assert torch.allclose(out(net, x), torch.stack(ref), atol=1e-5)
+
+
+def test_attention_layer_becomes_the_dot_product_vertex():
+    def model(causal, three):
+        ins = [["q", 0, 0, {}], ["v", 0, 0, {}]] + ([["k", 0, 0, {}]] if three else [])
+        names = ["q", "v"] + (["k"] if three else [])
+        return json.dumps({"class_name": "Model", "config": {
+            "name": "m", "input_layers": [[n, 0, 0] for n in names], "output_layers": [["att", 0, 0]],
+            "layers": [{"class_name": "InputLayer", "name": n, "config": {"name": n, "batch_input_shape": [None, 4 if n == "q" else 5, 3]}, "inbound_nodes": []} for n in names] +
+                      [{"class_name": "Attention", "name": "att", "config": {"name": "att", "use_scale": True, "causal": causal}, "inbound_nodes": [ins]}]}})
+    q, v, k = torch.randn(2, 4, 3), torch.randn(2, 5, 3), torch.randn(2, 5, 3)
+    cf = lambda a: a.permute(0, 2, 1).contiguous()
+    for causal in (False, True):
+        for three in (False, True):
+            net = KerasModelImport.importKerasModelAndWeights(model(causal, three), {"att": [np.asarray(0.7, dtype="f4")]})
+            kk = k if three else v
+            s = 0.7 * q @ kk.transpose(1, 2)
+            if causal:
+                s = s.masked_fill(torch.ones(4, 5).triu(1) > 0, float("-inf"))
+            ref = s.softmax(-1) @ v
+            got = net.output(*([cf(q), cf(v)] + ([cf(k)] if three else [])))
+            got = got[0] if isinstance(got, (list, tuple)) else got
+            got = torch.as_tensor(np.asarray(got.numpy() if hasattr(got, "numpy") else got))
+            assert torch.allclose(got.permute(0, 2, 1), ref, atol=1e-5), (causal, three)
+    with pytest.raises(Exception, match="score mode"):
+        KerasModelImport.importKerasModelAndWeights(model(False, False).replace('"use_scale": true', '"use_scale": true, "score_mode": "concat"'))
