@@ -4,7 +4,8 @@ from .records import (AlignmentMode, RecordReaderDataSetIterator, SequenceRecord
 from .transform import (AnalyzeLocal, BooleanCondition, CategoricalColumnCondition, ColumnCondition, ColumnType, ConditionFilter,  # noqa: F401
                         ConditionOp, DataAnalysis, DoubleColumnCondition, IntegerColumnCondition, InvalidValueColumnCondition,
                         LocalTransformExecutor, MathFunction, MathOp, NullWritableColumnCondition, ReduceOp, Reducer, Schema,
-                        StringColumnCondition, TransformProcess)
+                        StringColumnCondition, TransformProcess, Distance, OverlappingTimeWindowFunction, SequenceSplitTimeSeparation,
+                        SplitMaxLengthSequence, TimeWindowFunction)
 from .extra import (ArrowConverter, ArrowRecordReader, ArrowRecordWriter, BoxImageTransform, ColorConversionTransform,  # noqa: F401
                     CropImageTransform, DataQualityAnalysis, EqualizeHistTransform, ExcelRecordReader, ExcelRecordWriter,
                     FlipImageTransform, ImageTransform, JDBCRecordReader, Join, JoinType, MultiImageTransform, NativeImageLoader,

@@ -208,6 +208,106 @@ class Reducer:
         def build(self): return Reducer(self.keys, self.defaultOp, self.ops)
 
 
+_TIME_UNIT_MS = {"MILLISECONDS": 1, "SECONDS": 1000, "MINUTES": 60_000, "HOURS": 3_600_000, "DAYS": 86_400_000}
+
+
+def _nd_math():
+    import numpy as np
+    m = {"Add": lambda a, b: a + b, "Subtract": lambda a, b: a - b, "Multiply": lambda a, b: a * b, "Divide": lambda a, b: a / b,
+         "Modulus": lambda a, b: np.fmod(a, b), "ReverseSubtract": lambda a, b: b - a, "ReverseDivide": lambda a, b: b / a,
+         "ScalarMin": np.minimum, "ScalarMax": np.maximum}
+    f = {"ABS": np.abs, "CEIL": np.ceil, "EXP": np.exp, "FLOOR": np.floor, "LOG": np.log, "LOG10": np.log10, "SIGNUM": np.sign, "SIN": np.sin,
+         "COS": np.cos, "TAN": np.tan, "SQRT": np.sqrt, "TANH": np.tanh}
+    return m, f
+
+
+_MATH_ND, _FUNCS_ND = _nd_math()
+
+
+class Distance:
+    COSINE, EUCLIDEAN, MANHATTAN = "COSINE", "EUCLIDEAN", "MANHATTAN"
+
+
+class SplitMaxLengthSequence:
+    """``sequence/split/SplitMaxLengthSequence.java``: pieces of at most ``maxSequenceLength`` steps (of equal length when asked)."""
+    def __init__(self, maxSequenceLength, equalSplits=False): self.maxSequenceLength, self.equalSplits = int(maxSequenceLength), bool(equalSplits)
+    def bind(self, schema): pass
+    def split(self, seq):
+        n = self.maxSequenceLength
+        if len(seq) <= n:
+            return [list(seq)]
+        size = math.ceil(len(seq) / math.ceil(len(seq) / n)) if self.equalSplits else n
+        return [list(seq[k:k + size]) for k in range(0, len(seq), size)]
+    def to_dict(self): return {"@class": "SplitMaxLengthSequence", "maxSequenceLength": self.maxSequenceLength, "equalSplits": self.equalSplits}
+
+
+class SequenceSplitTimeSeparation:
+    """``sequence/split/SequenceSplitTimeSeparation.java``: a new sequence starts where two consecutive time stamps are more than the gap apart."""
+    def __init__(self, timeColumn, timeQuantity, timeUnit="MILLISECONDS"):
+        self.timeColumn, self.timeQuantity, self.timeUnit = timeColumn, int(timeQuantity), str(timeUnit).upper()
+    def bind(self, schema): self.idx = schema.getIndexOfColumn(self.timeColumn)
+    def split(self, seq):
+        gap, out, cur = self.timeQuantity * _TIME_UNIT_MS[self.timeUnit], [], []
+        for row in seq:
+            if cur and unwrap(row[self.idx]) - unwrap(cur[-1][self.idx]) > gap:
+                out.append(cur)
+                cur = []
+            cur.append(list(row))
+        return out + ([cur] if cur else [])
+    def to_dict(self): return {"@class": "SequenceSplitTimeSeparation", "timeColumn": self.timeColumn, "timeQuantity": self.timeQuantity, "timeUnit": self.timeUnit}
+
+
+class TimeWindowFunction:
+    """``sequence/window/TimeWindowFunction.java``: consecutive windows of ``windowSize`` starting at ``offset`` past the epoch; a step falls in the
+    window that holds its time stamp.  Empty windows between the first and the last are left out unless ``excludeEmptyWindows`` is ``False``."""
+    def __init__(self, timeColumn, windowSize, windowSizeUnit="MILLISECONDS", offset=0, offsetUnit="MILLISECONDS", excludeEmptyWindows=True):
+        self.timeColumn, self.windowSize, self.windowSizeUnit = timeColumn, int(windowSize), str(windowSizeUnit).upper()
+        self.offset, self.offsetUnit, self.excludeEmptyWindows = int(offset), str(offsetUnit).upper(), bool(excludeEmptyWindows)
+    def bind(self, schema): self.idx = schema.getIndexOfColumn(self.timeColumn)
+    def _ms(self): return self.windowSize * _TIME_UNIT_MS[self.windowSizeUnit], self.offset * _TIME_UNIT_MS[self.offsetUnit]
+    def applyToSequence(self, seq):
+        if not seq:
+            return []
+        size, off = self._ms()
+        buckets = OrderedDict()
+        for row in seq:
+            buckets.setdefault((unwrap(row[self.idx]) - off) // size, []).append(row)
+        if self.excludeEmptyWindows:
+            return list(buckets.values())
+        lo, hi = min(buckets), max(buckets)
+        return [buckets.get(b, []) for b in range(lo, hi + 1)]
+    def to_dict(self):
+        return {"@class": "TimeWindowFunction", "timeColumn": self.timeColumn, "windowSize": self.windowSize, "windowSizeUnit": self.windowSizeUnit,
+                "offset": self.offset, "offsetUnit": self.offsetUnit, "excludeEmptyWindows": self.excludeEmptyWindows}
+
+
+class OverlappingTimeWindowFunction(TimeWindowFunction):
+    """``sequence/window/OverlappingTimeWindowFunction.java``: windows of ``windowSize`` that start every ``windowSeparation``; a step belongs to
+    every window that covers its time stamp."""
+    def __init__(self, timeColumn, windowSize, windowSizeUnit, windowSeparation, windowSeparationUnit="MILLISECONDS", offset=0, offsetUnit="MILLISECONDS",
+                 excludeEmptyWindows=True):
+        super().__init__(timeColumn, windowSize, windowSizeUnit, offset, offsetUnit, excludeEmptyWindows)
+        self.windowSeparation, self.windowSeparationUnit = int(windowSeparation), str(windowSeparationUnit).upper()
+    def applyToSequence(self, seq):
+        if not seq:
+            return []
+        size, off = self._ms()
+        sep = self.windowSeparation * _TIME_UNIT_MS[self.windowSeparationUnit]
+        times = [unwrap(r[self.idx]) for r in seq]
+        first = (min(times) - off - size) // sep + 1                       # first window whose end lies past the first time stamp
+        last = (max(times) - off) // sep
+        out = []
+        for w in range(first, last + 1):
+            lo = off + w * sep
+            rows = [r for r, t in zip(seq, times) if lo <= t < lo + size]
+            if rows or not self.excludeEmptyWindows:
+                out.append(rows)
+        return out
+    def to_dict(self):
+        return dict(super().to_dict(), **{"@class": "OverlappingTimeWindowFunction", "windowSeparation": self.windowSeparation,
+                                          "windowSeparationUnit": self.windowSeparationUnit})
+
+
 # ----------------------------------------------------------------------------- transform process
 class _Step:
     def __init__(self, kind, **kw): self.kind, self.kw = kind, kw
@@ -263,6 +363,43 @@ class TransformProcess:
         def reduce(self, reducer): return self._s("reduce", reducer=reducer)
         def convertToSequence(self, keyColumn, sortColumn=None): return self._s("toSequence", key=keyColumn, sort=sortColumn)
         def offsetSequence(self, cols, offset, kind="InPlace"): return self._s("offsetSeq", columns=list(cols), offset=offset, mode=kind)
+        def renameColumns(self, oldNames, newNames):
+            for o, n in zip(oldNames, newNames):
+                self.renameColumn(o, n)
+            return self
+        def duplicateColumns(self, columnNames, newNames):
+            for c, n in zip(columnNames, newNames):
+                self.duplicateColumn(c, n)
+            return self
+        def addConstantColumn(self, name, columnType, v): return self._s("addConstant", name=name, type=columnType, value=unwrap(v))
+        def addConstantLongColumn(self, name, v): return self._s("addConstant", name=name, type=ColumnType.Long, value=int(v))
+        def floatMathOp(self, col, op, v): return self._s("math", column=col, op=op, value=v, integer=False)
+        def floatMathFunction(self, col, fn): return self._s("mathFn", column=col, fn=fn)
+        def floatColumnsMathOp(self, newName, op, *cols): return self._s("columnsMath", newName=newName, op=op, columns=list(cols), integer=False)
+        def longColumnsMathOp(self, newName, op, *cols): return self._s("columnsMath", newName=newName, op=op, columns=list(cols), integer=True)
+        def timeMathOp(self, col, op, timeQuantity, timeUnit="MILLISECONDS"):
+            """``TimeMathOpTransform``: Add / Subtract / ScalarMin / ScalarMax on an epoch-millisecond column, the scalar given in ``timeUnit``."""
+            if op not in ("Add", "Subtract", "ScalarMin", "ScalarMax"):
+                raise ValueError(f"Invalid MathOp for a time column: {op}")
+            return self._s("math", column=col, op=op, value=int(timeQuantity) * _TIME_UNIT_MS[str(timeUnit).upper()], integer=True)
+        def conditionalReplaceValueTransformWithDefault(self, col, yesVal, noVal, cond):
+            return self._s("condReplaceDefault", column=col, yes=unwrap(yesVal), no=unwrap(noVal), condition=cond)
+        def firstDigitTransform(self, inputColumn, outputColumn, mode="INCLUDE_OTHER_CATEGORY"):
+            return self._s("firstDigit", column=inputColumn, output=outputColumn, mode=mode)
+        def ndArrayScalarOpTransform(self, col, op, v): return self._s("ndScalar", column=col, op=op, value=float(v))
+        def ndArrayColumnsMathOpTransform(self, newName, op, *cols): return self._s("ndColumnsMath", newName=newName, op=op, columns=list(cols))
+        def ndArrayMathFunctionTransform(self, col, fn): return self._s("ndMathFn", column=col, fn=fn)
+        def ndArrayDistanceTransform(self, newName, distance, firstCol, secondCol):
+            return self._s("ndDistance", newName=newName, distance=str(distance).upper(), first=firstCol, second=secondCol)
+        def calculateSortedRank(self, newColumnName, sortOnColumn, comparator=None, ascending=True):
+            """``CalculateSortedRank``: appends a Long column with each record's rank (0 = first) after sorting all records on a column."""
+            return self._s("sortedRank", newName=newColumnName, column=sortOnColumn, ascending=bool(ascending))
+        def trimSequence(self, numStepsToTrim, trimFromStart=True): return self._s("trimSeq", n=int(numStepsToTrim), fromStart=bool(trimFromStart))
+        def trimSequenceToLength(self, maxLength): return self._s("trimSeqToLength", length=int(maxLength), pad=None)
+        def trimOrPadSequenceToLength(self, length, pad): return self._s("trimSeqToLength", length=int(length), pad=[unwrap(v) for v in pad])
+        def splitSequence(self, split): return self._s("splitSeq", split=split)
+        def reduceSequenceByWindow(self, reducer, windowFunction): return self._s("windowReduce", reducer=reducer, window=windowFunction)
+        def convertFromSequence(self): return self._s("fromSequence")
         def transform(self, fn): return self._s("custom", fn=fn)
         def build(self): return TransformProcess(self.schema, self.steps)
 
@@ -427,6 +564,98 @@ class TransformProcess:
             return ("GLOBAL", red, keys, [c.name for c in cols]), Schema(new)
         if k in ("toSequence", "offsetSeq"):
             return ("GLOBAL", k, kw, [c.name for c in cols]), sch
+        if k == "condReplaceDefault":
+            i, yes, no, c = ix(kw["column"]), kw["yes"], kw["no"], kw["condition"]
+            c.bind(sch)
+            return (lambda r: r[:i] + [yes if c.condition(r) else no] + r[i + 1:]), sch
+        if k == "firstDigit":
+            i, outn, mode = ix(kw["column"]), kw["output"], kw["mode"]
+            states = [str(d) for d in range(10)] + (["Other"] if mode == "INCLUDE_OTHER_CATEGORY" else [])
+            def digit(v):
+                t = str(unwrap(v))
+                t = t[1:] if t.startswith("-") and len(t) > 1 else t
+                if t and t[0].isdigit():
+                    return t[0]
+                if mode == "INCLUDE_OTHER_CATEGORY":
+                    return "Other"
+                raise ValueError(f"FirstDigitTransform in mode EXCEPTION_ON_INVALID met the non-numerical entry {unwrap(v)!r}")
+            meta = ColumnMeta(outn, ColumnType.Categorical, stateNames=states)
+            if outn == kw["column"]:
+                cols[i] = meta
+                return (lambda r: r[:i] + [digit(r[i])] + r[i + 1:]), Schema(cols)
+            return (lambda r: r[:i + 1] + [digit(r[i])] + r[i + 1:]), Schema(cols[:i + 1] + [meta] + cols[i + 1:])
+        if k in ("ndScalar", "ndMathFn", "ndColumnsMath", "ndDistance"):
+            import numpy as np
+            A = lambda v: np.asarray(unwrap(v), dtype=np.float64)
+            if k == "ndScalar":
+                i, op, b = ix(kw["column"]), _MATH_ND[kw["op"]], kw["value"]
+                return (lambda r: r[:i] + [op(A(r[i]), b)] + r[i + 1:]), sch
+            if k == "ndMathFn":
+                i, fn = ix(kw["column"]), _FUNCS_ND[kw["fn"]]
+                return (lambda r: r[:i] + [fn(A(r[i]))] + r[i + 1:]), sch
+            if k == "ndColumnsMath":
+                if kw["op"] not in ("Add", "Subtract", "Multiply", "Divide"):
+                    raise ValueError(f"Invalid MathOp for NDArray columns: {kw['op']}")
+                idx, op = [ix(c) for c in kw["columns"]], _MATH_ND[kw["op"]]
+                def f(r):
+                    v = A(r[idx[0]])
+                    for j in idx[1:]:
+                        v = op(v, A(r[j]))
+                    return r + [v]
+                return f, Schema(cols + [ColumnMeta(kw["newName"], ColumnType.NDArray, **cols[idx[0]].extra)])
+            a, b, d = ix(kw["first"]), ix(kw["second"]), kw["distance"]
+            def dist(x, y):
+                if d == "COSINE":
+                    return float(1.0 - (x * y).sum() / (np.linalg.norm(x) * np.linalg.norm(y)))
+                if d == "EUCLIDEAN":
+                    return float(np.linalg.norm(x - y))
+                if d == "MANHATTAN":
+                    return float(np.abs(x - y).sum())
+                raise ValueError(f"unknown distance {d}")
+            return (lambda r: r + [dist(A(r[a]).ravel(), A(r[b]).ravel())]), Schema(cols + [ColumnMeta(kw["newName"], ColumnType.Double)])
+        if k == "sortedRank":
+            i, asc = ix(kw["column"]), kw["ascending"]
+            def rank(rows):
+                order = sorted(range(len(rows)), key=lambda j: unwrap(rows[j][i]), reverse=not asc)
+                pos = {j: n for n, j in enumerate(order)}
+                return [list(r) + [pos[j]] for j, r in enumerate(rows)]
+            return ("GLOBAL", "rowsFn", rank, None), Schema(cols + [ColumnMeta(kw["newName"], ColumnType.Long)])
+        if k == "trimSeq":
+            n, start = kw["n"], kw["fromStart"]
+            return ("GLOBAL", "rowsFn", lambda seqs: [s[n:] if start else s[:max(len(s) - n, 0)] for s in seqs], None), sch
+        if k == "trimSeqToLength":
+            n, pad = kw["length"], kw["pad"]
+            if pad is not None and len(pad) != len(cols):
+                raise ValueError(f"the padding record has {len(pad)} values for {len(cols)} columns")
+            return ("GLOBAL", "rowsFn", lambda seqs: [list(s[:n]) + ([list(pad) for _ in range(n - len(s))] if pad is not None else []) for s in seqs], None), sch
+        if k == "splitSeq":
+            sp = kw["split"]
+            sp.bind(sch)
+            return ("GLOBAL", "rowsFn", lambda seqs: [piece for s in seqs for piece in sp.split(s)], None), sch
+        if k == "fromSequence":
+            return ("GLOBAL", "rowsFn", lambda seqs: [list(r) for s in seqs for r in s], None), sch
+        if k == "windowReduce":
+            red, win = kw["reducer"], kw["window"]
+            win.bind(sch)
+            names = [c.name for c in cols]
+            new = []
+            for c in cols:
+                op = red.ops.get(c.name, red.defaultOp)
+                t = ColumnType.Long if op in ("Count", "CountUnique") else (ColumnType.Double if op in ("Mean", "Stdev") else c.type)
+                new.append(ColumnMeta(f"{op.lower()}({c.name})", t))
+            def f(seqs):
+                out = []
+                for s in seqs:
+                    steps = []
+                    for w in win.applyToSequence(s):
+                        ops = [red.ops.get(n, red.defaultOp) for n in names]
+                        if w:
+                            steps.append([_reduce(op, [unwrap(r[i]) for r in w]) for i, op in enumerate(ops)])
+                        else:                                   # an empty window kept on request: counts are 0, everything else is missing
+                            steps.append([0 if op in ("Count", "CountUnique") else None for op in ops])
+                    out.append(steps)
+                return out
+            return ("GLOBAL", "rowsFn", f, None), Schema(new)
         raise ValueError(f"unknown transform step {k}")
 
     # -- execution
@@ -470,6 +699,8 @@ class TransformProcess:
                     for g in groups.values():
                         g.sort(key=lambda r: unwrap(r[si]))
                 rows = list(groups.values())
+            elif isinstance(fn, tuple) and fn[1] == "rowsFn":
+                rows = fn[2](rows)
             elif isinstance(fn, tuple) and fn[1] == "offsetSeq":
                 kw, names = fn[2], fn[3]
                 idx, off = [names.index(c) for c in kw["columns"]], kw["offset"]
@@ -496,7 +727,7 @@ class TransformProcess:
             if s.kind == "custom":
                 raise ValueError("custom function steps cannot be serialised")
             d = s.to_dict()
-            if s.kind == "reduce":
+            if s.kind in ("reduce", "windowReduce"):
                 r = s.kw["reducer"]
                 d["reducer"] = {"keys": r.keys, "defaultOp": r.defaultOp, "ops": r.ops}
             steps.append(d)
@@ -519,9 +750,13 @@ class TransformProcess:
             kind = st.pop("kind")
             if "condition" in st:
                 st["condition"] = cond(st["condition"])
-            if kind == "reduce":
+            if kind in ("reduce", "windowReduce"):
                 r = st["reducer"]
                 st["reducer"] = Reducer(r["keys"], r["defaultOp"], r["ops"])
+            for key in ("split", "window"):
+                if key in st:
+                    spec = dict(st[key])
+                    st[key] = globals()[spec.pop("@class")](**spec)
             steps.append(_Step(kind, **st))
         return TransformProcess(sch, steps)
 
