@@ -476,7 +476,351 @@ def _tf_ops():
         "RandomUniform": (lambda shape, dtype=None, seed=0, seed2=0, **k: torch.rand(_ints(shape)), 1),
         "NonMaxSuppressionV3": (nms_v3, 1),
     }
+    T.update(_tf_ops_more(T, nms_v3))
     return T
+
+
+def _tf_ops_more(T, nms_v3):
+    """Second table of GraphDef operators: special functions, bitwise, segment / scatter / partition ops, linear algebra,
+    random ops, image ops and the older spellings of ops the first table already has."""
+    import torch.nn.functional as F
+
+    def s_(v):
+        return v.decode() if isinstance(v, bytes) else v
+
+    def segment(kind):
+        def f(data, ids, num=None, **kw):
+            ids = ids.long()
+            n = int(num) if num is not None else (int(ids.max()) + 1 if ids.numel() else 0)
+            shape = [n] + list(data.shape[ids.dim():])
+            flat = data.reshape(-1, *data.shape[ids.dim():])
+            idx = ids.reshape(-1)
+            keep = idx >= 0                                                             # negative ids are dropped (unsorted variants)
+            flat, idx = flat[keep], idx[keep]
+            ix = idx.reshape(-1, *([1] * (flat.dim() - 1))).expand_as(flat)
+            if kind in ("sum", "mean"):
+                out = torch.zeros(shape, dtype=data.dtype).scatter_add(0, ix, flat)
+                if kind == "mean":
+                    cnt = torch.zeros(n, dtype=data.dtype).scatter_add(0, idx, torch.ones_like(idx, dtype=data.dtype)).clamp(min=1)
+                    out = out / cnt.reshape(-1, *([1] * (flat.dim() - 1)))
+                return out
+            if kind == "prod":
+                return torch.ones(shape, dtype=data.dtype).scatter_reduce(0, ix, flat, "prod")
+            fill = torch.finfo(data.dtype).min if data.dtype.is_floating_point else torch.iinfo(data.dtype).min
+            if kind == "min":
+                fill = torch.finfo(data.dtype).max if data.dtype.is_floating_point else torch.iinfo(data.dtype).max
+            empty = 0 if num is None else fill                                          # sorted variants give 0 for an empty segment
+            out = torch.full(shape, fill, dtype=data.dtype).scatter_reduce(0, ix, flat, "amax" if kind == "max" else "amin")
+            hit = torch.zeros(n, dtype=torch.bool).index_fill(0, idx, True).reshape(-1, *([1] * (flat.dim() - 1)))
+            return torch.where(hit, out, torch.full_like(out, empty))
+        return f
+
+    def tensor_scatter(kind):
+        def f(x, indices, updates, **kw):
+            idx = tuple(indices[..., j].long() for j in range(indices.shape[-1]))
+            if kind == "update":
+                return x.index_put(idx, updates)
+            return x.index_put(idx, updates if kind == "add" else -updates, accumulate=True)
+        return f
+
+    def dynamic_partition(data, partitions, num_partitions=2, **kw):
+        return tuple(data[partitions == i] for i in range(int(num_partitions)))
+
+    def dynamic_stitch(*args, N=None, **kw):
+        n = len(args) // 2
+        idx, data = args[:n], args[n:]
+        size = max(int(i.max()) + 1 for i in idx if i.numel())
+        tail = data[0].shape[idx[0].dim():]
+        out = torch.zeros([size] + list(tail), dtype=data[0].dtype)
+        for i, d in zip(idx, data):                                                     # later inputs win, as in TensorFlow
+            out[i.reshape(-1).long()] = d.reshape(-1, *tail)
+        return out
+
+    def fake_quant(x, lo, hi, num_bits=8, narrow_range=False, **kw):
+        qmin, qmax = (1 if narrow_range else 0), 2 ** int(num_bits) - 1
+        lo, hi = torch.as_tensor(lo, dtype=x.dtype), torch.as_tensor(hi, dtype=x.dtype)
+        scale = (hi - lo) / (qmax - qmin)
+        zp = qmin - lo / scale                                                          # nudged so that zero is exactly representable
+        nz = torch.where(zp < qmin, torch.full_like(zp, qmin), torch.where(zp > qmax, torch.full_like(zp, qmax), torch.round(zp)))
+        nlo, nhi = (qmin - nz) * scale, (qmax - nz) * scale
+        c = torch.minimum(torch.maximum(x, nlo), nhi)
+        return torch.floor((c - nlo) / scale + 0.5) * scale + nlo
+
+    def in_top_k(pred, targets, k, **kw):
+        k = int(k)
+        t = pred.gather(1, targets.long().reshape(-1, 1))
+        return (pred > t).sum(1) < k
+
+    def matrix_set_diag(x, d, k=0, **kw):
+        out = x.clone()
+        out.diagonal(int(k) if not torch.is_tensor(k) else int(k), -2, -1).copy_(d)
+        return out
+
+    def max_pool_argmax(x, ksize=(1, 1, 1, 1), strides=(1, 1, 1, 1), padding="VALID", include_batch_in_index=False, **kw):
+        xn = x.permute(0, 3, 1, 2)
+        k, st = list(ksize[1:3]), list(strides[1:3])
+        if s_(padding) == "SAME":
+            ph = max((-(-xn.shape[2] // st[0]) - 1) * st[0] + k[0] - xn.shape[2], 0)
+            pw = max((-(-xn.shape[3] // st[1]) - 1) * st[1] + k[1] - xn.shape[3], 0)
+            if ph or pw:
+                raise NotImplementedError("MaxPoolWithArgmax with SAME padding that pads")
+        y, ix = F.max_pool2d(xn, k, st, return_indices=True)                           # ix = h * W + w within a channel plane
+        H, W, C = x.shape[1], x.shape[2], x.shape[3]
+        c = torch.arange(C).reshape(1, C, 1, 1)
+        flat = ix * C + c                                                               # ((h * W) + w) * C + c, the NHWC flat index
+        if include_batch_in_index:
+            flat = flat + torch.arange(x.shape[0]).reshape(-1, 1, 1, 1) * (H * W * C)
+        return y.permute(0, 2, 3, 1), flat.permute(0, 2, 3, 1)
+
+    def resize(mode):
+        def f(x, size, align_corners=False, half_pixel_centers=False, **kw):
+            h, w = _ints(size)
+            xn = x.permute(0, 3, 1, 2).float()
+            if mode == "area":
+                y = F.adaptive_avg_pool2d(xn, (h, w))
+            else:
+                y = F.interpolate(xn, size=(h, w), mode="bicubic", align_corners=bool(align_corners))
+            return y.permute(0, 2, 3, 1)
+        return f
+
+    def crop_and_resize(image, boxes, box_ind, crop_size, method="bilinear", extrapolation_value=0.0, **kw):
+        ch, cw = _ints(crop_size)
+        N, H, W, C = image.shape
+        out = []
+        for b, bi in zip(boxes, box_ind.long()):
+            y1, x1, y2, x2 = [float(v) for v in b]
+            ys = torch.linspace(y1 * (H - 1), y2 * (H - 1), ch) if ch > 1 else torch.tensor([0.5 * (y1 + y2) * (H - 1)])
+            xs = torch.linspace(x1 * (W - 1), x2 * (W - 1), cw) if cw > 1 else torch.tensor([0.5 * (x1 + x2) * (W - 1)])
+            img = image[bi].float()
+            if s_(method) == "nearest":
+                yi, xi = ys.round().long().clamp(0, H - 1), xs.round().long().clamp(0, W - 1)
+                crop = img[yi][:, xi]
+            else:
+                y0, x0 = ys.floor().long().clamp(0, H - 1), xs.floor().long().clamp(0, W - 1)
+                y1i, x1i = (y0 + 1).clamp(max=H - 1), (x0 + 1).clamp(max=W - 1)
+                fy, fx = (ys - y0).reshape(-1, 1, 1), (xs - x0).reshape(1, -1, 1)
+                top = img[y0][:, x0] * (1 - fx) + img[y0][:, x1i] * fx
+                bot = img[y1i][:, x0] * (1 - fx) + img[y1i][:, x1i] * fx
+                crop = top * (1 - fy) + bot * fy
+            inside = ((ys >= 0) & (ys <= H - 1)).reshape(-1, 1, 1) & ((xs >= 0) & (xs <= W - 1)).reshape(1, -1, 1)
+            out.append(torch.where(inside, crop, torch.full_like(crop, float(extrapolation_value))))
+        return torch.stack(out)
+
+    def extract_patches(x, ksizes=(1, 1, 1, 1), strides=(1, 1, 1, 1), rates=(1, 1, 1, 1), padding="VALID", **kw):
+        if s_(padding) != "VALID":
+            raise NotImplementedError("ExtractImagePatches with SAME padding")
+        xn = x.permute(0, 3, 1, 2)
+        n, c = xn.shape[:2]
+        cols = F.unfold(xn, list(ksizes[1:3]), dilation=list(rates[1:3]), stride=list(strides[1:3]))   # [n, c*kh*kw, L]
+        kh, kw_ = ksizes[1], ksizes[2]
+        oh = (xn.shape[2] - (kh - 1) * rates[1] - 1) // strides[1] + 1
+        cols = cols.reshape(n, c, kh, kw_, oh, -1).permute(0, 4, 5, 2, 3, 1)             # patch depth in (row, col, channel) order
+        return cols.reshape(n, oh, cols.shape[2], kh * kw_ * c)
+
+    def rgb_to_hsv(x, **kw):
+        r, g, b = x.unbind(-1)
+        mx, mn = x.max(-1).values, x.min(-1).values
+        d = mx - mn
+        s = torch.where(mx > 0, d / mx.clamp(min=1e-30), torch.zeros_like(mx))
+        dd = d.clamp(min=1e-30)
+        h = torch.where(mx == r, ((g - b) / dd) % 6, torch.where(mx == g, (b - r) / dd + 2, (r - g) / dd + 4)) / 6
+        h = torch.where(d == 0, torch.zeros_like(h), h)
+        return torch.stack([h, s, mx], -1)
+
+    def hsv_to_rgb(x, **kw):
+        h, s, v = x.unbind(-1)
+        k = lambda n: (n + h * 6) % 6
+        f = lambda n: v - v * s * torch.clamp(torch.minimum(k(n), 4 - k(n)), 0, 1)
+        return torch.stack([f(5), f(3), f(1)], -1)
+
+    def adjust_hue(x, delta, **kw):
+        hsv = rgb_to_hsv(x)
+        return hsv_to_rgb(torch.stack([(hsv[..., 0] + delta) % 1.0, hsv[..., 1], hsv[..., 2]], -1))
+
+    def adjust_saturation(x, scale, **kw):
+        hsv = rgb_to_hsv(x)
+        return hsv_to_rgb(torch.stack([hsv[..., 0], (hsv[..., 1] * scale).clamp(0, 1), hsv[..., 2]], -1))
+
+    def nms_padded(boxes, scores, m, it, st, pad_to_max_output_size=False, **kw):
+        sel = nms_v3(boxes, scores, m, it, st)
+        n = torch.tensor(sel.numel(), dtype=torch.int32)
+        if pad_to_max_output_size:
+            sel = F.pad(sel, (0, int(m) - sel.numel()))
+        return sel, n
+
+    def nms_v5(boxes, scores, m, it, st, soft_nms_sigma=0.0, pad_to_max_output_size=False, **kw):
+        if float(soft_nms_sigma) != 0.0:
+            raise NotImplementedError("NonMaxSuppressionV5 with soft-NMS")
+        sel, n = nms_padded(boxes, scores, m, it, st, pad_to_max_output_size)
+        return sel, scores[sel.long()], n
+
+    def unique(x, out_idx=None, **kw):
+        seen, vals, idx = {}, [], []
+        for v in x.tolist():
+            if v not in seen:
+                seen[v] = len(vals)
+                vals.append(v)
+            idx.append(seen[v])
+        return torch.tensor(vals, dtype=x.dtype), torch.tensor(idx, dtype=torch.int32)
+
+    def unique_counts(x, **kw):
+        v, i = unique(x)
+        return v, i, torch.bincount(i.long(), minlength=v.numel()).to(torch.int32)
+
+    def list_diff(x, y, **kw):
+        drop = set(y.tolist())
+        keep = [j for j, v in enumerate(x.tolist()) if v not in drop]
+        return x[keep], torch.tensor(keep, dtype=torch.int32)
+
+    def polygamma(n, x, **kw):
+        return torch.stack([torch.special.polygamma(int(k), v) for k, v in zip(n.reshape(-1).tolist(), x.reshape(-1))]).reshape(x.shape) if torch.is_tensor(n) and n.numel() > 1 \
+            else torch.special.polygamma(int(n), x)
+
+    def lu(x, **kw):
+        LU, piv = torch.linalg.lu_factor(x)
+        perm = torch.arange(x.shape[-1]).repeat(*x.shape[:-2], 1) if x.dim() > 2 else torch.arange(x.shape[-1])
+        pv = (piv - 1).long()
+        for i in range(pv.shape[-1]):                                                   # LAPACK row swaps -> permutation vector
+            j = pv[..., i]
+            a, b = perm[..., i].clone(), perm.gather(-1, j.unsqueeze(-1)).squeeze(-1)
+            perm[..., i] = b
+            perm.scatter_(-1, j.unsqueeze(-1), a.unsqueeze(-1))
+        return LU, perm.to(torch.int32)
+
+    def dilation2d(x, filt, strides=(1, 1, 1, 1), rates=(1, 1, 1, 1), padding="VALID", **kw):
+        if s_(padding) != "VALID":
+            raise NotImplementedError("Dilation2D with SAME padding")
+        xn = x.permute(0, 3, 1, 2)
+        n, c = xn.shape[:2]
+        kh, kw_ = filt.shape[:2]
+        cols = F.unfold(xn, (kh, kw_), dilation=list(rates[1:3]), stride=list(strides[1:3])).reshape(n, c, kh * kw_, -1)
+        y = (cols + filt.permute(2, 0, 1).reshape(1, c, kh * kw_, 1)).amax(2)
+        oh = (xn.shape[2] - (kh - 1) * rates[1] - 1) // strides[1] + 1
+        return y.reshape(n, c, oh, -1).permute(0, 2, 3, 1)
+
+    def draw_boxes(images, boxes, colors=None, **kw):
+        out = images.clone()
+        N, H, W, C = out.shape
+        for n in range(N):
+            for bi, b in enumerate(boxes[n]):
+                y1, x1, y2, x2 = [float(v) for v in b]
+                r1, r2 = int(round(y1 * (H - 1))), int(round(y2 * (H - 1)))
+                c1, c2 = int(round(x1 * (W - 1))), int(round(x2 * (W - 1)))
+                if r1 > r2 or c1 > c2 or r1 >= H or c1 >= W or r2 < 0 or c2 < 0:
+                    continue
+                col = colors[bi % colors.shape[0]][:C].to(out.dtype) if colors is not None and torch.is_tensor(colors) and colors.numel() else \
+                    torch.tensor([1.0, 1.0, 0.0, 1.0][:C] if C > 1 else [1.0], dtype=out.dtype)
+                r1c, r2c, c1c, c2c = max(r1, 0), min(r2, H - 1), max(c1, 0), min(c2, W - 1)
+                if r1 >= 0: out[n, r1, c1c:c2c + 1] = col
+                if r2 < H: out[n, r2, c1c:c2c + 1] = col
+                if c1 >= 0: out[n, r1c:r2c + 1, c1] = col
+                if c2 < W: out[n, r1c:r2c + 1, c2] = col
+        return out
+
+    def conv3d_backprop_input(sizes, w, dy, strides=(1, 1, 1, 1, 1), padding="VALID", dilations=(1, 1, 1, 1, 1), **kw):
+        out = _ints(sizes)
+        st, dl = list(strides[1:4]), list(dilations[1:4])
+        g = dy.permute(0, 4, 1, 2, 3)
+        wk = w.permute(4, 3, 0, 1, 2)                                                   # DHWIO -> OIDHW; conv_transpose wants [in=O, out=I, ...]
+        pads, opad = [], []
+        for d in range(3):
+            eff = (wk.shape[2 + d] - 1) * dl[d] + 1
+            total = max((g.shape[2 + d] - 1) * st[d] + eff - out[1 + d], 0) if s_(padding) == "SAME" else 0
+            pads.append(total // 2)
+            opad.append(out[1 + d] - ((g.shape[2 + d] - 1) * st[d] - 2 * (total // 2) + eff))
+        y = F.conv_transpose3d(g, wk, None, st, pads, [max(o, 0) for o in opad], 1, dl)
+        y = y[:, :, :out[1], :out[2], :out[3]]
+        return y.permute(0, 2, 3, 4, 1)
+
+    def conv2d_backprop_filter(x, sizes, dy, strides=(1, 1, 1, 1), padding="VALID", dilations=(1, 1, 1, 1), **kw):
+        kh, kw_, ci, co = _ints(sizes)
+        xn, g = x.permute(0, 3, 1, 2).float(), dy.permute(0, 3, 1, 2).float()
+        st, dl = list(strides[1:3]), list(dilations[1:3])
+        pad = [0, 0]
+        if s_(padding) == "SAME":
+            flat = []
+            for d in (1, 0):
+                total = max((g.shape[2 + d] - 1) * st[d] + ([kh, kw_][d] - 1) * dl[d] + 1 - xn.shape[2 + d], 0)
+                flat += [total // 2, total - total // 2]
+            xn = F.pad(xn, flat)
+        gw = torch.nn.grad.conv2d_weight(xn, (co, ci, kh, kw_), g, st, pad, dl)
+        return gw.permute(2, 3, 1, 0).to(x.dtype)
+
+    M = {
+        "Acosh": (lambda x, **k: x.acosh(), 1), "Asinh": (lambda x, **k: x.asinh(), 1), "Atanh": (lambda x, **k: x.atanh(), 1),
+        "Erfc": (lambda x, **k: x.erfc(), 1), "Lgamma": (lambda x, **k: x.lgamma(), 1), "Digamma": (lambda x, **k: x.digamma(), 1),
+        "Igamma": (lambda a, x, **k: torch.special.gammainc(a, x), 1), "Igammac": (lambda a, x, **k: torch.special.gammaincc(a, x), 1),
+        "Polygamma": (polygamma, 1), "Zeta": (lambda x, q, **k: torch.special.zeta(x, q), 1),
+        "Xdivy": (lambda x, y, **k: torch.where(x == 0, torch.zeros_like(x), x / y), 1), "Xlogy": (lambda x, y, **k: torch.special.xlogy(x, y), 1),
+        "DivNoNan": (lambda x, y, **k: torch.where(y == 0, torch.zeros_like(x), x / y), 1),
+        "TruncateMod": (lambda x, y, **k: torch.fmod(x, y), 1),
+        "ApproximateEqual": (lambda x, y, tolerance=1e-5, **k: (x - y).abs() < tolerance, 1),
+        "BitwiseAnd": (lambda x, y, **k: x & y, 1), "BitwiseOr": (lambda x, y, **k: x | y, 1), "BitwiseXor": (lambda x, y, **k: x ^ y, 1),
+        "LeftShift": (lambda x, y, **k: x << y, 1), "RightShift": (lambda x, y, **k: x >> y, 1),
+        "Bitcast": (lambda x, type=None, **k: x.view(type) if isinstance(type, torch.dtype) else x, 1),
+        "CheckNumerics": (lambda x, **k: x, 1), "Empty": (lambda shape, dtype=None, init=False, **k: torch.zeros(_ints(shape)), 1),
+        "BroadcastArgs": (lambda a, b, **k: torch.tensor(list(torch.broadcast_shapes(tuple(_ints(a)), tuple(_ints(b)))), dtype=torch.int32), 1),
+        "Concat": (lambda axis, *xs, **k: torch.cat(xs, int(axis)), 1),
+        "Cross": (lambda a, b, **k: torch.linalg.cross(a, b), 1),
+        "Diag": (lambda x, **k: torch.diag(x.reshape(-1)).reshape(list(x.shape) * 2), 1),
+        "DiagPart": (lambda x, **k: x.reshape(int(np.prod(x.shape[:x.dim() // 2])), -1).diagonal().reshape(x.shape[:x.dim() // 2]), 1),
+        "MatrixSetDiag": (matrix_set_diag, 1), "MatrixSetDiagV3": (matrix_set_diag, 1),
+        "MatrixDeterminant": (lambda x, **k: torch.linalg.det(x), 1), "MatrixInverse": (lambda x, adjoint=False, **k: torch.linalg.inv(x.mH if adjoint else x), 1),
+        "LogMatrixDeterminant": (lambda x, **k: tuple(torch.linalg.slogdet(x)), 2),
+        "Cholesky": (lambda x, **k: torch.linalg.cholesky(x), 1),
+        "MatrixSolve": (lambda a, b, adjoint=False, **k: torch.linalg.solve(a.mH if adjoint else a, b), 1),
+        "MatrixTriangularSolve": (lambda a, b, lower=True, adjoint=False, **k: torch.linalg.solve_triangular(a.mH if adjoint else a, b, upper=(not lower) != bool(adjoint)), 1),
+        "Qr": (lambda x, full_matrices=False, **k: tuple(torch.linalg.qr(x, mode="complete" if full_matrices else "reduced")), 2),
+        "Svd": (lambda x, compute_uv=True, full_matrices=False, **k: (lambda u, s, vh: (s, u, vh.mH))(*torch.linalg.svd(x, full_matrices=bool(full_matrices))), 3),
+        "Lu": (lu, 2),
+        "DynamicPartition": (dynamic_partition, -1), "DynamicStitch": (dynamic_stitch, 1), "ParallelDynamicStitch": (dynamic_stitch, 1),
+        "FakeQuantWithMinMaxArgs": (lambda x, min=-6.0, max=6.0, **k: fake_quant(x, min, max, **k), 1),
+        "FakeQuantWithMinMaxVars": (lambda x, lo, hi, **k: fake_quant(x, lo, hi, **k), 1),
+        "FusedBatchNormV2": T["FusedBatchNorm"] if "FusedBatchNorm" in T else T.get("FusedBatchNormV3"),
+        "HistogramFixedWidth": (lambda v, rng, nbins, **k: torch.bucketize(v.reshape(-1).float().clamp(float(rng[0]), float(rng[1])),
+                                                                             torch.linspace(float(rng[0]), float(rng[1]), int(nbins) + 1)[1:-1], right=True)
+                                .bincount(minlength=int(nbins)).to(torch.int32), 1),
+        "Bincount": (lambda arr, size, weights, **k: (torch.bincount(arr.reshape(-1).long(), weights.reshape(-1) if weights.numel() else None, minlength=int(size))[:int(size)]), 1),
+        "InTopK": (lambda p, t, k=1, **kw: in_top_k(p, t, k), 1), "InTopKV2": (in_top_k, 1),
+        "InvertPermutation": (lambda x, **k: torch.argsort(x.long()).to(x.dtype), 1),
+        "LinSpace": (lambda a, b, n, **k: torch.linspace(float(a), float(b), int(n), dtype=a.dtype if a.dtype.is_floating_point else torch.float32), 1),
+        "ListDiff": (list_diff, 2),
+        "MaxPoolV2": (lambda x, ksize, strides, **k: T["MaxPool"][0](x, ksize=_ints(ksize), strides=_ints(strides), **k), 1),
+        "MaxPoolWithArgmax": (max_pool_argmax, 2),
+        "Multinomial": (lambda logits, n, seed=0, seed2=0, **k: torch.multinomial(logits.float().softmax(-1), int(n), True), 1),
+        "RandomStandardNormal": (lambda shape, **k: torch.randn(_ints(shape)), 1),
+        "TruncatedNormal": (lambda shape, **k: torch.nn.init.trunc_normal_(torch.empty(_ints(shape)), 0.0, 1.0, -2.0, 2.0), 1),
+        "RandomUniformInt": (lambda shape, lo, hi, **k: torch.randint(int(lo), int(hi), _ints(shape), dtype=lo.dtype), 1),
+        "RandomGamma": (lambda shape, alpha, **k: torch.distributions.Gamma(alpha.float().expand(_ints(shape) + list(alpha.shape)), 1.0).sample(), 1),
+        "RandomShuffle": (lambda x, **k: x[torch.randperm(x.shape[0])], 1),
+        "NonMaxSuppression": (lambda b, s, m, iou_threshold=0.5, **k: nms_v3(b, s, m, iou_threshold, float("-inf")), 1),
+        "NonMaxSuppressionV2": (lambda b, s, m, it, **k: nms_v3(b, s, m, it, float("-inf")), 1),
+        "NonMaxSuppressionV4": (nms_padded, 2), "NonMaxSuppressionV5": (nms_v5, 3),
+        "ResizeArea": (resize("area"), 1), "ResizeBicubic": (resize("bicubic"), 1), "CropAndResize": (crop_and_resize, 1),
+        "ExtractImagePatches": (extract_patches, 1), "Dilation2D": (dilation2d, 1), "DrawBoundingBoxes": (draw_boxes, 1), "DrawBoundingBoxesV2": (draw_boxes, 1),
+        "RGBToHSV": (rgb_to_hsv, 1), "HSVToRGB": (hsv_to_rgb, 1), "AdjustHue": (adjust_hue, 1), "AdjustSaturation": (adjust_saturation, 1),
+        "AdjustContrastV2": (lambda x, f, **k: (x - x.mean((-3, -2), keepdim=True)) * f + x.mean((-3, -2), keepdim=True), 1),
+        "Reverse": (lambda x, dims, **k: x.flip([i for i, d in enumerate(dims.tolist()) if d]) if dims.any() else x, 1),
+        "ReverseSequence": (lambda x, lens, seq_dim=1, batch_dim=0, **k: torch.stack(
+            [torch.cat([r.narrow(seq_dim - (seq_dim > batch_dim), 0, int(n)).flip(seq_dim - (seq_dim > batch_dim)),
+                        r.narrow(seq_dim - (seq_dim > batch_dim), int(n), r.shape[seq_dim - (seq_dim > batch_dim)] - int(n))], seq_dim - (seq_dim > batch_dim))
+             for r, n in zip(x.unbind(batch_dim), lens.tolist())], batch_dim), 1),
+        "Roll": (lambda x, shift, axis, **k: torch.roll(x, _ints(shift) if shift.dim() else int(shift), _ints(axis) if axis.dim() else int(axis)), 1),
+        "SegmentSum": (segment("sum"), 1), "SegmentMean": (segment("mean"), 1), "SegmentProd": (segment("prod"), 1),
+        "SegmentMax": (lambda d, i, **k: segment("max")(d, i), 1), "SegmentMin": (lambda d, i, **k: segment("min")(d, i), 1),
+        "UnsortedSegmentSum": (segment("sum"), 1), "UnsortedSegmentProd": (segment("prod"), 1),
+        "UnsortedSegmentMax": (segment("max"), 1), "UnsortedSegmentMin": (segment("min"), 1),
+        "TensorScatterAdd": (tensor_scatter("add"), 1), "TensorScatterSub": (tensor_scatter("sub"), 1), "TensorScatterUpdate": (tensor_scatter("update"), 1),
+        "TopK": (lambda x, k=1, sorted=True, **kw: tuple(torch.topk(x, int(k), sorted=True)), 2),
+        "Unique": (unique, 2), "UniqueWithCounts": (unique_counts, 3),
+        "BatchNormWithGlobalNormalization": (lambda t, m, v, beta, gamma, variance_epsilon=1e-3, scale_after_normalization=True, **k:
+                                             (t - m) * torch.rsqrt(v + variance_epsilon) * (gamma if scale_after_normalization else 1.0) + beta, 1),
+        "Betainc": (lambda a, b, x, **k: torch.as_tensor(__import__("scipy.special").special.betainc(a.numpy(), b.numpy(), x.numpy())), 1),
+        "ClipByNorm": (lambda x, c, **k: x * torch.clamp(c / x.norm().clamp(min=1e-30), max=1.0), 1),
+        "NthElement": (lambda x, n, reverse=False, **k: (x.sort(-1, descending=bool(reverse)).values)[..., int(n)], 1),
+        "Conv3DBackpropInputV2": (conv3d_backprop_input, 1), "Conv2DBackpropFilter": (conv2d_backprop_filter, 1),
+    }
+    return {k: v for k, v in M.items() if v is not None and k not in T}
 
 
 def _register_tf_ops():

@@ -316,3 +316,120 @@ def test_tensorflow_spatial_scatter_and_3d_rules_by_their_definitions():
     assert sel.tolist() == [3, 0, 5]
     sel = T["NonMaxSuppressionV3"](boxes, scores, torch.tensor(6), torch.tensor(0.5), torch.tensor(0.4))
     assert sel.tolist() == [3, 0]
+
+
+def test_tensorflow_second_operator_table_by_definitions():
+    """Special functions, segment / scatter / partition ops, linear algebra, image ops and older spellings: each against the
+    TensorFlow definition written out in plain torch / numpy (tensorflow/core/ops/{math,array,linalg,image,nn}_ops.cc)."""
+    from deeplearning4j_b200.importers.tf_import import _tf_ops
+    T = {k: v[0] for k, v in _tf_ops().items()}
+    g = torch.Generator().manual_seed(11)
+    R = lambda *s: torch.randn(*s, generator=g)
+
+    x = R(7).abs() + 0.5
+    assert torch.allclose(T["Lgamma"](x), torch.lgamma(x)) and torch.allclose(T["Digamma"](x), torch.digamma(x))
+    assert torch.allclose(T["Igamma"](x, x + 1) + T["Igammac"](x, x + 1), torch.ones(7), atol=1e-6)
+    assert torch.allclose(T["Polygamma"](torch.tensor(1), x), torch.special.polygamma(1, x))
+    assert T["Xdivy"](torch.tensor([0.0, 2.0]), torch.tensor([0.0, 4.0])).tolist() == [0.0, 0.5]
+    assert T["DivNoNan"](torch.tensor([1.0, 2.0]), torch.tensor([0.0, 4.0])).tolist() == [0.0, 0.5]
+    assert T["TruncateMod"](torch.tensor([-7, 7]), torch.tensor([3, -3])).tolist() == [-1, 1]
+    assert T["LeftShift"](torch.tensor([1, 3]), torch.tensor([2, 1])).tolist() == [4, 6] and T["BitwiseXor"](torch.tensor([6]), torch.tensor([3])).tolist() == [5]
+    assert T["BroadcastArgs"](torch.tensor([3, 1]), torch.tensor([1, 4])).tolist() == [3, 4]
+    assert torch.equal(T["Concat"](torch.tensor(1), torch.ones(2, 1), torch.zeros(2, 2)), torch.tensor([[1.0, 0, 0], [1.0, 0, 0]]))
+    d = T["Diag"](torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    assert d.shape == (2, 2, 2, 2) and d[1, 0, 1, 0] == 3 and d[0, 1, 1, 0] == 0 and torch.equal(T["DiagPart"](d), torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    m = R(3, 4, 4)
+    assert torch.equal(T["MatrixSetDiag"](m, torch.ones(3, 4)).diagonal(0, -2, -1), torch.ones(3, 4))
+    spd = m @ m.transpose(1, 2) + 4 * torch.eye(4)
+    L = T["Cholesky"](spd)
+    assert torch.allclose(L @ L.transpose(1, 2), spd, atol=1e-4)
+    b = R(3, 4, 2)
+    assert torch.allclose(spd @ T["MatrixSolve"](spd, b), b, atol=1e-3)
+    assert torch.allclose(L @ T["MatrixTriangularSolve"](L, b, lower=True), b, atol=1e-4)
+    assert torch.allclose(L.transpose(1, 2) @ T["MatrixTriangularSolve"](L, b, lower=True, adjoint=True), b, atol=1e-4)
+    sign, logdet = T["LogMatrixDeterminant"](spd)
+    assert torch.allclose(sign * logdet.exp(), T["MatrixDeterminant"](spd), rtol=1e-4)
+    s, u, v = T["Svd"](m)
+    assert torch.allclose(u @ torch.diag_embed(s) @ v.transpose(1, 2), m, atol=1e-4)
+    lu, perm = T["Lu"](m[0])
+    Lm, Um = torch.tril(lu, -1) + torch.eye(4), torch.triu(lu)
+    assert torch.allclose(Lm @ Um, m[0][perm.long()], atol=1e-5)                       # TensorFlow: P applied to the rows of the input
+
+    data = torch.tensor([[1.0, 2], [3, 4], [5, 6], [7, 8]])
+    ids = torch.tensor([0, 0, 2, 2])
+    assert T["SegmentSum"](data, ids).tolist() == [[4, 6], [0, 0], [12, 14]] and T["SegmentMean"](data, ids).tolist() == [[2, 3], [0, 0], [6, 7]]
+    assert T["SegmentMax"](data, ids).tolist() == [[3, 4], [0, 0], [7, 8]] and T["SegmentProd"](data, ids).tolist() == [[3, 8], [1, 1], [35, 48]]
+    um = T["UnsortedSegmentMax"](data, torch.tensor([1, -1, 1, 0]), torch.tensor(3))
+    assert um[:2].tolist() == [[7, 8], [5, 6]] and um[2, 0] == torch.finfo(torch.float32).min
+    assert T["UnsortedSegmentSum"](data, torch.tensor([1, -1, 1, 0]), torch.tensor(2)).tolist() == [[7, 8], [6, 8]]
+    idx = torch.tensor([[0, 1], [3, 0]])
+    assert T["TensorScatterAdd"](data, idx, torch.tensor([10.0, 20]))[0].tolist() == [1, 12] and T["TensorScatterUpdate"](data, idx, torch.tensor([10.0, 20]))[3, 0] == 20
+    assert T["TensorScatterSub"](data, torch.tensor([[1]]), torch.tensor([[1.0, 1]]))[1].tolist() == [2, 3]
+    p0, p1 = T["DynamicPartition"](data, torch.tensor([1, 0, 1, 0]), num_partitions=2)
+    assert p0.tolist() == [[3, 4], [7, 8]] and p1.tolist() == [[1, 2], [5, 6]]
+    assert torch.equal(T["DynamicStitch"](torch.tensor([1, 3]), torch.tensor([0, 2]), p0, p1), data)
+
+    fq = T["FakeQuantWithMinMaxArgs"](torch.tensor([-7.0, -0.02, 0.0, 0.03, 2.9, 9.0]), min=-6.0, max=6.0, num_bits=8)
+    step = 12.0 / 255
+    assert torch.allclose(fq[1:4] / step, torch.round(fq[1:4] / step), atol=1e-4) and fq[2] == 0 and abs(float(fq[0]) + 6) < step and abs(float(fq[5]) - 6) < step
+    assert T["InTopKV2"](torch.tensor([[0.1, 0.9, 0.5], [0.3, 0.2, 0.1]]), torch.tensor([2, 2]), torch.tensor(2)).tolist() == [True, False]
+    assert T["InvertPermutation"](torch.tensor([2, 0, 1])).tolist() == [1, 2, 0]
+    assert T["LinSpace"](torch.tensor(1.0), torch.tensor(2.0), torch.tensor(5)).tolist() == [1.0, 1.25, 1.5, 1.75, 2.0]
+    o, i = T["ListDiff"](torch.tensor([1, 2, 3, 4, 5, 6]), torch.tensor([1, 3, 5]))
+    assert o.tolist() == [2, 4, 6] and i.tolist() == [1, 3, 5]
+    assert T["HistogramFixedWidth"](torch.tensor([-1.0, 0.0, 1.5, 2.0, 5.0, 15.0]), torch.tensor([0.0, 5.0]), torch.tensor(5)).tolist() == [2, 1, 1, 0, 2]
+    assert T["Bincount"](torch.tensor([1, 1, 3]), torch.tensor(5), torch.tensor([])).tolist() == [0, 2, 0, 1, 0]
+    u_, ix_, cnt = T["UniqueWithCounts"](torch.tensor([4, 1, 4, 7, 1, 4]))
+    assert u_.tolist() == [4, 1, 7] and ix_.tolist() == [0, 1, 0, 2, 1, 0] and cnt.tolist() == [3, 2, 1]
+    assert T["NthElement"](torch.tensor([[5, 1, 3], [2, 9, 4]]), torch.tensor(1)).tolist() == [3, 4]
+    assert torch.allclose(T["ClipByNorm"](torch.tensor([3.0, 4.0]), torch.tensor(1.0)), torch.tensor([0.6, 0.8]))
+    assert T["Roll"](torch.arange(5), torch.tensor(2), torch.tensor(0)).tolist() == [3, 4, 0, 1, 2]
+    assert T["Reverse"](torch.arange(6).reshape(2, 3), torch.tensor([False, True])).tolist() == [[2, 1, 0], [5, 4, 3]]
+    rs = T["ReverseSequence"](torch.arange(8).reshape(2, 4), torch.tensor([3, 2]), seq_dim=1, batch_dim=0)
+    assert rs.tolist() == [[2, 1, 0, 3], [5, 4, 6, 7]]
+    assert T["RandomUniformInt"](torch.tensor([50]), torch.tensor(3), torch.tensor(6)).unique().tolist() == [3, 4, 5]
+    assert tuple(T["Multinomial"](R(2, 5), torch.tensor(7)).shape) == (2, 7) and float(T["TruncatedNormal"](torch.tensor([1000])).abs().max()) <= 2.0
+
+    img = R(2, 6, 6, 3)
+    y, am = T["MaxPoolWithArgmax"](img, ksize=[1, 2, 2, 1], strides=[1, 2, 2, 1], padding=b"VALID")
+    assert torch.equal(y, F.max_pool2d(img.permute(0, 3, 1, 2), 2).permute(0, 2, 3, 1))
+    assert torch.equal(img[0].reshape(-1)[am[0].reshape(-1)], y[0].reshape(-1))          # flat (h, w, c) index into one image
+    pt = T["ExtractImagePatches"](img, ksizes=[1, 2, 2, 1], strides=[1, 2, 2, 1], rates=[1, 1, 1, 1], padding=b"VALID")
+    assert pt.shape == (2, 3, 3, 12) and torch.equal(pt[1, 2, 1], img[1, 4:6, 2:4, :].reshape(-1))
+    dl = T["Dilation2D"](img, torch.zeros(2, 2, 3), strides=[1, 1, 1, 1], rates=[1, 1, 1, 1], padding=b"VALID")
+    assert torch.equal(dl, F.max_pool2d(img.permute(0, 3, 1, 2), 2, 1).permute(0, 2, 3, 1))
+    rgb = torch.rand(4, 5, 3, generator=g)
+    assert torch.allclose(T["HSVToRGB"](T["RGBToHSV"](rgb)), rgb, atol=1e-5)
+    assert T["RGBToHSV"](torch.tensor([[0.0, 1.0, 0.0]]))[0].tolist() == pytest.approx([1 / 3, 1.0, 1.0])
+    assert torch.allclose(T["AdjustHue"](rgb, 1.0), rgb, atol=1e-5) and torch.allclose(T["AdjustSaturation"](rgb, 0.0), rgb.max(-1, keepdim=True).values.expand_as(rgb), atol=1e-6)
+    ac = T["AdjustContrastV2"](img, 2.0)
+    assert torch.allclose(ac.mean((1, 2)), img.mean((1, 2)), atol=1e-5) and torch.allclose(ac - ac.mean((1, 2), keepdim=True), 2 * (img - img.mean((1, 2), keepdim=True)), atol=1e-5)
+    cr = T["CropAndResize"](img, torch.tensor([[0.0, 0.0, 1.0, 1.0], [0.2, 0.2, 0.6, 0.6]]), torch.tensor([1, 0]), torch.tensor([6, 6]))
+    assert torch.allclose(cr[0], img[1], atol=1e-6) and cr.shape == (2, 6, 6, 3)
+    cr = T["CropAndResize"](img, torch.tensor([[0.0, 0.0, 0.4, 0.4]]), torch.tensor([0]), torch.tensor([3, 3]))       # lands on the pixel centres 0, 1, 2
+    assert torch.allclose(cr[0], img[0, :3, :3], atol=1e-6)
+    assert T["ResizeArea"](img, torch.tensor([3, 3])).shape == (2, 3, 3, 3) and torch.allclose(T["ResizeArea"](img, torch.tensor([3, 3])), F.avg_pool2d(img.permute(0, 3, 1, 2), 2).permute(0, 2, 3, 1), atol=1e-6)
+    boxes = torch.tensor([[0, 0, 1, 1], [0, 0.05, 1, 1.05], [0, 3, 1, 4]], dtype=torch.float32)
+    sel, n = T["NonMaxSuppressionV4"](boxes, torch.tensor([0.9, 0.8, 0.7]), torch.tensor(3), torch.tensor(0.5), torch.tensor(0.0), pad_to_max_output_size=True)
+    assert sel.tolist() == [0, 2, 0] and int(n) == 2
+    sel, sc, n = T["NonMaxSuppressionV5"](boxes, torch.tensor([0.9, 0.8, 0.7]), torch.tensor(3), torch.tensor(0.5), torch.tensor(0.0), torch.tensor(0.0))
+    assert sel.tolist() == [0, 2] and sc.tolist() == pytest.approx([0.9, 0.7])
+    db = T["DrawBoundingBoxes"](torch.zeros(1, 5, 5, 3), torch.tensor([[[0.0, 0.0, 1.0, 1.0]]]), torch.tensor([[1.0, 0.0, 0.0]]))
+    assert db[0, 0, 2].tolist() == [1, 0, 0] and db[0, 2, 0].tolist() == [1, 0, 0] and db[0, 2, 2].tolist() == [0, 0, 0]
+
+    # gradients of the convolutions against autograd
+    x3 = R(1, 4, 5, 5, 2).requires_grad_(True)
+    w3 = R(2, 2, 2, 2, 3)
+    y3 = F.conv3d(x3.permute(0, 4, 1, 2, 3), w3.permute(4, 3, 0, 1, 2), stride=(1, 2, 1)).permute(0, 2, 3, 4, 1)
+    dy3 = R(*y3.shape)
+    y3.backward(dy3)
+    got = T["Conv3DBackpropInputV2"](torch.tensor([1, 4, 5, 5, 2]), w3, dy3, strides=[1, 1, 2, 1, 1], padding=b"VALID")
+    assert torch.allclose(got, x3.grad, atol=1e-5)
+    x2 = R(2, 6, 7, 3)
+    w2 = R(3, 3, 3, 4).requires_grad_(True)
+    xp = F.pad(x2.permute(0, 3, 1, 2), (1, 1, 0, 1))                                  # SAME for 6x7, k 3, stride 2: rows (0, 1), columns (1, 1)
+    y2 = F.conv2d(xp, w2.permute(3, 2, 0, 1), stride=2).permute(0, 2, 3, 1)
+    dy2 = R(*y2.shape)
+    y2.backward(dy2)
+    got = T["Conv2DBackpropFilter"](x2, torch.tensor([3, 3, 3, 4]), dy2, strides=[1, 2, 2, 1], padding=b"SAME")
+    assert torch.allclose(got, w2.grad, atol=1e-4)
