@@ -744,7 +744,230 @@ def _onnx_ops():
         "ReverseSequence": (reverse_sequence, 1), "Unique": (unique, 4),
         "NonMaxSuppression": (nms, 1), "RoiAlign": (roi_align, 1),
     }
+    T.update(_onnx_ops_more())
     return T
+
+
+def _onnx_ops_more():
+    """Second table: integer / quantised linear algebra, window and spectral ops, random ops, losses, unpooling, grid sampling."""
+    import math
+    import torch.nn.functional as F
+    TORCH_DT = {1: torch.float32, 2: torch.uint8, 3: torch.int8, 5: torch.int16, 6: torch.int32, 7: torch.int64, 9: torch.bool, 10: torch.float16,
+                11: torch.float64, 16: torch.bfloat16}
+
+    def window(kind):
+        def f(size, output_datatype=1, periodic=1, **kw):
+            n = int(size)
+            N = n if periodic else n - 1
+            k = torch.arange(n, dtype=torch.float64)
+            if kind == "hann":
+                w = 0.5 - 0.5 * torch.cos(2 * math.pi * k / N)
+            elif kind == "hamming":
+                w = 25 / 46 - 21 / 46 * torch.cos(2 * math.pi * k / N)
+            else:
+                w = 0.42 - 0.5 * torch.cos(2 * math.pi * k / N) + 0.08 * torch.cos(4 * math.pi * k / N)
+            return w.to(TORCH_DT[int(output_datatype)])
+        return f
+
+    def pads_of(x, kshape, strides, dilations, pads, auto_pad):
+        nd = len(kshape)
+        auto_pad = auto_pad.decode() if isinstance(auto_pad, bytes) else auto_pad
+        if auto_pad in ("SAME_UPPER", "SAME_LOWER"):
+            out = []
+            for d in range(nd):
+                total = max((-(-x.shape[2 + d] // strides[d]) - 1) * strides[d] + (kshape[d] - 1) * dilations[d] + 1 - x.shape[2 + d], 0)
+                lo = total // 2 if auto_pad == "SAME_UPPER" else total - total // 2
+                out.append((lo, total - lo))
+            return out
+        pads = list(pads) if pads is not None else [0] * (2 * nd)
+        return [(pads[d], pads[d + nd]) for d in range(nd)]
+
+    def conv_int(x, w, x_zp=None, w_zp=None, strides=None, dilations=None, pads=None, group=1, auto_pad="NOTSET", kernel_shape=None, **kw):
+        nd = w.dim() - 2
+        strides, dilations = list(strides or [1] * nd), list(dilations or [1] * nd)
+        xf = x.to(torch.float64) - (x_zp.to(torch.float64) if x_zp is not None else 0)
+        wz = w_zp.to(torch.float64).reshape(-1, *([1] * (w.dim() - 1))) if w_zp is not None and w_zp.numel() > 1 else (w_zp.to(torch.float64) if w_zp is not None else 0)
+        wf = w.to(torch.float64) - wz
+        pp = pads_of(x, list(w.shape[2:]), strides, dilations, pads, auto_pad)
+        flat = [v for lo_hi in reversed(pp) for v in lo_hi]
+        xf = F.pad(xf, flat)
+        conv = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[nd]
+        return conv(xf, wf, None, strides, 0, dilations, int(group))
+
+    def qlinear_conv(x, xs, xz, w, ws, wz, ys, yz, b=None, **kw):
+        acc = conv_int(x, w, xz, wz, **kw)
+        scale = (xs.double() * ws.double()).reshape(1, -1, *([1] * (acc.dim() - 2))) if ws.numel() > 1 else xs.double() * ws.double()
+        if b is not None:
+            acc = acc + b.double().reshape(1, -1, *([1] * (acc.dim() - 2)))
+        info = torch.iinfo(yz.dtype)
+        return torch.clamp(torch.round(acc * scale / ys.double()) + yz.double(), info.min, info.max).to(yz.dtype)
+
+    def matmul_int(a, b, a_zp=None, b_zp=None, **kw):
+        af = a.to(torch.int64) - (a_zp.to(torch.int64).reshape(-1, 1) if a_zp is not None and a_zp.numel() > 1 else (a_zp.to(torch.int64) if a_zp is not None else 0))
+        bf = b.to(torch.int64) - (b_zp.to(torch.int64) if b_zp is not None else 0)
+        return (af.double() @ bf.double()).to(torch.int32)
+
+    def qlinear_matmul(a, as_, az, b, bs, bz, ys, yz, **kw):
+        acc = (a.double() - az.double()) @ (b.double() - bz.double())
+        info = torch.iinfo(yz.dtype)
+        return torch.clamp(torch.round(acc * as_.double() * bs.double() / ys.double()) + yz.double(), info.min, info.max).to(yz.dtype)
+
+    def dyn_quant(x, **kw):
+        lo, hi = min(float(x.min()), 0.0), max(float(x.max()), 0.0)
+        scale = (hi - lo) / 255.0 or 1.0
+        zp = max(0.0, min(255.0, round(-lo / scale)))                                   # Python rounds half to even, as the specification asks
+        y = torch.clamp(torch.round(x / scale) + zp, 0, 255).to(torch.uint8)
+        return y, torch.tensor(scale, dtype=torch.float32), torch.tensor(zp, dtype=torch.uint8)
+
+    def lp_pool(x, kernel_shape=None, strides=None, pads=None, p=2, auto_pad="NOTSET", dilations=None, ceil_mode=0, **kw):
+        nd = len(kernel_shape)
+        strides, dilations = list(strides or [1] * nd), list(dilations or [1] * nd)
+        pp = pads_of(x, list(kernel_shape), strides, dilations, pads, auto_pad)
+        xp = F.pad(x.abs() ** p, [v for lo_hi in reversed(pp) for v in lo_hi])
+        pool = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nd]
+        return (pool(xp, list(kernel_shape), strides, 0, bool(ceil_mode)) * float(np.prod(kernel_shape))) ** (1.0 / p)
+
+    def max_unpool(x, idx, output_shape=None, kernel_shape=None, strides=None, pads=None, **kw):
+        nd = len(kernel_shape)
+        strides = list(strides or [1] * nd)
+        pads = list(pads or [0] * (2 * nd))
+        if output_shape is not None:
+            shape = _ints(output_shape)
+        else:
+            shape = list(x.shape[:2]) + [(x.shape[2 + d] - 1) * strides[d] + kernel_shape[d] - pads[d] - pads[d + nd] for d in range(nd)]
+        out = torch.zeros(int(np.prod(shape)), dtype=x.dtype)
+        out[idx.reshape(-1).long()] = x.reshape(-1)                                      # indices are flat offsets into the whole output tensor
+        return out.reshape(shape)
+
+    def max_roi_pool(x, rois, pooled_shape=None, spatial_scale=1.0, **kw):
+        ph, pw = pooled_shape
+        out = []
+        for r in rois:
+            b = int(r[0])
+            x1, y1, x2, y2 = [int(round(float(v) * spatial_scale)) for v in r[1:]]
+            h, w = max(y2 - y1 + 1, 1), max(x2 - x1 + 1, 1)
+            cell = torch.full((x.shape[1], ph, pw), 0.0, dtype=x.dtype)
+            for i in range(ph):
+                for j in range(pw):
+                    ys, ye = y1 + int(math.floor(i * h / ph)), y1 + int(math.ceil((i + 1) * h / ph))
+                    xs, xe = x1 + int(math.floor(j * w / pw)), x1 + int(math.ceil((j + 1) * w / pw))
+                    ys, ye, xs, xe = max(ys, 0), min(ye, x.shape[2]), max(xs, 0), min(xe, x.shape[3])
+                    if ye > ys and xe > xs:
+                        cell[:, i, j] = x[b, :, ys:ye, xs:xe].amax((1, 2))
+            out.append(cell)
+        return torch.stack(out)
+
+    def grid_sample(x, grid, mode="linear", padding_mode="zeros", align_corners=0, **kw):
+        dec = lambda v: v.decode() if isinstance(v, bytes) else v
+        mode = {"linear": "bilinear", "bilinear": "bilinear", "nearest": "nearest", "cubic": "bicubic", "bicubic": "bicubic"}[dec(mode)]
+        return F.grid_sample(x, grid.to(x.dtype), mode=mode, padding_mode=dec(padding_mode), align_corners=bool(align_corners))
+
+    def col2im(cols, image_shape, block_shape, dilations=None, pads=None, strides=None, **kw):
+        img, blk = _ints(image_shape), _ints(block_shape)
+        nd = len(img)
+        if nd != 2:
+            raise NotImplementedError("Col2Im for other than two spatial axes")
+        pads = list(pads or [0] * 4)
+        if pads[0] != pads[2] or pads[1] != pads[3]:
+            raise NotImplementedError("Col2Im with different begin and end pads")
+        return F.fold(cols, img, blk, list(dilations or [1, 1]), pads[:2], list(strides or [1, 1]))
+
+    def center_crop_pad(x, shape, axes=None, **kw):
+        tgt = _ints(shape)
+        axes = list(axes) if axes is not None else list(range(x.dim()))
+        for a, t in zip(axes, tgt):
+            a = a % x.dim()
+            cur = x.shape[a]
+            if cur > t:
+                x = x.narrow(a, (cur - t) // 2, t)
+            elif cur < t:
+                lo = (t - cur) // 2
+                pad = [0, 0] * x.dim()
+                pad[2 * (x.dim() - 1 - a)], pad[2 * (x.dim() - 1 - a) + 1] = lo, t - cur - lo
+                x = F.pad(x, pad)
+        return x
+
+    def nll_loss(x, target, weight=None, ignore_index=None, reduction="mean", **kw):
+        reduction = reduction.decode() if isinstance(reduction, bytes) else reduction
+        return F.nll_loss(x, target.long(), weight, ignore_index=-100 if ignore_index is None else int(ignore_index), reduction=reduction)
+
+    def sce_loss(scores, labels, weights=None, ignore_index=None, reduction="mean", **kw):
+        reduction = reduction.decode() if isinstance(reduction, bytes) else reduction
+        logp = F.log_softmax(scores, 1)
+        return F.nll_loss(logp, labels.long(), weights, ignore_index=-100 if ignore_index is None else int(ignore_index), reduction=reduction), logp
+
+    def dft(x, dft_length=None, axis=None, inverse=0, onesided=0, **kw):
+        ax = int(axis) if axis is not None else -2
+        ax = ax % x.dim()
+        n = int(dft_length) if dft_length is not None else None
+        z = torch.view_as_complex(x.contiguous()) if x.shape[-1] == 2 else x[..., 0].to(torch.complex64 if x.dtype != torch.float64 else torch.complex128)
+        if inverse:
+            y = torch.fft.ifft(z, n=n, dim=ax)
+        elif onesided:
+            if x.shape[-1] != 1:
+                raise ValueError("a one-sided DFT needs a real input")
+            y = torch.fft.rfft(x[..., 0], n=n, dim=ax)
+        else:
+            y = torch.fft.fft(z, n=n, dim=ax)
+        return torch.view_as_real(y)
+
+    def stft(signal, frame_step, window=None, frame_length=None, onesided=1, **kw):
+        step = int(frame_step)
+        n = int(frame_length) if frame_length is not None else window.numel()
+        sig = signal[..., 0] if signal.shape[-1] == 1 else torch.view_as_complex(signal.contiguous())
+        frames = sig.unfold(1, n, step)                                                  # [batch, frames, n]
+        if window is not None:
+            frames = frames * window.to(frames.dtype if not frames.is_complex() else window.dtype)
+        y = torch.fft.rfft(frames, dim=-1) if onesided and not frames.is_complex() else torch.fft.fft(frames, dim=-1)
+        return torch.view_as_real(y)
+
+    def mel_weights(num_mel_bins, dft_length, sample_rate, lower_edge_hertz, upper_edge_hertz, output_datatype=1, **kw):
+        nb, n, sr = int(num_mel_bins), int(dft_length), int(sample_rate)
+        lo, hi = float(lower_edge_hertz), float(upper_edge_hertz)
+        mel = lambda f: 2595.0 * math.log10(1.0 + f / 700.0)
+        pts = [lo_m for lo_m in np.linspace(mel(lo), mel(hi), nb + 2)]
+        bins = [int(math.floor((n + 1) * (700.0 * (10 ** (m / 2595.0) - 1.0)) / sr)) for m in pts]
+        out = torch.zeros(n // 2 + 1, nb, dtype=torch.float64)
+        for i in range(nb):
+            l, c, r = bins[i], bins[i + 1], bins[i + 2]
+            if c == l:
+                out[c, i] = 1.0
+            else:
+                for j in range(l, c + 1):
+                    out[j, i] = (j - l) / (c - l)
+            for j in range(c + 1, r):
+                out[j, i] = (r - j) / (r - c)
+        return out.to(TORCH_DT[int(output_datatype)])
+
+    def rnd(kind, like):
+        def f(*xs, shape=None, dtype=None, mean=0.0, scale=1.0, low=0.0, high=1.0, seed=None, **kw):
+            shp = list(xs[0].shape) if like else [int(v) for v in shape]
+            dt = TORCH_DT[int(dtype)] if dtype is not None else (xs[0].dtype if like and xs[0].dtype.is_floating_point else torch.float32)
+            gen = torch.Generator().manual_seed(int(seed)) if seed is not None else None
+            if kind == "normal":
+                return (torch.randn(shp, generator=gen) * scale + mean).to(dt)
+            return (torch.rand(shp, generator=gen) * (high - low) + low).to(dt)
+        return f
+
+    return {
+        "BitwiseAnd": (lambda a, b, **k: a & b, 1), "BitwiseOr": (lambda a, b, **k: a | b, 1), "BitwiseXor": (lambda a, b, **k: a ^ b, 1),
+        "BitwiseNot": (lambda a, **k: ~a, 1),
+        "CastLike": (lambda x, like, **k: x.to(like.dtype), 1),
+        "HannWindow": (window("hann"), 1), "HammingWindow": (window("hamming"), 1), "BlackmanWindow": (window("blackman"), 1),
+        "ConvInteger": (lambda x, w, xz=None, wz=None, **k: conv_int(x, w, xz, wz, **k).to(torch.int32), 1),
+        "MatMulInteger": (matmul_int, 1), "QLinearConv": (qlinear_conv, 1), "QLinearMatMul": (qlinear_matmul, 1),
+        "DynamicQuantizeLinear": (dyn_quant, 3),
+        "LpPool": (lp_pool, 1), "MaxUnpool": (max_unpool, 1), "MaxRoiPool": (max_roi_pool, 1), "GridSample": (grid_sample, 1),
+        "Col2Im": (col2im, 1), "CenterCropPad": (center_crop_pad, 1),
+        "NegativeLogLikelihoodLoss": (nll_loss, 1), "SoftmaxCrossEntropyLoss": (sce_loss, -1),
+        "DFT": (dft, 1), "STFT": (stft, 1), "MelWeightMatrix": (mel_weights, 1),
+        "RandomNormal": (rnd("normal", False), 1), "RandomNormalLike": (rnd("normal", True), 1),
+        "RandomUniform": (rnd("uniform", False), 1), "RandomUniformLike": (rnd("uniform", True), 1),
+        "Bernoulli": (lambda x, dtype=None, seed=None, **k: torch.bernoulli(x.float(), generator=torch.Generator().manual_seed(int(seed)) if seed is not None else None)
+                      .to(TORCH_DT[int(dtype)] if dtype is not None else x.dtype), 1),
+        "Multinomial": (lambda x, sample_size=1, dtype=6, seed=None, **k: torch.multinomial(
+            x.float().softmax(-1), int(sample_size), True, generator=torch.Generator().manual_seed(int(seed)) if seed is not None else None).to(TORCH_DT[int(dtype)]), 1),
+    }
 
 
 def _register_onnx_ops():

@@ -1,5 +1,6 @@
 """ONNX import: models are encoded with the bundled protobuf writer (no onnx package) and checked against torch."""
 import numpy as np
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -241,3 +242,78 @@ def test_remaining_standard_operators_by_their_definitions():
     # bin centres (1, 1), (1, 3), (3, 1), (3, 3) in input coordinates fall exactly on pixels
     ref = torch.tensor([[img[0, 0, 1, 1], img[0, 0, 1, 3]], [img[0, 0, 3, 1], img[0, 0, 3, 3]]])
     torch.testing.assert_close(ra[0, 0], ref)
+
+
+def test_second_operator_table_by_definitions():
+    """Integer / quantised linear algebra, windows and spectral ops, unpooling, losses: each against the operator's definition in the
+    ONNX specification written out in plain torch / numpy."""
+    import math
+    import torch.nn.functional as F
+    from deeplearning4j_b200.importers.onnx_import import _onnx_ops
+    T = {k: v[0] for k, v in _onnx_ops().items()}
+    g = torch.Generator().manual_seed(3)
+
+    w = T["HannWindow"](torch.tensor(8))
+    assert torch.allclose(w, torch.hann_window(8, periodic=True)) and torch.allclose(T["HannWindow"](torch.tensor(8), periodic=0), torch.hann_window(8, periodic=False))
+    assert torch.allclose(T["HammingWindow"](torch.tensor(6), periodic=0), torch.tensor([25 / 46 - 21 / 46 * math.cos(2 * math.pi * k / 5) for k in range(6)]))
+    assert torch.allclose(T["BlackmanWindow"](torch.tensor(7)), torch.blackman_window(7, periodic=True), atol=1e-6)
+    assert T["BitwiseNot"](torch.tensor([0, 5], dtype=torch.uint8)).tolist() == [255, 250] and T["CastLike"](torch.tensor([1.7]), torch.tensor([1])).dtype == torch.int64
+
+    x = torch.randint(0, 255, (1, 2, 5, 5), generator=g, dtype=torch.uint8)
+    wt = torch.randint(-100, 100, (3, 2, 3, 3), generator=g, dtype=torch.int8)
+    ref = F.conv2d(x.double() - 7, wt.double(), padding=1)
+    assert torch.equal(T["ConvInteger"](x, wt, torch.tensor(7, dtype=torch.uint8), pads=[1, 1, 1, 1]), ref.to(torch.int32))
+    a = torch.randint(0, 255, (4, 6), generator=g, dtype=torch.uint8)
+    b = torch.randint(-128, 127, (6, 3), generator=g, dtype=torch.int8)
+    assert torch.equal(T["MatMulInteger"](a, b, torch.tensor(12, dtype=torch.uint8)), ((a.long() - 12) @ b.long()).to(torch.int32))
+    q = T["QLinearMatMul"](a, torch.tensor(0.1), torch.tensor(12, dtype=torch.uint8), b, torch.tensor(0.05), torch.tensor(0, dtype=torch.int8),
+                           torch.tensor(2.0), torch.tensor(100, dtype=torch.uint8))
+    assert torch.equal(q, torch.clamp(torch.round(((a.double() - 12) @ b.double()) * 0.1 * 0.05 / 2.0) + 100, 0, 255).to(torch.uint8))
+    qc = T["QLinearConv"](x, torch.tensor(0.02), torch.tensor(7, dtype=torch.uint8), wt, torch.tensor(0.01), torch.tensor(0, dtype=torch.int8),
+                          torch.tensor(0.5), torch.tensor(3, dtype=torch.uint8), torch.tensor([5, -5, 0], dtype=torch.int32), pads=[1, 1, 1, 1])
+    refq = torch.clamp(torch.round((ref + torch.tensor([5.0, -5, 0]).reshape(1, 3, 1, 1)) * 0.02 * 0.01 / 0.5) + 3, 0, 255).to(torch.uint8)
+    assert torch.equal(qc, refq)
+    y, sc, zp = T["DynamicQuantizeLinear"](torch.tensor([0.0, 2.0, -3.0, -2.5, 1.34, 0.5]))
+    assert float(sc) == pytest.approx(5.0 / 255) and int(zp) == 153 and y.tolist() == [153, 255, 0, 26, 221, 179]      # the specification's own example
+
+    img = torch.randn(2, 3, 6, 6, generator=g)
+    lp = T["LpPool"](img, kernel_shape=[2, 2], strides=[2, 2], p=3)
+    assert torch.allclose(lp, (F.avg_pool2d(img.abs() ** 3, 2) * 4) ** (1 / 3), atol=1e-5)
+    pooled, idx = F.max_pool2d(img, 2, return_indices=True)
+    flat = idx + (torch.arange(2 * 3).reshape(2, 3, 1, 1) * 36)                         # ONNX indices address the whole tensor
+    un = T["MaxUnpool"](pooled, flat, kernel_shape=[2, 2], strides=[2, 2])
+    assert torch.equal(un, F.max_unpool2d(pooled, idx, 2))
+    rp = T["MaxRoiPool"](img, torch.tensor([[1.0, 0, 0, 3, 3], [0.0, 2, 2, 5, 5]]), pooled_shape=[2, 2], spatial_scale=1.0)
+    assert torch.equal(rp[0], F.max_pool2d(img[1, :, 0:4, 0:4], 2)) and torch.equal(rp[1], F.max_pool2d(img[0, :, 2:6, 2:6], 2))
+    grid = torch.rand(2, 4, 4, 2, generator=g) * 2 - 1
+    assert torch.allclose(T["GridSample"](img, grid, mode=b"linear", align_corners=1), F.grid_sample(img, grid, align_corners=True))
+    cols = F.unfold(img, (2, 2), stride=2)
+    assert torch.equal(T["Col2Im"](cols, torch.tensor([6, 6]), torch.tensor([2, 2]), strides=[2, 2]), img)
+    cc = T["CenterCropPad"](img, torch.tensor([4, 8]), axes=[2, 3])
+    assert cc.shape == (2, 3, 4, 8) and torch.equal(cc[:, :, :, 1:7], img[:, :, 1:5, :]) and cc[:, :, :, 0].abs().sum() == 0
+
+    logits = torch.randn(5, 4, generator=g)
+    labels = torch.tensor([0, 3, 1, 1, 2])
+    loss, logp = T["SoftmaxCrossEntropyLoss"](logits, labels, reduction=b"mean")
+    assert torch.allclose(loss, F.cross_entropy(logits, labels)) and torch.allclose(logp, logits.log_softmax(1))
+    wts = torch.tensor([1.0, 2.0, 0.5, 1.5])
+    assert torch.allclose(T["NegativeLogLikelihoodLoss"](logits.log_softmax(1), labels, wts, reduction=b"sum", ignore_index=1),
+                          F.nll_loss(logits.log_softmax(1), labels, wts, ignore_index=1, reduction="sum"))
+
+    sig = torch.randn(2, 16, 1, generator=g)
+    assert torch.allclose(T["DFT"](sig, axis=1), torch.view_as_real(torch.fft.fft(sig[..., 0], dim=1)), atol=1e-5)
+    assert torch.allclose(T["DFT"](sig, axis=1, onesided=1), torch.view_as_real(torch.fft.rfft(sig[..., 0], dim=1)), atol=1e-5)
+    spec = T["DFT"](sig, axis=1)
+    assert torch.allclose(T["DFT"](spec, axis=1, inverse=1)[..., 0], sig[..., 0], atol=1e-5)
+    st = T["STFT"](sig, torch.tensor(4), torch.hann_window(8), torch.tensor(8))
+    ref = torch.stft(sig[..., 0], 8, 4, window=torch.hann_window(8), center=False, return_complex=True).transpose(1, 2)
+    assert torch.allclose(st, torch.view_as_real(ref), atol=1e-5)
+    mw = T["MelWeightMatrix"](torch.tensor(8), torch.tensor(16), torch.tensor(8192), torch.tensor(0.0), torch.tensor(4096.0))
+    assert mw.shape == (9, 8) and float(mw.max()) == 1.0 and float(mw.min()) == 0.0 and bool((mw.sum(0) > 0).all())
+
+    r1 = T["RandomNormal"](shape=[1000], mean=2.0, scale=0.5, seed=1.0)
+    assert r1.shape == (1000,) and abs(float(r1.mean()) - 2.0) < 0.1 and torch.equal(r1, T["RandomNormal"](shape=[1000], mean=2.0, scale=0.5, seed=1.0))
+    r2 = T["RandomUniformLike"](torch.zeros(3, 4, dtype=torch.float64), low=2.0, high=3.0)
+    assert r2.dtype == torch.float64 and float(r2.min()) >= 2.0 and float(r2.max()) < 3.0
+    assert set(T["Bernoulli"](torch.full((50,), 0.5), seed=2.0).tolist()) <= {0.0, 1.0}
+    assert T["Multinomial"](torch.tensor([[0.0, 50.0, 0.0]]), sample_size=5).tolist() == [[1] * 5]
