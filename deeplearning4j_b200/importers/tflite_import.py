@@ -101,6 +101,10 @@ BUILTIN = {
     96: "RANGE", 97: "RESIZE_NEAREST_NEIGHBOR", 98: "LEAKY_RELU", 99: "SQUARED_DIFFERENCE", 100: "MIRROR_PAD", 101: "ABS",
     102: "SPLIT_V", 104: "CEIL", 105: "REVERSE_V2", 106: "ADD_N", 107: "GATHER_ND", 108: "COS", 110: "RANK", 111: "ELU",
     116: "ROUND", 117: "HARD_SWISH", 123: "SELECT_V2", 126: "BATCH_MATMUL", 128: "CUMSUM", 150: "GELU",
+    12: "L2_POOL_2D", 37: "BATCH_TO_SPACE_ND", 38: "SPACE_TO_BATCH_ND", 48: "TOPK_V2", 68: "SPARSE_TO_DENSE", 91: "REDUCE_ANY",
+    109: "WHERE", 113: "MATRIX_DIAG", 115: "MATRIX_SET_DIAG", 122: "SCATTER_ND", 125: "SEGMENT_SUM", 130: "BROADCAST_TO",
+    140: "REDUCE_ALL", 145: "BROADCAST_ARGS", 152: "RELU_0_TO_1", 153: "UNSORTED_SEGMENT_PROD", 154: "UNSORTED_SEGMENT_MAX",
+    155: "UNSORTED_SEGMENT_SUM", 156: "ATAN2", 157: "UNSORTED_SEGMENT_MIN", 158: "SIGN",
 }
 BUILTIN_CODES = {v: k for k, v in BUILTIN.items()}
 
@@ -480,6 +484,112 @@ def _tflite_ops():
         for v in xs[1:]:
             out = out + v
         return out
+
+    @reg("L2_POOL_2D")
+    def l2_pool(x, padding=0, stride_w=1, stride_h=1, filter_width=1, filter_height=1, fused_activation_function=0, **kw):
+        return avg_pool(x * x, padding, stride_w, stride_h, filter_width, filter_height, 0).sqrt() if not fused_activation_function else \
+            _fused(avg_pool(x * x, padding, stride_w, stride_h, filter_width, filter_height, 0).sqrt(), fused_activation_function)
+
+    @reg("SPACE_TO_BATCH_ND")
+    def space_to_batch(x, block_shape, paddings, **kw):
+        bs, pd = _ints(block_shape), paddings.reshape(-1, 2).tolist()
+        m = len(bs)
+        flat = []
+        for d in reversed(range(x.dim())):
+            lo, hi = (pd[d - 1] if 1 <= d <= m else (0, 0))
+            flat += [int(lo), int(hi)]
+        x = F.pad(x, flat)
+        n, rest = x.shape[0], list(x.shape[1 + m:])
+        shp = [n]
+        for i in range(m):
+            shp += [x.shape[1 + i] // bs[i], bs[i]]
+        x = x.reshape(shp + rest).permute([2 + 2 * i for i in range(m)] + [0] + [1 + 2 * i for i in range(m)] + list(range(1 + 2 * m, 1 + 2 * m + len(rest))))
+        prod = 1
+        for b in bs:
+            prod *= b
+        return x.reshape([n * prod] + [shp[1 + 2 * i] for i in range(m)] + rest)
+
+    @reg("BATCH_TO_SPACE_ND")
+    def batch_to_space(x, block_shape, crops, **kw):
+        bs, cr = _ints(block_shape), crops.reshape(-1, 2).tolist()
+        m = len(bs)
+        prod = 1
+        for b in bs:
+            prod *= b
+        n, rest = x.shape[0] // prod, list(x.shape[1 + m:])
+        x = x.reshape(bs + [n] + list(x.shape[1:1 + m]) + rest)
+        perm = [m]
+        for i in range(m):
+            perm += [m + 1 + i, i]
+        x = x.permute(perm + list(range(2 * m + 1, 2 * m + 1 + len(rest))))
+        x = x.reshape([n] + [x.shape[1 + 2 * i] * x.shape[2 + 2 * i] for i in range(m)] + rest)
+        return x[tuple([slice(None)] + [slice(int(cr[i][0]), x.shape[1 + i] - int(cr[i][1])) for i in range(m)])]
+
+    @reg("TOPK_V2", n_out=2)
+    def topk(x, k, **kw):
+        v, i = torch.topk(x, _ints(k)[0], dim=-1)
+        return v, i.to(torch.int32)
+
+    @reg("SPARSE_TO_DENSE")
+    def sparse_to_dense(indices, output_shape, values, default_value, **kw):
+        out = torch.full(_ints(output_shape), default_value.item(), dtype=values.dtype)
+        idx = indices.long().reshape(-1, 1) if indices.dim() < 2 else indices.long()
+        out[tuple(idx[:, j] for j in range(idx.shape[1]))] = values if values.dim() else values.expand(idx.shape[0])
+        return out
+
+    reducer("REDUCE_ANY", lambda x, ax, k: x.bool().sum(ax, keepdim=k) > 0)
+    reducer("REDUCE_ALL", lambda x, ax, k: (~x.bool()).sum(ax, keepdim=k) == 0)
+
+    @reg("WHERE")
+    def where(c, a=None, b=None, **kw): return torch.nonzero(c).to(torch.int64) if a is None else torch.where(c.bool(), a, b)
+
+    @reg("MATRIX_DIAG")
+    def matrix_diag(d, **kw): return torch.diag_embed(d)
+
+    @reg("MATRIX_SET_DIAG")
+    def matrix_set_diag(x, d, **kw):
+        out = x.clone()
+        out.diagonal(0, -2, -1).copy_(d)
+        return out
+
+    @reg("SCATTER_ND")
+    def scatter_nd(indices, updates, shape, **kw):
+        out = torch.zeros(_ints(shape), dtype=updates.dtype)
+        return out.index_put(tuple(indices[..., j].long() for j in range(indices.shape[-1])), updates, accumulate=True)
+
+    def segment(name, kind, sorted_ids):
+        @reg(name)
+        def f(data, ids, num=None, **kw):
+            ids = ids.long()
+            n = _ints(num)[0] if num is not None else int(ids.max()) + 1
+            tail = list(data.shape[ids.dim():])
+            flat, idx = data.reshape(-1, *tail), ids.reshape(-1)
+            keep = idx >= 0
+            flat, idx = flat[keep], idx[keep]
+            ix = idx.reshape(-1, *([1] * len(tail))).expand_as(flat)
+            if kind == "sum":
+                return torch.zeros([n] + tail, dtype=data.dtype).scatter_add(0, ix, flat)
+            if kind == "prod":
+                return torch.ones([n] + tail, dtype=data.dtype).scatter_reduce(0, ix, flat, "prod")
+            lim = torch.finfo(data.dtype) if data.dtype.is_floating_point else torch.iinfo(data.dtype)
+            return torch.full([n] + tail, lim.min if kind == "max" else lim.max, dtype=data.dtype).scatter_reduce(0, ix, flat, "amax" if kind == "max" else "amin")
+    segment("SEGMENT_SUM", "sum", True); segment("UNSORTED_SEGMENT_SUM", "sum", False); segment("UNSORTED_SEGMENT_PROD", "prod", False)
+    segment("UNSORTED_SEGMENT_MAX", "max", False); segment("UNSORTED_SEGMENT_MIN", "min", False)
+
+    @reg("BROADCAST_TO")
+    def broadcast_to(x, shape, **kw): return x.expand(_ints(shape)).contiguous()
+
+    @reg("BROADCAST_ARGS")
+    def broadcast_args(a, b, **kw): return torch.tensor(list(torch.broadcast_shapes(tuple(_ints(a)), tuple(_ints(b)))), dtype=a.dtype)
+
+    @reg("RELU_0_TO_1")
+    def relu01(x, **kw): return x.clamp(0, 1)
+
+    @reg("ATAN2")
+    def atan2(y, x, **kw): return torch.atan2(y, x)
+
+    @reg("SIGN")
+    def sign(x, **kw): return torch.sign(x)
 
     return ops
 

@@ -205,3 +205,34 @@ def test_runner_and_errors(tmp_path):
     with pytest.raises(NotImplementedError, match="builtin#27"):
         importTFLite(bad.build([0], [0]))
     assert len(supportedOps()) >= 90
+
+
+def test_further_builtin_operators_by_definitions():
+    """Builtin operators added after the first table (space / batch, segment, scatter, top-k, ...), each against its definition."""
+    import torch
+    from deeplearning4j_b200.importers.tflite_import import _tflite_ops, supportedOps
+    T = {k: v[0] for k, v in _tflite_ops().items()}
+    assert len(supportedOps()) >= 114
+    x = torch.arange(1 * 4 * 6 * 2, dtype=torch.float32).reshape(1, 4, 6, 2)
+    zero = torch.zeros(2, 2, dtype=torch.int64)
+    y = T["SPACE_TO_BATCH_ND"](x, torch.tensor([2, 2]), zero)
+    assert torch.equal(y[3], x[0, 1::2, 1::2]) and torch.equal(T["BATCH_TO_SPACE_ND"](y, torch.tensor([2, 2]), zero), x)
+    ref = torch.nn.functional.avg_pool2d((x * x).permute(0, 3, 1, 2), 2).sqrt().permute(0, 2, 3, 1)
+    assert torch.allclose(T["L2_POOL_2D"](x, padding=1, stride_w=2, stride_h=2, filter_width=2, filter_height=2), ref)
+    v, i = T["TOPK_V2"](torch.tensor([[1.0, 5, 3]]), torch.tensor(2))
+    assert v.tolist() == [[5, 3]] and i.tolist() == [[1, 2]]
+    assert T["SPARSE_TO_DENSE"](torch.tensor([[0, 1], [1, 0]]), torch.tensor([2, 2]), torch.tensor([5.0, 6]), torch.tensor(-1.0)).tolist() == [[-1, 5], [6, -1]]
+    assert T["REDUCE_ANY"](torch.tensor([[True, False], [False, False]]), torch.tensor([1])).tolist() == [True, False]
+    assert T["REDUCE_ALL"](torch.tensor([[True, True], [True, False]]), torch.tensor([1])).tolist() == [True, False]
+    assert T["WHERE"](torch.tensor([True, False, True])).tolist() == [[0], [2]]
+    assert T["MATRIX_DIAG"](torch.tensor([1.0, 2])).tolist() == [[1, 0], [0, 2]] and T["MATRIX_SET_DIAG"](torch.zeros(2, 2), torch.tensor([1.0, 2])).tolist() == [[1, 0], [0, 2]]
+    assert T["SCATTER_ND"](torch.tensor([[1], [1]]), torch.tensor([2.0, 3]), torch.tensor([3])).tolist() == [0, 5, 0]
+    d = torch.tensor([[1.0, 2], [3, 4], [5, 6]])
+    assert T["SEGMENT_SUM"](d, torch.tensor([0, 0, 1])).tolist() == [[4, 6], [5, 6]]
+    assert T["UNSORTED_SEGMENT_SUM"](d, torch.tensor([1, -1, 1]), torch.tensor(2)).tolist() == [[0, 0], [6, 8]]
+    assert T["UNSORTED_SEGMENT_MAX"](d, torch.tensor([1, 0, 1]), torch.tensor(2)).tolist() == [[3, 4], [5, 6]]
+    assert T["UNSORTED_SEGMENT_MIN"](d, torch.tensor([1, 0, 1]), torch.tensor(2)).tolist() == [[3, 4], [1, 2]]
+    assert T["UNSORTED_SEGMENT_PROD"](d, torch.tensor([1, 0, 1]), torch.tensor(2)).tolist() == [[3, 4], [5, 12]]
+    assert T["BROADCAST_ARGS"](torch.tensor([3, 1]), torch.tensor([1, 4])).tolist() == [3, 4] and T["BROADCAST_TO"](torch.tensor([1.0, 2]), torch.tensor([2, 2])).tolist() == [[1, 2], [1, 2]]
+    assert T["RELU_0_TO_1"](torch.tensor([-1.0, 0.5, 2])).tolist() == [0, 0.5, 1] and T["SIGN"](torch.tensor([-2.0, 0, 3])).tolist() == [-1, 0, 1]
+    assert torch.allclose(T["ATAN2"](torch.tensor([1.0]), torch.tensor([-1.0])), torch.tensor([3 * 3.141592653589793 / 4]))
